@@ -1,0 +1,19 @@
+"""rwkv7_b200: B200 (sm_100a) kernels for the RWKV-7 inference hot path behind the operator
+contract of rwkv-rs/hf-adapter (package ``rwkv7_hf``).  Importing this package loads the CUDA
+library; there is no CPU or PyTorch fallback."""
+from . import _lib  # noqa: F401  (fails loudly when the library is missing)
+from .cache import NativeRWKV7Cache
+from .lora import dense_small, fused_wa_lora, fused_wag_lora, fused_wavg_lora
+from .model import DecodeGraph, NativeRWKV7Config, RWKV7ForCausalLM
+from .norm_mix import (fused_attn_norm_mix6_decode, fused_attn_sequence_shift_mix, fused_attn_shift_mix,
+                       fused_ffn_add_norm_mix_decode, fused_ffn_sequence_shift_mix, layer_norm)
+from .prep import fused_attn_output_prepare, fused_prefill_state_prep
+from .quant import (A8W8Linear, MM4Linear, MM8Linear, a8w8_linear, dynamic_a8_quant, int8_mm, quantize_model,
+                    quantize_w4_groupwise, quantize_w8_row, quantize_weight_per_channel_int8, w4_dequant,
+                    w4_groupwise_linear, w8_dequant, w8_linear)
+from .recurrent import (dplr_chunk_scan, fused_recurrent_output_prepare, fused_recurrent_output_prepare_raw,
+                        fused_recurrent_scan, fused_recurrent_scan_clampw, fused_recurrent_scan_output_prepare,
+                        fused_recurrent_update, self_chunk_rwkv7)
+
+NativeRWKV7ForCausalLM = RWKV7ForCausalLM
+__version__ = "0.1.0"

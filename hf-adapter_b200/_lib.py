@@ -1,0 +1,83 @@
+"""ctypes binding of librwkv7_b200.so (the C ABI declared in include/rwkv7_b200.h).
+
+There is no fallback: if the library is missing the import of this module fails, and
+every wrapper raises on a non-zero status code.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_float, c_int, c_int64, c_void_p
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "librwkv7_b200.so")
+
+OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_ALIGN, ERR_CUDA, ERR_WORKSPACE = 0, -1, -2, -3, -4, -5
+F16, BF16, F32 = 0, 1, 2
+EPI_NONE, EPI_RELU2, EPI_ADD = 0, 1, 2
+
+P, I, F, L = c_void_p, c_int, c_float, c_int64
+PP = ctypes.POINTER(c_void_p)
+
+# name -> (restype, argtypes); must list every symbol of include/rwkv7_b200.h
+SIGNATURES = {
+    "rwkv7_abi_version": (I, []),
+    "rwkv7_last_error": (ctypes.c_char_p, []),
+    "rwkv7_wkv7_update": (I, [P] * 9 + [I, I, I, I, I, P]),
+    "rwkv7_wkv7_output_prepare": (I, [P] * 13 + [I, I, I, F, I, I, P]),
+    "rwkv7_wkv7_output_prepare_raw": (I, [P] * 14 + [P, P, I, P, P, P, I, P, I, I, I, F, I, P]),
+    "rwkv7_wkv7_scan": (I, [P] * 13 + [F, I, I, I, I, I, I, P]),
+    "rwkv7_wkv7_chunk_scan": (I, [P] * 9 + [I, I, I, I, I, I, I, P]),
+    "rwkv7_attn_norm_mix6": (I, [P, P, P, P, PP, PP, I, I, F, I, P]),
+    "rwkv7_ffn_add_norm_mix": (I, [P] * 8 + [I, I, F, I, P]),
+    "rwkv7_layer_norm": (I, [P] * 4 + [I, I, F, I, P]),
+    "rwkv7_seq_shift_mix": (I, [P, P, PP, PP, P, I, I, I, I, I, P]),
+    "rwkv7_dense_small": (I, [P] * 4 + [I, I, I, I, I, I, P]),
+    "rwkv7_prefill_state_prep": (I, [P] * 12 + [I, I, I, I, I, I, I, P]),
+    "rwkv7_attn_output_prepare": (I, [P] * 9 + [I, I, I, F, I, P]),
+    "rwkv7_w4g_gemv": (I, [P] * 6 + [I, I, I, I, I, I, P]),
+    "rwkv7_w8_gemv": (I, [P] * 5 + [I, I, I, I, I, P]),
+    "rwkv7_w4g_dequant": (I, [P] * 4 + [I, I, I, I, P]),
+    "rwkv7_w8_dequant": (I, [P] * 3 + [I, I, I, P]),
+    "rwkv7_a8_quant": (I, [P, P, P, I, I, I, P]),
+    "rwkv7_i8_gemm": (I, [P, P, P, I, I, I, P]),
+    "rwkv7_a8w8_dequant": (I, [P] * 6 + [I, I, I, P]),
+    "rwkv7_a8w8_workspace_bytes": (L, [I, I, I]),
+    "rwkv7_a8w8_linear": (I, [P] * 7 + [L, I, I, I, I, P]),
+}
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        f"{LIB_PATH} is missing: build it with `python hf-adapter_b200/build.py` "
+        "(this package has no CPU or PyTorch fallback)")
+
+lib = ctypes.CDLL(LIB_PATH)
+for _name, (_res, _args) in SIGNATURES.items():
+    _fn = getattr(lib, _name)  # AttributeError here = the library does not export a declared symbol
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+
+def last_error() -> str:
+    return lib.rwkv7_last_error().decode("utf-8", "replace")
+
+
+LAUNCHES = 0  # kernels launched through this binding (bench.py reports it as gpu_launches)
+
+
+def check(status: int, what: str, kernels: int = 1) -> None:
+    """Map a status code to the exception class the reference raises for the same mistake:
+    shape/dtype problems are ValueError (rwkv7_hf/fused_recurrent_update.py:993-1014), the rest RuntimeError."""
+    if status == OK:
+        global LAUNCHES
+        LAUNCHES += kernels
+        return
+    msg = f"{what}: {last_error()} (status {status})"
+    if status in (ERR_INVALID, ERR_UNSUPPORTED, ERR_ALIGN, ERR_WORKSPACE):
+        raise ValueError(msg)
+    raise RuntimeError(msg)
+
+
+def ptr_array(ptrs):
+    arr = (c_void_p * len(ptrs))(*ptrs)
+    return ctypes.cast(arr, PP), arr

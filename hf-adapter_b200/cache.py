@@ -1,0 +1,127 @@
+"""Recurrent cache with the reference's layout and methods (rwkv7_hf/model_cache.py:48-465):
+``state`` list[L] of ``[B,H,N,N]`` fp32, ``xpa`` / ``xpf`` list[L] of ``[B,D]`` (attention / FFN
+token-shift states, the NORMALISED previous inputs), ``v_first [B,H*N]``, plus ``seen_tokens``.
+Iterable as the 4-tuple ``(state, xpa, xpf, v_first)``."""
+from __future__ import annotations
+
+import torch
+
+
+class NativeRWKV7Cache:
+    is_compileable = True
+
+    def __init__(self, state=None, xpa=None, xpf=None, v_first=None, seen_tokens: int = 0):
+        self._state, self._xpa, self._xpf, self._v_first = state, xpa, xpf, v_first
+        self._seen_tokens = int(seen_tokens)
+        self._graph_owner = None  # decode-graph runner whose static buffers these tensors are, if any
+
+    # -- tuple protocol ---------------------------------------------------
+    def __iter__(self):
+        return iter((self._state, self._xpa, self._xpf, self._v_first))
+
+    def __len__(self):
+        return 4
+
+    def __getitem__(self, i):
+        return (self._state, self._xpa, self._xpf, self._v_first)[i]
+
+    @classmethod
+    def allocate(cls, num_layers, batch, hidden, heads, head_dim, device, dtype):
+        """Zero state (rwkv7_hf/native.py:283-295)."""
+        z = lambda *s, dt=dtype: torch.zeros(*s, device=device, dtype=dt)
+        return cls([z(batch, heads, head_dim, head_dim, dt=torch.float32) for _ in range(num_layers)],
+                   [z(batch, hidden) for _ in range(num_layers)], [z(batch, hidden) for _ in range(num_layers)],
+                   z(batch, heads * head_dim), 0)
+
+    # -- HF cache contract ---------------------------------------------------
+    def get_seq_length(self, layer_idx: int = 0) -> int:
+        return self._seen_tokens
+
+    @property
+    def seen_tokens(self) -> int:
+        return self._seen_tokens
+
+    def get_max_cache_shape(self):
+        return None
+
+    def get_batch_size(self):
+        if self._state:
+            return int(self._state[0].shape[0])
+        if self._v_first is not None:
+            return int(self._v_first.shape[0])
+        return None
+
+    def _is_initialized(self, layer_idx=None) -> bool:
+        return bool(self._state) and self._v_first is not None
+
+    def has_previous_state(self, layer_idx=None) -> bool:
+        return self._is_initialized(layer_idx) and self._seen_tokens > 0
+
+    def _map(self, fn, *, inplace):
+        ml = lambda vs: None if vs is None else [fn(v) for v in vs]
+        state, xpa, xpf = ml(self._state), ml(self._xpa), ml(self._xpf)
+        vf = None if self._v_first is None else fn(self._v_first)
+        if inplace:
+            self._state, self._xpa, self._xpf, self._v_first = state, xpa, xpf, vf
+            self._graph_owner = None
+            return self
+        return NativeRWKV7Cache(state, xpa, xpf, vf, self._seen_tokens)
+
+    def clone(self):
+        return self._map(lambda v: v.clone(), inplace=False)
+
+    def detach(self, *, inplace: bool = True):
+        return self._map(lambda v: v.detach(), inplace=inplace)
+
+    def to(self, *args, copy: bool = False, **kwargs):
+        def move(v):
+            if v.dtype == torch.float32 and ("dtype" in kwargs or any(isinstance(a, torch.dtype) for a in args)):
+                # the fp32 recurrent state keeps its dtype; only the device moves
+                dev = kwargs.get("device", next((a for a in args if not isinstance(a, torch.dtype)), v.device))
+                return v.to(device=dev, copy=copy)
+            return v.to(*args, copy=copy, **kwargs)
+        return self._map(move, inplace=False)
+
+    def reset(self) -> None:
+        for vs in (self._state, self._xpa, self._xpf):
+            for v in vs or ():
+                v.zero_()
+        if self._v_first is not None:
+            self._v_first.zero_()
+        self._seen_tokens = 0
+
+    def select_batch(self, indices, *, inplace: bool = True):
+        return self._map(lambda v: v.index_select(0, indices.to(v.device)), inplace=inplace)
+
+    batch_select = select_batch
+    compact = select_batch
+
+    def batch_select_indices(self, indices):
+        return self.select_batch(indices, inplace=True)
+
+    def reorder_cache(self, beam_idx):
+        return self.select_batch(beam_idx, inplace=True)
+
+    def batch_repeat_interleave(self, repeats: int):
+        return self._map(lambda v: v.repeat_interleave(int(repeats), dim=0), inplace=True)
+
+    def crop(self, max_length: int):
+        """A recurrent state cannot be rolled back to a shorter positive prefix
+        (rwkv7_hf/model_cache.py:368-380): only no-op crops and a crop to zero are possible."""
+        if max_length < 0:
+            max_length = self._seen_tokens + max_length
+        if max_length >= self._seen_tokens:
+            return self
+        if max_length == 0:
+            self.reset()
+            return self
+        raise ValueError("a recurrent RWKV-7 cache cannot be cropped to a positive prefix")
+
+    @classmethod
+    def from_legacy_cache(cls, legacy, seen_tokens: int = 0):
+        if legacy is None:
+            return cls(seen_tokens=seen_tokens)
+        if isinstance(legacy, cls):
+            return legacy
+        state, xpa, xpf, v_first = legacy
+        return cls(state, xpa, xpf, v_first, seen_tokens=seen_tokens)

@@ -1,0 +1,272 @@
+// LayerNorm + token-shift mixing kernels (memory-bound, one CTA per row).
+// Each row is read once into registers (128-bit loads), normalised in fp32 with a
+// centred two-pass variance, and every consumer of the normalised row (the six
+// time-mix streams, the shift state) is written from registers in the same pass.
+#include "common.cuh"
+
+namespace rwkv7 {
+
+constexpr int kNMThreads = 256;
+constexpr int kNMMaxVec = 4;  // 8-element vectors per thread -> D <= 8192
+
+template <typename T>
+struct RowStats {
+    float x[kNMMaxVec][8];
+    float mean, rstd;
+};
+
+// loads row (optionally + add row) into registers, returns mean / rstd
+template <typename T, bool ADD>
+__device__ __forceinline__ void load_row_stats(const T* x, const T* add, T* sum_out, int D, float eps, RowStats<T>& rs,
+                                               float* red) {
+    const int nvec = D / 8;
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < kNMMaxVec; ++i) {
+        const int vi = threadIdx.x + i * kNMThreads;
+        if (vi < nvec) {
+            load8(x + vi * 8, rs.x[i]);
+            if constexpr (ADD) {
+                float t[8];
+                load8(add + vi * 8, t);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) rs.x[i][e] += t[e];
+                if (sum_out) store8(sum_out + vi * 8, rs.x[i]);  // the norm below sees the unrounded fp32 sum
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) s += rs.x[i][e];
+        }
+    }
+    rs.mean = block_sum(s, red) / (float)D;
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < kNMMaxVec; ++i) {
+        const int vi = threadIdx.x + i * kNMThreads;
+        if (vi < nvec) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float d = rs.x[i][e] - rs.mean;
+                q += d * d;
+            }
+        }
+    }
+    rs.rstd = rsqrtf(block_sum(q, red) / (float)D + eps);
+}
+
+struct Mix6Args {
+    const void *x, *nw, *nb;
+    void* prev;
+    const void* mix[6];
+    void* out[6];
+    int D;
+    float eps;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kNMThreads) attn_norm_mix6_kernel(const Mix6Args p) {
+    __shared__ float red[32];
+    const size_t row = blockIdx.x;
+    const int D = p.D;
+    RowStats<T> rs;
+    load_row_stats<T, false>(reinterpret_cast<const T*>(p.x) + row * D, nullptr, nullptr, D, p.eps, rs, red);
+    T* prev = reinterpret_cast<T*>(p.prev) + row * D;
+    const int nvec = D / 8;
+#pragma unroll
+    for (int i = 0; i < kNMMaxVec; ++i) {
+        const int vi = threadIdx.x + i * kNMThreads;
+        if (vi < nvec) {
+            float w[8], b[8], pv[8], h[8], d[8];
+            load8(reinterpret_cast<const T*>(p.nw) + vi * 8, w);
+            load8(reinterpret_cast<const T*>(p.nb) + vi * 8, b);
+            load8(prev + vi * 8, pv);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                h[e] = (rs.x[i][e] - rs.mean) * rs.rstd * w[e] + b[e];
+                d[e] = pv[e] - h[e];
+            }
+            store8(prev + vi * 8, h);
+#pragma unroll
+            for (int m = 0; m < 6; ++m) {
+                float mx[8], o[8];
+                load8(reinterpret_cast<const T*>(p.mix[m]) + vi * 8, mx);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] = h[e] + d[e] * mx[e];
+                store8(reinterpret_cast<T*>(p.out[m]) + row * D + vi * 8, o);
+            }
+        }
+    }
+}
+
+struct FfnMixArgs {
+    const void *res, *attn, *nw, *nb, *mix;
+    void *prev, *res_out, *mixed;
+    int D;
+    float eps;
+};
+
+// ADD: x = res + attn (stored to res_out; normalised from the fp32 sum like the reference's fused kernel)
+// MIX: emit mixed + update prev; otherwise plain LayerNorm into `mixed`.
+template <typename T, bool ADD, bool MIX>
+__global__ void __launch_bounds__(kNMThreads) ffn_add_norm_mix_kernel(const FfnMixArgs p) {
+    __shared__ float red[32];
+    const size_t row = blockIdx.x;
+    const int D = p.D;
+    RowStats<T> rs;
+    load_row_stats<T, ADD>(reinterpret_cast<const T*>(p.res) + row * D,
+                           ADD ? reinterpret_cast<const T*>(p.attn) + row * D : nullptr,
+                           ADD ? reinterpret_cast<T*>(p.res_out) + row * D : nullptr, D, p.eps, rs, red);
+    const int nvec = D / 8;
+#pragma unroll
+    for (int i = 0; i < kNMMaxVec; ++i) {
+        const int vi = threadIdx.x + i * kNMThreads;
+        if (vi < nvec) {
+            float w[8], b[8], h[8];
+            load8(reinterpret_cast<const T*>(p.nw) + vi * 8, w);
+            load8(reinterpret_cast<const T*>(p.nb) + vi * 8, b);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) h[e] = (rs.x[i][e] - rs.mean) * rs.rstd * w[e] + b[e];
+            if constexpr (MIX) {
+                float pv[8], mx[8], o[8];
+                T* prev = reinterpret_cast<T*>(p.prev) + row * D;
+                load8(prev + vi * 8, pv);
+                load8(reinterpret_cast<const T*>(p.mix) + vi * 8, mx);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] = h[e] + (pv[e] - h[e]) * mx[e];
+                store8(prev + vi * 8, h);
+                store8(reinterpret_cast<T*>(p.mixed) + row * D + vi * 8, o);
+            } else {
+                store8(reinterpret_cast<T*>(p.mixed) + row * D + vi * 8, h);
+            }
+        }
+    }
+}
+
+struct SeqMixArgs {
+    const void *x, *init_prev;
+    const void* mix[6];
+    void* out[6];
+    void* next_state;
+    int T, D, n_mix;
+    long long total_vec;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) seq_shift_mix_kernel(const SeqMixArgs p) {
+    const int D = p.D, vecD = D / 8;
+    for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < p.total_vec;
+         v += (long long)gridDim.x * blockDim.x) {
+        const long long rowi = v / vecD;  // b*T + t
+        const int c = (int)(v % vecD) * 8;
+        const int t = (int)(rowi % p.T);
+        const long long b = rowi / p.T;
+        float x[8], pv[8];
+        const T* xp = reinterpret_cast<const T*>(p.x) + rowi * D + c;
+        load8(xp, x);
+        if (t == 0) load8(reinterpret_cast<const T*>(p.init_prev) + b * D + c, pv);
+        else load8(xp - D, pv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) pv[e] -= x[e];
+        for (int m = 0; m < p.n_mix; ++m) {
+            float mx[8], o[8];
+            load8(reinterpret_cast<const T*>(p.mix[m]) + c, mx);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[e] = x[e] + pv[e] * mx[e];
+            store8(reinterpret_cast<T*>(p.out[m]) + rowi * D + c, o);
+        }
+        if (t == p.T - 1 && p.next_state) store8(reinterpret_cast<T*>(p.next_state) + b * D + c, x);
+    }
+}
+
+static int check_row_shape(const char* what, int rows, int D) {
+    RWKV7_REQUIRE(rows > 0 && D > 0, RWKV7_ERR_INVALID, "%s: rows and D must be positive", what);
+    RWKV7_REQUIRE(D % 8 == 0 && D <= 8 * kNMThreads * kNMMaxVec, RWKV7_ERR_UNSUPPORTED,
+                  "%s: D must be a multiple of 8 and <= %d (got %d)", what, 8 * kNMThreads * kNMMaxVec, D);
+    return RWKV7_OK;
+}
+
+}  // namespace rwkv7
+
+using namespace rwkv7;
+
+extern "C" int rwkv7_attn_norm_mix6(const void* x, void* prev, const void* norm_w, const void* norm_b,
+                                    const void* const mixes[6], void* const outs[6], int rows, int D, float eps,
+                                    int dtype, void* stream) {
+    if (int e = check_row_shape("attn_norm_mix6", rows, D)) return e;
+    RWKV7_REQUIRE(x && prev && norm_w && norm_b && mixes && outs, RWKV7_ERR_INVALID, "attn_norm_mix6: null pointer");
+    RWKV7_REQUIRE(x != prev, RWKV7_ERR_INVALID, "attn_norm_mix6: x and prev must not alias");
+    Mix6Args p{x, norm_w, norm_b, prev, {}, {}, D, eps};
+    for (int m = 0; m < 6; ++m) {
+        RWKV7_REQUIRE(mixes[m] && outs[m], RWKV7_ERR_INVALID, "attn_norm_mix6: null mix/out pointer %d", m);
+        RWKV7_REQUIRE(aligned(mixes[m], 16) && aligned(outs[m], 16), RWKV7_ERR_ALIGN, "attn_norm_mix6: unaligned pointer");
+        p.mix[m] = mixes[m];
+        p.out[m] = outs[m];
+    }
+    RWKV7_REQUIRE(aligned(x, 16) && aligned(prev, 16) && aligned(norm_w, 16) && aligned(norm_b, 16), RWKV7_ERR_ALIGN,
+                  "attn_norm_mix6: unaligned pointer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    RWKV7_DISPATCH_DTYPE(dtype, T, {
+        attn_norm_mix6_kernel<T><<<rows, kNMThreads, 0, st>>>(p);
+        return check_launch("attn_norm_mix6_kernel");
+    });
+    return RWKV7_OK;
+}
+
+extern "C" int rwkv7_ffn_add_norm_mix(const void* residual, const void* attn_out, void* prev, const void* norm_w,
+                                      const void* norm_b, const void* mix, void* residual_out, void* mixed, int rows,
+                                      int D, float eps, int dtype, void* stream) {
+    if (int e = check_row_shape("ffn_add_norm_mix", rows, D)) return e;
+    RWKV7_REQUIRE(residual && prev && norm_w && norm_b && mix && mixed, RWKV7_ERR_INVALID, "ffn_add_norm_mix: null pointer");
+    RWKV7_REQUIRE(attn_out == nullptr || residual_out != nullptr, RWKV7_ERR_INVALID,
+                  "ffn_add_norm_mix: residual_out is required when attn_out is given");
+    const void* ptrs[] = {residual, attn_out, prev, norm_w, norm_b, mix, residual_out, mixed};
+    for (const void* q : ptrs) RWKV7_REQUIRE(aligned(q, 16), RWKV7_ERR_ALIGN, "ffn_add_norm_mix: unaligned pointer");
+    FfnMixArgs p{residual, attn_out, norm_w, norm_b, mix, prev, residual_out, mixed, D, eps};
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    RWKV7_DISPATCH_DTYPE(dtype, T, {
+        if (attn_out) ffn_add_norm_mix_kernel<T, true, true><<<rows, kNMThreads, 0, st>>>(p);
+        else ffn_add_norm_mix_kernel<T, false, true><<<rows, kNMThreads, 0, st>>>(p);
+        return check_launch("ffn_add_norm_mix_kernel");
+    });
+    return RWKV7_OK;
+}
+
+extern "C" int rwkv7_layer_norm(const void* x, const void* norm_w, const void* norm_b, void* out, int rows, int D,
+                                float eps, int dtype, void* stream) {
+    if (int e = check_row_shape("layer_norm", rows, D)) return e;
+    RWKV7_REQUIRE(x && norm_w && norm_b && out, RWKV7_ERR_INVALID, "layer_norm: null pointer");
+    const void* ptrs[] = {x, norm_w, norm_b, out};
+    for (const void* q : ptrs) RWKV7_REQUIRE(aligned(q, 16), RWKV7_ERR_ALIGN, "layer_norm: unaligned pointer");
+    FfnMixArgs p{x, nullptr, norm_w, norm_b, nullptr, nullptr, nullptr, out, D, eps};
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    RWKV7_DISPATCH_DTYPE(dtype, T, {
+        ffn_add_norm_mix_kernel<T, false, false><<<rows, kNMThreads, 0, st>>>(p);
+        return check_launch("layer_norm_kernel");
+    });
+    return RWKV7_OK;
+}
+
+extern "C" int rwkv7_seq_shift_mix(const void* x, const void* initial_prev, const void* const* mixes,
+                                   void* const* outs, void* next_state, int B, int T, int D, int n_mix, int dtype,
+                                   void* stream) {
+    RWKV7_REQUIRE(B > 0 && T > 0 && D > 0, RWKV7_ERR_INVALID, "seq_shift_mix: sizes must be positive");
+    RWKV7_REQUIRE(D % 8 == 0, RWKV7_ERR_UNSUPPORTED, "seq_shift_mix: D must be a multiple of 8");
+    RWKV7_REQUIRE(n_mix >= 1 && n_mix <= 6, RWKV7_ERR_INVALID, "seq_shift_mix: n_mix must be in 1..6");
+    RWKV7_REQUIRE(x && initial_prev && mixes && outs, RWKV7_ERR_INVALID, "seq_shift_mix: null pointer");
+    SeqMixArgs p{x, initial_prev, {}, {}, next_state, T, D, n_mix, (long long)B * T * (D / 8)};
+    for (int m = 0; m < n_mix; ++m) {
+        RWKV7_REQUIRE(mixes[m] && outs[m], RWKV7_ERR_INVALID, "seq_shift_mix: null mix/out pointer %d", m);
+        RWKV7_REQUIRE(aligned(mixes[m], 16) && aligned(outs[m], 16), RWKV7_ERR_ALIGN, "seq_shift_mix: unaligned pointer");
+        p.mix[m] = mixes[m];
+        p.out[m] = outs[m];
+    }
+    RWKV7_REQUIRE(aligned(x, 16) && aligned(initial_prev, 16) && aligned(next_state, 16), RWKV7_ERR_ALIGN,
+                  "seq_shift_mix: unaligned pointer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const long long blocks = (p.total_vec + 255) / 256;
+    const int grid = (int)(blocks < 148LL * 16 ? blocks : 148LL * 16);
+    RWKV7_DISPATCH_DTYPE(dtype, TT, {
+        seq_shift_mix_kernel<TT><<<grid, 256, 0, st>>>(p);
+        return check_launch("seq_shift_mix_kernel");
+    });
+    return RWKV7_OK;
+}

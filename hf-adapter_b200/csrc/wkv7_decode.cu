@@ -1,0 +1,249 @@
+// WKV-7 single-token recurrence for decode: one CTA per (sequence, head).
+//
+// The 64x64 fp32 state tile is streamed HBM -> registers -> HBM exactly once
+// (16 KiB in, 16 KiB out); everything else the decode layer does around the
+// recurrence (decay, kk normalisation, k adjustment, v interpolation, a/w LoRA
+// biases, GroupNorm, bonus term, output gate) is folded into the same pass so
+// no intermediate vector touches HBM.  The kernel is HBM-bound: algorithmic
+// traffic is 2*64*64*4 + ~7*64*sizeof(T) bytes per (sequence, head).
+//
+// Thread map (128 threads): lane16 = tid & 15 owns columns 4*lane16..+3 (key
+// index j), rowgroup = tid >> 4 owns rows rowgroup + 8*it (value index i), so a
+// warp instruction touches two full 256-byte state rows = 512 contiguous bytes.
+#include "common.cuh"
+
+namespace rwkv7 {
+
+constexpr int kN = 64;
+constexpr int kStepThreads = 128;
+
+enum StepMode { kUpdate = 0, kPrepare = 1, kRaw = 2 };
+
+struct StepArgs {
+    const void *r, *w, *k, *v, *kk, *a;
+    const float* state_in;
+    float* state_out;
+    void* out;
+    const void *g, *r_k, *gn_w, *gn_b;
+    const void *k_k, *k_a;
+    const void *w_bias, *a_bias, *v_first, *v_gate, *v_gate_bias;
+    void* v_out;
+    int a_is_raw, v_gate_is_raw;
+    int H;
+    float eps;
+};
+
+template <typename T, typename TW, int MODE>
+__global__ void __launch_bounds__(kStepThreads) wkv7_step_kernel(const StepArgs p) {
+    const int bh = blockIdx.x;
+    const int h = bh % p.H;
+    const int tid = threadIdx.x;
+    const int l16 = tid & 15;
+    const int rg = tid >> 4;
+    const size_t vbase = (size_t)bh * kN;
+    const int hbase = h * kN;
+    const int c0 = l16 * 4;
+
+    __shared__ float s_v[kN];
+    __shared__ float s_y[kN];
+
+    // ---- state tile: issue all 8 row loads first (memory-level parallelism)
+    const float* sin = p.state_in + (size_t)bh * kN * kN;
+    float4 S[8];
+#pragma unroll
+    for (int it = 0; it < 8; ++it)
+        S[it] = *reinterpret_cast<const float4*>(sin + (size_t)(it * 8 + rg) * kN + c0);  // plain load: may alias state_out
+
+    // ---- column-indexed vectors (4 columns per thread)
+    float r[4], w[4], k[4], kk[4], a[4];
+    load4(reinterpret_cast<const T*>(p.r) + vbase + c0, r);
+    load4(reinterpret_cast<const T*>(p.a) + vbase + c0, a);
+    if constexpr (MODE == kRaw) {
+        float wr[4], kr[4], ks[4], ka[4];
+        load4(reinterpret_cast<const T*>(p.w) + vbase + c0, wr);
+        load4(reinterpret_cast<const T*>(p.k) + vbase + c0, kr);
+        load4(reinterpret_cast<const T*>(p.k_k) + hbase + c0, ks);
+        load4(reinterpret_cast<const T*>(p.k_a) + hbase + c0, ka);
+        if (p.w_bias) {
+            float wb[4];
+            load4(reinterpret_cast<const T*>(p.w_bias) + hbase + c0, wb);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) wr[c] = round_to<T>(wr[c] + wb[c]);
+        }
+        if (p.a_is_raw) {
+            float ab[4] = {0.f, 0.f, 0.f, 0.f};
+            if (p.a_bias) load4(reinterpret_cast<const T*>(p.a_bias) + hbase + c0, ab);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) a[c] = round_to<T>(sigmoidf_(round_to<T>(a[c] + ab[c])));
+        }
+        float n2 = 0.f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            kk[c] = kr[c] * ks[c];
+            n2 += kk[c] * kk[c];
+        }
+        n2 = group_sum<16>(n2);
+        const float inv = 1.0f / fmaxf(sqrtf(n2), 1e-12f);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            kk[c] *= inv;
+            k[c] = kr[c] * (1.0f + (a[c] - 1.0f) * ka[c]);
+            w[c] = decay_from_raw(wr[c]);
+        }
+    } else {
+        load4(reinterpret_cast<const TW*>(p.w) + vbase + c0, w);
+        load4(reinterpret_cast<const T*>(p.k) + vbase + c0, k);
+        load4(reinterpret_cast<const T*>(p.kk) + vbase + c0, kk);
+    }
+    float kka[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) kka[c] = kk[c] * a[c];
+
+    // ---- row-indexed value vector (with the optional v_first interpolation)
+    if (tid < kN) {
+        float vv = to_f<T>(reinterpret_cast<const T*>(p.v)[vbase + tid]);
+        if constexpr (MODE == kRaw) {
+            if (p.v_first != nullptr && p.v_gate != nullptr) {
+                float gate = to_f<T>(reinterpret_cast<const T*>(p.v_gate)[vbase + tid]);
+                if (p.v_gate_is_raw) {
+                    const float gb = p.v_gate_bias ? to_f<T>(reinterpret_cast<const T*>(p.v_gate_bias)[hbase + tid]) : 0.f;
+                    gate = round_to<T>(sigmoidf_(round_to<T>(gate + gb)));
+                }
+                const float vf = to_f<T>(reinterpret_cast<const T*>(p.v_first)[vbase + tid]);
+                vv = round_to<T>(vv + (vf - vv) * gate);
+            }
+            if (p.v_out) reinterpret_cast<T*>(p.v_out)[vbase + tid] = from_f<T>(vv);
+        }
+        s_v[tid] = vv;
+    }
+    __syncthreads();
+
+    // ---- the recurrence, row by row
+    float* sout = p.state_out + (size_t)bh * kN * kN;
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+        const int i = it * 8 + rg;
+        float4 s = S[it];
+        float sa = s.x * kk[0] + s.y * kk[1] + s.z * kk[2] + s.w * kk[3];
+        sa = group_sum<16>(sa);
+        const float vi = s_v[i];
+        s.x = s.x * w[0] + vi * k[0] - sa * kka[0];
+        s.y = s.y * w[1] + vi * k[1] - sa * kka[1];
+        s.z = s.z * w[2] + vi * k[2] - sa * kka[2];
+        s.w = s.w * w[3] + vi * k[3] - sa * kka[3];
+        *reinterpret_cast<float4*>(sout + (size_t)i * kN + c0) = s;
+        float y = s.x * r[0] + s.y * r[1] + s.z * r[2] + s.w * r[3];
+        y = group_sum<16>(y);
+        if (l16 == 0) s_y[i] = y;
+    }
+
+    float corr = 0.f;
+    if constexpr (MODE != kUpdate) {
+        float rk[4];
+        load4(reinterpret_cast<const T*>(p.r_k) + hbase + c0, rk);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) corr += r[c] * k[c] * rk[c];
+        corr = group_sum<16>(corr);
+    }
+    __syncthreads();
+
+    if (tid < kN) {
+        T* out = reinterpret_cast<T*>(p.out) + vbase;
+        const float y = s_y[tid];
+        if constexpr (MODE == kUpdate) {
+            out[tid] = from_f<T>(y);
+        } else {
+            // both warps 0 and 1 compute the head statistics redundantly from shared memory
+            const int lane = tid & 31;
+            const float y0 = s_y[lane], y1 = s_y[lane + 32];
+            const float mean = group_sum<32>(y0 + y1) * (1.0f / kN);
+            const float d0 = y0 - mean, d1 = y1 - mean;
+            const float var = group_sum<32>(d0 * d0 + d1 * d1) * (1.0f / kN);
+            const float normed = (y - mean) * rsqrtf(var + p.eps);
+            const float gw = to_f<T>(reinterpret_cast<const T*>(p.gn_w)[hbase + tid]);
+            const float gb = to_f<T>(reinterpret_cast<const T*>(p.gn_b)[hbase + tid]);
+            const float gate = to_f<T>(reinterpret_cast<const T*>(p.g)[vbase + tid]);
+            out[tid] = from_f<T>((normed * gw + gb + corr * s_v[tid]) * gate);
+        }
+    }
+}
+
+template <typename T, typename TW, int MODE>
+static int launch_step(const StepArgs& p, int B, cudaStream_t st) {
+    wkv7_step_kernel<T, TW, MODE><<<B * p.H, kStepThreads, 0, st>>>(p);
+    return check_launch("wkv7_step_kernel");
+}
+
+static int check_step_common(const StepArgs& p, int B, int H, int N) {
+    RWKV7_REQUIRE(N == kN, RWKV7_ERR_UNSUPPORTED, "wkv7: head size must be 64, got %d", N);
+    RWKV7_REQUIRE(B > 0 && H > 0, RWKV7_ERR_INVALID, "wkv7: B and H must be positive (B=%d H=%d)", B, H);
+    RWKV7_REQUIRE(p.r && p.w && p.k && p.v && p.a && p.state_in && p.state_out && p.out, RWKV7_ERR_INVALID,
+                  "wkv7: null tensor pointer");
+    const void* ptrs[] = {p.r, p.w, p.k, p.v, p.a, p.kk, p.state_in, p.state_out, p.out, p.g, p.r_k, p.gn_w,
+                          p.gn_b, p.k_k, p.k_a, p.w_bias, p.a_bias, p.v_first, p.v_gate, p.v_gate_bias, p.v_out};
+    for (const void* q : ptrs) RWKV7_REQUIRE(aligned(q, 16), RWKV7_ERR_ALIGN, "wkv7: pointers must be 16-byte aligned");
+    return RWKV7_OK;
+}
+
+}  // namespace rwkv7
+
+using namespace rwkv7;
+
+extern "C" int rwkv7_wkv7_update(const void* r, const void* w, const void* k, const void* v, const void* kk,
+                                 const void* a, const float* state_in, float* state_out, void* y, int B, int H,
+                                 int N, int dtype, int w_is_f32, void* stream) {
+    StepArgs p{};
+    p.r = r; p.w = w; p.k = k; p.v = v; p.kk = kk; p.a = a;
+    p.state_in = state_in; p.state_out = state_out; p.out = y; p.H = H;
+    RWKV7_REQUIRE(kk != nullptr, RWKV7_ERR_INVALID, "wkv7_update: kk is null");
+    if (int e = check_step_common(p, B, H, N)) return e;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    RWKV7_DISPATCH_DTYPE(dtype, T, {
+        if (w_is_f32) return launch_step<T, float, kUpdate>(p, B, st);
+        return launch_step<T, T, kUpdate>(p, B, st);
+    });
+    return RWKV7_OK;
+}
+
+extern "C" int rwkv7_wkv7_output_prepare(const void* r, const void* w, const void* k, const void* v, const void* kk,
+                                         const void* a, const float* state_in, float* state_out, const void* g,
+                                         const void* r_k, const void* gn_w, const void* gn_b, void* out, int B,
+                                         int H, int N, float eps, int dtype, int w_is_f32, void* stream) {
+    StepArgs p{};
+    p.r = r; p.w = w; p.k = k; p.v = v; p.kk = kk; p.a = a;
+    p.state_in = state_in; p.state_out = state_out; p.out = out; p.H = H;
+    p.g = g; p.r_k = r_k; p.gn_w = gn_w; p.gn_b = gn_b; p.eps = eps;
+    RWKV7_REQUIRE(kk && g && r_k && gn_w && gn_b, RWKV7_ERR_INVALID, "wkv7_output_prepare: null tensor pointer");
+    if (int e = check_step_common(p, B, H, N)) return e;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    RWKV7_DISPATCH_DTYPE(dtype, T, {
+        if (w_is_f32) return launch_step<T, float, kPrepare>(p, B, st);
+        return launch_step<T, T, kPrepare>(p, B, st);
+    });
+    return RWKV7_OK;
+}
+
+extern "C" int rwkv7_wkv7_output_prepare_raw(const void* r, const void* w_raw, const void* k_raw, const void* v,
+                                             const void* a, const float* state_in, float* state_out, const void* g,
+                                             const void* k_k, const void* k_a, const void* r_k, const void* gn_w,
+                                             const void* gn_b, void* out, const void* w_bias, const void* a_bias,
+                                             int a_is_raw, const void* v_first, const void* v_gate,
+                                             const void* v_gate_bias, int v_gate_is_raw, void* v_out, int B, int H,
+                                             int N, float eps, int dtype, void* stream) {
+    StepArgs p{};
+    p.r = r; p.w = w_raw; p.k = k_raw; p.v = v; p.a = a;
+    p.state_in = state_in; p.state_out = state_out; p.out = out; p.H = H;
+    p.g = g; p.r_k = r_k; p.gn_w = gn_w; p.gn_b = gn_b; p.eps = eps;
+    p.k_k = k_k; p.k_a = k_a;
+    p.w_bias = w_bias; p.a_bias = a_bias; p.a_is_raw = a_is_raw;
+    p.v_first = v_first; p.v_gate = v_gate; p.v_gate_bias = v_gate_bias; p.v_gate_is_raw = v_gate_is_raw;
+    p.v_out = v_out;
+    RWKV7_REQUIRE(g && r_k && gn_w && gn_b && k_k && k_a, RWKV7_ERR_INVALID,
+                  "wkv7_output_prepare_raw: null tensor pointer");
+    RWKV7_REQUIRE((v_first == nullptr) == (v_gate == nullptr), RWKV7_ERR_INVALID,
+                  "wkv7_output_prepare_raw: v_first and v_gate must be given together");
+    if (int e = check_step_common(p, B, H, N)) return e;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    RWKV7_DISPATCH_DTYPE(dtype, T, { return launch_step<T, T, kRaw>(p, B, st); });
+    return RWKV7_OK;
+}

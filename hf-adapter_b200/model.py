@@ -1,0 +1,379 @@
+"""RWKV-7 causal LM running on the CUDA library: the reference's model classes and entry points
+(rwkv7_hf/native_model.py:371-853, model_layers.py, model_fast_api.py:58-265) with the same module
+tree, parameter names and cache, so a reference ``state_dict`` loads unchanged.
+
+Two execution paths, both made only of this package's kernels plus plain dense GEMMs:
+
+* ``_decode_step``: one token for B sequences, every buffer preallocated so the whole step can be
+  captured in a CUDA graph (``DecodeGraph``), the role of NativeGraphRunner
+  (rwkv7_hf/native_graph_runtime.py:212-711) and ``_block_ip_batched`` (native_jit_decode.py:481-901).
+* ``_prefill``: layer-wise over ``[B,T]`` tokens, the role of ``_prefill_current_device_impl``
+  (rwkv7_hf/native_jit_prefill.py:223-1057).
+
+Head-sharded tensor parallelism: constructed with ``tp_world > 1`` each rank holds H/P heads of
+r/k/v, the LoRA up-projections, the per-head parameters and the recurrent state, F/P of the FFN, and
+sums the ``[B,D]`` partial outputs of ``o_proj`` and ``ffn.value`` with an all-reduce.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from types import SimpleNamespace
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import lora as _lora
+from . import norm_mix as _nm
+from . import prep as _prep
+from . import quant as _q
+from . import recurrent as _rec
+from .cache import NativeRWKV7Cache
+
+
+@dataclass
+class NativeRWKV7Config:
+    """Field names of rwkv7_hf/model_config.py:59-107."""
+    vocab_size: int = 65536
+    hidden_size: int = 768
+    num_hidden_layers: int = 12
+    num_heads: int = 12
+    head_dim: int = 64
+    intermediate_size: int = 3072
+    decay_low_rank_dim: int = 64
+    gate_low_rank_dim: int = 128
+    a_low_rank_dim: int = 64
+    v_low_rank_dim: int = 32
+    use_cache: bool = True
+
+    @property
+    def attention_hidden_size(self) -> int:
+        return self.num_heads * self.head_dim
+
+
+class _LoRA(nn.Module):
+    def __init__(self, input_size, low_rank, bias, output_size):
+        super().__init__()
+        self.lora = nn.Sequential(nn.Linear(input_size, low_rank, bias=False), nn.Identity(),
+                                  nn.Linear(low_rank, output_size, bias=bias))
+
+
+class NativeRWKV7Attention(nn.Module):
+    def __init__(self, config, layer_idx, tp_world=1):
+        super().__init__()
+        self.layer_idx = layer_idx
+        self.num_heads = config.num_heads // tp_world  # heads held by this rank
+        self.head_dim = config.head_dim
+        self.hidden_size = config.hidden_size
+        hidden, A = config.hidden_size, self.num_heads * self.head_dim
+        self.attention_hidden_size = A
+        for p in ("x_r", "x_w", "x_k", "x_v", "x_a", "x_g"):
+            setattr(self, p, nn.Parameter(torch.zeros(1, 1, hidden)))
+        self.k_k = nn.Parameter(torch.zeros(A))
+        self.k_a = nn.Parameter(torch.zeros(A))
+        self.r_k = nn.Parameter(torch.zeros(self.num_heads, self.head_dim))
+        self.r_proj = nn.Linear(hidden, A, bias=False)
+        self.k_proj = nn.Linear(hidden, A, bias=False)
+        self.v_proj = nn.Linear(hidden, A, bias=False)
+        self.o_proj = nn.Linear(A, hidden, bias=False)
+        self.w_lora = _LoRA(hidden, config.decay_low_rank_dim, True, A)
+        self.a_lora = _LoRA(hidden, config.a_low_rank_dim, True, A)
+        self.g_lora = _LoRA(hidden, config.gate_low_rank_dim, False, A)
+        if layer_idx != 0:
+            self.v_lora = _LoRA(hidden, config.v_low_rank_dim, True, A)
+        self.g_norm = nn.GroupNorm(self.num_heads, A, eps=self.head_dim * 1e-5)
+
+
+class NativeRWKV7FFN(nn.Module):
+    def __init__(self, config, tp_world=1):
+        super().__init__()
+        self.x_k = nn.Parameter(torch.zeros(config.hidden_size))
+        self.key = nn.Linear(config.hidden_size, config.intermediate_size // tp_world, bias=False)
+        self.value = nn.Linear(config.intermediate_size // tp_world, config.hidden_size, bias=False)
+
+
+class NativeRWKV7Layer(nn.Module):
+    def __init__(self, config, layer_idx, tp_world=1):
+        super().__init__()
+        self.attn = NativeRWKV7Attention(config, layer_idx, tp_world)
+        self.ffn = NativeRWKV7FFN(config, tp_world)
+        self.attn_norm = nn.LayerNorm(config.hidden_size)
+        self.ffn_norm = nn.LayerNorm(config.hidden_size)
+        if layer_idx == 0:
+            self.pre_norm = nn.LayerNorm(config.hidden_size)
+
+
+class NativeRWKV7Model(nn.Module):
+    def __init__(self, config, tp_world=1):
+        super().__init__()
+        self.embeddings = nn.Embedding(config.vocab_size, config.hidden_size)
+        self.layers = nn.ModuleList([NativeRWKV7Layer(config, i, tp_world) for i in range(config.num_hidden_layers)])
+        self.norm = nn.LayerNorm(config.hidden_size)
+
+
+def _linear(mod, x, *, relu2=False, residual=None, out=None):
+    """Apply a projection operand: a quantised module of this package (epilogues fused through its
+    rwkv7_forward_* hooks, as the reference's dispatch probes them: native_jit_graph_dispatch.py:487-523)
+    or a dense nn.Linear (one library GEMM)."""
+    if isinstance(mod, (_q.MM4Linear, _q.MM8Linear, _q.A8W8Linear)):
+        if relu2:
+            if hasattr(mod, "rwkv7_forward_relu2"):
+                return mod.rwkv7_forward_relu2(x)
+            return torch.relu(mod(x)) ** 2
+        if residual is not None:
+            return mod.rwkv7_forward_add(x, residual)
+        if out is not None:
+            return mod.rwkv7_forward_into(x, out)
+        return mod(x)
+    y = F.linear(x, mod.weight, mod.bias)
+    if relu2:
+        y = torch.relu(y) ** 2
+    elif residual is not None:
+        y = y + residual
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+class RWKV7ForCausalLM(nn.Module):
+    """``RWKV7ForCausalLM`` == the native model, as in the reference (rwkv7_hf/__init__.py:17-20)."""
+
+    def __init__(self, config: NativeRWKV7Config, tp_world: int = 1, tp_rank: int = 0, tp_group=None):
+        super().__init__()
+        if config.head_dim != 64:
+            raise ValueError("the CUDA kernels require head_dim == 64")
+        if config.num_heads % tp_world or config.intermediate_size % tp_world:
+            raise ValueError("num_heads and intermediate_size must be divisible by the tensor-parallel world size")
+        self.config = config
+        self.tp_world, self.tp_rank, self.tp_group = int(tp_world), int(tp_rank), tp_group
+        self.model = NativeRWKV7Model(config, tp_world)
+        self.lm_head = nn.Linear(config.hidden_size, config.vocab_size, bias=False)
+        self._graphs = {}
+
+    # ------------------------------------------------------------------ helpers
+    @property
+    def device(self):
+        return self.model.embeddings.weight.device
+
+    @property
+    def dtype(self):
+        return self.model.embeddings.weight.dtype
+
+    def new_cache(self, batch_size: int) -> NativeRWKV7Cache:
+        c = self.config
+        return NativeRWKV7Cache.allocate(c.num_hidden_layers, batch_size, c.hidden_size, c.num_heads // self.tp_world,
+                                         c.head_dim, self.device, self.dtype)
+
+    def _all_reduce(self, t):
+        if self.tp_world > 1:
+            torch.distributed.all_reduce(t, group=self.tp_group)
+        return t
+
+    # ------------------------------------------------------------------ decode
+    @torch.no_grad()
+    def _decode_step(self, ids, cache: NativeRWKV7Cache):
+        """One token for every sequence; mutates the cache tensors in place.  Returns logits [B,V]."""
+        state, xpa, xpf, v_first = cache
+        H, N = self.model.layers[0].attn.num_heads, self.config.head_dim
+        x = F.embedding(ids.reshape(-1), self.model.embeddings.weight)
+        B = int(x.shape[0])
+        for i, layer in enumerate(self.model.layers):
+            at, ff = layer.attn, layer.ffn
+            if i == 0:
+                x = _nm.layer_norm(x, layer.pre_norm.weight, layer.pre_norm.bias)
+            xr, xw, xk, xv, xa, xg = _nm.fused_attn_norm_mix6_decode(
+                x, xpa[i], layer.attn_norm.weight, layer.attn_norm.bias, at.x_r, at.x_w, at.x_k, at.x_v, at.x_a, at.x_g)
+            r = _linear(at.r_proj, xr)
+            k = _linear(at.k_proj, xk)
+            v = _linear(at.v_proj, xv)
+            wl, al, gl = at.w_lora.lora, at.a_lora.lora, at.g_lora.lora
+            w_raw = _lora.dense_small(_lora.dense_small(xw, wl[0].weight, act_out=1), wl[2].weight)
+            a_pre = _lora.dense_small(_lora.dense_small(xa, al[0].weight), al[2].weight)
+            g = _lora.dense_small(_lora.dense_small(xg, gl[0].weight, act_out=2), gl[2].weight)
+            extra = {}
+            if i == 0:
+                extra = dict(v_out=v_first)
+            else:
+                vl = at.v_lora.lora
+                vg_pre = _lora.dense_small(_lora.dense_small(xv, vl[0].weight), vl[2].weight)
+                extra = dict(v_first=v_first, v_gate=vg_pre, v_gate_bias=vl[2].bias, v_gate_is_raw=True)
+            out, _ = _rec.fused_recurrent_output_prepare_raw(
+                r, w_raw, k, v, a_pre, state[i], g, at.k_k, at.k_a, at.r_k, at.g_norm.weight, at.g_norm.bias,
+                eps=N * 1e-5, new_state=state[i], w_bias=wl[2].bias, a_bias=al[2].bias, a_is_raw=True, **extra)
+            attn = self._all_reduce(_linear(at.o_proj, out))
+            x, mixed = _nm.fused_ffn_add_norm_mix_decode(x, attn, xpf[i], layer.ffn_norm.weight, layer.ffn_norm.bias, ff.x_k)
+            hidden = _linear(ff.key, mixed, relu2=True)
+            if self.tp_world > 1:
+                x = x + self._all_reduce(_linear(ff.value, hidden))
+            else:
+                x = _linear(ff.value, hidden, residual=x)
+        xn = _nm.layer_norm(x, self.model.norm.weight, self.model.norm.bias)
+        return _linear(self.lm_head, xn)
+
+    # ------------------------------------------------------------------ prefill
+    @torch.no_grad()
+    def _prefill(self, ids, cache: NativeRWKV7Cache, keep: int = 1, scan_chunk: int = 0):
+        """Layer-wise prefill of ``ids [B,T]`` continuing from ``cache`` (mutated in place).
+        Returns logits for the last ``keep`` tokens ``[B,keep,V]``."""
+        state, xpa, xpf, v_first_buf = cache
+        H, N = self.model.layers[0].attn.num_heads, self.config.head_dim
+        B, T = (int(v) for v in ids.shape)
+        x = F.embedding(ids, self.model.embeddings.weight)  # [B,T,D]
+        v_first = None
+        for i, layer in enumerate(self.model.layers):
+            at, ff = layer.attn, layer.ffn
+            if i == 0:
+                x = _nm.layer_norm(x, layer.pre_norm.weight, layer.pre_norm.bias)
+            h = _nm.layer_norm(x, layer.attn_norm.weight, layer.attn_norm.bias)
+            xr, xw, xk, xv, xa, xg, nxt = _nm.fused_attn_sequence_shift_mix(
+                h, xpa[i], at.x_r, at.x_w, at.x_k, at.x_v, at.x_a, at.x_g)
+            xpa[i].copy_(nxt)
+            r = _linear(at.r_proj, xr)
+            k_raw = _linear(at.k_proj, xk)
+            v_raw = _linear(at.v_proj, xv)
+            wl, al, gl = at.w_lora.lora, at.a_lora.lora, at.g_lora.lora
+            w_raw = F.linear(torch.tanh(F.linear(xw, wl[0].weight)), wl[2].weight, wl[2].bias)
+            a_pre = F.linear(F.linear(xa, al[0].weight), al[2].weight, al[2].bias)
+            g = F.linear(torch.sigmoid(F.linear(xg, gl[0].weight)), gl[2].weight)
+            if i == 0:
+                vf, vg = None, None
+            else:
+                vl = at.v_lora.lora
+                vf, vg = v_first, F.linear(F.linear(xv, vl[0].weight), vl[2].weight, vl[2].bias)
+            w, k, v, kk = _prep.fused_prefill_state_prep(
+                w_raw, k_raw, v_raw, a_pre, at.k_k, at.k_a, v_first=vf, v_gate=vg, num_heads=H, head_dim=N,
+                a_is_raw=True, v_gate_is_raw=True)
+            if i == 0:
+                v_first = v
+            a_sig = torch.sigmoid(a_pre)
+            if scan_chunk and T % scan_chunk == 0 and x.dtype != torch.float32:
+                y, new_state = _rec.self_chunk_rwkv7(r, w, k, v, kk, a_sig, state[i], chunk_size=scan_chunk)
+                out = _prep.fused_attn_output_prepare(y, r, k, v, g, at.r_k, at.g_norm.weight, at.g_norm.bias,
+                                                      num_heads=H, head_dim=N, head_v_dim=N, eps=N * 1e-5)
+            else:
+                out, new_state = _rec.fused_recurrent_scan_output_prepare(
+                    r, w, k, v, kk, a_sig, state[i], g, at.r_k, at.g_norm.weight, at.g_norm.bias, eps=N * 1e-5)
+            state[i].copy_(new_state)
+            x = x + self._all_reduce(_linear(at.o_proj, out))
+            h2 = _nm.layer_norm(x, layer.ffn_norm.weight, layer.ffn_norm.bias)
+            mixed, nxt = _nm.fused_ffn_sequence_shift_mix(h2, xpf[i], ff.x_k)
+            xpf[i].copy_(nxt)
+            hidden = _linear(ff.key, mixed, relu2=True)
+            x = x + self._all_reduce(_linear(ff.value, hidden))
+        if v_first is not None:
+            v_first_buf.copy_(v_first[:, -1])
+        cache._seen_tokens += T
+        xn = _nm.layer_norm(x[:, T - keep:].contiguous(), self.model.norm.weight, self.model.norm.bias)
+        return _linear(self.lm_head, xn)
+
+    # ------------------------------------------------------------------ reference-facing API
+    @torch.no_grad()
+    def rwkv7_forward_token(self, token_ids, cache: NativeRWKV7Cache, *, use_graph: bool = True):
+        """One decode token per sequence (rwkv7_hf/model_fast_api.py:190-244).  Returns logits ``[B,V]``."""
+        ids = token_ids.reshape(-1)
+        if use_graph:
+            g = self._decode_graph(int(ids.shape[0]))
+            logits = g.replay(ids, cache)
+        else:
+            logits = self._decode_step(ids, cache)
+        cache._seen_tokens += 1
+        return logits
+
+    @torch.no_grad()
+    def rwkv7_prefill_native(self, input_ids, cache=None, *, logits_to_keep: int = 1, scan_chunk: int = 0):
+        """Layer-wise prefill (rwkv7_hf/model_fast_api.py:58-94).  Returns ``(logits [B,keep,V], cache)``."""
+        if input_ids.dim() != 2 or int(input_ids.shape[1]) < 1:
+            raise ValueError("input_ids must be [batch, tokens] with at least one token")
+        if cache is None:
+            cache = self.new_cache(int(input_ids.shape[0]))
+        keep = int(input_ids.shape[1]) if logits_to_keep in (0, None) else min(int(logits_to_keep), int(input_ids.shape[1]))
+        return self._prefill(input_ids, cache, keep=keep, scan_chunk=scan_chunk), cache
+
+    @torch.no_grad()
+    def rwkv7_prefill_chunks(self, input_ids, cache=None, *, chunk_size: int = 512, scan_chunk: int = 0):
+        """Long prompts: prefill in ``chunk_size`` slices carrying the cache (rwkv7_hf/model_fast_api.py:96-149)."""
+        if chunk_size <= 0:
+            raise ValueError("chunk_size must be positive")
+        logits = None
+        for t0 in range(0, int(input_ids.shape[1]), int(chunk_size)):
+            logits, cache = self.rwkv7_prefill_native(input_ids[:, t0:t0 + chunk_size], cache, logits_to_keep=1,
+                                                      scan_chunk=scan_chunk)
+        return logits, cache
+
+    @torch.no_grad()
+    def forward(self, input_ids, past_key_values=None, use_cache=None, logits_to_keep: int = 0, **_):
+        """HF-style forward (rwkv7_hf/native_model.py:618-783).  Returns an object with ``.logits``
+        ``[B,T or keep,V]`` and ``.past_key_values`` (a NativeRWKV7Cache)."""
+        if input_ids.dim() == 1:
+            input_ids = input_ids[None]
+        cache = NativeRWKV7Cache.from_legacy_cache(past_key_values) if past_key_values is not None else None
+        if cache is None or not cache._is_initialized():
+            cache = self.new_cache(int(input_ids.shape[0]))
+        T = int(input_ids.shape[1])
+        if T == 1:
+            logits = self.rwkv7_forward_token(input_ids[:, 0], cache, use_graph=False)[:, None]
+        else:
+            logits, cache = self.rwkv7_prefill_native(input_ids, cache, logits_to_keep=logits_to_keep)
+        return SimpleNamespace(logits=logits, past_key_values=cache if use_cache is not False else None)
+
+    @torch.no_grad()
+    def generate(self, input_ids, max_new_tokens: int = 16, do_sample: bool = False, use_graph: bool = True, **_):
+        """Greedy generation: prefill, then one decode step per new token.  Returns ``[B, T + new]`` ids."""
+        if do_sample:
+            raise NotImplementedError("only greedy decoding is implemented")
+        logits, cache = self.rwkv7_prefill_native(input_ids, None, logits_to_keep=1)
+        tok = logits[:, -1].argmax(-1)
+        out = [input_ids, tok[:, None]]
+        for _ in range(int(max_new_tokens) - 1):
+            tok = self.rwkv7_forward_token(tok, cache, use_graph=use_graph).argmax(-1)
+            out.append(tok[:, None])
+        return torch.cat(out, dim=1)
+
+    # ------------------------------------------------------------------ CUDA graph
+    def _decode_graph(self, batch: int) -> "DecodeGraph":
+        g = self._graphs.get(batch)
+        if g is None:
+            g = self._graphs[batch] = DecodeGraph(self, batch)
+        return g
+
+
+class DecodeGraph:
+    """Fixed-batch CUDA graph of one decode step with its own static cache buffers.
+
+    Binding protocol of the reference runner (rwkv7_hf/native_graph_runtime.py:633-660): a cache that is
+    not yet backed by this runner's buffers is copied in once and then re-pointed at them, so later
+    replays touch no host-side copies."""
+
+    def __init__(self, model: RWKV7ForCausalLM, batch: int):
+        self.model, self.batch = model, batch
+        dev = model.device
+        self.ids = torch.zeros((batch,), device=dev, dtype=torch.long)
+        self.cache = model.new_cache(batch)
+        self.launches = 0
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(2):  # warm-up outside capture (allocator, lazy module loading)
+                model._decode_step(self.ids, self.cache)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        self.cache.reset()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.logits = model._decode_step(self.ids, self.cache)
+
+    def bind(self, cache: NativeRWKV7Cache):
+        if cache._graph_owner is self:
+            return
+        for dst, src in zip(self.cache._state + self.cache._xpa + self.cache._xpf + [self.cache._v_first],
+                            cache._state + cache._xpa + cache._xpf + [cache._v_first]):
+            dst.copy_(src)
+        cache._state, cache._xpa, cache._xpf, cache._v_first = (
+            self.cache._state, self.cache._xpa, self.cache._xpf, self.cache._v_first)
+        cache._graph_owner = self
+
+    def replay(self, ids, cache: NativeRWKV7Cache):
+        self.bind(cache)
+        self.ids.copy_(ids)
+        self.graph.replay()
+        return self.logits

@@ -1,0 +1,373 @@
+"""Quantised projections: formats, free functions and ``nn.Linear`` replacements.
+
+Formats and names follow the reference so packed buffers are interchangeable:
+
+* int8 per-output-channel ("MM8"): ``quantize_w8_row`` / ``w8_linear``
+  (rwkv7_hf/sm70_quant.py:485-489,522) and ``MM8Linear`` with buffers ``q_row [out,in] i8``,
+  ``row_scale [out]`` (rwkv7_hf/native_quant_mm8.py:577-580).
+* int4 group-128/256 ("MM4"): ``quantize_w4_groupwise`` / ``w4_groupwise_linear``
+  (rwkv7_hf/sm70_quant.py:502-519,579) and ``MM4Linear(group_size=128)`` with buffers
+  ``packed_group [out,in/2] u8``, ``group_scales [out,in/group]`` (rwkv7_hf/native_quant_mm4.py:601-607);
+  an optional ``group_zeros [out,in/group] u8`` buffer generalises the implicit zero-point 8.
+* A8W8: ``quantize_weight_per_channel_int8`` / ``a8w8_linear`` / ``A8W8Linear`` with buffers
+  ``q_weight_t [in,out] i8`` and ``weight_scale [out] fp32`` (rwkv7_hf/native_quant_a8w8.py:312-571).
+
+The quantisers are load-time tensor code (plain torch, any device).  Every forward runs on the
+CUDA library; there is no CPU forward.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from ._util import dt_code, ptr, require_cuda, stream_ptr
+
+GEMV_MAX_ROWS = 64  # rows up to which the weight-streaming kernels are used; above: dequantise + GEMM
+
+
+# ------------------------------------------------------------------ quantisers (load time)
+def quantize_w8_row(weight):
+    w = weight.detach().float()
+    s = (w.abs().amax(1) / 127).clamp_min(1e-6)
+    q = (w / s[:, None]).round().clamp(-127, 127).to(torch.int8)
+    return q.contiguous(), s.to(weight.dtype)
+
+
+def quantize_w4_groupwise(weight, group_size=128):
+    group_size = int(group_size)
+    if group_size not in {128, 256}:
+        raise ValueError("groupwise W4 requires group_size=128 or 256")
+    if weight.dim() != 2 or weight.shape[1] % group_size:
+        raise ValueError("groupwise W4 requires rank-2 weight with K divisible by group_size")
+    w = weight.detach().float()
+    out_features, in_features = w.shape
+    grouped = w.reshape(out_features, in_features // group_size, group_size)
+    scales = (grouped.abs().amax(dim=2) / 7).clamp_min(1e-6)
+    q = (grouped / scales[:, :, None]).round().clamp(-7, 7).to(torch.int16) + 8
+    q = q.reshape(out_features, in_features)
+    packed = ((q[:, 0::2] | (q[:, 1::2] << 4)).to(torch.uint8)).contiguous()
+    return packed, scales.to(weight.dtype).contiguous(), in_features
+
+
+def quantize_weight_per_channel_int8(weight):
+    """Returns ``(q_weight_t [in,out] int8, scales [out] fp32)``.  ``q_weight_t`` is the transposed VIEW of a
+    contiguous ``[out,in]`` tensor: same values and shape as the reference's buffer, K-major in memory,
+    which is the operand layout the tensor-core GEMM reads."""
+    fp32 = weight.detach().float()
+    scales = (fp32.abs().amax(dim=1) / 127.0).clamp_min(1.0e-5)
+    quantized = (fp32 / scales[:, None]).round().clamp(-127, 127).to(torch.int8).contiguous()
+    return quantized.t(), scales.contiguous()
+
+
+# ------------------------------------------------------------------ free functions
+def _rows(x, K):
+    if int(x.shape[-1]) != K:
+        raise ValueError(f"input must end in {K} features; got {tuple(x.shape)}")
+    return x.reshape(-1, K).contiguous()
+
+
+def _epi(relu2, residual, M, Nout, x2):
+    if relu2 and residual is not None:
+        raise ValueError("choose one epilogue")
+    if residual is not None:
+        res = residual.reshape(M, Nout).contiguous()
+        require_cuda(res, what="quant linear")
+        if res.dtype != x2.dtype:
+            raise ValueError("residual dtype must match the activations")
+        return _lib.EPI_ADD, res
+    return (_lib.EPI_RELU2 if relu2 else _lib.EPI_NONE), None
+
+
+def w4_dequant(q, scales, in_features, group_size=128, zeros=None, out=None):
+    """Dense ``[out,in]`` weight in the dtype of ``scales``."""
+    Nout = int(q.shape[0])
+    require_cuda(q, scales, zeros, what="w4_dequant")
+    if out is None:
+        out = torch.empty((Nout, int(in_features)), device=q.device, dtype=scales.dtype)
+    _lib.check(_lib.lib.rwkv7_w4g_dequant(ptr(q), ptr(scales), ptr(zeros), ptr(out), int(in_features), Nout,
+                                          int(group_size), dt_code(scales), stream_ptr(q)), "w4_dequant")
+    return out
+
+
+def w8_dequant(q, s, out=None):
+    Nout, K = (int(v) for v in q.shape)
+    require_cuda(q, s, what="w8_dequant")
+    if out is None:
+        out = torch.empty((Nout, K), device=q.device, dtype=s.dtype)
+    _lib.check(_lib.lib.rwkv7_w8_dequant(ptr(q), ptr(s), ptr(out), K, Nout, dt_code(s), stream_ptr(q)), "w8_dequant")
+    return out
+
+
+def w4_groupwise_linear(x, q, scales, out_features, in_features, *, group_size=128, out=None, zeros=None,
+                        relu2: bool = False, residual=None):
+    """y = x @ ((nibble - zero) * scale)^T.  Up to GEMV_MAX_ROWS rows run the weight-streaming kernel with the
+    optional relu^2 / residual-add epilogue fused; more rows dequantise the weight and call one dense GEMM
+    (what the reference does on every call off sm_70, rwkv7_hf/sm70_quant.py:598-610)."""
+    group_size = int(group_size)
+    if group_size not in {128, 256} or int(in_features) % group_size:
+        raise ValueError("groupwise W4 requires group_size=128/256 and divisible K")
+    K, Nout = int(in_features), int(out_features)
+    x2 = _rows(x, K)
+    M = int(x2.shape[0])
+    require_cuda(x2, q, scales, zeros, what="w4_groupwise_linear")
+    if scales.dtype != x2.dtype:
+        raise ValueError(f"scales dtype {scales.dtype} must match the activation dtype {x2.dtype}")
+    epi, res = _epi(relu2, residual, M, Nout, x2)
+    if M <= GEMV_MAX_ROWS:
+        y = torch.empty((M, Nout), device=x2.device, dtype=x2.dtype) if out is None else out.reshape(M, Nout)
+        _lib.check(_lib.lib.rwkv7_w4g_gemv(ptr(x2), ptr(q), ptr(scales), ptr(zeros), ptr(res), ptr(y), M, K, Nout,
+                                           group_size, epi, dt_code(x2), stream_ptr(x2)), "w4_groupwise_linear")
+    else:
+        y = torch.matmul(x2, w4_dequant(q, scales, K, group_size, zeros).t())
+        if relu2:
+            y = torch.relu(y) ** 2
+        elif res is not None:
+            y = y + res
+        if out is not None:
+            out.reshape(M, Nout).copy_(y)
+            y = out
+    return y.reshape(*x.shape[:-1], Nout)
+
+
+def w8_linear(x, q, s, out=None, *, relu2: bool = False, residual=None):
+    """y = x @ (q * s[:,None])^T for int8 per-output-channel weights ``q [out,in]``."""
+    Nout, K = (int(v) for v in q.shape)
+    x2 = _rows(x, K)
+    M = int(x2.shape[0])
+    require_cuda(x2, q, s, what="w8_linear")
+    if s.dtype != x2.dtype:
+        raise ValueError(f"scale dtype {s.dtype} must match the activation dtype {x2.dtype}")
+    epi, res = _epi(relu2, residual, M, Nout, x2)
+    if M <= GEMV_MAX_ROWS:
+        y = torch.empty((M, Nout), device=x2.device, dtype=x2.dtype) if out is None else out.reshape(M, Nout)
+        _lib.check(_lib.lib.rwkv7_w8_gemv(ptr(x2), ptr(q), ptr(s), ptr(res), ptr(y), M, K, Nout, epi, dt_code(x2),
+                                          stream_ptr(x2)), "w8_linear")
+    else:
+        y = torch.matmul(x2, w8_dequant(q, s).t())
+        if relu2:
+            y = torch.relu(y) ** 2
+        elif res is not None:
+            y = y + res
+        if out is not None:
+            out.reshape(M, Nout).copy_(y)
+            y = out
+    return y.reshape(*x.shape[:-1], Nout)
+
+
+def dynamic_a8_quant(x):
+    """Per-row int8 quantisation of ``x [rows,K]``: returns ``(q int8, scale fp32 [rows])``."""
+    K = int(x.shape[-1])
+    x2 = _rows(x, K)
+    require_cuda(x2, what="dynamic_a8_quant")
+    q = torch.empty(x2.shape, device=x2.device, dtype=torch.int8)
+    s = torch.empty((x2.shape[0],), device=x2.device, dtype=torch.float32)
+    _lib.check(_lib.lib.rwkv7_a8_quant(ptr(x2), ptr(q), ptr(s), int(x2.shape[0]), K, dt_code(x2), stream_ptr(x2)),
+               "dynamic_a8_quant")
+    return q, s
+
+
+def int8_mm(qa, qw_row):
+    """Bit-exact ``qa [M,K] i8 @ qw_row[N,K]^T -> [M,N] i32`` (the role of torch._int_mm in the reference)."""
+    M, K = (int(v) for v in qa.shape)
+    N = int(qw_row.shape[0])
+    if int(qw_row.shape[1]) != K:
+        raise ValueError("inner dimensions differ")
+    require_cuda(qa, qw_row, what="int8_mm")
+    qa, qw_row = qa.contiguous(), qw_row.contiguous()
+    acc = torch.empty((M, N), device=qa.device, dtype=torch.int32)
+    _lib.check(_lib.lib.rwkv7_i8_gemm(ptr(qa), ptr(qw_row), ptr(acc), M, K, N, stream_ptr(qa)), "int8_mm")
+    return acc
+
+
+def _k_major(q_weight_t):
+    """[in,out] reference-shaped weight -> contiguous [out,in] (free when it is the transposed view this
+    package creates)."""
+    qw = q_weight_t.t()
+    return qw if qw.is_contiguous() else qw.contiguous()
+
+
+def a8w8_workspace(M, K, Nout, device):
+    n = int(_lib.lib.rwkv7_a8w8_workspace_bytes(int(M), int(K), int(Nout)))
+    return torch.empty((n,), device=device, dtype=torch.uint8)
+
+
+def a8w8_linear(x, q_weight_t, weight_scale, bias=None, *, out=None, residual=None, workspace=None):
+    """Dynamic-A8 / W8 linear (rwkv7_hf/native_quant_a8w8.py:323): quantise rows, int8 GEMM with exact int32
+    accumulators, dequantise (+bias, +residual)."""
+    K = int(q_weight_t.shape[0])
+    Nout = int(q_weight_t.shape[1])
+    x2 = _rows(x, K)
+    M = int(x2.shape[0])
+    if K % 16 or Nout % 8:
+        raise ValueError("a8w8_linear requires in_features % 16 == 0 and out_features % 8 == 0")
+    qw = _k_major(q_weight_t)
+    require_cuda(x2, qw, weight_scale, bias, residual, what="a8w8_linear")
+    if weight_scale.dtype != torch.float32:
+        raise ValueError("weight_scale must be float32")
+    res = None if residual is None else residual.reshape(M, Nout).contiguous()
+    if workspace is None:
+        workspace = a8w8_workspace(M, K, Nout, x2.device)
+    y = torch.empty((M, Nout), device=x2.device, dtype=x2.dtype) if out is None else out.reshape(M, Nout)
+    _lib.check(_lib.lib.rwkv7_a8w8_linear(ptr(x2), ptr(qw), ptr(weight_scale), ptr(bias), ptr(res), ptr(y),
+                                          ptr(workspace), int(workspace.numel()), M, K, Nout, dt_code(x2),
+                                          stream_ptr(x2)), "a8w8_linear", kernels=3)
+    return y.reshape(*x.shape[:-1], Nout)
+
+
+# ------------------------------------------------------------------ modules
+class MM8Linear(torch.nn.Module):
+    """``nn.Linear`` replacement with int8 per-output-channel weights (buffers ``q_row``, ``row_scale``)."""
+
+    def __init__(self, linear, *, fused=True):
+        super().__init__()
+        self.in_features, self.out_features = int(linear.weight.shape[1]), int(linear.weight.shape[0])
+        q_row, row_scale = quantize_w8_row(linear.weight.data)
+        self.register_buffer("q_row", q_row)
+        self.register_buffer("row_scale", row_scale)
+        if linear.bias is not None:
+            self.register_buffer("bias", linear.bias.data.clone())
+        else:
+            self.bias = None
+        self.fused = bool(fused)
+        self.sm7x_rowwise = True  # the rowwise format is the one this package implements
+
+    def forward(self, x):
+        y = w8_linear(x, self.q_row, self.row_scale)
+        return y if self.bias is None else y + self.bias
+
+    def rwkv7_forward_into(self, x, out):
+        if self.bias is None:
+            return w8_linear(x, self.q_row, self.row_scale, out=out)
+        out.copy_(self.forward(x))
+        return out
+
+    def rwkv7_forward_relu2(self, x):
+        if self.bias is None:
+            return w8_linear(x, self.q_row, self.row_scale, relu2=True)
+        return torch.relu(self.forward(x)) ** 2
+
+    def rwkv7_forward_add(self, x, residual):
+        if self.bias is None:
+            return w8_linear(x, self.q_row, self.row_scale, residual=residual)
+        return self.forward(x) + residual
+
+    def extra_repr(self):
+        return f"in={self.in_features}, out={self.out_features}, mm8(rowwise int8)"
+
+
+class MM4Linear(torch.nn.Module):
+    """``nn.Linear`` replacement with int4 group-wise weights (buffers ``packed_group``, ``group_scales``)."""
+
+    def __init__(self, linear, *, fused=True, group_size=128):
+        super().__init__()
+        self.in_features, self.out_features = int(linear.weight.shape[1]), int(linear.weight.shape[0])
+        self.group_size = int(group_size)
+        if self.group_size not in {128, 256}:
+            raise ValueError("MM4Linear in this package requires group_size 128 or 256")
+        if self.in_features % self.group_size:
+            raise ValueError("in_features must be divisible by group_size")
+        self.groupwise = True
+        packed_group, group_scales, packed_inputs = quantize_w4_groupwise(linear.weight.data, group_size=self.group_size)
+        self.register_buffer("packed_group", packed_group)
+        self.register_buffer("group_scales", group_scales)
+        self.group_zeros = None
+        self.packed_inputs = int(packed_inputs)
+        self.m_orig = self.out_features
+        if linear.bias is not None:
+            self.register_buffer("bias", linear.bias.data.clone())
+        else:
+            self.bias = None
+        self.fused = bool(fused)
+
+    def _lin(self, x, **kw):
+        return w4_groupwise_linear(x, self.packed_group, self.group_scales, self.out_features, self.in_features,
+                                   group_size=self.group_size, zeros=self.group_zeros, **kw)
+
+    def forward(self, x):
+        y = self._lin(x)
+        return y if self.bias is None else y + self.bias
+
+    def rwkv7_forward_into(self, x, out):
+        if self.bias is None:
+            return self._lin(x, out=out)
+        out.copy_(self.forward(x))
+        return out
+
+    def rwkv7_forward_relu2(self, x):
+        if self.bias is None:
+            return self._lin(x, relu2=True)
+        return torch.relu(self.forward(x)) ** 2
+
+    def rwkv7_forward_add(self, x, residual):
+        if self.bias is None:
+            return self._lin(x, residual=residual)
+        return self.forward(x) + residual
+
+    def extra_repr(self):
+        return f"in={self.in_features}, out={self.out_features}, mm4(group_size={self.group_size})"
+
+
+class A8W8Linear(torch.nn.Module):
+    """Inference-only ``nn.Linear`` replacement using dynamic A8 and W8 (buffers ``q_weight_t``, ``weight_scale``)."""
+
+    def __init__(self, linear):
+        super().__init__()
+        self.in_features = int(linear.in_features)
+        self.out_features = int(linear.out_features)
+        q_weight_t, weight_scale = quantize_weight_per_channel_int8(linear.weight)
+        self.register_buffer("q_weight_t", q_weight_t)
+        self.register_buffer("weight_scale", weight_scale)
+        if linear.bias is None:
+            self.bias = None
+        else:
+            self.register_buffer("bias", linear.bias.detach().clone())
+        self.fused_ffn = True
+        self.sm70_rowwise = False
+
+    def forward(self, x):
+        return a8w8_linear(x, self.q_weight_t, self.weight_scale, self.bias)
+
+    def rwkv7_forward_into(self, x, out):
+        return a8w8_linear(x, self.q_weight_t, self.weight_scale, self.bias, out=out)
+
+    def rwkv7_forward_add(self, x, residual):
+        return a8w8_linear(x, self.q_weight_t, self.weight_scale, self.bias, residual=residual)
+
+    def rwkv7_forward_ffn(self, x, down, residual):
+        """up -> relu^2 (fp16 boundary) -> down + residual; returns None when the pairing does not apply."""
+        if not isinstance(down, A8W8Linear) or self.out_features != down.in_features:
+            return None
+        hidden = torch.relu(self.forward(x)) ** 2
+        return down.rwkv7_forward_add(hidden, residual)
+
+    def extra_repr(self) -> str:
+        return f"in={self.in_features}, out={self.out_features}, dynamic_a8w8"
+
+
+def quantize_model(model, kind: str, *, min_params: int = 8_000_000, group_size: int = 128, skip=("lm_head",)) -> int:
+    """Swap eligible ``nn.Linear`` modules in place (role of quantize_model_mm8 / quantize_model_mm4,
+    rwkv7_hf/native_quant_mm8.py:631-684, rwkv7_hf/native_quant_mm4.py:761-832).  ``kind`` in
+    {"mm8","mm4","a8w8"}; modules with fewer than ``min_params`` weights or whose name is in ``skip`` stay dense."""
+    n = 0
+    for parent_name, parent in list(model.named_modules()):
+        for name, child in list(parent.named_children()):
+            full = f"{parent_name}.{name}" if parent_name else name
+            if not isinstance(child, torch.nn.Linear) or child.weight.numel() < min_params:
+                continue
+            if any(full == s or full.endswith("." + s) for s in skip):
+                continue
+            if kind == "mm8":
+                new = MM8Linear(child)
+            elif kind == "mm4":
+                if child.in_features % group_size:
+                    continue
+                new = MM4Linear(child, group_size=group_size)
+            elif kind == "a8w8":
+                if child.in_features % 16 or child.out_features % 8:
+                    continue
+                new = A8W8Linear(child)
+            else:
+                raise ValueError(f"unknown quantisation kind {kind!r}")
+            setattr(parent, name, new)
+            n += 1
+    return n

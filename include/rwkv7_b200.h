@@ -1,0 +1,201 @@
+/*
+ * rwkv7_b200 — C ABI of the B200 (sm_100a) RWKV-7 inference kernels.
+ *
+ * Every entry point:
+ *   - takes plain device pointers owned by the caller, sizes, and the CUDA stream
+ *     (a cudaStream_t passed as void*; NULL = the legacy default stream);
+ *   - launches asynchronously on that stream, allocates nothing, keeps no mutable
+ *     global state, and can be called from any host thread with the device current;
+ *   - returns RWKV7_OK or a negative RWKV7_ERR_* code and never aborts;
+ *     rwkv7_last_error() returns a thread-local message for the last failure.
+ *
+ * Tensors are contiguous row-major unless a stride is passed.  `dtype` selects the
+ * activation storage type (RWKV7_F16 / RWKV7_BF16 / RWKV7_F32); arithmetic is fp32
+ * everywhere, the recurrent state is always fp32 [B,H,64,64] with rows = value
+ * index and columns = key index (the reference's "native" orientation).
+ *
+ * The reference project (rwkv-rs/hf-adapter, package rwkv7_hf) has no C ABI: its
+ * boundary is Python functions with a pure-torch fallback plus optional pybind
+ * extensions.  Each declaration below cites the reference interface it replaces.
+ */
+#ifndef RWKV7_B200_H
+#define RWKV7_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RWKV7_OK 0
+#define RWKV7_ERR_INVALID (-1)     /* null pointer, bad size, bad enum */
+#define RWKV7_ERR_UNSUPPORTED (-2) /* shape outside what the kernels handle (e.g. head size != 64) */
+#define RWKV7_ERR_ALIGN (-3)       /* pointer or leading dimension not aligned for vector loads */
+#define RWKV7_ERR_CUDA (-4)        /* the CUDA runtime reported an error at launch */
+#define RWKV7_ERR_WORKSPACE (-5)   /* caller-provided workspace too small */
+
+#define RWKV7_F16 0
+#define RWKV7_BF16 1
+#define RWKV7_F32 2
+
+/* epilogues of the quantised linears (rwkv7_forward_relu2 / rwkv7_forward_add hooks,
+ * rwkv7_hf/native_quant_mm4.py:662-712, native_quant_a8w8.py:555-571) */
+#define RWKV7_EPI_NONE 0
+#define RWKV7_EPI_RELU2 1 /* out = relu(y)^2, y rounded to the activation dtype first */
+#define RWKV7_EPI_ADD 2   /* out = y + residual */
+
+int rwkv7_abi_version(void);
+const char* rwkv7_last_error(void);
+
+/* ------------------------------------------------------------------ WKV-7 recurrence, one token
+ * Replaces fused_recurrent_update (rwkv7_hf/fused_recurrent_update.py:1214),
+ * fused_recurrent_output_prepare (:967) and fused_recurrent_output_prepare_raw (:1089).
+ *
+ *   sa[i]   = sum_m S[i,m] kk[m]
+ *   S'[i,j] = S[i,j] w[j] + v[i] k[j] - sa[i] kk[j] a[j]
+ *   y[i]    = sum_j S'[i,j] r[j]
+ *
+ * state_out may equal state_in (in-place update) or be a different buffer (the reference
+ * contract: input state untouched).  Vectors are [B,H,64] in `dtype`; `w` is the decay in
+ * fp32 when w_is_f32 != 0, else in `dtype`.
+ */
+int rwkv7_wkv7_update(const void* r, const void* w, const void* k, const void* v, const void* kk, const void* a,
+                      const float* state_in, float* state_out, void* y,
+                      int B, int H, int N, int dtype, int w_is_f32, void* stream);
+
+/* update + GroupNorm(eps) + (sum_n r k r_k) v bonus + gate g.  r_k [H,64]; gn_w, gn_b [H*64]. */
+int rwkv7_wkv7_output_prepare(const void* r, const void* w, const void* k, const void* v, const void* kk,
+                              const void* a, const float* state_in, float* state_out, const void* g,
+                              const void* r_k, const void* gn_w, const void* gn_b, void* out,
+                              int B, int H, int N, float eps, int dtype, int w_is_f32, void* stream);
+
+/* Same from raw projections: w = exp(-0.606531*sigmoid(w_raw)), kk = l2norm_head(k_raw*k_k),
+ * k = k_raw*(1+(a-1)*k_a).  Optional fusions of the LoRA epilogues that precede the step in the
+ * decode layer (rwkv7_hf/native_jit_decode.py:747-767); each is enabled by a non-NULL pointer/flag:
+ *   w_bias  [H*64] : w_raw += w_bias           (w_lora up bias "w0")
+ *   a_bias  [H*64] + a_is_raw : a = sigmoid(a + a_bias)  (a_lora up bias "a0")
+ *   v_first [B,H*64], v_gate [B,H*64] (+v_gate_bias, v_gate_is_raw): v = v + (v_first - v)*gate
+ *   v_out   [B,H*64] : receives the v actually used (layer 0 stores it as v_first)
+ */
+int rwkv7_wkv7_output_prepare_raw(const void* r, const void* w_raw, const void* k_raw, const void* v, const void* a,
+                                  const float* state_in, float* state_out, const void* g,
+                                  const void* k_k, const void* k_a, const void* r_k,
+                                  const void* gn_w, const void* gn_b, void* out,
+                                  const void* w_bias, const void* a_bias, int a_is_raw,
+                                  const void* v_first, const void* v_gate, const void* v_gate_bias, int v_gate_is_raw,
+                                  void* v_out,
+                                  int B, int H, int N, float eps, int dtype, void* stream);
+
+/* ------------------------------------------------------------------ WKV-7 scan over T tokens
+ * Replaces fused_recurrent_scan (rwkv7_hf/fused_recurrent_update.py:1299), _clampw (:1420),
+ * _output_prepare (:1710), self_chunk_rwkv7 (rwkv7_hf/self_chunk_rwkv7.py:33) and dplr_chunk_scan
+ * (rwkv7_hf/dplr_prefill.py:505).  Inputs [B,T,H,64]; y [B,T,H,64]; state [B,H,64,64] fp32.
+ *   w_mode: 0 = w is the decay in `dtype`, 1 = decay in fp32, 2 = raw w in `dtype` (decay computed in-kernel)
+ *   g/r_k/gn_w/gn_b: all NULL = plain scan; all non-NULL = fused per-token GroupNorm/bonus/gate.
+ */
+int rwkv7_wkv7_scan(const void* r, const void* w, const void* k, const void* v, const void* kk, const void* a,
+                    const float* state_in, float* state_out, void* y,
+                    const void* g, const void* r_k, const void* gn_w, const void* gn_b, float eps,
+                    int B, int T, int H, int N, int dtype, int w_mode, void* stream);
+
+/* Chunked (WY / DPLR) form of the same scan with the intra-chunk products on tensor cores.
+ * chunk in {16, 32, 64}; T % chunk == 0; fp16 or bf16 activations.  Same arguments as above. */
+int rwkv7_wkv7_chunk_scan(const void* r, const void* w, const void* k, const void* v, const void* kk, const void* a,
+                          const float* state_in, float* state_out, void* y,
+                          int B, int T, int H, int N, int chunk, int dtype, int w_mode, void* stream);
+
+/* ------------------------------------------------------------------ LayerNorm + token-shift mixes
+ * Replaces fused_attn_norm_mix6_decode (rwkv7_hf/fused_decode_norm_mix.py:161): h = LN(x);
+ * out_m = h + (prev - h)*mix_m for m in r,w,k,v,a,g; prev <- h (in place).  outs: 6 device pointers
+ * (host array).  x [rows,D]. */
+int rwkv7_attn_norm_mix6(const void* x, void* prev, const void* norm_w, const void* norm_b,
+                         const void* const mixes[6], void* const outs[6],
+                         int rows, int D, float eps, int dtype, void* stream);
+
+/* Replaces fused_ffn_add_norm_mix_decode (rwkv7_hf/fused_decode_norm_mix.py:296) and the sm_120-only
+ * ffn_add_norm_mix extension (rwkv7_hf/blackwell_norm_mix.py:56-63): x = residual + attn_out (attn_out
+ * may be NULL); h = LN(x); mixed = h + (prev-h)*mix; prev <- h. */
+int rwkv7_ffn_add_norm_mix(const void* residual, const void* attn_out, void* prev, const void* norm_w,
+                           const void* norm_b, const void* mix, void* residual_out, void* mixed,
+                           int rows, int D, float eps, int dtype, void* stream);
+
+/* Plain LayerNorm (pre_norm of layer 0 and the final norm; rwkv7_hf/native.py:404,450). */
+int rwkv7_layer_norm(const void* x, const void* norm_w, const void* norm_b, void* out,
+                     int rows, int D, float eps, int dtype, void* stream);
+
+/* Replaces fused_attn_sequence_shift_mix / fused_ffn_sequence_shift_mix (rwkv7_hf/fused_time_mix.py:413,470):
+ * x [B,T,D] (already normalised), prev_t = x_{t-1} (initial_prev for t = 0), out_m = x + (prev-x)*mix_m for
+ * n_mix in {1,6} mixes; next_state [B,D] = x[:, T-1]. */
+int rwkv7_seq_shift_mix(const void* x, const void* initial_prev, const void* const* mixes, void* const* outs,
+                        void* next_state, int B, int T, int D, int n_mix, int dtype, void* stream);
+
+/* ------------------------------------------------------------------ LoRA group
+ * Replaces fused_wa_lora / fused_wag_lora / fused_wavg_lora (rwkv7_hf/fused_lora.py:409,559,706) as a
+ * generic small dense linear with fused activation:
+ *   out[rows,Nout] = act_out( act_in(x)[rows,K] . W[Nout,K]^T + bias )
+ * act codes: 0 none, 1 tanh, 2 sigmoid.  Intended for the rank-R projections (K or Nout <= 256). */
+int rwkv7_dense_small(const void* x, const void* W, const void* bias, void* out,
+                      int rows, int K, int Nout, int act_in, int act_out, int dtype, void* stream);
+
+/* ------------------------------------------------------------------ prefill state / output prep
+ * Replaces fused_prefill_state_prep (rwkv7_hf/fused_prefill.py:184): per row of [rows,H*64]
+ *   w_out = exp(-0.606531*sigmoid(w_raw)) (fp32; the log-decay when log_decay != 0),
+ *   kk = l2norm_head(k_raw*k_k), k = k_raw*(1+(a-1)*k_a), v = v_raw + (v_first - v_raw)*v_gate.
+ * v_first/v_gate may be NULL (layer 0). */
+int rwkv7_prefill_state_prep(const void* w_raw, const void* k_raw, const void* v_raw, const void* a,
+                             const void* k_k, const void* k_a, const void* v_first, const void* v_gate,
+                             float* w_out, void* k_out, void* v_out, void* kk_out,
+                             int rows, int H, int N, int a_is_raw, int v_gate_is_raw, int log_decay,
+                             int dtype, void* stream);
+
+/* Replaces fused_attn_output_prepare (rwkv7_hf/fused_output.py:190): (GroupNorm(y) + (sum r k r_k) v) * g. */
+int rwkv7_attn_output_prepare(const void* recurrent, const void* r, const void* k, const void* v, const void* g,
+                              const void* r_k, const void* gn_w, const void* gn_b, void* out,
+                              int rows, int H, int N, float eps, int dtype, void* stream);
+
+/* ------------------------------------------------------------------ quantised projections
+ * int4 group-wise weights, the reference's quantize_w4_groupwise format (rwkv7_hf/sm70_quant.py:502-519):
+ * packed [Nout, K/2] u8 (low nibble = even k), scales [Nout, K/group] in `dtype`, optional zeros
+ * [Nout, K/group] u8 (NULL = 8).  Replaces w4_groupwise_linear (:579) / MM4Linear(group_size=128).forward:
+ *   out[M,Nout] = epilogue( x[M,K] . ((nibble - zero)*scale)^T ).  M <= 64 (decode GEMV regime). */
+int rwkv7_w4g_gemv(const void* x, const uint8_t* packed, const void* scales, const uint8_t* zeros,
+                   const void* residual, void* out, int M, int K, int Nout, int group, int epilogue,
+                   int dtype, void* stream);
+
+/* int8 per-output-channel weights, quantize_w8_row format (rwkv7_hf/sm70_quant.py:485-489): q [Nout,K] i8,
+ * scale [Nout] in `dtype`.  Replaces w8_linear (:522) / the W8A16 GEMV (native_quant_a8w8.py:50-132). */
+int rwkv7_w8_gemv(const void* x, const int8_t* q, const void* scale, const void* residual, void* out,
+                  int M, int K, int Nout, int epilogue, int dtype, void* stream);
+
+/* Materialise the dense weight W[Nout,K] = (q - zero)*scale in `dtype`, for many-row (prefill) inputs where the
+ * reference dequantises and calls a GEMM (w4_dequant, rwkv7_hf/sm70_quant.py:68-71,598-610; :522-531 for int8). */
+int rwkv7_w4g_dequant(const uint8_t* packed, const void* scales, const uint8_t* zeros, void* W, int K, int Nout,
+                      int group, int dtype, void* stream);
+int rwkv7_w8_dequant(const int8_t* q, const void* scale, void* W, int K, int Nout, int dtype, void* stream);
+
+/* Dynamic per-row int8 activation quantiser; replaces _dynamic_a8_quant_kernel
+ * (rwkv7_hf/native_quant_a8w8.py:134-164) with IEEE fp32 division: s = max(amax/127, 1e-5),
+ * q = clamp(round_half_away(x/s), +-127).  q [rows,K] i8, scale [rows] fp32. */
+int rwkv7_a8_quant(const void* x, int8_t* q, float* scale, int rows, int K, int dtype, void* stream);
+
+/* int8 x int8 -> int32 GEMM, bit-exact; replaces torch._int_mm (rwkv7_hf/native_quant_a8w8.py:413).
+ * qa [M,K] i8 row-major; qw [Nout,K] i8 row-major (the transpose of the reference's q_weight_t);
+ * acc [M,Nout] i32. */
+int rwkv7_i8_gemm(const int8_t* qa, const int8_t* qw, int32_t* acc, int M, int K, int Nout, void* stream);
+
+/* Dequant epilogue; replaces _a8w8_dequant_kernel / _a8w8_dequant_add_kernel
+ * (rwkv7_hf/native_quant_a8w8.py:166-264): out = fp32(acc)*sa[row]*sw[col] (+bias) (+residual). */
+int rwkv7_a8w8_dequant(const int32_t* acc, const float* sa, const float* sw, const void* bias,
+                       const void* residual, void* out, int M, int Nout, int dtype, void* stream);
+
+/* a8w8_linear (rwkv7_hf/native_quant_a8w8.py:323): quantise rows, integer GEMM, dequantise.
+ * workspace: caller-owned scratch of at least rwkv7_a8w8_workspace_bytes(M,K,Nout) bytes, 256-byte aligned. */
+int64_t rwkv7_a8w8_workspace_bytes(int M, int K, int Nout);
+int rwkv7_a8w8_linear(const void* x, const int8_t* qw, const float* sw, const void* bias, const void* residual,
+                      void* out, void* workspace, int64_t workspace_bytes, int M, int K, int Nout, int dtype,
+                      void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RWKV7_B200_H */

@@ -1,0 +1,123 @@
+"""GPU parity of the quantised projections: bit-exact integer work (activation quantiser, int8 GEMM
+accumulators), reference-format GEMV/GEMM outputs against the golden fixtures and the oracle."""
+import numpy as np
+import pytest
+import torch
+
+import hf_adapter_b200 as hb
+from oracle import rwkv7_oracle as O
+from tests.gpu_util import cu, golden, npf
+
+pytestmark = pytest.mark.gpu
+
+
+def test_formats_against_golden():
+    g = golden("quant.npz")
+    x = cu(g["x"])
+    y = hb.w8_linear(x, cu(g["w8_q"]), cu(g["w8_s"]))
+    np.testing.assert_allclose(npf(y), g["w8_y"].astype(np.float32), rtol=2e-3, atol=2e-3)
+    y = hb.w4_groupwise_linear(x, cu(g["w4g_packed"]), cu(g["w4g_scales"]), 96, 256, group_size=128)
+    np.testing.assert_allclose(npf(y), g["w4g_y"].astype(np.float32), rtol=2e-3, atol=2e-3)
+    y = hb.a8w8_linear(x, cu(g["a8w8_q_t"]), cu(g["a8w8_s"]))
+    ref = g["a8w8_y"].astype(np.float64).ravel()
+    mine = npf(y).astype(np.float64).ravel()
+    assert mine @ ref / np.linalg.norm(mine) / np.linalg.norm(ref) >= 0.9999  # the reference's own gate
+    yo = O.a8w8_linear(g["x"], g["a8w8_q_t"], g["a8w8_s"])[0]
+    np.testing.assert_allclose(npf(y), yo.astype(np.float32), rtol=1e-3, atol=1e-3)
+
+
+@pytest.mark.parametrize("rows,K", [(1, 8), (5, 256), (64, 4096), (3, 16384)])
+def test_a8_quantiser_bit_exact(rows, K):
+    rng = np.random.default_rng(K)
+    x = rng.standard_normal((rows, K)).astype(np.float16)
+    x[0, :4] = [0.5, -0.5, 1.5, -2.5]  # ties
+    if rows > 2:
+        x[2] = 0  # all-zero row -> scale floor 1e-5
+    qo, so = O.dynamic_a8_quant(x)
+    q, s = hb.dynamic_a8_quant(cu(x))
+    assert np.array_equal(s.cpu().numpy(), so)
+    assert np.array_equal(q.cpu().numpy(), qo)
+
+
+@pytest.mark.parametrize("M,K,Nn", [(1, 16, 8), (17, 64, 24), (64, 256, 96), (130, 4096, 136), (256, 512, 256), (384, 1024, 512)])
+def test_int8_gemm_bit_exact(M, K, Nn):
+    rng = np.random.default_rng(M * 7 + Nn)
+    qa = rng.integers(-127, 128, (M, K), dtype=np.int8)
+    qw = rng.integers(-127, 128, (Nn, K), dtype=np.int8)
+    acc = hb.int8_mm(cu(qa), cu(qw))
+    assert np.array_equal(acc.cpu().numpy(), O.int8_gemm_i32(qa, qw.T))
+
+
+def test_int8_gemm_extreme_values():
+    M, K, Nn = 128, 4096, 128
+    qa = np.full((M, K), -127, np.int8)
+    qw = np.full((Nn, K), 127, np.int8)
+    qw[::2] = -127
+    acc = hb.int8_mm(cu(qa), cu(qw))
+    assert np.array_equal(acc.cpu().numpy(), O.int8_gemm_i32(qa, qw.T))
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 8, 17, 64])
+@pytest.mark.parametrize("K,Nn", [(256, 40), (1024, 264)])
+def test_w4g_w8_gemv_against_oracle(M, K, Nn):
+    rng = np.random.default_rng(M + K)
+    W = (0.02 * rng.standard_normal((Nn, K))).astype(np.float16)
+    x = rng.standard_normal((M, K)).astype(np.float16)
+    res = rng.standard_normal((M, Nn)).astype(np.float16)
+    packed, scales = O.quantize_w4_groupwise(W, 128)
+    yo = O.w4_groupwise_linear(x, packed, scales)
+    y = hb.w4_groupwise_linear(cu(x), cu(packed), cu(scales), Nn, K, group_size=128)
+    np.testing.assert_allclose(npf(y), yo.astype(np.float32), rtol=2e-3, atol=2e-3)
+    yr = hb.w4_groupwise_linear(cu(x), cu(packed), cu(scales), Nn, K, relu2=True)
+    ro = np.maximum(yo.astype(np.float32), 0) ** 2
+    np.testing.assert_allclose(npf(yr), ro.astype(np.float16).astype(np.float32), rtol=4e-3, atol=4e-3)
+    ya = hb.w4_groupwise_linear(cu(x), cu(packed), cu(scales), Nn, K, residual=cu(res))
+    np.testing.assert_allclose(npf(ya), (yo.astype(np.float32) + res.astype(np.float32)), rtol=2e-3, atol=4e-3)
+    # explicit zero-points: zeros == 8 reproduces the implicit format bit for bit; random zeros follow the oracle
+    z8 = np.full(scales.shape, 8, np.uint8)
+    assert torch.equal(hb.w4_groupwise_linear(cu(x), cu(packed), cu(scales), Nn, K, zeros=cu(z8)), y)
+    zr = rng.integers(5, 12, scales.shape, dtype=np.uint8)
+    yz = hb.w4_groupwise_linear(cu(x), cu(packed), cu(scales), Nn, K, zeros=cu(zr))
+    np.testing.assert_allclose(npf(yz), O.w4_groupwise_linear(x, packed, scales, zr).astype(np.float32), rtol=2e-3, atol=3e-3)
+    # dequantised weight is bit-exact
+    Wd = hb.w4_dequant(cu(packed), cu(scales), K, 128)
+    assert np.array_equal(Wd.cpu().numpy(), O.dequant_w4_groupwise(packed, scales))
+    q, s = O.quantize_w8_row(W)
+    y8 = hb.w8_linear(cu(x), cu(q), cu(s))
+    np.testing.assert_allclose(npf(y8), O.w8_linear(x, q, s).astype(np.float32), rtol=2e-3, atol=2e-3)
+
+
+def test_many_rows_take_the_gemm_route():
+    rng = np.random.default_rng(9)
+    K, Nn, M = 512, 128, 200
+    W = (0.02 * rng.standard_normal((Nn, K))).astype(np.float16)
+    x = rng.standard_normal((M, K)).astype(np.float16)
+    packed, scales = O.quantize_w4_groupwise(W, 128)
+    y = hb.w4_groupwise_linear(cu(x), cu(packed), cu(scales), Nn, K)
+    np.testing.assert_allclose(npf(y), O.w4_groupwise_linear(x, packed, scales).astype(np.float32), rtol=2e-3, atol=2e-3)
+    q, s = O.quantize_w8_row(W)
+    np.testing.assert_allclose(npf(hb.w8_linear(cu(x), cu(q), cu(s))), O.w8_linear(x, q, s).astype(np.float32), rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.parametrize("M", [1, 17, 300])
+def test_a8w8_linear_against_oracle(M):
+    rng = np.random.default_rng(M)
+    K, Nn = 512, 264
+    W = (0.02 * rng.standard_normal((Nn, K))).astype(np.float16)
+    x = rng.standard_normal((M, K)).astype(np.float16)
+    bias = (0.1 * rng.standard_normal(Nn)).astype(np.float16)
+    res = rng.standard_normal((M, Nn)).astype(np.float16)
+    qt, st = O.quantize_weight_per_channel_int8(W)
+    yo, acc, qa, sa = O.a8w8_linear(x, qt, st, bias, res)
+    lin = torch.nn.Linear(K, Nn, bias=True)
+    with torch.no_grad():
+        lin.weight.copy_(torch.from_numpy(W.astype(np.float32)))
+        lin.bias.copy_(torch.from_numpy(bias.astype(np.float32)))
+    mod = hb.A8W8Linear(lin.half()).cuda()
+    assert np.array_equal(mod.q_weight_t.cpu().numpy(), qt) and np.array_equal(mod.weight_scale.cpu().numpy(), st)
+    y = mod.rwkv7_forward_add(cu(x), cu(res))
+    np.testing.assert_allclose(npf(y), yo.astype(np.float32), rtol=1e-3, atol=2e-3)
+    # the pieces: integer accumulators bit-exact
+    q_gpu, s_gpu = hb.dynamic_a8_quant(cu(x))
+    assert np.array_equal(q_gpu.cpu().numpy(), qa)
+    assert np.array_equal(hb.int8_mm(q_gpu, mod.q_weight_t.t()).cpu().numpy(), acc)
