@@ -23,6 +23,7 @@ PP = ctypes.POINTER(c_void_p)
 SIGNATURES = {
     "rwkv7_abi_version": (I, []),
     "rwkv7_last_error": (ctypes.c_char_p, []),
+    "rwkv7_kernel_status": (I, [I]),
     "rwkv7_wkv7_update": (I, [P] * 9 + [I, I, I, I, I, P]),
     "rwkv7_wkv7_output_prepare": (I, [P] * 13 + [I, I, I, F, I, I, P]),
     "rwkv7_wkv7_output_prepare_raw": (I, [P] * 14 + [P, P, I, P, P, P, I, P, I, I, I, F, I, P]),
@@ -33,9 +34,13 @@ SIGNATURES = {
     "rwkv7_layer_norm": (I, [P] * 4 + [I, I, F, I, P]),
     "rwkv7_seq_shift_mix": (I, [P, P, PP, PP, P, I, I, I, I, I, P]),
     "rwkv7_dense_small": (I, [P] * 4 + [I, I, I, I, I, I, P]),
+    "rwkv7_small_gemm_group": (I, [I, PP, PP, PP, PP, ctypes.POINTER(c_int), ctypes.POINTER(c_int), ctypes.POINTER(c_int), I, I, P]),
     "rwkv7_prefill_state_prep": (I, [P] * 12 + [I, I, I, I, I, I, I, P]),
     "rwkv7_attn_output_prepare": (I, [P] * 9 + [I, I, I, F, I, P]),
     "rwkv7_w4g_gemv": (I, [P] * 6 + [I, I, I, I, I, I, P]),
+    "rwkv7_w4g_tiled_bytes": (L, [I, I, ctypes.POINTER(c_int64)]),
+    "rwkv7_w4g_repack": (I, [P] * 6 + [I, I, I, I, P]),
+    "rwkv7_w4g_gemv_tiled": (I, [P] * 6 + [I, I, I, I, I, P]),
     "rwkv7_w8_gemv": (I, [P] * 5 + [I, I, I, I, I, P]),
     "rwkv7_w4g_dequant": (I, [P] * 4 + [I, I, I, I, P]),
     "rwkv7_w8_dequant": (I, [P] * 3 + [I, I, I, P]),
@@ -81,3 +86,8 @@ def check(status: int, what: str, kernels: int = 1) -> None:
 def ptr_array(ptrs):
     arr = (c_void_p * len(ptrs))(*ptrs)
     return ctypes.cast(arr, PP), arr
+
+
+def kernel_status(reset: bool = True) -> int:
+    """0 unless a tensor-core kernel's bounded wait gave up since the last reset (synchronises the device)."""
+    return int(lib.rwkv7_kernel_status(1 if reset else 0))

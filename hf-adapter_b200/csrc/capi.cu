@@ -9,7 +9,35 @@ void set_error(const char* fmt, ...) {
     vsnprintf(g_err, sizeof(g_err), fmt, ap);
     va_end(ap);
 }
+// Set (first code wins) by a tensor-core kernel whose bounded wait gave up; see umma.cuh.
+__device__ unsigned int rwkv7_kernel_error = 0;
+
+unsigned int* kernel_error_word() {
+    static unsigned int* cache[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!cache[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, rwkv7_kernel_error) != cudaSuccess) return nullptr;
+        cache[dev] = static_cast<unsigned int*>(p);
+    }
+    return cache[dev];
+}
 }  // namespace rwkv7
+
+extern "C" int rwkv7_kernel_status(int reset) {
+    unsigned int v = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(&v, rwkv7::rwkv7_kernel_error, sizeof(v));
+    if (e != cudaSuccess) {
+        rwkv7::set_error("kernel_status: %s", cudaGetErrorString(e));
+        return RWKV7_ERR_CUDA;
+    }
+    if (reset && v) {
+        unsigned int z = 0;
+        cudaMemcpyToSymbol(rwkv7::rwkv7_kernel_error, &z, sizeof(z));
+    }
+    return (int)v;
+}
 
 extern "C" int rwkv7_abi_version(void) { return 1; }
 extern "C" const char* rwkv7_last_error(void) { return rwkv7::g_err; }

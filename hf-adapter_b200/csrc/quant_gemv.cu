@@ -7,8 +7,8 @@
 // round_T((q - zero) * scale) -- and accumulates in fp32 against MB activation rows
 // at a time; activations come from L1/L2 (they are M*K*2 bytes, shared by every
 // warp).  The lane partial sums are combined with warp shuffles.  HBM-bound for
-// small M; for large M the FMA rate takes over and the tensor-core path
-// (w4g_mma.cu) is the one the model uses.
+// small M; for larger M the FMA rate takes over and the tensor-core kernel on the tiled
+// weight copy (w4g_umma.cu, rwkv7_w4g_gemv_tiled) is the one the model uses.
 #include "common.cuh"
 
 namespace rwkv7 {

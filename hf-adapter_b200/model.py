@@ -188,15 +188,15 @@ class RWKV7ForCausalLM(nn.Module):
             k = _linear(at.k_proj, xk)
             v = _linear(at.v_proj, xv)
             wl, al, gl = at.w_lora.lora, at.a_lora.lora, at.g_lora.lora
-            w_raw = _lora.dense_small(_lora.dense_small(xw, wl[0].weight, act_out=1), wl[2].weight)
-            a_pre = _lora.dense_small(_lora.dense_small(xa, al[0].weight), al[2].weight)
-            g = _lora.dense_small(_lora.dense_small(xg, gl[0].weight, act_out=2), gl[2].weight)
-            extra = {}
             if i == 0:
+                hs = _lora.small_gemm_group((xw, xa, xg), (wl[0].weight, al[0].weight, gl[0].weight), acts=(1, 0, 2))
+                w_raw, a_pre, g = _lora.small_gemm_group(hs, (wl[2].weight, al[2].weight, gl[2].weight))
                 extra = dict(v_out=v_first)
             else:
                 vl = at.v_lora.lora
-                vg_pre = _lora.dense_small(_lora.dense_small(xv, vl[0].weight), vl[2].weight)
+                hs = _lora.small_gemm_group((xw, xa, xg, xv), (wl[0].weight, al[0].weight, gl[0].weight, vl[0].weight),
+                                            acts=(1, 0, 2, 0))
+                w_raw, a_pre, g, vg_pre = _lora.small_gemm_group(hs, (wl[2].weight, al[2].weight, gl[2].weight, vl[2].weight))
                 extra = dict(v_first=v_first, v_gate=vg_pre, v_gate_bias=vl[2].bias, v_gate_is_raw=True)
             out, _ = _rec.fused_recurrent_output_prepare_raw(
                 r, w_raw, k, v, a_pre, state[i], g, at.k_k, at.k_a, at.r_k, at.g_norm.weight, at.g_norm.bias,

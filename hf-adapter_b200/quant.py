@@ -89,6 +89,41 @@ def w4_dequant(q, scales, in_features, group_size=128, zeros=None, out=None):
     return out
 
 
+def w4_repack_tiled(q, scales, in_features, group_size=128, zeros=None):
+    """Build the tiled copy of a group-wise int4 weight that the tensor-core decode kernel streams (one 8 KiB block
+    per [128 channels x 128 k] tile).  Returns ``(tiled_w u8, tiled_scales f16, tiled_zeros u8)``.  Done once at
+    load time; the reference-layout tensors stay the interchange format."""
+    import ctypes
+    Nout, K = int(q.shape[0]), int(in_features)
+    require_cuda(q, scales, zeros, what="w4_repack_tiled")
+    if scales.dtype != torch.float16:
+        raise ValueError("the tiled format holds fp16 scales")
+    n_scale = ctypes.c_int64(0)
+    nbytes = int(_lib.lib.rwkv7_w4g_tiled_bytes(K, Nout, ctypes.byref(n_scale)))
+    if nbytes == 0:
+        raise ValueError(f"in_features={K} is not a multiple of 128")
+    tw = torch.empty((nbytes,), device=q.device, dtype=torch.uint8)
+    ts = torch.empty((n_scale.value,), device=q.device, dtype=torch.float16)
+    tz = torch.empty((n_scale.value,), device=q.device, dtype=torch.uint8)
+    _lib.check(_lib.lib.rwkv7_w4g_repack(ptr(q.contiguous()), ptr(scales.contiguous()), ptr(zeros), ptr(tw), ptr(ts), ptr(tz),
+                                         K, Nout, int(group_size), _lib.F16, stream_ptr(q)), "w4_repack_tiled")
+    return tw, ts, tz
+
+
+def w4_tiled_linear(x, tiled, out_features, in_features, *, out=None, relu2: bool = False, residual=None):
+    """y = x @ W^T on the tensor-core kernel from the tiled weight copy (1..64 rows, fp16)."""
+    K, Nout = int(in_features), int(out_features)
+    x2 = _rows(x, K)
+    M = int(x2.shape[0])
+    tw, ts, tz = tiled
+    require_cuda(x2, tw, ts, tz, what="w4_tiled_linear")
+    epi, res = _epi(relu2, residual, M, Nout, x2)
+    y = torch.empty((M, Nout), device=x2.device, dtype=x2.dtype) if out is None else out.reshape(M, Nout)
+    _lib.check(_lib.lib.rwkv7_w4g_gemv_tiled(ptr(x2), ptr(tw), ptr(ts), ptr(tz), ptr(res), ptr(y), M, K, Nout, epi,
+                                             dt_code(x2), stream_ptr(x2)), "w4_tiled_linear")
+    return y.reshape(*x.shape[:-1], Nout)
+
+
 def w8_dequant(q, s, out=None):
     Nout, K = (int(v) for v in q.shape)
     require_cuda(q, s, what="w8_dequant")
@@ -271,6 +306,7 @@ class MM4Linear(torch.nn.Module):
         self.register_buffer("packed_group", packed_group)
         self.register_buffer("group_scales", group_scales)
         self.group_zeros = None
+        self._tiled = None  # tiled copy for the tensor-core decode kernel (derived, not part of the state dict)
         self.packed_inputs = int(packed_inputs)
         self.m_orig = self.out_features
         if linear.bias is not None:
@@ -280,6 +316,14 @@ class MM4Linear(torch.nn.Module):
         self.fused = bool(fused)
 
     def _lin(self, x, **kw):
+        rows = x.numel() // self.in_features
+        if rows <= GEMV_MAX_ROWS and x.dtype == torch.float16 and x.is_cuda and self.in_features % 128 == 0:
+            # decode: tensor-core kernel on the tiled copy (built once per device, on first use)
+            t = self._tiled
+            if t is None or t[0].device != x.device:
+                t = self._tiled = w4_repack_tiled(self.packed_group, self.group_scales, self.in_features,
+                                                  self.group_size, self.group_zeros)
+            return w4_tiled_linear(x, t, self.out_features, self.in_features, **kw)
         return w4_groupwise_linear(x, self.packed_group, self.group_scales, self.out_features, self.in_features,
                                    group_size=self.group_size, zeros=self.group_zeros, **kw)
 
@@ -354,8 +398,8 @@ def quantize_model(model, kind: str, *, min_params: int = 8_000_000, group_size:
             full = f"{parent_name}.{name}" if parent_name else name
             if not isinstance(child, torch.nn.Linear) or child.weight.numel() < min_params:
                 continue
-            if any(full == s or full.endswith("." + s) for s in skip):
-                continue
+            if any(full == s or full.endswith("." + s) for s in skip) or ".lora." in full:
+                continue  # the rank-R LoRA linears stay dense (they run on the grouped small-GEMM kernel)
             if kind == "mm8":
                 new = MM8Linear(child)
             elif kind == "mm4":

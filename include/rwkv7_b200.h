@@ -47,6 +47,11 @@ extern "C" {
 int rwkv7_abi_version(void);
 const char* rwkv7_last_error(void);
 
+/* The tensor-core kernels bound every wait on an mbarrier; a wait that gives up records a positive code in a
+ * device-side word instead of hanging.  This call synchronises with the device, returns that word (0 = no kernel
+ * ever gave up; > 0 = code; < 0 = RWKV7_ERR_*) and clears it when reset != 0.  No counterpart in the reference. */
+int rwkv7_kernel_status(int reset);
+
 /* ------------------------------------------------------------------ WKV-7 recurrence, one token
  * Replaces fused_recurrent_update (rwkv7_hf/fused_recurrent_update.py:1214),
  * fused_recurrent_output_prepare (:967) and fused_recurrent_output_prepare_raw (:1089).
@@ -137,6 +142,15 @@ int rwkv7_seq_shift_mix(const void* x, const void* initial_prev, const void* con
 int rwkv7_dense_small(const void* x, const void* W, const void* bias, void* out,
                       int rows, int K, int Nout, int act_in, int act_out, int dtype, void* stream);
 
+/* The same for up to four independent problems in ONE launch (the four rank-R "down" projections, or the four "up"
+ * projections, of a layer: the reference's _wavg_lora_down_kernel / _wavg_lora_up_kernel pair,
+ * rwkv7_hf/fused_lora.py:244-384), on warp-level tensor-core MMA with split-K inside a thread-block cluster.
+ * Arrays have n_problems entries; bias may be NULL or hold NULL entries; M <= 64 rows; fp16 or bf16.
+ *   out_p[M,Nout_p] = act_out_p( x_p[M,K_p] . W_p[Nout_p,K_p]^T + bias_p ) */
+int rwkv7_small_gemm_group(int n_problems, const void* const* x, const void* const* W, const void* const* bias,
+                           void* const* out, const int* K, const int* Nout, const int* act_out, int M, int dtype,
+                           void* stream);
+
 /* ------------------------------------------------------------------ prefill state / output prep
  * Replaces fused_prefill_state_prep (rwkv7_hf/fused_prefill.py:184): per row of [rows,H*64]
  *   w_out = exp(-0.606531*sigmoid(w_raw)) (fp32; the log-decay when log_decay != 0),
@@ -161,6 +175,18 @@ int rwkv7_attn_output_prepare(const void* recurrent, const void* r, const void* 
 int rwkv7_w4g_gemv(const void* x, const uint8_t* packed, const void* scales, const uint8_t* zeros,
                    const void* residual, void* out, int M, int K, int Nout, int group, int epilogue,
                    int dtype, void* stream);
+
+/* Tensor-core version of the same projection for 1..64 rows, reading a TILED copy of the weights built once at load
+ * time by rwkv7_w4g_repack (8 KiB per [128 channels x 128 k] tile, tiles of a channel block consecutive, so each CTA
+ * streams one contiguous region; scales / zero-points re-laid per tile).  Same values, same arithmetic as above.
+ * rwkv7_w4g_tiled_bytes returns the byte size of the tiled weight buffer (0 for unsupported shapes) and, through
+ * scale_elems, the element count of the tiled scale (fp16) and zero (u8) buffers.  fp16 only, K % 128 == 0.
+ * No counterpart in the reference (its group-wise format has no fused kernel off sm_70). */
+int64_t rwkv7_w4g_tiled_bytes(int K, int Nout, int64_t* scale_elems);
+int rwkv7_w4g_repack(const uint8_t* packed, const void* scales, const uint8_t* zeros, uint8_t* tiled_w, void* tiled_scales,
+                     uint8_t* tiled_zeros, int K, int Nout, int group, int dtype, void* stream);
+int rwkv7_w4g_gemv_tiled(const void* x, const uint8_t* tiled_w, const void* tiled_scales, const uint8_t* tiled_zeros,
+                         const void* residual, void* out, int M, int K, int Nout, int epilogue, int dtype, void* stream);
 
 /* int8 per-output-channel weights, quantize_w8_row format (rwkv7_hf/sm70_quant.py:485-489): q [Nout,K] i8,
  * scale [Nout] in `dtype`.  Replaces w8_linear (:522) / the W8A16 GEMV (native_quant_a8w8.py:50-132). */

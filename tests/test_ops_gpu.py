@@ -199,3 +199,30 @@ def test_norm_mix_shapes(rows, D):
     np.testing.assert_allclose(npf(mg), mo.astype(np.float32), rtol=4e-3, atol=6e-3)
     ln = hb.layer_norm(cu(x), cu(nw), cu(nb))
     np.testing.assert_allclose(npf(ln), O.layer_norm(x, nw, nb).astype(np.float32), rtol=4e-3, atol=4e-3)
+
+
+@pytest.mark.parametrize("M", [1, 5, 64])
+def test_grouped_lora_gemm_against_oracle(M):
+    """The one-launch grouped projection (tensor-core MMA, cluster split-K) for decode-size LoRA shapes."""
+    from hf_adapter_b200.lora import small_gemm_group
+    rng = np.random.default_rng(M)
+    D, A = 4096, 512
+    ranks = (64, 64, 128, 32)
+    f = lambda *s, sc=1.0: (sc * rng.standard_normal(s)).astype(np.float16)
+    xs = [f(M, D) for _ in ranks]
+    downs = [f(r, D, sc=0.02) for r in ranks]
+    ups = [f(A, r, sc=0.1) for r in ranks]
+    biases = [f(A, sc=0.5), f(A, sc=0.5), None, f(A, sc=0.5)]
+    wo, ao, go, vo = O.wavg_lora(xs[0], xs[1], xs[2], xs[3], downs, ups, biases)
+    w, a, g, v = hb.fused_wavg_lora(*(cu(x) for x in xs), *(cu(d) for d in downs), *(cu(u) for u in ups),
+                                    *(None if b is None else cu(b) for b in biases))
+    for mine, ref in ((w, wo), (a, ao), (g, go), (v, vo)):
+        np.testing.assert_allclose(npf(mine), ref.astype(np.float32), rtol=4e-3, atol=4e-3)
+    again = hb.fused_wavg_lora(*(cu(x) for x in xs), *(cu(d) for d in downs), *(cu(u) for u in ups),
+                               *(None if b is None else cu(b) for b in biases))
+    assert all(torch.equal(p, q) for p, q in zip((w, a, g, v), again))
+    # odd output width / K not a multiple of the 64-wide chunk
+    x1, w1, b1 = f(M, 72), f(40, 72, sc=0.1), f(40)
+    (y1,) = small_gemm_group((cu(x1),), (cu(w1),), (cu(b1),), acts=(1,))
+    ref = np.tanh((x1.astype(np.float32) @ w1.astype(np.float32).T + b1.astype(np.float32)).astype(np.float16).astype(np.float32))
+    np.testing.assert_allclose(npf(y1), ref, rtol=4e-3, atol=4e-3)

@@ -121,3 +121,45 @@ def test_a8w8_linear_against_oracle(M):
     q_gpu, s_gpu = hb.dynamic_a8_quant(cu(x))
     assert np.array_equal(q_gpu.cpu().numpy(), qa)
     assert np.array_equal(hb.int8_mm(q_gpu, mod.q_weight_t.t()).cpu().numpy(), acc)
+
+
+@pytest.mark.parametrize("M,K,Nn", [(1, 128, 8), (5, 512, 128), (16, 1024, 200), (33, 2048, 384), (64, 4096, 512), (64, 16384, 256),
+                                    (64, 4096, 4096)])
+def test_w4g_tensor_core_path(M, K, Nn):
+    """tcgen05 kernel on the tiled weight copy (fp16, K % 128 == 0, 1..64 rows, any Nout): all epilogues, zero-points,
+    group 256, determinism, and no bounded wait ever giving up."""
+    from hf_adapter_b200 import _lib
+    rng = np.random.default_rng(M + K + Nn)
+    W = (0.02 * rng.standard_normal((Nn, K))).astype(np.float16)
+    x = rng.standard_normal((M, K)).astype(np.float16)
+    res = rng.standard_normal((M, Nn)).astype(np.float16)
+    packed, scales = O.quantize_w4_groupwise(W, 128)
+    yo = O.w4_groupwise_linear(x, packed, scales).astype(np.float32)
+    xg, pg, sg = cu(x), cu(packed), cu(scales)
+    _lib.kernel_status(True)
+    tiled = hb.w4_repack_tiled(pg, sg, K, 128)
+    y = hb.w4_tiled_linear(xg, tiled, Nn, K)
+    assert _lib.kernel_status(True) == 0
+    tol_abs = 2e-3 * max(1.0, float(np.abs(yo).max()))
+    np.testing.assert_allclose(npf(y), yo, rtol=2e-3, atol=tol_abs)
+    assert torch.equal(hb.w4_tiled_linear(xg, tiled, Nn, K), y)  # deterministic split-K
+    yr = hb.w4_tiled_linear(xg, tiled, Nn, K, relu2=True)
+    ro = (np.maximum(yo.astype(np.float16).astype(np.float32), 0) ** 2).astype(np.float16).astype(np.float32)
+    np.testing.assert_allclose(npf(yr), ro, rtol=6e-3, atol=tol_abs * 4)
+    ya = hb.w4_tiled_linear(xg, tiled, Nn, K, residual=cu(res))
+    np.testing.assert_allclose(npf(ya), yo + res.astype(np.float32), rtol=2e-3, atol=tol_abs * 2)
+    zr = rng.integers(5, 12, scales.shape, dtype=np.uint8)
+    yz = hb.w4_tiled_linear(xg, hb.w4_repack_tiled(pg, sg, K, 128, zeros=cu(zr)), Nn, K)
+    zo = O.w4_groupwise_linear(x, packed, scales, zr).astype(np.float32)
+    np.testing.assert_allclose(npf(yz), zo, rtol=2e-3, atol=2e-3 * max(1.0, float(np.abs(zo).max())))
+    if K % 256 == 0:
+        p2, s2 = O.quantize_w4_groupwise(W, 256)
+        y2 = hb.w4_tiled_linear(xg, hb.w4_repack_tiled(cu(p2), cu(s2), K, 256), Nn, K)
+        np.testing.assert_allclose(npf(y2), O.w4_groupwise_linear(x, p2, s2, None, 256).astype(np.float32), rtol=2e-3, atol=tol_abs)
+    # the module routes decode-size inputs through the same kernel
+    lin = torch.nn.Linear(K, Nn, bias=False)
+    with torch.no_grad():
+        lin.weight.copy_(torch.from_numpy(W.astype(np.float32)))
+    mod = hb.MM4Linear(lin.half(), group_size=128).cuda()
+    assert torch.equal(mod(xg), y) and mod._tiled is not None
+    assert _lib.kernel_status(True) == 0
