@@ -57,7 +57,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const AbortCtx& ctx, unsigned code) {
     for (unsigned it = 0; it < kSpinLimit; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
+        // back off: a hot polling loop steals issue slots from the compute warps on the same scheduler
+        __nanosleep(32);
         if ((it & 63u) == 63u && *ctx.flag) return false;
+    }
+    *ctx.flag = 1;
+    atomicCAS(ctx.error, 0u, code);
+    return false;
+}
+
+// Same without the back-off, for the one thread per CTA whose wake-up latency is on the critical path.
+__device__ __forceinline__ bool mbar_wait_hot(uint64_t* bar, uint32_t parity, const AbortCtx& ctx, unsigned code) {
+    for (unsigned it = 0; it < kSpinLimit * 4; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 255u) == 255u && *ctx.flag) return false;
     }
     *ctx.flag = 1;
     atomicCAS(ctx.error, 0u, code);

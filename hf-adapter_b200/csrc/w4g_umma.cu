@@ -21,8 +21,8 @@
 //     shared memory in a fixed order (deterministic, no scratch buffer, no atomics), then the
 //     relu^2 / residual epilogue is applied and fp16 results are stored coalesced.
 //
-// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM allocator + MMA issuer, warps 2-5 =
-// dequantise + epilogue.  All mbarrier waits are bounded (umma.cuh).
+// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = TMEM allocator + MMA issuer, warps 2-9 = two
+// dequantise groups (even / odd k-blocks) + epilogue.  All mbarrier waits are bounded (umma.cuh).
 #include <cooperative_groups.h>
 
 #include "umma.cuh"
@@ -43,9 +43,12 @@ constexpr int META_BYTES = 512;             // scales + zeros, padded
 constexpr int XATOM_BYTES = NB * 128;       // one 64-k swizzle atom of the activation tile
 constexpr int X_BYTES = 2 * XATOM_BYTES;    // 16384
 constexpr int STAGE_BYTES = RAW_BYTES + SC_BYTES + Z_BYTES + X_BYTES;  // bytes that land per stage
-constexpr int TMEM_COLS = 256;  // A: 2 x 64 columns, D: 64 columns
-constexpr int D_COL = 128;
-constexpr int THREADS = 192;
+constexpr int SB = 2;            // k-blocks per super-block = dequant warp groups
+constexpr int NAB = 3;           // super-block A buffers in tensor memory (SB x 64 columns each)
+constexpr int NA = NAB;          // barrier pairs for the A buffers
+constexpr int TMEM_COLS = 512;   // A: NAB x SB x 64 columns, D: 64 columns
+constexpr int D_COL = NAB * SB * 64;
+constexpr int THREADS = 64 + SB * 128;
 }  // namespace w4
 
 struct W4UmmaArgs {
@@ -96,9 +99,9 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
     uint64_t* bars = reinterpret_cast<uint64_t*>(metas + STAGES * META_BYTES);
     uint64_t* full = bars;                   // [STAGES]
     uint64_t* empty = bars + STAGES;         // [STAGES]
-    uint64_t* a_ready = bars + 2 * STAGES;   // [2]
-    uint64_t* a_free = a_ready + 2;          // [2]
-    uint64_t* d_full = a_free + 2;           // [1]
+    uint64_t* a_ready = bars + 2 * STAGES;   // [NA]
+    uint64_t* a_free = a_ready + NA;         // [NA]
+    uint64_t* d_full = a_free + NA;          // [1]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_full + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const AbortCtx actx{abort_flag, p.error};
@@ -116,8 +119,8 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 4 + 1);  // 4 dequant warps + the MMA commit
         }
-        for (int a = 0; a < 2; ++a) {
-            mbar_init(&a_ready[a], 4);
+        for (int a = 0; a < NA; ++a) {
+            mbar_init(&a_ready[a], 4 * SB);  // every dequant warp arrives once per super-block
             mbar_init(&a_free[a], 1);
         }
         mbar_init(d_full, 1);
@@ -130,6 +133,7 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
+    const int nsb = (nkb + SB - 1) / SB;  // super-blocks (SB k-blocks share one A buffer and one MMA hand-off)
     if (warp == 0) {
         if (lane == 0) {
             for (int i = 0; i < nkb; ++i) {
@@ -147,78 +151,103 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
         }
     } else if (warp == 1) {
         if (lane == 0) {
+            // One barrier hand-off per super-block: every mbarrier hop costs ~150-200 cycles on this thread and
+            // a 128x64x16 MMA issues in ~55, so the hops are amortised over SB*8 MMAs.  The activation tile of a
+            // stage is covered by a_ready as well: the dequant warps observed full[s] before arriving on it.
             constexpr uint32_t idesc = make_idesc(TILE_N, NB, /*F32*/ 1, /*F16*/ 0, /*F16*/ 0);
             const uint32_t d_tmem = tmem_base + D_COL;
-            bool ok = true;
-            for (int i = 0; i < nkb && ok; ++i) {
-                const int s = i % STAGES, a = i & 1;
-                ok = mbar_wait(&full[s], (i / STAGES) & 1, actx, kErrWaitFull) &&
-                     mbar_wait(&a_ready[a], (i / 2) & 1, actx, kErrWaitAReady);
-                if (!ok) break;
+            for (int u = 0; u < nsb; ++u) {
+                const int ab = u % NAB;
+                if (!mbar_wait_hot(&a_ready[ab], (u / NAB) & 1, actx, kErrWaitAReady)) break;
                 tc_fence_after();
-                const uint32_t xbase = smem_u32(xs + s * X_BYTES);
 #pragma unroll
-                for (int j = 0; j < KB / 16; ++j) {
-                    const uint64_t bdesc = make_sw128_kmajor_desc(xbase + (j >> 2) * XATOM_BYTES + (j & 3) * 32);
-                    umma_f16_ts(d_tmem, tmem_base + a * 64 + j * 8, bdesc, idesc, (i > 0 || j > 0) ? 1u : 0u);
+                for (int g = 0; g < SB; ++g) {
+                    const int i = u * SB + g;
+                    if (i < nkb) {
+                        const int s = i % STAGES;
+                        // descriptor of the stage's first atom; the start-address field counts 16-byte units
+                        const uint64_t bdesc0 = make_sw128_kmajor_desc(smem_u32(xs + s * X_BYTES));
+                        const uint32_t a_tmem = tmem_base + (ab * SB + g) * 64;
+#pragma unroll
+                        for (int j = 0; j < KB / 16; ++j) {
+                            const uint64_t bdesc = bdesc0 + (uint64_t)(((j >> 2) * XATOM_BYTES + (j & 3) * 32) >> 4);
+                            umma_f16_ts(d_tmem, a_tmem + j * 8, bdesc, idesc, (i > 0 || j > 0) ? 1u : 0u);
+                        }
+                        tc_commit(&empty[s]);
+                    }
                 }
-                tc_commit(&a_free[a]);
-                tc_commit(&empty[s]);
+                tc_commit(&a_free[ab]);
             }
             tc_commit(d_full);
         }
     } else {
-        const int q = warp & 3;
+        const int q = warp & 3;            // TMEM lane quarter this warp may access
+        const int grp = (warp - 2) >> 2;   // dequant group: handles k-block grp of every super-block
         const int row = q * 32 + lane;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
         bool ok = true;
-        for (int i = 0; i < nkb && ok; ++i) {
-            const int s = i % STAGES, a = i & 1;
-            ok = mbar_wait(&full[s], (i / STAGES) & 1, actx, kErrWaitFull);
-            if (!ok) break;
-            // this channel's 64 packed bytes: chunk c (32 k) of all 128 channels is one 2 KiB slab, so the
-            // threads of a warp read consecutive 16-byte pieces (no bank conflicts, no swizzle)
-            const unsigned char* rrow = raws + s * RAW_BYTES + row * 16;
+        for (int u = 0; u < nsb && ok; ++u) {
+            const int i = u * SB + grp, ab = u % NAB;
+            const bool have = i < nkb;
+            const int s = i % STAGES;
             uint4 pk[4];
+            __half sch = __float2half(0.f);
+            float z = 8.f;
+            if (have) {
+                // one lane per warp polls; the others wait at the shuffle
+                if (lane == 0) ok = mbar_wait(&full[s], (i / STAGES) & 1, actx, kErrWaitFull);
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                // this channel's 64 packed bytes: chunk c (32 k) of all 128 channels is one 2 KiB slab, so the
+                // threads of a warp read consecutive 16-byte pieces (no bank conflicts, no swizzle)
+                const unsigned char* rrow = raws + s * RAW_BYTES + row * 16;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) pk[c] = *reinterpret_cast<const uint4*>(rrow + c * 2048);
-            const __half sch = reinterpret_cast<const __half*>(metas + s * META_BYTES)[row];
-            const float z = (float)(metas + s * META_BYTES + SC_BYTES)[row];
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[s]);
-            if (i >= 2) {
-                ok = mbar_wait(&a_free[a], ((i / 2) - 1) & 1, actx, kErrWaitAFree);
+                for (int c = 0; c < 4; ++c) pk[c] = *reinterpret_cast<const uint4*>(rrow + c * 2048);
+                sch = reinterpret_cast<const __half*>(metas + s * META_BYTES)[row];
+                z = (float)(metas + s * META_BYTES + SC_BYTES)[row];
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[s]);
+            }
+            if (u >= NAB) {
+                if (lane == 0) ok = mbar_wait(&a_free[ab], ((u / NAB) - 1) & 1, actx, kErrWaitAFree);
+                ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
             }
-            tc_fence_after();
-            const __half2 sc = __half2half2(sch);
-            const __half2 zlo = __float2half2_rn(1024.0f + z);
-            const __half2 zhi = __float2half2_rn(-(64.0f + z));
+            if (have) {
+                tc_fence_after();
+                const __half2 sc = __half2half2(sch);
+                const __half2 zlo = __float2half2_rn(1024.0f + z);
+                const __half2 zhi = __float2half2_rn(-(64.0f + z));
+                const uint32_t a_addr = lane_addr + (ab * SB + grp) * 64;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint32_t v[16];
-                dequant_word(pk[c].x, zlo, zhi, sc, v + 0);
-                dequant_word(pk[c].y, zlo, zhi, sc, v + 4);
-                dequant_word(pk[c].z, zlo, zhi, sc, v + 8);
-                dequant_word(pk[c].w, zlo, zhi, sc, v + 12);
-                tmem_st16(lane_addr + a * 64 + c * 16, v);
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t v[16];
+                    dequant_word(pk[c].x, zlo, zhi, sc, v + 0);
+                    dequant_word(pk[c].y, zlo, zhi, sc, v + 4);
+                    dequant_word(pk[c].z, zlo, zhi, sc, v + 8);
+                    dequant_word(pk[c].w, zlo, zhi, sc, v + 12);
+                    tmem_st16(a_addr + c * 16, v);
+                }
+                tc_wait_st();
+                tc_fence_before();
             }
-            tc_wait_st();
-            tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&a_ready[a]);
+            if (lane == 0) mbar_arrive(&a_ready[ab]);
         }
-        // ---- accumulator tile -> shared memory partial P[m][n]
-        if (ok) ok = mbar_wait(d_full, 0, actx, kErrWaitDFull);
+        // ---- accumulator tile -> shared memory partial P[m][n]; the two groups split the 64 columns
+        if (ok && lane == 0) ok = mbar_wait(d_full, 0, actx, kErrWaitDFull);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
         if (ok) {
             tc_fence_after();
+            constexpr int CPG = NB / SB;  // columns per group
 #pragma unroll
-            for (int c = 0; c < NB / 16; ++c) {
+            for (int c = 0; c < CPG / 16; ++c) {
                 uint32_t v[16];
-                tmem_ld16(lane_addr + D_COL + c * 16, v);
+                const int col0 = grp * CPG + c * 16;
+                tmem_ld16(lane_addr + D_COL + col0, v);
                 tc_wait_ld();
 #pragma unroll
-                for (int e = 0; e < 16; ++e) P[(c * 16 + e) * TILE_N + row] = __uint_as_float(v[e]);
+                for (int e = 0; e < 16; ++e) P[(col0 + e) * TILE_N + row] = __uint_as_float(v[e]);
             }
             tc_fence_before();
         }
@@ -229,41 +258,71 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
     __syncthreads();
     if (p.splits > 1) cluster.sync();
     const bool aborted = (*abort_flag != 0);
-    if (warp >= 2 && !aborted && n0 + (warp & 3) * 32 + lane < p.Nout) {
-        const int n = (warp & 3) * 32 + lane;
+    if (!aborted) {
+        // Each thread owns one channel pair (n, n+1) and walks the rows of this rank's share in steps of
+        // THREADS/64, four rows per batch so that the (distributed) shared-memory loads of a batch are all in
+        // flight before the first conversion: float2 partial loads in fixed rank order, fp16 rounding, epilogue,
+        // one 4-byte store; 64 consecutive threads cover one 256-byte output row segment.
         const int rows_per_rank = NB / p.splits;
         const int m_begin = split * rows_per_rank;
         const int m_end = min(p.M, m_begin + rows_per_rank);
-        const float* Pr[8];
-        for (int r = 0; r < 8; ++r) Pr[r] = (r < p.splits && p.splits > 1) ? cluster.map_shared_rank(P, r) : P;
-        for (int mb = m_begin; mb < m_end; mb += 8) {  // 8 rows at a time: all loads in flight before any store
-            float acc[8], res[8];
+        const int n = (tid & 63) * 2;
+        const bool n_ok = n0 + n < p.Nout;
+        const bool pair = (n0 + n + 1 < p.Nout) && ((p.Nout & 1) == 0);
+        constexpr int RSTEP = THREADS / 64;
+        const float* P0 = P + n;
+        const float* P1 = p.splits > 1 ? cluster.map_shared_rank(P, 1) + n : P0;
+        const float* P2 = p.splits > 2 ? cluster.map_shared_rank(P, 2) + n : P0;
+        const float* P3 = p.splits > 2 ? cluster.map_shared_rank(P, 3) + n : P0;
+        if (p.splits > 1) P0 = cluster.map_shared_rank(P, 0) + n;
+        for (int mb = m_begin + (tid >> 6); mb < m_end && n_ok; mb += 4 * RSTEP) {
+            float2 acc[4];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                acc[u] = 0.f;
-                res[u] = 0.f;
-            }
-            for (int r = 0; r < p.splits; ++r) {
-#pragma unroll
-                for (int u = 0; u < 8; ++u)
-                    if (mb + u < m_end) acc[u] += Pr[r][(mb + u) * TILE_N + n];
-            }
-            if (p.epilogue == RWKV7_EPI_ADD) {
-#pragma unroll
-                for (int u = 0; u < 8; ++u)
-                    if (mb + u < m_end) res[u] = __half2float(p.residual[(size_t)(mb + u) * p.Nout + n0 + n]);
-            }
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                if (mb + u < m_end) {
-                    float y = __half2float(__float2half_rn(acc[u]));
-                    if (p.epilogue == RWKV7_EPI_RELU2) {
-                        y = fmaxf(y, 0.f);
-                        y = y * y;
-                    } else if (p.epilogue == RWKV7_EPI_ADD) {
-                        y += res[u];
+            for (int u = 0; u < 4; ++u) {
+                const int m = mb + u * RSTEP;
+                acc[u] = make_float2(0.f, 0.f);
+                if (m < m_end) {
+                    acc[u] = *reinterpret_cast<const float2*>(P0 + m * TILE_N);
+                    if (p.splits > 1) {
+                        const float2 v = *reinterpret_cast<const float2*>(P1 + m * TILE_N);
+                        acc[u].x += v.x; acc[u].y += v.y;
                     }
-                    p.out[(size_t)(mb + u) * p.Nout + n0 + n] = __float2half_rn(y);
+                    if (p.splits > 2) {
+                        const float2 v = *reinterpret_cast<const float2*>(P2 + m * TILE_N);
+                        const float2 w = *reinterpret_cast<const float2*>(P3 + m * TILE_N);
+                        acc[u].x += v.x; acc[u].y += v.y;
+                        acc[u].x += w.x; acc[u].y += w.y;
+                    }
+                    for (int r = 4; r < p.splits; ++r) {
+                        const float2 v = *reinterpret_cast<const float2*>(cluster.map_shared_rank(P, r) + n + m * TILE_N);
+                        acc[u].x += v.x; acc[u].y += v.y;
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int m = mb + u * RSTEP;
+                if (m >= m_end) continue;
+                const size_t o = (size_t)m * p.Nout + n0 + n;
+                float y0 = __half2float(__float2half_rn(acc[u].x)), y1 = __half2float(__float2half_rn(acc[u].y));
+                if (p.epilogue == RWKV7_EPI_RELU2) {
+                    y0 = fmaxf(y0, 0.f); y0 *= y0;
+                    y1 = fmaxf(y1, 0.f); y1 *= y1;
+                } else if (p.epilogue == RWKV7_EPI_ADD) {
+                    if (pair) {
+                        const float2 rr = __half22float2(*reinterpret_cast<const __half2*>(p.residual + o));
+                        y0 += rr.x;
+                        y1 += rr.y;
+                    } else {
+                        y0 += __half2float(p.residual[o]);
+                        if (n0 + n + 1 < p.Nout) y1 += __half2float(p.residual[o + 1]);
+                    }
+                }
+                if (pair) {
+                    *reinterpret_cast<__half2*>(p.out + o) = __floats2half2_rn(y0, y1);
+                } else {
+                    p.out[o] = __float2half_rn(y0);
+                    if (n0 + n + 1 < p.Nout) p.out[o + 1] = __float2half_rn(y1);
                 }
             }
         }
@@ -275,6 +334,7 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
         tmem_dealloc(tmem_base, TMEM_COLS);
     }
 }
+
 
 // ---------------------------------------------------------------- repack (load time)
 // reference layout -> tiled layout described at the top of this file
@@ -330,7 +390,7 @@ int launch_w4g_umma_tiled(const void* x, const uint8_t* tw, const void* ts, cons
     W4UmmaArgs a{tw, reinterpret_cast<const __half*>(ts), tz, reinterpret_cast<const __half*>(residual),
                  reinterpret_cast<__half*>(out), M, K, Nout, epilogue, nkb, total_kb, splits, kernel_error_word()};
     RWKV7_REQUIRE(a.error != nullptr, RWKV7_ERR_CUDA, "w4g_gemv_tiled: cannot resolve the device error word");
-    const size_t smem = (size_t)STAGES * (X_BYTES + RAW_BYTES + META_BYTES) + (2 * STAGES + 5) * 8 + 16 + 1024;
+    const size_t smem = (size_t)STAGES * (X_BYTES + RAW_BYTES + META_BYTES) + (2 * STAGES + 2 * NA + 1) * 8 + 16 + 1024;
     cudaError_t e = cudaFuncSetAttribute(w4g_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     RWKV7_REQUIRE(e == cudaSuccess, RWKV7_ERR_CUDA, "w4g_gemv_tiled: %s", cudaGetErrorString(e));
     cudaLaunchConfig_t cfg{};
