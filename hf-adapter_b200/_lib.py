@@ -49,6 +49,8 @@ SIGNATURES = {
     "rwkv7_a8w8_dequant": (I, [P] * 6 + [I, I, I, P]),
     "rwkv7_a8w8_workspace_bytes": (L, [I, I, I]),
     "rwkv7_a8w8_linear": (I, [P] * 7 + [L, I, I, I, I, P]),
+    "rwkv7_a8w8_static_capacity_bytes": (L, []),
+    "rwkv7_a8w8_linear_static": (I, [P] * 6 + [I, I, I, I, P]),
 }
 
 if not os.path.exists(LIB_PATH):

@@ -246,3 +246,54 @@ extern "C" int rwkv7_a8w8_linear(const void* x, const int8_t* qw, const float* s
     if (int e = rwkv7_i8_gemm(qa, qw, acc, M, K, Nout, stream)) return e;
     return rwkv7_a8w8_dequant(acc, sa, sw, bias, residual, out, M, Nout, dtype, stream);
 }
+
+// ---------------------------------------------------------------- no-allocation variant
+// Some callers cannot obtain device memory at call time: a serving process that has handed the whole GPU
+// memory pool to its own arena, a real-time or signal-restricted thread that must not enter the CUDA
+// allocator, a plugin host that forbids cudaMalloc inside operator calls.  For them the scratch that
+// rwkv7_a8w8_linear takes from the caller (quantised rows, row scales, int32 accumulators) lives in a
+// fixed array inside the library instead.  Every GPU that loads the library holds kStaticScratchBytes of
+// it until the process exits.
+constexpr long long kStaticScratchBytes = 8ll << 20;  // 8 MiB
+static __device__ __align__(256) unsigned char g_a8w8_static_scratch[kStaticScratchBytes];
+
+namespace {
+// In host code the array's name is only a handle for the runtime: the device address has to be asked
+// for, once per device, with that device current.
+void* static_scratch_ptr() {
+    static void* cache[64] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        rwkv7::set_error("a8w8_linear_static: cannot query the current device");
+        return nullptr;
+    }
+    if (cache[dev] == nullptr) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_a8w8_static_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            rwkv7::set_error("a8w8_linear_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+            return nullptr;
+        }
+        cache[dev] = p;
+    }
+    return cache[dev];
+}
+}  // namespace
+
+extern "C" int64_t rwkv7_a8w8_static_capacity_bytes(void) { return kStaticScratchBytes; }
+
+extern "C" int rwkv7_a8w8_linear_static(const void* x, const int8_t* qw, const float* sw, const void* bias,
+                                        const void* residual, void* out, int M, int K, int Nout, int dtype,
+                                        void* stream) {
+    RWKV7_REQUIRE(M > 0 && K > 0 && Nout > 0, RWKV7_ERR_INVALID, "a8w8_linear_static: sizes must be positive");
+    const int64_t need = rwkv7_a8w8_workspace_bytes(M, K, Nout);
+    RWKV7_REQUIRE(need <= kStaticScratchBytes, RWKV7_ERR_WORKSPACE,
+                  "a8w8_linear_static: M=%d K=%d Nout=%d needs %lld bytes of scratch, the built-in array holds %lld; "
+                  "use rwkv7_a8w8_linear with a caller-provided workspace",
+                  M, K, Nout, (long long)need, (long long)kStaticScratchBytes);
+    void* ws = static_scratch_ptr();
+    if (ws == nullptr) return RWKV7_ERR_CUDA;
+    // nothing in the scratch has to start at zero: the quantiser, the GEMM and the epilogue each overwrite
+    // every element they later read
+    return rwkv7_a8w8_linear(x, qw, sw, bias, residual, out, ws, kStaticScratchBytes, M, K, Nout, dtype, stream);
+}

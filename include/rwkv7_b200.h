@@ -221,6 +221,19 @@ int rwkv7_a8w8_linear(const void* x, const int8_t* qw, const float* sw, const vo
                       void* out, void* workspace, int64_t workspace_bytes, int M, int K, int Nout, int dtype,
                       void* stream);
 
+/* rwkv7_a8w8_linear for callers that cannot allocate device memory when they call (a server that gave the whole
+ * GPU to its own memory pool, a thread that must not enter the CUDA allocator, a host that forbids cudaMalloc inside
+ * operators).  No counterpart in the reference.  The scratch is a fixed array of rwkv7_a8w8_static_capacity_bytes()
+ * bytes (8 MiB) inside the library, held by every GPU that loads it; the call allocates nothing and returns
+ * RWKV7_ERR_WORKSPACE when rwkv7_a8w8_workspace_bytes(M,K,Nout) exceeds that capacity.
+ *   - The first call on each device looks up the array's device address (one runtime query, no allocation): make
+ *     that first call before any stream capture.
+ *   - All calls on a device share the one array, which keeps the previous call's contents; nothing in it needs
+ *     clearing, but two calls that overlap on the GPU (different streams, no dependency) race on it. */
+int64_t rwkv7_a8w8_static_capacity_bytes(void);
+int rwkv7_a8w8_linear_static(const void* x, const int8_t* qw, const float* sw, const void* bias, const void* residual,
+                             void* out, int M, int K, int Nout, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
