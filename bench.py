@@ -285,11 +285,18 @@ def main():
     e2e_ms = float(t.item()) / steps
     clocks = sampler.stop() if sampler else None
 
-    if rank != 0:
-        # the remaining sections are single-GPU measurements on rank 0
+    def leave():
+        """Multi-rank exit.  Tearing the NCCL communicator down while CUDA graphs that captured its all-reduces are
+        alive was seen to block here, so the graphs go first and the process ends without the destructor chain."""
         if world > 1:
+            model._graphs.clear()
+            torch.cuda.synchronize()
             dist.barrier()
-            dist.destroy_process_group()
+            sys.stdout.flush()
+            os._exit(0)
+
+    if rank != 0:
+        leave()  # the remaining sections are rank-0 measurements
         return
 
     hbm_peak, tc_peak, peak_src = measured_peaks()
@@ -396,9 +403,7 @@ def main():
     if args.layers:
         line["config"]["INVALID"] = "layer count overridden for debugging"
     print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    leave()
 
 
 if __name__ == "__main__":

@@ -15,5 +15,7 @@ from .recurrent import (dplr_chunk_scan, fused_recurrent_output_prepare, fused_r
                         fused_recurrent_scan, fused_recurrent_scan_clampw, fused_recurrent_scan_output_prepare,
                         fused_recurrent_update, self_chunk_rwkv7)
 
+from .sharding import shard_spec, shard_state_dict
+
 NativeRWKV7ForCausalLM = RWKV7ForCausalLM
 __version__ = "0.1.0"

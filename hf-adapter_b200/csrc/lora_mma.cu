@@ -27,7 +27,7 @@ struct GroupArgs {
     const void* bias[kMaxProblems];
     void* out[kMaxProblems];
     int K[kMaxProblems], Nout[kMaxProblems], act[kMaxProblems];
-    int M, splits;
+    int M, splits, max_tiles;
 };
 
 __device__ __forceinline__ void lcp16(void* smem, const void* g, bool valid) {
@@ -69,7 +69,8 @@ __global__ void __launch_bounds__(LTHREADS) small_gemm_group_kernel(const GroupA
 
     const int prob = blockIdx.y;
     const int K = p.K[prob], Nout = p.Nout[prob];
-    const int n0 = blockIdx.x * LT;
+    const int n0 = (blockIdx.x % p.max_tiles) * LT;
+    const int r0 = (blockIdx.x / p.max_tiles) * LT;  // activation row block
     if (n0 >= Nout) return;  // whole cluster shares blockIdx.x / y, so it leaves together
     const int split = blockIdx.z, S = p.splits;
     const int chunks_total = (K + LK - 1) / LK;
@@ -96,9 +97,9 @@ __global__ void __launch_bounds__(LTHREADS) small_gemm_group_kernel(const GroupA
             const int idx = tid + it * LTHREADS;
             const int row = idx >> 3, ch = idx & 7;
             const bool kin = (k0 + ch * 8) < K;
-            const bool vx = kin && row < p.M;
+            const bool vx = kin && (r0 + row) < p.M;
             const bool vw = kin && (n0 + row) < Nout;
-            lcp16(&sX[buf][lswz(row, ch)], vx ? X + (size_t)row * K + k0 + ch * 8 : X, vx);
+            lcp16(&sX[buf][lswz(row, ch)], vx ? X + (size_t)(r0 + row) * K + k0 + ch * 8 : X, vx);
             lcp16(&sW[buf][lswz(row, ch)], vw ? W + (size_t)(n0 + row) * K + k0 + ch * 8 : W, vw);
         }
         asm volatile("cp.async.commit_group;\n" ::);
@@ -156,11 +157,11 @@ __global__ void __launch_bounds__(LTHREADS) small_gemm_group_kernel(const GroupA
             const int r = split * rows_per + idx / LT, cidx = idx % LT;
             float v = 0.f;
             for (int q = 0; q < S; ++q) v += cluster.map_shared_rank(sP, q)[r * LT + cidx];
-            if (r < p.M && n0 + cidx < Nout) {
+            if (r0 + r < p.M && n0 + cidx < Nout) {
                 if (bias) v += to_f<T>(bias[n0 + cidx]);
                 v = round_to<T>(v);
                 if (p.act[prob]) v = lora_act(v, p.act[prob]);
-                out[(size_t)r * Nout + n0 + cidx] = from_f<T>(v);
+                out[(size_t)(r0 + r) * Nout + n0 + cidx] = from_f<T>(v);
             }
         }
         cluster.sync();
@@ -174,12 +175,12 @@ __global__ void __launch_bounds__(LTHREADS) small_gemm_group_kernel(const GroupA
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int r = wm * 32 + i * 16 + gid + (e >> 1) * 8, cidx = n0 + wn * 32 + j * 8 + tig * 2 + (e & 1);
-                    if (r < p.M && cidx < Nout) {
+                    if (r0 + r < p.M && cidx < Nout) {
                         float v = acc[i][j][e];
                         if (bias) v += to_f<T>(bias[cidx]);
                         v = round_to<T>(v);
                         if (p.act[prob]) v = lora_act(v, p.act[prob]);
-                        out[(size_t)r * Nout + cidx] = from_f<T>(v);
+                        out[(size_t)(r0 + r) * Nout + cidx] = from_f<T>(v);
                     }
                 }
     }
@@ -193,7 +194,8 @@ extern "C" int rwkv7_small_gemm_group(int n_problems, const void* const* x, cons
                                       void* const* out, const int* K, const int* Nout, const int* act_out, int M, int dtype,
                                       void* stream) {
     RWKV7_REQUIRE(n_problems >= 1 && n_problems <= kMaxProblems, RWKV7_ERR_INVALID, "small_gemm_group: 1..%d problems", kMaxProblems);
-    RWKV7_REQUIRE(M >= 1 && M <= LT, RWKV7_ERR_UNSUPPORTED, "small_gemm_group: M must be in 1..%d (got %d)", LT, M);
+    RWKV7_REQUIRE(M >= 1 && M <= 16384, RWKV7_ERR_UNSUPPORTED, "small_gemm_group: M must be in 1..16384 (got %d)", M);
+    const int row_blocks = (M + LT - 1) / LT;
     RWKV7_REQUIRE(dtype == RWKV7_F16 || dtype == RWKV7_BF16, RWKV7_ERR_UNSUPPORTED, "small_gemm_group: fp16 / bf16 only");
     RWKV7_REQUIRE(x && W && out && K && Nout && act_out, RWKV7_ERR_INVALID, "small_gemm_group: null argument array");
     GroupArgs a{};
@@ -213,10 +215,11 @@ extern "C" int rwkv7_small_gemm_group(int n_problems, const void* const* x, cons
     // split K across a cluster when there are few output tiles and a long K (the "down" projections)
     int splits = 1;
     const int chunks = (max_k + LK - 1) / LK;
-    while (splits < 8 && max_tiles * n_problems * splits * 2 <= 160 && chunks / (splits * 2) >= 4) splits *= 2;
+    while (splits < 8 && max_tiles * row_blocks * n_problems * splits * 2 <= 160 && chunks / (splits * 2) >= 4) splits *= 2;
     a.splits = splits;
+    a.max_tiles = max_tiles;
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(max_tiles, n_problems, splits);
+    cfg.gridDim = dim3(max_tiles * row_blocks, n_problems, splits);
     cfg.blockDim = dim3(LTHREADS);
     cfg.dynamicSmemBytes = 0;
     cfg.stream = static_cast<cudaStream_t>(stream);

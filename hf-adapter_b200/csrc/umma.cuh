@@ -135,7 +135,7 @@ __device__ __forceinline__ uint64_t make_sw128_kmajor_desc(uint32_t smem_addr) {
 }
 
 // Instruction descriptor for kind::f16 / kind::i8 (dense, no negate, K-major A and B).
-//   c_format: 1 = F32, 2 = S32; a/b format: f16 kinds 0 = F16, 1 = BF16; i8 kinds 0 = U8, 1 = S8.
+//   c_format: 1 = F32, 2 = S32; a/b format: f16 kind 0 = F16, 1 = BF16; tf32 kind 2 = TF32; i8 kind 0 = U8, 1 = S8.
 __host__ __device__ constexpr uint32_t make_idesc(int M, int N, int c_format, int a_format, int b_format) {
     return ((uint32_t)c_format << 4) | ((uint32_t)a_format << 7) | ((uint32_t)b_format << 10) |
            ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
@@ -157,12 +157,27 @@ __device__ __forceinline__ void umma_f16_ss(uint32_t d_tmem, uint64_t a_desc, ui
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
+__device__ __forceinline__ void umma_tf32_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void umma_i8_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// Byte offset of element (row, byte position kbyte along K) inside a K-major SWIZZLE_128B tile of `rows` rows:
+// the tile is a sequence of 128-byte-wide "atoms" along K (rows*128 bytes each); inside an atom the 16-byte chunk
+// index is XORed with (row & 7).  This is the layout make_sw128_kmajor_desc describes.
+__device__ __forceinline__ uint32_t sw128_offset(uint32_t row, uint32_t kbyte, uint32_t rows) {
+    const uint32_t atom = kbyte >> 7, inb = kbyte & 127u;
+    return atom * rows * 128u + row * 128u + ((((inb >> 4) ^ (row & 7u)) << 4) | (inb & 15u));
 }
 
 // ---------------------------------------------------------------- host: tensor maps

@@ -109,6 +109,8 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.x * TILE_N;
+    const int m0 = blockIdx.y * NB;                 // activation row block of this CTA
+    const int m_rows = min(NB, p.M - m0);           // valid rows in the block
     const int split = blockIdx.z;
     const int kb0 = split * p.nkb;
     const int nkb = p.nkb;
@@ -145,8 +147,8 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
                 bulk_load(raws + s * RAW_BYTES, p.tw + blk * RAW_BYTES, RAW_BYTES, &full[s]);
                 bulk_load(metas + s * META_BYTES, p.ts + blk * TILE_N, SC_BYTES, &full[s]);
                 bulk_load(metas + s * META_BYTES + SC_BYTES, p.tz + blk * TILE_N, Z_BYTES, &full[s]);
-                tma_load_2d(xs + s * X_BYTES, &tm_x, &full[s], kblk * KB, 0);
-                tma_load_2d(xs + s * X_BYTES + XATOM_BYTES, &tm_x, &full[s], kblk * KB + 64, 0);
+                tma_load_2d(xs + s * X_BYTES, &tm_x, &full[s], kblk * KB, m0);
+                tma_load_2d(xs + s * X_BYTES + XATOM_BYTES, &tm_x, &full[s], kblk * KB + 64, m0);
             }
         }
     } else if (warp == 1) {
@@ -265,7 +267,7 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
         // one 4-byte store; 64 consecutive threads cover one 256-byte output row segment.
         const int rows_per_rank = NB / p.splits;
         const int m_begin = split * rows_per_rank;
-        const int m_end = min(p.M, m_begin + rows_per_rank);
+        const int m_end = min(m_rows, m_begin + rows_per_rank);
         const int n = (tid & 63) * 2;
         const bool n_ok = n0 + n < p.Nout;
         const bool pair = (n0 + n + 1 < p.Nout) && ((p.Nout & 1) == 0);
@@ -303,7 +305,7 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
             for (int u = 0; u < 4; ++u) {
                 const int m = mb + u * RSTEP;
                 if (m >= m_end) continue;
-                const size_t o = (size_t)m * p.Nout + n0 + n;
+                const size_t o = (size_t)(m0 + m) * p.Nout + n0 + n;
                 float y0 = __half2float(__float2half_rn(acc[u].x)), y1 = __half2float(__float2half_rn(acc[u].y));
                 if (p.epilogue == RWKV7_EPI_RELU2) {
                     y0 = fmaxf(y0, 0.f); y0 *= y0;
@@ -373,13 +375,14 @@ __global__ void w4g_repack_kernel(const uint8_t* __restrict__ packed, const T* _
 int launch_w4g_umma_tiled(const void* x, const uint8_t* tw, const void* ts, const uint8_t* tz, const void* residual,
                           void* out, int M, int K, int Nout, int epilogue, cudaStream_t st) {
     using namespace w4;
-    RWKV7_REQUIRE(M >= 1 && M <= NB, RWKV7_ERR_UNSUPPORTED, "w4g_gemv_tiled: M must be in 1..%d (got %d)", NB, M);
+    RWKV7_REQUIRE(M >= 1 && M <= 65535 * NB, RWKV7_ERR_UNSUPPORTED, "w4g_gemv_tiled: M out of range (got %d)", M);
+    const int row_blocks = (M + NB - 1) / NB;  // each block of 64 activation rows is one pass over the weights
     RWKV7_REQUIRE(K % KB == 0, RWKV7_ERR_UNSUPPORTED, "w4g_gemv_tiled: K must be a multiple of %d (got %d)", KB, K);
     const int tiles = (Nout + TILE_N - 1) / TILE_N;
     const int total_kb = K / KB;
     int splits = 1;
     for (int s = 8; s >= 2; s >>= 1) {
-        if (tiles * s <= 160 && total_kb % s == 0 && (total_kb / s) >= 4) {
+        if (tiles * row_blocks * s <= 160 && total_kb % s == 0 && (total_kb / s) >= 4) {
             splits = s;
             break;
         }
@@ -394,7 +397,7 @@ int launch_w4g_umma_tiled(const void* x, const uint8_t* tw, const void* ts, cons
     cudaError_t e = cudaFuncSetAttribute(w4g_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     RWKV7_REQUIRE(e == cudaSuccess, RWKV7_ERR_CUDA, "w4g_gemv_tiled: %s", cudaGetErrorString(e));
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(tiles, 1, splits);
+    cfg.gridDim = dim3(tiles, row_blocks, splits);
     cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;

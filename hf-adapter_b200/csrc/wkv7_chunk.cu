@@ -1,8 +1,241 @@
-// Chunked (WY / DPLR) WKV-7 scan on tensor cores -- placeholder until the kernel lands.
-#include "common.cuh"
+// Chunked (WY / DPLR) WKV-7 prefill scan with the intra-chunk contractions on tcgen05 tensor cores.
+//
+// One CTA per (sequence, head) walks the sequence in tiles of 64 tokens (the result does not depend on the
+// tile length, so the caller's chunk size is only validated).  With a~ = -kk, b~ = kk*a, per-channel log-decay
+// sums gi (inclusive) / ge (exclusive), gl = gi at the tile end and a centring point gref = gi at token 31:
+//
+//   A1 = [ a~ e^{ge-gref} ; r e^{gi-gref} ]   (128 x 64, tf32)      B1 = [ k e^{gref-gi} ; b~ e^{gref-gi} ]  (128 x 64)
+//   D1 = A1 B1^T = [[A_ak A_ab],[A_qk A_qb]]  (128 x 128)           D2 = A1 (S0 e^{gref})^T = [ a~E S0^T ; rP S0^T ]
+//   rhs = D2[0:64] + tril_strict(A_ak) V      (fp16 MMA)            U = (I - tril_strict(A_ab))^-1 rhs   (CUDA cores)
+//   Y   = D2[64:128] + [tril(A_qk) tril(A_qb)] [V ; U]              S' = S0 e^{gl} + [V^T U^T] [k e^{gl-gi} ; b~ e^{gl-gi}]
+//
+// The decay-scaled factors span many orders of magnitude, so the products that contain them run as kind::tf32 on
+// operands rounded to tf32 in shared memory; the products of bounded quantities (A_* against V, U and the
+// end-of-tile-decayed keys) run as kind::f16.  All operands are written by the CTA's threads straight into
+// K-major 128-byte-swizzled tiles; accumulators D1/D2/D3 live in tensor memory (256 columns); the state row of
+// each value index stays in registers between tiles.  Every mbarrier wait is bounded (umma.cuh).
+#include "umma.cuh"
 
-extern "C" int rwkv7_wkv7_chunk_scan(const void*, const void*, const void*, const void*, const void*, const void*,
-                                     const float*, float*, void*, int, int, int, int, int, int, int, void*) {
-    rwkv7::set_error("wkv7_chunk_scan: not built in this library version");
-    return RWKV7_ERR_UNSUPPORTED;
+namespace rwkv7 {
+namespace ck {
+constexpr int C = 64, N = 64, THREADS = 256;
+constexpr int ABS = 68;  // row stride (floats) of the fp32 A_ab / rhs arrays: 16-byte aligned, conflict-free
+// shared-memory regions (bytes)
+constexpr int R_A = 0;                      // A1 (tf32 128x64) | later AE (fp16 128 x 128)
+constexpr int R_B = R_A + 32768;            // B1 (tf32 128x64) | later AB + RH (fp32 64 x 68 each)
+constexpr int R_S0 = R_B + 36864;           // S0 e^{gref} (tf32 64 x 64)
+constexpr int R_AK = R_S0 + 16384;          // tril_strict(A_ak) (fp16 128 x 64, rows 64.. zero)
+constexpr int R_VU = R_AK + 16384;          // [V^T | U^T] (fp16 128 x 128, rows 64.. zero)
+constexpr int R_KB = R_VU + 32768;          // [kD ; bD]^T (fp16 64 x 128)
+constexpr int R_RAW = R_KB + 16384;         // r,k,v,kk,a (T 64x64 each) + w (fp32 64x64)
+constexpr int R_SMALL = R_RAW + 5 * 8192 + 16384;
+constexpr int SMEM_BYTES = R_SMALL + 2048 + 1024;
+constexpr int D1_COL = 0, D2_COL = 128, D3_COL = 192, TMEM_COLS = 256;
+}  // namespace ck
+
+struct ChunkArgs {
+    const __half *r, *k, *v, *kk, *a;
+    const void* w;
+    const float* state_in;
+    float* state_out;
+    __half* y;
+    int T, H, w_mode;
+    unsigned int* error;
+};
+
+__device__ __forceinline__ float to_tf32(float x) {
+    uint32_t u;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
+    return __uint_as_float(u);
 }
+__device__ __forceinline__ void ck_cp16(void* smem, const void* g, bool valid) {
+    const int sz = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(smem)), "l"(g), "r"(sz));
+}
+
+__global__ void __launch_bounds__(ck::THREADS, 1) wkv7_chunk_kernel(const ChunkArgs p) {
+    using namespace ck;
+    extern __shared__ unsigned char smem_unaligned[];
+    unsigned char* sm = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);
+    float* AB = reinterpret_cast<float*>(sm + R_B);
+    float* RH = AB + C * ABS;
+    __half* raw_r = reinterpret_cast<__half*>(sm + R_RAW);
+    __half* raw_k = raw_r + 4096;
+    __half* raw_v = raw_k + 4096;
+    __half* raw_kk = raw_v + 4096;
+    __half* raw_a = raw_kk + 4096;
+    float* raw_w = reinterpret_cast<float*>(raw_a + 4096);
+    float* part = reinterpret_cast<float*>(sm + R_SMALL);  // [4][64] partial log-decay sums
+    float* gref = part + 256;                              // [64]
+    float* gl = gref + 64;                                 // [64]
+    uint64_t* bar = reinterpret_cast<uint64_t*>(gl + 64);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const AbortCtx actx{abort_flag, p.error};
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int q = warp & 3, hi = warp >> 2;  // TMEM lane quarter / column half
+    const int tl = q * 32 + lane;            // TMEM lane = accumulator row of this thread
+    const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
+    const size_t tok_stride = (size_t)p.H * N;
+    const size_t base = ((size_t)b * p.T * p.H + h) * N;
+    const int wbytes = p.w_mode == 1 ? 4 : 2;
+
+    if (tid == 0) {
+        mbar_init(bar, 1);
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 0) tmem_alloc(tmem_slot, TMEM_COLS);
+    // rows 64..127 of the fp16 A-operand tiles stay zero for the whole kernel
+    for (int i = tid; i < (16384 + 32768) / 16; i += THREADS) reinterpret_cast<uint4*>(sm + R_AK)[i] = make_uint4(0, 0, 0, 0);
+
+    // state row of value index i = tl (< 64), columns hi*32..+31, kept in registers across tiles
+    float S[32];
+    if (tl < 64) {
+        const float* sp = p.state_in + ((size_t)bh * N + tl) * N + hi * 32;
+#pragma unroll
+        for (int c = 0; c < 32; c += 4) {
+            const float4 t4 = *reinterpret_cast<const float4*>(sp + c);
+            S[c] = t4.x; S[c + 1] = t4.y; S[c + 2] = t4.z; S[c + 3] = t4.w;
+        }
+    }
+
+    auto load_raw = [&](int t0) {
+        // 5 x (64 tokens x 8 chunks) + w (64 x 8 or 16 chunks)
+        const int wch = 64 * wbytes / 16;
+        const int per_tok = 40 + wch;
+        for (int idx = tid; idx < C * per_tok; idx += THREADS) {
+            const int t = idx / per_tok, qq = idx % per_tok;
+            const bool valid = (t0 + t) < p.T;
+            const size_t goff = base + (size_t)(valid ? t0 + t : 0) * tok_stride;
+            if (qq < 40) {
+                const int which = qq >> 3, ch = qq & 7;
+                const __half* src = which == 0 ? p.r : which == 1 ? p.k : which == 2 ? p.v : which == 3 ? p.kk : p.a;
+                ck_cp16(raw_r + which * 4096 + t * 64 + ch * 8, src + goff + ch * 8, valid);
+            } else {
+                const int ch = qq - 40;
+                ck_cp16(reinterpret_cast<char*>(raw_w) + t * 64 * wbytes + ch * 16,
+                        reinterpret_cast<const char*>(p.w) + goff * wbytes + ch * 16, valid);
+            }
+        }
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16);
+    uint32_t phase = 0;
+    bool ok = true;
+    auto wait_mma = [&]() {  // one polling lane per warp; result broadcast
+        if (lane == 0) ok = mbar_wait(bar, phase, actx, kErrWaitDFull);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        phase ^= 1;
+        tc_fence_after();
+    };
+
+    const int ntiles = (p.T + C - 1) / C;
+    load_raw(0);
+    for (int tile = 0; tile < ntiles && ok; ++tile) {
+        const int t0 = tile * C;
+        asm volatile("cp.async.wait_group 0;\n" ::);
+        __syncthreads();
+        // ---------------- phase A: log-decay prefix sums, decay factors, operand tiles
+        const int n = tid & 63, tq = tid >> 6;
+        float lw[16];
+        {
+            float run = 0.f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const int t = tq * 16 + j;
+                float v = 0.f;
+                if (t0 + t < p.T) {
+                    if (p.w_mode == 1) v = logf(raw_w[t * 64 + n]);
+                    else {
+                        const float wv = __half2float(reinterpret_cast<const __half*>(raw_w)[t * 64 + n]);
+                        v = p.w_mode == 2 ? -0.606531f * sigmoidf_(wv) : logf(wv);
+                    }
+                }
+                run += v;
+                lw[j] = v;
+            }
+            part[tq * 64 + n] = run;
+        }
+        __syncthreads();
+        {
+            const float p0 = part[n], p1 = part[64 + n], p2 = part[128 + n], p3 = part[192 + n];
+            const float g_ref = p0 + p1, g_l = p0 + p1 + p2 + p3;
+            if (tq == 0) {
+                gref[n] = g_ref;
+                gl[n] = g_l;
+            }
+            float gi = tq == 0 ? 0.f : tq == 1 ? p0 : tq == 2 ? p0 + p1 : p0 + p1 + p2;
+#pragma unroll
+            for (int j = 0; j < 16; j += 2) {
+                float kd[2], bd[2];
+                __half vv[2];
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const int t = tq * 16 + j + u;
+                    const float ge = gi;
+                    gi += lw[j + u];
+                    const float f1 = expf(gi - g_ref), f2 = expf(ge - g_ref), f3 = expf(g_ref - gi), f4 = expf(g_l - gi);
+                    const float rr = __half2float(raw_r[t * 64 + n]), kx = __half2float(raw_k[t * 64 + n]);
+                    const float kkx = __half2float(raw_kk[t * 64 + n]), ax = __half2float(raw_a[t * 64 + n]);
+                    const float bx = kkx * ax;
+                    *reinterpret_cast<float*>(sm + R_A + sw128_offset(t, n * 4, 128)) = to_tf32(-kkx * f2);
+                    *reinterpret_cast<float*>(sm + R_A + sw128_offset(64 + t, n * 4, 128)) = to_tf32(rr * f1);
+                    *reinterpret_cast<float*>(sm + R_B + sw128_offset(t, n * 4, 128)) = to_tf32(kx * f3);
+                    *reinterpret_cast<float*>(sm + R_B + sw128_offset(64 + t, n * 4, 128)) = to_tf32(bx * f3);
+                    kd[u] = kx * f4;
+                    bd[u] = bx * f4;
+                    vv[u] = raw_v[t * 64 + n];
+                }
+                const int t = tq * 16 + j;  // even: (t, t+1) share one 4-byte word of the transposed tiles
+                *reinterpret_cast<__half2*>(sm + R_KB + sw128_offset(n, t * 2, 64)) = __floats2half2_rn(kd[0], kd[1]);
+                *reinterpret_cast<__half2*>(sm + R_KB + sw128_offset(n, (64 + t) * 2, 64)) = __floats2half2_rn(bd[0], bd[1]);
+                *reinterpret_cast<__half2*>(sm + R_VU + sw128_offset(n, t * 2, 128)) = __halves2half2(vv[0], vv[1]);
+            }
+        }
+        __syncthreads();  // gref / gl visible; raw buffer consumed
+        if (tile + 1 < ntiles) load_raw(t0 + C);
+        if (tl < 64) {  // S0 e^{gref} operand tile and the D3 accumulator initialised with S0 e^{gl}
+            uint32_t d3[32];
+#pragma unroll
+            for (int c = 0; c < 32; c += 4) {
+                float4 o;
+                o.x = to_tf32(S[c] * expf(gref[hi * 32 + c]));
+                o.y = to_tf32(S[c + 1] * expf(gref[hi * 32 + c + 1]));
+                o.z = to_tf32(S[c + 2] * expf(gref[hi * 32 + c + 2]));
+                o.w = to_tf32(S[c + 3] * expf(gref[hi * 32 + c + 3]));
+                *reinterpret_cast<float4*>(sm + R_S0 + sw128_offset(tl, (hi * 32 + c) * 4, 64)) = o;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) d3[c + e] = __float_as_uint(S[c + e] * expf(gl[hi * 32 + c + e]));
+            }
+            tmem_st16(lane_addr + D3_COL + hi * 32, reinterpret_cast<uint32_t(&)[16]>(d3[0]));
+            tmem_st16(lane_addr + D3_COL + hi * 32 + 16, reinterpret_cast<uint32_t(&)[16]>(d3[16]));
+            tc_wait_st();
+        }
+        fence_proxy_async_smem();
+        tc_fence_before();
+        __syncthreads();
+        // ---------------- phase B: D1 = A1 B1^T, D2 = A1 S0^T (tf32)
+        if (tid == 0) {
+            tc_fence_after();
+            constexpr uint32_t id128 = make_idesc(128, 128, 1, 2, 2), id64 = make_idesc(128, 64, 1, 2, 2);
+            const uint64_t da = make_sw128_kmajor_desc(smem_u32(sm + R_A));
+            const uint64_t db = make_sw128_kmajor_desc(smem_u32(sm + R_B));
+            const uint64_t ds = make_sw128_kmajor_desc(smem_u32(sm + R_S0));
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint64_t oa = (uint64_t)(((j >> 2) * 128 * 128 + (j & 3) * 32) >> 4);
+                const uint64_t os = (uint64_t)(((j >> 2) * 64 * 128 + (j & 3) * 32) >> 4);
+                umma_tf32_ss(tmem + D1_COL, da + oa, db + oa, id128, j > 0);
+                umma_tf32_ss(tmem + D2_COL, da + oa, ds + os, id64, j > 0);
+            }
+            tc_commit(bar);
+        }
+        wait_mma();
+        if (!ok) break;

@@ -31,7 +31,7 @@ def dense_small(x, weight, bias=None, *, act_in: int = 0, act_out: int = 0, out=
 
 def small_gemm_group(xs, weights, biases=None, acts=None, outs=None):
     """One launch for up to four independent small linears ``out_i = act_i(x_i @ W_i.T + b_i)`` sharing the row
-    count (<= 64 rows, fp16/bf16: tensor-core kernel; otherwise one ``dense_small`` call per problem)."""
+    count (fp16/bf16: tensor-core kernel, 64-row blocks; fp32: one ``dense_small`` call per problem)."""
     n = len(xs)
     biases = list(biases) if biases is not None else [None] * n
     acts = list(acts) if acts is not None else [0] * n
@@ -43,7 +43,7 @@ def small_gemm_group(xs, weights, biases=None, acts=None, outs=None):
             raise ValueError("all problems must have the same number of rows")
         if w.dim() != 2 or int(w.shape[1]) != int(x.shape[1]):
             raise ValueError(f"weight must be [out, {int(x.shape[1])}], got {tuple(w.shape)}")
-    if M > 64 or x2[0].dtype == torch.float32 or n > 4 or any(int(w.shape[1]) % 8 for w in ws):
+    if M > 16384 or x2[0].dtype == torch.float32 or n > 4 or any(int(w.shape[1]) % 8 for w in ws):
         res = [dense_small(x, w, b, act_out=a) for x, w, b, a in zip(xs, ws, biases, acts)]
         if outs is not None:
             for o, r in zip(outs, res):

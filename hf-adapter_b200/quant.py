@@ -23,6 +23,7 @@ from . import _lib
 from ._util import dt_code, ptr, require_cuda, stream_ptr
 
 GEMV_MAX_ROWS = 64  # rows up to which the weight-streaming kernels are used; above: dequantise + GEMM
+TILED_MAX_ROWS = 512  # rows up to which MM4Linear uses the tensor-core decode kernel (one weight pass per 64 rows)
 
 
 # ------------------------------------------------------------------ quantisers (load time)
@@ -317,7 +318,7 @@ class MM4Linear(torch.nn.Module):
 
     def _lin(self, x, **kw):
         rows = x.numel() // self.in_features
-        if rows <= GEMV_MAX_ROWS and x.dtype == torch.float16 and x.is_cuda and self.in_features % 128 == 0:
+        if rows <= TILED_MAX_ROWS and x.dtype == torch.float16 and x.is_cuda and self.in_features % 128 == 0:
             # decode: tensor-core kernel on the tiled copy (built once per device, on first use)
             t = self._tiled
             if t is None or t[0].device != x.device:

@@ -145,7 +145,7 @@ int rwkv7_dense_small(const void* x, const void* W, const void* bias, void* out,
 /* The same for up to four independent problems in ONE launch (the four rank-R "down" projections, or the four "up"
  * projections, of a layer: the reference's _wavg_lora_down_kernel / _wavg_lora_up_kernel pair,
  * rwkv7_hf/fused_lora.py:244-384), on warp-level tensor-core MMA with split-K inside a thread-block cluster.
- * Arrays have n_problems entries; bias may be NULL or hold NULL entries; M <= 64 rows; fp16 or bf16.
+ * Arrays have n_problems entries; bias may be NULL or hold NULL entries; any M (64-row blocks); fp16 or bf16.
  *   out_p[M,Nout_p] = act_out_p( x_p[M,K_p] . W_p[Nout_p,K_p]^T + bias_p ) */
 int rwkv7_small_gemm_group(int n_problems, const void* const* x, const void* const* W, const void* const* bias,
                            void* const* out, const int* K, const int* Nout, const int* act_out, int M, int dtype,
@@ -176,7 +176,7 @@ int rwkv7_w4g_gemv(const void* x, const uint8_t* packed, const void* scales, con
                    const void* residual, void* out, int M, int K, int Nout, int group, int epilogue,
                    int dtype, void* stream);
 
-/* Tensor-core version of the same projection for 1..64 rows, reading a TILED copy of the weights built once at load
+/* Tensor-core version of the same projection (any row count, one pass over the weights per 64 rows), reading a TILED copy of the weights built once at load
  * time by rwkv7_w4g_repack (8 KiB per [128 channels x 128 k] tile, tiles of a channel block consecutive, so each CTA
  * streams one contiguous region; scales / zero-points re-laid per tile).  Same values, same arithmetic as above.
  * rwkv7_w4g_tiled_bytes returns the byte size of the tiled weight buffer (0 for unsupported shapes) and, through

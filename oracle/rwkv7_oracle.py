@@ -455,6 +455,8 @@ def linear_op(x, op, hi=False):
     """A projection operand: dense [out,in] array, or a dict describing one of
     the quantised formats (keys: kind in {'w4g','w8','a8w8'})."""
     dt = np.asarray(x).dtype
+    if callable(op):  # e.g. a sharded projection followed by a cross-rank sum (tensor-parallel tests)
+        return op(x)
     if isinstance(op, dict):
         kind = op["kind"]
         if kind == "w4g":

@@ -201,7 +201,7 @@ def test_norm_mix_shapes(rows, D):
     np.testing.assert_allclose(npf(ln), O.layer_norm(x, nw, nb).astype(np.float32), rtol=4e-3, atol=4e-3)
 
 
-@pytest.mark.parametrize("M", [1, 5, 64])
+@pytest.mark.parametrize("M", [1, 5, 64, 130])
 def test_grouped_lora_gemm_against_oracle(M):
     """The one-launch grouped projection (tensor-core MMA, cluster split-K) for decode-size LoRA shapes."""
     from hf_adapter_b200.lora import small_gemm_group
