@@ -366,7 +366,8 @@ def main():
         ws = torch.exp(-0.606531 * torch.sigmoid(torch.randn(Bs, Ts, Hs, N, device=dev)))
         s0 = torch.zeros(Bs, Hs, N, N, device=dev)
         scan = {}
-        for name, fn in (("sequential", lambda: hb.fused_recurrent_scan(rs, ws, ks, vs, kks, as_, s0)),):
+        for name, fn in (("sequential", lambda: hb.fused_recurrent_scan(rs, ws, ks, vs, kks, as_, s0)),
+                         ("chunked_tcgen05", lambda: hb.self_chunk_rwkv7(rs, ws, ks, vs, kks, as_, s0, chunk_size=64))):
             fn()
             torch.cuda.synchronize()
             s_0, s_1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -377,7 +378,9 @@ def main():
             torch.cuda.synchronize()
             sms = s_0.elapsed_time(s_1) / 3
             sbytes = 5 * Bs * Ts * Hs * N * 2 + Bs * Ts * Hs * N * 4 + Bs * Ts * Hs * N * 2 + 2 * Bs * Hs * N * N * 4
-            scan[name] = {"ms": sms, "tok_per_s": Bs * Ts / (sms * 1e-3), "hbm_frac": sbytes / (sms * 1e-3) / 1e9 / hbm_peak}
+            flops = Bs * Ts * Hs * (16 * 64 * N + 8 * N * N + 2 * 64 * 64)  # chunked-form tensor flops, C = 64
+            scan[name] = {"ms": sms, "tok_per_s": Bs * Ts / (sms * 1e-3), "hbm_frac": sbytes / (sms * 1e-3) / 1e9 / hbm_peak,
+                          "tensor_frac_of_bf16_peak": flops / (sms * 1e-3) / 1e12 / tc_peak}
         del rs, ks, vs, kks, as_, ws
         torch.cuda.empty_cache()
 

@@ -239,3 +239,193 @@ __global__ void __launch_bounds__(ck::THREADS, 1) wkv7_chunk_kernel(const ChunkA
         }
         wait_mma();
         if (!ok) break;
+        // ---------------- phase C: mask D1 into tril_strict(A_ak) (fp16), tril_strict(A_ab) (fp32), [tril A_qk | tril A_qb] (fp16)
+        for (int i = tid; i < 1024; i += THREADS) {  // rows 0..63 of both AE atoms are zero
+            const int atom = i >> 9, rem = i & 511;
+            reinterpret_cast<uint4*>(sm + R_A + atom * 16384)[rem] = make_uint4(0, 0, 0, 0);
+        }
+        {
+            const int t = tl & 63;
+            const bool low = tl < 64;  // rows of a~E (low) or rP (high)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t v[16];
+                tmem_ld16(lane_addr + D1_COL + hi * 64 + c * 16, v);
+                tc_wait_ld();
+                if (low && hi == 1) {  // A_ab, strict lower triangle, fp32
+#pragma unroll
+                    for (int e = 0; e < 16; e += 4) {
+                        const int s = c * 16 + e;
+                        float4 o;
+                        o.x = (s + 0 < t) ? __uint_as_float(v[e + 0]) : 0.f;
+                        o.y = (s + 1 < t) ? __uint_as_float(v[e + 1]) : 0.f;
+                        o.z = (s + 2 < t) ? __uint_as_float(v[e + 2]) : 0.f;
+                        o.w = (s + 3 < t) ? __uint_as_float(v[e + 3]) : 0.f;
+                        *reinterpret_cast<float4*>(AB + t * ABS + s) = o;
+                    }
+                } else {
+                    uint32_t pk[8];
+#pragma unroll
+                    for (int e = 0; e < 16; e += 2) {
+                        const int s = c * 16 + e;
+                        const bool k0 = low ? (s < t) : (s <= t), k1 = low ? (s + 1 < t) : (s + 1 <= t);
+                        const __half2 h2 = __floats2half2_rn(k0 ? __uint_as_float(v[e]) : 0.f, k1 ? __uint_as_float(v[e + 1]) : 0.f);
+                        pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&h2);
+                    }
+                    unsigned char* dst = low ? sm + R_AK + sw128_offset(t, c * 32, 128)
+                                             : sm + R_A + sw128_offset(64 + t, (hi * 64 + c * 16) * 2, 128);
+                    // 16 halves = two 16-byte chunks (chunk index differs by one: separate swizzled addresses)
+                    *reinterpret_cast<uint4*>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    unsigned char* dst2 = low ? sm + R_AK + sw128_offset(t, c * 32 + 16, 128)
+                                              : sm + R_A + sw128_offset(64 + t, (hi * 64 + c * 16) * 2 + 16, 128);
+                    *reinterpret_cast<uint4*>(dst2) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                }
+            }
+        }
+        fence_proxy_async_smem();
+        tc_fence_before();
+        __syncthreads();
+        // ---------------- phase C2: rhs = D2[0:64] += tril_strict(A_ak) V   (fp16, K = 64)
+        if (tid == 0) {
+            tc_fence_after();
+            constexpr uint32_t idh = make_idesc(128, 64, 1, 0, 0);
+            const uint64_t da = make_sw128_kmajor_desc(smem_u32(sm + R_AK));
+            const uint64_t db = make_sw128_kmajor_desc(smem_u32(sm + R_VU));
+#pragma unroll
+            for (int j = 0; j < 4; ++j) umma_f16_ss(tmem + D2_COL, da + (uint64_t)(j * 2), db + (uint64_t)(j * 2), idh, 1);
+            tc_commit(bar);
+        }
+        wait_mma();
+        if (!ok) break;
+        // ---------------- phase D: U = (I - tril_strict(A_ab))^-1 rhs  (forward substitution, one thread per value column)
+        if (tl < 64) {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                uint32_t v[16];
+                tmem_ld16(lane_addr + D2_COL + hi * 32 + c * 16, v);
+                tc_wait_ld();
+#pragma unroll
+                for (int e = 0; e < 16; e += 4)
+                    *reinterpret_cast<float4*>(RH + tl * ABS + hi * 32 + c * 16 + e) =
+                        make_float4(__uint_as_float(v[e]), __uint_as_float(v[e + 1]), __uint_as_float(v[e + 2]), __uint_as_float(v[e + 3]));
+            }
+        }
+        tc_fence_before();
+        __syncthreads();
+        if (tid < 64) {
+            float U[64];
+#pragma unroll
+            for (int t = 0; t < 64; ++t) {
+                float a0 = RH[t * ABS + tid], a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+                for (int s = 0; s + 3 < t; s += 4) {
+                    const float4 m = *reinterpret_cast<const float4*>(AB + t * ABS + s);
+                    a0 = fmaf(m.x, U[s], a0); a1 = fmaf(m.y, U[s + 1], a1);
+                    a2 = fmaf(m.z, U[s + 2], a2); a3 = fmaf(m.w, U[s + 3], a3);
+                }
+#pragma unroll
+                for (int s = t & ~3; s < t; ++s) a0 = fmaf(AB[t * ABS + s], U[s], a0);
+                U[t] = (a0 + a1) + (a2 + a3);
+            }
+            // U^T into the second K atom of [V^T | U^T]: row = value index, k = 64 + token
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                uint32_t pk[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const __half2 h2 = __floats2half2_rn(U[c * 8 + 2 * e], U[c * 8 + 2 * e + 1]);
+                    pk[e] = *reinterpret_cast<const uint32_t*>(&h2);
+                }
+                *reinterpret_cast<uint4*>(sm + R_VU + sw128_offset(tid, (64 + c * 8) * 2, 128)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
+        }
+        fence_proxy_async_smem();
+        __syncthreads();
+        // ---------------- phase E / F: Y = D2[64:128] += [A_qk A_qb][V;U];  S' = D3 += [V^T U^T][kD;bD]   (fp16, K = 128)
+        if (tid == 0) {
+            tc_fence_after();
+            constexpr uint32_t idh = make_idesc(128, 64, 1, 0, 0);
+            const uint64_t dae = make_sw128_kmajor_desc(smem_u32(sm + R_A));
+            const uint64_t dvu = make_sw128_kmajor_desc(smem_u32(sm + R_VU));
+            const uint64_t dkb = make_sw128_kmajor_desc(smem_u32(sm + R_KB));
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint64_t o128 = (uint64_t)(((j >> 2) * 128 * 128 + (j & 3) * 32) >> 4);
+                const uint64_t o64 = (uint64_t)(((j >> 2) * 64 * 128 + (j & 3) * 32) >> 4);
+                umma_f16_ss(tmem + D2_COL, dae + o128, dvu + o128, idh, 1);
+                umma_f16_ss(tmem + D3_COL, dvu + o128, dkb + o64, idh, 1);
+            }
+            tc_commit(bar);
+        }
+        wait_mma();
+        if (!ok) break;
+        // ---------------- phase G: outputs of the tile, new state rows back to registers
+        {
+            uint32_t v[32];
+            const uint32_t col = (tl < 64 ? D3_COL : D2_COL) + hi * 32;
+            tmem_ld16(lane_addr + col, reinterpret_cast<uint32_t(&)[16]>(v[0]));
+            tmem_ld16(lane_addr + col + 16, reinterpret_cast<uint32_t(&)[16]>(v[16]));
+            tc_wait_ld();
+            if (tl < 64) {
+#pragma unroll
+                for (int c = 0; c < 32; ++c) S[c] = __uint_as_float(v[c]);
+            } else {
+                const int t = tl - 64;
+                if (t0 + t < p.T) {
+                    __half* yp = p.y + base + (size_t)(t0 + t) * tok_stride + hi * 32;
+#pragma unroll
+                    for (int c = 0; c < 32; c += 8) {
+                        uint32_t pk[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const __half2 h2 = __floats2half2_rn(__uint_as_float(v[c + 2 * e]), __uint_as_float(v[c + 2 * e + 1]));
+                            pk[e] = *reinterpret_cast<const uint32_t*>(&h2);
+                        }
+                        *reinterpret_cast<uint4*>(yp + c) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    }
+                }
+            }
+        }
+        tc_fence_before();
+        __syncthreads();  // accumulators and operand tiles are free for the next tile
+    }
+
+    asm volatile("cp.async.wait_group 0;\n" ::);
+    if (tl < 64 && *abort_flag == 0) {
+        float* sp = p.state_out + ((size_t)bh * N + tl) * N + hi * 32;
+#pragma unroll
+        for (int c = 0; c < 32; c += 4) *reinterpret_cast<float4*>(sp + c) = make_float4(S[c], S[c + 1], S[c + 2], S[c + 3]);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        tmem_dealloc(tmem, TMEM_COLS);
+    }
+}
+
+}  // namespace rwkv7
+
+using namespace rwkv7;
+
+extern "C" int rwkv7_wkv7_chunk_scan(const void* r, const void* w, const void* k, const void* v, const void* kk, const void* a,
+                                     const float* state_in, float* state_out, void* y, int B, int T, int H, int N, int chunk,
+                                     int dtype, int w_mode, void* stream) {
+    RWKV7_REQUIRE(N == 64, RWKV7_ERR_UNSUPPORTED, "wkv7_chunk_scan: head size must be 64, got %d", N);
+    RWKV7_REQUIRE(dtype == RWKV7_F16, RWKV7_ERR_UNSUPPORTED, "wkv7_chunk_scan: fp16 activations only");
+    RWKV7_REQUIRE(chunk == 16 || chunk == 32 || chunk == 64, RWKV7_ERR_UNSUPPORTED, "wkv7_chunk_scan: chunk must be 16, 32 or 64");
+    RWKV7_REQUIRE(B > 0 && H > 0 && T > 0 && T % chunk == 0, RWKV7_ERR_INVALID,
+                  "wkv7_chunk_scan: B, H, T must be positive and T a multiple of chunk (B=%d T=%d H=%d chunk=%d)", B, T, H, chunk);
+    RWKV7_REQUIRE(w_mode >= 0 && w_mode <= 2, RWKV7_ERR_INVALID, "wkv7_chunk_scan: w_mode must be 0, 1 or 2");
+    RWKV7_REQUIRE(r && w && k && v && kk && a && state_in && state_out && y, RWKV7_ERR_INVALID, "wkv7_chunk_scan: null pointer");
+    const void* ptrs[] = {r, w, k, v, kk, a, state_in, state_out, y};
+    for (const void* q : ptrs) RWKV7_REQUIRE(aligned(q, 16), RWKV7_ERR_ALIGN, "wkv7_chunk_scan: pointers must be 16-byte aligned");
+    ChunkArgs p{reinterpret_cast<const __half*>(r), reinterpret_cast<const __half*>(k), reinterpret_cast<const __half*>(v),
+                reinterpret_cast<const __half*>(kk), reinterpret_cast<const __half*>(a), w, state_in, state_out,
+                reinterpret_cast<__half*>(y), T, H, w_mode, kernel_error_word()};
+    RWKV7_REQUIRE(p.error != nullptr, RWKV7_ERR_CUDA, "wkv7_chunk_scan: cannot resolve the device error word");
+    cudaError_t e = cudaFuncSetAttribute(wkv7_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ck::SMEM_BYTES);
+    RWKV7_REQUIRE(e == cudaSuccess, RWKV7_ERR_CUDA, "wkv7_chunk_scan: %s", cudaGetErrorString(e));
+    wkv7_chunk_kernel<<<B * H, ck::THREADS, ck::SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(p);
+    return check_launch("wkv7_chunk_kernel");
+}

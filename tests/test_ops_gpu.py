@@ -226,3 +226,56 @@ def test_grouped_lora_gemm_against_oracle(M):
     (y1,) = small_gemm_group((cu(x1),), (cu(w1),), (cu(b1),), acts=(1,))
     ref = np.tanh((x1.astype(np.float32) @ w1.astype(np.float32).T + b1.astype(np.float32)).astype(np.float16).astype(np.float32))
     np.testing.assert_allclose(npf(y1), ref, rtol=4e-3, atol=4e-3)
+
+
+@pytest.mark.parametrize("B,T,Hh,chunk", [(1, 64, 1, 64), (2, 128, 3, 16), (2, 192, 2, 32), (1, 1024, 2, 64)])
+def test_chunk_scan_tensor_core_against_oracle(B, T, Hh, chunk):
+    """tcgen05 chunked WY scan == the sequential recurrence (fp64 oracle on the same fp16 inputs):
+    state relative error <= 1e-3, outputs within fp16 tolerance, no bounded wait gave up."""
+    from hf_adapter_b200 import _lib
+    r, w, k, v, kk, a = wkv_inputs(B, T, Hh, N, seed=T + chunk)
+    rng = np.random.default_rng(T)
+    s0 = (0.1 * rng.standard_normal((B, Hh, N, N))).astype(np.float32)
+    yo, so = O.recurrent_scan(r, w, k, v, kk, a, s0, hi=True)
+    _lib.kernel_status(True)
+    args = [cu(x) for x in (r, w, k, v, kk, a, s0)]
+    y, s = hb.self_chunk_rwkv7(*args, chunk_size=chunk)
+    assert _lib.kernel_status(True) == 0
+    assert rel_err(npf(s), so) < 1e-3
+    scale = max(1.0, float(np.abs(yo.astype(np.float32)).max()))
+    np.testing.assert_allclose(npf(y), yo.astype(np.float32), rtol=4e-3, atol=4e-3 * scale)
+    assert rel_err(npf(y), yo.astype(np.float32)) < 2e-3
+    y2, s2 = hb.dplr_chunk_scan(*args, chunk_size=chunk, algorithm="wy")
+    assert torch.equal(y2, y) and torch.equal(s2, s)
+    # the sequential kernel and the chunked kernel agree with each other as well
+    y3, s3 = hb.fused_recurrent_scan(*args)
+    assert rel_err(npf(s3), npf(s)) < 1e-3
+    # decay in the activation dtype / raw w
+    y16, s16 = hb.self_chunk_rwkv7(args[0], cu(w.astype(np.float16)), *args[2:], chunk_size=chunk)
+    yo16, so16 = O.recurrent_scan(r, w.astype(np.float16), k, v, kk, a, s0, hi=True)
+    assert rel_err(npf(s16), so16) < 1e-3
+    with pytest.raises(ValueError):
+        hb.self_chunk_rwkv7(*args, chunk_size=48)
+
+
+def test_scan_full_size_config2():
+    """Isolated WKV-7 op at the benchmark's size (B8 T4096 H32 N64, zero state): chunked tensor-core scan vs the
+    sequential kernel over all heads (state rel-err <= 1e-3, outputs <= 2e-3 relative), and both against the fp64
+    oracle on a two-head slice (the oracle needs seconds per head at this length)."""
+    B, T, Hh = 8, 4096, 32
+    g = torch.Generator(device="cuda").manual_seed(0)
+    rn = lambda *s: torch.randn(*s, device="cuda", generator=g)
+    r, k, v = (rn(B, T, Hh, N).half() for _ in range(3))
+    kk = torch.nn.functional.normalize(k.float(), dim=-1).half()
+    a = torch.sigmoid(rn(B, T, Hh, N)).half()
+    w = torch.exp(-0.606531 * torch.sigmoid(rn(B, T, Hh, N)))
+    s0 = torch.zeros(B, Hh, N, N, device="cuda")
+    ys, ss = hb.fused_recurrent_scan(r, w, k, v, kk, a, s0)
+    yc, sc = hb.self_chunk_rwkv7(r, w, k, v, kk, a, s0, chunk_size=64)
+    assert rel_err(npf(sc), npf(ss)) < 1e-3
+    assert rel_err(npf(yc), npf(ys)) < 2e-3
+    sl = lambda t: t[:1, :, :2].contiguous().cpu().numpy()
+    yo, so = O.recurrent_scan(sl(r), sl(w), sl(k), sl(v), sl(kk), sl(a), np.zeros((1, 2, N, N), np.float32), hi=True)
+    for s_gpu, y_gpu in ((ss, ys), (sc, yc)):
+        assert rel_err(npf(s_gpu[:1, :2]), so) < 1e-3
+        assert rel_err(npf(y_gpu[:1, :, :2]), yo.astype(np.float32)) < 2e-3
