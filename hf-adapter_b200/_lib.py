@@ -38,9 +38,9 @@ SIGNATURES = {
     "rwkv7_prefill_state_prep": (I, [P] * 12 + [I, I, I, I, I, I, I, P]),
     "rwkv7_attn_output_prepare": (I, [P] * 9 + [I, I, I, F, I, P]),
     "rwkv7_w4g_gemv": (I, [P] * 6 + [I, I, I, I, I, I, P]),
-    "rwkv7_w4g_tiled_bytes": (L, [I, I, ctypes.POINTER(c_int64)]),
-    "rwkv7_w4g_repack": (I, [P] * 6 + [I, I, I, I, P]),
-    "rwkv7_w4g_gemv_tiled": (I, [P] * 6 + [I, I, I, I, I, P]),
+    "rwkv7_w4g_tiled_bytes": (L, [I, I]),
+    "rwkv7_w4g_repack": (I, [P] * 4 + [I, I, I, I, P]),
+    "rwkv7_w4g_gemv_tiled": (I, [P] * 4 + [I, I, I, I, I, P]),
     "rwkv7_w8_gemv": (I, [P] * 5 + [I, I, I, I, I, P]),
     "rwkv7_w4g_dequant": (I, [P] * 4 + [I, I, I, I, P]),
     "rwkv7_w8_dequant": (I, [P] * 3 + [I, I, I, P]),

@@ -83,6 +83,11 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* t
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(smem_u32(smem_dst)), "l"(tmap), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* tmap, uint64_t* bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(tmap), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
@@ -214,6 +219,29 @@ inline int make_tmap_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes
     if (r != CUDA_SUCCESS) {
         set_error("cuTensorMapEncodeTiled failed with code %d (rows=%llu cols=%llu box=%ux%u)", (int)r,
                   (unsigned long long)rows, (unsigned long long)cols, box_rows, box_cols);
+        return RWKV7_ERR_CUDA;
+    }
+    return RWKV7_OK;
+}
+
+// fp16 activations x[rows, K] viewed as (k_in = 64, row, k_out = K/64) so that ONE box {64, box_rows, 2} lands two
+// consecutive 64-k swizzle atoms [k_out][row][128 B] -- the K-major SW128 operand layout for 128 k.
+inline int make_tmap_x3d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, uint32_t box_rows) {
+    EncodeTiledFn fn = get_encode_tiled();
+    if (!fn) {
+        set_error("cuTensorMapEncodeTiled is unavailable (no CUDA driver?)");
+        return RWKV7_ERR_CUDA;
+    }
+    cuuint64_t dims[3] = {64, rows, K / 64};
+    cuuint64_t strides[2] = {K * 2, 128};
+    cuuint32_t box[3] = {64, box_rows, 2};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled (3-D activation map) failed with code %d (rows=%llu K=%llu)", (int)r,
+                  (unsigned long long)rows, (unsigned long long)K);
         return RWKV7_ERR_CUDA;
     }
     return RWKV7_OK;

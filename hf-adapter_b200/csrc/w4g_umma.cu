@@ -7,8 +7,8 @@
 // around keeping shared-memory traffic low, which is what otherwise caps a dequantising GEMM:
 //
 //   * the weights are read from a TILED copy of the reference's [Nout, K/2] array (rwkv7_w4g_repack, built once
-//     at load): one 8 KiB block per [128 channels x 128 k] tile, blocks of a channel tile consecutive in memory,
-//     so every CTA streams one contiguous region with 8 KiB bulk copies -- row-strided 64-byte pieces of the
+//     at load): one 8.5 KiB block per [128 channels x 128 k] tile (nibbles, then the tile's scales and zero-points),
+//     blocks of a channel tile consecutive in memory, so every CTA streams one contiguous region, one bulk copy per block -- row-strided 64-byte pieces of the
 //     row-major array reach under 1 TB/s on HBM3e, contiguous blocks run at copy speed;
 //   * four dequant warps (thread = output channel) read their 64 packed bytes, expand them to 128
 //     fp16 values in registers (lop3 magic-number conversion, exact (q - zero), one fp16 rounding
@@ -21,8 +21,9 @@
 //     shared memory in a fixed order (deterministic, no scratch buffer, no atomics), then the
 //     relu^2 / residual epilogue is applied and fp16 results are stored coalesced.
 //
-// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = TMEM allocator + MMA issuer, warps 2-9 = two
-// dequantise groups (even / odd k-blocks) + epilogue.  All mbarrier waits are bounded (umma.cuh).
+// Warp roles: warp 0 = weight-stream producer, last warp = activation-tile producer, warp 1 and the last but one =
+// MMA issuers (warp 1 also owns the TMEM allocation), warps 2..2+4*SB-1 = SB dequantise groups (k-block i of a
+// super-block goes to group i) + epilogue.  All mbarrier waits are bounded (umma.cuh).
 #include <cooperative_groups.h>
 
 #include "umma.cuh"
@@ -35,26 +36,27 @@ namespace w4 {
 constexpr int TILE_N = 128;  // output channels per CTA = UMMA M
 constexpr int KB = 128;      // k elements per pipeline stage
 constexpr int NB = 64;       // activation rows per MMA = UMMA N
-constexpr int STAGES = 6;
-constexpr int RAW_BYTES = TILE_N * KB / 2;  // 8192
-constexpr int SC_BYTES = TILE_N * 2;        // per-channel fp16 scale of the k-block
-constexpr int Z_BYTES = TILE_N;             // per-channel zero-point of the k-block
-constexpr int META_BYTES = 512;             // scales + zeros, padded
+constexpr int STAGES = 6;    // activation-tile ring (L2-resident source, freed by the MMA commit)
+constexpr int WSTAGES = 12;  // weight-block ring (HBM source, freed as soon as the dequant warps have read it)
+constexpr int RAW_BYTES = TILE_N * KB / 2;  // 8192 packed nibbles
+constexpr int SC_OFF = RAW_BYTES;           // then 128 fp16 scales of the k-block
+constexpr int Z_OFF = SC_OFF + TILE_N * 2;  // then 128 u8 zero-points, then padding
+constexpr int BLOCK_BYTES = 8704;           // one tile block in memory = one bulk copy (68 x 128 B)
 constexpr int XATOM_BYTES = NB * 128;       // one 64-k swizzle atom of the activation tile
 constexpr int X_BYTES = 2 * XATOM_BYTES;    // 16384
-constexpr int STAGE_BYTES = RAW_BYTES + SC_BYTES + Z_BYTES + X_BYTES;  // bytes that land per stage
-constexpr int SB = 2;            // k-blocks per super-block = dequant warp groups
-constexpr int NAB = 3;           // super-block A buffers in tensor memory (SB x 64 columns each)
+constexpr int SB = 3;            // k-blocks per super-block = dequant warp groups
+constexpr int NAB = 2;           // super-block A buffers in tensor memory (SB x 64 columns each)
 constexpr int NA = NAB;          // barrier pairs for the A buffers
-constexpr int TMEM_COLS = 512;   // A: NAB x SB x 64 columns, D: 64 columns
+constexpr int NISS = 2;          // MMA issuer warps, each with its own accumulator (summed in the epilogue)
+constexpr int TMEM_COLS = 512;   // A: NAB x SB x 64 columns, D: NISS x 64 columns
 constexpr int D_COL = NAB * SB * 64;
-constexpr int THREADS = 64 + SB * 128;
+constexpr int ISS2_WARP = 2 + SB * 4;           // second issuer = last warp
+constexpr int XPROD_WARP = ISS2_WARP + 1;       // activation-tile producer
+constexpr int THREADS = 64 + SB * 128 + 64;
 }  // namespace w4
 
 struct W4UmmaArgs {
-    const uint8_t* tw;   // tiled weights  [tiles][K/128][4 chunks][128 channels][16 B]
-    const __half* ts;    // tiled scales   [tiles][K/128][128]
-    const uint8_t* tz;   // tiled zeros    [tiles][K/128][128]
+    const uint8_t* tw;   // tiled weights: [tiles][K/128] blocks of BLOCK_BYTES = [4 chunks][128 channels][16 B] | scales | zeros
     const __half* residual;
     __half* out;
     int M, K, Nout, epilogue, nkb, kbt, splits;  // kbt = K / 128 (k-blocks per channel tile)
@@ -92,14 +94,17 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
     extern __shared__ unsigned char smem_unaligned[];
     // the swizzled TMA / UMMA tiles need 1024-byte alignment; the offset is the same in every CTA
     unsigned char* smem = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);
-    // [stage][x atom 0 | x atom 1] | [stage][raw] | [stage][scales | zeros] | barriers
+    // [x stage][atom 0 | atom 1] | [weight stage][nibbles | scales | zeros] | barriers.  Two independent rings: the
+    // recycle latency of a stage (consumer release -> producer wake-up -> copy latency) bounds the throughput of
+    // a ring, and a weight block can be released ~10x earlier than the activation tile the MMAs still read.
     unsigned char* xs = smem;
     unsigned char* raws = smem + STAGES * X_BYTES;
-    unsigned char* metas = raws + STAGES * RAW_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(metas + STAGES * META_BYTES);
-    uint64_t* full = bars;                   // [STAGES]
-    uint64_t* empty = bars + STAGES;         // [STAGES]
-    uint64_t* a_ready = bars + 2 * STAGES;   // [NA]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(raws + WSTAGES * BLOCK_BYTES);
+    uint64_t* full = bars;                   // [STAGES]  activation tile landed
+    uint64_t* empty = bars + STAGES;         // [STAGES]  MMAs that read it completed
+    uint64_t* wfull = bars + 2 * STAGES;     // [WSTAGES] weight block landed
+    uint64_t* wempty = wfull + WSTAGES;      // [WSTAGES] the four dequant warps of its group have read it
+    uint64_t* a_ready = wempty + WSTAGES;    // [NA]
     uint64_t* a_free = a_ready + NA;         // [NA]
     uint64_t* d_full = a_free + NA;          // [1]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_full + 1);
@@ -119,13 +124,17 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
         tma_prefetch_desc(&tm_x);
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], 4 + 1);  // 4 dequant warps + the MMA commit
+            mbar_init(&empty[s], 1);
+        }
+        for (int s = 0; s < WSTAGES; ++s) {
+            mbar_init(&wfull[s], 1);
+            mbar_init(&wempty[s], 4);
         }
         for (int a = 0; a < NA; ++a) {
             mbar_init(&a_ready[a], 4 * SB);  // every dequant warp arrives once per super-block
             mbar_init(&a_free[a], 1);
         }
-        mbar_init(d_full, 1);
+        mbar_init(d_full, NISS);
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -137,28 +146,36 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
 
     const int nsb = (nkb + SB - 1) / SB;  // super-blocks (SB k-blocks share one A buffer and one MMA hand-off)
     if (warp == 0) {
-        if (lane == 0) {
+        if (lane == 0) {  // weight stream: one bulk copy per block (nibbles + scales + zero-points)
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % WSTAGES;
+                if (i >= WSTAGES && !mbar_wait(&wempty[s], ((i / WSTAGES) - 1) & 1, actx, kErrWaitEmpty)) break;
+                mbar_expect_tx(&wfull[s], BLOCK_BYTES);
+                const size_t blk = (size_t)blockIdx.x * p.kbt + kb0 + i;  // tile-major block index
+                bulk_load(raws + s * BLOCK_BYTES, p.tw + blk * BLOCK_BYTES, BLOCK_BYTES, &wfull[s]);
+            }
+        }
+    } else if (warp == XPROD_WARP) {
+        if (lane == 0) {  // activation tiles: both 64-k atoms of a block through one 3-D map (k_in, row, k_out)
             for (int i = 0; i < nkb; ++i) {
                 const int s = i % STAGES;
                 if (i >= STAGES && !mbar_wait(&empty[s], ((i / STAGES) - 1) & 1, actx, kErrWaitEmpty)) break;
-                mbar_expect_tx(&full[s], STAGE_BYTES);
-                const int kblk = kb0 + i;
-                const size_t blk = (size_t)blockIdx.x * p.kbt + kblk;  // tile-major block index
-                bulk_load(raws + s * RAW_BYTES, p.tw + blk * RAW_BYTES, RAW_BYTES, &full[s]);
-                bulk_load(metas + s * META_BYTES, p.ts + blk * TILE_N, SC_BYTES, &full[s]);
-                bulk_load(metas + s * META_BYTES + SC_BYTES, p.tz + blk * TILE_N, Z_BYTES, &full[s]);
-                tma_load_2d(xs + s * X_BYTES, &tm_x, &full[s], kblk * KB, m0);
-                tma_load_2d(xs + s * X_BYTES + XATOM_BYTES, &tm_x, &full[s], kblk * KB + 64, m0);
+                mbar_expect_tx(&full[s], X_BYTES);
+                tma_load_3d(xs + s * X_BYTES, &tm_x, &full[s], 0, m0, (kb0 + i) * 2);
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == 1 || warp == ISS2_WARP) {
         if (lane == 0) {
-            // One barrier hand-off per super-block: every mbarrier hop costs ~150-200 cycles on this thread and
-            // a 128x64x16 MMA issues in ~55, so the hops are amortised over SB*8 MMAs.  The activation tile of a
-            // stage is covered by a_ready as well: the dequant warps observed full[s] before arriving on it.
+            // One barrier hand-off per super-block: every mbarrier hop costs ~150-200 cycles on the issuing thread
+            // and a 128x64x16 MMA issues in ~55, so the hops are amortised over SB*8 MMAs, and two issuer threads
+            // take alternate super-blocks (separate accumulators) so that one issues while the other waits.
+            // The dequant warps' critical path is barrier latency, not arithmetic, so the activation-tile barrier
+            // is waited for here, where the second issuer gives slack.
             constexpr uint32_t idesc = make_idesc(TILE_N, NB, /*F32*/ 1, /*F16*/ 0, /*F16*/ 0);
-            const uint32_t d_tmem = tmem_base + D_COL;
-            for (int u = 0; u < nsb; ++u) {
+            const int me = warp == 1 ? 0 : 1;
+            const uint32_t d_tmem = tmem_base + D_COL + me * 64;
+            bool first = true;
+            for (int u = me; u < nsb; u += NISS) {
                 const int ab = u % NAB;
                 if (!mbar_wait_hot(&a_ready[ab], (u / NAB) & 1, actx, kErrWaitAReady)) break;
                 tc_fence_after();
@@ -167,14 +184,16 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
                     const int i = u * SB + g;
                     if (i < nkb) {
                         const int s = i % STAGES;
+                        if (!mbar_wait_hot(&full[s], (i / STAGES) & 1, actx, kErrWaitFull)) break;
                         // descriptor of the stage's first atom; the start-address field counts 16-byte units
                         const uint64_t bdesc0 = make_sw128_kmajor_desc(smem_u32(xs + s * X_BYTES));
                         const uint32_t a_tmem = tmem_base + (ab * SB + g) * 64;
 #pragma unroll
                         for (int j = 0; j < KB / 16; ++j) {
                             const uint64_t bdesc = bdesc0 + (uint64_t)(((j >> 2) * XATOM_BYTES + (j & 3) * 32) >> 4);
-                            umma_f16_ts(d_tmem, a_tmem + j * 8, bdesc, idesc, (i > 0 || j > 0) ? 1u : 0u);
+                            umma_f16_ts(d_tmem, a_tmem + j * 8, bdesc, idesc, (first && j == 0) ? 0u : 1u);
                         }
+                        first = false;
                         tc_commit(&empty[s]);
                     }
                 }
@@ -182,7 +201,7 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
             }
             tc_commit(d_full);
         }
-    } else {
+    } else if (warp >= 2 && warp < ISS2_WARP) {
         const int q = warp & 3;            // TMEM lane quarter this warp may access
         const int grp = (warp - 2) >> 2;   // dequant group: handles k-block grp of every super-block
         const int row = q * 32 + lane;
@@ -191,24 +210,24 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
         for (int u = 0; u < nsb && ok; ++u) {
             const int i = u * SB + grp, ab = u % NAB;
             const bool have = i < nkb;
-            const int s = i % STAGES;
+            const int s = i % STAGES, ws = i % WSTAGES;
             uint4 pk[4];
             __half sch = __float2half(0.f);
             float z = 8.f;
             if (have) {
                 // one lane per warp polls; the others wait at the shuffle
-                if (lane == 0) ok = mbar_wait(&full[s], (i / STAGES) & 1, actx, kErrWaitFull);
+                if (lane == 0) ok = mbar_wait(&wfull[ws], (i / WSTAGES) & 1, actx, kErrWaitFull);
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
                 // this channel's 64 packed bytes: chunk c (32 k) of all 128 channels is one 2 KiB slab, so the
                 // threads of a warp read consecutive 16-byte pieces (no bank conflicts, no swizzle)
-                const unsigned char* rrow = raws + s * RAW_BYTES + row * 16;
+                const unsigned char* rrow = raws + ws * BLOCK_BYTES + row * 16;
 #pragma unroll
                 for (int c = 0; c < 4; ++c) pk[c] = *reinterpret_cast<const uint4*>(rrow + c * 2048);
-                sch = reinterpret_cast<const __half*>(metas + s * META_BYTES)[row];
-                z = (float)(metas + s * META_BYTES + SC_BYTES)[row];
+                sch = reinterpret_cast<const __half*>(raws + ws * BLOCK_BYTES + SC_OFF)[row];
+                z = (float)(raws + ws * BLOCK_BYTES + Z_OFF)[row];
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&empty[s]);
+                if (lane == 0) mbar_arrive(&wempty[ws]);
             }
             if (u >= NAB) {
                 if (lane == 0) ok = mbar_wait(&a_free[ab], ((u / NAB) - 1) & 1, actx, kErrWaitAFree);
@@ -241,15 +260,17 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (ok) {
             tc_fence_after();
-            constexpr int CPG = NB / SB;  // columns per group
+            constexpr int CPG = 32;  // accumulator columns per reading group (groups 0 and 1 read; others idle)
 #pragma unroll
-            for (int c = 0; c < CPG / 16; ++c) {
-                uint32_t v[16];
+            for (int c = 0; c < (grp < 2 ? CPG / 16 : 0); ++c) {
+                uint32_t v[16], v2[16];
                 const int col0 = grp * CPG + c * 16;
                 tmem_ld16(lane_addr + D_COL + col0, v);
+                if (nsb > 1) tmem_ld16(lane_addr + D_COL + 64 + col0, v2);  // second issuer's accumulator (unused when it had no work)
                 tc_wait_ld();
 #pragma unroll
-                for (int e = 0; e < 16; ++e) P[(col0 + e) * TILE_N + row] = __uint_as_float(v[e]);
+                for (int e = 0; e < 16; ++e)
+                    P[(col0 + e) * TILE_N + row] = __uint_as_float(v[e]) + (nsb > 1 ? __uint_as_float(v2[e]) : 0.f);
             }
             tc_fence_before();
         }
@@ -271,13 +292,13 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
         const int n = (tid & 63) * 2;
         const bool n_ok = n0 + n < p.Nout;
         const bool pair = (n0 + n + 1 < p.Nout) && ((p.Nout & 1) == 0);
-        constexpr int RSTEP = THREADS / 64;
+        constexpr int RSTEP = (THREADS - 64) / 64;  // the last two warps (second issuer, x producer) sit the epilogue out
         const float* P0 = P + n;
         const float* P1 = p.splits > 1 ? cluster.map_shared_rank(P, 1) + n : P0;
         const float* P2 = p.splits > 2 ? cluster.map_shared_rank(P, 2) + n : P0;
         const float* P3 = p.splits > 2 ? cluster.map_shared_rank(P, 3) + n : P0;
         if (p.splits > 1) P0 = cluster.map_shared_rank(P, 0) + n;
-        for (int mb = m_begin + (tid >> 6); mb < m_end && n_ok; mb += 4 * RSTEP) {
+        for (int mb = m_begin + (tid >> 6); mb < m_end && n_ok && tid < RSTEP * 64; mb += 4 * RSTEP) {
             float2 acc[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
@@ -342,8 +363,7 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
 // reference layout -> tiled layout described at the top of this file
 template <typename T>
 __global__ void w4g_repack_kernel(const uint8_t* __restrict__ packed, const T* __restrict__ scales, const uint8_t* __restrict__ zeros,
-                                  uint32_t* __restrict__ tw, T* __restrict__ ts, uint8_t* __restrict__ tz,
-                                  int K, int Nout, int group, long long total_words) {
+                                  uint8_t* __restrict__ tiled, int K, int Nout, int group, long long total_words) {
     const long long widx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (widx >= total_words) return;
     // widx = (((tile * kbt + b) * 4 + c) * 128 + r) * 4 + j
@@ -364,16 +384,17 @@ __global__ void w4g_repack_kernel(const uint8_t* __restrict__ packed, const T* _
 #pragma unroll
         for (int i = 0; i < 8; ++i) out |= ((w >> (4 * order[i])) & 15u) << (4 * i);
     }
-    tw[widx] = out;
+    uint8_t* block = tiled + blk * w4::BLOCK_BYTES;
+    reinterpret_cast<uint32_t*>(block)[widx & 2047] = out;
     if (c == 0 && j == 0) {
         const long long gi = n * (K / group) + (b * 128) / group;
-        ts[blk * 128 + r] = (n < Nout) ? scales[gi] : from_f<T>(0.f);
-        tz[blk * 128 + r] = (n < Nout && zeros) ? zeros[gi] : (uint8_t)8;
+        reinterpret_cast<T*>(block + w4::SC_OFF)[r] = (n < Nout) ? scales[gi] : from_f<T>(0.f);
+        (block + w4::Z_OFF)[r] = (n < Nout && zeros) ? zeros[gi] : (uint8_t)8;
     }
 }
 
-int launch_w4g_umma_tiled(const void* x, const uint8_t* tw, const void* ts, const uint8_t* tz, const void* residual,
-                          void* out, int M, int K, int Nout, int epilogue, cudaStream_t st) {
+int launch_w4g_umma_tiled(const void* x, const uint8_t* tw, const void* residual, void* out, int M, int K, int Nout,
+                          int epilogue, cudaStream_t st) {
     using namespace w4;
     RWKV7_REQUIRE(M >= 1 && M <= 65535 * NB, RWKV7_ERR_UNSUPPORTED, "w4g_gemv_tiled: M out of range (got %d)", M);
     const int row_blocks = (M + NB - 1) / NB;  // each block of 64 activation rows is one pass over the weights
@@ -389,11 +410,11 @@ int launch_w4g_umma_tiled(const void* x, const uint8_t* tw, const void* ts, cons
     }
     const int nkb = total_kb / splits;
     CUtensorMap tm_x;
-    if (int e = make_tmap_2d(&tm_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x, M, K, NB, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
-    W4UmmaArgs a{tw, reinterpret_cast<const __half*>(ts), tz, reinterpret_cast<const __half*>(residual),
+    if (int e = make_tmap_x3d(&tm_x, x, M, K, NB)) return e;
+    W4UmmaArgs a{tw, reinterpret_cast<const __half*>(residual),
                  reinterpret_cast<__half*>(out), M, K, Nout, epilogue, nkb, total_kb, splits, kernel_error_word()};
     RWKV7_REQUIRE(a.error != nullptr, RWKV7_ERR_CUDA, "w4g_gemv_tiled: cannot resolve the device error word");
-    const size_t smem = (size_t)STAGES * (X_BYTES + RAW_BYTES + META_BYTES) + (2 * STAGES + 2 * NA + 1) * 8 + 16 + 1024;
+    const size_t smem = (size_t)STAGES * X_BYTES + (size_t)WSTAGES * BLOCK_BYTES + (2 * STAGES + 2 * WSTAGES + 2 * NA + 1) * 8 + 16 + 1024;
     cudaError_t e = cudaFuncSetAttribute(w4g_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     RWKV7_REQUIRE(e == cudaSuccess, RWKV7_ERR_CUDA, "w4g_gemv_tiled: %s", cudaGetErrorString(e));
     cudaLaunchConfig_t cfg{};
@@ -417,39 +438,33 @@ int launch_w4g_umma_tiled(const void* x, const uint8_t* tw, const void* ts, cons
 
 using namespace rwkv7;
 
-extern "C" int64_t rwkv7_w4g_tiled_bytes(int K, int Nout, int64_t* scale_elems) {
+extern "C" int64_t rwkv7_w4g_tiled_bytes(int K, int Nout) {
     if (K <= 0 || Nout <= 0 || K % 128) return 0;
     const int64_t tiles = (Nout + 127) / 128, kbt = K / 128;
-    if (scale_elems) *scale_elems = tiles * kbt * 128;
-    return tiles * kbt * 8192;
+    return tiles * kbt * w4::BLOCK_BYTES;
 }
 
-extern "C" int rwkv7_w4g_repack(const uint8_t* packed, const void* scales, const uint8_t* zeros, uint8_t* tiled_w,
-                                void* tiled_scales, uint8_t* tiled_zeros, int K, int Nout, int group, int dtype, void* stream) {
+extern "C" int rwkv7_w4g_repack(const uint8_t* packed, const void* scales, const uint8_t* zeros, uint8_t* tiled, int K,
+                                int Nout, int group, int dtype, void* stream) {
     RWKV7_REQUIRE(K > 0 && Nout > 0 && K % 128 == 0, RWKV7_ERR_UNSUPPORTED, "w4g_repack: K must be a positive multiple of 128");
     RWKV7_REQUIRE(group > 0 && group % 128 == 0 && K % group == 0, RWKV7_ERR_UNSUPPORTED,
                   "w4g_repack: group must be a multiple of 128 dividing K (group=%d K=%d)", group, K);
-    RWKV7_REQUIRE(packed && scales && tiled_w && tiled_scales && tiled_zeros, RWKV7_ERR_INVALID, "w4g_repack: null pointer");
+    RWKV7_REQUIRE(packed && scales && tiled, RWKV7_ERR_INVALID, "w4g_repack: null pointer");
     RWKV7_REQUIRE(dtype == RWKV7_F16, RWKV7_ERR_UNSUPPORTED, "w4g_repack: the tiled format holds fp16 scales");
-    RWKV7_REQUIRE(aligned(packed, 4) && aligned(tiled_w, 16) && aligned(tiled_scales, 16) && aligned(tiled_zeros, 16),
-                  RWKV7_ERR_ALIGN, "w4g_repack: unaligned pointer");
+    RWKV7_REQUIRE(aligned(packed, 4) && aligned(tiled, 16), RWKV7_ERR_ALIGN, "w4g_repack: unaligned pointer");
     const long long tiles = (Nout + 127) / 128;
     const long long words = tiles * (K / 128) * 2048;
     w4g_repack_kernel<__half><<<(unsigned)((words + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        packed, reinterpret_cast<const __half*>(scales), zeros, reinterpret_cast<uint32_t*>(tiled_w),
-        reinterpret_cast<__half*>(tiled_scales), tiled_zeros, K, Nout, group, words);
+        packed, reinterpret_cast<const __half*>(scales), zeros, tiled, K, Nout, group, words);
     return check_launch("w4g_repack_kernel");
 }
 
-extern "C" int rwkv7_w4g_gemv_tiled(const void* x, const uint8_t* tiled_w, const void* tiled_scales, const uint8_t* tiled_zeros,
-                                    const void* residual, void* out, int M, int K, int Nout, int epilogue, int dtype,
-                                    void* stream) {
-    RWKV7_REQUIRE(x && tiled_w && tiled_scales && tiled_zeros && out, RWKV7_ERR_INVALID, "w4g_gemv_tiled: null pointer");
+extern "C" int rwkv7_w4g_gemv_tiled(const void* x, const uint8_t* tiled, const void* residual, void* out, int M, int K,
+                                    int Nout, int epilogue, int dtype, void* stream) {
+    RWKV7_REQUIRE(x && tiled && out, RWKV7_ERR_INVALID, "w4g_gemv_tiled: null pointer");
     RWKV7_REQUIRE(dtype == RWKV7_F16, RWKV7_ERR_UNSUPPORTED, "w4g_gemv_tiled: fp16 activations only");
     RWKV7_REQUIRE(epilogue >= 0 && epilogue <= 2, RWKV7_ERR_INVALID, "w4g_gemv_tiled: bad epilogue code %d", epilogue);
     RWKV7_REQUIRE(epilogue != RWKV7_EPI_ADD || residual, RWKV7_ERR_INVALID, "w4g_gemv_tiled: residual is required for the add epilogue");
-    RWKV7_REQUIRE(aligned(x, 16) && aligned(tiled_w, 16) && aligned(tiled_scales, 16) && aligned(tiled_zeros, 16),
-                  RWKV7_ERR_ALIGN, "w4g_gemv_tiled: pointers must be 16-byte aligned");
-    return launch_w4g_umma_tiled(x, tiled_w, tiled_scales, tiled_zeros, residual, out, M, K, Nout, epilogue,
-                                 static_cast<cudaStream_t>(stream));
+    RWKV7_REQUIRE(aligned(x, 16) && aligned(tiled, 16), RWKV7_ERR_ALIGN, "w4g_gemv_tiled: pointers must be 16-byte aligned");
+    return launch_w4g_umma_tiled(x, tiled, residual, out, M, K, Nout, epilogue, static_cast<cudaStream_t>(stream));
 }

@@ -150,6 +150,7 @@ class RWKV7ForCausalLM(nn.Module):
         self.model = NativeRWKV7Model(config, tp_world)
         self.lm_head = nn.Linear(config.hidden_size, config.vocab_size, bias=False)
         self._graphs = {}
+        self._side_streams = {}
 
     # ------------------------------------------------------------------ helpers
     @property
@@ -164,6 +165,12 @@ class RWKV7ForCausalLM(nn.Module):
         c = self.config
         return NativeRWKV7Cache.allocate(c.num_hidden_layers, batch_size, c.hidden_size, c.num_heads // self.tp_world,
                                          c.head_dim, self.device, self.dtype)
+
+    def _side_stream(self, device):
+        st = self._side_streams.get(device)
+        if st is None:
+            st = self._side_streams[device] = torch.cuda.Stream(device=device)
+        return st
 
     def _all_reduce(self, t):
         if self.tp_world > 1:
@@ -184,20 +191,29 @@ class RWKV7ForCausalLM(nn.Module):
                 x = _nm.layer_norm(x, layer.pre_norm.weight, layer.pre_norm.bias)
             xr, xw, xk, xv, xa, xg = _nm.fused_attn_norm_mix6_decode(
                 x, xpa[i], layer.attn_norm.weight, layer.attn_norm.bias, at.x_r, at.x_w, at.x_k, at.x_v, at.x_a, at.x_g)
+            # The LoRA chain does not depend on r/k/v: it runs on a side stream (a parallel branch of the decode
+            # graph once captured) and joins before the recurrence.
+            main = torch.cuda.current_stream(x.device)
+            side = self._side_stream(x.device)
+            side.wait_stream(main)
+            wl, al, gl = at.w_lora.lora, at.a_lora.lora, at.g_lora.lora
+            with torch.cuda.stream(side):
+                if i == 0:
+                    hs = _lora.small_gemm_group((xw, xa, xg), (wl[0].weight, al[0].weight, gl[0].weight), acts=(1, 0, 2))
+                    w_raw, a_pre, g = _lora.small_gemm_group(hs, (wl[2].weight, al[2].weight, gl[2].weight))
+                    extra = dict(v_out=v_first)
+                else:
+                    vl = at.v_lora.lora
+                    hs = _lora.small_gemm_group((xw, xa, xg, xv), (wl[0].weight, al[0].weight, gl[0].weight, vl[0].weight),
+                                                acts=(1, 0, 2, 0))
+                    w_raw, a_pre, g, vg_pre = _lora.small_gemm_group(hs, (wl[2].weight, al[2].weight, gl[2].weight, vl[2].weight))
+                    extra = dict(v_first=v_first, v_gate=vg_pre, v_gate_bias=vl[2].bias, v_gate_is_raw=True)
             r = _linear(at.r_proj, xr)
             k = _linear(at.k_proj, xk)
             v = _linear(at.v_proj, xv)
-            wl, al, gl = at.w_lora.lora, at.a_lora.lora, at.g_lora.lora
-            if i == 0:
-                hs = _lora.small_gemm_group((xw, xa, xg), (wl[0].weight, al[0].weight, gl[0].weight), acts=(1, 0, 2))
-                w_raw, a_pre, g = _lora.small_gemm_group(hs, (wl[2].weight, al[2].weight, gl[2].weight))
-                extra = dict(v_out=v_first)
-            else:
-                vl = at.v_lora.lora
-                hs = _lora.small_gemm_group((xw, xa, xg, xv), (wl[0].weight, al[0].weight, gl[0].weight, vl[0].weight),
-                                            acts=(1, 0, 2, 0))
-                w_raw, a_pre, g, vg_pre = _lora.small_gemm_group(hs, (wl[2].weight, al[2].weight, gl[2].weight, vl[2].weight))
-                extra = dict(v_first=v_first, v_gate=vg_pre, v_gate_bias=vl[2].bias, v_gate_is_raw=True)
+            main.wait_stream(side)
+            for t_ in (xw, xa, xg, xv, w_raw, a_pre, g):
+                t_.record_stream(side)
             out, _ = _rec.fused_recurrent_output_prepare_raw(
                 r, w_raw, k, v, a_pre, state[i], g, at.k_k, at.k_a, at.r_k, at.g_norm.weight, at.g_norm.bias,
                 eps=N * 1e-5, new_state=state[i], w_bias=wl[2].bias, a_bias=al[2].bias, a_is_raw=True, **extra)

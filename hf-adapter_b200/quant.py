@@ -91,37 +91,32 @@ def w4_dequant(q, scales, in_features, group_size=128, zeros=None, out=None):
 
 
 def w4_repack_tiled(q, scales, in_features, group_size=128, zeros=None):
-    """Build the tiled copy of a group-wise int4 weight that the tensor-core decode kernel streams (one 8 KiB block
-    per [128 channels x 128 k] tile).  Returns ``(tiled_w u8, tiled_scales f16, tiled_zeros u8)``.  Done once at
+    """Build the tiled copy of a group-wise int4 weight that the tensor-core decode kernel streams (one 8704-byte
+    block per [128 channels x 128 k] tile: nibbles, scales, zero-points).  Returns one uint8 tensor.  Done once at
     load time; the reference-layout tensors stay the interchange format."""
-    import ctypes
     Nout, K = int(q.shape[0]), int(in_features)
     require_cuda(q, scales, zeros, what="w4_repack_tiled")
     if scales.dtype != torch.float16:
         raise ValueError("the tiled format holds fp16 scales")
-    n_scale = ctypes.c_int64(0)
-    nbytes = int(_lib.lib.rwkv7_w4g_tiled_bytes(K, Nout, ctypes.byref(n_scale)))
+    nbytes = int(_lib.lib.rwkv7_w4g_tiled_bytes(K, Nout))
     if nbytes == 0:
         raise ValueError(f"in_features={K} is not a multiple of 128")
-    tw = torch.empty((nbytes,), device=q.device, dtype=torch.uint8)
-    ts = torch.empty((n_scale.value,), device=q.device, dtype=torch.float16)
-    tz = torch.empty((n_scale.value,), device=q.device, dtype=torch.uint8)
-    _lib.check(_lib.lib.rwkv7_w4g_repack(ptr(q.contiguous()), ptr(scales.contiguous()), ptr(zeros), ptr(tw), ptr(ts), ptr(tz),
+    tiled = torch.empty((nbytes,), device=q.device, dtype=torch.uint8)
+    _lib.check(_lib.lib.rwkv7_w4g_repack(ptr(q.contiguous()), ptr(scales.contiguous()), ptr(zeros), ptr(tiled),
                                          K, Nout, int(group_size), _lib.F16, stream_ptr(q)), "w4_repack_tiled")
-    return tw, ts, tz
+    return tiled
 
 
 def w4_tiled_linear(x, tiled, out_features, in_features, *, out=None, relu2: bool = False, residual=None):
-    """y = x @ W^T on the tensor-core kernel from the tiled weight copy (1..64 rows, fp16)."""
+    """y = x @ W^T on the tensor-core kernel from the tiled weight copy (fp16; one weight pass per 64 rows)."""
     K, Nout = int(in_features), int(out_features)
     x2 = _rows(x, K)
     M = int(x2.shape[0])
-    tw, ts, tz = tiled
-    require_cuda(x2, tw, ts, tz, what="w4_tiled_linear")
+    require_cuda(x2, tiled, what="w4_tiled_linear")
     epi, res = _epi(relu2, residual, M, Nout, x2)
     y = torch.empty((M, Nout), device=x2.device, dtype=x2.dtype) if out is None else out.reshape(M, Nout)
-    _lib.check(_lib.lib.rwkv7_w4g_gemv_tiled(ptr(x2), ptr(tw), ptr(ts), ptr(tz), ptr(res), ptr(y), M, K, Nout, epi,
-                                             dt_code(x2), stream_ptr(x2)), "w4_tiled_linear")
+    _lib.check(_lib.lib.rwkv7_w4g_gemv_tiled(ptr(x2), ptr(tiled), ptr(res), ptr(y), M, K, Nout, epi, dt_code(x2),
+                                             stream_ptr(x2)), "w4_tiled_linear")
     return y.reshape(*x.shape[:-1], Nout)
 
 
@@ -321,7 +316,7 @@ class MM4Linear(torch.nn.Module):
         if rows <= TILED_MAX_ROWS and x.dtype == torch.float16 and x.is_cuda and self.in_features % 128 == 0:
             # decode: tensor-core kernel on the tiled copy (built once per device, on first use)
             t = self._tiled
-            if t is None or t[0].device != x.device:
+            if t is None or t.device != x.device:
                 t = self._tiled = w4_repack_tiled(self.packed_group, self.group_scales, self.in_features,
                                                   self.group_size, self.group_zeros)
             return w4_tiled_linear(x, t, self.out_features, self.in_features, **kw)

@@ -176,17 +176,17 @@ int rwkv7_w4g_gemv(const void* x, const uint8_t* packed, const void* scales, con
                    const void* residual, void* out, int M, int K, int Nout, int group, int epilogue,
                    int dtype, void* stream);
 
-/* Tensor-core version of the same projection (any row count, one pass over the weights per 64 rows), reading a TILED copy of the weights built once at load
- * time by rwkv7_w4g_repack (8 KiB per [128 channels x 128 k] tile, tiles of a channel block consecutive, so each CTA
- * streams one contiguous region; scales / zero-points re-laid per tile).  Same values, same arithmetic as above.
- * rwkv7_w4g_tiled_bytes returns the byte size of the tiled weight buffer (0 for unsupported shapes) and, through
- * scale_elems, the element count of the tiled scale (fp16) and zero (u8) buffers.  fp16 only, K % 128 == 0.
- * No counterpart in the reference (its group-wise format has no fused kernel off sm_70). */
-int64_t rwkv7_w4g_tiled_bytes(int K, int Nout, int64_t* scale_elems);
-int rwkv7_w4g_repack(const uint8_t* packed, const void* scales, const uint8_t* zeros, uint8_t* tiled_w, void* tiled_scales,
-                     uint8_t* tiled_zeros, int K, int Nout, int group, int dtype, void* stream);
-int rwkv7_w4g_gemv_tiled(const void* x, const uint8_t* tiled_w, const void* tiled_scales, const uint8_t* tiled_zeros,
-                         const void* residual, void* out, int M, int K, int Nout, int epilogue, int dtype, void* stream);
+/* Tensor-core version of the same projection (any row count, one pass over the weights per 64 rows), reading a TILED
+ * copy of the weights built once at load time by rwkv7_w4g_repack: one 8704-byte block per [128 channels x 128 k] tile
+ * (packed nibbles, then that tile's fp16 scales and u8 zero-points), blocks of a channel tile consecutive, so each CTA
+ * streams one contiguous region.  Same values, same arithmetic as above.  rwkv7_w4g_tiled_bytes returns the size of
+ * the tiled buffer (0 for unsupported shapes).  fp16 only, K % 128 == 0.  No counterpart in the reference (its
+ * group-wise format has no fused kernel off sm_70). */
+int64_t rwkv7_w4g_tiled_bytes(int K, int Nout);
+int rwkv7_w4g_repack(const uint8_t* packed, const void* scales, const uint8_t* zeros, uint8_t* tiled, int K, int Nout,
+                     int group, int dtype, void* stream);
+int rwkv7_w4g_gemv_tiled(const void* x, const uint8_t* tiled, const void* residual, void* out, int M, int K, int Nout,
+                         int epilogue, int dtype, void* stream);
 
 /* int8 per-output-channel weights, quantize_w8_row format (rwkv7_hf/sm70_quant.py:485-489): q [Nout,K] i8,
  * scale [Nout] in `dtype`.  Replaces w8_linear (:522) / the W8A16 GEMV (native_quant_a8w8.py:50-132). */
