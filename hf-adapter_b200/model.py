@@ -166,10 +166,10 @@ class RWKV7ForCausalLM(nn.Module):
         return NativeRWKV7Cache.allocate(c.num_hidden_layers, batch_size, c.hidden_size, c.num_heads // self.tp_world,
                                          c.head_dim, self.device, self.dtype)
 
-    def _side_stream(self, device):
-        st = self._side_streams.get(device)
+    def _side_stream(self, device, index: int = 0):
+        st = self._side_streams.get((device, index))
         if st is None:
-            st = self._side_streams[device] = torch.cuda.Stream(device=device)
+            st = self._side_streams[(device, index)] = torch.cuda.Stream(device=device)
         return st
 
     def _all_reduce(self, t):
@@ -208,12 +208,22 @@ class RWKV7ForCausalLM(nn.Module):
                                                 acts=(1, 0, 2, 0))
                     w_raw, a_pre, g, vg_pre = _lora.small_gemm_group(hs, (wl[2].weight, al[2].weight, gl[2].weight, vl[2].weight))
                     extra = dict(v_first=v_first, v_gate=vg_pre, v_gate_bias=vl[2].bias, v_gate_is_raw=True)
+            # r / k / v are independent too: separate branches let the tail of one projection overlap the ramp-up
+            # of the next
+            sk, sv = self._side_stream(x.device, 1), self._side_stream(x.device, 2)
+            sk.wait_stream(main)
+            sv.wait_stream(main)
+            with torch.cuda.stream(sk):
+                k = _linear(at.k_proj, xk)
+            with torch.cuda.stream(sv):
+                v = _linear(at.v_proj, xv)
             r = _linear(at.r_proj, xr)
-            k = _linear(at.k_proj, xk)
-            v = _linear(at.v_proj, xv)
             main.wait_stream(side)
+            main.wait_stream(sk)
+            main.wait_stream(sv)
             for t_ in (xw, xa, xg, xv, w_raw, a_pre, g):
                 t_.record_stream(side)
+            xk.record_stream(sk); k.record_stream(sk); xv.record_stream(sv); v.record_stream(sv)
             out, _ = _rec.fused_recurrent_output_prepare_raw(
                 r, w_raw, k, v, a_pre, state[i], g, at.k_k, at.k_a, at.r_k, at.g_norm.weight, at.g_norm.bias,
                 eps=N * 1e-5, new_state=state[i], w_bias=wl[2].bias, a_bias=al[2].bias, a_is_raw=True, **extra)
