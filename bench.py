@@ -333,7 +333,10 @@ def main():
     achieved = wkv_bytes / (wkv_ms * 1e-3) / 1e9
     roofline = {"kernel": "wkv7_step_kernel (decode recurrence + fused epilogues)", "bound": "hbm", "achieved": achieved,
                 "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak, "peak_source": peak_src + " (burst copy)",
-                "traffic": None, "bytes_per_launch": wkv_bytes, "us_per_launch": wkv_ms * 1e3}
+                # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture at B*H = 4096 (profiles/): 80.5 MB per
+                # launch (reads = state in; most of the written state is still dirty in L2 when the kernel ends),
+                # scaled by the sequence-heads of this launch
+                "traffic": 80.5e6 * (B * Hl) / 4096.0, "bytes_per_launch": wkv_bytes, "us_per_launch": wkv_ms * 1e3}
 
     extra = {"step_bytes": step_bytes, "step_hbm_frac": step_bytes / (ms_per_step * 1e-3) / 1e9 / hbm_peak,
              "wkv_share_of_step": wkv_ms * len(states) / ms_per_step}

@@ -44,12 +44,12 @@ constexpr int Z_OFF = SC_OFF + TILE_N * 2;  // then 128 u8 zero-points, then pad
 constexpr int BLOCK_BYTES = 8704;           // one tile block in memory = one bulk copy (68 x 128 B)
 constexpr int XATOM_BYTES = NB * 128;       // one 64-k swizzle atom of the activation tile
 constexpr int X_BYTES = 2 * XATOM_BYTES;    // 16384
-constexpr int SB = 3;            // k-blocks per super-block = dequant warp groups
-constexpr int NAB = 2;           // super-block A buffers in tensor memory (SB x 64 columns each)
+constexpr int SB = 3;            // dequant warp groups: group g expands k-blocks g, g + SB, g + 2 SB, ...
+constexpr int NAB = 6;           // dequantised-A buffers in tensor memory (one k-block = 64 columns each)
 constexpr int NA = NAB;          // barrier pairs for the A buffers
 constexpr int NISS = 2;          // MMA issuer warps, each with its own accumulator (summed in the epilogue)
-constexpr int TMEM_COLS = 512;   // A: NAB x SB x 64 columns, D: NISS x 64 columns
-constexpr int D_COL = NAB * SB * 64;
+constexpr int TMEM_COLS = 512;   // A: NAB x 64 columns, D: NISS x 64 columns
+constexpr int D_COL = NAB * 64;
 constexpr int ISS2_WARP = 2 + SB * 4;           // second issuer = last warp
 constexpr int XPROD_WARP = ISS2_WARP + 1;       // activation-tile producer
 constexpr int THREADS = 64 + SB * 128 + 64;
@@ -131,7 +131,7 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
             mbar_init(&wempty[s], 4);
         }
         for (int a = 0; a < NA; ++a) {
-            mbar_init(&a_ready[a], 4 * SB);  // every dequant warp arrives once per super-block
+            mbar_init(&a_ready[a], 4);  // the four warps of the group that filled the buffer
             mbar_init(&a_free[a], 1);
         }
         mbar_init(d_full, NISS);
@@ -144,7 +144,6 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int nsb = (nkb + SB - 1) / SB;  // super-blocks (SB k-blocks share one A buffer and one MMA hand-off)
     if (warp == 0) {
         if (lane == 0) {  // weight stream: one bulk copy per block (nibbles + scales + zero-points)
             for (int i = 0; i < nkb; ++i) {
@@ -166,92 +165,74 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
         }
     } else if (warp == 1 || warp == ISS2_WARP) {
         if (lane == 0) {
-            // One barrier hand-off per super-block: every mbarrier hop costs ~150-200 cycles on the issuing thread
-            // and a 128x64x16 MMA issues in ~55, so the hops are amortised over SB*8 MMAs, and two issuer threads
-            // take alternate super-blocks (separate accumulators) so that one issues while the other waits.
-            // The dequant warps' critical path is barrier latency, not arithmetic, so the activation-tile barrier
-            // is waited for here, where the second issuer gives slack.
+            // Throughput of the A path = (buffers in flight) / (dequantise + barrier hop + MMA + commit + hop), so
+            // tensor memory holds six single-block A buffers; every mbarrier hop costs this thread ~150-200 cycles
+            // against ~55 per 128x64x16 MMA, so two issuer threads take alternate k-blocks (separate accumulators,
+            // summed in the epilogue): one issues while the other waits.
             constexpr uint32_t idesc = make_idesc(TILE_N, NB, /*F32*/ 1, /*F16*/ 0, /*F16*/ 0);
             const int me = warp == 1 ? 0 : 1;
             const uint32_t d_tmem = tmem_base + D_COL + me * 64;
-            bool first = true;
-            for (int u = me; u < nsb; u += NISS) {
-                const int ab = u % NAB;
-                if (!mbar_wait_hot(&a_ready[ab], (u / NAB) & 1, actx, kErrWaitAReady)) break;
+            for (int i = me; i < nkb; i += NISS) {
+                const int ab = i % NAB, s = i % STAGES;
+                if (!mbar_wait_hot(&a_ready[ab], (i / NAB) & 1, actx, kErrWaitAReady)) break;
+                if (!mbar_wait_hot(&full[s], (i / STAGES) & 1, actx, kErrWaitFull)) break;
                 tc_fence_after();
+                // descriptor of the stage's first atom; the start-address field counts 16-byte units
+                const uint64_t bdesc0 = make_sw128_kmajor_desc(smem_u32(xs + s * X_BYTES));
+                const uint32_t a_tmem = tmem_base + ab * 64;
 #pragma unroll
-                for (int g = 0; g < SB; ++g) {
-                    const int i = u * SB + g;
-                    if (i < nkb) {
-                        const int s = i % STAGES;
-                        if (!mbar_wait_hot(&full[s], (i / STAGES) & 1, actx, kErrWaitFull)) break;
-                        // descriptor of the stage's first atom; the start-address field counts 16-byte units
-                        const uint64_t bdesc0 = make_sw128_kmajor_desc(smem_u32(xs + s * X_BYTES));
-                        const uint32_t a_tmem = tmem_base + (ab * SB + g) * 64;
-#pragma unroll
-                        for (int j = 0; j < KB / 16; ++j) {
-                            const uint64_t bdesc = bdesc0 + (uint64_t)(((j >> 2) * XATOM_BYTES + (j & 3) * 32) >> 4);
-                            umma_f16_ts(d_tmem, a_tmem + j * 8, bdesc, idesc, (first && j == 0) ? 0u : 1u);
-                        }
-                        first = false;
-                        tc_commit(&empty[s]);
-                    }
+                for (int j = 0; j < KB / 16; ++j) {
+                    const uint64_t bdesc = bdesc0 + (uint64_t)(((j >> 2) * XATOM_BYTES + (j & 3) * 32) >> 4);
+                    umma_f16_ts(d_tmem, a_tmem + j * 8, bdesc, idesc, (i == me && j == 0) ? 0u : 1u);
                 }
+                tc_commit(&empty[s]);
                 tc_commit(&a_free[ab]);
             }
             tc_commit(d_full);
         }
     } else if (warp >= 2 && warp < ISS2_WARP) {
         const int q = warp & 3;            // TMEM lane quarter this warp may access
-        const int grp = (warp - 2) >> 2;   // dequant group: handles k-block grp of every super-block
+        const int grp = (warp - 2) >> 2;   // dequant group
         const int row = q * 32 + lane;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
         bool ok = true;
-        for (int u = 0; u < nsb && ok; ++u) {
-            const int i = u * SB + grp, ab = u % NAB;
-            const bool have = i < nkb;
-            const int s = i % STAGES, ws = i % WSTAGES;
+        for (int i = grp; i < nkb && ok; i += SB) {
+            const int ab = i % NAB, ws = i % WSTAGES;
+            // one lane per warp polls; the others wait at the shuffle
+            if (lane == 0) ok = mbar_wait(&wfull[ws], (i / WSTAGES) & 1, actx, kErrWaitFull);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            // this channel's 64 packed bytes: chunk c (32 k) of all 128 channels is one 2 KiB slab, so the
+            // threads of a warp read consecutive 16-byte pieces (no bank conflicts, no swizzle)
+            const unsigned char* rrow = raws + ws * BLOCK_BYTES + row * 16;
             uint4 pk[4];
-            __half sch = __float2half(0.f);
-            float z = 8.f;
-            if (have) {
-                // one lane per warp polls; the others wait at the shuffle
-                if (lane == 0) ok = mbar_wait(&wfull[ws], (i / WSTAGES) & 1, actx, kErrWaitFull);
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-                if (!ok) break;
-                // this channel's 64 packed bytes: chunk c (32 k) of all 128 channels is one 2 KiB slab, so the
-                // threads of a warp read consecutive 16-byte pieces (no bank conflicts, no swizzle)
-                const unsigned char* rrow = raws + ws * BLOCK_BYTES + row * 16;
 #pragma unroll
-                for (int c = 0; c < 4; ++c) pk[c] = *reinterpret_cast<const uint4*>(rrow + c * 2048);
-                sch = reinterpret_cast<const __half*>(raws + ws * BLOCK_BYTES + SC_OFF)[row];
-                z = (float)(raws + ws * BLOCK_BYTES + Z_OFF)[row];
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&wempty[ws]);
-            }
-            if (u >= NAB) {
-                if (lane == 0) ok = mbar_wait(&a_free[ab], ((u / NAB) - 1) & 1, actx, kErrWaitAFree);
+            for (int c = 0; c < 4; ++c) pk[c] = *reinterpret_cast<const uint4*>(rrow + c * 2048);
+            const __half sch = reinterpret_cast<const __half*>(raws + ws * BLOCK_BYTES + SC_OFF)[row];
+            const float z = (float)(raws + ws * BLOCK_BYTES + Z_OFF)[row];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&wempty[ws]);
+            if (i >= NAB) {
+                if (lane == 0) ok = mbar_wait(&a_free[ab], ((i / NAB) - 1) & 1, actx, kErrWaitAFree);
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
             }
-            if (have) {
-                tc_fence_after();
-                const __half2 sc = __half2half2(sch);
-                const __half2 zlo = __float2half2_rn(1024.0f + z);
-                const __half2 zhi = __float2half2_rn(-(64.0f + z));
-                const uint32_t a_addr = lane_addr + (ab * SB + grp) * 64;
+            tc_fence_after();
+            const __half2 sc = __half2half2(sch);
+            const __half2 zlo = __float2half2_rn(1024.0f + z);
+            const __half2 zhi = __float2half2_rn(-(64.0f + z));
+            const uint32_t a_addr = lane_addr + ab * 64;
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t v[16];
-                    dequant_word(pk[c].x, zlo, zhi, sc, v + 0);
-                    dequant_word(pk[c].y, zlo, zhi, sc, v + 4);
-                    dequant_word(pk[c].z, zlo, zhi, sc, v + 8);
-                    dequant_word(pk[c].w, zlo, zhi, sc, v + 12);
-                    tmem_st16(a_addr + c * 16, v);
-                }
-                tc_wait_st();
-                tc_fence_before();
+            for (int c = 0; c < 4; ++c) {
+                uint32_t v[16];
+                dequant_word(pk[c].x, zlo, zhi, sc, v + 0);
+                dequant_word(pk[c].y, zlo, zhi, sc, v + 4);
+                dequant_word(pk[c].z, zlo, zhi, sc, v + 8);
+                dequant_word(pk[c].w, zlo, zhi, sc, v + 12);
+                tmem_st16(a_addr + c * 16, v);
             }
+            tc_wait_st();
+            tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&a_ready[ab]);
         }
@@ -266,11 +247,11 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
                 uint32_t v[16], v2[16];
                 const int col0 = grp * CPG + c * 16;
                 tmem_ld16(lane_addr + D_COL + col0, v);
-                if (nsb > 1) tmem_ld16(lane_addr + D_COL + 64 + col0, v2);  // second issuer's accumulator (unused when it had no work)
+                if (nkb > 1) tmem_ld16(lane_addr + D_COL + 64 + col0, v2);  // second issuer's accumulator (unused when it had no work)
                 tc_wait_ld();
 #pragma unroll
                 for (int e = 0; e < 16; ++e)
-                    P[(col0 + e) * TILE_N + row] = __uint_as_float(v[e]) + (nsb > 1 ? __uint_as_float(v2[e]) : 0.f);
+                    P[(col0 + e) * TILE_N + row] = __uint_as_float(v[e]) + (nkb > 1 ? __uint_as_float(v2[e]) : 0.f);
             }
             tc_fence_before();
         }
