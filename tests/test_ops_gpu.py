@@ -279,3 +279,44 @@ def test_scan_full_size_config2():
     for s_gpu, y_gpu in ((ss, ys), (sc, yc)):
         assert rel_err(npf(s_gpu[:1, :2]), so) < 1e-3
         assert rel_err(npf(y_gpu[:1, :, :2]), yo.astype(np.float32)) < 2e-3
+
+
+def test_bf16_activations():
+    """The CUDA-core kernels and the LoRA MMA kernel take bf16 storage as well (fp32 arithmetic inside)."""
+    rng = np.random.default_rng(21)
+    B, Hh, D = 3, 2, 256
+    bf = lambda a: torch.from_numpy(np.asarray(a, np.float32)).cuda().to(torch.bfloat16)
+    rt = lambda t: t.float().cpu().numpy()  # bf16-rounded values as fp32 for the oracle
+    r, w_raw, k, v, g = (bf(rng.standard_normal((B, Hh, N))) for _ in range(5))
+    a = bf(1 / (1 + np.exp(-rng.standard_normal((B, Hh, N)))))
+    state = (0.3 * rng.standard_normal((B, Hh, N, N))).astype(np.float32)
+    k_k, k_a = bf(0.85 + 0.1 * rng.standard_normal(Hh * N)), bf(1 + 0.1 * rng.standard_normal(Hh * N))
+    r_k, gw, gb = bf(0.1 * rng.standard_normal((Hh, N))), bf(1 + 0.1 * rng.standard_normal(Hh * N)), bf(0.1 * rng.standard_normal(Hh * N))
+    yo, so = O.recurrent_output_prepare_raw(rt(r), rt(w_raw), rt(k), rt(v), rt(a), state, rt(g), rt(k_k), rt(k_a), rt(r_k), rt(gw), rt(gb), EPS)
+    y, s = hb.fused_recurrent_output_prepare_raw(r, w_raw, k, v, a, cu(state), g, k_k, k_a, r_k, gw, gb, eps=EPS)
+    assert y.dtype == torch.bfloat16
+    np.testing.assert_allclose(npf(s), so, rtol=2e-5, atol=2e-5)
+    np.testing.assert_allclose(npf(y), yo, rtol=2e-2, atol=2e-2)
+    x, prev = bf(rng.standard_normal((B, D))), bf(rng.standard_normal((B, D)))
+    nw, nb = bf(1 + 0.1 * rng.standard_normal(D)), bf(0.1 * rng.standard_normal(D))
+    mixes = [bf(rng.random(D)) for _ in range(6)]
+    outs_o, prev_o = O.attn_norm_mix6_decode(rt(x), rt(prev), rt(nw), rt(nb), [rt(m) for m in mixes])
+    pv = prev.clone()
+    outs = hb.fused_attn_norm_mix6_decode(x, pv, nw, nb, *mixes)
+    np.testing.assert_allclose(npf(torch.stack(outs)), np.stack(outs_o), rtol=2e-2, atol=2e-2)
+    np.testing.assert_allclose(npf(pv), prev_o, rtol=2e-2, atol=2e-2)
+    from hf_adapter_b200.lora import small_gemm_group
+    W = bf(0.05 * rng.standard_normal((72, D)))
+    (yl,) = small_gemm_group((x,), (W,), acts=(2,))
+    ref = 1 / (1 + np.exp(-(rt(x) @ rt(W).T)))
+    np.testing.assert_allclose(npf(yl), ref, rtol=2e-2, atol=2e-2)
+    # scan in bf16 storage
+    T = 20
+    rs, ks, vs = (bf(rng.standard_normal((B, T, Hh, N))) for _ in range(3))
+    kks = bf(rt(ks) / np.linalg.norm(rt(ks), axis=-1, keepdims=True))
+    as_ = bf(1 / (1 + np.exp(-rng.standard_normal((B, T, Hh, N)))))
+    ws = np.exp(-0.606531 / (1 + np.exp(-rng.standard_normal((B, T, Hh, N))))).astype(np.float32)
+    yo2, so2 = O.recurrent_scan(rt(rs), ws, rt(ks), rt(vs), rt(kks), rt(as_), state)
+    y2, s2 = hb.fused_recurrent_scan(rs, cu(ws), ks, vs, kks, as_, cu(state))
+    assert rel_err(npf(s2), so2) < 2e-5
+    np.testing.assert_allclose(npf(y2), yo2, rtol=2e-2, atol=3e-2)
