@@ -247,4 +247,27 @@ inline int make_tmap_x3d(CUtensorMap* map, const void* base, uint64_t rows, uint
     return RWKV7_OK;
 }
 
+// Token vectors [tokens, H, 64] of 2- or 4-byte elements viewed as (64 channels, H, tokens): a box {64, 1, 64} at
+// (0, h, t0) lands the 64-token slice of one head densely ([token][channel], no swizzle).
+inline int make_tmap_tokens(CUtensorMap* map, const void* base, int elem_bytes, uint64_t tokens, uint64_t H) {
+    EncodeTiledFn fn = get_encode_tiled();
+    if (!fn) {
+        set_error("cuTensorMapEncodeTiled is unavailable (no CUDA driver?)");
+        return RWKV7_ERR_CUDA;
+    }
+    cuuint64_t dims[3] = {64, H, tokens};
+    cuuint64_t strides[2] = {(cuuint64_t)64 * elem_bytes, (cuuint64_t)64 * elem_bytes * H};
+    cuuint32_t box[3] = {64, 1, 64};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                    const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled (token map) failed with code %d (tokens=%llu H=%llu)", (int)r,
+                  (unsigned long long)tokens, (unsigned long long)H);
+        return RWKV7_ERR_CUDA;
+    }
+    return RWKV7_OK;
+}
+
 }  // namespace rwkv7

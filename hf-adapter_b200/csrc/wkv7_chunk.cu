@@ -48,12 +48,12 @@ __device__ __forceinline__ float to_tf32(float x) {
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
     return __uint_as_float(u);
 }
-__device__ __forceinline__ void ck_cp16(void* smem, const void* g, bool valid) {
-    const int sz = valid ? 16 : 0;
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(smem)), "l"(g), "r"(sz));
-}
 
-__global__ void __launch_bounds__(ck::THREADS, 1) wkv7_chunk_kernel(const ChunkArgs p) {
+struct ChunkMaps {
+    CUtensorMap m[6];  // r, k, v, kk, a, w viewed as (64 channels, H, B*T tokens)
+};
+
+__global__ void __launch_bounds__(ck::THREADS, 1) wkv7_chunk_kernel(const __grid_constant__ ChunkMaps maps, const ChunkArgs p) {
     using namespace ck;
     extern __shared__ unsigned char smem_unaligned[];
     unsigned char* sm = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);
@@ -68,8 +68,11 @@ __global__ void __launch_bounds__(ck::THREADS, 1) wkv7_chunk_kernel(const ChunkA
     float* part = reinterpret_cast<float*>(sm + R_SMALL);  // [4][64] partial log-decay sums
     float* gref = part + 256;                              // [64]
     float* gl = gref + 64;                                 // [64]
-    uint64_t* bar = reinterpret_cast<uint64_t*>(gl + 64);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 1);
+    float* egref = gl + 64;                                // [64] e^{gref}
+    float* egl = egref + 64;                               // [64] e^{gl}
+    uint64_t* bar = reinterpret_cast<uint64_t*>(egl + 64);
+    uint64_t* raw_bar = bar + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(raw_bar + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const AbortCtx actx{abort_flag, p.error};
 
@@ -83,8 +86,10 @@ __global__ void __launch_bounds__(ck::THREADS, 1) wkv7_chunk_kernel(const ChunkA
 
     if (tid == 0) {
         mbar_init(bar, 1);
+        mbar_init(raw_bar, 1);
         *abort_flag = 0;
         mbar_fence_init();
+        for (int i = 0; i < 6; ++i) tma_prefetch_desc(&maps.m[i]);
     }
     if (warp == 0) tmem_alloc(tmem_slot, TMEM_COLS);
     // rows 64..127 of the fp16 A-operand tiles stay zero for the whole kernel
@@ -101,25 +106,17 @@ __global__ void __launch_bounds__(ck::THREADS, 1) wkv7_chunk_kernel(const ChunkA
         }
     }
 
+    // one thread fetches the six [64 tokens x 64 channels] slices of a tile with TMA (rows of the other heads are
+    // skipped by the tensor map); tokens past T in the last tile are masked where they are consumed
     auto load_raw = [&](int t0) {
-        // 5 x (64 tokens x 8 chunks) + w (64 x 8 or 16 chunks)
-        const int wch = 64 * wbytes / 16;
-        const int per_tok = 40 + wch;
-        for (int idx = tid; idx < C * per_tok; idx += THREADS) {
-            const int t = idx / per_tok, qq = idx % per_tok;
-            const bool valid = (t0 + t) < p.T;
-            const size_t goff = base + (size_t)(valid ? t0 + t : 0) * tok_stride;
-            if (qq < 40) {
-                const int which = qq >> 3, ch = qq & 7;
-                const __half* src = which == 0 ? p.r : which == 1 ? p.k : which == 2 ? p.v : which == 3 ? p.kk : p.a;
-                ck_cp16(raw_r + which * 4096 + t * 64 + ch * 8, src + goff + ch * 8, valid);
-            } else {
-                const int ch = qq - 40;
-                ck_cp16(reinterpret_cast<char*>(raw_w) + t * 64 * wbytes + ch * 16,
-                        reinterpret_cast<const char*>(p.w) + goff * wbytes + ch * 16, valid);
-            }
-        }
-        asm volatile("cp.async.commit_group;\n" ::);
+        mbar_expect_tx(raw_bar, 5 * 8192 + 64 * 64 * wbytes);
+        const int row = b * p.T + t0;
+        tma_load_3d(raw_r, &maps.m[0], raw_bar, 0, h, row);
+        tma_load_3d(raw_k, &maps.m[1], raw_bar, 0, h, row);
+        tma_load_3d(raw_v, &maps.m[2], raw_bar, 0, h, row);
+        tma_load_3d(raw_kk, &maps.m[3], raw_bar, 0, h, row);
+        tma_load_3d(raw_a, &maps.m[4], raw_bar, 0, h, row);
+        tma_load_3d(raw_w, &maps.m[5], raw_bar, 0, h, row);
     };
 
     tc_fence_before();
@@ -137,13 +134,19 @@ __global__ void __launch_bounds__(ck::THREADS, 1) wkv7_chunk_kernel(const ChunkA
     };
 
     const int ntiles = (p.T + C - 1) / C;
-    load_raw(0);
+    if (tid == 0) load_raw(0);
+    uint32_t raw_phase = 0;
     for (int tile = 0; tile < ntiles && ok; ++tile) {
         const int t0 = tile * C;
-        asm volatile("cp.async.wait_group 0;\n" ::);
-        __syncthreads();
+        if (lane == 0) ok = mbar_wait(raw_bar, raw_phase, actx, kErrWaitFull);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        raw_phase ^= 1;
+        if (!ok) break;
         // ---------------- phase A: log-decay prefix sums, decay factors, operand tiles
+        // step 1, thread = (channel n, token quarter tq): prefix sums along tokens, f1 = e^{gi-gref} to shared memory,
+        // and the token-transposed fp16 tiles (rows = channel) with 16-byte stores
         const int n = tid & 63, tq = tid >> 6;
+        float* F1 = reinterpret_cast<float*>(sm + R_S0);  // [64 tokens][64 channels]; the S0 tile is written after phase A
         float lw[16];
         {
             float run = 0.f;
@@ -152,10 +155,10 @@ __global__ void __launch_bounds__(ck::THREADS, 1) wkv7_chunk_kernel(const ChunkA
                 const int t = tq * 16 + j;
                 float v = 0.f;
                 if (t0 + t < p.T) {
-                    if (p.w_mode == 1) v = logf(raw_w[t * 64 + n]);
+                    if (p.w_mode == 1) v = __logf(raw_w[t * 64 + n]);
                     else {
                         const float wv = __half2float(reinterpret_cast<const __half*>(raw_w)[t * 64 + n]);
-                        v = p.w_mode == 2 ? -0.606531f * sigmoidf_(wv) : logf(wv);
+                        v = p.w_mode == 2 ? -0.606531f * sigmoidf_(wv) : __logf(wv);
                     }
                 }
                 run += v;
@@ -170,8 +173,13 @@ __global__ void __launch_bounds__(ck::THREADS, 1) wkv7_chunk_kernel(const ChunkA
             if (tq == 0) {
                 gref[n] = g_ref;
                 gl[n] = g_l;
+                egref[n] = __expf(g_ref);
+                egl[n] = __expf(g_l);
             }
             float gi = tq == 0 ? 0.f : tq == 1 ? p0 : tq == 2 ? p0 + p1 : p0 + p1 + p2;
+            // e^{gref-gi} = 1/f1 and e^{gl-gi} = e^{gl-gref}/f1
+            const float e_lr = __expf(g_l - g_ref);
+            uint32_t kdp[8], bdp[8], vvp[8];
 #pragma unroll
             for (int j = 0; j < 16; j += 2) {
                 float kd[2], bd[2];
@@ -179,40 +187,90 @@ __global__ void __launch_bounds__(ck::THREADS, 1) wkv7_chunk_kernel(const ChunkA
 #pragma unroll
                 for (int u = 0; u < 2; ++u) {
                     const int t = tq * 16 + j + u;
-                    const float ge = gi;
+                    const bool valid = t0 + t < p.T;
                     gi += lw[j + u];
-                    const float f1 = expf(gi - g_ref), f2 = expf(ge - g_ref), f3 = expf(g_ref - gi), f4 = expf(g_l - gi);
-                    const float rr = __half2float(raw_r[t * 64 + n]), kx = __half2float(raw_k[t * 64 + n]);
-                    const float kkx = __half2float(raw_kk[t * 64 + n]), ax = __half2float(raw_a[t * 64 + n]);
-                    const float bx = kkx * ax;
-                    *reinterpret_cast<float*>(sm + R_A + sw128_offset(t, n * 4, 128)) = to_tf32(-kkx * f2);
-                    *reinterpret_cast<float*>(sm + R_A + sw128_offset(64 + t, n * 4, 128)) = to_tf32(rr * f1);
-                    *reinterpret_cast<float*>(sm + R_B + sw128_offset(t, n * 4, 128)) = to_tf32(kx * f3);
-                    *reinterpret_cast<float*>(sm + R_B + sw128_offset(64 + t, n * 4, 128)) = to_tf32(bx * f3);
+                    const float f1 = __expf(gi - g_ref);
+                    F1[t * 64 + n] = f1;
+                    const float f4 = e_lr * __frcp_rn(f1);
+                    const float kx = valid ? __half2float(raw_k[t * 64 + n]) : 0.f;
+                    const float bx = valid ? __half2float(raw_kk[t * 64 + n]) * __half2float(raw_a[t * 64 + n]) : 0.f;
                     kd[u] = kx * f4;
                     bd[u] = bx * f4;
-                    vv[u] = raw_v[t * 64 + n];
+                    vv[u] = valid ? raw_v[t * 64 + n] : __float2half(0.f);
                 }
-                const int t = tq * 16 + j;  // even: (t, t+1) share one 4-byte word of the transposed tiles
-                *reinterpret_cast<__half2*>(sm + R_KB + sw128_offset(n, t * 2, 64)) = __floats2half2_rn(kd[0], kd[1]);
-                *reinterpret_cast<__half2*>(sm + R_KB + sw128_offset(n, (64 + t) * 2, 64)) = __floats2half2_rn(bd[0], bd[1]);
-                *reinterpret_cast<__half2*>(sm + R_VU + sw128_offset(n, t * 2, 128)) = __halves2half2(vv[0], vv[1]);
+                const __half2 hk = __floats2half2_rn(kd[0], kd[1]), hb = __floats2half2_rn(bd[0], bd[1]), hv = __halves2half2(vv[0], vv[1]);
+                kdp[j >> 1] = *reinterpret_cast<const uint32_t*>(&hk);
+                bdp[j >> 1] = *reinterpret_cast<const uint32_t*>(&hb);
+                vvp[j >> 1] = *reinterpret_cast<const uint32_t*>(&hv);
+            }
+            // 16 tokens = 32 bytes = two 16-byte chunks of row n
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const uint32_t kb = (tq * 16 + c * 8) * 2;
+                *reinterpret_cast<uint4*>(sm + R_KB + sw128_offset(n, kb, 64)) = make_uint4(kdp[c * 4], kdp[c * 4 + 1], kdp[c * 4 + 2], kdp[c * 4 + 3]);
+                *reinterpret_cast<uint4*>(sm + R_KB + sw128_offset(n, 128 + kb, 64)) = make_uint4(bdp[c * 4], bdp[c * 4 + 1], bdp[c * 4 + 2], bdp[c * 4 + 3]);
+                *reinterpret_cast<uint4*>(sm + R_VU + sw128_offset(n, kb, 128)) = make_uint4(vvp[c * 4], vvp[c * 4 + 1], vvp[c * 4 + 2], vvp[c * 4 + 3]);
             }
         }
-        __syncthreads();  // gref / gl visible; raw buffer consumed
-        if (tile + 1 < ntiles) load_raw(t0 + C);
+        __syncthreads();  // F1, gref visible
+        // step 2, thread = (token t, 16 channels): the token-major tf32 tiles with 16-byte loads and stores
+        {
+            const int t = tid >> 2, nb = (tid & 3) * 16;
+            const bool valid = t0 + t < p.T;
+            float r16[16], k16[16], kk16[16], a16[16];
+            load8(raw_r + t * 64 + nb, reinterpret_cast<float(&)[8]>(r16[0]));
+            load8(raw_r + t * 64 + nb + 8, reinterpret_cast<float(&)[8]>(r16[8]));
+            load8(raw_k + t * 64 + nb, reinterpret_cast<float(&)[8]>(k16[0]));
+            load8(raw_k + t * 64 + nb + 8, reinterpret_cast<float(&)[8]>(k16[8]));
+            load8(raw_kk + t * 64 + nb, reinterpret_cast<float(&)[8]>(kk16[0]));
+            load8(raw_kk + t * 64 + nb + 8, reinterpret_cast<float(&)[8]>(kk16[8]));
+            load8(raw_a + t * 64 + nb, reinterpret_cast<float(&)[8]>(a16[0]));
+            load8(raw_a + t * 64 + nb + 8, reinterpret_cast<float(&)[8]>(a16[8]));
+#pragma unroll
+            for (int c = 0; c < 16; c += 4) {
+                const float4 f1 = *reinterpret_cast<const float4*>(F1 + t * 64 + nb + c);
+                float4 f2;  // e^{ge-gref}: f1 of the previous token; e^{-gref} for the first one
+                if (t > 0) f2 = *reinterpret_cast<const float4*>(F1 + (t - 1) * 64 + nb + c);
+                else {
+                    const float4 er = *reinterpret_cast<const float4*>(egref + nb + c);
+                    f2 = make_float4(__frcp_rn(er.x), __frcp_rn(er.y), __frcp_rn(er.z), __frcp_rn(er.w));
+                }
+                const float f1v[4] = {f1.x, f1.y, f1.z, f1.w}, f2v[4] = {f2.x, f2.y, f2.z, f2.w};
+                float ae[4], rp[4], ki[4], bi[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float m = valid ? 1.f : 0.f;
+                    const float f3 = __frcp_rn(f1v[e]);
+                    ae[e] = to_tf32(-kk16[c + e] * f2v[e] * m);
+                    rp[e] = to_tf32(r16[c + e] * f1v[e] * m);
+                    ki[e] = to_tf32(k16[c + e] * f3 * m);
+                    bi[e] = to_tf32(kk16[c + e] * a16[c + e] * f3 * m);
+                }
+                const uint32_t kb = (nb + c) * 4;
+                *reinterpret_cast<float4*>(sm + R_A + sw128_offset(t, kb, 128)) = make_float4(ae[0], ae[1], ae[2], ae[3]);
+                *reinterpret_cast<float4*>(sm + R_A + sw128_offset(64 + t, kb, 128)) = make_float4(rp[0], rp[1], rp[2], rp[3]);
+                *reinterpret_cast<float4*>(sm + R_B + sw128_offset(t, kb, 128)) = make_float4(ki[0], ki[1], ki[2], ki[3]);
+                *reinterpret_cast<float4*>(sm + R_B + sw128_offset(64 + t, kb, 128)) = make_float4(bi[0], bi[1], bi[2], bi[3]);
+            }
+        }
+        __syncthreads();  // raw buffers and F1 consumed
+        if (tid == 0 && tile + 1 < ntiles) {
+            fence_proxy_async_smem();  // generic reads of the raw buffers are ordered before the refill
+            load_raw(t0 + C);
+        }
         if (tl < 64) {  // S0 e^{gref} operand tile and the D3 accumulator initialised with S0 e^{gl}
             uint32_t d3[32];
 #pragma unroll
             for (int c = 0; c < 32; c += 4) {
                 float4 o;
-                o.x = to_tf32(S[c] * expf(gref[hi * 32 + c]));
-                o.y = to_tf32(S[c + 1] * expf(gref[hi * 32 + c + 1]));
-                o.z = to_tf32(S[c + 2] * expf(gref[hi * 32 + c + 2]));
-                o.w = to_tf32(S[c + 3] * expf(gref[hi * 32 + c + 3]));
+                const float4 er = *reinterpret_cast<const float4*>(egref + hi * 32 + c);
+                o.x = to_tf32(S[c] * er.x);
+                o.y = to_tf32(S[c + 1] * er.y);
+                o.z = to_tf32(S[c + 2] * er.z);
+                o.w = to_tf32(S[c + 3] * er.w);
                 *reinterpret_cast<float4*>(sm + R_S0 + sw128_offset(tl, (hi * 32 + c) * 4, 64)) = o;
 #pragma unroll
-                for (int e = 0; e < 4; ++e) d3[c + e] = __float_as_uint(S[c + e] * expf(gl[hi * 32 + c + e]));
+                for (int e = 0; e < 4; ++e) d3[c + e] = __float_as_uint(S[c + e] * egl[hi * 32 + c + e]);
             }
             tmem_st16(lane_addr + D3_COL + hi * 32, reinterpret_cast<uint32_t(&)[16]>(d3[0]));
             tmem_st16(lane_addr + D3_COL + hi * 32 + 16, reinterpret_cast<uint32_t(&)[16]>(d3[16]));
@@ -297,7 +355,7 @@ __global__ void __launch_bounds__(ck::THREADS, 1) wkv7_chunk_kernel(const ChunkA
         }
         wait_mma();
         if (!ok) break;
-        // ---------------- phase D: U = (I - tril_strict(A_ab))^-1 rhs  (forward substitution, one thread per value column)
+        // ---------------- phase D: U = (I - tril_strict(A_ab))^-1 rhs
         if (tl < 64) {
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
@@ -312,32 +370,56 @@ __global__ void __launch_bounds__(ck::THREADS, 1) wkv7_chunk_kernel(const ChunkA
         }
         tc_fence_before();
         __syncthreads();
-        if (tid < 64) {
-            float U[64];
+        // Blocked forward substitution on 16-row blocks, U overwriting rhs in RH: the off-diagonal update
+        // rhs_b += L[b][0..b) U[0..b) is spread over all threads, the 16-step in-block solve runs one thread per
+        // value column.
+        {
+            const int i = tid & 63, tg = tid >> 6;
+#pragma unroll 1
+            for (int blk = 0; blk < 4; ++blk) {
+                if (blk > 0) {
+                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                    const int tr = blk * 16 + tg * 4;  // this thread's four rows
+                    for (int s0 = 0; s0 < blk * 16; s0 += 4) {
+                        const float u0 = RH[(s0 + 0) * ABS + i], u1 = RH[(s0 + 1) * ABS + i];
+                        const float u2 = RH[(s0 + 2) * ABS + i], u3 = RH[(s0 + 3) * ABS + i];
 #pragma unroll
-            for (int t = 0; t < 64; ++t) {
-                float a0 = RH[t * ABS + tid], a1 = 0.f, a2 = 0.f, a3 = 0.f;
+                        for (int rr = 0; rr < 4; ++rr) {
+                            const float4 m = *reinterpret_cast<const float4*>(AB + (tr + rr) * ABS + s0);
+                            acc[rr] = fmaf(m.x, u0, fmaf(m.y, u1, fmaf(m.z, u2, fmaf(m.w, u3, acc[rr]))));
+                        }
+                    }
 #pragma unroll
-                for (int s = 0; s + 3 < t; s += 4) {
-                    const float4 m = *reinterpret_cast<const float4*>(AB + t * ABS + s);
-                    a0 = fmaf(m.x, U[s], a0); a1 = fmaf(m.y, U[s + 1], a1);
-                    a2 = fmaf(m.z, U[s + 2], a2); a3 = fmaf(m.w, U[s + 3], a3);
+                    for (int rr = 0; rr < 4; ++rr) RH[(tr + rr) * ABS + i] += acc[rr];
+                    __syncthreads();
                 }
+                if (tid < 64) {
+                    float u[16];
 #pragma unroll
-                for (int s = t & ~3; s < t; ++s) a0 = fmaf(AB[t * ABS + s], U[s], a0);
-                U[t] = (a0 + a1) + (a2 + a3);
-            }
-            // U^T into the second K atom of [V^T | U^T]: row = value index, k = 64 + token
+                    for (int tt = 0; tt < 16; ++tt) {
+                        const int t = blk * 16 + tt;
+                        float a0 = RH[t * ABS + tid], a1 = 0.f;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                uint32_t pk[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const __half2 h2 = __floats2half2_rn(U[c * 8 + 2 * e], U[c * 8 + 2 * e + 1]);
-                    pk[e] = *reinterpret_cast<const uint32_t*>(&h2);
+                        for (int ss = 0; ss + 1 < tt; ss += 2) {
+                            a0 = fmaf(AB[t * ABS + blk * 16 + ss], u[ss], a0);
+                            a1 = fmaf(AB[t * ABS + blk * 16 + ss + 1], u[ss + 1], a1);
+                        }
+                        if (tt & 1) a0 = fmaf(AB[t * ABS + blk * 16 + tt - 1], u[tt - 1], a0);
+                        u[tt] = a0 + a1;
+                        RH[t * ABS + tid] = u[tt];
+                    }
                 }
-                *reinterpret_cast<uint4*>(sm + R_VU + sw128_offset(tid, (64 + c * 8) * 2, 128)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                __syncthreads();
             }
+            // U^T into the second K atom of [V^T | U^T]: row = value index i, k = 64 + token; thread (i, tg) packs 16 tokens
+            uint32_t pk[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const __half2 h2 = __floats2half2_rn(RH[(tg * 16 + 2 * e) * ABS + i], RH[(tg * 16 + 2 * e + 1) * ABS + i]);
+                pk[e] = *reinterpret_cast<const uint32_t*>(&h2);
+            }
+            *reinterpret_cast<uint4*>(sm + R_VU + sw128_offset(i, (64 + tg * 16) * 2, 128)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            *reinterpret_cast<uint4*>(sm + R_VU + sw128_offset(i, (64 + tg * 16 + 8) * 2, 128)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
         }
         fence_proxy_async_smem();
         __syncthreads();
@@ -390,7 +472,6 @@ __global__ void __launch_bounds__(ck::THREADS, 1) wkv7_chunk_kernel(const ChunkA
         __syncthreads();  // accumulators and operand tiles are free for the next tile
     }
 
-    asm volatile("cp.async.wait_group 0;\n" ::);
     if (tl < 64 && *abort_flag == 0) {
         float* sp = p.state_out + ((size_t)bh * N + tl) * N + hi * 32;
 #pragma unroll
@@ -424,8 +505,14 @@ extern "C" int rwkv7_wkv7_chunk_scan(const void* r, const void* w, const void* k
                 reinterpret_cast<const __half*>(kk), reinterpret_cast<const __half*>(a), w, state_in, state_out,
                 reinterpret_cast<__half*>(y), T, H, w_mode, kernel_error_word()};
     RWKV7_REQUIRE(p.error != nullptr, RWKV7_ERR_CUDA, "wkv7_chunk_scan: cannot resolve the device error word");
+    ChunkMaps maps;
+    const void* srcs[6] = {r, k, v, kk, a, w};
+    for (int i = 0; i < 6; ++i) {
+        const bool f32 = (i == 5 && w_mode == 1);
+        if (int e2 = make_tmap_tokens(&maps.m[i], srcs[i], f32 ? 4 : 2, (uint64_t)B * T, H)) return e2;
+    }
     cudaError_t e = cudaFuncSetAttribute(wkv7_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ck::SMEM_BYTES);
     RWKV7_REQUIRE(e == cudaSuccess, RWKV7_ERR_CUDA, "wkv7_chunk_scan: %s", cudaGetErrorString(e));
-    wkv7_chunk_kernel<<<B * H, ck::THREADS, ck::SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(p);
+    wkv7_chunk_kernel<<<B * H, ck::THREADS, ck::SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(maps, p);
     return check_launch("wkv7_chunk_kernel");
 }
