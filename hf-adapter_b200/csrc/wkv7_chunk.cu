@@ -18,7 +18,7 @@
 
 namespace rwkv7 {
 namespace ck {
-constexpr int C = 64, N = 64, THREADS = 256;
+constexpr int C = 64, N = 64, THREADS = 512;  // warps 0-7 own the TMEM lanes; warps 8-15 help in the CUDA-core phases
 constexpr int ABS = 68;  // row stride (floats) of the fp32 A_ab / rhs arrays: 16-byte aligned, conflict-free
 // shared-memory regions (bytes)
 constexpr int R_A = 0;                      // A1 (tf32 128x64) | later AE (fp16 128 x 128)
@@ -29,7 +29,9 @@ constexpr int R_VU = R_AK + 16384;          // [V^T | U^T] (fp16 128 x 128, rows
 constexpr int R_KB = R_VU + 32768;          // [kD ; bD]^T (fp16 64 x 128)
 constexpr int R_RAW = R_KB + 16384;         // r,k,v,kk,a (T 64x64 each) + w (fp32 64x64)
 constexpr int R_SMALL = R_RAW + 5 * 8192 + 16384;
-constexpr int SMEM_BYTES = R_SMALL + 2048 + 1024;
+constexpr int R_INV = R_SMALL + 4096;     // inverses of the four 16 x 16 diagonal blocks of I - tril_strict(A_ab) (fp32)
+constexpr int INVS = 20;                  // row stride (floats) of one inverse block: conflict-free 16-byte row reads
+constexpr int SMEM_BYTES = R_INV + 4 * 16 * INVS * 4 + 1024;
 constexpr int D1_COL = 0, D2_COL = 128, D3_COL = 192, TMEM_COLS = 256;
 }  // namespace ck
 
@@ -43,10 +45,14 @@ struct ChunkArgs {
     unsigned int* error;
 };
 
-__device__ __forceinline__ float to_tf32(float x) {
-    uint32_t u;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
-    return __uint_as_float(u);
+// Round to tf32 (nearest, ties away) with one integer add: the tensor core ignores the 13 low mantissa bits, so adding
+// half an ulp of tf32 to the bit pattern is all the rounding needs (cvt.rna.tf32 runs on the quarter-rate conversion
+// pipe, and this kernel rounds 16k values per tile).
+__device__ __forceinline__ float to_tf32(float x) { return __uint_as_float(__float_as_uint(x) + 0x1000u); }
+__device__ __forceinline__ float fast_rcp(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 
 struct ChunkMaps {
@@ -59,14 +65,16 @@ __global__ void __launch_bounds__(ck::THREADS, 1) wkv7_chunk_kernel(const __grid
     unsigned char* sm = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);
     float* AB = reinterpret_cast<float*>(sm + R_B);
     float* RH = AB + C * ABS;
+    float* UU = reinterpret_cast<float*>(sm + R_S0);   // U (fp32 64 x 64) during the solve; the S0 tile is dead by then
+    float* INV = reinterpret_cast<float*>(sm + R_INV);
     __half* raw_r = reinterpret_cast<__half*>(sm + R_RAW);
     __half* raw_k = raw_r + 4096;
     __half* raw_v = raw_k + 4096;
     __half* raw_kk = raw_v + 4096;
     __half* raw_a = raw_kk + 4096;
     float* raw_w = reinterpret_cast<float*>(raw_a + 4096);
-    float* part = reinterpret_cast<float*>(sm + R_SMALL);  // [4][64] partial log-decay sums
-    float* gref = part + 256;                              // [64]
+    float* part = reinterpret_cast<float*>(sm + R_SMALL);  // [8][64] partial log-decay sums
+    float* gref = part + 512;                              // [64]
     float* gl = gref + 64;                                 // [64]
     float* egref = gl + 64;                                // [64] e^{gref}
     float* egl = egref + 64;                               // [64] e^{gl}
@@ -77,7 +85,8 @@ __global__ void __launch_bounds__(ck::THREADS, 1) wkv7_chunk_kernel(const __grid
     const AbortCtx actx{abort_flag, p.error};
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int q = warp & 3, hi = warp >> 2;  // TMEM lane quarter / column half
+    const bool main_warp = warp < 8;
+    const int q = warp & 3, hi = (warp >> 2) & 1;  // TMEM lane quarter / column half (main warps)
     const int tl = q * 32 + lane;            // TMEM lane = accumulator row of this thread
     const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
     const size_t tok_stride = (size_t)p.H * N;
@@ -97,7 +106,7 @@ __global__ void __launch_bounds__(ck::THREADS, 1) wkv7_chunk_kernel(const __grid
 
     // state row of value index i = tl (< 64), columns hi*32..+31, kept in registers across tiles
     float S[32];
-    if (tl < 64) {
+    if (main_warp && tl < 64) {
         const float* sp = p.state_in + ((size_t)bh * N + tl) * N + hi * 32;
 #pragma unroll
         for (int c = 0; c < 32; c += 4) {
@@ -145,22 +154,21 @@ __global__ void __launch_bounds__(ck::THREADS, 1) wkv7_chunk_kernel(const __grid
         // ---------------- phase A: log-decay prefix sums, decay factors, operand tiles
         // step 1, thread = (channel n, token quarter tq): prefix sums along tokens, f1 = e^{gi-gref} to shared memory,
         // and the token-transposed fp16 tiles (rows = channel) with 16-byte stores
-        const int n = tid & 63, tq = tid >> 6;
+        const int n = tid & 63, tq = tid >> 6;  // tq = 0..7: tokens tq*8 .. tq*8+7
         float* F1 = reinterpret_cast<float*>(sm + R_S0);  // [64 tokens][64 channels]; the S0 tile is written after phase A
-        float lw[16];
+        float lw[8];
         {
+            float wv[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int t = tq * 8 + j;
+                wv[j] = p.w_mode == 1 ? raw_w[t * 64 + n] : __half2float(reinterpret_cast<const __half*>(raw_w)[t * 64 + n]);
+            }
             float run = 0.f;
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const int t = tq * 16 + j;
-                float v = 0.f;
-                if (t0 + t < p.T) {
-                    if (p.w_mode == 1) v = __logf(raw_w[t * 64 + n]);
-                    else {
-                        const float wv = __half2float(reinterpret_cast<const __half*>(raw_w)[t * 64 + n]);
-                        v = p.w_mode == 2 ? -0.606531f * sigmoidf_(wv) : __logf(wv);
-                    }
-                }
+            for (int j = 0; j < 8; ++j) {
+                float v = p.w_mode == 2 ? -0.606531f * sigmoidf_(wv[j]) : __logf(wv[j]);
+                v = (t0 + tq * 8 + j < p.T) ? v : 0.f;
                 run += v;
                 lw[j] = v;
             }
@@ -168,89 +176,94 @@ __global__ void __launch_bounds__(ck::THREADS, 1) wkv7_chunk_kernel(const __grid
         }
         __syncthreads();
         {
-            const float p0 = part[n], p1 = part[64 + n], p2 = part[128 + n], p3 = part[192 + n];
-            const float g_ref = p0 + p1, g_l = p0 + p1 + p2 + p3;
+            float gi = 0.f, g_ref = 0.f, g_l = 0.f;
+#pragma unroll
+            for (int qq = 0; qq < 8; ++qq) {
+                const float pv = part[qq * 64 + n];
+                gi += qq < tq ? pv : 0.f;
+                g_ref += qq < 4 ? pv : 0.f;
+                g_l += pv;
+            }
             if (tq == 0) {
                 gref[n] = g_ref;
                 gl[n] = g_l;
                 egref[n] = __expf(g_ref);
                 egl[n] = __expf(g_l);
             }
-            float gi = tq == 0 ? 0.f : tq == 1 ? p0 : tq == 2 ? p0 + p1 : p0 + p1 + p2;
             // e^{gref-gi} = 1/f1 and e^{gl-gi} = e^{gl-gref}/f1
             const float e_lr = __expf(g_l - g_ref);
-            uint32_t kdp[8], bdp[8], vvp[8];
+            float kx[8], bx[8];
+            __half vx[8];
 #pragma unroll
-            for (int j = 0; j < 16; j += 2) {
-                float kd[2], bd[2];
-                __half vv[2];
+            for (int j = 0; j < 8; ++j) {
+                const int t = tq * 8 + j;
+                const bool valid = t0 + t < p.T;
+                const float kv = __half2float(raw_k[t * 64 + n]);
+                const float bv = __half2float(raw_kk[t * 64 + n]) * __half2float(raw_a[t * 64 + n]);
+                const __half vv = raw_v[t * 64 + n];
+                kx[j] = valid ? kv : 0.f;
+                bx[j] = valid ? bv : 0.f;
+                vx[j] = valid ? vv : __float2half(0.f);
+            }
+            uint32_t kdp[4], bdp[4], vvp[4];
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {
+                float f4[2];
 #pragma unroll
                 for (int u = 0; u < 2; ++u) {
-                    const int t = tq * 16 + j + u;
-                    const bool valid = t0 + t < p.T;
                     gi += lw[j + u];
                     const float f1 = __expf(gi - g_ref);
-                    F1[t * 64 + n] = f1;
-                    const float f4 = e_lr * __frcp_rn(f1);
-                    const float kx = valid ? __half2float(raw_k[t * 64 + n]) : 0.f;
-                    const float bx = valid ? __half2float(raw_kk[t * 64 + n]) * __half2float(raw_a[t * 64 + n]) : 0.f;
-                    kd[u] = kx * f4;
-                    bd[u] = bx * f4;
-                    vv[u] = valid ? raw_v[t * 64 + n] : __float2half(0.f);
+                    F1[(tq * 8 + j + u) * 64 + n] = f1;
+                    f4[u] = e_lr * fast_rcp(f1);
                 }
-                const __half2 hk = __floats2half2_rn(kd[0], kd[1]), hb = __floats2half2_rn(bd[0], bd[1]), hv = __halves2half2(vv[0], vv[1]);
+                const __half2 hk = __floats2half2_rn(kx[j] * f4[0], kx[j + 1] * f4[1]);
+                const __half2 hb = __floats2half2_rn(bx[j] * f4[0], bx[j + 1] * f4[1]);
+                const __half2 hv = __halves2half2(vx[j], vx[j + 1]);
                 kdp[j >> 1] = *reinterpret_cast<const uint32_t*>(&hk);
                 bdp[j >> 1] = *reinterpret_cast<const uint32_t*>(&hb);
                 vvp[j >> 1] = *reinterpret_cast<const uint32_t*>(&hv);
             }
-            // 16 tokens = 32 bytes = two 16-byte chunks of row n
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                const uint32_t kb = (tq * 16 + c * 8) * 2;
-                *reinterpret_cast<uint4*>(sm + R_KB + sw128_offset(n, kb, 64)) = make_uint4(kdp[c * 4], kdp[c * 4 + 1], kdp[c * 4 + 2], kdp[c * 4 + 3]);
-                *reinterpret_cast<uint4*>(sm + R_KB + sw128_offset(n, 128 + kb, 64)) = make_uint4(bdp[c * 4], bdp[c * 4 + 1], bdp[c * 4 + 2], bdp[c * 4 + 3]);
-                *reinterpret_cast<uint4*>(sm + R_VU + sw128_offset(n, kb, 128)) = make_uint4(vvp[c * 4], vvp[c * 4 + 1], vvp[c * 4 + 2], vvp[c * 4 + 3]);
-            }
+            // 8 tokens = one 16-byte chunk of row n
+            const uint32_t kb = tq * 16;
+            *reinterpret_cast<uint4*>(sm + R_KB + sw128_offset(n, kb, 64)) = make_uint4(kdp[0], kdp[1], kdp[2], kdp[3]);
+            *reinterpret_cast<uint4*>(sm + R_KB + sw128_offset(n, 128 + kb, 64)) = make_uint4(bdp[0], bdp[1], bdp[2], bdp[3]);
+            *reinterpret_cast<uint4*>(sm + R_VU + sw128_offset(n, kb, 128)) = make_uint4(vvp[0], vvp[1], vvp[2], vvp[3]);
         }
         __syncthreads();  // F1, gref visible
-        // step 2, thread = (token t, 16 channels): the token-major tf32 tiles with 16-byte loads and stores
+        // step 2, thread = (token t, 8 channels): the token-major tf32 tiles with 16-byte loads and stores
         {
-            const int t = tid >> 2, nb = (tid & 3) * 16;
-            const bool valid = t0 + t < p.T;
-            float r16[16], k16[16], kk16[16], a16[16];
-            load8(raw_r + t * 64 + nb, reinterpret_cast<float(&)[8]>(r16[0]));
-            load8(raw_r + t * 64 + nb + 8, reinterpret_cast<float(&)[8]>(r16[8]));
-            load8(raw_k + t * 64 + nb, reinterpret_cast<float(&)[8]>(k16[0]));
-            load8(raw_k + t * 64 + nb + 8, reinterpret_cast<float(&)[8]>(k16[8]));
-            load8(raw_kk + t * 64 + nb, reinterpret_cast<float(&)[8]>(kk16[0]));
-            load8(raw_kk + t * 64 + nb + 8, reinterpret_cast<float(&)[8]>(kk16[8]));
-            load8(raw_a + t * 64 + nb, reinterpret_cast<float(&)[8]>(a16[0]));
-            load8(raw_a + t * 64 + nb + 8, reinterpret_cast<float(&)[8]>(a16[8]));
+            const int t = tid >> 3, nb = (tid & 7) * 8;
+            const float m = t0 + t < p.T ? 1.f : 0.f;
+            float r8[8], k8[8], kk8[8], a8[8], f1v[8], f2v[8];
+            load8(raw_r + t * 64 + nb, r8);
+            load8(raw_k + t * 64 + nb, k8);
+            load8(raw_kk + t * 64 + nb, kk8);
+            load8(raw_a + t * 64 + nb, a8);
+            load8(F1 + t * 64 + nb, f1v);
+            // e^{ge-gref}: f1 of the previous token; e^{-gref} for the first one
+            if (t > 0) load8(F1 + (t - 1) * 64 + nb, f2v);
+            else {
+                load8(egref + nb, f2v);
 #pragma unroll
-            for (int c = 0; c < 16; c += 4) {
-                const float4 f1 = *reinterpret_cast<const float4*>(F1 + t * 64 + nb + c);
-                float4 f2;  // e^{ge-gref}: f1 of the previous token; e^{-gref} for the first one
-                if (t > 0) f2 = *reinterpret_cast<const float4*>(F1 + (t - 1) * 64 + nb + c);
-                else {
-                    const float4 er = *reinterpret_cast<const float4*>(egref + nb + c);
-                    f2 = make_float4(__frcp_rn(er.x), __frcp_rn(er.y), __frcp_rn(er.z), __frcp_rn(er.w));
-                }
-                const float f1v[4] = {f1.x, f1.y, f1.z, f1.w}, f2v[4] = {f2.x, f2.y, f2.z, f2.w};
-                float ae[4], rp[4], ki[4], bi[4];
+                for (int e = 0; e < 8; ++e) f2v[e] = fast_rcp(f2v[e]);
+            }
+            float ae[8], rp[8], ki[8], bi[8];
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float m = valid ? 1.f : 0.f;
-                    const float f3 = __frcp_rn(f1v[e]);
-                    ae[e] = to_tf32(-kk16[c + e] * f2v[e] * m);
-                    rp[e] = to_tf32(r16[c + e] * f1v[e] * m);
-                    ki[e] = to_tf32(k16[c + e] * f3 * m);
-                    bi[e] = to_tf32(kk16[c + e] * a16[c + e] * f3 * m);
-                }
+            for (int e = 0; e < 8; ++e) {
+                const float f3 = fast_rcp(f1v[e]) * m;
+                const float kkm = kk8[e] * m;
+                ae[e] = to_tf32(-kkm * f2v[e]);
+                rp[e] = to_tf32(r8[e] * f1v[e] * m);
+                ki[e] = to_tf32(k8[e] * f3);
+                bi[e] = to_tf32(kk8[e] * a8[e] * f3);
+            }
+#pragma unroll
+            for (int c = 0; c < 8; c += 4) {
                 const uint32_t kb = (nb + c) * 4;
-                *reinterpret_cast<float4*>(sm + R_A + sw128_offset(t, kb, 128)) = make_float4(ae[0], ae[1], ae[2], ae[3]);
-                *reinterpret_cast<float4*>(sm + R_A + sw128_offset(64 + t, kb, 128)) = make_float4(rp[0], rp[1], rp[2], rp[3]);
-                *reinterpret_cast<float4*>(sm + R_B + sw128_offset(t, kb, 128)) = make_float4(ki[0], ki[1], ki[2], ki[3]);
-                *reinterpret_cast<float4*>(sm + R_B + sw128_offset(64 + t, kb, 128)) = make_float4(bi[0], bi[1], bi[2], bi[3]);
+                *reinterpret_cast<float4*>(sm + R_A + sw128_offset(t, kb, 128)) = make_float4(ae[c], ae[c + 1], ae[c + 2], ae[c + 3]);
+                *reinterpret_cast<float4*>(sm + R_A + sw128_offset(64 + t, kb, 128)) = make_float4(rp[c], rp[c + 1], rp[c + 2], rp[c + 3]);
+                *reinterpret_cast<float4*>(sm + R_B + sw128_offset(t, kb, 128)) = make_float4(ki[c], ki[c + 1], ki[c + 2], ki[c + 3]);
+                *reinterpret_cast<float4*>(sm + R_B + sw128_offset(64 + t, kb, 128)) = make_float4(bi[c], bi[c + 1], bi[c + 2], bi[c + 3]);
             }
         }
         __syncthreads();  // raw buffers and F1 consumed
@@ -258,7 +271,7 @@ __global__ void __launch_bounds__(ck::THREADS, 1) wkv7_chunk_kernel(const __grid
             fence_proxy_async_smem();  // generic reads of the raw buffers are ordered before the refill
             load_raw(t0 + C);
         }
-        if (tl < 64) {  // S0 e^{gref} operand tile and the D3 accumulator initialised with S0 e^{gl}
+        if (main_warp && tl < 64) {  // S0 e^{gref} operand tile and the D3 accumulator initialised with S0 e^{gl}
             uint32_t d3[32];
 #pragma unroll
             for (int c = 0; c < 32; c += 4) {
@@ -302,7 +315,7 @@ __global__ void __launch_bounds__(ck::THREADS, 1) wkv7_chunk_kernel(const __grid
             const int atom = i >> 9, rem = i & 511;
             reinterpret_cast<uint4*>(sm + R_A + atom * 16384)[rem] = make_uint4(0, 0, 0, 0);
         }
-        {
+        if (main_warp) {
             const int t = tl & 63;
             const bool low = tl < 64;  // rows of a~E (low) or rP (high)
 #pragma unroll
@@ -353,10 +366,29 @@ __global__ void __launch_bounds__(ck::THREADS, 1) wkv7_chunk_kernel(const __grid
             for (int j = 0; j < 4; ++j) umma_f16_ss(tmem + D2_COL, da + (uint64_t)(j * 2), db + (uint64_t)(j * 2), idh, 1);
             tc_commit(bar);
         }
+        // While that product runs, four helper warps invert the 16 x 16 diagonal blocks of I - tril_strict(A_ab):
+        // lane c of warp 8 + b builds column c of block b by forward substitution in registers.
+        if (warp >= 8 && warp < 12 && lane < 16) {
+            const int blk = warp - 8;
+            const float* L = AB + (blk * 16) * ABS + blk * 16;
+            float x[16];
+#pragma unroll
+            for (int t = 0; t < 16; ++t) {
+                float a0 = t == lane ? 1.f : 0.f, a1 = 0.f;
+#pragma unroll
+                for (int ss = 0; ss + 1 < t; ss += 2) {
+                    a0 = fmaf(L[t * ABS + ss], x[ss], a0);
+                    a1 = fmaf(L[t * ABS + ss + 1], x[ss + 1], a1);
+                }
+                if (t & 1) a0 = fmaf(L[t * ABS + t - 1], x[t - 1], a0);
+                x[t] = a0 + a1;
+                INV[(blk * 16 + t) * INVS + lane] = x[t];
+            }
+        }
         wait_mma();
         if (!ok) break;
         // ---------------- phase D: U = (I - tril_strict(A_ab))^-1 rhs
-        if (tl < 64) {
+        if (main_warp && tl < 64) {
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 uint32_t v[16];
@@ -370,56 +402,66 @@ __global__ void __launch_bounds__(ck::THREADS, 1) wkv7_chunk_kernel(const __grid
         }
         tc_fence_before();
         __syncthreads();
-        // Blocked forward substitution on 16-row blocks, U overwriting rhs in RH: the off-diagonal update
-        // rhs_b += L[b][0..b) U[0..b) is spread over all threads, the 16-step in-block solve runs one thread per
-        // value column.
-        {
-            const int i = tid & 63, tg = tid >> 6;
+        // Blocked forward substitution on 16-row blocks.  Value columns are independent, so warp w < 4 sweeps columns
+        // 16 w .. 16 w + 15 through all four blocks with warp-level syncs only; a lane owns rows rg, rg+4, rg+8, rg+12 of
+        // the block and two columns (a 4 x 2 register tile keeps the shared-memory wavefronts per FMA low):
+        //   (a) rhs_b += L[b][0..b) U[0..b)        (b) U_b = inv(I - L_bb) rhs_b
+        if (warp < 4) {
+            const int rg = lane >> 3, col = warp * 16 + (lane & 7) * 2;
 #pragma unroll 1
             for (int blk = 0; blk < 4; ++blk) {
+                const int r0 = blk * 16 + rg;
                 if (blk > 0) {
-                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-                    const int tr = blk * 16 + tg * 4;  // this thread's four rows
+                    float2 acc[4];
+#pragma unroll
+                    for (int rr = 0; rr < 4; ++rr) acc[rr] = *reinterpret_cast<const float2*>(RH + (r0 + 4 * rr) * ABS + col);
+#pragma unroll 2
                     for (int s0 = 0; s0 < blk * 16; s0 += 4) {
-                        const float u0 = RH[(s0 + 0) * ABS + i], u1 = RH[(s0 + 1) * ABS + i];
-                        const float u2 = RH[(s0 + 2) * ABS + i], u3 = RH[(s0 + 3) * ABS + i];
+                        float2 u[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) u[e] = *reinterpret_cast<const float2*>(UU + (s0 + e) * 64 + col);
 #pragma unroll
                         for (int rr = 0; rr < 4; ++rr) {
-                            const float4 m = *reinterpret_cast<const float4*>(AB + (tr + rr) * ABS + s0);
-                            acc[rr] = fmaf(m.x, u0, fmaf(m.y, u1, fmaf(m.z, u2, fmaf(m.w, u3, acc[rr]))));
+                            const float4 m = *reinterpret_cast<const float4*>(AB + (r0 + 4 * rr) * ABS + s0);
+                            acc[rr].x = fmaf(m.x, u[0].x, fmaf(m.y, u[1].x, fmaf(m.z, u[2].x, fmaf(m.w, u[3].x, acc[rr].x))));
+                            acc[rr].y = fmaf(m.x, u[0].y, fmaf(m.y, u[1].y, fmaf(m.z, u[2].y, fmaf(m.w, u[3].y, acc[rr].y))));
                         }
                     }
 #pragma unroll
-                    for (int rr = 0; rr < 4; ++rr) RH[(tr + rr) * ABS + i] += acc[rr];
-                    __syncthreads();
+                    for (int rr = 0; rr < 4; ++rr) *reinterpret_cast<float2*>(RH + (r0 + 4 * rr) * ABS + col) = acc[rr];
+                    __syncwarp();
                 }
-                if (tid < 64) {
-                    float u[16];
+                float2 o[4];
 #pragma unroll
-                    for (int tt = 0; tt < 16; ++tt) {
-                        const int t = blk * 16 + tt;
-                        float a0 = RH[t * ABS + tid], a1 = 0.f;
+                for (int rr = 0; rr < 4; ++rr) o[rr] = make_float2(0.f, 0.f);
 #pragma unroll
-                        for (int ss = 0; ss + 1 < tt; ss += 2) {
-                            a0 = fmaf(AB[t * ABS + blk * 16 + ss], u[ss], a0);
-                            a1 = fmaf(AB[t * ABS + blk * 16 + ss + 1], u[ss + 1], a1);
-                        }
-                        if (tt & 1) a0 = fmaf(AB[t * ABS + blk * 16 + tt - 1], u[tt - 1], a0);
-                        u[tt] = a0 + a1;
-                        RH[t * ABS + tid] = u[tt];
+                for (int s0 = 0; s0 < 16; s0 += 4) {
+                    float2 x[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) x[e] = *reinterpret_cast<const float2*>(RH + (blk * 16 + s0 + e) * ABS + col);
+#pragma unroll
+                    for (int rr = 0; rr < 4; ++rr) {
+                        const float4 m = *reinterpret_cast<const float4*>(INV + (r0 + 4 * rr) * INVS + s0);
+                        o[rr].x = fmaf(m.x, x[0].x, fmaf(m.y, x[1].x, fmaf(m.z, x[2].x, fmaf(m.w, x[3].x, o[rr].x))));
+                        o[rr].y = fmaf(m.x, x[0].y, fmaf(m.y, x[1].y, fmaf(m.z, x[2].y, fmaf(m.w, x[3].y, o[rr].y))));
                     }
                 }
-                __syncthreads();
+#pragma unroll
+                for (int rr = 0; rr < 4; ++rr) *reinterpret_cast<float2*>(UU + (r0 + 4 * rr) * 64 + col) = o[rr];
+                __syncwarp();
             }
-            // U^T into the second K atom of [V^T | U^T]: row = value index i, k = 64 + token; thread (i, tg) packs 16 tokens
-            uint32_t pk[8];
+        }
+        __syncthreads();
+        {
+            const int i = tid & 63, tg = tid >> 6;
+            // U^T into the second K atom of [V^T | U^T]: row = value index i, k = 64 + token; thread (i, tg) packs 8 tokens
+            uint32_t pk[4];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                const __half2 h2 = __floats2half2_rn(RH[(tg * 16 + 2 * e) * ABS + i], RH[(tg * 16 + 2 * e + 1) * ABS + i]);
+            for (int e = 0; e < 4; ++e) {
+                const __half2 h2 = __floats2half2_rn(UU[(tg * 8 + 2 * e) * 64 + i], UU[(tg * 8 + 2 * e + 1) * 64 + i]);
                 pk[e] = *reinterpret_cast<const uint32_t*>(&h2);
             }
-            *reinterpret_cast<uint4*>(sm + R_VU + sw128_offset(i, (64 + tg * 16) * 2, 128)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-            *reinterpret_cast<uint4*>(sm + R_VU + sw128_offset(i, (64 + tg * 16 + 8) * 2, 128)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+            *reinterpret_cast<uint4*>(sm + R_VU + sw128_offset(i, (64 + tg * 8) * 2, 128)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
         }
         fence_proxy_async_smem();
         __syncthreads();
@@ -442,7 +484,7 @@ __global__ void __launch_bounds__(ck::THREADS, 1) wkv7_chunk_kernel(const __grid
         wait_mma();
         if (!ok) break;
         // ---------------- phase G: outputs of the tile, new state rows back to registers
-        {
+        if (main_warp) {
             uint32_t v[32];
             const uint32_t col = (tl < 64 ? D3_COL : D2_COL) + hi * 32;
             tmem_ld16(lane_addr + col, reinterpret_cast<uint32_t(&)[16]>(v[0]));
@@ -472,7 +514,7 @@ __global__ void __launch_bounds__(ck::THREADS, 1) wkv7_chunk_kernel(const __grid
         __syncthreads();  // accumulators and operand tiles are free for the next tile
     }
 
-    if (tl < 64 && *abort_flag == 0) {
+    if (main_warp && tl < 64 && *abort_flag == 0) {
         float* sp = p.state_out + ((size_t)bh * N + tl) * N + hi * 32;
 #pragma unroll
         for (int c = 0; c < 32; c += 4) *reinterpret_cast<float4*>(sp + c) = make_float4(S[c], S[c + 1], S[c + 2], S[c + 3]);
