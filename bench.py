@@ -187,6 +187,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="debug: override the layer count (invalidates the metric)")
     ap.add_argument("--prefill-tokens", type=int, default=1024)
     ap.add_argument("--prefill-chunk", type=int, default=512)
+    ap.add_argument("--prefill-scan-chunk", type=int, default=64,
+                    help="tile of the tensor-core WKV scan in the prefill sample (0 = sequential scan)")
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-scan", action="store_true")
@@ -346,15 +348,16 @@ def main():
     if not args.no_prefill and world == 1:
         Tp, ch = args.prefill_tokens, args.prefill_chunk
         pids = torch.randint(0, V, (B, Tp), generator=gen).to(dev)
-        model.rwkv7_prefill_chunks(pids[:, :ch], None, chunk_size=ch)
+        model.rwkv7_prefill_chunks(pids[:, :ch], None, chunk_size=ch, scan_chunk=args.prefill_scan_chunk)
         torch.cuda.synchronize()
         p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         p0.record()
-        model.rwkv7_prefill_chunks(pids, None, chunk_size=ch)
+        model.rwkv7_prefill_chunks(pids, None, chunk_size=ch, scan_chunk=args.prefill_scan_chunk)
         p1.record()
         torch.cuda.synchronize()
         pms = p0.elapsed_time(p1)
         prefill = {"value": B * Tp / (pms * 1e-3), "unit": "tok/s", "batch": B, "tokens": Tp, "chunk": ch, "ms": pms,
+                   "wkv_scan": "chunked_tcgen05" if args.prefill_scan_chunk else "sequential",
                    "note": "sample of the 8192-token prompts; throughput is chunk-invariant because only the O(1) state carries over"}
         del pids
         torch.cuda.empty_cache()

@@ -4,6 +4,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+
+#include <cstdlib>
 #include <stdint.h>
 
 #include <cstdarg>
@@ -34,6 +36,15 @@ inline int check_launch(const char* what) {
 }
 
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+// Programmatic dependent launch of the projection kernels is on unless RWKV7_B200_NO_PDL is set (read once).
+inline bool programmatic_launch_enabled() {
+    static const bool on = [] {
+        const char* v = getenv("RWKV7_B200_NO_PDL");
+        return !(v && *v && *v != '0');
+    }();
+    return on;
+}
 
 // ---- scalar conversion ----------------------------------------------------
 template <typename T> __device__ __forceinline__ float to_f(T v);
@@ -107,6 +118,14 @@ __device__ __forceinline__ void store8(T* p, const float (&o)[8]) {
         *reinterpret_cast<uint4*>(p) = t;
     }
 }
+
+// ---- programmatic dependent launch ------------------------------------------
+// A kernel launched with the programmatic-stream-serialization attribute may start while its predecessor in the
+// stream is still running; it must not touch anything the predecessor writes before grid_dependency_wait() returns
+// (which also makes the predecessor's writes visible).  Without the attribute both instructions are no-ops.
+// grid_launch_dependents() lets the successor start once every CTA of this grid has issued it (or exited).
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // ---- math -----------------------------------------------------------------
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }

@@ -65,6 +65,7 @@ struct Mix6Args {
 template <typename T>
 __global__ void __launch_bounds__(kNMThreads) attn_norm_mix6_kernel(const Mix6Args p) {
     __shared__ float red[32];
+    if (threadIdx.x == 0) grid_launch_dependents();  // the projections that follow prefetch their weights meanwhile
     const size_t row = blockIdx.x;
     const int D = p.D;
     RowStats<T> rs;
@@ -109,6 +110,7 @@ struct FfnMixArgs {
 template <typename T, bool ADD, bool MIX>
 __global__ void __launch_bounds__(kNMThreads) ffn_add_norm_mix_kernel(const FfnMixArgs p) {
     __shared__ float red[32];
+    if (threadIdx.x == 0) grid_launch_dependents();
     const size_t row = blockIdx.x;
     const int D = p.D;
     RowStats<T> rs;

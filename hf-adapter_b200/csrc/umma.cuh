@@ -77,6 +77,12 @@ __device__ __forceinline__ bool mbar_wait_hot(uint64_t* bar, uint32_t parity, co
     return false;
 }
 
+// ---------------------------------------------------------------- cluster barrier, split into arrive / wait
+// Every thread of every CTA of the cluster runs arrive and wait alternately, the same number of times.
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed;" ::: "memory"); }
+__device__ __forceinline__ void cluster_arrive_release() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
+
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* tmap, uint64_t* bar, int c0, int c1) {
     asm volatile(

@@ -17,14 +17,19 @@
 //     memory;
 //   * the activation tile [64 rows x 128 k] arrives by TMA (128-byte swizzle) and is the B operand
 //     from shared memory; D [128 x 64] fp32 accumulates in tensor memory;
-//   * split-K runs as a thread-block cluster along z; partial tiles are reduced through distributed
-//     shared memory in a fixed order (deterministic, no scratch buffer, no atomics), then the
-//     relu^2 / residual epilogue is applied and fp16 results are stored coalesced.
+//   * split-K runs as a thread-block cluster along z; every CTA PUSHES the rows of its partial tile that belong to
+//     rank k straight from the accumulator registers into slot [own rank] of rank k's shared memory (remote
+//     stores are fire-and-forget, remote loads would cost a round trip), one cluster barrier, then each rank sums
+//     its slots in fixed rank order (deterministic, no scratch buffer, no atomics), applies the relu^2 / residual
+//     epilogue and stores fp16 results coalesced.
 //
 // Warp roles: warp 0 = weight-stream producer, last warp = activation-tile producer, warp 1 and the last but one =
 // MMA issuers (warp 1 also owns the TMEM allocation), warps 2..2+4*SB-1 = SB dequantise groups (k-block i of a
 // super-block goes to group i) + epilogue.  All mbarrier waits are bounded (umma.cuh).
 #include <cooperative_groups.h>
+
+#include <mutex>
+#include <unordered_set>
 
 #include "umma.cuh"
 
@@ -37,7 +42,7 @@ constexpr int TILE_N = 128;  // output channels per CTA = UMMA M
 constexpr int KB = 128;      // k elements per pipeline stage
 constexpr int NB = 64;       // activation rows per MMA = UMMA N
 constexpr int STAGES = 6;    // activation-tile ring (L2-resident source, freed by the MMA commit)
-constexpr int WSTAGES = 12;  // weight-block ring (HBM source, freed as soon as the dequant warps have read it)
+constexpr int WSTAGES = 10;  // weight-block ring (HBM source, freed as soon as the dequant warps have read it)
 constexpr int RAW_BYTES = TILE_N * KB / 2;  // 8192 packed nibbles
 constexpr int SC_OFF = RAW_BYTES;           // then 128 fp16 scales of the k-block
 constexpr int Z_OFF = SC_OFF + TILE_N * 2;  // then 128 u8 zero-points, then padding
@@ -53,6 +58,7 @@ constexpr int D_COL = NAB * 64;
 constexpr int ISS2_WARP = 2 + SB * 4;           // second issuer = last warp
 constexpr int XPROD_WARP = ISS2_WARP + 1;       // activation-tile producer
 constexpr int THREADS = 64 + SB * 128 + 64;
+constexpr int Q_BYTES = NB * TILE_N * 4;        // split-K exchange: [rank slot][rows of this rank][128 channels] fp32
 }  // namespace w4
 
 struct W4UmmaArgs {
@@ -99,7 +105,8 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
     // a ring, and a weight block can be released ~10x earlier than the activation tile the MMAs still read.
     unsigned char* xs = smem;
     unsigned char* raws = smem + STAGES * X_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(raws + WSTAGES * BLOCK_BYTES);
+    float* Q = reinterpret_cast<float*>(raws + WSTAGES * BLOCK_BYTES);  // never aliased: peers write it while this CTA still streams
+    uint64_t* bars = reinterpret_cast<uint64_t*>(raws + WSTAGES * BLOCK_BYTES + Q_BYTES);
     uint64_t* full = bars;                   // [STAGES]  activation tile landed
     uint64_t* empty = bars + STAGES;         // [STAGES]  MMAs that read it completed
     uint64_t* wfull = bars + 2 * STAGES;     // [WSTAGES] weight block landed
@@ -110,7 +117,6 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_full + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const AbortCtx actx{abort_flag, p.error};
-    float* P = reinterpret_cast<float*>(smem);  // [NB][TILE_N] partial tile, reuses the x stages after the main loop
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.x * TILE_N;
@@ -121,6 +127,7 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
     const int nkb = p.nkb;
 
     if (tid == 0) {
+        grid_launch_dependents();
         tma_prefetch_desc(&tm_x);
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&full[s], 1);
@@ -143,6 +150,13 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Cluster barrier phase 0 = "every CTA of the cluster runs" (precondition of remote shared-memory stores): arrive
+    // now, wait only just before the first push.  Phase 1 orders the pushes before the reduction.
+    cg::cluster_group cluster = cg::this_cluster();
+    const bool clustered = p.splits > 1;
+    const int rows_per_rank = NB / p.splits;
+    if (clustered) cluster_arrive_relaxed();
+    bool waited0 = false;
 
     if (warp == 0) {
         if (lane == 0) {  // weight stream: one bulk copy per block (nibbles + scales + zero-points)
@@ -156,6 +170,10 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
         }
     } else if (warp == XPROD_WARP) {
         if (lane == 0) {  // activation tiles: both 64-k atoms of a block through one 3-D map (k_in, row, k_out)
+            // The activations are the only input the preceding kernel of the stream may still be writing: under a
+            // programmatic launch the weight stream, the dequantisation and the tensor-memory A buffers above run
+            // ahead of this point, in the shadow of that kernel.
+            grid_dependency_wait();
             for (int i = 0; i < nkb; ++i) {
                 const int s = i % STAGES;
                 if (i >= STAGES && !mbar_wait(&empty[s], ((i / STAGES) - 1) & 1, actx, kErrWaitEmpty)) break;
@@ -236,49 +254,66 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
             __syncwarp();
             if (lane == 0) mbar_arrive(&a_ready[ab]);
         }
-        // ---- accumulator tile -> shared memory partial P[m][n]; the two groups split the 64 columns
+        // ---- accumulator tile -> slot [this rank] of the owning rank's exchange buffer; groups 0 and 1 split the 64 columns
         if (ok && lane == 0) ok = mbar_wait(d_full, 0, actx, kErrWaitDFull);
         ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (ok) {
-            tc_fence_after();
-            constexpr int CPG = 32;  // accumulator columns per reading group (groups 0 and 1 read; others idle)
-#pragma unroll
-            for (int c = 0; c < (grp < 2 ? CPG / 16 : 0); ++c) {
-                uint32_t v[16], v2[16];
-                const int col0 = grp * CPG + c * 16;
-                tmem_ld16(lane_addr + D_COL + col0, v);
-                if (nkb > 1) tmem_ld16(lane_addr + D_COL + 64 + col0, v2);  // second issuer's accumulator (unused when it had no work)
-                tc_wait_ld();
-#pragma unroll
-                for (int e = 0; e < 16; ++e)
-                    P[(col0 + e) * TILE_N + row] = __uint_as_float(v[e]) + (nkb > 1 ? __uint_as_float(v2[e]) : 0.f);
+        if (grp < 2) {
+            if (clustered) {
+                cluster_wait();
+                waited0 = true;
             }
-            tc_fence_before();
+            if (ok) {
+                tc_fence_after();
+                constexpr int CPG = 32;  // accumulator columns (activation rows) per reading group
+#pragma unroll
+                for (int c = 0; c < CPG / 16; ++c) {
+                    uint32_t v[16], v2[16];
+                    const int col0 = grp * CPG + c * 16;
+                    tmem_ld16(lane_addr + D_COL + col0, v);
+                    if (nkb > 1) tmem_ld16(lane_addr + D_COL + 64 + col0, v2);  // second issuer's accumulator (unused when it had no work)
+                    tc_wait_ld();
+                    if (col0 < m_rows) {
+                        // 16 consecutive rows never straddle two ranks (rows_per_rank is 8, 16, 32 or 64)
+#pragma unroll
+                        for (int h8 = 0; h8 < 2; ++h8) {
+                            const int m = col0 + h8 * 8;
+                            const int dst = m / rows_per_rank;
+                            float* q = (clustered ? cluster.map_shared_rank(Q, dst) : Q) +
+                                       ((size_t)split * rows_per_rank + (m - dst * rows_per_rank)) * TILE_N + row;
+#pragma unroll
+                            for (int e = 0; e < 8; ++e)
+                                q[e * TILE_N] = __uint_as_float(v[h8 * 8 + e]) + (nkb > 1 ? __uint_as_float(v2[h8 * 8 + e]) : 0.f);
+                        }
+                    }
+                }
+                tc_fence_before();
+            }
         }
     }
 
-    // ---- split-K reduction across the cluster (fixed rank order) + epilogue
-    cg::cluster_group cluster = cg::this_cluster();
-    __syncthreads();
-    if (p.splits > 1) cluster.sync();
+    // ---- split-K reduction (fixed rank order) + epilogue, from this CTA's own shared memory
+    if (clustered) {
+        if (!waited0) cluster_wait();
+        cluster_arrive_release();
+        cluster_wait();
+    } else {
+        __syncthreads();
+    }
     const bool aborted = (*abort_flag != 0);
+    grid_dependency_wait();  // residual reads and output writes are ordered after the preceding kernel (returns at once here:
+                             // the accumulators already depend on the activations)
     if (!aborted) {
         // Each thread owns one channel pair (n, n+1) and walks the rows of this rank's share in steps of
-        // THREADS/64, four rows per batch so that the (distributed) shared-memory loads of a batch are all in
-        // flight before the first conversion: float2 partial loads in fixed rank order, fp16 rounding, epilogue,
+        // THREADS/64, four rows per batch: float2 loads of the rank slots in fixed order, fp16 rounding, epilogue,
         // one 4-byte store; 64 consecutive threads cover one 256-byte output row segment.
-        const int rows_per_rank = NB / p.splits;
         const int m_begin = split * rows_per_rank;
         const int m_end = min(m_rows, m_begin + rows_per_rank);
         const int n = (tid & 63) * 2;
         const bool n_ok = n0 + n < p.Nout;
         const bool pair = (n0 + n + 1 < p.Nout) && ((p.Nout & 1) == 0);
         constexpr int RSTEP = (THREADS - 64) / 64;  // the last two warps (second issuer, x producer) sit the epilogue out
-        const float* P0 = P + n;
-        const float* P1 = p.splits > 1 ? cluster.map_shared_rank(P, 1) + n : P0;
-        const float* P2 = p.splits > 2 ? cluster.map_shared_rank(P, 2) + n : P0;
-        const float* P3 = p.splits > 2 ? cluster.map_shared_rank(P, 3) + n : P0;
-        if (p.splits > 1) P0 = cluster.map_shared_rank(P, 0) + n;
+        const float* Q0 = Q + n - (size_t)m_begin * TILE_N;  // slot r, global row m: Q0[(r * rows_per_rank + m) * TILE_N]
+        const int slot = rows_per_rank * TILE_N;
         for (int mb = m_begin + (tid >> 6); mb < m_end && n_ok && tid < RSTEP * 64; mb += 4 * RSTEP) {
             float2 acc[4];
 #pragma unroll
@@ -286,19 +321,9 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
                 const int m = mb + u * RSTEP;
                 acc[u] = make_float2(0.f, 0.f);
                 if (m < m_end) {
-                    acc[u] = *reinterpret_cast<const float2*>(P0 + m * TILE_N);
-                    if (p.splits > 1) {
-                        const float2 v = *reinterpret_cast<const float2*>(P1 + m * TILE_N);
-                        acc[u].x += v.x; acc[u].y += v.y;
-                    }
-                    if (p.splits > 2) {
-                        const float2 v = *reinterpret_cast<const float2*>(P2 + m * TILE_N);
-                        const float2 w = *reinterpret_cast<const float2*>(P3 + m * TILE_N);
-                        acc[u].x += v.x; acc[u].y += v.y;
-                        acc[u].x += w.x; acc[u].y += w.y;
-                    }
-                    for (int r = 4; r < p.splits; ++r) {
-                        const float2 v = *reinterpret_cast<const float2*>(cluster.map_shared_rank(P, r) + n + m * TILE_N);
+                    acc[u] = *reinterpret_cast<const float2*>(Q0 + m * TILE_N);
+                    for (int r = 1; r < p.splits; ++r) {
+                        const float2 v = *reinterpret_cast<const float2*>(Q0 + r * slot + m * TILE_N);
                         acc[u].x += v.x; acc[u].y += v.y;
                     }
                 }
@@ -331,8 +356,7 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
             }
         }
     }
-    if (p.splits > 1) cluster.sync();  // peers may still be reading this CTA's partial tile
-    __syncthreads();
+    __syncthreads();  // nothing remote is touched after the barrier above, so the CTA may leave on its own
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, TMEM_COLS);
@@ -374,6 +398,21 @@ __global__ void w4g_repack_kernel(const uint8_t* __restrict__ packed, const T* _
     }
 }
 
+// Tiled buffers written by rwkv7_w4g_repack and not yet read by a projection.  The projection kernel streams the
+// weights BEFORE its grid-dependency wait, so the first projection after a repack is launched with full stream
+// ordering (it may directly follow the repack kernel); every later one is ordered behind that launch.
+static std::mutex g_fresh_mu;
+static std::unordered_set<const void*> g_fresh_tiled;
+
+static void mark_tiled_fresh(const void* tiled) {
+    std::lock_guard<std::mutex> lk(g_fresh_mu);
+    g_fresh_tiled.insert(tiled);
+}
+static bool take_tiled_fresh(const void* tiled) {
+    std::lock_guard<std::mutex> lk(g_fresh_mu);
+    return g_fresh_tiled.erase(tiled) != 0;
+}
+
 int launch_w4g_umma_tiled(const void* x, const uint8_t* tw, const void* residual, void* out, int M, int K, int Nout,
                           int epilogue, cudaStream_t st) {
     using namespace w4;
@@ -395,7 +434,7 @@ int launch_w4g_umma_tiled(const void* x, const uint8_t* tw, const void* residual
     W4UmmaArgs a{tw, reinterpret_cast<const __half*>(residual),
                  reinterpret_cast<__half*>(out), M, K, Nout, epilogue, nkb, total_kb, splits, kernel_error_word()};
     RWKV7_REQUIRE(a.error != nullptr, RWKV7_ERR_CUDA, "w4g_gemv_tiled: cannot resolve the device error word");
-    const size_t smem = (size_t)STAGES * X_BYTES + (size_t)WSTAGES * BLOCK_BYTES + (2 * STAGES + 2 * WSTAGES + 2 * NA + 1) * 8 + 16 + 1024;
+    const size_t smem = (size_t)STAGES * X_BYTES + (size_t)WSTAGES * BLOCK_BYTES + Q_BYTES + (2 * STAGES + 2 * WSTAGES + 2 * NA + 1) * 8 + 16 + 1024;
     cudaError_t e = cudaFuncSetAttribute(w4g_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     RWKV7_REQUIRE(e == cudaSuccess, RWKV7_ERR_CUDA, "w4g_gemv_tiled: %s", cudaGetErrorString(e));
     cudaLaunchConfig_t cfg{};
@@ -403,13 +442,16 @@ int launch_w4g_umma_tiled(const void* x, const uint8_t* tw, const void* residual
     cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = splits;
+    // programmatic dependent launch: start under the tail of the preceding kernel (see grid_dependency_wait in the kernel)
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = (programmatic_launch_enabled() && !take_tiled_fresh(tw)) ? 2 : 1;
     e = cudaLaunchKernelEx(&cfg, w4g_umma_kernel, tm_x, a);
     RWKV7_REQUIRE(e == cudaSuccess, RWKV7_ERR_CUDA, "w4g_gemv_tiled launch: %s", cudaGetErrorString(e));
     return RWKV7_OK;
@@ -437,6 +479,7 @@ extern "C" int rwkv7_w4g_repack(const uint8_t* packed, const void* scales, const
     const long long words = tiles * (K / 128) * 2048;
     w4g_repack_kernel<__half><<<(unsigned)((words + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         packed, reinterpret_cast<const __half*>(scales), zeros, tiled, K, Nout, group, words);
+    mark_tiled_fresh(tiled);
     return check_launch("w4g_repack_kernel");
 }
 

@@ -38,6 +38,7 @@ __global__ void __launch_bounds__(kStepThreads) wkv7_step_kernel(const StepArgs 
     const int bh = blockIdx.x;
     const int h = bh % p.H;
     const int tid = threadIdx.x;
+    if (tid == 0) grid_launch_dependents();  // the output projection sets up and prefetches weights under this grid's tail
     const int l16 = tid & 15;
     const int rg = tid >> 4;
     const size_t vbase = (size_t)bh * kN;

@@ -273,7 +273,7 @@ class RWKV7ForCausalLM(nn.Module):
             if i == 0:
                 v_first = v
             a_sig = torch.sigmoid(a_pre)
-            if scan_chunk and T % scan_chunk == 0 and x.dtype != torch.float32:
+            if scan_chunk and T % scan_chunk == 0 and x.dtype == torch.float16:
                 y, new_state = _rec.self_chunk_rwkv7(r, w, k, v, kk, a_sig, state[i], chunk_size=scan_chunk)
                 out = _prep.fused_attn_output_prepare(y, r, k, v, g, at.r_k, at.g_norm.weight, at.g_norm.bias,
                                                       num_heads=H, head_dim=N, head_v_dim=N, eps=N * 1e-5)

@@ -101,3 +101,18 @@ def test_quantised_fp16_model_against_oracle(kind):
     # prefill path (dequantise + GEMM for many rows) agrees with the decode path
     lp, cp = model.rwkv7_prefill_native(cu(ids), None)
     np.testing.assert_allclose(npf(lp[:, -1]), npf(lg), rtol=3e-2, atol=3e-2)
+
+
+def test_prefill_with_tensor_core_scan_matches_sequential_scan():
+    """fp16 prefill of 128 tokens: the chunked (tcgen05) scan and the sequential scan give the same logits
+    and final recurrent state within fp16 tolerances."""
+    g = golden("model_tiny.npz")
+    model = load_tiny(g, torch.float16)
+    ids = torch.randint(0, 256, (3, 128), generator=torch.Generator().manual_seed(5)).cuda()
+    la, ca = model.rwkv7_prefill_native(ids, None, logits_to_keep=4)
+    lb, cb = model.rwkv7_prefill_native(ids, None, logits_to_keep=4, scan_chunk=64)
+    np.testing.assert_allclose(npf(lb), npf(la), rtol=2e-2, atol=2e-2)
+    sa, sb = npf(torch.stack(ca._state)), npf(torch.stack(cb._state))
+    assert np.linalg.norm(sa - sb) / np.linalg.norm(sa) < 5e-3
+    lc, cc = model.rwkv7_prefill_chunks(ids, None, chunk_size=64, scan_chunk=64)
+    np.testing.assert_allclose(npf(lc[:, -1]), npf(la[:, -1]), rtol=2e-2, atol=2e-2)
