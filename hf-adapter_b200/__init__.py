@@ -10,7 +10,7 @@ from .norm_mix import (fused_attn_norm_mix6_decode, fused_attn_sequence_shift_mi
 from .prep import fused_attn_output_prepare, fused_prefill_state_prep
 from .quant import (A8W8Linear, MM4Linear, MM8Linear, a8w8_linear, dynamic_a8_quant, int8_mm, quantize_model,
                     quantize_w4_groupwise, quantize_w8_row, quantize_weight_per_channel_int8, w4_dequant,
-                    w4_groupwise_linear, w4_repack_tiled, w4_tiled_linear, w8_dequant, w8_linear)
+                    w4_groupwise_linear, w4_repack_tiled, w4_tiled_linear, w4_tiled_linear_group, w8_dequant, w8_linear)
 from .recurrent import (dplr_chunk_scan, fused_recurrent_output_prepare, fused_recurrent_output_prepare_raw,
                         fused_recurrent_scan, fused_recurrent_scan_clampw, fused_recurrent_scan_output_prepare,
                         fused_recurrent_update, self_chunk_rwkv7)

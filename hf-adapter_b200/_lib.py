@@ -41,6 +41,7 @@ SIGNATURES = {
     "rwkv7_w4g_tiled_bytes": (L, [I, I]),
     "rwkv7_w4g_repack": (I, [P] * 4 + [I, I, I, I, P]),
     "rwkv7_w4g_gemv_tiled": (I, [P] * 4 + [I, I, I, I, I, P]),
+    "rwkv7_w4g_gemv_tiled_group": (I, [P] * 3 + [I, I, I, I, I, I, P]),
     "rwkv7_w8_gemv": (I, [P] * 5 + [I, I, I, I, I, P]),
     "rwkv7_w4g_dequant": (I, [P] * 4 + [I, I, I, I, P]),
     "rwkv7_w8_dequant": (I, [P] * 3 + [I, I, I, P]),

@@ -61,12 +61,18 @@ constexpr int THREADS = 64 + SB * 128 + 64;
 constexpr int Q_BYTES = NB * TILE_N * 4;        // split-K exchange: [rank slot][rows of this rank][128 channels] fp32
 }  // namespace w4
 
+constexpr int kW4MaxGroup = 4;  // projections of equal shape served by one launch (r / k / v of a layer)
+
 struct W4UmmaArgs {
-    const uint8_t* tw;   // tiled weights: [tiles][K/128] blocks of BLOCK_BYTES = [4 chunks][128 channels][16 B] | scales | zeros
-    const __half* residual;
-    __half* out;
-    int M, K, Nout, epilogue, nkb, kbt, splits;  // kbt = K / 128 (k-blocks per channel tile)
+    const uint8_t* tw[kW4MaxGroup];  // tiled weights: [tiles][K/128] blocks of BLOCK_BYTES = [4 chunks][128 channels][16 B] | scales | zeros
+    __half* out[kW4MaxGroup];
+    const __half* residual;          // add epilogue (single projection only)
+    int M, K, Nout, epilogue, nkb, kbt, splits, row_blocks;  // kbt = K / 128 (k-blocks per channel tile)
     unsigned int* error;
+};
+
+struct W4Maps {
+    CUtensorMap x[kW4MaxGroup];  // activations of each projection as (k_in 64, row, k_out)
 };
 
 // One 32-bit word of the tiled format holds 8 consecutive k in the nibble order [k0 k2 k4 k6 k1 k3 k5 k7]
@@ -95,7 +101,7 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint
 }
 
 __global__ void __launch_bounds__(w4::THREADS, 1)
-w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
+w4g_umma_kernel(const __grid_constant__ W4Maps maps, const W4UmmaArgs p) {
     using namespace w4;
     extern __shared__ unsigned char smem_unaligned[];
     // the swizzled TMA / UMMA tiles need 1024-byte alignment; the offset is the same in every CTA
@@ -120,7 +126,11 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.x * TILE_N;
-    const int m0 = blockIdx.y * NB;                 // activation row block of this CTA
+    const int grp_idx = blockIdx.y / p.row_blocks;  // which projection of the group
+    const CUtensorMap* tm_x = &maps.x[grp_idx];
+    const uint8_t* tw = p.tw[grp_idx];
+    __half* outp = p.out[grp_idx];
+    const int m0 = (blockIdx.y % p.row_blocks) * NB;  // activation row block of this CTA
     const int m_rows = min(NB, p.M - m0);           // valid rows in the block
     const int split = blockIdx.z;
     const int kb0 = split * p.nkb;
@@ -128,7 +138,7 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
 
     if (tid == 0) {
         grid_launch_dependents();
-        tma_prefetch_desc(&tm_x);
+        tma_prefetch_desc(tm_x);
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
@@ -165,7 +175,7 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
                 if (i >= WSTAGES && !mbar_wait(&wempty[s], ((i / WSTAGES) - 1) & 1, actx, kErrWaitEmpty)) break;
                 mbar_expect_tx(&wfull[s], BLOCK_BYTES);
                 const size_t blk = (size_t)blockIdx.x * p.kbt + kb0 + i;  // tile-major block index
-                bulk_load(raws + s * BLOCK_BYTES, p.tw + blk * BLOCK_BYTES, BLOCK_BYTES, &wfull[s]);
+                bulk_load(raws + s * BLOCK_BYTES, tw + blk * BLOCK_BYTES, BLOCK_BYTES, &wfull[s]);
             }
         }
     } else if (warp == XPROD_WARP) {
@@ -178,7 +188,7 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
                 const int s = i % STAGES;
                 if (i >= STAGES && !mbar_wait(&empty[s], ((i / STAGES) - 1) & 1, actx, kErrWaitEmpty)) break;
                 mbar_expect_tx(&full[s], X_BYTES);
-                tma_load_3d(xs + s * X_BYTES, &tm_x, &full[s], 0, m0, (kb0 + i) * 2);
+                tma_load_3d(xs + s * X_BYTES, tm_x, &full[s], 0, m0, (kb0 + i) * 2);
             }
         }
     } else if (warp == 1 || warp == ISS2_WARP) {
@@ -348,10 +358,10 @@ w4g_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4UmmaArgs p) {
                     }
                 }
                 if (pair) {
-                    *reinterpret_cast<__half2*>(p.out + o) = __floats2half2_rn(y0, y1);
+                    *reinterpret_cast<__half2*>(outp + o) = __floats2half2_rn(y0, y1);
                 } else {
-                    p.out[o] = __float2half_rn(y0);
-                    if (n0 + n + 1 < p.Nout) p.out[o + 1] = __float2half_rn(y1);
+                    outp[o] = __float2half_rn(y0);
+                    if (n0 + n + 1 < p.Nout) outp[o + 1] = __float2half_rn(y1);
                 }
             }
         }
@@ -413,32 +423,44 @@ static bool take_tiled_fresh(const void* tiled) {
     return g_fresh_tiled.erase(tiled) != 0;
 }
 
-int launch_w4g_umma_tiled(const void* x, const uint8_t* tw, const void* residual, void* out, int M, int K, int Nout,
-                          int epilogue, cudaStream_t st) {
+// G projections of equal shape (their own activations, weights and outputs) in one launch.
+int launch_w4g_umma_tiled(const void* const* xs, const uint8_t* const* tws, const void* residual, void* const* outs, int G,
+                          int M, int K, int Nout, int epilogue, cudaStream_t st) {
     using namespace w4;
-    RWKV7_REQUIRE(M >= 1 && M <= 65535 * NB, RWKV7_ERR_UNSUPPORTED, "w4g_gemv_tiled: M out of range (got %d)", M);
+    RWKV7_REQUIRE(G >= 1 && G <= kW4MaxGroup, RWKV7_ERR_UNSUPPORTED, "w4g_gemv_tiled: 1..%d projections per launch (got %d)", kW4MaxGroup, G);
+    RWKV7_REQUIRE(M >= 1 && (long long)G * ((M + NB - 1) / NB) <= 65535, RWKV7_ERR_UNSUPPORTED, "w4g_gemv_tiled: M out of range (got %d)", M);
     const int row_blocks = (M + NB - 1) / NB;  // each block of 64 activation rows is one pass over the weights
     RWKV7_REQUIRE(K % KB == 0, RWKV7_ERR_UNSUPPORTED, "w4g_gemv_tiled: K must be a multiple of %d (got %d)", KB, K);
     const int tiles = (Nout + TILE_N - 1) / TILE_N;
     const int total_kb = K / KB;
     int splits = 1;
     for (int s = 8; s >= 2; s >>= 1) {
-        if (tiles * row_blocks * s <= 160 && total_kb % s == 0 && (total_kb / s) >= 4) {
+        if (tiles * row_blocks * G * s <= 160 && total_kb % s == 0 && (total_kb / s) >= 4) {
             splits = s;
             break;
         }
     }
     const int nkb = total_kb / splits;
-    CUtensorMap tm_x;
-    if (int e = make_tmap_x3d(&tm_x, x, M, K, NB)) return e;
-    W4UmmaArgs a{tw, reinterpret_cast<const __half*>(residual),
-                 reinterpret_cast<__half*>(out), M, K, Nout, epilogue, nkb, total_kb, splits, kernel_error_word()};
+    W4Maps maps;
+    W4UmmaArgs a{};
+    bool fresh = false;
+    for (int g = 0; g < G; ++g) {
+        if (int e = make_tmap_x3d(&maps.x[g], xs[g], M, K, NB)) return e;
+        a.tw[g] = tws[g];
+        a.out[g] = reinterpret_cast<__half*>(outs[g]);
+        fresh |= take_tiled_fresh(tws[g]);
+    }
+    for (int g = G; g < kW4MaxGroup; ++g) maps.x[g] = maps.x[0];
+    a.residual = reinterpret_cast<const __half*>(residual);
+    a.M = M; a.K = K; a.Nout = Nout; a.epilogue = epilogue; a.nkb = nkb; a.kbt = total_kb; a.splits = splits;
+    a.row_blocks = row_blocks;
+    a.error = kernel_error_word();
     RWKV7_REQUIRE(a.error != nullptr, RWKV7_ERR_CUDA, "w4g_gemv_tiled: cannot resolve the device error word");
     const size_t smem = (size_t)STAGES * X_BYTES + (size_t)WSTAGES * BLOCK_BYTES + Q_BYTES + (2 * STAGES + 2 * WSTAGES + 2 * NA + 1) * 8 + 16 + 1024;
     cudaError_t e = cudaFuncSetAttribute(w4g_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     RWKV7_REQUIRE(e == cudaSuccess, RWKV7_ERR_CUDA, "w4g_gemv_tiled: %s", cudaGetErrorString(e));
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(tiles, row_blocks, splits);
+    cfg.gridDim = dim3(tiles, row_blocks * G, splits);
     cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
@@ -451,8 +473,8 @@ int launch_w4g_umma_tiled(const void* x, const uint8_t* tw, const void* residual
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = (programmatic_launch_enabled() && !take_tiled_fresh(tw)) ? 2 : 1;
-    e = cudaLaunchKernelEx(&cfg, w4g_umma_kernel, tm_x, a);
+    cfg.numAttrs = (programmatic_launch_enabled() && !fresh) ? 2 : 1;
+    e = cudaLaunchKernelEx(&cfg, w4g_umma_kernel, maps, a);
     RWKV7_REQUIRE(e == cudaSuccess, RWKV7_ERR_CUDA, "w4g_gemv_tiled launch: %s", cudaGetErrorString(e));
     return RWKV7_OK;
 }
@@ -490,5 +512,19 @@ extern "C" int rwkv7_w4g_gemv_tiled(const void* x, const uint8_t* tiled, const v
     RWKV7_REQUIRE(epilogue >= 0 && epilogue <= 2, RWKV7_ERR_INVALID, "w4g_gemv_tiled: bad epilogue code %d", epilogue);
     RWKV7_REQUIRE(epilogue != RWKV7_EPI_ADD || residual, RWKV7_ERR_INVALID, "w4g_gemv_tiled: residual is required for the add epilogue");
     RWKV7_REQUIRE(aligned(x, 16) && aligned(tiled, 16), RWKV7_ERR_ALIGN, "w4g_gemv_tiled: pointers must be 16-byte aligned");
-    return launch_w4g_umma_tiled(x, tiled, residual, out, M, K, Nout, epilogue, static_cast<cudaStream_t>(stream));
+    return launch_w4g_umma_tiled(&x, &tiled, residual, &out, 1, M, K, Nout, epilogue, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int rwkv7_w4g_gemv_tiled_group(const void* const* xs, const uint8_t* const* tiled, void* const* outs, int G, int M,
+                                          int K, int Nout, int epilogue, int dtype, void* stream) {
+    RWKV7_REQUIRE(xs && tiled && outs, RWKV7_ERR_INVALID, "w4g_gemv_tiled_group: null pointer");
+    RWKV7_REQUIRE(G >= 1 && G <= kW4MaxGroup, RWKV7_ERR_UNSUPPORTED, "w4g_gemv_tiled_group: 1..%d projections (got %d)", kW4MaxGroup, G);
+    RWKV7_REQUIRE(dtype == RWKV7_F16, RWKV7_ERR_UNSUPPORTED, "w4g_gemv_tiled_group: fp16 activations only");
+    RWKV7_REQUIRE(epilogue == RWKV7_EPI_NONE || epilogue == RWKV7_EPI_RELU2, RWKV7_ERR_INVALID,
+                  "w4g_gemv_tiled_group: epilogue must be none or relu^2 (got %d)", epilogue);
+    for (int g = 0; g < G; ++g) {
+        RWKV7_REQUIRE(xs[g] && tiled[g] && outs[g], RWKV7_ERR_INVALID, "w4g_gemv_tiled_group: null pointer in projection %d", g);
+        RWKV7_REQUIRE(aligned(xs[g], 16) && aligned(tiled[g], 16), RWKV7_ERR_ALIGN, "w4g_gemv_tiled_group: pointers must be 16-byte aligned");
+    }
+    return launch_w4g_umma_tiled(xs, tiled, nullptr, outs, G, M, K, Nout, epilogue, static_cast<cudaStream_t>(stream));
 }

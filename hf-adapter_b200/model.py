@@ -111,6 +111,20 @@ class NativeRWKV7Model(nn.Module):
         self.norm = nn.LayerNorm(config.hidden_size)
 
 
+def _rkv_grouped(at, xr, xk, xv):
+    """r / k / v through one grouped launch when all three are int4 projections of one shape that the tensor-core
+    decode kernel takes; None otherwise."""
+    mods = (at.r_proj, at.k_proj, at.v_proj)
+    if not all(isinstance(m, _q.MM4Linear) and m.bias is None for m in mods):
+        return None
+    if len({(m.in_features, m.out_features) for m in mods}) != 1:
+        return None
+    tiled = [m.tiled_for(x_) for m, x_ in zip(mods, (xr, xk, xv))]
+    if any(t is None for t in tiled):
+        return None
+    return _q.w4_tiled_linear_group((xr, xk, xv), tiled, mods[0].out_features, mods[0].in_features)
+
+
 def _linear(mod, x, *, relu2=False, residual=None, out=None):
     """Apply a projection operand: a quantised module of this package (epilogues fused through its
     rwkv7_forward_* hooks, as the reference's dispatch probes them: native_jit_graph_dispatch.py:487-523)
@@ -208,22 +222,28 @@ class RWKV7ForCausalLM(nn.Module):
                                                 acts=(1, 0, 2, 0))
                     w_raw, a_pre, g, vg_pre = _lora.small_gemm_group(hs, (wl[2].weight, al[2].weight, gl[2].weight, vl[2].weight))
                     extra = dict(v_first=v_first, v_gate=vg_pre, v_gate_bias=vl[2].bias, v_gate_is_raw=True)
-            # r / k / v are independent too: separate branches let the tail of one projection overlap the ramp-up
-            # of the next
-            sk, sv = self._side_stream(x.device, 1), self._side_stream(x.device, 2)
-            sk.wait_stream(main)
-            sv.wait_stream(main)
-            with torch.cuda.stream(sk):
-                k = _linear(at.k_proj, xk)
-            with torch.cuda.stream(sv):
-                v = _linear(at.v_proj, xv)
-            r = _linear(at.r_proj, xr)
-            main.wait_stream(side)
-            main.wait_stream(sk)
-            main.wait_stream(sv)
+            rkv = _rkv_grouped(at, xr, xk, xv)
+            if rkv is not None:
+                # int4 r / k / v of equal shape: one launch streams all three weight sets (one pipeline fill, no
+                # split-K exchange) instead of three launches competing for the SMs
+                r, k, v = rkv
+                main.wait_stream(side)
+            else:
+                # independent projections on separate branches: the tail of one overlaps the ramp-up of the next
+                sk, sv = self._side_stream(x.device, 1), self._side_stream(x.device, 2)
+                sk.wait_stream(main)
+                sv.wait_stream(main)
+                with torch.cuda.stream(sk):
+                    k = _linear(at.k_proj, xk)
+                with torch.cuda.stream(sv):
+                    v = _linear(at.v_proj, xv)
+                r = _linear(at.r_proj, xr)
+                main.wait_stream(side)
+                main.wait_stream(sk)
+                main.wait_stream(sv)
+                xk.record_stream(sk); k.record_stream(sk); xv.record_stream(sv); v.record_stream(sv)
             for t_ in (xw, xa, xg, xv, w_raw, a_pre, g):
                 t_.record_stream(side)
-            xk.record_stream(sk); k.record_stream(sk); xv.record_stream(sv); v.record_stream(sv)
             out, _ = _rec.fused_recurrent_output_prepare_raw(
                 r, w_raw, k, v, a_pre, state[i], g, at.k_k, at.k_a, at.r_k, at.g_norm.weight, at.g_norm.bias,
                 eps=N * 1e-5, new_state=state[i], w_bias=wl[2].bias, a_bias=al[2].bias, a_is_raw=True, **extra)

@@ -120,6 +120,25 @@ def w4_tiled_linear(x, tiled, out_features, in_features, *, out=None, relu2: boo
     return y.reshape(*x.shape[:-1], Nout)
 
 
+def w4_tiled_linear_group(xs, tileds, out_features, in_features, *, relu2: bool = False):
+    """Up to four projections of the same shape in ONE launch of the tensor-core kernel: ``ys[g] = xs[g] @ W_g^T``
+    (the r / k / v projections of a layer).  Returns the list of outputs."""
+    import ctypes
+    K, Nout, G = int(in_features), int(out_features), len(xs)
+    if not 1 <= G <= 4 or len(tileds) != G:
+        raise ValueError("w4_tiled_linear_group takes 1..4 activations and as many tiled weights")
+    x2 = [_rows(x, K).contiguous() for x in xs]
+    M = int(x2[0].shape[0])
+    if any(int(t.shape[0]) != M or t.dtype != x2[0].dtype for t in x2):
+        raise ValueError("grouped projections need the same row count and dtype")
+    require_cuda(*x2, *tileds, what="w4_tiled_linear_group")
+    ys = [torch.empty((M, Nout), device=x2[0].device, dtype=x2[0].dtype) for _ in range(G)]
+    arr = lambda ts: (ctypes.c_void_p * G)(*[t.data_ptr() for t in ts])
+    _lib.check(_lib.lib.rwkv7_w4g_gemv_tiled_group(arr(x2), arr(tileds), arr(ys), G, M, K, Nout, _lib.EPI_RELU2 if relu2 else
+                                                   _lib.EPI_NONE, dt_code(x2[0]), stream_ptr(x2[0])), "w4_tiled_linear_group")
+    return [y.reshape(*x.shape[:-1], Nout) for y, x in zip(ys, xs)]
+
+
 def w8_dequant(q, s, out=None):
     Nout, K = (int(v) for v in q.shape)
     require_cuda(q, s, what="w8_dequant")
@@ -311,14 +330,21 @@ class MM4Linear(torch.nn.Module):
             self.bias = None
         self.fused = bool(fused)
 
-    def _lin(self, x, **kw):
+    def tiled_for(self, x):
+        """The tiled weight copy when ``x`` is eligible for the tensor-core decode kernel (built once per device,
+        on first use), else None."""
         rows = x.numel() // self.in_features
-        if rows <= TILED_MAX_ROWS and x.dtype == torch.float16 and x.is_cuda and self.in_features % 128 == 0:
-            # decode: tensor-core kernel on the tiled copy (built once per device, on first use)
-            t = self._tiled
-            if t is None or t.device != x.device:
-                t = self._tiled = w4_repack_tiled(self.packed_group, self.group_scales, self.in_features,
-                                                  self.group_size, self.group_zeros)
+        if not (rows <= TILED_MAX_ROWS and x.dtype == torch.float16 and x.is_cuda and self.in_features % 128 == 0):
+            return None
+        t = self._tiled
+        if t is None or t.device != x.device:
+            t = self._tiled = w4_repack_tiled(self.packed_group, self.group_scales, self.in_features,
+                                              self.group_size, self.group_zeros)
+        return t
+
+    def _lin(self, x, **kw):
+        t = self.tiled_for(x)
+        if t is not None:
             return w4_tiled_linear(x, t, self.out_features, self.in_features, **kw)
         return w4_groupwise_linear(x, self.packed_group, self.group_scales, self.out_features, self.in_features,
                                    group_size=self.group_size, zeros=self.group_zeros, **kw)

@@ -187,6 +187,12 @@ int rwkv7_w4g_repack(const uint8_t* packed, const void* scales, const uint8_t* z
                      int group, int dtype, void* stream);
 int rwkv7_w4g_gemv_tiled(const void* x, const uint8_t* tiled, const void* residual, void* out, int M, int K, int Nout,
                          int epilogue, int dtype, void* stream);
+/* G (1..4) projections of the same shape in one launch, each with its own activations xs[g] [M,K], tiled weights and
+ * output outs[g] [M,Nout] (the r / k / v projections of a layer: rwkv7_hf/native_model.py RWKV7Attention.forward calls
+ * them back to back on different mixes of the same hidden state).  The three pointer arrays live in host memory and
+ * are read during the call.  Epilogue none or relu^2. */
+int rwkv7_w4g_gemv_tiled_group(const void* const* xs, const uint8_t* const* tiled, void* const* outs, int G, int M, int K,
+                               int Nout, int epilogue, int dtype, void* stream);
 
 /* int8 per-output-channel weights, quantize_w8_row format (rwkv7_hf/sm70_quant.py:485-489): q [Nout,K] i8,
  * scale [Nout] in `dtype`.  Replaces w8_linear (:522) / the W8A16 GEMV (native_quant_a8w8.py:50-132). */

@@ -163,3 +163,34 @@ def test_w4g_tensor_core_path(M, K, Nn):
     mod = hb.MM4Linear(lin.half(), group_size=128).cuda()
     assert torch.equal(mod(xg), y) and mod._tiled is not None
     assert _lib.kernel_status(True) == 0
+
+
+@pytest.mark.parametrize("G,M,K,Nn", [(3, 64, 4096, 4096), (3, 7, 512, 200), (2, 130, 1024, 256), (4, 64, 1024, 128), (1, 33, 2048, 384)])
+def test_w4g_grouped_projections(G, M, K, Nn):
+    """G projections of one shape in a single launch: each output equals the oracle (and, where the split-K plan is
+    the same, the single-projection launch bit for bit); relu^2 epilogue; wrong group sizes are refused."""
+    from hf_adapter_b200 import _lib
+    rng = np.random.default_rng(G * 1000 + M + K + Nn)
+    xs, tiled, ref = [], [], []
+    for g in range(G):
+        W = (0.02 * rng.standard_normal((Nn, K))).astype(np.float16)
+        x = rng.standard_normal((M, K)).astype(np.float16)
+        packed, scales = O.quantize_w4_groupwise(W, 128)
+        ref.append(O.w4_groupwise_linear(x, packed, scales).astype(np.float32))
+        xs.append(cu(x))
+        tiled.append(hb.w4_repack_tiled(cu(packed), cu(scales), K, 128))
+    _lib.kernel_status(True)
+    ys = hb.w4_tiled_linear_group(xs, tiled, Nn, K)
+    assert _lib.kernel_status(True) == 0 and len(ys) == G
+    for y, yo, x, t in zip(ys, ref, xs, tiled):
+        tol_abs = 2e-3 * max(1.0, float(np.abs(yo).max()))
+        np.testing.assert_allclose(npf(y), yo, rtol=2e-3, atol=tol_abs)
+        np.testing.assert_allclose(npf(y), npf(hb.w4_tiled_linear(x, t, Nn, K)), rtol=2e-3, atol=tol_abs)
+    again = hb.w4_tiled_linear_group(xs, tiled, Nn, K)
+    assert all(torch.equal(a, b) for a, b in zip(again, ys))
+    yr = hb.w4_tiled_linear_group(xs, tiled, Nn, K, relu2=True)
+    for y, yo in zip(yr, ref):
+        ro = (np.maximum(yo.astype(np.float16).astype(np.float32), 0) ** 2).astype(np.float16).astype(np.float32)
+        np.testing.assert_allclose(npf(y), ro, rtol=6e-3, atol=8e-3 * max(1.0, float(np.abs(yo).max())))
+    with pytest.raises(ValueError):
+        hb.w4_tiled_linear_group(xs * 5, tiled * 5, Nn, K)
