@@ -165,8 +165,14 @@ w4g_umma_kernel(const __grid_constant__ W4Maps maps, const W4UmmaArgs p) {
     cg::cluster_group cluster = cg::this_cluster();
     const bool clustered = p.splits > 1;
     const int rows_per_rank = NB / p.splits;
+    // The two producer threads have work that does not depend on anything; everybody else would only idle until the
+    // first weight block lands, so they take the phase-0 wait now, off the tail of the kernel.
     if (clustered) cluster_arrive_relaxed();
     bool waited0 = false;
+    if (clustered && !((warp == 0 || warp == XPROD_WARP) && lane == 0)) {
+        cluster_wait();
+        waited0 = true;
+    }
 
     if (warp == 0) {
         if (lane == 0) {  // weight stream: one bulk copy per block (nibbles + scales + zero-points)
@@ -268,10 +274,6 @@ w4g_umma_kernel(const __grid_constant__ W4Maps maps, const W4UmmaArgs p) {
         if (ok && lane == 0) ok = mbar_wait(d_full, 0, actx, kErrWaitDFull);
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (grp < 2) {
-            if (clustered) {
-                cluster_wait();
-                waited0 = true;
-            }
             if (ok) {
                 tc_fence_after();
                 constexpr int CPG = 32;  // accumulator columns (activation rows) per reading group
@@ -331,10 +333,19 @@ w4g_umma_kernel(const __grid_constant__ W4Maps maps, const W4UmmaArgs p) {
                 const int m = mb + u * RSTEP;
                 acc[u] = make_float2(0.f, 0.f);
                 if (m < m_end) {
-                    acc[u] = *reinterpret_cast<const float2*>(Q0 + m * TILE_N);
-                    for (int r = 1; r < p.splits; ++r) {
-                        const float2 v = *reinterpret_cast<const float2*>(Q0 + r * slot + m * TILE_N);
-                        acc[u].x += v.x; acc[u].y += v.y;
+                    const float* q = Q0 + m * TILE_N;
+                    acc[u] = *reinterpret_cast<const float2*>(q);
+                    if (p.splits == 4) {  // the common plan: all four loads in flight, summed in rank order
+                        const float2 v1 = *reinterpret_cast<const float2*>(q + slot);
+                        const float2 v2 = *reinterpret_cast<const float2*>(q + 2 * slot);
+                        const float2 v3 = *reinterpret_cast<const float2*>(q + 3 * slot);
+                        acc[u].x = ((acc[u].x + v1.x) + v2.x) + v3.x;
+                        acc[u].y = ((acc[u].y + v1.y) + v2.y) + v3.y;
+                    } else {
+                        for (int r = 1; r < p.splits; ++r) {
+                            const float2 v = *reinterpret_cast<const float2*>(q + r * slot);
+                            acc[u].x += v.x; acc[u].y += v.y;
+                        }
                     }
                 }
             }
