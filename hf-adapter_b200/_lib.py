@@ -24,6 +24,7 @@ SIGNATURES = {
     "rwkv7_abi_version": (I, []),
     "rwkv7_last_error": (ctypes.c_char_p, []),
     "rwkv7_kernel_status": (I, [I]),
+    "rwkv7_set_option": (I, [I, I]),
     "rwkv7_wkv7_update": (I, [P] * 9 + [I, I, I, I, I, P]),
     "rwkv7_wkv7_output_prepare": (I, [P] * 13 + [I, I, I, F, I, I, P]),
     "rwkv7_wkv7_output_prepare_raw": (I, [P] * 14 + [P, P, I, P, P, P, I, P, I, I, I, F, I, P]),
@@ -94,3 +95,20 @@ def ptr_array(ptrs):
 def kernel_status(reset: bool = True) -> int:
     """0 unless a tensor-core kernel's bounded wait gave up since the last reset (synchronises the device)."""
     return int(lib.rwkv7_kernel_status(1 if reset else 0))
+
+
+OPT_STATE_PREFETCH = 1
+
+
+class state_prefetch:
+    """Context manager: inside it the one-token recurrence kernels load their state tile before waiting for the
+    preceding kernel of the stream (``RWKV7_OPT_STATE_PREFETCH``).  Only for call sequences in which that preceding
+    kernel never writes the state, e.g. a decode step (a projection precedes the recurrence)."""
+
+    def __enter__(self):
+        self._prev = int(lib.rwkv7_set_option(OPT_STATE_PREFETCH, 1))
+        return self
+
+    def __exit__(self, *exc):
+        lib.rwkv7_set_option(OPT_STATE_PREFETCH, self._prev)
+        return False

@@ -46,6 +46,25 @@ inline bool programmatic_launch_enabled() {
     return on;
 }
 
+int option_state_prefetch();  // RWKV7_OPT_STATE_PREFETCH (capi.cu)
+
+// Launch with the programmatic-stream-serialization attribute: the kernel may become resident while its predecessor
+// in the stream still runs and must call grid_dependency_wait() before touching anything that kernel writes.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_programmatic(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = programmatic_launch_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // ---- scalar conversion ----------------------------------------------------
 template <typename T> __device__ __forceinline__ float to_f(T v);
 template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }

@@ -65,7 +65,10 @@ struct Mix6Args {
 template <typename T>
 __global__ void __launch_bounds__(kNMThreads) attn_norm_mix6_kernel(const Mix6Args p) {
     __shared__ float red[32];
-    if (threadIdx.x == 0) grid_launch_dependents();  // the projections that follow prefetch their weights meanwhile
+    // Resident under the tail of the preceding kernel; the wait orders every access below after it, and only then may
+    // the projections that follow start (they stream their weights meanwhile).
+    grid_dependency_wait();
+    if (threadIdx.x == 0) grid_launch_dependents();
     const size_t row = blockIdx.x;
     const int D = p.D;
     RowStats<T> rs;
@@ -110,6 +113,7 @@ struct FfnMixArgs {
 template <typename T, bool ADD, bool MIX>
 __global__ void __launch_bounds__(kNMThreads) ffn_add_norm_mix_kernel(const FfnMixArgs p) {
     __shared__ float red[32];
+    grid_dependency_wait();
     if (threadIdx.x == 0) grid_launch_dependents();
     const size_t row = blockIdx.x;
     const int D = p.D;
@@ -207,7 +211,7 @@ extern "C" int rwkv7_attn_norm_mix6(const void* x, void* prev, const void* norm_
                   "attn_norm_mix6: unaligned pointer");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     RWKV7_DISPATCH_DTYPE(dtype, T, {
-        attn_norm_mix6_kernel<T><<<rows, kNMThreads, 0, st>>>(p);
+        launch_programmatic(attn_norm_mix6_kernel<T>, dim3(rows), dim3(kNMThreads), 0, st, p);
         return check_launch("attn_norm_mix6_kernel");
     });
     return RWKV7_OK;
@@ -225,8 +229,8 @@ extern "C" int rwkv7_ffn_add_norm_mix(const void* residual, const void* attn_out
     FfnMixArgs p{residual, attn_out, norm_w, norm_b, mix, prev, residual_out, mixed, D, eps};
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     RWKV7_DISPATCH_DTYPE(dtype, T, {
-        if (attn_out) ffn_add_norm_mix_kernel<T, true, true><<<rows, kNMThreads, 0, st>>>(p);
-        else ffn_add_norm_mix_kernel<T, false, true><<<rows, kNMThreads, 0, st>>>(p);
+        if (attn_out) launch_programmatic(ffn_add_norm_mix_kernel<T, true, true>, dim3(rows), dim3(kNMThreads), 0, st, p);
+        else launch_programmatic(ffn_add_norm_mix_kernel<T, false, true>, dim3(rows), dim3(kNMThreads), 0, st, p);
         return check_launch("ffn_add_norm_mix_kernel");
     });
     return RWKV7_OK;
@@ -241,7 +245,7 @@ extern "C" int rwkv7_layer_norm(const void* x, const void* norm_w, const void* n
     FfnMixArgs p{x, nullptr, norm_w, norm_b, nullptr, nullptr, nullptr, out, D, eps};
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     RWKV7_DISPATCH_DTYPE(dtype, T, {
-        ffn_add_norm_mix_kernel<T, false, false><<<rows, kNMThreads, 0, st>>>(p);
+        launch_programmatic(ffn_add_norm_mix_kernel<T, false, false>, dim3(rows), dim3(kNMThreads), 0, st, p);
         return check_launch("layer_norm_kernel");
     });
     return RWKV7_OK;

@@ -137,7 +137,6 @@ w4g_umma_kernel(const __grid_constant__ W4Maps maps, const W4UmmaArgs p) {
     const int nkb = p.nkb;
 
     if (tid == 0) {
-        grid_launch_dependents();
         tma_prefetch_desc(tm_x);
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&full[s], 1);
@@ -190,6 +189,10 @@ w4g_umma_kernel(const __grid_constant__ W4Maps maps, const W4UmmaArgs p) {
             // programmatic launch the weight stream, the dequantisation and the tensor-memory A buffers above run
             // ahead of this point, in the shadow of that kernel.
             grid_dependency_wait();
+            // Only now may the next kernel of the stream start: every kernel of this library releases its successor
+            // after its own wait, so a programmatically launched kernel knows that everything before its immediate
+            // predecessor has completed.
+            grid_launch_dependents();
             for (int i = 0; i < nkb; ++i) {
                 const int s = i % STAGES;
                 if (i >= STAGES && !mbar_wait(&empty[s], ((i / STAGES) - 1) & 1, actx, kErrWaitEmpty)) break;

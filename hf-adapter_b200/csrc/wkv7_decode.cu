@@ -31,6 +31,7 @@ struct StepArgs {
     int a_is_raw, v_gate_is_raw;
     int H;
     float eps;
+    int prefetch_state;  // load the state tile before the grid-dependency wait (RWKV7_OPT_STATE_PREFETCH)
 };
 
 template <typename T, typename TW, int MODE>
@@ -38,7 +39,6 @@ __global__ void __launch_bounds__(kStepThreads) wkv7_step_kernel(const StepArgs 
     const int bh = blockIdx.x;
     const int h = bh % p.H;
     const int tid = threadIdx.x;
-    if (tid == 0) grid_launch_dependents();  // the output projection sets up and prefetches weights under this grid's tail
     const int l16 = tid & 15;
     const int rg = tid >> 4;
     const size_t vbase = (size_t)bh * kN;
@@ -48,12 +48,21 @@ __global__ void __launch_bounds__(kStepThreads) wkv7_step_kernel(const StepArgs 
     __shared__ float s_v[kN];
     __shared__ float s_y[kN];
 
+    // Launched programmatically: resident under the tail of the preceding kernel.  By default everything waits for it.
+    if (!p.prefetch_state) grid_dependency_wait();
     // ---- state tile: issue all 8 row loads first (memory-level parallelism)
     const float* sin = p.state_in + (size_t)bh * kN * kN;
     float4 S[8];
 #pragma unroll
     for (int it = 0; it < 8; ++it)
         S[it] = *reinterpret_cast<const float4*>(sin + (size_t)(it * 8 + rg) * kN + c0);  // plain load: may alias state_out
+
+    // With the state-prefetch option the loads above are already in flight while the preceding kernel (the r/k/v
+    // projection of a decode step) finishes: the caller promises that kernel does not write the state, and every
+    // kernel of this library releases its successor only after its own wait, so whatever wrote the state earlier has
+    // completed.  Everything below reads the preceding kernel's output.
+    if (p.prefetch_state) grid_dependency_wait();
+    if (tid == 0) grid_launch_dependents();  // the output projection sets up and streams weights under this grid's tail
 
     // ---- column-indexed vectors (4 columns per thread)
     float r[4], w[4], k[4], kk[4], a[4];
@@ -170,8 +179,9 @@ __global__ void __launch_bounds__(kStepThreads) wkv7_step_kernel(const StepArgs 
 }
 
 template <typename T, typename TW, int MODE>
-static int launch_step(const StepArgs& p, int B, cudaStream_t st) {
-    wkv7_step_kernel<T, TW, MODE><<<B * p.H, kStepThreads, 0, st>>>(p);
+static int launch_step(StepArgs p, int B, cudaStream_t st) {
+    p.prefetch_state = option_state_prefetch();
+    launch_programmatic(wkv7_step_kernel<T, TW, MODE>, dim3(B * p.H), dim3(kStepThreads), 0, st, p);
     return check_launch("wkv7_step_kernel");
 }
 

@@ -23,6 +23,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from . import _lib
 from . import lora as _lora
 from . import norm_mix as _nm
 from . import prep as _prep
@@ -244,9 +245,11 @@ class RWKV7ForCausalLM(nn.Module):
                 xk.record_stream(sk); k.record_stream(sk); xv.record_stream(sv); v.record_stream(sv)
             for t_ in (xw, xa, xg, xv, w_raw, a_pre, g):
                 t_.record_stream(side)
-            out, _ = _rec.fused_recurrent_output_prepare_raw(
-                r, w_raw, k, v, a_pre, state[i], g, at.k_k, at.k_a, at.r_k, at.g_norm.weight, at.g_norm.bias,
-                eps=N * 1e-5, new_state=state[i], w_bias=wl[2].bias, a_bias=al[2].bias, a_is_raw=True, **extra)
+            # the kernel launched just before the recurrence is a projection: it never writes the state
+            with _lib.state_prefetch():
+                out, _ = _rec.fused_recurrent_output_prepare_raw(
+                    r, w_raw, k, v, a_pre, state[i], g, at.k_k, at.k_a, at.r_k, at.g_norm.weight, at.g_norm.bias,
+                    eps=N * 1e-5, new_state=state[i], w_bias=wl[2].bias, a_bias=al[2].bias, a_is_raw=True, **extra)
             attn = self._all_reduce(_linear(at.o_proj, out))
             x, mixed = _nm.fused_ffn_add_norm_mix_decode(x, attn, xpf[i], layer.ffn_norm.weight, layer.ffn_norm.bias, ff.x_k)
             hidden = _linear(ff.key, mixed, relu2=True)

@@ -52,6 +52,15 @@ const char* rwkv7_last_error(void);
  * ever gave up; > 0 = code; < 0 = RWKV7_ERR_*) and clears it when reset != 0.  No counterpart in the reference. */
 int rwkv7_kernel_status(int reset);
 
+/* Process-wide launch options.  Returns the previous value (or RWKV7_ERR_INVALID for an unknown option).
+ *   RWKV7_OPT_STATE_PREFETCH (default 0): the one-token recurrence kernels load the state tile BEFORE waiting for
+ *   the kernel that precedes them in the stream (they are launched programmatically, under its tail).  Set it only
+ *   while that preceding kernel never writes the state passed in -- true inside a decode step, where a projection
+ *   precedes the recurrence; false for back-to-back recurrence calls that feed each other's state.
+ * No counterpart in the reference. */
+#define RWKV7_OPT_STATE_PREFETCH 1
+int rwkv7_set_option(int option, int value);
+
 /* ------------------------------------------------------------------ WKV-7 recurrence, one token
  * Replaces fused_recurrent_update (rwkv7_hf/fused_recurrent_update.py:1214),
  * fused_recurrent_output_prepare (:967) and fused_recurrent_output_prepare_raw (:1089).
