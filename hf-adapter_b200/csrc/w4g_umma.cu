@@ -42,7 +42,11 @@ constexpr int TILE_N = 128;  // output channels per CTA = UMMA M
 constexpr int KB = 128;      // k elements per pipeline stage
 constexpr int NB = 64;       // activation rows per MMA = UMMA N
 constexpr int STAGES = 6;    // activation-tile ring (L2-resident source, freed by the MMA commit)
-constexpr int WSTAGES = 10;  // weight-block ring (HBM source, freed as soon as the dequant warps have read it)
+constexpr int WB = 2;        // tile blocks per bulk copy (17 KiB requests: a bare copy ring of this shape moved 33.5 MB in
+                             // 6.9 us against 9.5-10.6 us with 8.5 KiB ones; in this kernel, whose ring is kept full
+                             // by the slower consumer side, the step time did not change)
+constexpr int WSTAGES = 5;   // weight ring, in copies (HBM source, freed as soon as the dequant warps have read both blocks)
+constexpr int WRING_BYTES = WSTAGES * WB * 8704;
 constexpr int RAW_BYTES = TILE_N * KB / 2;  // 8192 packed nibbles
 constexpr int SC_OFF = RAW_BYTES;           // then 128 fp16 scales of the k-block
 constexpr int Z_OFF = SC_OFF + TILE_N * 2;  // then 128 u8 zero-points, then padding
@@ -111,8 +115,8 @@ w4g_umma_kernel(const __grid_constant__ W4Maps maps, const W4UmmaArgs p) {
     // a ring, and a weight block can be released ~10x earlier than the activation tile the MMAs still read.
     unsigned char* xs = smem;
     unsigned char* raws = smem + STAGES * X_BYTES;
-    float* Q = reinterpret_cast<float*>(raws + WSTAGES * BLOCK_BYTES);  // never aliased: peers write it while this CTA still streams
-    uint64_t* bars = reinterpret_cast<uint64_t*>(raws + WSTAGES * BLOCK_BYTES + Q_BYTES);
+    float* Q = reinterpret_cast<float*>(raws + WRING_BYTES);  // never aliased: peers write it while this CTA still streams
+    uint64_t* bars = reinterpret_cast<uint64_t*>(raws + WRING_BYTES + Q_BYTES);
     uint64_t* full = bars;                   // [STAGES]  activation tile landed
     uint64_t* empty = bars + STAGES;         // [STAGES]  MMAs that read it completed
     uint64_t* wfull = bars + 2 * STAGES;     // [WSTAGES] weight block landed
@@ -144,7 +148,7 @@ w4g_umma_kernel(const __grid_constant__ W4Maps maps, const W4UmmaArgs p) {
         }
         for (int s = 0; s < WSTAGES; ++s) {
             mbar_init(&wfull[s], 1);
-            mbar_init(&wempty[s], 4);
+            mbar_init(&wempty[s], 4 * WB);  // the four warps of each block's dequant group
         }
         for (int a = 0; a < NA; ++a) {
             mbar_init(&a_ready[a], 4);  // the four warps of the group that filled the buffer
@@ -174,13 +178,15 @@ w4g_umma_kernel(const __grid_constant__ W4Maps maps, const W4UmmaArgs p) {
     }
 
     if (warp == 0) {
-        if (lane == 0) {  // weight stream: one bulk copy per block (nibbles + scales + zero-points)
-            for (int i = 0; i < nkb; ++i) {
-                const int s = i % WSTAGES;
-                if (i >= WSTAGES && !mbar_wait(&wempty[s], ((i / WSTAGES) - 1) & 1, actx, kErrWaitEmpty)) break;
-                mbar_expect_tx(&wfull[s], BLOCK_BYTES);
-                const size_t blk = (size_t)blockIdx.x * p.kbt + kb0 + i;  // tile-major block index
-                bulk_load(raws + s * BLOCK_BYTES, tw + blk * BLOCK_BYTES, BLOCK_BYTES, &wfull[s]);
+        if (lane == 0) {  // weight stream: one bulk copy per WB consecutive blocks (nibbles + scales + zero-points each)
+            const int ncopy = (nkb + WB - 1) / WB;
+            for (int c = 0; c < ncopy; ++c) {
+                const int s = c % WSTAGES;
+                if (c >= WSTAGES && !mbar_wait(&wempty[s], ((c / WSTAGES) - 1) & 1, actx, kErrWaitEmpty)) break;
+                const uint32_t bytes = (uint32_t)min(WB, nkb - c * WB) * BLOCK_BYTES;
+                mbar_expect_tx(&wfull[s], bytes);
+                const size_t blk = (size_t)blockIdx.x * p.kbt + kb0 + c * WB;  // tile-major block index
+                bulk_load(raws + s * (WB * BLOCK_BYTES), tw + blk * BLOCK_BYTES, bytes, &wfull[s]);
             }
         }
     } else if (warp == XPROD_WARP) {
@@ -234,19 +240,20 @@ w4g_umma_kernel(const __grid_constant__ W4Maps maps, const W4UmmaArgs p) {
         const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
         bool ok = true;
         for (int i = grp; i < nkb && ok; i += SB) {
-            const int ab = i % NAB, ws = i % WSTAGES;
+            const int ab = i % NAB, wc = i / WB, ws = wc % WSTAGES;
+            const unsigned char* wblk = raws + (ws * WB + (i - wc * WB)) * BLOCK_BYTES;
             // one lane per warp polls; the others wait at the shuffle
-            if (lane == 0) ok = mbar_wait(&wfull[ws], (i / WSTAGES) & 1, actx, kErrWaitFull);
+            if (lane == 0) ok = mbar_wait(&wfull[ws], (wc / WSTAGES) & 1, actx, kErrWaitFull);
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
             // this channel's 64 packed bytes: chunk c (32 k) of all 128 channels is one 2 KiB slab, so the
             // threads of a warp read consecutive 16-byte pieces (no bank conflicts, no swizzle)
-            const unsigned char* rrow = raws + ws * BLOCK_BYTES + row * 16;
+            const unsigned char* rrow = wblk + row * 16;
             uint4 pk[4];
 #pragma unroll
             for (int c = 0; c < 4; ++c) pk[c] = *reinterpret_cast<const uint4*>(rrow + c * 2048);
-            const __half sch = reinterpret_cast<const __half*>(raws + ws * BLOCK_BYTES + SC_OFF)[row];
-            const float z = (float)(raws + ws * BLOCK_BYTES + Z_OFF)[row];
+            const __half sch = reinterpret_cast<const __half*>(wblk + SC_OFF)[row];
+            const float z = (float)(wblk + Z_OFF)[row];
             __syncwarp();
             if (lane == 0) mbar_arrive(&wempty[ws]);
             if (i >= NAB) {
@@ -470,7 +477,7 @@ int launch_w4g_umma_tiled(const void* const* xs, const uint8_t* const* tws, cons
     a.row_blocks = row_blocks;
     a.error = kernel_error_word();
     RWKV7_REQUIRE(a.error != nullptr, RWKV7_ERR_CUDA, "w4g_gemv_tiled: cannot resolve the device error word");
-    const size_t smem = (size_t)STAGES * X_BYTES + (size_t)WSTAGES * BLOCK_BYTES + Q_BYTES + (2 * STAGES + 2 * WSTAGES + 2 * NA + 1) * 8 + 16 + 1024;
+    const size_t smem = (size_t)STAGES * X_BYTES + (size_t)WRING_BYTES + Q_BYTES + (2 * STAGES + 2 * WSTAGES + 2 * NA + 1) * 8 + 16 + 1024;
     cudaError_t e = cudaFuncSetAttribute(w4g_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     RWKV7_REQUIRE(e == cudaSuccess, RWKV7_ERR_CUDA, "w4g_gemv_tiled: %s", cudaGetErrorString(e));
     cudaLaunchConfig_t cfg{};
