@@ -9,6 +9,21 @@ namespace rwkv7 {
 constexpr int kNMThreads = 256;
 constexpr int kNMMaxVec = 4;  // 8-element vectors per thread -> D <= 8192
 
+// Eight elements in storage type, fetched with one 16- or 32-byte load and converted where they are used: the
+// per-channel constants of a row kernel (norm weight / bias, mix vectors) are fetched BEFORE the grid-dependency wait
+// and before the row statistics, so their latency hides under the preceding kernel's tail and the reductions.
+template <typename T>
+struct alignas(sizeof(T) * 8) Raw8 {
+    T v[8];
+};
+template <typename T>
+__device__ __forceinline__ Raw8<T> ld_raw8(const T* p) { return *reinterpret_cast<const Raw8<T>*>(p); }
+template <typename T>
+__device__ __forceinline__ void cvt8(const Raw8<T>& r, float (&o)[8]) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[e] = to_f<T>(r.v[e]);
+}
+
 template <typename T>
 struct RowStats {
     float x[kNMMaxVec][8];
@@ -65,23 +80,34 @@ struct Mix6Args {
 template <typename T>
 __global__ void __launch_bounds__(kNMThreads) attn_norm_mix6_kernel(const Mix6Args p) {
     __shared__ float red[32];
+    const size_t row = blockIdx.x;
+    const int D = p.D;
+    const int nvec = D / 8;
+    Raw8<T> cw[kNMMaxVec], cb[kNMMaxVec], cm[6][kNMMaxVec];
+#pragma unroll
+    for (int i = 0; i < kNMMaxVec; ++i) {
+        const int vi = threadIdx.x + i * kNMThreads;
+        if (vi < nvec) {
+            cw[i] = ld_raw8(reinterpret_cast<const T*>(p.nw) + vi * 8);
+            cb[i] = ld_raw8(reinterpret_cast<const T*>(p.nb) + vi * 8);
+#pragma unroll
+            for (int m = 0; m < 6; ++m) cm[m][i] = ld_raw8(reinterpret_cast<const T*>(p.mix[m]) + vi * 8);
+        }
+    }
     // Resident under the tail of the preceding kernel; the wait orders every access below after it, and only then may
     // the projections that follow start (they stream their weights meanwhile).
     grid_dependency_wait();
     if (threadIdx.x == 0) grid_launch_dependents();
-    const size_t row = blockIdx.x;
-    const int D = p.D;
     RowStats<T> rs;
     load_row_stats<T, false>(reinterpret_cast<const T*>(p.x) + row * D, nullptr, nullptr, D, p.eps, rs, red);
     T* prev = reinterpret_cast<T*>(p.prev) + row * D;
-    const int nvec = D / 8;
 #pragma unroll
     for (int i = 0; i < kNMMaxVec; ++i) {
         const int vi = threadIdx.x + i * kNMThreads;
         if (vi < nvec) {
             float w[8], b[8], pv[8], h[8], d[8];
-            load8(reinterpret_cast<const T*>(p.nw) + vi * 8, w);
-            load8(reinterpret_cast<const T*>(p.nb) + vi * 8, b);
+            cvt8(cw[i], w);
+            cvt8(cb[i], b);
             load8(prev + vi * 8, pv);
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
@@ -92,7 +118,7 @@ __global__ void __launch_bounds__(kNMThreads) attn_norm_mix6_kernel(const Mix6Ar
 #pragma unroll
             for (int m = 0; m < 6; ++m) {
                 float mx[8], o[8];
-                load8(reinterpret_cast<const T*>(p.mix[m]) + vi * 8, mx);
+                cvt8(cm[m][i], mx);
 #pragma unroll
                 for (int e = 0; e < 8; ++e) o[e] = h[e] + d[e] * mx[e];
                 store8(reinterpret_cast<T*>(p.out[m]) + row * D + vi * 8, o);
@@ -113,29 +139,39 @@ struct FfnMixArgs {
 template <typename T, bool ADD, bool MIX>
 __global__ void __launch_bounds__(kNMThreads) ffn_add_norm_mix_kernel(const FfnMixArgs p) {
     __shared__ float red[32];
-    grid_dependency_wait();
-    if (threadIdx.x == 0) grid_launch_dependents();
     const size_t row = blockIdx.x;
     const int D = p.D;
+    const int nvec = D / 8;
+    Raw8<T> cw[kNMMaxVec], cb[kNMMaxVec], cm[kNMMaxVec];
+#pragma unroll
+    for (int i = 0; i < kNMMaxVec; ++i) {
+        const int vi = threadIdx.x + i * kNMThreads;
+        if (vi < nvec) {
+            cw[i] = ld_raw8(reinterpret_cast<const T*>(p.nw) + vi * 8);
+            cb[i] = ld_raw8(reinterpret_cast<const T*>(p.nb) + vi * 8);
+            if constexpr (MIX) cm[i] = ld_raw8(reinterpret_cast<const T*>(p.mix) + vi * 8);
+        }
+    }
+    grid_dependency_wait();
+    if (threadIdx.x == 0) grid_launch_dependents();
     RowStats<T> rs;
     load_row_stats<T, ADD>(reinterpret_cast<const T*>(p.res) + row * D,
                            ADD ? reinterpret_cast<const T*>(p.attn) + row * D : nullptr,
                            ADD ? reinterpret_cast<T*>(p.res_out) + row * D : nullptr, D, p.eps, rs, red);
-    const int nvec = D / 8;
 #pragma unroll
     for (int i = 0; i < kNMMaxVec; ++i) {
         const int vi = threadIdx.x + i * kNMThreads;
         if (vi < nvec) {
             float w[8], b[8], h[8];
-            load8(reinterpret_cast<const T*>(p.nw) + vi * 8, w);
-            load8(reinterpret_cast<const T*>(p.nb) + vi * 8, b);
+            cvt8(cw[i], w);
+            cvt8(cb[i], b);
 #pragma unroll
             for (int e = 0; e < 8; ++e) h[e] = (rs.x[i][e] - rs.mean) * rs.rstd * w[e] + b[e];
             if constexpr (MIX) {
                 float pv[8], mx[8], o[8];
                 T* prev = reinterpret_cast<T*>(p.prev) + row * D;
                 load8(prev + vi * 8, pv);
-                load8(reinterpret_cast<const T*>(p.mix) + vi * 8, mx);
+                cvt8(cm[i], mx);
 #pragma unroll
                 for (int e = 0; e < 8; ++e) o[e] = h[e] + (pv[e] - h[e]) * mx[e];
                 store8(prev + vi * 8, h);
