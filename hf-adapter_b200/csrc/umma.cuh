@@ -29,7 +29,6 @@ struct AbortCtx {
     unsigned int* error;  // device-global error word
 };
 
-constexpr unsigned kSpinLimit = 1u << 22;  // try_wait iterations before giving up (each has its own HW time-out)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -44,37 +43,43 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+// try_wait with a suspend-time hint: the hardware parks the thread until the phase completes (or the hint runs out), so
+// a waiting warp issues no instructions.  Spinning on plain try_wait instead more than doubled the instruction count
+// of the int4 kernel and competed with its dequantising warps for the integer pipe.
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity, uint32_t suspend_ns) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(suspend_ns) : "memory");
     return ok != 0;
 }
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+constexpr uint32_t kSuspendNs = 20000;            // per try_wait
+constexpr uint64_t kWaitLimitNs = 2000000000ull;  // a wait gives up after two seconds
+
 // Bounded wait.  Returns false (and raises the CTA abort flag) if the phase never completes.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const AbortCtx& ctx, unsigned code) {
-    for (unsigned it = 0; it < kSpinLimit; ++it) {
-        if (mbar_try_wait(bar, parity)) return true;
-        // back off: a hot polling loop steals issue slots from the compute warps on the same scheduler
-        __nanosleep(32);
-        if ((it & 63u) == 63u && *ctx.flag) return false;
+    if (mbar_try_wait(bar, parity, kSuspendNs)) return true;
+    const uint64_t t0 = global_timer_ns();
+    for (;;) {
+        if (mbar_try_wait(bar, parity, kSuspendNs)) return true;
+        if (*ctx.flag) return false;
+        if (global_timer_ns() - t0 > kWaitLimitNs) break;
     }
     *ctx.flag = 1;
     atomicCAS(ctx.error, 0u, code);
     return false;
 }
 
-// Same without the back-off, for the one thread per CTA whose wake-up latency is on the critical path.
+// Kept as a separate name for the threads whose wake-up latency is on the critical path (MMA issuers).
 __device__ __forceinline__ bool mbar_wait_hot(uint64_t* bar, uint32_t parity, const AbortCtx& ctx, unsigned code) {
-    for (unsigned it = 0; it < kSpinLimit * 4; ++it) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 255u) == 255u && *ctx.flag) return false;
-    }
-    *ctx.flag = 1;
-    atomicCAS(ctx.error, 0u, code);
-    return false;
+    return mbar_wait(bar, parity, ctx, code);
 }
 
 // ---------------------------------------------------------------- cluster barrier, split into arrive / wait

@@ -239,13 +239,16 @@ w4g_umma_kernel(const __grid_constant__ W4Maps maps, const W4UmmaArgs p) {
         const int row = q * 32 + lane;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
         bool ok = true;
-        for (int i = grp; i < nkb && ok; i += SB) {
+        // a group takes whole copies (WB consecutive blocks): one poll of the copy's barrier serves all of them
+        for (int i = grp * WB; i < nkb && ok; i += ((i % WB) == WB - 1) ? (SB - 1) * WB + 1 : 1) {
             const int ab = i % NAB, wc = i / WB, ws = wc % WSTAGES;
             const unsigned char* wblk = raws + (ws * WB + (i - wc * WB)) * BLOCK_BYTES;
-            // one lane per warp polls; the others wait at the shuffle
-            if (lane == 0) ok = mbar_wait(&wfull[ws], (wc / WSTAGES) & 1, actx, kErrWaitFull);
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) break;
+            if (i == wc * WB) {
+                // one lane per warp polls; the others wait at the shuffle
+                if (lane == 0) ok = mbar_wait(&wfull[ws], (wc / WSTAGES) & 1, actx, kErrWaitFull);
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+            }
             // this channel's 64 packed bytes: chunk c (32 k) of all 128 channels is one 2 KiB slab, so the
             // threads of a warp read consecutive 16-byte pieces (no bank conflicts, no swizzle)
             const unsigned char* rrow = wblk + row * 16;
