@@ -235,7 +235,9 @@ def main():
     ids_host = torch.randint(0, V, (steps + warmup + 8, B), generator=gen).pin_memory()
     cache = model.new_cache(B)
 
-    # kernels of this library launched per decode step (counted on one eager step through the C ABI)
+    # kernels of this library launched per decode step (counted on one eager step through the C ABI; the step before
+    # it builds the tiled weight copies, whose one-time repack kernels are not part of a step)
+    model.rwkv7_forward_token(ids_host[0].to(dev), cache, use_graph=False)
     _lib.LAUNCHES = 0
     model.rwkv7_forward_token(ids_host[0].to(dev), cache, use_graph=False)
     launches_per_step = _lib.LAUNCHES

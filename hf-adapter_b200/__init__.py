@@ -7,13 +7,16 @@ from .lora import dense_small, fused_wa_lora, fused_wag_lora, fused_wavg_lora
 from .model import DecodeGraph, NativeRWKV7Config, RWKV7ForCausalLM
 from .norm_mix import (fused_attn_norm_mix6_decode, fused_attn_sequence_shift_mix, fused_attn_shift_mix,
                        fused_ffn_add_norm_mix_decode, fused_ffn_sequence_shift_mix, layer_norm)
-from .prep import fused_attn_output_prepare, fused_prefill_state_prep
-from .quant import (A8W8Linear, MM4Linear, MM8Linear, a8w8_linear, dynamic_a8_quant, int8_mm, quantize_model,
-                    quantize_w4_groupwise, quantize_w8_row, quantize_weight_per_channel_int8, w4_dequant,
-                    w4_groupwise_linear, w4_repack_tiled, w4_tiled_linear, w4_tiled_linear_group, w8_dequant, w8_linear)
+from .prep import (fused_attn_output_prepare, fused_attn_output_project, fused_ffn, fused_prefill_kv_kk_prep,
+                   fused_prefill_state_prep, fused_sequence_ffn)
+from .quant import (A8W8Linear, MM4Linear, MM8Linear, a8w8_ffn, a8w8_linear, dequantize_mm4, dequantize_mm8,
+                    dynamic_a8_quant, int8_mm, mm4_matmul, mm4_matmul_triton, mm8_matmul, mm8_matmul_triton,
+                    quantize_mm4, quantize_mm8, quantize_model, quantize_w4_groupwise, quantize_w8_row,
+                    quantize_weight_per_channel_int8, w4_dequant, w4_groupwise_linear, w4_repack_tiled,
+                    w4_tiled_linear, w4_tiled_linear_group, w8_dequant, w8_linear)
 from .recurrent import (dplr_chunk_scan, fused_recurrent_output_prepare, fused_recurrent_output_prepare_raw,
                         fused_recurrent_scan, fused_recurrent_scan_clampw, fused_recurrent_scan_output_prepare,
-                        fused_recurrent_update, self_chunk_rwkv7)
+                        fused_recurrent_scan_state_prep, fused_recurrent_update, self_chunk_rwkv7)
 
 from .sharding import shard_spec, shard_state_dict
 

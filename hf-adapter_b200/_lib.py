@@ -25,6 +25,11 @@ SIGNATURES = {
     "rwkv7_last_error": (ctypes.c_char_p, []),
     "rwkv7_kernel_status": (I, [I]),
     "rwkv7_set_option": (I, [I, I]),
+    "rwkv7_relu2": (I, [P, P, ctypes.c_longlong, I, P]),
+    "rwkv7_affine_gemv_workspace_bytes": (ctypes.c_int64, [I, I, I]),
+    "rwkv7_affine_gemv": (I, [P] * 8 + [ctypes.c_int64, I, I, I, I, I, P]),
+    "rwkv7_affine_dequant": (I, [P] * 6 + [I, I, I, I, P]),
+    "rwkv7_a8w8_relu2_requant": (I, [P] * 6 + [I, I, I, P]),
     "rwkv7_wkv7_update": (I, [P] * 9 + [I, I, I, I, I, P]),
     "rwkv7_wkv7_output_prepare": (I, [P] * 13 + [I, I, I, F, I, I, P]),
     "rwkv7_wkv7_output_prepare_raw": (I, [P] * 14 + [P, P, I, P, P, P, I, P, I, I, I, F, I, P]),

@@ -41,6 +41,37 @@ __global__ void __launch_bounds__(256) a8_quant_kernel(const T* __restrict__ x, 
     }
 }
 
+// ---------------------------------------------------------------- FFN boundary: dequantise, relu^2, requantise
+// one CTA per row: h = fp16(acc * sa[row] * sw[n] (+ bias)); r = fp16(max(h, 0)^2); then the activation quantiser on r
+// (rwkv7_hf/native_quant_a8w8.py:189-232).  The hidden activation never exists in fp16 in memory.
+template <typename T>
+__global__ void __launch_bounds__(256) a8w8_relu2_requant_kernel(const int32_t* __restrict__ acc, const float* __restrict__ sa,
+                                                                 const float* __restrict__ sw, const T* __restrict__ bias,
+                                                                 int8_t* __restrict__ q, float* __restrict__ scale, int N) {
+    __shared__ float red[32];
+    const size_t row = blockIdx.x;
+    const int32_t* ar = acc + row * N;
+    const float a_s = sa[row];
+    auto value = [&](int n) {
+        float pre = (float)ar[n] * a_s * sw[n];
+        if (bias) pre += to_f<T>(bias[n]);
+        pre = __half2float(__float2half_rn(pre));
+        const float act = fmaxf(pre, 0.f);
+        return __half2float(__float2half_rn(act * act));
+    };
+    float amax = 0.f;
+    for (int n = threadIdx.x; n < N; n += 256) amax = fmaxf(amax, fabsf(value(n)));
+    amax = block_max(amax, red);
+    const float s = fmaxf(__fdiv_rn(amax, 127.0f), 1.0e-5f);
+    if (threadIdx.x == 0) scale[row] = s;
+    for (int n = threadIdx.x; n < N; n += 256) {
+        const float t = __fdiv_rn(value(n), s);
+        float r = (t >= 0.f) ? floorf(t + 0.5f) : ceilf(t - 0.5f);
+        r = fminf(fmaxf(r, -127.f), 127.f);
+        q[row * N + n] = (int8_t)(int)r;
+    }
+}
+
 // ---------------------------------------------------------------- dequant epilogue
 template <typename T>
 __global__ void __launch_bounds__(256) a8w8_dequant_kernel(const int32_t* __restrict__ acc, const float* __restrict__ sa,
@@ -223,6 +254,16 @@ extern "C" int rwkv7_a8w8_dequant(const int32_t* acc, const float* sa, const flo
         return check_launch("a8w8_dequant_kernel");
     });
     return RWKV7_OK;
+}
+
+extern "C" int rwkv7_a8w8_relu2_requant(const int32_t* acc, const float* sa, const float* sw, const void* bias, int8_t* q,
+                                        float* scale, int M, int N, int dtype, void* stream) {
+    RWKV7_REQUIRE(M > 0 && N > 0, RWKV7_ERR_INVALID, "a8w8_relu2_requant: sizes must be positive");
+    RWKV7_REQUIRE(acc && sa && sw && q && scale, RWKV7_ERR_INVALID, "a8w8_relu2_requant: null pointer");
+    RWKV7_REQUIRE(dtype == RWKV7_F16, RWKV7_ERR_UNSUPPORTED, "a8w8_relu2_requant: the fused FFN boundary is defined for fp16 activations");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    a8w8_relu2_requant_kernel<__half><<<M, 256, 0, st>>>(acc, sa, sw, reinterpret_cast<const __half*>(bias), q, scale, N);
+    return check_launch("a8w8_relu2_requant_kernel");
 }
 
 extern "C" int64_t rwkv7_a8w8_workspace_bytes(int M, int K, int Nout) {

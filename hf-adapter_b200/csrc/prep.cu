@@ -79,8 +79,8 @@ __global__ void __launch_bounds__(256) state_prep_kernel(const PrepArgs p) {
     const int h = (int)(g % p.H);
     const size_t off = (size_t)g * 64 + l16 * 4;
     const int hoff = h * 64 + l16 * 4;
-    float w[4], k[4], v[4], a[4], ks[4], ka[4];
-    load4(reinterpret_cast<const T*>(p.w_raw) + off, w);
+    float w[4] = {0.f, 0.f, 0.f, 0.f}, k[4], v[4], a[4], ks[4], ka[4];
+    if (p.w_raw) load4(reinterpret_cast<const T*>(p.w_raw) + off, w);  // absent: K / V / KK only (the scan takes raw w)
     load4(reinterpret_cast<const T*>(p.k_raw) + off, k);
     load4(reinterpret_cast<const T*>(p.v_raw) + off, v);
     load4(reinterpret_cast<const T*>(p.a) + off, a);
@@ -114,7 +114,7 @@ __global__ void __launch_bounds__(256) state_prep_kernel(const PrepArgs p) {
         }
     }
     if (active) {
-        *reinterpret_cast<float4*>(p.w_out + off) = make_float4(wo[0], wo[1], wo[2], wo[3]);
+        if (p.w_out) *reinterpret_cast<float4*>(p.w_out + off) = make_float4(wo[0], wo[1], wo[2], wo[3]);
         store4(reinterpret_cast<T*>(p.k_out) + off, ko);
         store4(reinterpret_cast<T*>(p.v_out) + off, v);
         store4(reinterpret_cast<T*>(p.kk_out) + off, kk);
@@ -192,8 +192,10 @@ extern "C" int rwkv7_prefill_state_prep(const void* w_raw, const void* k_raw, co
                                         int a_is_raw, int v_gate_is_raw, int log_decay, int dtype, void* stream) {
     RWKV7_REQUIRE(N == 64, RWKV7_ERR_UNSUPPORTED, "prefill_state_prep: head size must be 64, got %d", N);
     RWKV7_REQUIRE(rows > 0 && H > 0, RWKV7_ERR_INVALID, "prefill_state_prep: sizes must be positive");
-    RWKV7_REQUIRE(w_raw && k_raw && v_raw && a && k_k && k_a && w_out && k_out && v_out && kk_out, RWKV7_ERR_INVALID,
+    RWKV7_REQUIRE(k_raw && v_raw && a && k_k && k_a && k_out && v_out && kk_out, RWKV7_ERR_INVALID,
                   "prefill_state_prep: null pointer");
+    RWKV7_REQUIRE((w_raw == nullptr) == (w_out == nullptr), RWKV7_ERR_INVALID,
+                  "prefill_state_prep: w_raw and w_out must be given together (both NULL = no decay output)");
     RWKV7_REQUIRE((v_first == nullptr) == (v_gate == nullptr), RWKV7_ERR_INVALID,
                   "prefill_state_prep: v_first and v_gate must be given together");
     const void* ptrs[] = {w_raw, k_raw, v_raw, a, k_k, k_a, v_first, v_gate, w_out, k_out, v_out, kk_out};
@@ -206,6 +208,35 @@ extern "C" int rwkv7_prefill_state_prep(const void* w_raw, const void* k_raw, co
     RWKV7_DISPATCH_DTYPE(dtype, T, {
         state_prep_kernel<T><<<grid, 256, 0, st>>>(p);
         return check_launch("state_prep_kernel");
+    });
+    return RWKV7_OK;
+}
+
+// y = max(x, 0)^2 elementwise (in place allowed), 8 elements per thread
+template <typename T>
+__global__ void __launch_bounds__(256) relu2_kernel(const T* __restrict__ x, T* __restrict__ y, long long nvec) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+        float v[8];
+        load8(x + i * 8, v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float r = fmaxf(round_to<T>(v[e]), 0.f);
+            v[e] = r * r;
+        }
+        store8(y + i * 8, v);
+    }
+}
+
+extern "C" int rwkv7_relu2(const void* x, void* y, long long n, int dtype, void* stream) {
+    RWKV7_REQUIRE(n > 0 && n % 8 == 0, RWKV7_ERR_UNSUPPORTED, "relu2: element count must be a positive multiple of 8");
+    RWKV7_REQUIRE(x && y, RWKV7_ERR_INVALID, "relu2: null pointer");
+    RWKV7_REQUIRE(aligned(x, 16) && aligned(y, 16), RWKV7_ERR_ALIGN, "relu2: unaligned pointer");
+    const long long nvec = n / 8;
+    const int grid = (int)((nvec + 255) / 256 < 148LL * 32 ? (nvec + 255) / 256 : 148LL * 32);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    RWKV7_DISPATCH_DTYPE(dtype, T, {
+        relu2_kernel<T><<<grid, 256, 0, st>>>(reinterpret_cast<const T*>(x), reinterpret_cast<T*>(y), nvec);
+        return check_launch("relu2_kernel");
     });
     return RWKV7_OK;
 }

@@ -82,21 +82,31 @@ struct W4Maps {
 // One 32-bit word of the tiled format holds 8 consecutive k in the nibble order [k0 k2 k4 k6 k1 k3 k5 k7]
 // (nibble i at bits 4i), so the two-nibble masks below yield (k0,k1) (k2,k3) (k4,k5) (k6,k7) directly.
 // 0x6400 | q is the fp16 number 1024 + q; the high-nibble form 1024 + 16 q is brought back with an exact fma.
-__device__ __forceinline__ void dequant_word(uint32_t w, __half2 zlo, __half2 zhi, __half2 sc, uint32_t* out) {
-    const __half2 sixteenth = __float2half2_rn(0.0625f);
-    uint32_t t0 = (w & 0x000F000Fu) | 0x64006400u;   // 1024 + (k0, k1)
-    uint32_t t1 = (w & 0x00F000F0u) | 0x64006400u;   // 1024 + 16*(k2, k3)
+// All in 32-bit registers (packed fp16 pairs), one instruction per step: lop3 (w & mask) | magic, then
+// sub / fma and mul on f16x2.
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t mask, uint32_t orv) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(mask), "r"(orv));
+    return d;
+}
+__device__ __forceinline__ uint32_t sub_mul_h2(uint32_t t, uint32_t z, uint32_t sc) {
+    uint32_t d;
+    asm("{\n\t.reg .b32 u;\n\tsub.f16x2 u, %1, %2;\n\tmul.f16x2 %0, u, %3;\n\t}" : "=r"(d) : "r"(t), "r"(z), "r"(sc));
+    return d;
+}
+__device__ __forceinline__ uint32_t fma_mul_h2(uint32_t t, uint32_t m, uint32_t z, uint32_t sc) {
+    uint32_t d;
+    asm("{\n\t.reg .b32 u;\n\tfma.rn.f16x2 u, %1, %2, %3;\n\tmul.f16x2 %0, u, %4;\n\t}" : "=r"(d) : "r"(t), "r"(m), "r"(z), "r"(sc));
+    return d;
+}
+__device__ __forceinline__ void dequant_word(uint32_t w, uint32_t zlo, uint32_t zhi, uint32_t sc, uint32_t* out) {
+    constexpr uint32_t kSixteenth = 0x2C002C00u;  // (1/16, 1/16) in fp16
+    constexpr uint32_t kMagic = 0x64006400u;      // (1024, 1024)
     const uint32_t w2 = w >> 8;
-    uint32_t t2 = (w2 & 0x000F000Fu) | 0x64006400u;  // 1024 + (k4, k5)
-    uint32_t t3 = (w2 & 0x00F000F0u) | 0x64006400u;  // 1024 + 16*(k6, k7)
-    const __half2 v0 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&t0), zlo), sc);
-    const __half2 v1 = __hmul2(__hfma2(*reinterpret_cast<__half2*>(&t1), sixteenth, zhi), sc);
-    const __half2 v2 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&t2), zlo), sc);
-    const __half2 v3 = __hmul2(__hfma2(*reinterpret_cast<__half2*>(&t3), sixteenth, zhi), sc);
-    out[0] = *reinterpret_cast<const uint32_t*>(&v0);
-    out[1] = *reinterpret_cast<const uint32_t*>(&v1);
-    out[2] = *reinterpret_cast<const uint32_t*>(&v2);
-    out[3] = *reinterpret_cast<const uint32_t*>(&v3);
+    out[0] = sub_mul_h2(and_or(w, 0x000F000Fu, kMagic), zlo, sc);               // 1024 + (k0, k1)
+    out[1] = fma_mul_h2(and_or(w, 0x00F000F0u, kMagic), kSixteenth, zhi, sc);   // 1024 + 16*(k2, k3)
+    out[2] = sub_mul_h2(and_or(w2, 0x000F000Fu, kMagic), zlo, sc);              // 1024 + (k4, k5)
+    out[3] = fma_mul_h2(and_or(w2, 0x00F000F0u, kMagic), kSixteenth, zhi, sc);  // 1024 + 16*(k6, k7)
 }
 
 __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
@@ -265,9 +275,9 @@ w4g_umma_kernel(const __grid_constant__ W4Maps maps, const W4UmmaArgs p) {
                 if (!ok) break;
             }
             tc_fence_after();
-            const __half2 sc = __half2half2(sch);
-            const __half2 zlo = __float2half2_rn(1024.0f + z);
-            const __half2 zhi = __float2half2_rn(-(64.0f + z));
+            const __half2 sc2 = __half2half2(sch), zlo2 = __float2half2_rn(1024.0f + z), zhi2 = __float2half2_rn(-(64.0f + z));
+            const uint32_t sc = *reinterpret_cast<const uint32_t*>(&sc2), zlo = *reinterpret_cast<const uint32_t*>(&zlo2),
+                           zhi = *reinterpret_cast<const uint32_t*>(&zhi2);
             const uint32_t a_addr = lane_addr + ab * 64;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {

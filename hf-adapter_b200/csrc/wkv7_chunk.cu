@@ -353,19 +353,26 @@ __global__ void __launch_bounds__(ck::THREADS, 1) wkv7_chunk_kernel(const __grid
                 }
             }
         }
+        // ---------------- phase C2: rhs = D2[0:64] += tril_strict(A_ak) V   (fp16, K = 64)
+        // Warps 0 and 1 wrote tril_strict(A_ak): they hand it to the tensor core at once (named barrier of 64 threads),
+        // so the product runs under the other warps' masks and the block inverses below.
+        if (warp < 2) {
+            fence_proxy_async_smem();
+            tc_fence_before();
+            asm volatile("bar.sync 1, 64;" ::: "memory");
+            if (tid == 0) {
+                tc_fence_after();
+                constexpr uint32_t idh = make_idesc(128, 64, 1, 0, 0);
+                const uint64_t da = make_sw128_kmajor_desc(smem_u32(sm + R_AK));
+                const uint64_t db = make_sw128_kmajor_desc(smem_u32(sm + R_VU));
+#pragma unroll
+                for (int j = 0; j < 4; ++j) umma_f16_ss(tmem + D2_COL, da + (uint64_t)(j * 2), db + (uint64_t)(j * 2), idh, 1);
+                tc_commit(bar);
+            }
+        }
         fence_proxy_async_smem();
         tc_fence_before();
         __syncthreads();
-        // ---------------- phase C2: rhs = D2[0:64] += tril_strict(A_ak) V   (fp16, K = 64)
-        if (tid == 0) {
-            tc_fence_after();
-            constexpr uint32_t idh = make_idesc(128, 64, 1, 0, 0);
-            const uint64_t da = make_sw128_kmajor_desc(smem_u32(sm + R_AK));
-            const uint64_t db = make_sw128_kmajor_desc(smem_u32(sm + R_VU));
-#pragma unroll
-            for (int j = 0; j < 4; ++j) umma_f16_ss(tmem + D2_COL, da + (uint64_t)(j * 2), db + (uint64_t)(j * 2), idh, 1);
-            tc_commit(bar);
-        }
         // While that product runs, four helper warps invert the 16 x 16 diagonal blocks of I - tril_strict(A_ab):
         // lane c of warp 8 + b builds column c of block b by forward substitution in registers.
         if (warp >= 8 && warp < 12 && lane < 16) {

@@ -264,45 +264,216 @@ def a8w8_linear(x, q_weight_t, weight_scale, bias=None, *, out=None, residual=No
     return y.reshape(*x.shape[:-1], Nout)
 
 
+def a8w8_ffn(x, up, down, residual):
+    """Paired A8W8 ``up -> relu^2 -> down + residual`` with the hidden activation kept in int8
+    (rwkv7_hf/native_quant_a8w8.py:436): quantise rows, int8 GEMM, one kernel that dequantises, applies the fp16
+    relu^2 boundary and requantises per row, int8 GEMM, dequantise + residual.  Returns ``None`` when the pairing
+    does not meet the reference's contract (callers then run the two linears)."""
+    if not isinstance(up, A8W8Linear) or not isinstance(down, A8W8Linear):
+        return None
+    if (not x.is_cuda or x.dtype != torch.float16 or up.out_features != down.in_features
+            or up.in_features != down.out_features or up.in_features > 4096 or up.in_features % 16
+            or up.out_features % 16):
+        return None
+    K, F_, D = up.in_features, up.out_features, down.out_features
+    x2 = _rows(x, K)
+    M = int(x2.shape[0])
+    res = residual.reshape(-1, D)
+    if M < 1 or int(res.shape[0]) != M or not res.is_contiguous():
+        return None
+    dev = x2.device
+    qa = torch.empty((M, K), device=dev, dtype=torch.int8)
+    sa = torch.empty((M,), device=dev, dtype=torch.float32)
+    acc1 = torch.empty((M, F_), device=dev, dtype=torch.int32)
+    qh = torch.empty((M, F_), device=dev, dtype=torch.int8)
+    sh = torch.empty((M,), device=dev, dtype=torch.float32)
+    acc2 = torch.empty((M, D), device=dev, dtype=torch.int32)
+    y = torch.empty((M, D), device=dev, dtype=x2.dtype)
+    st, dt = stream_ptr(x2), dt_code(x2)
+    L = _lib.lib
+    _lib.check(L.rwkv7_a8_quant(ptr(x2), ptr(qa), ptr(sa), M, K, dt, st), "a8w8_ffn: quantise")
+    _lib.check(L.rwkv7_i8_gemm(ptr(qa), ptr(_k_major(up.q_weight_t)), ptr(acc1), M, K, F_, st), "a8w8_ffn: up GEMM")
+    _lib.check(L.rwkv7_a8w8_relu2_requant(ptr(acc1), ptr(sa), ptr(up.weight_scale), ptr(up.bias), ptr(qh), ptr(sh), M, F_,
+                                          dt, st), "a8w8_ffn: relu2 + requantise")
+    _lib.check(L.rwkv7_i8_gemm(ptr(qh), ptr(_k_major(down.q_weight_t)), ptr(acc2), M, F_, D, st), "a8w8_ffn: down GEMM")
+    _lib.check(L.rwkv7_a8w8_dequant(ptr(acc2), ptr(sh), ptr(down.weight_scale), ptr(down.bias), ptr(res), ptr(y), M, D,
+                                    dt, st), "a8w8_ffn: dequantise")
+    return y.reshape(*x.shape[:-1], D)
+
+
+# ------------------------------------------------------------------ affine 8-bit / 4-bit formats
+AFFINE_GEMV_MAX_ROWS = 32  # up to four 8-row passes over the weight bytes; beyond that: dequantise + one GEMM
+
+
+def _affine_quant(weight, levels):
+    """Shared body of quantize_mm8 / quantize_mm4 (rwkv7_hf/native_quant_mm8.py:62-97, native_quant_mm4.py:77-108):
+    ``weight`` [N(in), M(out)]; two-sided min subtraction and max scaling, ``floor(w * levels)``."""
+    w = weight.float()
+    n, m = w.shape
+    eps = 1e-8
+    if n > m:
+        my = w.amin(dim=1, keepdim=True); w = w - my
+        mx = w.amin(dim=0); w = w - mx
+    else:
+        mx = w.amin(dim=0); w = w - mx
+        my = w.amin(dim=1, keepdim=True); w = w - my
+    rx = w.amax(dim=0).clamp(min=eps); w = w / rx
+    ry = w.amax(dim=1, keepdim=True).clamp(min=eps); w = w / ry
+    q = torch.clamp(torch.floor(w * float(levels)), 0, levels - 1).to(torch.uint8)
+    return q, mx, rx, my, ry
+
+
+def quantize_mm8(weight):
+    """``weight`` [N, M] -> ``(w_u8 [N,M], mx [M], rx [M], my [N,1], ry [N,1])`` in ``weight.dtype`` (fp16i8)."""
+    q, mx, rx, my, ry = _affine_quant(weight, 256)
+    od = weight.dtype
+    return q, mx.to(od), (rx / 16.0).to(od), my.to(od), (ry / 16.0).to(od)
+
+
+def quantize_mm4(weight):
+    """``weight`` [N, M] -> ``(packed [N, Mp/2] u8, mx [Mp], rx_s [Mp], my [N,1], ry_s [N,1], M, Mp)``; low nibble =
+    even output column, the output width padded to even."""
+    m_orig = int(weight.shape[1])
+    w = weight.float()
+    if m_orig % 2:
+        w = torch.nn.functional.pad(w, (0, 1))
+    q, mx, rx, my, ry = _affine_quant(w, 16)
+    packed = (q[:, 0::2] | (q[:, 1::2] << 4)).to(torch.uint8).contiguous()
+    od = weight.dtype
+    return packed, mx.to(od), (rx / 4.0).to(od), my.to(od), (ry / 4.0).to(od), m_orig, int(w.shape[1])
+
+
+def _affine_dequant(q, mx, rx, my, ry, Nout, bits, dtype):
+    K = int(q.shape[0])
+    require_cuda(q, mx, rx, my, ry, what="affine dequant")
+    cast = lambda t: t.reshape(-1).to(dtype).contiguous()
+    mx_, rx_, my_, ry_ = cast(mx), cast(rx), cast(my), cast(ry)
+    W = torch.empty((K, Nout), device=q.device, dtype=dtype)
+    _lib.check(_lib.lib.rwkv7_affine_dequant(ptr(q.contiguous()), ptr(mx_), ptr(rx_), ptr(my_), ptr(ry_), ptr(W), K, Nout,
+                                             bits, dt_code(W), stream_ptr(q)), "affine dequant")
+    return W
+
+
+def dequantize_mm8(w_u8, mx, rx, my, ry, out_dtype=None):
+    """The dequantised weight [N, M] with the reference's operation order and rounding (native_quant_mm8.py:100)."""
+    return _affine_dequant(w_u8, mx, rx, my, ry, int(w_u8.shape[1]), 8, out_dtype if out_dtype is not None else mx.dtype)
+
+
+def dequantize_mm4(packed, mx, rx_s, my, ry_s, m_orig, out_dtype=None):
+    return _affine_dequant(packed, mx, rx_s, my, ry_s, int(m_orig), 4, out_dtype if out_dtype is not None else mx.dtype)
+
+
+def _affine_matmul(x, q, mx, rx, my, ry, Nout, bits, what):
+    K = int(q.shape[0])
+    x2 = _rows(x, K)
+    M = int(x2.shape[0])
+    require_cuda(x2, q, mx, rx, my, ry, what=what)
+    if M <= AFFINE_GEMV_MAX_ROWS and Nout % 8 == 0 and (bits == 8 or int(q.shape[1]) * 2 == Nout):
+        dt = x2.dtype
+        cast = lambda t: t.reshape(-1).to(dt).contiguous()
+        mx_, rx_, my_, ry_ = cast(mx), cast(rx), cast(my), cast(ry)
+        qc = q.contiguous()
+        y = torch.empty((M, Nout), device=x2.device, dtype=dt)
+        for m0 in range(0, M, 8):
+            rows = min(8, M - m0)
+            nbytes = int(_lib.lib.rwkv7_affine_gemv_workspace_bytes(rows, K, Nout))
+            ws = torch.empty((nbytes // 4,), device=x2.device, dtype=torch.float32)
+            _lib.check(_lib.lib.rwkv7_affine_gemv(ptr(x2[m0:m0 + rows]), ptr(qc), ptr(mx_), ptr(rx_), ptr(my_), ptr(ry_),
+                                                  ptr(y[m0:m0 + rows]), ptr(ws), nbytes, rows, K, Nout, bits, dt_code(x2),
+                                                  stream_ptr(x2)), what, kernels=2)
+        return y.reshape(*x.shape[:-1], Nout)
+    W = _affine_dequant(q, mx, rx, my, ry, Nout, bits, x2.dtype)  # many rows: materialise, then one library GEMM
+    return (x2 @ W).reshape(*x.shape[:-1], Nout)
+
+
+def mm8_matmul(x, w_u8, mx, rx, my, ry):
+    """``y = x @ dequant(W)`` for ``x [..., N]`` (rwkv7_hf/native_quant_mm8.py:110, fused route :468): up to
+    AFFINE_GEMV_MAX_ROWS rows stream the u8 weights through the GEMV kernel, more rows dequantise once and call a GEMM."""
+    return _affine_matmul(x, w_u8, mx, rx, my, ry, int(w_u8.shape[1]), 8, "mm8_matmul")
+
+
+def mm4_matmul(x, packed, mx, rx_s, my, ry_s, m_orig):
+    """4-bit affine counterpart (rwkv7_hf/native_quant_mm4.py:128, fused route :545)."""
+    return _affine_matmul(x, packed, mx, rx_s, my, ry_s, int(m_orig), 4, "mm4_matmul")
+
+
+def mm8_matmul_triton(x, w_u8, mx, rx, my, ry, *, max_gemv_rows=None):
+    """The reference's name for its fused route; here the CUDA kernels above."""
+    return mm8_matmul(x, w_u8, mx, rx, my, ry)
+
+
+def mm4_matmul_triton(x, packed, mx, rx_s, my, ry_s, m_orig, *, max_gemv_rows=None):
+    return mm4_matmul(x, packed, mx, rx_s, my, ry_s, m_orig)
+
+
+mm8_gemv_triton = mm8_matmul
+mm4_gemv_triton = mm4_matmul
+
+
 # ------------------------------------------------------------------ modules
 class MM8Linear(torch.nn.Module):
-    """``nn.Linear`` replacement with int8 per-output-channel weights (buffers ``q_row``, ``row_scale``)."""
+    """``nn.Linear`` replacement with 8-bit weights.  Default: the reference's fp16i8 affine format (buffers ``w_u8``
+    [in,out], ``mx``, ``rx`` [out], ``my``, ``ry`` [in,1]: what rwkv7_hf/native_quant_mm8.py:564-592 stores on devices
+    other than sm7x).  ``rowwise=True``: per-output-channel symmetric int8 (buffers ``q_row``, ``row_scale``: its sm7x
+    format), whose kernel fuses the relu^2 / residual epilogues."""
 
-    def __init__(self, linear, *, fused=True):
+    def __init__(self, linear, *, fused=True, rowwise=False):
         super().__init__()
         self.in_features, self.out_features = int(linear.weight.shape[1]), int(linear.weight.shape[0])
-        q_row, row_scale = quantize_w8_row(linear.weight.data)
-        self.register_buffer("q_row", q_row)
-        self.register_buffer("row_scale", row_scale)
+        self.sm7x_rowwise = bool(rowwise)
+        if self.sm7x_rowwise:
+            q_row, row_scale = quantize_w8_row(linear.weight.data)
+            self.register_buffer("q_row", q_row)
+            self.register_buffer("row_scale", row_scale)
+        else:
+            wu8, mx, rx, my, ry = quantize_mm8(linear.weight.data.t().contiguous())
+            self.register_buffer("w_u8", wu8)
+            self.register_buffer("mx", mx)
+            self.register_buffer("rx", rx)
+            self.register_buffer("my", my)
+            self.register_buffer("ry", ry)
         if linear.bias is not None:
             self.register_buffer("bias", linear.bias.data.clone())
         else:
             self.bias = None
         self.fused = bool(fused)
-        self.sm7x_rowwise = True  # the rowwise format is the one this package implements
+
+    def _lin(self, x, **kw):
+        if self.sm7x_rowwise:
+            return w8_linear(x, self.q_row, self.row_scale, **kw)
+        y = mm8_matmul(x, self.w_u8, self.mx, self.rx, self.my, self.ry)
+        if kw.get("relu2"):
+            from .prep import relu2_
+            y = relu2_(y.contiguous()) if y.numel() % 8 == 0 else torch.relu(y) ** 2
+        if kw.get("residual") is not None:
+            y = y + kw["residual"].reshape(y.shape)
+        if kw.get("out") is not None:
+            kw["out"].copy_(y.reshape(kw["out"].shape))
+            return kw["out"]
+        return y
 
     def forward(self, x):
-        y = w8_linear(x, self.q_row, self.row_scale)
+        y = self._lin(x)
         return y if self.bias is None else y + self.bias
 
     def rwkv7_forward_into(self, x, out):
         if self.bias is None:
-            return w8_linear(x, self.q_row, self.row_scale, out=out)
+            return self._lin(x, out=out)
         out.copy_(self.forward(x))
         return out
 
     def rwkv7_forward_relu2(self, x):
         if self.bias is None:
-            return w8_linear(x, self.q_row, self.row_scale, relu2=True)
+            return self._lin(x, relu2=True)
         return torch.relu(self.forward(x)) ** 2
 
     def rwkv7_forward_add(self, x, residual):
         if self.bias is None:
-            return w8_linear(x, self.q_row, self.row_scale, residual=residual)
+            return self._lin(x, residual=residual)
         return self.forward(x) + residual
 
     def extra_repr(self):
-        return f"in={self.in_features}, out={self.out_features}, mm8(rowwise int8)"
+        return f"in={self.in_features}, out={self.out_features}, mm8(fused={self.fused}, sm7x_rowwise={self.sm7x_rowwise})"
 
 
 class MM4Linear(torch.nn.Module):
@@ -403,8 +574,11 @@ class A8W8Linear(torch.nn.Module):
         """up -> relu^2 (fp16 boundary) -> down + residual; returns None when the pairing does not apply."""
         if not isinstance(down, A8W8Linear) or self.out_features != down.in_features:
             return None
-        hidden = torch.relu(self.forward(x)) ** 2
-        return down.rwkv7_forward_add(hidden, residual)
+        y = a8w8_ffn(x, self, down, residual)
+        if y is not None:
+            return y
+        from .prep import relu2_
+        return down.rwkv7_forward_add(relu2_(self.forward(x).contiguous()), residual)
 
     def extra_repr(self) -> str:
         return f"in={self.in_features}, out={self.out_features}, dynamic_a8w8"
@@ -413,7 +587,7 @@ class A8W8Linear(torch.nn.Module):
 def quantize_model(model, kind: str, *, min_params: int = 8_000_000, group_size: int = 128, skip=("lm_head",)) -> int:
     """Swap eligible ``nn.Linear`` modules in place (role of quantize_model_mm8 / quantize_model_mm4,
     rwkv7_hf/native_quant_mm8.py:631-684, rwkv7_hf/native_quant_mm4.py:761-832).  ``kind`` in
-    {"mm8","mm4","a8w8"}; modules with fewer than ``min_params`` weights or whose name is in ``skip`` stay dense."""
+    {"mm8" (fp16i8 affine), "w8" (row-wise int8), "mm4" (int4 group-wise), "a8w8"}; modules with fewer than ``min_params`` weights or whose name is in ``skip`` stay dense."""
     n = 0
     for parent_name, parent in list(model.named_modules()):
         for name, child in list(parent.named_children()):
@@ -424,6 +598,8 @@ def quantize_model(model, kind: str, *, min_params: int = 8_000_000, group_size:
                 continue  # the rank-R LoRA linears stay dense (they run on the grouped small-GEMM kernel)
             if kind == "mm8":
                 new = MM8Linear(child)
+            elif kind == "w8":
+                new = MM8Linear(child, rowwise=True)
             elif kind == "mm4":
                 if child.in_features % group_size:
                     continue

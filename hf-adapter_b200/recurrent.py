@@ -215,6 +215,34 @@ def fused_recurrent_scan_output_prepare(r, w, k, v, kk, a, state, g, r_k, group_
                  prep=(g, r_k, group_norm_weight, group_norm_bias), eps=eps)
 
 
+def fused_recurrent_scan_state_prep(r, w_raw, k_raw, v_raw, a, state, k_k, k_a, *, v_first=None, v_gate=None,
+                                    block_n: int = 64, block_m=None, num_warps=None, force_fallback: bool = False):
+    """State prep folded into the scan (rwkv7_hf/fused_recurrent_update.py:1541): raw w / k / v and sigmoided a / v-gate
+    in, ``(out, final_state, k_adjusted, v_interpolated)`` out.  Two launches: the K / V / KK prep kernel, then the
+    scan kernel, which computes the decay from raw w itself."""
+    from . import prep as _prep
+    no_fallback(force_fallback, "fused_recurrent_scan_state_prep")
+    B, H, N = _state_shape(state)
+    if int(block_n) < N:
+        raise ValueError(f"block_n must be >= head_dim={N}; got {block_n}")
+    if block_m is not None and not 0 < int(block_m) <= N:
+        raise ValueError(f"block_m must be in [1, head_dim={N}]; got {block_m}")
+    if num_warps is not None and int(num_warps) not in {1, 2, 4, 8}:
+        raise ValueError(f"num_warps must be one of 1, 2, 4, or 8; got {num_warps}")
+    hidden = H * N
+    if int(k_k.numel()) != hidden or int(k_a.numel()) != hidden:
+        raise ValueError(f"k_k and k_a must have {hidden} elements")
+    r4, flat = _as_bthn(r, B, H, N, "r")
+    T = int(r4.shape[1])
+    as3 = lambda t, n: None if t is None else _as_bthn(t, B, H, N, n)[0].reshape(B, T, hidden)
+    k, v, kk = _prep.fused_prefill_kv_kk_prep(as3(k_raw, "k_raw"), as3(v_raw, "v_raw"), as3(a, "a"), k_k, k_a,
+                                              v_first=as3(v_first, "v_first"), v_gate=as3(v_gate, "v_gate"),
+                                              num_heads=H, head_dim=N)
+    out, final = _scan("fused_recurrent_scan_state_prep", r4, as3(w_raw, "w_raw"), k, v, kk, as3(a, "a"), state, 2)
+    shape = (B, T, hidden) if flat else (B, T, H, N)
+    return out.reshape(shape), final, k.reshape(shape), v.reshape(shape)
+
+
 def self_chunk_rwkv7(r, w_decay, k, v, kk, a_gate, state_native, *, chunk_size: int = 16, w_is_log: bool = False,
                      safe_gate=None, h_tiles=None):
     """Chunked WY/DPLR scan on tensor cores (rwkv7_hf/self_chunk_rwkv7.py:33).  ``T`` must be a

@@ -164,7 +164,8 @@ int rwkv7_small_gemm_group(int n_problems, const void* const* x, const void* con
  * Replaces fused_prefill_state_prep (rwkv7_hf/fused_prefill.py:184): per row of [rows,H*64]
  *   w_out = exp(-0.606531*sigmoid(w_raw)) (fp32; the log-decay when log_decay != 0),
  *   kk = l2norm_head(k_raw*k_k), k = k_raw*(1+(a-1)*k_a), v = v_raw + (v_first - v_raw)*v_gate.
- * v_first/v_gate may be NULL (layer 0). */
+ * v_first/v_gate may be NULL (layer 0).  w_raw and w_out may both be NULL: then only k, v, kk are produced, which is
+ * fused_prefill_kv_kk_prep (rwkv7_hf/fused_prefill.py:324), the companion of the raw-w scan. */
 int rwkv7_prefill_state_prep(const void* w_raw, const void* k_raw, const void* v_raw, const void* a,
                              const void* k_k, const void* k_a, const void* v_first, const void* v_gate,
                              float* w_out, void* k_out, void* v_out, void* kk_out,
@@ -175,6 +176,10 @@ int rwkv7_prefill_state_prep(const void* w_raw, const void* k_raw, const void* v
 int rwkv7_attn_output_prepare(const void* recurrent, const void* r, const void* k, const void* v, const void* g,
                               const void* r_k, const void* gn_w, const void* gn_b, void* out,
                               int rows, int H, int N, float eps, int dtype, void* stream);
+
+/* y = max(x, 0)^2 elementwise over n elements (n % 8 == 0; in place allowed): the activation between the FFN key and
+ * value projections when they are dense GEMMs (fused_ffn / fused_sequence_ffn, rwkv7_hf/fused_ffn.py:245-485). */
+int rwkv7_relu2(const void* x, void* y, long long n, int dtype, void* stream);
 
 /* ------------------------------------------------------------------ quantised projections
  * int4 group-wise weights, the reference's quantize_w4_groupwise format (rwkv7_hf/sm70_quant.py:502-519):
@@ -214,6 +219,22 @@ int rwkv7_w4g_dequant(const uint8_t* packed, const void* scales, const uint8_t* 
                       int group, int dtype, void* stream);
 int rwkv7_w8_dequant(const int8_t* q, const void* scale, void* W, int K, int Nout, int dtype, void* stream);
 
+/* Affine 8-bit ("fp16i8") and 4-bit weights in the reference's layouts (quantize_mm8,
+ * rwkv7_hf/native_quant_mm8.py:62-97; quantize_mm4, rwkv7_hf/native_quant_mm4.py:77-108):
+ *   W[k,n] = (q[k,n] + 0.5)*ry[k]*rx[n] + my[k] + mx[n],  q u8 [K,Nout] (bits 8) or two nibbles per byte
+ *   [K,ceil(Nout/2)] (bits 4, low nibble = even n); mx,rx [Nout], my,ry [K] in `dtype`.
+ * rwkv7_affine_gemv replaces mm8_gemv_triton / mm8_matmul_triton / mm4_matmul_triton (native_quant_mm8.py:147-215,
+ * native_quant_mm4.py:150-330) for 1..8 rows (Nout % 8 == 0): one pass over the weight bytes, fp32 accumulation,
+ * fixed summation order; workspace of rwkv7_affine_gemv_workspace_bytes bytes, 16-byte aligned.
+ * rwkv7_affine_dequant replaces dequantize_mm8 / dequantize_mm4 (:100-107 / :111-125): W [K,Nout] in `dtype`, every
+ * operation rounded to `dtype` in the reference's order, for the many-row route (dequantise, then one GEMM). */
+int64_t rwkv7_affine_gemv_workspace_bytes(int M, int K, int Nout);
+int rwkv7_affine_gemv(const void* x, const uint8_t* q, const void* mx, const void* rx, const void* my, const void* ry,
+                      void* out, float* workspace, int64_t workspace_bytes, int M, int K, int Nout, int bits, int dtype,
+                      void* stream);
+int rwkv7_affine_dequant(const uint8_t* q, const void* mx, const void* rx, const void* my, const void* ry, void* W,
+                         int K, int Nout, int bits, int dtype, void* stream);
+
 /* Dynamic per-row int8 activation quantiser; replaces _dynamic_a8_quant_kernel
  * (rwkv7_hf/native_quant_a8w8.py:134-164) with IEEE fp32 division: s = max(amax/127, 1e-5),
  * q = clamp(round_half_away(x/s), +-127).  q [rows,K] i8, scale [rows] fp32. */
@@ -228,6 +249,11 @@ int rwkv7_i8_gemm(const int8_t* qa, const int8_t* qw, int32_t* acc, int M, int K
  * (rwkv7_hf/native_quant_a8w8.py:166-264): out = fp32(acc)*sa[row]*sw[col] (+bias) (+residual). */
 int rwkv7_a8w8_dequant(const int32_t* acc, const float* sa, const float* sw, const void* bias,
                        const void* residual, void* out, int M, int Nout, int dtype, void* stream);
+
+/* The boundary inside a8w8_ffn (rwkv7_hf/native_quant_a8w8.py:189-232, 436-524): per row, h = fp16(acc*sa*sw (+bias)),
+ * r = fp16(max(h,0)^2), then the activation quantiser on r; the fp16 hidden activation is never written.  fp16 only. */
+int rwkv7_a8w8_relu2_requant(const int32_t* acc, const float* sa, const float* sw, const void* bias, int8_t* q,
+                             float* scale, int M, int N, int dtype, void* stream);
 
 /* a8w8_linear (rwkv7_hf/native_quant_a8w8.py:323): quantise rows, integer GEMM, dequantise.
  * workspace: caller-owned scratch of at least rwkv7_a8w8_workspace_bytes(M,K,Nout) bytes, 256-byte aligned. */

@@ -153,6 +153,12 @@ def prefill_state_prep(w_raw, k_raw, v_raw, a, k_k, k_a, H, N, v_first=None, v_g
     return w_out.astype(np.float32), k_out.astype(dt), vf.astype(dt), kk.astype(dt)
 
 
+def prefill_kv_kk_prep(k_raw, v_raw, a, k_k, k_a, H, N, v_first=None, v_gate=None, hi=False):
+    """rwkv7_hf/fused_prefill.py:324-392: state prep without the decay.  Returns (k, v, kk)."""
+    _, k, v, kk = prefill_state_prep(np.zeros_like(k_raw), k_raw, v_raw, a, k_k, k_a, H, N, v_first, v_gate, hi=hi)
+    return k, v, kk
+
+
 def group_norm_heads(y, H, N, weight, bias, eps):
     """GroupNorm with H groups over [.., H*N], biased variance
     (rwkv7_hf/fused_recurrent_update.py:136-141)."""
@@ -176,6 +182,33 @@ def attn_output_prepare(recurrent, r, k, v, g, r_k, gn_w, gn_b, H, N, eps, hi=Fa
     corr = (rf * kf * _f(r_k, hi).reshape(H, N)).sum(-1, keepdims=True) * vf
     out = (normed + corr.reshape(y.shape)) * _f(g, hi)
     return out.astype(dt)
+
+
+def attn_output_project(recurrent, r, k, v, g, r_k, gn_w, gn_b, o_w, o_b, H, N, eps, hi=False):
+    """rwkv7_hf/fused_output.py:278-394: output prep followed by o_proj (dense [out, H*N] weight, optional bias)."""
+    dt = np.asarray(r).dtype
+    prepared = attn_output_prepare(recurrent, r, k, v, g, r_k, gn_w, gn_b, H, N, eps, hi)
+    y = _f(prepared, hi) @ _f(o_w, hi).T
+    if o_b is not None:
+        y = y + _f(o_b, hi)
+    return y.astype(dt)
+
+
+def ffn(x, prev, mix, key_w, value_w, hi=False):
+    """rwkv7_hf/fused_ffn.py:394-486 (one token) and :245-376 (sequence: prev is the state before the first token).
+    k = x + (shift(x) - x) * mix; out = value(relu(key(k))^2).  Returns (out, next_state = last x)."""
+    dt = np.asarray(x).dtype
+    xf = _f(x, hi)
+    if xf.ndim == 3:
+        shifted = np.concatenate([_f(prev, hi)[:, None], xf[:, :-1]], axis=1)
+        nxt = np.asarray(x)[:, -1]
+    else:
+        shifted = _f(prev, hi)
+        nxt = np.asarray(x)
+    kx = (xf + (shifted - xf) * _f(mix, hi).reshape(-1)).astype(dt)
+    mid = (np.maximum(_f(kx, hi) @ _f(key_w, hi).T, 0).astype(dt).astype(xf.dtype) ** 2).astype(dt)
+    out = (_f(mid, hi) @ _f(value_w, hi).T).astype(dt)
+    return out, nxt
 
 
 # --------------------------------------------------------------------------
@@ -252,6 +285,17 @@ def recurrent_scan(r, w, k, v, kk, a, state, hi=False):
             - sa[..., :, None] * bq[:, t, :, None, :]
         y[:, t] = np.einsum("bhij,bhj->bhi", S, rf[:, t])
     return y.astype(dt), S.astype(np.float32)
+
+
+def recurrent_scan_state_prep(r, w_raw, k_raw, v_raw, a, state, k_k, k_a, H, N, v_first=None, v_gate=None, hi=False):
+    """rwkv7_hf/fused_recurrent_update.py:1541-1650: state prep folded into the scan.
+    Inputs [B,T,H,N]; returns (y, final state, adjusted k, interpolated v)."""
+    shp = np.asarray(r).shape
+    flat = lambda t: None if t is None else np.asarray(t).reshape(shp[0], shp[1], H * N)
+    w, k, v, kk = prefill_state_prep(flat(w_raw), flat(k_raw), flat(v_raw), flat(a), k_k, k_a, H, N, flat(v_first),
+                                     flat(v_gate), hi=hi)
+    y, S = recurrent_scan(r, w.reshape(shp), k.reshape(shp), v.reshape(shp), kk.reshape(shp), a, state, hi)
+    return y, S, k.reshape(shp), v.reshape(shp)
 
 
 def chunk_scan(r, w, k, v, kk, a, state, chunk=16):
@@ -447,6 +491,84 @@ def mm8_matmul(x, w_u8, mx, rx, my, ry, hi=False):
     return (_f(x, hi) @ W).astype(dt)
 
 
+def _ops_in(dtype, q, ry, rx, my, mx):
+    """(q + 0.5) * ry * rx + my + mx with every operation rounded to ``dtype``, the order of dequantize_mm8 /
+    dequantize_mm4 (rwkv7_hf/native_quant_mm8.py:100-107, native_quant_mm4.py:111-125)."""
+    t = np.dtype(dtype).type
+    v = (q.astype(dtype) + t(0.5)).astype(dtype)
+    v = (v * np.asarray(ry, dtype).reshape(-1, 1)).astype(dtype)
+    v = (v * np.asarray(rx, dtype).reshape(1, -1)).astype(dtype)
+    v = (v + np.asarray(my, dtype).reshape(-1, 1)).astype(dtype)
+    return (v + np.asarray(mx, dtype).reshape(1, -1)).astype(dtype)
+
+
+def dequantize_mm8(w_u8, mx, rx, my, ry, dtype=np.float16):
+    return _ops_in(dtype, w_u8, ry, rx, my, mx)
+
+
+def quantize_mm4(weight, out_dtype=np.float16):
+    """4-bit affine format, rwkv7_hf/native_quant_mm4.py:77-108.  ``weight`` [K, M] (transposed Linear weight).
+    Returns (packed [K, Mp/2] u8, mx [Mp], rx_s [Mp], my [K,1], ry_s [K,1], M, Mp)."""
+    w = np.asarray(weight).astype(np.float32)
+    K, M = w.shape
+    if M % 2:
+        w = np.pad(w, ((0, 0), (0, 1)))
+    Mp = w.shape[1]
+    if K > Mp:
+        my = w.min(1, keepdims=True); w = w - my
+        mx = w.min(0); w = w - mx
+    else:
+        mx = w.min(0); w = w - mx
+        my = w.min(1, keepdims=True); w = w - my
+    rx = np.maximum(w.max(0), np.float32(1e-8)); w = w / rx
+    ry = np.maximum(w.max(1, keepdims=True), np.float32(1e-8)); w = w / ry
+    u4 = np.clip(np.floor(w * np.float32(16)), 0, 15).astype(np.uint8)
+    packed = (u4[:, 0::2] | (u4[:, 1::2] << 4)).astype(np.uint8)
+    od = np.dtype(out_dtype)
+    return packed, mx.astype(od), (rx / np.float32(4)).astype(od), my.astype(od), (ry / np.float32(4)).astype(od), M, Mp
+
+
+def unpack_mm4(packed):
+    u4 = np.empty((packed.shape[0], packed.shape[1] * 2), np.uint8)
+    u4[:, 0::2] = packed & 15
+    u4[:, 1::2] = packed >> 4
+    return u4
+
+
+def dequantize_mm4(packed, mx, rx_s, my, ry_s, m_orig, dtype=np.float16):
+    return _ops_in(dtype, unpack_mm4(packed), ry_s, rx_s, my, mx)[:, :m_orig]
+
+
+def mm4_matmul(x, packed, mx, rx_s, my, ry_s, m_orig, hi=False):
+    """y = x @ W with W the affine 4-bit weight, fp32 accumulate (the fused kernel's arithmetic,
+    rwkv7_hf/native_quant_mm4.py:150-215)."""
+    dt = np.asarray(x).dtype
+    W = (unpack_mm4(packed).astype(np.float32) + 0.5) * _f(ry_s, hi).reshape(-1, 1) * _f(rx_s, hi).reshape(1, -1) \
+        + _f(my, hi).reshape(-1, 1) + _f(mx, hi).reshape(1, -1)
+    return (_f(x, hi) @ W[:, :m_orig]).astype(dt)
+
+
+def a8w8_ffn(x, up_q_t, up_s, down_q_t, down_s, residual, up_bias=None, down_bias=None):
+    """rwkv7_hf/native_quant_a8w8.py:436-524: up GEMM, relu^2 + requantise at the boundary, down GEMM + residual.
+    The reference path for this function is GPU-only (Triton + torch._int_mm): this restatement follows its kernels
+    line by line but is not checked against a reference output (parity unpinned for this one function)."""
+    qa, sa = dynamic_a8_quant(x)
+    acc = int8_gemm_i32(qa, up_q_t)
+    pre = acc.astype(np.float32) * sa[:, None] * np.asarray(up_s, np.float32)[None, :]
+    if up_bias is not None:
+        pre = pre + np.asarray(up_bias, np.float32)
+    pre = pre.astype(np.float16).astype(np.float32)
+    act = np.maximum(pre, 0)
+    act = (act * act).astype(np.float16).astype(np.float32)
+    qh, sh = dynamic_a8_quant(act)
+    acc2 = int8_gemm_i32(qh, down_q_t)
+    y = acc2.astype(np.float32) * sh[:, None] * np.asarray(down_s, np.float32)[None, :]
+    if down_bias is not None:
+        y = y + np.asarray(down_bias, np.float32)
+    y = y + np.asarray(residual, np.float32)
+    return y.astype(np.asarray(x).dtype), qh, sh
+
+
 # --------------------------------------------------------------------------
 # Whole token step / model (per-layer parameter dict, see tests/golden)
 # --------------------------------------------------------------------------
@@ -465,6 +587,10 @@ def linear_op(x, op, hi=False):
             return w8_linear(x, op["q"], op["s"], hi)
         if kind == "a8w8":
             return a8w8_linear(x, op["q_t"], op["s"])[0]
+        if kind == "mm8":
+            return mm8_matmul(x, op["u8"], op["mx"], op["rx"], op["my"], op["ry"], hi)
+        if kind == "mm4":
+            return mm4_matmul(x, op["packed"], op["mx"], op["rx"], op["my"], op["ry"], op["m"], hi)
         raise ValueError(kind)
     return (_f(x, hi) @ _f(op, hi).T).astype(dt)
 

@@ -136,6 +136,33 @@ def gen_ops(dtype, seed):
                                       gq, r_k, gn_w, gn_b, num_heads=H, head_dim=N,
                                       head_v_dim=N, eps=eps, force_fallback=True)
     out.update(op_rec=rec, op_r=rr, op_k=kq, op_v=vq, op_g=gq, op_out=op)
+
+    # ---- later additions (drawn after everything above so the earlier entries keep their values) ----------
+    from rwkv7_hf import fused_ffn as ff
+    ok_, ov_, okk_ = fp.fused_prefill_kv_kk_prep(k_r, v_r, a_in, k_k, k_a, v_first=vf, v_gate=vg, num_heads=H,
+                                                  head_dim=N, force_fallback=True)
+    out.update(kvkk_k=ok_, kvkk_v=ov_, kvkk_kk=okk_)
+    a_seq = torch.sigmoid(rn(B, T, H, N)).to(dtype)
+    w_seq, k_seq, v_seq = (rn(B, T, H, N).to(dtype) for _ in range(3))
+    vf_seq, vg_seq = rn(B, T, H, N).to(dtype), torch.sigmoid(rn(B, T, H, N)).to(dtype)
+    so, sst, sk, sv = fru.fused_recurrent_scan_state_prep(rs, w_seq, k_seq, v_seq, a_seq, s0, k_k, k_a, v_first=vf_seq,
+                                                          v_gate=vg_seq, force_fallback=True)
+    out.update(ssp_w_raw=w_seq, ssp_k_raw=k_seq, ssp_v_raw=v_seq, ssp_a=a_seq, ssp_vf=vf_seq, ssp_vg=vg_seq,
+               ssp_y=so, ssp_state_out=sst, ssp_k=sk, ssp_v=sv)
+    ow = (0.05 * rn(D, A)).to(dtype)
+    ob = (0.1 * rn(D)).to(dtype)
+    opj = fo.fused_attn_output_project(rec, rr.view(rows, H, N), kq.view(rows, H, N), vq.view(rows, H, N), gq, r_k,
+                                       gn_w, gn_b, ow, ob, num_heads=H, head_dim=N, head_v_dim=N, eps=eps,
+                                       force_fallback=True)
+    out.update(oproj_w=ow, oproj_b=ob, oproj_out=opj)
+    Fi = 256
+    kw_, vw_ = (0.05 * rn(Fi, D)).to(dtype), (0.05 * rn(D, Fi)).to(dtype)
+    fx, fprev = rn(3, D).to(dtype), rn(3, D).to(dtype)
+    fo1, fn1 = ff.fused_ffn(fx, fprev, mixes[0], kw_, vw_, force_fallback=True)
+    fxs, fps = rn(B, 5, D).to(dtype), rn(B, D).to(dtype)
+    fo2, fn2 = ff.fused_sequence_ffn(fxs, fps, mixes[0], kw_, vw_, force_fallback=True)
+    out.update(ffn_key=kw_, ffn_value=vw_, ffn_x=fx, ffn_prev=fprev, ffn_out=fo1, ffn_next=fn1,
+               sffn_x=fxs, sffn_prev=fps, sffn_out=fo2, sffn_next=fn2)
     return {k_: npy(v_) for k_, v_ in out.items()}
 
 
@@ -159,6 +186,20 @@ def gen_quant(seed):
     u8, mx, rx, my, ry = m8.quantize_mm8(Wt)
     out.update(mm8_u8=u8, mm8_mx=mx, mm8_rx=rx, mm8_my=my, mm8_ry=ry,
                mm8_y=m8.mm8_matmul(x.float(), u8, mx, rx, my, ry))
+    # the formats as the modules store them (fp16 scales), the dequantised fp16 weight with the reference's operation
+    # order, and the 4-bit affine format (even and odd output widths)
+    from rwkv7_hf import native_quant_mm4 as m4
+    Wh = W.t().contiguous()  # fp16 [K, O]
+    u8h, mxh, rxh, myh, ryh = m8.quantize_mm8(Wh)
+    out.update(mm8h_u8=u8h, mm8h_mx=mxh, mm8h_rx=rxh, mm8h_my=myh, mm8h_ry=ryh,
+               mm8h_W=m8.dequantize_mm8(u8h, mxh, rxh, myh, ryh), mm8h_y=m8.mm8_matmul(x, u8h, mxh, rxh, myh, ryh))
+    p4a, mx4, rx4, my4, ry4, mo, mp = m4.quantize_mm4(Wh)
+    out.update(mm4a_packed=p4a, mm4a_mx=mx4, mm4a_rx=rx4, mm4a_my=my4, mm4a_ry=ry4,
+               mm4a_W=m4.dequantize_mm4(p4a, mx4, rx4, my4, ry4, mo), mm4a_y=m4.mm4_matmul(x, p4a, mx4, rx4, my4, ry4, mo))
+    Wodd = Wh[:, :95].contiguous()
+    p4o, mxo, rxo, myo, ryo, moo, mpo = m4.quantize_mm4(Wodd)
+    out.update(mm4o_packed=p4o, mm4o_mx=mxo, mm4o_rx=rxo, mm4o_my=myo, mm4o_ry=ryo,
+               mm4o_W=m4.dequantize_mm4(p4o, mxo, rxo, myo, ryo, moo))
     return {k_: npy(v_) for k_, v_ in out.items()}
 
 

@@ -96,7 +96,16 @@ def test_host_quantisers_match_oracle():
 def test_quant_modules_keep_reference_buffer_names():
     lin = torch.nn.Linear(256, 64, bias=False)
     assert set(dict(hb.MM4Linear(lin, group_size=128).named_buffers())) == {"packed_group", "group_scales"}
-    assert set(dict(hb.MM8Linear(lin).named_buffers())) == {"q_row", "row_scale"}
+    mm8 = hb.MM8Linear(lin.half())
+    assert set(dict(mm8.named_buffers())) == {"w_u8", "mx", "rx", "my", "ry"}  # the reference's format off sm7x
+    assert tuple(mm8.w_u8.shape) == (256, 64) and tuple(mm8.my.shape) == (256, 1) and tuple(mm8.rx.shape) == (64,)
+    Wt = lin.weight.data.t().contiguous()
+    u8, mx, rx, my, ry = O.quantize_mm8(Wt.float().numpy())
+    assert np.array_equal(mm8.w_u8.numpy(), u8) and np.array_equal(mm8.rx.numpy(), rx.astype(np.float16))
+    p4, mx4, rx4, my4, ry4, m, mp = hb.quantize_mm4(Wt[:, :63].contiguous())
+    po, mxo, rxo, myo, ryo, mo, mpo = O.quantize_mm4(Wt[:, :63].numpy())
+    assert (m, mp) == (63, 64) == (mo, mpo) and np.array_equal(p4.numpy(), po) and np.array_equal(ry4.numpy(), ryo)
+    assert set(dict(hb.MM8Linear(lin, rowwise=True).named_buffers())) == {"q_row", "row_scale"}  # its sm7x format
     assert set(dict(hb.A8W8Linear(lin).named_buffers())) == {"q_weight_t", "weight_scale"}
     m = torch.nn.Sequential(torch.nn.Linear(256, 64), torch.nn.Linear(64, 8))
     assert hb.quantize_model(m, "mm4", min_params=1000) == 1 and isinstance(m[0], hb.MM4Linear)

@@ -61,7 +61,7 @@ def test_tiny_fp32_model_matches_reference_golden():
     assert tuple(full.shape) == (2, T, 256)
 
 
-@pytest.mark.parametrize("kind", ["mm4", "mm8", "a8w8"])
+@pytest.mark.parametrize("kind", ["mm4", "mm8", "w8", "a8w8"])
 def test_quantised_fp16_model_against_oracle(kind):
     g = golden("model_tiny.npz")
     model = load_tiny(g, torch.float16)
@@ -78,9 +78,12 @@ def test_quantised_fp16_model_against_oracle(kind):
             if kind == "mm4":
                 p, s = O.quantize_w4_groupwise(W, 128)
                 d[nm] = dict(kind="w4g", packed=p, scales=s)
-            elif kind == "mm8":
+            elif kind == "w8":
                 q, s = O.quantize_w8_row(W)
                 d[nm] = dict(kind="w8", q=q, s=s)
+            elif kind == "mm8":
+                u8, mx, rx, my, ry = O.quantize_mm8(W.astype(np.float32).T)
+                d[nm] = dict(kind="mm8", u8=u8, mx=f16(mx), rx=f16(rx), my=f16(my), ry=f16(ry))
             else:
                 qt, s = O.quantize_weight_per_channel_int8(W)
                 d[nm] = dict(kind="a8w8", q_t=qt, s=s)
