@@ -149,13 +149,14 @@ def fused_ffn_sequence_shift_mix(x, initial_prev, mix, *, block_size: int = 256,
     return storage[0], nxt
 
 
-def fused_attn_shift_mix(x, x_prev, mix_r, mix_w, mix_k, mix_v, mix_a, mix_g, *, force_fallback: bool = False):
-    """Six mixes of ``x`` against an explicit previous tensor of the same shape (``[B,D]`` decode form,
-    rwkv7_hf/fused_time_mix.py:340): each row is a one-token sequence whose initial state is ``x_prev``."""
+def fused_attn_shift_mix(x, prev, x_r, x_w, x_k, x_v, x_a, x_g, *, block_size: int = 256, force_fallback: bool = False):
+    """Six mixes of ``x`` against an explicit previous tensor of the same shape, ``[batch, hidden]`` or
+    ``[batch, tokens, hidden]`` (rwkv7_hf/fused_time_mix.py:340): each row is a one-token sequence whose initial state
+    is its row of ``prev``.  Mix vectors may have any shape with ``hidden`` elements."""
     no_fallback(force_fallback, "fused_attn_shift_mix")
-    if x.shape != x_prev.shape:
-        raise ValueError("x and x_prev must have identical shapes")
+    if x.shape != prev.shape:
+        raise ValueError("x and prev must have identical flattened shapes")
     D = int(x.shape[-1])
     x3 = x.reshape(-1, 1, D)
-    outs = fused_attn_sequence_shift_mix(x3, x_prev.reshape(-1, D), mix_r, mix_w, mix_k, mix_v, mix_a, mix_g)
+    outs = fused_attn_sequence_shift_mix(x3, prev.reshape(-1, D), *(m.reshape(-1) for m in (x_r, x_w, x_k, x_v, x_a, x_g)))
     return tuple(o.reshape(x.shape) for o in outs[:6])

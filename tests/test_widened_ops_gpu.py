@@ -150,3 +150,19 @@ def test_a8w8_fused_ffn_against_oracle(M):
     # contract violations fall back to None like the reference
     assert hb.a8w8_ffn(cu(x).float(), up, down, cu(res)) is None
     assert hb.a8w8_ffn(cu(x), up, torch.nn.Linear(Fi, D).cuda().half(), cu(res)) is None
+
+
+@pytest.mark.parametrize("shape", [(3, 128), (2, 5, 256)])
+def test_attn_shift_mix_explicit_previous(shape):
+    """out_i = x + (prev - x) * mix_i for the six streams, any leading shape, mix vectors of any shape with D elements."""
+    rng = np.random.default_rng(sum(shape))
+    x, prev = (rng.standard_normal(shape).astype(np.float16) for _ in range(2))
+    mixes = [rng.random((1, 1, shape[-1])).astype(np.float16) for _ in range(6)]
+    outs = hb.fused_attn_shift_mix(cu(x), cu(prev), *(cu(m) for m in mixes))
+    assert len(outs) == 6
+    for o, m in zip(outs, mixes):
+        ref = x.astype(np.float32) + (prev.astype(np.float32) - x.astype(np.float32)) * m.reshape(-1).astype(np.float32)
+        assert tuple(o.shape) == shape
+        np.testing.assert_allclose(npf(o), ref, rtol=2e-3, atol=2e-3)
+    with pytest.raises(ValueError):
+        hb.fused_attn_shift_mix(cu(x), cu(prev)[:1], *(cu(m) for m in mixes))
