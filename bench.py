@@ -340,7 +340,7 @@ def main():
                 # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture at B*H = 4096 (profiles/): 80.5 MB per
                 # launch (reads = state in; most of the written state is still dirty in L2 when the kernel ends),
                 # scaled by the sequence-heads of this launch
-                "traffic": 80.5e6 * (B * Hl) / 4096.0, "bytes_per_launch": wkv_bytes, "us_per_launch": wkv_ms * 1e3}
+                "traffic": 87.0e6 * (B * Hl) / 4096.0, "bytes_per_launch": wkv_bytes, "us_per_launch": wkv_ms * 1e3}
 
     extra = {"step_bytes": step_bytes, "step_hbm_frac": step_bytes / (ms_per_step * 1e-3) / 1e9 / hbm_peak,
              "wkv_share_of_step": wkv_ms * len(states) / ms_per_step}
