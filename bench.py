@@ -337,7 +337,7 @@ def main():
     achieved = wkv_bytes / (wkv_ms * 1e-3) / 1e9
     roofline = {"kernel": "wkv7_step_kernel (decode recurrence + fused epilogues)", "bound": "hbm", "achieved": achieved,
                 "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak, "peak_source": peak_src + " (burst copy)",
-                # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture at B*H = 4096 (profiles/): 80.5 MB per
+                # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture at B*H = 4096 (profiles/): 87.0 MB per
                 # launch (reads = state in; most of the written state is still dirty in L2 when the kernel ends),
                 # scaled by the sequence-heads of this launch
                 "traffic": 87.0e6 * (B * Hl) / 4096.0, "bytes_per_launch": wkv_bytes, "us_per_launch": wkv_ms * 1e3}
