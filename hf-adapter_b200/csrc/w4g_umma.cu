@@ -40,29 +40,44 @@ namespace rwkv7 {
 namespace w4 {
 constexpr int TILE_N = 128;  // output channels per CTA = UMMA M
 constexpr int KB = 128;      // k elements per pipeline stage
-constexpr int NB = 64;       // activation rows per MMA = UMMA N
-constexpr int STAGES = 6;    // activation-tile ring (L2-resident source, freed by the MMA commit)
 constexpr int WB = 2;        // tile blocks per bulk copy (17 KiB requests: a bare copy ring of this shape moved 33.5 MB in
                              // 6.9 us against 9.5-10.6 us with 8.5 KiB ones; in this kernel, whose ring is kept full
                              // by the slower consumer side, the step time did not change)
-constexpr int WSTAGES = 5;   // weight ring, in copies (HBM source, freed as soon as the dequant warps have read both blocks)
-constexpr int WRING_BYTES = WSTAGES * WB * 8704;
 constexpr int RAW_BYTES = TILE_N * KB / 2;  // 8192 packed nibbles
 constexpr int SC_OFF = RAW_BYTES;           // then 128 fp16 scales of the k-block
 constexpr int Z_OFF = SC_OFF + TILE_N * 2;  // then 128 u8 zero-points, then padding
 constexpr int BLOCK_BYTES = 8704;           // one tile block in memory = one bulk copy (68 x 128 B)
-constexpr int XATOM_BYTES = NB * 128;       // one 64-k swizzle atom of the activation tile
-constexpr int X_BYTES = 2 * XATOM_BYTES;    // 16384
-constexpr int SB = 3;            // dequant warp groups: group g expands k-blocks g, g + SB, g + 2 SB, ...
-constexpr int NAB = 6;           // dequantised-A buffers in tensor memory (one k-block = 64 columns each)
-constexpr int NA = NAB;          // barrier pairs for the A buffers
-constexpr int NISS = 2;          // MMA issuer warps, each with its own accumulator (summed in the epilogue)
-constexpr int TMEM_COLS = 512;   // A: NAB x 64 columns, D: NISS x 64 columns
-constexpr int D_COL = NAB * 64;
+constexpr int SB = 3;            // dequant warp groups: group g expands copies g, g + SB, g + 2 SB, ...
+constexpr int TMEM_COLS = 512;   // A: NAB x 64 columns, D: NISS x NB columns
 constexpr int ISS2_WARP = 2 + SB * 4;           // second issuer = last warp
 constexpr int XPROD_WARP = ISS2_WARP + 1;       // activation-tile producer
 constexpr int THREADS = 64 + SB * 128 + 64;
-constexpr int Q_BYTES = NB * TILE_N * 4;        // split-K exchange: [rank slot][rows of this rank][128 channels] fp32
+
+// Two shapes of the same kernel: 64 activation rows per weight pass (decode batches up to 64: deep rings, six A buffers)
+// and 128 rows per pass (larger batches, e.g. tensor-parallel decode: every dequantised block feeds an MMA twice as
+// wide, so the dequantisation and the weight stream are paid once per 128 rows; shorter rings pay for the wider tiles).
+template <int NB_>
+struct Cfg;
+// NISS = MMA issuer warps, each with its own accumulator (summed in the epilogue), taking k-blocks i = me (mod NISS).
+// A waiter must see every phase of a barrier it waits on, so the activation ring and the A buffers, which are indexed
+// by i, need a length that is a multiple of NISS: then a stage or buffer always belongs to the same issuer.  (With
+// three stages and two issuers an issuer skips every other phase of a stage's barrier, a parity wait passes a phase
+// early and the ring runs out of step until a wait never completes.)  The same holds for the dequant groups: the
+// weight ring (in copies) is a multiple of SB and the A buffers a multiple of WB * SB.
+template <>
+struct Cfg<64> {
+    static constexpr int NB = 64, STAGES = 4, WSTAGES = 6, NAB = 6, NISS = 2;
+};
+template <>
+struct Cfg<128> {
+    static constexpr int NB = 128, STAGES = 3, WSTAGES = 3, NAB = 6, NISS = 1;
+};
+template <int NB_>
+constexpr size_t smem_bytes() {
+    using C = Cfg<NB_>;
+    return (size_t)C::STAGES * 2 * C::NB * 128 + (size_t)C::WSTAGES * WB * BLOCK_BYTES + (size_t)C::NB * TILE_N * 4 +
+           (2 * C::STAGES + 2 * C::WSTAGES + 2 * C::NAB + 1) * 8 + 16 + 1024;
+}
 }  // namespace w4
 
 constexpr int kW4MaxGroup = 4;  // projections of equal shape served by one launch (r / k / v of a layer)
@@ -114,9 +129,25 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint
                  ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 
+template <int NBT>
 __global__ void __launch_bounds__(w4::THREADS, 1)
 w4g_umma_kernel(const __grid_constant__ W4Maps maps, const W4UmmaArgs p) {
     using namespace w4;
+    using C = Cfg<NBT>;
+    constexpr int NB = C::NB;            // activation rows per MMA = UMMA N
+    constexpr int STAGES = C::STAGES;    // activation-tile ring (L2-resident source, freed by the MMA commit)
+    constexpr int WSTAGES = C::WSTAGES;  // weight ring, in copies (HBM source, freed as soon as the dequant warps have read both blocks)
+    constexpr int NAB = C::NAB;          // dequantised-A buffers in tensor memory (one k-block = 64 columns each)
+    constexpr int NA = NAB;              // barrier pairs for the A buffers
+    constexpr int WRING_BYTES = WSTAGES * WB * BLOCK_BYTES;
+    constexpr int XATOM_BYTES = NB * 128;     // one 64-k swizzle atom of the activation tile
+    constexpr int X_BYTES = 2 * XATOM_BYTES;
+    constexpr int D_COL = NAB * 64;
+    constexpr int Q_BYTES = NB * TILE_N * 4;  // split-K exchange: [rank slot][rows of this rank][128 channels] fp32
+    constexpr int NISS = C::NISS;
+    static_assert(D_COL + NISS * NB <= TMEM_COLS, "tensor memory budget");
+    static_assert(STAGES % NISS == 0 && NAB % NISS == 0, "a stage / A buffer must always belong to the same issuer");
+    static_assert(WSTAGES % SB == 0 && NAB % (WB * SB) == 0, "a weight stage / A buffer must always belong to the same dequant group");
     extern __shared__ unsigned char smem_unaligned[];
     // the swizzled TMA / UMMA tiles need 1024-byte alignment; the offset is the same in every CTA
     unsigned char* smem = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);
@@ -216,7 +247,7 @@ w4g_umma_kernel(const __grid_constant__ W4Maps maps, const W4UmmaArgs p) {
                 tma_load_3d(xs + s * X_BYTES, tm_x, &full[s], 0, m0, (kb0 + i) * 2);
             }
         }
-    } else if (warp == 1 || warp == ISS2_WARP) {
+    } else if (warp == 1 || (NISS == 2 && warp == ISS2_WARP)) {
         if (lane == 0) {
             // Throughput of the A path = (buffers in flight) / (dequantise + barrier hop + MMA + commit + hop), so
             // tensor memory holds six single-block A buffers; every mbarrier hop costs this thread ~150-200 cycles
@@ -224,7 +255,7 @@ w4g_umma_kernel(const __grid_constant__ W4Maps maps, const W4UmmaArgs p) {
             // summed in the epilogue): one issues while the other waits.
             constexpr uint32_t idesc = make_idesc(TILE_N, NB, /*F32*/ 1, /*F16*/ 0, /*F16*/ 0);
             const int me = warp == 1 ? 0 : 1;
-            const uint32_t d_tmem = tmem_base + D_COL + me * 64;
+            const uint32_t d_tmem = tmem_base + D_COL + me * NB;
             for (int i = me; i < nkb; i += NISS) {
                 const int ab = i % NAB, s = i % STAGES;
                 if (!mbar_wait_hot(&a_ready[ab], (i / NAB) & 1, actx, kErrWaitAReady)) break;
@@ -299,13 +330,13 @@ w4g_umma_kernel(const __grid_constant__ W4Maps maps, const W4UmmaArgs p) {
         if (grp < 2) {
             if (ok) {
                 tc_fence_after();
-                constexpr int CPG = 32;  // accumulator columns (activation rows) per reading group
+                constexpr int CPG = NB / 2;  // accumulator columns (activation rows) per reading group
 #pragma unroll
                 for (int c = 0; c < CPG / 16; ++c) {
                     uint32_t v[16], v2[16];
                     const int col0 = grp * CPG + c * 16;
                     tmem_ld16(lane_addr + D_COL + col0, v);
-                    if (nkb > 1) tmem_ld16(lane_addr + D_COL + 64 + col0, v2);  // second issuer's accumulator (unused when it had no work)
+                    if (NISS == 2 && nkb > 1) tmem_ld16(lane_addr + D_COL + NB + col0, v2);  // second issuer's accumulator (unused when it had no work)
                     tc_wait_ld();
                     if (col0 < m_rows) {
                         // 16 consecutive rows never straddle two ranks (rows_per_rank is 8, 16, 32 or 64)
@@ -317,7 +348,7 @@ w4g_umma_kernel(const __grid_constant__ W4Maps maps, const W4UmmaArgs p) {
                                        ((size_t)split * rows_per_rank + (m - dst * rows_per_rank)) * TILE_N + row;
 #pragma unroll
                             for (int e = 0; e < 8; ++e)
-                                q[e * TILE_N] = __uint_as_float(v[h8 * 8 + e]) + (nkb > 1 ? __uint_as_float(v2[h8 * 8 + e]) : 0.f);
+                                q[e * TILE_N] = __uint_as_float(v[h8 * 8 + e]) + ((NISS == 2 && nkb > 1) ? __uint_as_float(v2[h8 * 8 + e]) : 0.f);
                         }
                     }
                 }
@@ -462,8 +493,9 @@ int launch_w4g_umma_tiled(const void* const* xs, const uint8_t* const* tws, cons
                           int M, int K, int Nout, int epilogue, cudaStream_t st) {
     using namespace w4;
     RWKV7_REQUIRE(G >= 1 && G <= kW4MaxGroup, RWKV7_ERR_UNSUPPORTED, "w4g_gemv_tiled: 1..%d projections per launch (got %d)", kW4MaxGroup, G);
+    const int NB = M > 64 ? 128 : 64;          // activation rows per pass over the weights
     RWKV7_REQUIRE(M >= 1 && (long long)G * ((M + NB - 1) / NB) <= 65535, RWKV7_ERR_UNSUPPORTED, "w4g_gemv_tiled: M out of range (got %d)", M);
-    const int row_blocks = (M + NB - 1) / NB;  // each block of 64 activation rows is one pass over the weights
+    const int row_blocks = (M + NB - 1) / NB;
     RWKV7_REQUIRE(K % KB == 0, RWKV7_ERR_UNSUPPORTED, "w4g_gemv_tiled: K must be a multiple of %d (got %d)", KB, K);
     const int tiles = (Nout + TILE_N - 1) / TILE_N;
     const int total_kb = K / KB;
@@ -490,8 +522,10 @@ int launch_w4g_umma_tiled(const void* const* xs, const uint8_t* const* tws, cons
     a.row_blocks = row_blocks;
     a.error = kernel_error_word();
     RWKV7_REQUIRE(a.error != nullptr, RWKV7_ERR_CUDA, "w4g_gemv_tiled: cannot resolve the device error word");
-    const size_t smem = (size_t)STAGES * X_BYTES + (size_t)WRING_BYTES + Q_BYTES + (2 * STAGES + 2 * WSTAGES + 2 * NA + 1) * 8 + 16 + 1024;
-    cudaError_t e = cudaFuncSetAttribute(w4g_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const size_t smem = NB == 128 ? smem_bytes<128>() : smem_bytes<64>();
+    cudaError_t e = NB == 128
+        ? cudaFuncSetAttribute(w4g_umma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+        : cudaFuncSetAttribute(w4g_umma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     RWKV7_REQUIRE(e == cudaSuccess, RWKV7_ERR_CUDA, "w4g_gemv_tiled: %s", cudaGetErrorString(e));
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(tiles, row_blocks * G, splits);
@@ -508,7 +542,7 @@ int launch_w4g_umma_tiled(const void* const* xs, const uint8_t* const* tws, cons
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = (programmatic_launch_enabled() && !fresh) ? 2 : 1;
-    e = cudaLaunchKernelEx(&cfg, w4g_umma_kernel, maps, a);
+    e = NB == 128 ? cudaLaunchKernelEx(&cfg, w4g_umma_kernel<128>, maps, a) : cudaLaunchKernelEx(&cfg, w4g_umma_kernel<64>, maps, a);
     RWKV7_REQUIRE(e == cudaSuccess, RWKV7_ERR_CUDA, "w4g_gemv_tiled launch: %s", cudaGetErrorString(e));
     return RWKV7_OK;
 }
