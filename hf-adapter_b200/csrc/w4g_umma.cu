@@ -145,7 +145,7 @@ w4g_umma_kernel(const __grid_constant__ W4Maps maps, const W4UmmaArgs p) {
     constexpr int D_COL = NAB * 64;
     constexpr int Q_BYTES = NB * TILE_N * 4;  // split-K exchange: [rank slot][rows of this rank][128 channels] fp32
     constexpr int NISS = C::NISS;
-    static_assert(D_COL + NISS * NB <= TMEM_COLS, "tensor memory budget");
+    static_assert(D_COL + NISS * NB <= TMEM_COLS, "tensor memory capacity");
     static_assert(STAGES % NISS == 0 && NAB % NISS == 0, "a stage / A buffer must always belong to the same issuer");
     static_assert(WSTAGES % SB == 0 && NAB % (WB * SB) == 0, "a weight stage / A buffer must always belong to the same dequant group");
     extern __shared__ unsigned char smem_unaligned[];
