@@ -190,7 +190,8 @@ int rwkv7_w4g_gemv(const void* x, const uint8_t* packed, const void* scales, con
                    const void* residual, void* out, int M, int K, int Nout, int group, int epilogue,
                    int dtype, void* stream);
 
-/* Tensor-core version of the same projection (any row count, one pass over the weights per 64 rows), reading a TILED
+/* Tensor-core version of the same projection (any row count; one pass over the weights per 64 rows up to 64 rows, per
+ * 128 rows above), reading a TILED
  * copy of the weights built once at load time by rwkv7_w4g_repack: one 8704-byte block per [128 channels x 128 k] tile
  * (packed nibbles, then that tile's fp16 scales and u8 zero-points), blocks of a channel tile consecutive, so each CTA
  * streams one contiguous region.  Same values, same arithmetic as above.  rwkv7_w4g_tiled_bytes returns the size of
@@ -202,8 +203,9 @@ int rwkv7_w4g_repack(const uint8_t* packed, const void* scales, const uint8_t* z
 int rwkv7_w4g_gemv_tiled(const void* x, const uint8_t* tiled, const void* residual, void* out, int M, int K, int Nout,
                          int epilogue, int dtype, void* stream);
 /* G (1..4) projections of the same shape in one launch, each with its own activations xs[g] [M,K], tiled weights and
- * output outs[g] [M,Nout] (the r / k / v projections of a layer: rwkv7_hf/native_model.py RWKV7Attention.forward calls
- * them back to back on different mixes of the same hidden state).  The three pointer arrays live in host memory and
+ * output outs[g] [M,Nout] (the r / k / v projections of a layer: rwkv7_hf/native.py:208-211 calls them back to back on
+ * different mixes of the same hidden state; the graph path groups them in _native_graph_rkv_project,
+ * rwkv7_hf/native_jit_decode.py:175).  The three pointer arrays live in host memory and
  * are read during the call.  Epilogue none or relu^2. */
 int rwkv7_w4g_gemv_tiled_group(const void* const* xs, const uint8_t* const* tiled, void* const* outs, int G, int M, int K,
                                int Nout, int epilogue, int dtype, void* stream);
