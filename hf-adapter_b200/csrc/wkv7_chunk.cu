@@ -409,52 +409,68 @@ __global__ void __launch_bounds__(ck::THREADS, 1) wkv7_chunk_kernel(const __grid
         }
         tc_fence_before();
         __syncthreads();
-        // Blocked forward substitution on 16-row blocks.  Value columns are independent, so warp w < 4 sweeps columns
-        // 16 w .. 16 w + 15 through all four blocks with warp-level syncs only; a lane owns rows rg, rg+4, rg+8, rg+12 of
-        // the block and two columns (a 4 x 2 register tile keeps the shared-memory wavefronts per FMA low):
+        // Blocked forward substitution on 16-row blocks.  Value columns are independent, so each sweeping warp takes a
+        // group of columns through all four blocks with warp-level syncs only; a lane owns rows rg, rg+4, rg+8, rg+12
+        // of the block and CW columns:
         //   (a) rhs_b += L[b][0..b) U[0..b)        (b) U_b = inv(I - L_bb) rhs_b
-        if (warp < 4) {
-            const int rg = lane >> 3, col = warp * 16 + (lane & 7) * 2;
+        constexpr int CW = 1;                   // value columns per lane
+        constexpr int SWEEP_WARPS = 8 / CW;     // 8 lanes x CW columns per warp
+        if (warp < SWEEP_WARPS) {
+            const int rg = lane >> 3, col = warp * (8 * CW) + (lane & 7) * CW;
 #pragma unroll 1
             for (int blk = 0; blk < 4; ++blk) {
                 const int r0 = blk * 16 + rg;
                 if (blk > 0) {
-                    float2 acc[4];
+                    float acc[4][CW];
 #pragma unroll
-                    for (int rr = 0; rr < 4; ++rr) acc[rr] = *reinterpret_cast<const float2*>(RH + (r0 + 4 * rr) * ABS + col);
+                    for (int rr = 0; rr < 4; ++rr)
+#pragma unroll
+                        for (int c = 0; c < CW; ++c) acc[rr][c] = RH[(r0 + 4 * rr) * ABS + col + c];
 #pragma unroll 2
                     for (int s0 = 0; s0 < blk * 16; s0 += 4) {
-                        float2 u[4];
+                        float u[4][CW];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) u[e] = *reinterpret_cast<const float2*>(UU + (s0 + e) * 64 + col);
+                        for (int e = 0; e < 4; ++e)
+#pragma unroll
+                            for (int c = 0; c < CW; ++c) u[e][c] = UU[(s0 + e) * 64 + col + c];
 #pragma unroll
                         for (int rr = 0; rr < 4; ++rr) {
                             const float4 m = *reinterpret_cast<const float4*>(AB + (r0 + 4 * rr) * ABS + s0);
-                            acc[rr].x = fmaf(m.x, u[0].x, fmaf(m.y, u[1].x, fmaf(m.z, u[2].x, fmaf(m.w, u[3].x, acc[rr].x))));
-                            acc[rr].y = fmaf(m.x, u[0].y, fmaf(m.y, u[1].y, fmaf(m.z, u[2].y, fmaf(m.w, u[3].y, acc[rr].y))));
+#pragma unroll
+                            for (int c = 0; c < CW; ++c)
+                                acc[rr][c] = fmaf(m.x, u[0][c], fmaf(m.y, u[1][c], fmaf(m.z, u[2][c], fmaf(m.w, u[3][c], acc[rr][c]))));
                         }
                     }
 #pragma unroll
-                    for (int rr = 0; rr < 4; ++rr) *reinterpret_cast<float2*>(RH + (r0 + 4 * rr) * ABS + col) = acc[rr];
+                    for (int rr = 0; rr < 4; ++rr)
+#pragma unroll
+                        for (int c = 0; c < CW; ++c) RH[(r0 + 4 * rr) * ABS + col + c] = acc[rr][c];
                     __syncwarp();
                 }
-                float2 o[4];
+                float o[4][CW];
 #pragma unroll
-                for (int rr = 0; rr < 4; ++rr) o[rr] = make_float2(0.f, 0.f);
+                for (int rr = 0; rr < 4; ++rr)
+#pragma unroll
+                    for (int c = 0; c < CW; ++c) o[rr][c] = 0.f;
 #pragma unroll
                 for (int s0 = 0; s0 < 16; s0 += 4) {
-                    float2 x[4];
+                    float x[4][CW];
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) x[e] = *reinterpret_cast<const float2*>(RH + (blk * 16 + s0 + e) * ABS + col);
+                    for (int e = 0; e < 4; ++e)
+#pragma unroll
+                        for (int c = 0; c < CW; ++c) x[e][c] = RH[(blk * 16 + s0 + e) * ABS + col + c];
 #pragma unroll
                     for (int rr = 0; rr < 4; ++rr) {
                         const float4 m = *reinterpret_cast<const float4*>(INV + (r0 + 4 * rr) * INVS + s0);
-                        o[rr].x = fmaf(m.x, x[0].x, fmaf(m.y, x[1].x, fmaf(m.z, x[2].x, fmaf(m.w, x[3].x, o[rr].x))));
-                        o[rr].y = fmaf(m.x, x[0].y, fmaf(m.y, x[1].y, fmaf(m.z, x[2].y, fmaf(m.w, x[3].y, o[rr].y))));
+#pragma unroll
+                        for (int c = 0; c < CW; ++c)
+                            o[rr][c] = fmaf(m.x, x[0][c], fmaf(m.y, x[1][c], fmaf(m.z, x[2][c], fmaf(m.w, x[3][c], o[rr][c]))));
                     }
                 }
 #pragma unroll
-                for (int rr = 0; rr < 4; ++rr) *reinterpret_cast<float2*>(UU + (r0 + 4 * rr) * 64 + col) = o[rr];
+                for (int rr = 0; rr < 4; ++rr)
+#pragma unroll
+                    for (int c = 0; c < CW; ++c) UU[(r0 + 4 * rr) * 64 + col + c] = o[rr][c];
                 __syncwarp();
             }
         }
