@@ -189,6 +189,9 @@ def main():
     ap.add_argument("--prefill-chunk", type=int, default=512)
     ap.add_argument("--prefill-scan-chunk", type=int, default=64,
                     help="tile of the tensor-core WKV scan in the prefill sample (0 = sequential scan)")
+    ap.add_argument("--parallelism", default="dp", choices=["dp", "tp"],
+                    help="N > 1: dp = independent sequence batches on full replicas (headline) with the head-sharded "
+                         "tensor-parallel form measured beside it; tp = the head-sharded form as the headline")
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-scan", action="store_true")
@@ -226,68 +229,95 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
         tp_group = dist.group.WORLD
-    # weak scaling: the batch grows with the number of GPUs while heads / projections are sharded
-    B = args.batch * world
-    model, cfg, nq = build_model(args.shape, world, rank, tp_group, dev, args.layers)
-    Lr = cfg.num_hidden_layers
-
-    gen = torch.Generator().manual_seed(0)
-    ids_host = torch.randint(0, V, (steps + warmup + 8, B), generator=gen).pin_memory()
-    cache = model.new_cache(B)
-
-    # kernels of this library launched per decode step (counted on one eager step through the C ABI; the step before
-    # it builds the tiled weight copies, whose one-time repack kernels are not part of a step)
-    model.rwkv7_forward_token(ids_host[0].to(dev), cache, use_graph=False)
-    _lib.LAUNCHES = 0
-    model.rwkv7_forward_token(ids_host[0].to(dev), cache, use_graph=False)
-    launches_per_step = _lib.LAUNCHES
-    graph = model._decode_graph(B)
-    graph.bind(cache)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---------------- device-resident timing (value): graph replays, ids already on the device
-    ids_dev = ids_host.to(dev)
-    for i in range(warmup):
-        graph.ids.copy_(ids_dev[i])
-        graph.graph.replay()
-    barrier()
-    sampler = ClockSampler(local) if rank == 0 else None
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
-    for i in range(steps):
-        graph.ids.copy_(ids_dev[warmup + i])
-        graph.graph.replay()
-    ev1.record()
-    barrier()
-    ms = ev0.elapsed_time(ev1)
-    t = torch.tensor([ms], device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_per_step = float(t.item()) / steps
+    def max_over_ranks(ms):
+        t = torch.tensor([ms], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
 
-    # ---------------- end-to-end through the public API: pinned ids -> H2D -> step -> argmax -> D2H
-    tok_host = torch.empty((B,), dtype=torch.long).pin_memory()
-    for i in range(3):
-        lg = model.rwkv7_forward_token(ids_host[i].to(dev, non_blocking=True), cache)
-        tok_host.copy_(lg.argmax(-1), non_blocking=True)
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(steps):
-        lg = model.rwkv7_forward_token(ids_host[warmup + i].to(dev, non_blocking=True), cache)
-        tok_host.copy_(lg.argmax(-1), non_blocking=True)
-        torch.cuda.current_stream().synchronize()  # the caller consumes the token before the next step
-    e1.record()
-    barrier()
-    t = torch.tensor([e0.elapsed_time(e1)], device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t.item()) / steps
-    clocks = sampler.stop() if sampler else None
+    def time_decode(model, B, seed, clocks_on_rank0):
+        """Device-resident graph replays (-> ms per step), then the end-to-end loop through the public API; both are
+        bracketed by a barrier + synchronize and reduced with MAX over the ranks."""
+        gen = torch.Generator().manual_seed(seed)
+        ids_host = torch.randint(0, V, (steps + warmup + 8, B), generator=gen).pin_memory()
+        cache = model.new_cache(B)
+        # kernels of this library launched per decode step (counted on one eager step through the C ABI; the step
+        # before it builds the tiled weight copies, whose one-time repack kernels are not part of a step)
+        model.rwkv7_forward_token(ids_host[0].to(dev), cache, use_graph=False)
+        _lib.LAUNCHES = 0
+        model.rwkv7_forward_token(ids_host[0].to(dev), cache, use_graph=False)
+        launches = _lib.LAUNCHES
+        graph = model._decode_graph(B)
+        graph.bind(cache)
+        ids_dev = ids_host.to(dev)
+        for i in range(warmup):
+            graph.ids.copy_(ids_dev[i])
+            graph.graph.replay()
+        barrier()
+        sampler = ClockSampler(local) if (clocks_on_rank0 and rank == 0) else None
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for i in range(steps):
+            graph.ids.copy_(ids_dev[warmup + i])
+            graph.graph.replay()
+        ev1.record()
+        barrier()
+        ms_step = max_over_ranks(ev0.elapsed_time(ev1)) / steps
+        # end to end: pinned ids -> H2D -> step -> argmax -> D2H, the caller consuming the token before the next step
+        tok_host = torch.empty((B,), dtype=torch.long).pin_memory()
+        for i in range(3):
+            lg = model.rwkv7_forward_token(ids_host[i].to(dev, non_blocking=True), cache)
+            tok_host.copy_(lg.argmax(-1), non_blocking=True)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            lg = model.rwkv7_forward_token(ids_host[warmup + i].to(dev, non_blocking=True), cache)
+            tok_host.copy_(lg.argmax(-1), non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+        e1.record()
+        barrier()
+        e2e = max_over_ranks(e0.elapsed_time(e1)) / steps
+        return ms_step, e2e, launches, cache, (sampler.stop() if sampler else None), gen
+
+    # ---------------- more than one GPU, head-sharded form: heads, their state and the projections are sharded, the
+    # batch grows with N (B = batch * N on every rank), two NCCL all-reduces per layer.  Measured first and reported
+    # beside the headline, which for N > 1 is the partition without any data-path collective (below).
+    tp_result = None
+    if world > 1 and args.parallelism == "dp":
+        tp_model, tp_cfg, _ = build_model(args.shape, world, rank, tp_group, dev, args.layers)
+        tp_ms, tp_e2e, tp_launch, tp_cache, _, _ = time_decode(tp_model, args.batch * world, 0, False)
+        tp_result = {"value": args.batch * world / (tp_ms * 1e-3), "unit": "tok/s", "ms_per_step": tp_ms,
+                     "e2e_tok_per_s": args.batch * world / (tp_e2e * 1e-3), "global_batch": args.batch * world,
+                     "parallelism": f"tp{world}: heads, state and projections sharded, batch {args.batch * world} on every "
+                                    "rank, two NCCL all-reduces per layer in the decode graph"}
+        tp_model._graphs.clear()
+        del tp_cache, tp_model
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
+
+    # ---------------- headline.  N = 1: the model on one GPU.  N > 1 (default): independent sequence batches -- every
+    # GPU holds a full replica and decodes its own `batch` sequences, no collective on the data path (weak scaling);
+    # --parallelism tp makes the head-sharded form the headline instead.
+    use_tp = world > 1 and args.parallelism == "tp"
+    if use_tp:
+        model, cfg, nq = build_model(args.shape, world, rank, tp_group, dev, args.layers)
+        B, shard = args.batch * world, world
+        parallelism = f"tp{world} (heads + projections sharded, batch {B} on every rank, two NCCL all-reduces per layer)"
+    else:
+        model, cfg, nq = build_model(args.shape, 1, 0, None, dev, args.layers)
+        B, shard = args.batch, 1
+        parallelism = "single GPU" if world == 1 else \
+            f"dp{world}: independent sequence batches, one full replica per GPU, {args.batch} sequences each, no data-path collective"
+    Lr = cfg.num_hidden_layers
+    ms_per_step, e2e_ms, launches_per_step, cache, clocks, gen = time_decode(model, B, 0 if use_tp else rank, True)
+    global_batch = B if use_tp else args.batch * world
 
     def leave():
         """Multi-rank exit.  Tearing the NCCL communicator down while CUDA graphs that captured its all-reduces are
@@ -304,12 +334,10 @@ def main():
         return
 
     hbm_peak, tc_peak, peak_src = measured_peaks()
-    step_bytes, w_bytes, s_bytes = decode_step_bytes(Lr, D, H // world, Fd // world, V, B)
-    if world > 1:  # per-GPU bytes: sharded projections, replicated LoRA-down/head (approximation noted in config)
-        pass
+    step_bytes, w_bytes, s_bytes = decode_step_bytes(Lr, D, H // shard, Fd // shard, V, B)  # per GPU
 
     # ---------------- roofline of the dominant kernel (WKV-7 decode step), timed alone over all layers' states
-    Hl = H // world
+    Hl = H // shard
     N = 64
     f16 = lambda *s: torch.randn(*s, device=dev, dtype=torch.float16)
     r, w_raw, k, v, a, g = (f16(B, Hl * N) for _ in range(6))
@@ -398,16 +426,20 @@ def main():
         cpu_baseline = {k_: cb[k_] for k_ in ("value", "unit", "cores", "kind", "sample")}
 
     line = {
-        "metric": metric, "value": B / (ms_per_step * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": steps,
+        "metric": metric, "value": global_batch / (ms_per_step * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": steps,
         "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f16", "data": "synthetic",
-        "config": {"workload": workload, "global_batch": B, "layers": Lr, "d_model": D, "heads": H, "ffn": Fd, "vocab": V,
-                   "lora_ranks": RANKS, "quantised_modules": nq, "parallelism": f"tp{world} (heads + projections sharded)" if world > 1 else "single GPU",
+        "config": {"workload": workload, "global_batch": global_batch, "batch_per_gpu_step": B, "layers": Lr, "d_model": D, "heads": H, "ffn": Fd, "vocab": V,
+                   "lora_ranks": RANKS, "quantised_modules": nq, "parallelism": parallelism,
                    "l2": "working set per step (weights + state, GBs) exceeds the 126 MB L2; no flush needed",
                    "cuda_graph": True},
-        "e2e": {"value": B / (e2e_ms * 1e-3), "unit": "tok/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": B * 8,
-                "d2h_bytes_per_step": B * 8, "api": "RWKV7ForCausalLM.rwkv7_forward_token + argmax"},
-        "gpu_launches": launches_per_step * steps, "gpu_launches_per_step": launches_per_step,
+        "e2e": {"value": global_batch / (e2e_ms * 1e-3), "unit": "tok/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": global_batch * 8, "d2h_bytes_per_step": global_batch * 8,
+                "api": "RWKV7ForCausalLM.rwkv7_forward_token + argmax"},
+        # kernels of this library launched in the timed region, summed over the GPUs
+        "gpu_launches": launches_per_step * steps * world,
+        "gpu_launches_per_step": launches_per_step,
+        "head_sharded_tp": tp_result,
         "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu_baseline, "prefill": prefill, "wkv_scan": scan,
         **extra,
     }
