@@ -126,7 +126,9 @@ def test_a8w8_linear_against_oracle(M):
 @pytest.mark.parametrize("M,K,Nn", [(1, 128, 8), (5, 512, 128), (16, 1024, 200), (33, 2048, 384), (64, 4096, 512), (64, 16384, 256),
                                     (64, 4096, 4096), (130, 1024, 256), (256, 4096, 512),
                                     # long K ranges per CTA with 128 rows per pass: every ring of that variant wraps
-                                    (128, 2048, 8192), (192, 4096, 4096)])
+                                    (128, 2048, 8192), (192, 4096, 4096),
+                                    # the per-rank shards of an 8-way head-sharded run at batch 512: r/k/v, o, key, value
+                                    (512, 4096, 512), (512, 512, 4096), (512, 4096, 2048), (512, 2048, 4096)])
 def test_w4g_tensor_core_path(M, K, Nn):
     """tcgen05 kernel on the tiled weight copy (fp16, K % 128 == 0, 1..64 rows, any Nout): all epilogues, zero-points,
     group 256, determinism, and no bounded wait ever giving up."""
