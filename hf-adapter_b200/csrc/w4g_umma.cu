@@ -338,7 +338,31 @@ w4g_umma_kernel(const __grid_constant__ W4Maps maps, const W4UmmaArgs p) {
                     tmem_ld16(lane_addr + D_COL + col0, v);
                     if (NISS == 2 && nkb > 1) tmem_ld16(lane_addr + D_COL + NB + col0, v2);  // second issuer's accumulator (unused when it had no work)
                     tc_wait_ld();
-                    if (col0 < m_rows) {
+                    if (!clustered) {
+                        // No split-K: nothing to exchange, so the accumulator goes straight to global memory (fp16
+                        // rounding, epilogue, 2-byte stores: the 32 lanes of a warp cover 64 contiguous bytes of a row).
+                        // The activations arrived after the grid-dependency wait of the producer thread, so the
+                        // preceding kernel has completed; the residual it may have written is read here.
+                        const int nn = n0 + row;
+                        grid_dependency_wait();  // returns at once (see above); keeps the ordering explicit
+                        if (nn < p.Nout) {
+#pragma unroll
+                            for (int e = 0; e < 16; ++e) {
+                                const int m = col0 + e;
+                                if (m >= m_rows) break;
+                                const float a = __uint_as_float(v[e]) + ((NISS == 2 && nkb > 1) ? __uint_as_float(v2[e]) : 0.f);
+                                const size_t o = (size_t)(m0 + m) * p.Nout + nn;
+                                float y = __half2float(__float2half_rn(a));
+                                if (p.epilogue == RWKV7_EPI_RELU2) {
+                                    y = fmaxf(y, 0.f);
+                                    y *= y;
+                                } else if (p.epilogue == RWKV7_EPI_ADD) {
+                                    y += __half2float(p.residual[o]);
+                                }
+                                outp[o] = __float2half_rn(y);
+                            }
+                        }
+                    } else if (col0 < m_rows) {
                         // 16 consecutive rows never straddle two ranks (rows_per_rank is 8, 16, 32 or 64)
 #pragma unroll
                         for (int h8 = 0; h8 < 2; ++h8) {
@@ -368,7 +392,7 @@ w4g_umma_kernel(const __grid_constant__ W4Maps maps, const W4UmmaArgs p) {
     const bool aborted = (*abort_flag != 0);
     grid_dependency_wait();  // residual reads and output writes are ordered after the preceding kernel (returns at once here:
                              // the accumulators already depend on the activations)
-    if (!aborted) {
+    if (!aborted && clustered) {
         // Each thread owns one channel pair (n, n+1) and walks the rows of this rank's share in steps of
         // THREADS/64, four rows per batch: float2 loads of the rank slots in fixed order, fp16 rounding, epilogue,
         // one 4-byte store; 64 consecutive threads cover one 256-byte output row segment.
