@@ -55,7 +55,7 @@ class ClockSampler:
         self.rows, self.proc = [], None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                                          "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
@@ -157,8 +157,11 @@ def run_cpu_baseline(shape, B, steps, warmup, layers_sample=1):
     vf = torch.randn(B, H * 64, generator=g)
     st = [0.1 * torch.randn(B, H, 64, 64, generator=g) for _ in layers]
     times = []
+    t_begin = time.perf_counter()
     with torch.no_grad():
         for it in range(warmup + steps):
+            if len(times) >= 3 and time.perf_counter() - t_begin > 180.0:
+                break  # bounded: the run ends within a few minutes whatever --steps says; `sample` gives the count
             t0 = time.perf_counter()
             y = x
             for i, p in enumerate(layers):
@@ -170,7 +173,7 @@ def run_cpu_baseline(shape, B, steps, warmup, layers_sample=1):
                 times.append(((t1 - t0) * L / layers_sample) + (t2 - t1))
     step_s = sum(times) / len(times)
     return {"value": B / step_s, "unit": "tok/s", "cores": cores, "kind": "port",
-            "sample": f"{layers_sample} of {L} layers + head per step at B={B}, fp32 activations, int4-g128 weights "
+            "sample": f"{len(times)} timed steps of {layers_sample} of {L} layers + head per step at B={B}, fp32 activations, int4-g128 weights "
                       f"dequantised per call as the reference does on CPU; step time extrapolated x{L // layers_sample} for layers",
             "ms_per_step": step_s * 1e3}
 
@@ -179,7 +182,7 @@ def run_cpu_baseline(shape, B, steps, warmup, layers_sample=1):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--shape", default="7.2B", choices=sorted(SHAPES))
@@ -256,11 +259,13 @@ def main():
         graph = model._decode_graph(B)
         graph.bind(cache)
         ids_dev = ids_host.to(dev)
+        # the clock sampler starts before the warm-up replays: nvidia-smi needs a moment before its first sample, and
+        # the GPU is under the same load from here to the end of the end-to-end loop
+        sampler = ClockSampler(local) if (clocks_on_rank0 and rank == 0) else None
         for i in range(warmup):
             graph.ids.copy_(ids_dev[i])
             graph.graph.replay()
         barrier()
-        sampler = ClockSampler(local) if (clocks_on_rank0 and rank == 0) else None
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record()
         for i in range(steps):
