@@ -67,6 +67,9 @@ __global__ void __launch_bounds__(LTHREADS) small_gemm_group_kernel(const GroupA
     __shared__ __align__(128) unsigned char sW[2][LT * 128];
     __shared__ __align__(16) float sP[LT * LT];  // partial tile for the split-K reduction
 
+    // launched programmatically: resident under the tail of the preceding kernel of the stream, everything below after it
+    grid_dependency_wait();
+    if (threadIdx.x == 0) grid_launch_dependents();
     const int prob = blockIdx.y;
     const int K = p.K[prob], Nout = p.Nout[prob];
     const int n0 = (blockIdx.x % p.max_tiles) * LT;
@@ -223,13 +226,15 @@ extern "C" int rwkv7_small_gemm_group(int n_problems, const void* const* x, cons
     cfg.blockDim = dim3(LTHREADS);
     cfg.dynamicSmemBytes = 0;
     cfg.stream = static_cast<cudaStream_t>(stream);
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = splits;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = programmatic_launch_enabled() ? 2 : 1;
     cudaError_t e;
     if (dtype == RWKV7_F16) e = cudaLaunchKernelEx(&cfg, small_gemm_group_kernel<__half>, a);
     else e = cudaLaunchKernelEx(&cfg, small_gemm_group_kernel<__nv_bfloat16>, a);
