@@ -4,8 +4,9 @@ group-128 projections and an fp16 head, random weights, synthetic token ids.
     python bench.py --gpus 1 --steps K --warmup W            # this framework
     python bench.py --impl reference --steps K --warmup W    # CPU baseline arm (host cores)
     torchrun ... bench.py --gpus N ...                       # N>1: head-sharded tensor parallel
+    python bench.py --shape 2.9B --quant w8                  # 2.9B shape, int8 per-output-channel projections
 
-One "step" = one decode token for every sequence of the batch (all 32 layers + head), replayed as a
+One "step" = one decode token for every sequence of the batch (all layers + head), replayed as a
 CUDA graph.  Prints ONE JSON line on rank 0.
 """
 from __future__ import annotations
@@ -29,20 +30,30 @@ SHAPES = {
     "0.1B": (12, 768, 12, 3072, 65536),
 }
 RANKS = dict(decay_low_rank_dim=64, a_low_rank_dim=64, v_low_rank_dim=32, gate_low_rank_dim=128)
+METRIC = "decode tok/s @B=64 + prefill tok/s, 7.2B RWKV-7 MM4; WKV scan % HBM/TC peak"
 
 
-def decode_step_bytes(L, D, H, Fd, V, B, group=128, ranks=(64, 64, 32, 128)):
-    """Algorithmic HBM bytes of one decode step: int4 weights + fp16 group scales, fp16 LoRA and head,
-    fp32 state read+write, shift states read+write."""
+def decode_step_bytes(L, D, H, Fd, V, B, quant="mm4", group=128, ranks=(64, 64, 32, 128), state_bytes=4):
+    """Algorithmic HBM bytes of one decode step: quantised weights + scales, fp16 LoRA and head,
+    recurrent state read+write, shift states read+write."""
     A = H * 64
-    w_int4 = (4 * D * A + 2 * D * Fd) // 2
-    w_scales = (4 * D * A + 2 * D * Fd) // group * 2
+    n_w = 4 * D * A + 2 * D * Fd
+    if quant == "mm4":
+        w_q, w_scales = n_w // 2, n_w // group * 2
+    else:  # int8 per output channel
+        w_q, w_scales = n_w, (4 * A + 2 * Fd) * 2
     rw, ra, rv, rg = ranks
     lora = (rw + ra + rg + rv) * (D + A) * 2
-    weights = L * (w_int4 + w_scales + lora) + V * D * 2
-    state = B * L * H * 64 * 64 * 4 * 2
+    weights = L * (w_q + w_scales + lora) + V * D * 2
+    state = B * L * H * 64 * 64 * state_bytes * 2
     shift = B * L * 2 * D * 2 * 2
     return weights + state + shift, weights, state
+
+
+def w4_launch_bytes(M, K, Nout, n=1):
+    """Algorithmic bytes of one int4 group-128 projection launch: nibbles, fp16 scale + u8 zero-point per group and
+    channel, activations in, outputs out."""
+    return n * (K * Nout // 2 + K * Nout // 128 * 3 + M * (K + Nout) * 2)
 
 
 class ClockSampler:
@@ -83,19 +94,29 @@ class ClockSampler:
 
 
 def measured_peaks():
+    """(HBM GB/s, bf16 TFLOP/s burst, bf16 TFLOP/s sustained, source)."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         with open(path) as f:
             p = json.load(f)
-        return float(p["hbm_gbs"]), float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "measured"
-    return 6650.0, 1590.0, "fallback"
+        burst = float(p["bf16_tflops"])
+        return float(p["hbm_gbs"]), burst, float(p.get("bf16_tflops_sustained", burst)), "measured"
+    return 6650.0, 1590.0, 1400.0, "fallback"
+
+
+def shape_config(shape, quant, batch, layers=0):
+    L, D, H, Fd, V = SHAPES[shape]
+    return {"workload": f"rwkv7-{shape}-shape {'mm4-g128' if quant == 'mm4' else 'int8-per-channel'} decode, batch {batch}, "
+                        "fp16 head, cache resident",
+            "layers": layers or L, "d_model": D, "heads": H, "ffn": Fd, "vocab": V, "lora_ranks": RANKS}
 
 
 # ------------------------------------------------------------------------------------------ model
-def build_model(shape, tp_world, tp_rank, tp_group, device, layers_override=0):
-    """Random-init model of the named shape, projections quantised to int4 group-128 on the GPU, fp16 head.
+def build_model(shape, tp_world, tp_rank, tp_group, device, layers_override=0, quant="mm4", seed=0, full_then_shard=False):
+    """Random-init model of the named shape, projections quantised on the GPU, fp16 head.
     The token-shift / key-scale parameters the reference constructs as zeros are re-initialised (seeded) so
-    that every term of the recurrence is exercised."""
+    that every term of the recurrence is exercised.  ``full_then_shard``: build the unsharded model from the seed
+    on every rank and keep this rank's head shard of it (so that sharded and unsharded runs can be compared)."""
     import torch
 
     import hf_adapter_b200 as hb
@@ -105,41 +126,57 @@ def build_model(shape, tp_world, tp_rank, tp_group, device, layers_override=0):
         L = layers_override
     cfg = hb.NativeRWKV7Config(vocab_size=V, hidden_size=D, num_hidden_layers=L, num_heads=H, head_dim=64,
                                intermediate_size=Fd, **RANKS)
-    torch.manual_seed(0)
-    old = torch.get_default_dtype()
-    torch.set_default_dtype(torch.float16)
-    try:
-        with torch.device(device):
-            model = hb.RWKV7ForCausalLM(cfg, tp_world=tp_world, tp_rank=tp_rank, tp_group=tp_group)
-    finally:
-        torch.set_default_dtype(old)
-    g = torch.Generator(device=device).manual_seed(1 + tp_rank)
-    with torch.no_grad():
-        for name, p in model.named_parameters():
-            if p.dim() == 2 and "embeddings" not in name:
-                p.normal_(0.0, 0.02, generator=g)
-        for i, layer in enumerate(model.model.layers):
-            at = layer.attn
-            for nme in ("x_r", "x_w", "x_k", "x_v", "x_a", "x_g"):
-                getattr(at, nme).uniform_(0, 1, generator=g)
-            layer.ffn.x_k.uniform_(0, 1, generator=g)
-            at.k_k.normal_(0.85, 0.1, generator=g)
-            at.k_a.normal_(1.0, 0.1, generator=g)
-            at.r_k.normal_(0.0, 0.1, generator=g)
-            at.w_lora.lora[2].bias.uniform_(-5, -1, generator=g)
-            at.a_lora.lora[2].bias.normal_(0, 0.5, generator=g)
-            if i:
-                at.v_lora.lora[2].bias.normal_(0, 0.5, generator=g)
-    n = hb.quantize_model(model, "mm4", min_params=1_000_000, group_size=128, skip=("lm_head",))
+
+    def construct(world, rank, group):
+        torch.manual_seed(seed)
+        old = torch.get_default_dtype()
+        torch.set_default_dtype(torch.float16)
+        try:
+            with torch.device(device):
+                return hb.RWKV7ForCausalLM(cfg, tp_world=world, tp_rank=rank, tp_group=group)
+        finally:
+            torch.set_default_dtype(old)
+
+    def init(model, gseed):
+        g = torch.Generator(device=device).manual_seed(gseed)
+        with torch.no_grad():
+            for name, p in model.named_parameters():
+                if p.dim() == 2 and "embeddings" not in name:
+                    p.normal_(0.0, 0.02, generator=g)
+            for i, layer in enumerate(model.model.layers):
+                at = layer.attn
+                for nme in ("x_r", "x_w", "x_k", "x_v", "x_a", "x_g"):
+                    getattr(at, nme).uniform_(0, 1, generator=g)
+                layer.ffn.x_k.uniform_(0, 1, generator=g)
+                at.k_k.normal_(0.85, 0.1, generator=g)
+                at.k_a.normal_(1.0, 0.1, generator=g)
+                at.r_k.normal_(0.0, 0.1, generator=g)
+                at.w_lora.lora[2].bias.uniform_(-5, -1, generator=g)
+                at.a_lora.lora[2].bias.normal_(0, 0.5, generator=g)
+                if i:
+                    at.v_lora.lora[2].bias.normal_(0, 0.5, generator=g)
+
+    if full_then_shard and tp_world > 1:
+        full = construct(1, 0, None)
+        init(full, 1 + seed)
+        sd = hb.shard_state_dict(full.state_dict(), tp_world, tp_rank)
+        model = construct(tp_world, tp_rank, tp_group)
+        model.load_state_dict({k: v.contiguous() for k, v in sd.items()})
+        del full, sd
+    else:
+        model = construct(tp_world, tp_rank, tp_group)
+        init(model, 1 + seed + (0 if full_then_shard else tp_rank))
+    n = hb.quantize_model(model, quant, min_params=1_000_000, group_size=128, skip=("lm_head",))
     torch.cuda.empty_cache()
     return model.eval(), cfg, n
 
 
 # ------------------------------------------------------------------------------------------ reference arm
-def run_cpu_baseline(shape, B, steps, warmup, layers_sample=1):
-    """Times the CPU port of the reference's decode layer on the host cores.  A step = `layers_sample`
-    layers of the model at batch B (plus the head once per step, scaled); the full-model step time is
-    extrapolated as L/layers_sample * t_layers + t_head and says so in `sample`."""
+def run_cpu_baseline(shape, B, steps, warmup, distinct_layers=4, budget_s=170.0):
+    """Times the CPU port of the reference's decode step on the host cores: every step runs ALL L layers and the head
+    at batch B (no extrapolation).  To bound the set-up time the L layer calls cycle over `distinct_layers` distinct
+    weight sets (400 MB of int4 weights: larger than the host caches, so every call streams its weights from memory
+    and dequantises them, as the reference does on CPU); every layer has its own recurrent state."""
     import torch
 
     from oracle import cpu_port_torch as P
@@ -148,33 +185,32 @@ def run_cpu_baseline(shape, B, steps, warmup, layers_sample=1):
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     ranks = (RANKS["decay_low_rank_dim"], RANKS["a_low_rank_dim"], RANKS["v_low_rank_dim"], RANKS["gate_low_rank_dim"])
-    layers = [P.make_layer(D, H, 64, Fd, ranks, layer_id=1 + i, seed=i) for i in range(layers_sample)]
+    sets = [P.make_layer(D, H, 64, Fd, ranks, layer_id=1 + i, seed=i) for i in range(distinct_layers)]
     g = torch.Generator().manual_seed(0)
     head_w = torch.randn(V, D, generator=g) * 0.02
     nw, nb = torch.ones(D), torch.zeros(D)
     x = torch.randn(B, D, generator=g)
     xpa, xpf = torch.randn(B, D, generator=g), torch.randn(B, D, generator=g)
     vf = torch.randn(B, H * 64, generator=g)
-    st = [0.1 * torch.randn(B, H, 64, 64, generator=g) for _ in layers]
+    st = [0.1 * torch.randn(B, H, 64, 64, generator=g) for _ in range(L)]
     times = []
     t_begin = time.perf_counter()
     with torch.no_grad():
         for it in range(warmup + steps):
-            if len(times) >= 3 and time.perf_counter() - t_begin > 180.0:
+            if len(times) >= 3 and time.perf_counter() - t_begin > budget_s:
                 break  # bounded: the run ends within a few minutes whatever --steps says; `sample` gives the count
             t0 = time.perf_counter()
             y = x
-            for i, p in enumerate(layers):
-                y, _, _, _, st[i] = P.layer_step(p, y, xpa, xpf, vf, st[i], H, 64)
-            t1 = time.perf_counter()
+            for i in range(L):
+                y, _, _, _, st[i] = P.layer_step(sets[i % distinct_layers], y, xpa, xpf, vf, st[i], H, 64)
             P.head_step(y, nw, nb, head_w)
-            t2 = time.perf_counter()
             if it >= warmup:
-                times.append(((t1 - t0) * L / layers_sample) + (t2 - t1))
+                times.append(time.perf_counter() - t0)
     step_s = sum(times) / len(times)
-    return {"value": B / step_s, "unit": "tok/s", "cores": cores, "kind": "port",
-            "sample": f"{len(times)} timed steps of {layers_sample} of {L} layers + head per step at B={B}, fp32 activations, int4-g128 weights "
-                      f"dequantised per call as the reference does on CPU; step time extrapolated x{L // layers_sample} for layers",
+    return {"value": B / step_s, "unit": "tok/s", "cores": cores, "kind": "port", "timed_steps": len(times),
+            "sample": f"{len(times)} timed full steps ({L} layers + head) at B={B} after {warmup} warm-up, fp32 activations, int4-g128 "
+                      f"weights dequantised per call as the reference does on CPU; the {L} layer calls cycle over "
+                      f"{distinct_layers} distinct weight sets, every layer has its own state",
             "ms_per_step": step_s * 1e3}
 
 
@@ -186,34 +222,39 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--shape", default="7.2B", choices=sorted(SHAPES))
+    ap.add_argument("--quant", default="mm4", choices=["mm4", "w8"],
+                    help="projection format: mm4 = int4 group-128 (headline), w8 = int8 per output channel (the 2.9B configuration)")
     ap.add_argument("--batch", type=int, default=64, help="sequences per GPU group (global batch = batch for N=1)")
     ap.add_argument("--layers", type=int, default=0, help="debug: override the layer count (invalidates the metric)")
     ap.add_argument("--prefill-tokens", type=int, default=1024)
     ap.add_argument("--prefill-chunk", type=int, default=512)
     ap.add_argument("--prefill-scan-chunk", type=int, default=64,
                     help="tile of the tensor-core WKV scan in the prefill sample (0 = sequential scan)")
-    ap.add_argument("--parallelism", default="dp", choices=["dp", "tp"],
-                    help="N > 1: dp = independent sequence batches on full replicas (headline) with the head-sharded "
-                         "tensor-parallel form measured beside it; tp = the head-sharded form as the headline")
+    ap.add_argument("--parallelism", default="tp", choices=["tp", "dp"],
+                    help="N > 1: tp = head-sharded tensor parallelism (headline; independent replicas measured beside "
+                         "it), dp = independent sequence batches on full replicas as the headline")
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-scan", action="store_true")
+    ap.add_argument("--no-ops", action="store_true", help="skip the isolated projection-operator table")
+    ap.add_argument("--no-b256", action="store_true", help="skip the batch-256 decode measurement")
+    ap.add_argument("--no-side", action="store_true", help="N > 1: skip the side measurements (replicas, strong scaling)")
     args = ap.parse_args()
     steps, warmup = max(1, args.steps), max(3, args.warmup)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     L, D, H, Fd, V = SHAPES[args.shape]
-    metric = "decode tok/s @B=64 + prefill tok/s, 7.2B RWKV-7 MM4; WKV scan % HBM/TC peak"
-    workload = f"rwkv7-{args.shape}-shape mm4-g128 decode, batch {args.batch}, fp16 head, cache resident"
+    base_cfg = shape_config(args.shape, args.quant, args.batch, args.layers)
 
     if args.impl == "reference":
         if rank != 0:
             return
-        cb = run_cpu_baseline(args.shape, args.batch, steps, warmup)
-        line = {"impl": "reference", "metric": metric, "value": cb["value"], "unit": "tok/s", "n_gpus": args.gpus,
-                "steps": steps, "warmup": warmup, "ms_per_step": cb["ms_per_step"], "higher_is_better": True,
+        cb = run_cpu_baseline(args.shape, args.batch, steps, 1)
+        line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "tok/s", "n_gpus": args.gpus,
+                "steps": cb["timed_steps"], "warmup": 1, "ms_per_step": cb["ms_per_step"], "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": {"workload": workload, "note": "reference's CPU path (torch CPU port), host cores"},
+                "config": dict(base_cfg, note="reference's CPU path (torch CPU port) on the host cores; full steps, "
+                                              "bounded to about three minutes"),
                 "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
                 "e2e": {"value": cb["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
         print(json.dumps(line), flush=True)
@@ -224,6 +265,7 @@ def main():
 
     import hf_adapter_b200 as hb
     from hf_adapter_b200 import _lib
+    from hf_adapter_b200 import model as hbm
 
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -244,11 +286,12 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    def time_decode(model, B, seed, clocks_on_rank0):
+    def time_decode(model, B, seed, clocks_on_rank0, n_steps=None, e2e=True):
         """Device-resident graph replays (-> ms per step), then the end-to-end loop through the public API; both are
         bracketed by a barrier + synchronize and reduced with MAX over the ranks."""
+        n_steps = n_steps or steps
         gen = torch.Generator().manual_seed(seed)
-        ids_host = torch.randint(0, V, (steps + warmup + 8, B), generator=gen).pin_memory()
+        ids_host = torch.randint(0, V, (n_steps + warmup + 8, B), generator=gen).pin_memory()
         cache = model.new_cache(B)
         # kernels of this library launched per decode step (counted on one eager step through the C ABI; the step
         # before it builds the tiled weight copies, whose one-time repack kernels are not part of a step)
@@ -268,64 +311,115 @@ def main():
         barrier()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record()
-        for i in range(steps):
+        for i in range(n_steps):
             graph.ids.copy_(ids_dev[warmup + i])
             graph.graph.replay()
         ev1.record()
         barrier()
-        ms_step = max_over_ranks(ev0.elapsed_time(ev1)) / steps
-        # end to end: pinned ids -> H2D -> step -> argmax -> D2H, the caller consuming the token before the next step
-        tok_host = torch.empty((B,), dtype=torch.long).pin_memory()
-        for i in range(3):
-            lg = model.rwkv7_forward_token(ids_host[i].to(dev, non_blocking=True), cache)
-            tok_host.copy_(lg.argmax(-1), non_blocking=True)
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for i in range(steps):
-            lg = model.rwkv7_forward_token(ids_host[warmup + i].to(dev, non_blocking=True), cache)
-            tok_host.copy_(lg.argmax(-1), non_blocking=True)
-            torch.cuda.current_stream().synchronize()
-        e1.record()
-        barrier()
-        e2e = max_over_ranks(e0.elapsed_time(e1)) / steps
-        return ms_step, e2e, launches, cache, (sampler.stop() if sampler else None), gen
+        ms_step = max_over_ranks(ev0.elapsed_time(ev1)) / n_steps
+        e2e_ms = None
+        if e2e:
+            # end to end: pinned ids -> H2D -> step -> argmax -> D2H, the caller consuming the token before the next step
+            tok_host = torch.empty((B,), dtype=torch.long).pin_memory()
+            for i in range(3):
+                lg = model.rwkv7_forward_token(ids_host[i].to(dev, non_blocking=True), cache)
+                tok_host.copy_(lg.argmax(-1), non_blocking=True)
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(n_steps):
+                lg = model.rwkv7_forward_token(ids_host[warmup + i].to(dev, non_blocking=True), cache)
+                tok_host.copy_(lg.argmax(-1), non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+            e1.record()
+            barrier()
+            e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / n_steps
+        return ms_step, e2e_ms, launches, cache, (sampler.stop() if sampler else None), gen
 
-    # ---------------- more than one GPU, head-sharded form: heads, their state and the projections are sharded, the
-    # batch grows with N (B = batch * N on every rank), two NCCL all-reduces per layer.  Measured first and reported
-    # beside the headline, which for N > 1 is the partition without any data-path collective (below).
-    tp_result = None
-    if world > 1 and args.parallelism == "dp":
-        try:
-            tp_model, tp_cfg, _ = build_model(args.shape, world, rank, tp_group, dev, args.layers)
-            tp_ms, tp_e2e, tp_launch, tp_cache, _, _ = time_decode(tp_model, args.batch * world, 0, False)
-            tp_result = {"value": args.batch * world / (tp_ms * 1e-3), "unit": "tok/s", "ms_per_step": tp_ms,
-                         "e2e_tok_per_s": args.batch * world / (tp_e2e * 1e-3), "global_batch": args.batch * world,
-                         "parallelism": f"tp{world}: heads, state and projections sharded, batch {args.batch * world} on "
-                                        "every rank, two NCCL all-reduces per layer in the decode graph"}
-            tp_model._graphs.clear()
-            del tp_cache, tp_model
-        except Exception as exc:  # the headline below does not depend on this measurement
-            tp_result = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+    def drop(model):
+        model._graphs.clear()
         torch.cuda.synchronize()
         torch.cuda.empty_cache()
 
-    # ---------------- headline.  N = 1: the model on one GPU.  N > 1 (default): independent sequence batches -- every
-    # GPU holds a full replica and decodes its own `batch` sequences, no collective on the data path (weak scaling);
-    # --parallelism tp makes the head-sharded form the headline instead.
+    # ---------------- N > 1: parity of the head-sharded form before anything is timed.  Two layers at this shape's
+    # width, the unsharded model built from the same seed on every rank: logits and greedy tokens of the sharded run
+    # (eager and CUDA-graph steps, NCCL all-reduces inside) must match the single-GPU run of the same weights.
+    tp_parity = None
+    if world > 1:
+        try:
+            Bp = 8
+            ref_model, _, _ = build_model(args.shape, 1, 0, None, dev, 2, args.quant, seed=7)
+            tpm, _, _ = build_model(args.shape, world, rank, tp_group, dev, 2, args.quant, seed=7, full_then_shard=True)
+            gen = torch.Generator().manual_seed(11)
+            pids = torch.randint(0, V, (Bp, 6), generator=gen).to(dev)
+            c_ref, c_tp = ref_model.new_cache(Bp), tpm.new_cache(Bp)
+            worst, same_tokens = 1.0, True
+            for t in range(6):
+                lr = ref_model.rwkv7_forward_token(pids[:, t], c_ref, use_graph=False)
+                lt = tpm.rwkv7_forward_token(pids[:, t], c_tp, use_graph=(t >= 3))
+                a, b = lr.double().flatten(), lt.double().flatten()
+                worst = min(worst, float(a @ b / a.norm() / b.norm()))
+                # the sharded run's best logit may differ from the unsharded choice only within fp16 noise
+                top = lr.argmax(-1)
+                same_tokens &= bool(((lt.max(-1).values - lt.gather(1, top[:, None])[:, 0]) < 2e-2).all())
+            s_ref = torch.stack(c_ref._state)[:, :, rank * (H // world):(rank + 1) * (H // world)]
+            s_err = float((torch.stack(c_tp._state) - s_ref).norm() / s_ref.norm())
+            flag = torch.tensor([1.0 if (worst > 0.9995 and same_tokens and s_err < 1e-2) else 0.0], device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            tp_parity = {"status": "ok" if float(flag.item()) == 1.0 else "FAILED", "min_logit_cosine": worst,
+                         "greedy_tokens_match": same_tokens, "state_rel_err": s_err,
+                         "case": f"2 layers at {args.shape} width, batch {Bp}, 6 tokens, eager + graph steps, vs the unsharded model"}
+            drop(tpm)
+            drop(ref_model)
+            del ref_model, tpm, c_ref, c_tp
+        except Exception as exc:
+            tp_parity = {"status": "FAILED", "error": f"{type(exc).__name__}: {exc}"[:300]}
+        torch.cuda.empty_cache()
+
+    # ---------------- N > 1, side measurement: independent sequence batches on full replicas (no collective)
+    replicas = None
     use_tp = world > 1 and args.parallelism == "tp"
+    if world > 1 and not args.no_side:
+        other_tp = not use_tp
+        m2, _, _ = build_model(args.shape, world if other_tp else 1, rank if other_tp else 0, tp_group if other_tp else None,
+                               dev, args.layers, args.quant)
+        B2 = args.batch * world if other_tp else args.batch
+        ms2, _, _, c2, _, _ = time_decode(m2, B2, 0 if other_tp else rank, False, n_steps=min(steps, 20), e2e=False)
+        side = {"value": args.batch * world / (ms2 * 1e-3), "unit": "tok/s", "ms_per_step": ms2, "global_batch": args.batch * world,
+                "parallelism": (f"tp{world}: heads, state and projections sharded, batch {B2} on every rank" if other_tp else
+                                f"dp{world}: independent sequence batches, one full replica per GPU, {args.batch} sequences each, "
+                                "no data-path collective")}
+        replicas = side
+        drop(m2)
+        del m2, c2
+
+    # ---------------- headline.  N = 1: the model on one GPU.  N > 1 (default): head-sharded tensor parallelism --
+    # heads, their state and the projections sharded, a global batch of batch*N on every rank (per-GPU state work
+    # fixed: weak scaling), NCCL all-reduces of the [B,D] partial sums inside the decode graph.
     if use_tp:
-        model, cfg, nq = build_model(args.shape, world, rank, tp_group, dev, args.layers)
+        model, cfg, nq = build_model(args.shape, world, rank, tp_group, dev, args.layers, args.quant)
         B, shard = args.batch * world, world
-        parallelism = f"tp{world} (heads + projections sharded, batch {B} on every rank, two NCCL all-reduces per layer)"
+        parallelism = (f"tp{world}: heads, recurrent state and projections sharded, global batch {B} on every rank, "
+                       "two NCCL all-reduces per layer inside the decode graph")
     else:
-        model, cfg, nq = build_model(args.shape, 1, 0, None, dev, args.layers)
+        model, cfg, nq = build_model(args.shape, 1, 0, None, dev, args.layers, args.quant)
         B, shard = args.batch, 1
         parallelism = "single GPU" if world == 1 else \
             f"dp{world}: independent sequence batches, one full replica per GPU, {args.batch} sequences each, no data-path collective"
     Lr = cfg.num_hidden_layers
     ms_per_step, e2e_ms, launches_per_step, cache, clocks, gen = time_decode(model, B, 0 if use_tp else rank, True)
     global_batch = B if use_tp else args.batch * world
+
+    # ---------------- N > 1: strong scaling of the head-sharded form (the global batch stays 64 and 256)
+    strong = None
+    if use_tp and not args.no_side:
+        strong = {}
+        for Bg in (64, 256):
+            ms_s, _, _, c_s, _, _ = time_decode(model, Bg, 0, False, n_steps=min(steps, 20), e2e=False)
+            strong[f"global_batch_{Bg}"] = {"value": Bg / (ms_s * 1e-3), "unit": "tok/s", "ms_per_step": ms_s}
+            model._graphs.pop(Bg, None)
+            del c_s
+            torch.cuda.empty_cache()
 
     def leave():
         """Multi-rank exit.  Tearing the NCCL communicator down while CUDA graphs that captured its all-reduces are
@@ -341,23 +435,84 @@ def main():
         leave()  # the remaining sections are rank-0 measurements
         return
 
-    hbm_peak, tc_peak, peak_src = measured_peaks()
-    step_bytes, w_bytes, s_bytes = decode_step_bytes(Lr, D, H // shard, Fd // shard, V, B)  # per GPU
-
-    # ---------------- roofline of the dominant kernel (WKV-7 decode step), timed alone over all layers' states
-    Hl = H // shard
+    hbm_peak, tc_burst, tc_sustained, peak_src = measured_peaks()
+    Hl, Fl, A_l = H // shard, Fd // shard, (H // shard) * 64
+    step_bytes, w_bytes, s_bytes = decode_step_bytes(Lr, D, Hl, Fl, V, B, args.quant)  # per GPU
     N = 64
     f16 = lambda *s: torch.randn(*s, device=dev, dtype=torch.float16)
+
+    def time_graph(fn, launches_inside, reps=None):
+        """fn launches `launches_inside` kernels back to back; captured once, replayed, timed with CUDA events on the
+        launching stream -> microseconds per launch."""
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            fn()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        reps = reps or max(3, min(steps, 10))
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(reps):
+            g.replay()
+        t1.record()
+        torch.cuda.synchronize()
+        us = t0.elapsed_time(t1) * 1e3 / (reps * launches_inside)
+        del g
+        return us
+
+    # ---------------- roofline of the dominant kernel: the int4 projections (four launches per layer), each launch shape
+    # timed alone over every layer's own weights (GBs in total: far above the 126 MB L2, so no flush is needed)
+    roofline = None
+    layers = list(model.model.layers)
+    if args.quant == "mm4" and all(isinstance(l.ffn.key, hb.MM4Linear) for l in layers):
+        xr, xk, xv, xf = (f16(B, D) for _ in range(4))
+        xo, xh, xres = f16(B, A_l), f16(B, Fl).abs_(), f16(B, D)
+        per = {}
+
+        def add(name, fn, nbytes):
+            us = time_graph(fn, len(layers))
+            per[name] = {"us_per_launch": us, "bytes_per_launch": nbytes, "achieved_gbs": nbytes / us / 1e3,
+                         "frac": nbytes / us / 1e3 / hbm_peak}
+
+        assert hbm._rkv_grouped(layers[0].attn, xr, xk, xv) is not None, "r/k/v are not served by the grouped int4 launch"
+        add("rkv_grouped", lambda: [hbm._rkv_grouped(l.attn, xr, xk, xv) for l in layers], w4_launch_bytes(B, D, A_l, 3))
+        add("o_proj", lambda: [hbm._linear(l.attn.o_proj, xo) for l in layers], w4_launch_bytes(B, A_l, D))
+        add("ffn_key_relu2", lambda: [hbm._linear(l.ffn.key, xf, relu2=True) for l in layers], w4_launch_bytes(B, D, Fl))
+        add("ffn_value_add", lambda: [hbm._linear(l.ffn.value, xh, residual=xres) for l in layers], w4_launch_bytes(B, Fl, D))
+        tot_b = sum(v["bytes_per_launch"] for v in per.values())
+        tot_us = sum(v["us_per_launch"] for v in per.values())
+        roofline = {"kernel": "w4g_umma64_kernel / w4g_umma_kernel (int4 group-128 projections on tcgen05: the four launches of a layer)",
+                    "bound": "hbm", "achieved": tot_b / tot_us / 1e3, "peak": hbm_peak, "unit": "GB/s",
+                    "frac": tot_b / tot_us / 1e3 / hbm_peak, "peak_source": peak_src + " (burst copy)",
+                    "bytes_per_launch": tot_b / 4, "us_per_launch": tot_us / 4, "launches": per,
+                    "share_of_step": tot_us * 1e-3 * len(layers) / ms_per_step,
+                    # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of the ffn.key launch at B = 64
+                    # (profiles/): 36.4 MB against 37.7 MB algorithmic (activations and outputs stay in L2); the other
+                    # launches stream the same format, so the figure is scaled by the weight bytes of a layer
+                    "traffic": (36.4e6 / w4_launch_bytes(64, 4096, 16384)) * tot_b / 4 if B == 64 else None,
+                    "note": "achieved = algorithmic bytes of the four launches / their CUDA-event time, each shape replayed "
+                            "alone as a graph over all layers' weights; at 64 rows the tensor pipe (N = 64 MMAs) bounds this "
+                            "kernel at about 0.7 of the copy peak"}
+        del xr, xk, xv, xf, xo, xh, xres
+
+    # ---------------- second kernel: the WKV-7 decode recurrence, timed alone over all layers' states
     r, w_raw, k, v, a, g = (f16(B, Hl * N) for _ in range(6))
-    at0 = model.model.layers[1].attn if Lr > 1 else model.model.layers[0].attn
+    at0 = layers[1].attn if Lr > 1 else layers[0].attn
     states = cache._state
+    wkv_out = torch.empty((B, Hl * N), device=dev, dtype=torch.float16)
 
     def wkv_pass():
         for s in states:
             hb.fused_recurrent_output_prepare_raw(r, w_raw, k, v, a, s, g, at0.k_k, at0.k_a, at0.r_k, at0.g_norm.weight,
                                                   at0.g_norm.bias, eps=N * 1e-5, new_state=s, out=wkv_out)
 
-    wkv_out = torch.empty((B, Hl * N), device=dev, dtype=torch.float16)
     for _ in range(3):
         wkv_pass()
     torch.cuda.synchronize()
@@ -371,15 +526,33 @@ def main():
     wkv_ms = k0.elapsed_time(k1) / (reps * len(states))
     wkv_bytes = B * Hl * (2 * N * N * 4 + 7 * N * 2)
     achieved = wkv_bytes / (wkv_ms * 1e-3) / 1e9
-    roofline = {"kernel": "wkv7_step_kernel (decode recurrence + fused epilogues)", "bound": "hbm", "achieved": achieved,
-                "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak, "peak_source": peak_src + " (burst copy)",
-                # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture at B*H = 4096 (profiles/): 87.0 MB per
-                # launch (reads = state in; most of the written state is still dirty in L2 when the kernel ends),
-                # scaled by the sequence-heads of this launch
-                "traffic": 87.0e6 * (B * Hl) / 4096.0, "bytes_per_launch": wkv_bytes, "us_per_launch": wkv_ms * 1e3}
+    roofline_wkv = {"kernel": "wkv7_step_kernel (decode recurrence + fused epilogues)", "bound": "hbm", "achieved": achieved,
+                    "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak, "peak_source": peak_src + " (burst copy)",
+                    # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture at B*H = 4096 (profiles/): 87.0 MB per
+                    # launch (reads = state in; most of the written state is still dirty in L2 when the kernel ends),
+                    # scaled by the sequence-heads of this launch
+                    "traffic": 87.0e6 * (B * Hl) / 4096.0, "bytes_per_launch": wkv_bytes, "us_per_launch": wkv_ms * 1e3,
+                    "share_of_step": wkv_ms * len(states) / ms_per_step}
+    if roofline is None:
+        roofline, roofline_wkv = roofline_wkv, None
 
     extra = {"step_bytes": step_bytes, "step_hbm_frac": step_bytes / (ms_per_step * 1e-3) / 1e9 / hbm_peak,
-             "wkv_share_of_step": wkv_ms * len(states) / ms_per_step}
+             "targets": {"step_hbm_frac": 0.70, "scan_tensor_frac": 0.50,
+                         "note": "north-star targets; step_hbm_frac and wkv_scan.*.tensor_frac_of_bf16_burst_peak are the measured values"}}
+
+    # ---------------- decode at batch 256 (the second batch size of the 7.2B configuration), single GPU
+    b256 = None
+    if not args.no_b256 and world == 1 and args.batch != 256:
+        try:
+            ms256, _, _, c256, _, _ = time_decode(model, 256, 3, False, n_steps=min(steps, 20), e2e=False)
+            sb256 = decode_step_bytes(Lr, D, H, Fd, V, 256, args.quant)[0]
+            b256 = {"value": 256 / (ms256 * 1e-3), "unit": "tok/s", "ms_per_step": ms256, "step_bytes": sb256,
+                    "step_hbm_frac": sb256 / (ms256 * 1e-3) / 1e9 / hbm_peak}
+            model._graphs.pop(256, None)
+            del c256
+        except Exception as exc:
+            b256 = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+        torch.cuda.empty_cache()
 
     # ---------------- prefill tok/s (bounded sample of the 8192-token prompts: the state carries over chunks)
     prefill = None
@@ -424,36 +597,79 @@ def main():
             sbytes = 5 * Bs * Ts * Hs * N * 2 + Bs * Ts * Hs * N * 4 + Bs * Ts * Hs * N * 2 + 2 * Bs * Hs * N * N * 4
             flops = Bs * Ts * Hs * (16 * 64 * N + 8 * N * N + 2 * 64 * 64)  # chunked-form tensor flops, C = 64
             scan[name] = {"ms": sms, "tok_per_s": Bs * Ts / (sms * 1e-3), "hbm_frac": sbytes / (sms * 1e-3) / 1e9 / hbm_peak,
-                          "tensor_frac_of_bf16_peak": flops / (sms * 1e-3) / 1e12 / tc_peak}
+                          # an isolated kernel: against the burst figure of the measured bf16 GEMM peak
+                          "tensor_frac_of_bf16_burst_peak": flops / (sms * 1e-3) / 1e12 / tc_burst}
         del rs, ks, vs, kks, as_, ws
+        torch.cuda.empty_cache()
+
+    # ---------------- isolated projection operators: weights [4096,4096], [16384,4096], [4096,16384]; activation rows
+    # 1, 8, 64 (decode GEMV) over 32 rotated weight buffers, and the int8 tensor-core GEMM at 4096 rows
+    ops = None
+    if not args.no_ops and world == 1:
+        ops = {"gemv": {}, "a8w8_gemm": {}, "note": "GEMV: 32 distinct weight buffers per shape rotated inside one graph replay "
+               "(>= 0.27 GB per shape: above L2); frac = algorithmic bytes / time / measured copy peak.  GEMM: int8 x int8 -> "
+               "int32 on tcgen05 kind::i8; frac against 2 x the measured bf16 burst peak (no measured int8 peak is available)"}
+        nbuf = 32
+        for (Nout, K) in ((4096, 4096), (16384, 4096), (4096, 16384)):
+            tiled = []
+            for _ in range(nbuf):
+                pk = torch.randint(0, 256, (Nout, K // 2), device=dev, dtype=torch.uint8)
+                sc = (torch.rand(Nout, K // 128, device=dev) * 0.01 + 0.002).half()
+                tiled.append(hb.w4_repack_tiled(pk, sc, K, 128))
+                del pk, sc
+            q8 = [torch.randint(-127, 128, (Nout, K), device=dev, dtype=torch.int8) for _ in range(nbuf)]
+            s8 = (torch.rand(Nout, device=dev) * 0.01 + 0.002).half()
+            for M in (1, 8, 64):
+                x = f16(M, K)
+                us4 = time_graph(lambda: [hb.w4_tiled_linear(x, t, Nout, K) for t in tiled], nbuf, reps=5)
+                us8 = time_graph(lambda: [hb.w8_linear(x, q, s8) for q in q8], nbuf, reps=5)
+                b4, b8 = w4_launch_bytes(M, K, Nout), K * Nout + Nout * 2 + M * (K + Nout) * 2
+                ops["gemv"][f"w{Nout}x{K}_m{M}"] = {
+                    "int4_g128_tcgen05": {"us": us4, "gbs": b4 / us4 / 1e3, "frac": b4 / us4 / 1e3 / hbm_peak},
+                    "int8_per_channel": {"us": us8, "gbs": b8 / us8 / 1e3, "frac": b8 / us8 / 1e3 / hbm_peak}}
+            del tiled, q8
+            torch.cuda.empty_cache()
+        for (Mg, K, Nout) in ((4096, 4096, 4096), (4096, 4096, 16384)):
+            qa = torch.randint(-127, 128, (Mg, K), device=dev, dtype=torch.int8)
+            qws = [torch.randint(-127, 128, (Nout, K), device=dev, dtype=torch.int8) for _ in range(4)]
+            us = time_graph(lambda: [hb.int8_mm(qa, qw) for qw in qws], 4, reps=5)
+            tops = 2.0 * Mg * K * Nout / us / 1e6
+            ops["a8w8_gemm"][f"m{Mg}_k{K}_n{Nout}"] = {"us": us, "tops": tops, "frac_of_2x_bf16_burst": tops / (2 * tc_burst)}
+            del qa, qws
         torch.cuda.empty_cache()
 
     cpu_baseline = None
     if not args.no_cpu_baseline and world == 1:
-        cb = run_cpu_baseline(args.shape, args.batch, steps=1, warmup=1)
+        cb = run_cpu_baseline(args.shape, args.batch, steps=3, warmup=1, budget_s=60.0)
         cpu_baseline = {k_: cb[k_] for k_ in ("value", "unit", "cores", "kind", "sample")}
 
     line = {
-        "metric": metric, "value": global_batch / (ms_per_step * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": steps,
+        "metric": METRIC, "value": global_batch / (ms_per_step * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": steps,
         "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f16", "data": "synthetic",
-        "config": {"workload": workload, "global_batch": global_batch, "batch_per_gpu_step": B, "layers": Lr, "d_model": D, "heads": H, "ffn": Fd, "vocab": V,
-                   "lora_ranks": RANKS, "quantised_modules": nq, "parallelism": parallelism,
-                   "l2": "working set per step (weights + state, GBs) exceeds the 126 MB L2; no flush needed",
-                   "cuda_graph": True},
+        "config": dict(base_cfg, global_batch=global_batch, batch_per_gpu_step=B, layers=Lr, quantised_modules=nq,
+                       parallelism=parallelism,
+                       l2="working set per step (weights + state, GBs) exceeds the 126 MB L2; no flush needed",
+                       cuda_graph=True),
         "e2e": {"value": global_batch / (e2e_ms * 1e-3), "unit": "tok/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": global_batch * 8, "d2h_bytes_per_step": global_batch * 8,
                 "api": "RWKV7ForCausalLM.rwkv7_forward_token + argmax"},
         # kernels of this library launched in the timed region, summed over the GPUs
         "gpu_launches": launches_per_step * steps * world,
         "gpu_launches_per_step": launches_per_step,
-        "head_sharded_tp": tp_result,
-        "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu_baseline, "prefill": prefill, "wkv_scan": scan,
+        "tp_parity": tp_parity, "replicas" if use_tp else "head_sharded_tp": replicas, "strong_scaling": strong,
+        "clocks": clocks, "roofline": roofline, "roofline_secondary": roofline_wkv, "cpu_baseline": cpu_baseline,
+        "decode_b256": b256, "prefill": prefill, "wkv_scan": scan, "ops": ops,
         **extra,
     }
     if args.layers:
         line["config"]["INVALID"] = "layer count overridden for debugging"
+    if tp_parity is not None and tp_parity.get("status") != "ok":
+        line["config"]["INVALID"] = "head-sharded parity check failed: " + json.dumps(tp_parity)[:200]
     print(json.dumps(line), flush=True)
+    if tp_parity is not None and tp_parity.get("status") != "ok":
+        sys.stdout.flush()
+        os._exit(3)
     leave()
 
 

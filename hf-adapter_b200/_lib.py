@@ -24,7 +24,6 @@ SIGNATURES = {
     "rwkv7_abi_version": (I, []),
     "rwkv7_last_error": (ctypes.c_char_p, []),
     "rwkv7_kernel_status": (I, [I]),
-    "rwkv7_set_option": (I, [I, I]),
     "rwkv7_relu2": (I, [P, P, ctypes.c_longlong, I, P]),
     "rwkv7_affine_gemv_workspace_bytes": (ctypes.c_int64, [I, I, I]),
     "rwkv7_affine_gemv": (I, [P] * 8 + [ctypes.c_int64, I, I, I, I, I, P]),
@@ -32,13 +31,13 @@ SIGNATURES = {
     "rwkv7_a8w8_relu2_requant": (I, [P] * 6 + [I, I, I, P]),
     "rwkv7_wkv7_update": (I, [P] * 9 + [I, I, I, I, I, P]),
     "rwkv7_wkv7_output_prepare": (I, [P] * 13 + [I, I, I, F, I, I, P]),
-    "rwkv7_wkv7_output_prepare_raw": (I, [P] * 14 + [P, P, I, P, P, P, I, P, I, I, I, F, I, P]),
+    "rwkv7_wkv7_output_prepare_raw": (I, [P] * 14 + [P, P, I, P, P, P, I, P, I, I, I, I, F, I, P]),
     "rwkv7_wkv7_scan": (I, [P] * 13 + [F, I, I, I, I, I, I, P]),
     "rwkv7_wkv7_chunk_scan": (I, [P] * 9 + [I, I, I, I, I, I, I, P]),
     "rwkv7_attn_norm_mix6": (I, [P, P, P, P, PP, PP, I, I, F, I, P]),
     "rwkv7_ffn_add_norm_mix": (I, [P] * 8 + [I, I, F, I, P]),
     "rwkv7_layer_norm": (I, [P] * 4 + [I, I, F, I, P]),
-    "rwkv7_seq_shift_mix": (I, [P, P, PP, PP, P, I, I, I, I, I, P]),
+    "rwkv7_seq_shift_mix": (I, [P, P, PP, PP, P, I, I, I, I, I, I, P]),
     "rwkv7_dense_small": (I, [P] * 4 + [I, I, I, I, I, I, P]),
     "rwkv7_small_gemm_group": (I, [I, PP, PP, PP, PP, ctypes.POINTER(c_int), ctypes.POINTER(c_int), ctypes.POINTER(c_int), I, I, P]),
     "rwkv7_prefill_state_prep": (I, [P] * 12 + [I, I, I, I, I, I, I, P]),
@@ -100,20 +99,3 @@ def ptr_array(ptrs):
 def kernel_status(reset: bool = True) -> int:
     """0 unless a tensor-core kernel's bounded wait gave up since the last reset (synchronises the device)."""
     return int(lib.rwkv7_kernel_status(1 if reset else 0))
-
-
-OPT_STATE_PREFETCH = 1
-
-
-class state_prefetch:
-    """Context manager: inside it the one-token recurrence kernels load their state tile before waiting for the
-    preceding kernel of the stream (``RWKV7_OPT_STATE_PREFETCH``).  Only for call sequences in which that preceding
-    kernel never writes the state, e.g. a decode step (a projection precedes the recurrence)."""
-
-    def __enter__(self):
-        self._prev = int(lib.rwkv7_set_option(OPT_STATE_PREFETCH, 1))
-        return self
-
-    def __exit__(self, *exc):
-        lib.rwkv7_set_option(OPT_STATE_PREFETCH, self._prev)
-        return False

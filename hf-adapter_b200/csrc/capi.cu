@@ -27,17 +27,6 @@ unsigned int* kernel_error_word() {
 }
 }  // namespace rwkv7
 
-namespace rwkv7 {
-static std::atomic<int> g_opt_state_prefetch{0};
-int option_state_prefetch() { return g_opt_state_prefetch.load(std::memory_order_relaxed); }
-}  // namespace rwkv7
-
-extern "C" int rwkv7_set_option(int option, int value) {
-    if (option == RWKV7_OPT_STATE_PREFETCH) return rwkv7::g_opt_state_prefetch.exchange(value != 0);
-    rwkv7::set_error("set_option: unknown option %d", option);
-    return RWKV7_ERR_INVALID;
-}
-
 extern "C" int rwkv7_kernel_status(int reset) {
     unsigned int v = 0;
     cudaError_t e = cudaMemcpyFromSymbol(&v, rwkv7::rwkv7_kernel_error, sizeof(v));

@@ -46,8 +46,6 @@ inline bool programmatic_launch_enabled() {
     return on;
 }
 
-int option_state_prefetch();  // RWKV7_OPT_STATE_PREFETCH (capi.cu)
-
 // Launch with the programmatic-stream-serialization attribute: the kernel may become resident while its predecessor
 // in the stream still runs and must call grid_dependency_wait() before touching anything that kernel writes.
 template <typename... KArgs, typename... Args>

@@ -190,6 +190,7 @@ struct SeqMixArgs {
     void* next_state;
     int T, D, n_mix;
     long long total_vec;
+    bool strict;  // fp16: round the difference and the product separately (the reference's strict_fp16_rounding)
 };
 
 template <typename T>
@@ -212,7 +213,12 @@ __global__ void __launch_bounds__(256) seq_shift_mix_kernel(const SeqMixArgs p) 
             float mx[8], o[8];
             load8(reinterpret_cast<const T*>(p.mix[m]) + c, mx);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) o[e] = x[e] + pv[e] * mx[e];
+            for (int e = 0; e < 8; ++e) {
+                // strict: the difference and the product are each rounded to the storage type (fp32 arithmetic on
+                // 11-bit significands followed by one rounding equals the fp16 instruction: 24 >= 2*11 + 2)
+                if (p.strict) o[e] = __fadd_rn(x[e], round_to<T>(__fmul_rn(round_to<T>(pv[e]), mx[e])));
+                else o[e] = x[e] + pv[e] * mx[e];
+            }
             store8(reinterpret_cast<T*>(p.out[m]) + rowi * D + c, o);
         }
         if (t == p.T - 1 && p.next_state) store8(reinterpret_cast<T*>(p.next_state) + b * D + c, x);
@@ -288,13 +294,14 @@ extern "C" int rwkv7_layer_norm(const void* x, const void* norm_w, const void* n
 }
 
 extern "C" int rwkv7_seq_shift_mix(const void* x, const void* initial_prev, const void* const* mixes,
-                                   void* const* outs, void* next_state, int B, int T, int D, int n_mix, int dtype,
-                                   void* stream) {
+                                   void* const* outs, void* next_state, int B, int T, int D, int n_mix, int strict_rounding,
+                                   int dtype, void* stream) {
     RWKV7_REQUIRE(B > 0 && T > 0 && D > 0, RWKV7_ERR_INVALID, "seq_shift_mix: sizes must be positive");
     RWKV7_REQUIRE(D % 8 == 0, RWKV7_ERR_UNSUPPORTED, "seq_shift_mix: D must be a multiple of 8");
     RWKV7_REQUIRE(n_mix >= 1 && n_mix <= 6, RWKV7_ERR_INVALID, "seq_shift_mix: n_mix must be in 1..6");
     RWKV7_REQUIRE(x && initial_prev && mixes && outs, RWKV7_ERR_INVALID, "seq_shift_mix: null pointer");
-    SeqMixArgs p{x, initial_prev, {}, {}, next_state, T, D, n_mix, (long long)B * T * (D / 8)};
+    RWKV7_REQUIRE(!strict_rounding || dtype == RWKV7_F16, RWKV7_ERR_UNSUPPORTED, "seq_shift_mix: strict rounding is defined for fp16 only");
+    SeqMixArgs p{x, initial_prev, {}, {}, next_state, T, D, n_mix, (long long)B * T * (D / 8), strict_rounding != 0};
     for (int m = 0; m < n_mix; ++m) {
         RWKV7_REQUIRE(mixes[m] && outs[m], RWKV7_ERR_INVALID, "seq_shift_mix: null mix/out pointer %d", m);
         RWKV7_REQUIRE(aligned(mixes[m], 16) && aligned(outs[m], 16), RWKV7_ERR_ALIGN, "seq_shift_mix: unaligned pointer");

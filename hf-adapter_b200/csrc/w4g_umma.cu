@@ -463,6 +463,326 @@ w4g_umma_kernel(const __grid_constant__ W4Maps maps, const W4UmmaArgs p) {
 }
 
 
+// ================================================================ 64 activation rows: self-issuing dequant groups
+// The kernel above hands every dequantised block from a dequant group to a separate MMA-issuer warp and back (two
+// mbarrier hops of 150-200 cycles each per block, two polling issuer threads, six A buffers to cover the round trip)
+// and spends about as many warp instructions on that plumbing as on the dequantisation itself.  This variant for
+// batches up to 64 rows removes the hand-off:
+//
+//   * four dequant groups (four warps each = the 128 tensor-memory lanes); group g owns k-blocks g, g+4, ... of the
+//     CTA's k range, ONE A buffer (64 columns) and ONE accumulator (64 columns) in tensor memory;
+//   * a group loads its block from the weight ring, expands it into 64 registers per thread, waits until the MMAs of
+//     its previous block have completed (they were issued a whole block-time earlier), stores the registers into its
+//     A buffer, meets at a 128-thread named barrier and one of its threads issues the eight MMAs itself; the commit of
+//     those MMAs releases both the A buffer and the activation stage;
+//   * the four accumulators are summed in the epilogue (fixed order), where group g takes activation rows
+//     16 g .. 16 g + 15 of all of them.
+//
+// Rings: weights 8 stages of one block (two per group, released as soon as the block is in registers), activations 8
+// stages (two per group).  A stage always belongs to the same group (ring lengths are multiples of the group count),
+// so every waiter sees every phase of the barriers it waits on.  The split-K exchange buffer aliases the weight ring:
+// a CTA announces the end of its main loop with a cluster-barrier arrive and peers wait for that phase before they
+// push, so nobody writes into a ring that is still being read.
+namespace w4b {
+using namespace w4;
+constexpr int G = 4;                      // dequant groups
+constexpr int NB = 64;                    // activation rows = UMMA N
+constexpr int WST = 8, XST = 8;           // ring lengths (stages)
+constexpr int XATOM = NB * 128, X_BYTES = 2 * XATOM;
+constexpr int NTHREADS = 64 + G * 128;    // warp 0: weight producer, warp 1: activation producer + TMEM owner, then the groups
+constexpr int A_COL = 0, D_COL = G * 64;  // tensor memory: A buffers | accumulators
+constexpr int Q_BYTES = NB * TILE_N * 4;
+constexpr int WRING_BYTES = WST * BLOCK_BYTES;
+static_assert(WST % G == 0 && XST % G == 0, "a stage must always belong to the same group");
+static_assert(Q_BYTES <= WRING_BYTES, "the exchange buffer aliases the weight ring");
+static_assert(D_COL + G * NB <= TMEM_COLS, "tensor memory capacity");
+constexpr size_t SMEM = (size_t)XST * X_BYTES + WRING_BYTES + (2 * XST + 2 * WST + 1) * 8 + 16 + 1024;
+}  // namespace w4b
+
+// Named barrier of one dequant group that also agrees on whether every thread is still healthy.
+__device__ __forceinline__ bool group_barrier_and(int id, bool ok) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.b32 p, %1, 0;\n\t"
+        "barrier.cta.red.and.pred q, %2, 128, p;\n\t"
+        "selp.b32 %0, 1, 0, q;\n\t}"
+        : "=r"(r) : "r"((uint32_t)ok), "r"(id) : "memory");
+    return r != 0;
+}
+
+__global__ void __launch_bounds__(w4b::NTHREADS, 1)
+w4g_umma64_kernel(const __grid_constant__ W4Maps maps, const W4UmmaArgs p) {
+    using namespace w4b;
+    extern __shared__ unsigned char smem_unaligned[];
+    unsigned char* smem = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);
+    unsigned char* xs = smem;                                   // [XST][atom 0 | atom 1]
+    unsigned char* raws = smem + XST * X_BYTES;                 // [WST][nibbles | scales | zeros]
+    float* Q = reinterpret_cast<float*>(raws);                  // split-K exchange (after the main loop)
+    uint64_t* bars = reinterpret_cast<uint64_t*>(raws + WRING_BYTES);
+    uint64_t* full = bars;               // [XST] activation tile landed
+    uint64_t* done = bars + XST;         // [XST] the MMAs that read the tile (and the group's A buffer) completed
+    uint64_t* wfull = done + XST;        // [WST] weight block landed
+    uint64_t* wempty = wfull + WST;      // [WST] the group's four warps hold the block in registers
+    uint64_t* d_full = wempty + WST;     // [1]   every group's last MMA completed
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_full + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const AbortCtx actx{abort_flag, p.error};
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * TILE_N;
+    const int grp_idx = blockIdx.y / p.row_blocks;
+    const CUtensorMap* tm_x = &maps.x[grp_idx];
+    const uint8_t* tw = p.tw[grp_idx];
+    __half* outp = p.out[grp_idx];
+    const int m0 = (blockIdx.y % p.row_blocks) * NB;
+    const int m_rows = min(NB, p.M - m0);
+    const int split = blockIdx.z;
+    const int kb0 = split * p.nkb;
+    const int nkb = p.nkb;
+    const bool clustered = p.splits > 1;
+    const int rows_per_rank = NB / p.splits;
+    const uint8_t* wsrc = tw + ((size_t)blockIdx.x * p.kbt + kb0) * BLOCK_BYTES;
+
+    if (tid == 0) {
+        for (int s = 0; s < XST; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&done[s], 1);
+        }
+        for (int s = 0; s < WST; ++s) {
+            mbar_init(&wfull[s], 1);
+            mbar_init(&wempty[s], 4);
+        }
+        mbar_init(d_full, G);
+        *abort_flag = 0;
+        mbar_fence_init();
+        // the first ring fill does not depend on anything: start it before the tensor-memory allocation
+        const int pre = min(WST, nkb);
+        for (int c = 0; c < pre; ++c) {
+            mbar_expect_tx(&wfull[c], BLOCK_BYTES);
+            bulk_load(raws + c * BLOCK_BYTES, wsrc + (size_t)c * BLOCK_BYTES, BLOCK_BYTES, &wfull[c]);
+        }
+    }
+    if (warp == 1) {
+        if (lane == 0) tma_prefetch_desc(tm_x);
+        __syncwarp();
+        tmem_alloc(tmem_slot, TMEM_COLS);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    cg::cluster_group cluster = cg::this_cluster();
+
+    if (warp == 0) {
+        if (lane == 0) {  // weight stream, one block per copy
+            for (int c = WST; c < nkb; ++c) {
+                const int s = c % WST;
+                if (!mbar_wait(&wempty[s], ((c / WST) - 1) & 1, actx, kErrWaitEmpty)) break;
+                mbar_expect_tx(&wfull[s], BLOCK_BYTES);
+                bulk_load(raws + s * BLOCK_BYTES, wsrc + (size_t)c * BLOCK_BYTES, BLOCK_BYTES, &wfull[s]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {  // activation tiles: the only input the preceding kernel of the stream may still be writing
+            grid_dependency_wait();
+            grid_launch_dependents();
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % XST;
+                if (i >= XST && !mbar_wait(&done[s], ((i / XST) - 1) & 1, actx, kErrWaitEmpty)) break;
+                mbar_expect_tx(&full[s], X_BYTES);
+                tma_load_3d(xs + s * X_BYTES, tm_x, &full[s], 0, m0, (kb0 + i) * 2);
+            }
+        }
+    } else {
+        const int q = warp & 3;                // TMEM lane quarter this warp may access
+        const int g = (warp - 2) >> 2;         // dequant group
+        const int wig = (warp - 2) & 3;        // warp within the group
+        const int row = q * 32 + lane;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+        const uint32_t a_addr = lane_addr + A_COL + g * 64;
+        const uint32_t a_tmem = tmem_base + A_COL + g * 64;
+        const uint32_t d_tmem = tmem_base + D_COL + g * NB;
+        constexpr uint32_t idesc = make_idesc(TILE_N, NB, /*F32*/ 1, /*F16*/ 0, /*F16*/ 0);
+        bool ok = true;
+        for (int i = g; i < nkb; i += G) {
+            const int ws = i % WST, xst = i % XST;
+            const unsigned char* wblk = raws + ws * BLOCK_BYTES;
+            if (lane == 0 && ok) ok = mbar_wait(&wfull[ws], (i / WST) & 1, actx, kErrWaitFull);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            uint4 pk[4];
+            uint32_t sc = 0, zlo = 0, zhi = 0;
+            if (ok) {
+                const unsigned char* rrow = wblk + row * 16;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) pk[c] = *reinterpret_cast<const uint4*>(rrow + c * 2048);
+                const uint32_t s16 = reinterpret_cast<const unsigned short*>(wblk + SC_OFF)[row];
+                const uint32_t z = (wblk + Z_OFF)[row];
+                sc = s16 * 0x00010001u;               // (scale, scale)
+                zlo = z * 0x00010001u + 0x64006400u;  // 1024 + z as fp16: 0x6400 | z
+                zhi = z * 0x00100010u + 0xD400D400u;  // -(64 + z) as fp16: 0xD400 | (z << 4)
+            }
+            __syncwarp();
+            if (lane == 0 && ok) mbar_arrive(&wempty[ws]);
+            uint32_t v[4][16];
+            if (ok) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    dequant_word(pk[c].x, zlo, zhi, sc, v[c] + 0);
+                    dequant_word(pk[c].y, zlo, zhi, sc, v[c] + 4);
+                    dequant_word(pk[c].z, zlo, zhi, sc, v[c] + 8);
+                    dequant_word(pk[c].w, zlo, zhi, sc, v[c] + 12);
+                }
+            }
+            if (i >= G && ok) {  // the MMAs of this group's previous block (A buffer, stage xst - G) completed
+                const int ps = (i - G) % XST;
+                if (lane == 0) ok = mbar_wait(&done[ps], ((i - G) / XST) & 1, actx, kErrWaitAFree);
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+            }
+            if (ok) {
+                tc_fence_after();
+#pragma unroll
+                for (int c = 0; c < 4; ++c) tmem_st16(a_addr + c * 16, v[c]);
+                tc_wait_st();
+                tc_fence_before();
+            }
+            ok = group_barrier_and(1 + g, ok);
+            if (!ok) break;
+            if (wig == ((i / G) & 3)) {  // the issuing warp rotates
+                if (lane == 0) {
+                    ok = mbar_wait(&full[xst], (i / XST) & 1, actx, kErrWaitFull);
+                    if (ok) {
+                        tc_fence_after();
+                        const uint64_t bdesc0 = make_sw128_kmajor_desc(smem_u32(xs + xst * X_BYTES));
+#pragma unroll
+                        for (int j = 0; j < KB / 16; ++j) {
+                            const uint64_t bdesc = bdesc0 + (uint64_t)(((j >> 2) * XATOM + (j & 3) * 32) >> 4);
+                            umma_f16_ts(d_tmem, a_tmem + j * 8, bdesc, idesc, (i == g && j == 0) ? 0u : 1u);
+                        }
+                        tc_commit(&done[xst]);
+                        if (i + G >= nkb) tc_commit(d_full);
+                    }
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+            }
+        }
+        // groups that issued nothing (fewer blocks than groups) or gave up still owe their arrival
+        ok = group_barrier_and(1 + g, ok);
+        if (wig == 0 && lane == 0 && (g >= nkb || !ok)) mbar_arrive(d_full);
+
+        // ---- the main loop of this CTA has released the weight ring: peers may push into the exchange buffer
+        if (clustered) cluster_arrive_release();
+        if (ok && lane == 0) ok = mbar_wait(d_full, 0, actx, kErrWaitDFull);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (clustered) cluster_wait();
+        if (ok && *abort_flag == 0) {
+            tc_fence_after();
+            const int nacc = min(G, nkb);
+            const int col0 = g * 16;  // activation rows of this group in every accumulator
+            uint32_t v[16], t[16];
+            tmem_ld16(lane_addr + D_COL + col0, v);
+            tc_wait_ld();
+            for (int a = 1; a < nacc; ++a) {
+                tmem_ld16(lane_addr + D_COL + a * NB + col0, t);
+                tc_wait_ld();
+#pragma unroll
+                for (int e = 0; e < 16; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) + __uint_as_float(t[e]));
+            }
+            if (!clustered) {
+                const int nn = n0 + row;
+                grid_dependency_wait();  // returns at once (the accumulators already depend on the activations)
+                if (nn < p.Nout) {
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) {
+                        const int m = col0 + e;
+                        if (m >= m_rows) break;
+                        const size_t o = (size_t)(m0 + m) * p.Nout + nn;
+                        float y = __half2float(__float2half_rn(__uint_as_float(v[e])));
+                        if (p.epilogue == RWKV7_EPI_RELU2) {
+                            y = fmaxf(y, 0.f);
+                            y *= y;
+                        } else if (p.epilogue == RWKV7_EPI_ADD) {
+                            y += __half2float(p.residual[o]);
+                        }
+                        outp[o] = __float2half_rn(y);
+                    }
+                }
+            } else if (col0 < m_rows) {
+                // 8 consecutive rows never straddle two ranks (rows_per_rank is 8, 16 or 32)
+#pragma unroll
+                for (int h8 = 0; h8 < 2; ++h8) {
+                    const int m = col0 + h8 * 8;
+                    const int dst = m / rows_per_rank;
+                    float* qd = cluster.map_shared_rank(Q, dst) + ((size_t)split * rows_per_rank + (m - dst * rows_per_rank)) * TILE_N + row;
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) qd[e * TILE_N] = __uint_as_float(v[h8 * 8 + e]);
+                }
+            }
+            tc_fence_before();
+        }
+    }
+    if (warp < 2 && clustered) {  // the producer warps take part in the same cluster-barrier phases
+        cluster_arrive_release();
+        cluster_wait();
+    }
+
+    // ---- split-K reduction (fixed rank order) + epilogue, from this CTA's own shared memory
+    if (clustered) {
+        cluster_arrive_release();
+        cluster_wait();
+    } else {
+        __syncthreads();
+    }
+    const bool aborted = (*abort_flag != 0);
+    grid_dependency_wait();
+    if (!aborted && clustered) {
+        const int m_begin = split * rows_per_rank;
+        const int m_end = min(m_rows, m_begin + rows_per_rank);
+        const int n = (tid & 63) * 2;
+        const bool n_ok = n0 + n < p.Nout;
+        const bool pair = (n0 + n + 1 < p.Nout) && ((p.Nout & 1) == 0);
+        constexpr int RSTEP = NTHREADS / 64;
+        const float* Q0 = Q + n - (size_t)m_begin * TILE_N;
+        const int slot = rows_per_rank * TILE_N;
+        for (int m = m_begin + (tid >> 6); m < m_end && n_ok; m += RSTEP) {
+            const float* qq = Q0 + m * TILE_N;
+            float2 acc = *reinterpret_cast<const float2*>(qq);
+            for (int r = 1; r < p.splits; ++r) {
+                const float2 t2 = *reinterpret_cast<const float2*>(qq + r * slot);
+                acc.x += t2.x;
+                acc.y += t2.y;
+            }
+            const size_t o = (size_t)(m0 + m) * p.Nout + n0 + n;
+            float y0 = __half2float(__float2half_rn(acc.x)), y1 = __half2float(__float2half_rn(acc.y));
+            if (p.epilogue == RWKV7_EPI_RELU2) {
+                y0 = fmaxf(y0, 0.f); y0 *= y0;
+                y1 = fmaxf(y1, 0.f); y1 *= y1;
+            } else if (p.epilogue == RWKV7_EPI_ADD) {
+                if (pair) {
+                    const float2 rr = __half22float2(*reinterpret_cast<const __half2*>(p.residual + o));
+                    y0 += rr.x;
+                    y1 += rr.y;
+                } else {
+                    y0 += __half2float(p.residual[o]);
+                    if (n0 + n + 1 < p.Nout) y1 += __half2float(p.residual[o + 1]);
+                }
+            }
+            if (pair) {
+                *reinterpret_cast<__half2*>(outp + o) = __floats2half2_rn(y0, y1);
+            } else {
+                outp[o] = __float2half_rn(y0);
+                if (n0 + n + 1 < p.Nout) outp[o + 1] = __float2half_rn(y1);
+            }
+        }
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+
 // ---------------------------------------------------------------- repack (load time)
 // reference layout -> tiled layout described at the top of this file
 template <typename T>
@@ -546,14 +866,20 @@ int launch_w4g_umma_tiled(const void* const* xs, const uint8_t* const* tws, cons
     a.row_blocks = row_blocks;
     a.error = kernel_error_word();
     RWKV7_REQUIRE(a.error != nullptr, RWKV7_ERR_CUDA, "w4g_gemv_tiled: cannot resolve the device error word");
-    const size_t smem = NB == 128 ? smem_bytes<128>() : smem_bytes<64>();
-    cudaError_t e = NB == 128
-        ? cudaFuncSetAttribute(w4g_umma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-        : cudaFuncSetAttribute(w4g_umma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    // up to 64 rows: the self-issuing dequant-group kernel; RWKV7_B200_W4G_HANDOFF=1 keeps the hand-off kernel for A/B timing
+    static const bool handoff = [] {
+        const char* v = getenv("RWKV7_B200_W4G_HANDOFF");
+        return v && *v && *v != '0';
+    }();
+    const bool v64 = NB == 64 && !handoff;
+    const size_t smem = v64 ? w4b::SMEM : NB == 128 ? smem_bytes<128>() : smem_bytes<64>();
+    cudaError_t e = v64 ? cudaFuncSetAttribute(w4g_umma64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+        : NB == 128 ? cudaFuncSetAttribute(w4g_umma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                    : cudaFuncSetAttribute(w4g_umma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     RWKV7_REQUIRE(e == cudaSuccess, RWKV7_ERR_CUDA, "w4g_gemv_tiled: %s", cudaGetErrorString(e));
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(tiles, row_blocks * G, splits);
-    cfg.blockDim = dim3(THREADS);
+    cfg.blockDim = dim3(v64 ? w4b::NTHREADS : w4::THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[2];
@@ -566,7 +892,8 @@ int launch_w4g_umma_tiled(const void* const* xs, const uint8_t* const* tws, cons
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = (programmatic_launch_enabled() && !fresh) ? 2 : 1;
-    e = NB == 128 ? cudaLaunchKernelEx(&cfg, w4g_umma_kernel<128>, maps, a) : cudaLaunchKernelEx(&cfg, w4g_umma_kernel<64>, maps, a);
+    e = v64 ? cudaLaunchKernelEx(&cfg, w4g_umma64_kernel, maps, a)
+        : NB == 128 ? cudaLaunchKernelEx(&cfg, w4g_umma_kernel<128>, maps, a) : cudaLaunchKernelEx(&cfg, w4g_umma_kernel<64>, maps, a);
     RWKV7_REQUIRE(e == cudaSuccess, RWKV7_ERR_CUDA, "w4g_gemv_tiled launch: %s", cudaGetErrorString(e));
     return RWKV7_OK;
 }

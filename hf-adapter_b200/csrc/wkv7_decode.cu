@@ -31,7 +31,7 @@ struct StepArgs {
     int a_is_raw, v_gate_is_raw;
     int H;
     float eps;
-    int prefetch_state;  // load the state tile before the grid-dependency wait (RWKV7_OPT_STATE_PREFETCH)
+    int prefetch_state;  // load the state tile before the grid-dependency wait (state_prefetch argument of the raw entry point)
 };
 
 template <typename T, typename TW, int MODE>
@@ -182,7 +182,6 @@ __global__ void __launch_bounds__(kStepThreads, 8) wkv7_step_kernel(const StepAr
 
 template <typename T, typename TW, int MODE>
 static int launch_step(StepArgs p, int B, cudaStream_t st) {
-    p.prefetch_state = option_state_prefetch();
     launch_programmatic(wkv7_step_kernel<T, TW, MODE>, dim3(B * p.H), dim3(kStepThreads), 0, st, p);
     return check_launch("wkv7_step_kernel");
 }
@@ -241,8 +240,8 @@ extern "C" int rwkv7_wkv7_output_prepare_raw(const void* r, const void* w_raw, c
                                              const void* k_k, const void* k_a, const void* r_k, const void* gn_w,
                                              const void* gn_b, void* out, const void* w_bias, const void* a_bias,
                                              int a_is_raw, const void* v_first, const void* v_gate,
-                                             const void* v_gate_bias, int v_gate_is_raw, void* v_out, int B, int H,
-                                             int N, float eps, int dtype, void* stream) {
+                                             const void* v_gate_bias, int v_gate_is_raw, void* v_out, int state_prefetch,
+                                             int B, int H, int N, float eps, int dtype, void* stream) {
     StepArgs p{};
     p.r = r; p.w = w_raw; p.k = k_raw; p.v = v; p.a = a;
     p.state_in = state_in; p.state_out = state_out; p.out = out; p.H = H;
@@ -251,6 +250,7 @@ extern "C" int rwkv7_wkv7_output_prepare_raw(const void* r, const void* w_raw, c
     p.w_bias = w_bias; p.a_bias = a_bias; p.a_is_raw = a_is_raw;
     p.v_first = v_first; p.v_gate = v_gate; p.v_gate_bias = v_gate_bias; p.v_gate_is_raw = v_gate_is_raw;
     p.v_out = v_out;
+    p.prefetch_state = state_prefetch != 0;
     RWKV7_REQUIRE(g && r_k && gn_w && gn_b && k_k && k_a, RWKV7_ERR_INVALID,
                   "wkv7_output_prepare_raw: null tensor pointer");
     RWKV7_REQUIRE((v_first == nullptr) == (v_gate == nullptr), RWKV7_ERR_INVALID,

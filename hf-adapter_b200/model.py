@@ -16,6 +16,7 @@ sums the ``[B,D]`` partial outputs of ``o_proj`` and ``ffn.value`` with an all-r
 """
 from __future__ import annotations
 
+import weakref
 from dataclasses import dataclass
 from types import SimpleNamespace
 
@@ -246,10 +247,10 @@ class RWKV7ForCausalLM(nn.Module):
             for t_ in (xw, xa, xg, xv, w_raw, a_pre, g):
                 t_.record_stream(side)
             # the kernel launched just before the recurrence is a projection: it never writes the state
-            with _lib.state_prefetch():
-                out, _ = _rec.fused_recurrent_output_prepare_raw(
-                    r, w_raw, k, v, a_pre, state[i], g, at.k_k, at.k_a, at.r_k, at.g_norm.weight, at.g_norm.bias,
-                    eps=N * 1e-5, new_state=state[i], w_bias=wl[2].bias, a_bias=al[2].bias, a_is_raw=True, **extra)
+            out, _ = _rec.fused_recurrent_output_prepare_raw(
+                r, w_raw, k, v, a_pre, state[i], g, at.k_k, at.k_a, at.r_k, at.g_norm.weight, at.g_norm.bias,
+                eps=N * 1e-5, new_state=state[i], w_bias=wl[2].bias, a_bias=al[2].bias, a_is_raw=True,
+                state_prefetch=True, **extra)
             attn = self._all_reduce(_linear(at.o_proj, out))
             x, mixed = _nm.fused_ffn_add_norm_mix_decode(x, attn, xpf[i], layer.ffn_norm.weight, layer.ffn_norm.bias, ff.x_k)
             hidden = _linear(ff.key, mixed, relu2=True)
@@ -390,9 +391,13 @@ class RWKV7ForCausalLM(nn.Module):
 class DecodeGraph:
     """Fixed-batch CUDA graph of one decode step with its own static cache buffers.
 
-    Binding protocol of the reference runner (rwkv7_hf/native_graph_runtime.py:633-660): a cache that is
+    Binding protocol of the reference runner (rwkv7_hf/native_graph_runtime.py:618-660): a cache that is
     not yet backed by this runner's buffers is copied in once and then re-pointed at them, so later
-    replays touch no host-side copies."""
+    replays touch no host-side copies.  Only one cache can alias the buffers at a time: when another
+    cache binds, the one bound before gets its own copies of the buffers back and loses its binding
+    (``_detach_bound_cache_if_different`` in the reference), so two caches of the same batch size can be
+    stepped alternately through one graph.  ``replay`` returns a copy of the static logits buffer unless
+    ``copy_logits=False`` (the reference's default is to copy too)."""
 
     def __init__(self, model: RWKV7ForCausalLM, batch: int):
         self.model, self.batch = model, batch
@@ -400,6 +405,7 @@ class DecodeGraph:
         self.ids = torch.zeros((batch,), device=dev, dtype=torch.long)
         self.cache = model.new_cache(batch)
         self.launches = 0
+        self._bound = None  # weak reference to the cache whose tensors are this runner's static buffers
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side):
@@ -411,18 +417,35 @@ class DecodeGraph:
         with torch.cuda.graph(self.graph):
             self.logits = model._decode_step(self.ids, self.cache)
 
-    def bind(self, cache: NativeRWKV7Cache):
-        if cache._graph_owner is self:
+    def _static(self):
+        c = self.cache
+        return c._state + c._xpa + c._xpf + [c._v_first]
+
+    def _detach_bound(self):
+        """Give the cache bound so far its own copies of the static buffers and drop its binding."""
+        old = self._bound() if self._bound is not None else None
+        self._bound = None
+        if old is None or old._graph_owner is not self:
             return
-        for dst, src in zip(self.cache._state + self.cache._xpa + self.cache._xpf + [self.cache._v_first],
-                            cache._state + cache._xpa + cache._xpf + [cache._v_first]):
-            dst.copy_(src)
+        L = len(self.cache._state)
+        own = [t.clone() for t in self._static()]
+        old._state, old._xpa, old._xpf, old._v_first = own[:L], own[L:2 * L], own[2 * L:3 * L], own[3 * L]
+        old._graph_owner = None
+
+    def bind(self, cache: NativeRWKV7Cache):
+        if cache._graph_owner is self and self._bound is not None and self._bound() is cache:
+            return
+        self._detach_bound()
+        for dst, src in zip(self._static(), cache._state + cache._xpa + cache._xpf + [cache._v_first]):
+            if dst.data_ptr() != src.data_ptr():
+                dst.copy_(src)
         cache._state, cache._xpa, cache._xpf, cache._v_first = (
             self.cache._state, self.cache._xpa, self.cache._xpf, self.cache._v_first)
         cache._graph_owner = self
+        self._bound = weakref.ref(cache)
 
-    def replay(self, ids, cache: NativeRWKV7Cache):
+    def replay(self, ids, cache: NativeRWKV7Cache, *, copy_logits: bool = True):
         self.bind(cache)
         self.ids.copy_(ids)
         self.graph.replay()
-        return self.logits
+        return self.logits.clone() if copy_logits else self.logits

@@ -102,7 +102,7 @@ def layer_norm(x, weight, bias, eps: float = 1e-5, out=None):
     return out.reshape(x.shape)
 
 
-def _seq_mix(x, initial_prev, mixes, workspace, name):
+def _seq_mix(x, initial_prev, mixes, workspace, name, strict=False):
     if x.dim() != 3:
         raise ValueError(f"{name}: x must be [batch, tokens, hidden]")
     B, T, D = (int(v) for v in x.shape)
@@ -111,42 +111,49 @@ def _seq_mix(x, initial_prev, mixes, workspace, name):
     require_cuda(x, initial, *flat, what=name)
     same_dtype(x, initial, *flat, what=name)
     src = x.contiguous()
+    if strict and x.dtype != torch.float16:
+        strict = False  # the reference applies strict rounding to fp16 sources only (fused_time_mix.py:448,509)
     n = len(flat)
-    expected = (n, B, T, D)
+    expected = (n, B, T, D) if name == "fused_attn_sequence_shift_mix" else (B, T, D)
     if workspace is not None and tuple(workspace.shape) == expected and workspace.device == x.device \
             and workspace.dtype == x.dtype and workspace.is_contiguous():
         storage = workspace
     else:
         storage = torch.empty(expected, device=x.device, dtype=x.dtype)
     nxt = torch.empty((B, D), device=x.device, dtype=x.dtype)
-    return src, initial, flat, storage, nxt, (B, T, D)
+    return src, initial, flat, storage, nxt, (B, T, D), int(bool(strict))
 
 
 def fused_attn_sequence_shift_mix(x, initial_prev, *mixes, block_size: int = 256, num_warps: int = 4, workspace=None,
                                   strict_fp16_rounding: bool = False):
     """Shift-mix a whole ``[B,T,C]`` sequence.  Returns ``(xr,xw,xk,xv,xa,xg,next_state)``; the six
-    streams share one ``[6,B,T,C]`` allocation in the physical order R,K,V,W,A,G like the reference."""
+    streams share one ``[6,B,T,C]`` allocation in the physical order R,K,V,W,A,G like the reference.
+    ``strict_fp16_rounding=True`` (fp16 sources) rounds the difference, the product and the sum separately, as the
+    reference's strict lowering and eager PyTorch do (rwkv7_hf/fused_time_mix.py:63-134)."""
     if len(mixes) != 6:
         raise ValueError("fused_attn_sequence_shift_mix requires six mix vectors")
-    src, initial, flat, storage, nxt, (B, T, D) = _seq_mix(x, initial_prev, mixes, workspace, "fused_attn_sequence_shift_mix")
+    src, initial, flat, storage, nxt, (B, T, D), strict = _seq_mix(x, initial_prev, mixes, workspace,
+                                                                    "fused_attn_sequence_shift_mix", strict_fp16_rounding)
     slots = storage.unbind(0)
     outs = (slots[0], slots[3], slots[1], slots[2], slots[4], slots[5])
     mp, _k1 = _lib.ptr_array([m.data_ptr() for m in flat])
     op, _k2 = _lib.ptr_array([o.data_ptr() for o in outs])
-    _lib.check(_lib.lib.rwkv7_seq_shift_mix(ptr(src), ptr(initial), mp, op, ptr(nxt), B, T, D, 6, dt_code(src),
+    _lib.check(_lib.lib.rwkv7_seq_shift_mix(ptr(src), ptr(initial), mp, op, ptr(nxt), B, T, D, 6, strict, dt_code(src),
                                             stream_ptr(src)), "fused_attn_sequence_shift_mix")
     return (*outs, nxt)
 
 
-def fused_ffn_sequence_shift_mix(x, initial_prev, mix, *, block_size: int = 256, num_warps: int = 4, workspace=None,
+def fused_ffn_sequence_shift_mix(x, initial_prev, mix, block_size: int = 256, num_warps: int = 4, workspace=None,
                                  strict_fp16_rounding: bool = False):
-    """Single-stream sequence shift-mix for the FFN.  Returns ``(mixed, next_state)``."""
-    src, initial, flat, storage, nxt, (B, T, D) = _seq_mix(x, initial_prev, (mix,), workspace, "fused_ffn_sequence_shift_mix")
+    """Single-stream sequence shift-mix for the FFN (rwkv7_hf/fused_time_mix.py:470; all parameters positional or
+    keyword as there; ``workspace`` is a ``[B,T,C]`` output buffer).  Returns ``(mixed, next_state)``."""
+    src, initial, flat, storage, nxt, (B, T, D), strict = _seq_mix(x, initial_prev, (mix,), workspace,
+                                                                    "fused_ffn_sequence_shift_mix", strict_fp16_rounding)
     mp, _k1 = _lib.ptr_array([flat[0].data_ptr()])
-    op, _k2 = _lib.ptr_array([storage[0].data_ptr()])
-    _lib.check(_lib.lib.rwkv7_seq_shift_mix(ptr(src), ptr(initial), mp, op, ptr(nxt), B, T, D, 1, dt_code(src),
+    op, _k2 = _lib.ptr_array([storage.data_ptr()])
+    _lib.check(_lib.lib.rwkv7_seq_shift_mix(ptr(src), ptr(initial), mp, op, ptr(nxt), B, T, D, 1, strict, dt_code(src),
                                             stream_ptr(src)), "fused_ffn_sequence_shift_mix")
-    return storage[0], nxt
+    return storage, nxt
 
 
 def fused_attn_shift_mix(x, prev, x_r, x_w, x_k, x_v, x_a, x_g, *, block_size: int = 256, force_fallback: bool = False):

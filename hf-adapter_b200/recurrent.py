@@ -118,13 +118,16 @@ def fused_recurrent_output_prepare_raw(r, w_raw, k_raw, v, a, state, g, k_k, k_a
                                        group_norm_bias, *, eps: float, block_n: int = 64, num_warps: int = 8,
                                        force_fallback: bool = False, out=None, new_state=None, w_bias=None,
                                        a_bias=None, a_is_raw: bool = False, v_first=None, v_gate=None,
-                                       v_gate_bias=None, v_gate_is_raw: bool = False, v_out=None):
+                                       v_gate_bias=None, v_gate_is_raw: bool = False, v_out=None,
+                                       state_prefetch: bool = False):
     """Decode recurrence / output prep straight from raw w, k and sigmoid(a).
 
     The keyword arguments after ``force_fallback`` are extensions of this package (the reference
     signature ends there): they fold the LoRA biases, the sigmoid of ``a`` and of the v gate and
     the ``v_first`` interpolation into the same kernel, and allow in-place operation by passing
-    ``new_state=state``."""
+    ``new_state=state``.  ``state_prefetch=True`` lets the kernel load its state tile before it waits for the
+    kernel that precedes it in the stream: only for call sequences in which that kernel never writes ``state``
+    (a decode step, where a projection precedes the recurrence)."""
     no_fallback(force_fallback, "fused_recurrent_output_prepare_raw")
     B, H, N = _state_shape(state)
     if int(block_n) < N:
@@ -152,7 +155,7 @@ def fused_recurrent_output_prepare_raw(r, w_raw, k_raw, v, a, state, g, k_k, k_a
         ptr(r_), ptr(w_), ptr(k_), ptr(v_), ptr(a_), ptr(state_c), ptr(new_state), ptr(g_), ptr(params[0]),
         ptr(params[1]), ptr(params[2]), ptr(params[3]), ptr(params[4]), ptr(out), ptr(opt[0]), ptr(opt[1]),
         int(bool(a_is_raw)), ptr(opt[2]), ptr(opt[3]), ptr(opt[4]), int(bool(v_gate_is_raw)), ptr(v_out),
-        B, H, N, float(eps), dt_code(r_), stream_ptr(r_)), "fused_recurrent_output_prepare_raw")
+        int(bool(state_prefetch)), B, H, N, float(eps), dt_code(r_), stream_ptr(r_)), "fused_recurrent_output_prepare_raw")
     return (out.reshape(B, hidden) if flat else out.reshape(B, H, N)), new_state
 
 
@@ -252,6 +255,8 @@ def self_chunk_rwkv7(r, w_decay, k, v, kk, a_gate, state_native, *, chunk_size: 
     T = int(r.shape[1])
     if chunk_size not in (16, 32, 64) or T % int(chunk_size):
         raise ValueError(f"self_chunk_rwkv7 requires chunk_size in (16, 32, 64) dividing T={T}; got {chunk_size}")
+    if r.dtype != torch.float16:  # the tensor-core kernel is fp16 only; the sequential kernel computes the same scan
+        return _scan("self_chunk_rwkv7", r, w_decay, k, v, kk, a_gate, state_native, 0)
     return _scan("self_chunk_rwkv7", r, w_decay, k, v, kk, a_gate, state_native, 0, chunk=int(chunk_size))
 
 
@@ -264,6 +269,6 @@ def dplr_chunk_scan(r, w, k, v, kk, a, state, *, chunk_size: int = 64, force_fal
         raise ValueError("chunk_size must be positive")
     T = int(r.shape[1])
     if algorithm in ("wy", "lowrank", "cuda_wy") and chunk_size in (16, 32, 64) and T % chunk_size == 0 and T > 0 \
-            and r.dtype in (torch.float16, torch.bfloat16):
+            and r.dtype == torch.float16:  # the tensor-core kernel is fp16 only
         return _scan("dplr_chunk_scan", r, w, k, v, kk, a, state, 0, chunk=int(chunk_size))
     return _scan("dplr_chunk_scan", r, w, k, v, kk, a, state, 0)

@@ -4,8 +4,14 @@
  * Every entry point:
  *   - takes plain device pointers owned by the caller, sizes, and the CUDA stream
  *     (a cudaStream_t passed as void*; NULL = the legacy default stream);
- *   - launches asynchronously on that stream, allocates nothing, keeps no mutable
- *     global state, and can be called from any host thread with the device current;
+ *   - launches asynchronously on that stream, allocates nothing, and can be called from
+ *     any host thread with the device current.  What the library keeps between calls:
+ *     a thread-local error string; one device-side error word per GPU (set by a
+ *     tensor-core kernel whose bounded wait gave up, read by rwkv7_kernel_status) and
+ *     its cached address; the set of tiled int4 buffers written by rwkv7_w4g_repack
+ *     and not yet read by a projection (mutex-protected); the cached address of the
+ *     static scratch of rwkv7_a8w8_linear_static.  No option or mode is process-wide:
+ *     everything that changes what a launch does is an argument of the call;
  *   - returns RWKV7_OK or a negative RWKV7_ERR_* code and never aborts;
  *     rwkv7_last_error() returns a thread-local message for the last failure.
  *
@@ -52,15 +58,6 @@ const char* rwkv7_last_error(void);
  * ever gave up; > 0 = code; < 0 = RWKV7_ERR_*) and clears it when reset != 0.  No counterpart in the reference. */
 int rwkv7_kernel_status(int reset);
 
-/* Process-wide launch options.  Returns the previous value (or RWKV7_ERR_INVALID for an unknown option).
- *   RWKV7_OPT_STATE_PREFETCH (default 0): the one-token recurrence kernels load the state tile BEFORE waiting for
- *   the kernel that precedes them in the stream (they are launched programmatically, under its tail).  Set it only
- *   while that preceding kernel never writes the state passed in -- true inside a decode step, where a projection
- *   precedes the recurrence; false for back-to-back recurrence calls that feed each other's state.
- * No counterpart in the reference. */
-#define RWKV7_OPT_STATE_PREFETCH 1
-int rwkv7_set_option(int option, int value);
-
 /* ------------------------------------------------------------------ WKV-7 recurrence, one token
  * Replaces fused_recurrent_update (rwkv7_hf/fused_recurrent_update.py:1214),
  * fused_recurrent_output_prepare (:967) and fused_recurrent_output_prepare_raw (:1089).
@@ -90,6 +87,10 @@ int rwkv7_wkv7_output_prepare(const void* r, const void* w, const void* k, const
  *   a_bias  [H*64] + a_is_raw : a = sigmoid(a + a_bias)  (a_lora up bias "a0")
  *   v_first [B,H*64], v_gate [B,H*64] (+v_gate_bias, v_gate_is_raw): v = v + (v_first - v)*gate
  *   v_out   [B,H*64] : receives the v actually used (layer 0 stores it as v_first)
+ * state_prefetch != 0: the kernel (launched programmatically, under the tail of the kernel that precedes it in the
+ * stream) loads its state tile BEFORE waiting for that kernel.  Pass it only when the preceding kernel never writes
+ * state_in -- true inside a decode step, where a projection precedes the recurrence; false for back-to-back
+ * recurrence calls that feed each other's state.
  */
 int rwkv7_wkv7_output_prepare_raw(const void* r, const void* w_raw, const void* k_raw, const void* v, const void* a,
                                   const float* state_in, float* state_out, const void* g,
@@ -97,7 +98,7 @@ int rwkv7_wkv7_output_prepare_raw(const void* r, const void* w_raw, const void* 
                                   const void* gn_w, const void* gn_b, void* out,
                                   const void* w_bias, const void* a_bias, int a_is_raw,
                                   const void* v_first, const void* v_gate, const void* v_gate_bias, int v_gate_is_raw,
-                                  void* v_out,
+                                  void* v_out, int state_prefetch,
                                   int B, int H, int N, float eps, int dtype, void* stream);
 
 /* ------------------------------------------------------------------ WKV-7 scan over T tokens
@@ -113,7 +114,8 @@ int rwkv7_wkv7_scan(const void* r, const void* w, const void* k, const void* v, 
                     int B, int T, int H, int N, int dtype, int w_mode, void* stream);
 
 /* Chunked (WY / DPLR) form of the same scan with the intra-chunk products on tensor cores.
- * chunk in {16, 32, 64}; T % chunk == 0; fp16 or bf16 activations.  Same arguments as above. */
+ * chunk in {16, 32, 64}; T % chunk == 0; fp16 activations only (RWKV7_ERR_UNSUPPORTED otherwise: callers route
+ * other dtypes to rwkv7_wkv7_scan, which computes the same recurrence).  Same arguments as above. */
 int rwkv7_wkv7_chunk_scan(const void* r, const void* w, const void* k, const void* v, const void* kk, const void* a,
                           const float* state_in, float* state_out, void* y,
                           int B, int T, int H, int N, int chunk, int dtype, int w_mode, void* stream);
@@ -139,9 +141,13 @@ int rwkv7_layer_norm(const void* x, const void* norm_w, const void* norm_b, void
 
 /* Replaces fused_attn_sequence_shift_mix / fused_ffn_sequence_shift_mix (rwkv7_hf/fused_time_mix.py:413,470):
  * x [B,T,D] (already normalised), prev_t = x_{t-1} (initial_prev for t = 0), out_m = x + (prev-x)*mix_m for
- * n_mix in {1,6} mixes; next_state [B,D] = x[:, T-1]. */
+ * n_mix in {1,6} mixes; next_state [B,D] = x[:, T-1].  strict_rounding != 0 (fp16 only) reproduces the reference's
+ * strict_fp16_rounding=True lowering (:63-134): delta = fp16(prev - x), product = fp16(delta * mix),
+ * out = fp16(x + product), three separately rounded fp16 operations like eager PyTorch; 0 = one fp32 expression
+ * rounded once at the store. */
 int rwkv7_seq_shift_mix(const void* x, const void* initial_prev, const void* const* mixes, void* const* outs,
-                        void* next_state, int B, int T, int D, int n_mix, int dtype, void* stream);
+                        void* next_state, int B, int T, int D, int n_mix, int strict_rounding, int dtype,
+                        void* stream);
 
 /* ------------------------------------------------------------------ LoRA group
  * Replaces fused_wa_lora / fused_wag_lora / fused_wavg_lora (rwkv7_hf/fused_lora.py:409,559,706) as a

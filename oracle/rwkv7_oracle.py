@@ -550,8 +550,10 @@ def mm4_matmul(x, packed, mx, rx_s, my, ry_s, m_orig, hi=False):
 
 def a8w8_ffn(x, up_q_t, up_s, down_q_t, down_s, residual, up_bias=None, down_bias=None):
     """rwkv7_hf/native_quant_a8w8.py:436-524: up GEMM, relu^2 + requantise at the boundary, down GEMM + residual.
-    The reference path for this function is GPU-only (Triton + torch._int_mm): this restatement follows its kernels
-    line by line but is not checked against a reference output (parity unpinned for this one function)."""
+    The reference's fused path is GPU-only (Triton + torch._int_mm); this restatement follows its kernels line by
+    line and is pinned against the reference's own CPU composition of the same FFN (a8w8_linear -> relu^2 ->
+    a8w8_linear + residual on the dequantised weights, fixture a8w8_ffn.npz) at the reference's gate for the A8
+    approximation, cosine >= 0.999 (tests/test_native_quant_a8w8.py:63,92)."""
     qa, sa = dynamic_a8_quant(x)
     acc = int8_gemm_i32(qa, up_q_t)
     pre = acc.astype(np.float32) * sa[:, None] * np.asarray(up_s, np.float32)[None, :]

@@ -6,8 +6,8 @@ runs on CPU):
 
     python tests/golden/make_golden.py --reference /path/to/hf-adapter
 
-Outputs ``ops_fp32.npz``, ``ops_fp16.npz``, ``quant.npz`` and
-``model_tiny.npz`` next to this script.  The fixtures hold the seeded inputs
+Outputs ``ops_fp32.npz``, ``ops_fp16.npz``, ``quant.npz``, ``model_tiny.npz``,
+``config1.npz`` and ``a8w8_ffn.npz`` next to this script (``--only`` selects a subset).  The fixtures hold the seeded inputs
 AND the reference's outputs, so the parity tests never need the reference at
 run time.  All shapes are small (N=64 heads, a few rows) to keep every file
 well under a megabyte.
@@ -264,19 +264,98 @@ def gen_model(seed):
     return {k_: npy(v_) for k_, v_ in out.items()}
 
 
+def gen_config1(seed, weight_seed):
+    """The 0.1B-shape model (12 layers, d_model 768, 12 heads of 64, FFN 3072, vocabulary 65536, LoRA ranks
+    64/64/32/128) in fp32 on the reference's CPU path: a 512-token random prompt through ``forward`` (eager prefill),
+    then 128 greedy steps through the cached decode.  The weights come from ``seeded_weights.seeded_state_dict``
+    (``weight_seed``: chosen among a few so that no greedy step is a near-tie between its two best logits) and are
+    not stored; the fixture keeps their checksum, the prompt, the last-token logits, the greedy tokens with the
+    top-1 / top-2 logit gap of every step, and norms of the final cache."""
+    from rwkv7_hf import NativeRWKV7Config, NativeRWKV7ForCausalLM
+    sys.path.insert(0, HERE)
+    from seeded_weights import checksum, seeded_state_dict
+
+    cfg = NativeRWKV7Config(vocab_size=65536, hidden_size=768, num_hidden_layers=12, num_heads=12, head_dim=64,
+                            intermediate_size=3072, decay_low_rank_dim=64, a_low_rank_dim=64, v_low_rank_dim=32,
+                            gate_low_rank_dim=128)
+    torch.manual_seed(seed)
+    model = NativeRWKV7ForCausalLM(cfg).eval().float()
+    sd = seeded_state_dict({k: v.shape for k, v in model.state_dict().items()}, weight_seed)
+    model.load_state_dict(sd)
+    g = torch.Generator().manual_seed(seed)
+    ids = torch.randint(0, 65536, (1, 512), generator=g)
+    out = dict(ids=ids, weight_seed=np.int64(weight_seed), weights_checksum=checksum(sd))
+    with torch.no_grad():
+        o = model(ids, use_cache=True, logits_to_keep=1)
+        logits = o.logits[:, -1]
+        cache = o.past_key_values
+        out["prefill_logits"] = logits
+        toks, gaps, tops = [], [], []
+        for _ in range(128):
+            top2 = logits.topk(2, dim=-1)
+            tok = top2.indices[:, 0]
+            toks.append(tok)
+            tops.append(top2.values[:, 0])
+            gaps.append(top2.values[:, 0] - top2.values[:, 1])
+            o = model(tok[:, None], past_key_values=cache, use_cache=True)
+            logits, cache = o.logits[:, -1], o.past_key_values
+        state, xpa, xpf, v_first = tuple(cache)[:4]
+        out.update(greedy=torch.stack(toks, 1), top1=torch.stack(tops, 1), top2_gap=torch.stack(gaps, 1),
+                   final_logits=logits,
+                   final_state_norm=torch.stack([s.double().norm() for s in state]),
+                   final_xpa_norm=torch.stack([s.double().norm() for s in xpa]),
+                   final_xpf_norm=torch.stack([s.double().norm() for s in xpf]),
+                   final_state_l11_h0=state[-1][0, 0], final_v_first=v_first)
+    return {k_: npy(v_) for k_, v_ in out.items()}
+
+
+def gen_a8w8_ffn(seed):
+    """The reference's A8W8 FFN pair on its CPU route: ``a8w8_linear`` falls back to the dequantised dense weight off
+    CUDA (rwkv7_hf/native_quant_a8w8.py:345-351), so up -> relu^2 (fp16) -> down + residual here is the weight-only
+    composition that the fused GPU path approximates; the reference gates the two at cosine >= 0.999
+    (tests/test_native_quant_a8w8.py:63,92)."""
+    from rwkv7_hf import native_quant_a8w8 as a8
+
+    g = torch.Generator().manual_seed(seed)
+    M, D, Fi = 19, 128, 512
+    x = torch.randn(M, D, generator=g).half()
+    res = torch.randn(M, D, generator=g).half()
+    Wu = (0.05 * torch.randn(Fi, D, generator=g)).half()
+    Wd = (0.05 * torch.randn(D, Fi, generator=g)).half()
+    qu, su = a8.quantize_weight_per_channel_int8(Wu)
+    qd, sd_ = a8.quantize_weight_per_channel_int8(Wd)
+    h = a8.a8w8_linear(x, qu, su)
+    h = torch.relu(h) ** 2
+    y = a8.a8w8_linear(h, qd, sd_) + res
+    return {k_: npy(v_) for k_, v_ in dict(x=x, res=res, Wu=Wu, Wd=Wd, su=su, sd=sd_, hidden=h, y=y).items()}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of the hf-adapter checkout")
+    ap.add_argument("--only", default="", help="comma-separated subset of: ops,quant,model_tiny,config1,a8w8_ffn")
+    ap.add_argument("--config1-weight-seed", type=int, default=3)
+    ap.add_argument("--out", default=HERE, help="output folder (default: next to this script)")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     torch.set_num_threads(4)
-    np.savez_compressed(os.path.join(HERE, "ops_fp32.npz"), **gen_ops(torch.float32, 7007))
-    np.savez_compressed(os.path.join(HERE, "ops_fp16.npz"), **gen_ops(torch.float16, 7008))
-    np.savez_compressed(os.path.join(HERE, "quant.npz"), **gen_quant(11))
-    np.savez_compressed(os.path.join(HERE, "model_tiny.npz"), **gen_model(0))
-    for f in sorted(os.listdir(HERE)):
+    only = {s for s in args.only.split(",") if s}
+    want = lambda name: not only or name in only
+    save = lambda name, d: np.savez_compressed(os.path.join(args.out, name), **d)
+    if want("ops"):
+        save("ops_fp32.npz", gen_ops(torch.float32, 7007))
+        save("ops_fp16.npz", gen_ops(torch.float16, 7008))
+    if want("quant"):
+        save("quant.npz", gen_quant(11))
+    if want("model_tiny"):
+        save("model_tiny.npz", gen_model(0))
+    if want("config1"):
+        save("config1.npz", gen_config1(0, args.config1_weight_seed))
+    if want("a8w8_ffn"):
+        save("a8w8_ffn.npz", gen_a8w8_ffn(21))
+    for f in sorted(os.listdir(args.out)):
         if f.endswith(".npz"):
-            print(f, os.path.getsize(os.path.join(HERE, f)))
+            print(f, os.path.getsize(os.path.join(args.out, f)))
 
 
 if __name__ == "__main__":

@@ -164,3 +164,44 @@ def test_full_width_layers_size_independent_properties():
     sa, sb = npf(torch.stack(cp._state)), npf(torch.stack(c_eager._state))
     assert np.linalg.norm(sa - sb) / np.linalg.norm(sb) < 1e-2
     assert torch.isfinite(le).all() and float(le.float().std()) > 0
+
+
+def test_two_caches_share_one_decode_graph():
+    """Two caches of equal batch size stepped alternately through the same CUDA graph (the graph is keyed by batch size
+    only): each must see its own state, a clone of a bound cache must not disturb the original, and logits returned at
+    step t must survive step t+1.  Checked against eager decoding and the reference's greedy tokens."""
+    g = golden("model_tiny.npz")
+    model = load_tiny(g)
+    ids = cu(g["ids"])
+    B, T = ids.shape
+    ids_b = torch.flip(ids, dims=[1])  # a second, different prompt
+    # eager truth for both prompts
+    eager = []
+    for prompt in (ids, ids_b):
+        c = model.new_cache(B)
+        rows = [model.rwkv7_forward_token(prompt[:, t], c, use_graph=False).clone() for t in range(T)]
+        eager.append((rows, c))
+    ca, cb = model.new_cache(B), model.new_cache(B)
+    kept = []
+    for t in range(T):
+        la = model.rwkv7_forward_token(ids[:, t], ca, use_graph=True)
+        lb = model.rwkv7_forward_token(ids_b[:, t], cb, use_graph=True)
+        kept.append((la, lb))
+    for t, (la, lb) in enumerate(kept):  # logits of earlier steps were not overwritten by later replays
+        np.testing.assert_allclose(npf(la), npf(eager[0][0][t]), rtol=1e-5, atol=1e-5)
+        np.testing.assert_allclose(npf(lb), npf(eager[1][0][t]), rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(npf(kept[-1][0]), g["prefill_logits"], rtol=3e-4, atol=3e-4)
+    for c, (_, ce) in ((ca, eager[0]), (cb, eager[1])):
+        np.testing.assert_allclose(npf(torch.stack(c._state)), npf(torch.stack(ce._state)), rtol=1e-5, atol=1e-6)
+    # greedy continuation of the first prompt from a CLONE of the bound cache, then from the original: same tokens as
+    # the reference, and the clone's replays leave the original's state alone
+    def greedy(cache, first):
+        toks, tok = [], first
+        for _ in range(4):
+            toks.append(tok)
+            tok = model.rwkv7_forward_token(tok, cache, use_graph=True).argmax(-1)
+        return torch.stack(toks, 1).cpu().numpy()
+    first = kept[-1][0].argmax(-1)
+    cc = ca.clone()
+    assert np.array_equal(greedy(cc, first), g["greedy"])
+    assert np.array_equal(greedy(ca, first), g["greedy"])

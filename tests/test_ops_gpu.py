@@ -74,8 +74,7 @@ def test_step_against_oracle_and_inplace(B, Hh):
 def test_back_to_back_steps_feed_each_other():
     """Twelve one-token updates launched back to back, each reading the state the previous launch wrote in place
     (the kernels are launched programmatically: a launch must wait for its predecessor before it loads the state),
-    against the oracle's sequential scan; and the state-prefetch option is scoped to its context manager."""
-    from hf_adapter_b200 import _lib
+    against the oracle's sequential scan."""
     B, T, Hh = 64, 12, 32
     r, w, k, v, kk, a = wkv_inputs(B, T, Hh, N, seed=77)
     state = (0.3 * np.random.default_rng(6).standard_normal((B, Hh, N, N))).astype(np.float32)
@@ -86,11 +85,6 @@ def test_back_to_back_steps_feed_each_other():
     outs = [hb.fused_recurrent_update(*steps[t], st, new_state=st)[0] for t in range(T)]
     np.testing.assert_allclose(npf(st), so, rtol=1e-4, atol=1e-4)
     np.testing.assert_allclose(npf(torch.stack(outs, 1)), yo.astype(np.float32), rtol=4e-3, atol=4e-3)
-    assert int(_lib.lib.rwkv7_set_option(_lib.OPT_STATE_PREFETCH, 0)) == 0
-    with _lib.state_prefetch():
-        assert int(_lib.lib.rwkv7_set_option(_lib.OPT_STATE_PREFETCH, 1)) == 1
-    assert int(_lib.lib.rwkv7_set_option(_lib.OPT_STATE_PREFETCH, 0)) == 0
-    assert int(_lib.lib.rwkv7_set_option(99, 1)) == _lib.ERR_INVALID
 
 
 def test_step_fused_lora_epilogues():
