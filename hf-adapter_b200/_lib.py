@@ -10,7 +10,8 @@ import os
 from ctypes import c_float, c_int, c_int64, c_void_p
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "librwkv7_b200.so")
+# RWKV7_B200_LIB selects another build of the same library (e.g. one compiled with different tuning macros)
+LIB_PATH = os.environ.get("RWKV7_B200_LIB") or os.path.join(_HERE, "librwkv7_b200.so")
 
 OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_ALIGN, ERR_CUDA, ERR_WORKSPACE = 0, -1, -2, -3, -4, -5
 F16, BF16, F32 = 0, 1, 2

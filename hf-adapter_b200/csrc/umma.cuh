@@ -60,11 +60,25 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
+// Non-blocking test of a phase.  On a phase that has already completed this returns in about 20 cycles, while
+// try_wait with a suspend-time hint takes 50 (175 when one lane polls and the warp then reconverges on a shuffle),
+// measured on one idle SM: every wait below tests first and only parks when the phase is still open.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
 constexpr uint32_t kSuspendNs = 20000;            // per try_wait
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // a wait gives up after two seconds
 
 // Bounded wait.  Returns false (and raises the CTA abort flag) if the phase never completes.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const AbortCtx& ctx, unsigned code) {
+    if (mbar_test_wait(bar, parity)) return true;
+    if (*ctx.flag) return false;  // the CTA is already giving up: do not park
     if (mbar_try_wait(bar, parity, kSuspendNs)) return true;
     const uint64_t t0 = global_timer_ns();
     for (;;) {
