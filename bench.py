@@ -56,6 +56,11 @@ def w4_launch_bytes(M, K, Nout, n=1):
     return n * (K * Nout // 2 + K * Nout // 128 * 3 + M * (K + Nout) * 2)
 
 
+def w8_launch_bytes(M, K, Nout, n=1):
+    """The same for int8 weights with one fp16 scale per output channel."""
+    return n * (K * Nout + Nout * 2 + M * (K + Nout) * 2)
+
+
 class ClockSampler:
     """nvidia-smi clock / throttle sampling during the timed region."""
 
@@ -471,7 +476,8 @@ def main():
     # timed alone over every layer's own weights (GBs in total: far above the 126 MB L2, so no flush is needed)
     roofline = None
     layers = list(model.model.layers)
-    if args.quant == "mm4" and all(isinstance(l.ffn.key, hb.MM4Linear) for l in layers):
+    launch_bytes = w4_launch_bytes if args.quant == "mm4" else w8_launch_bytes
+    if all(isinstance(l.ffn.key, (hb.MM4Linear, hb.MM8Linear)) and l.ffn.key.tiled_for(f16(B, D)) is not None for l in layers):
         xr, xk, xv, xf = (f16(B, D) for _ in range(4))
         xo, xh, xres = f16(B, A_l), f16(B, Fl).abs_(), f16(B, D)
         per = {}
@@ -481,25 +487,26 @@ def main():
             per[name] = {"us_per_launch": us, "bytes_per_launch": nbytes, "achieved_gbs": nbytes / us / 1e3,
                          "frac": nbytes / us / 1e3 / hbm_peak}
 
-        assert hbm._rkv_grouped(layers[0].attn, xr, xk, xv) is not None, "r/k/v are not served by the grouped int4 launch"
-        add("rkv_grouped", lambda: [hbm._rkv_grouped(l.attn, xr, xk, xv) for l in layers], w4_launch_bytes(B, D, A_l, 3))
-        add("o_proj", lambda: [hbm._linear(l.attn.o_proj, xo) for l in layers], w4_launch_bytes(B, A_l, D))
-        add("ffn_key_relu2", lambda: [hbm._linear(l.ffn.key, xf, relu2=True) for l in layers], w4_launch_bytes(B, D, Fl))
-        add("ffn_value_add", lambda: [hbm._linear(l.ffn.value, xh, residual=xres) for l in layers], w4_launch_bytes(B, Fl, D))
+        assert hbm._rkv_grouped(layers[0].attn, xr, xk, xv) is not None, "r/k/v are not served by the grouped launch"
+        add("rkv_grouped", lambda: [hbm._rkv_grouped(l.attn, xr, xk, xv) for l in layers], launch_bytes(B, D, A_l, 3))
+        add("o_proj", lambda: [hbm._linear(l.attn.o_proj, xo) for l in layers], launch_bytes(B, A_l, D))
+        add("ffn_key_relu2", lambda: [hbm._linear(l.ffn.key, xf, relu2=True) for l in layers], launch_bytes(B, D, Fl))
+        add("ffn_value_add", lambda: [hbm._linear(l.ffn.value, xh, residual=xres) for l in layers], launch_bytes(B, Fl, D))
         tot_b = sum(v["bytes_per_launch"] for v in per.values())
         tot_us = sum(v["us_per_launch"] for v in per.values())
-        roofline = {"kernel": "w4g_umma64_kernel / w4g_umma_kernel (int4 group-128 projections on tcgen05: the four launches of a layer)",
+        roofline = {"kernel": "w4g_umma_kernel (%s projections on tcgen05: the four launches of a layer)" %
+                              ("int4 group-128" if args.quant == "mm4" else "int8 per-channel"),
                     "bound": "hbm", "achieved": tot_b / tot_us / 1e3, "peak": hbm_peak, "unit": "GB/s",
                     "frac": tot_b / tot_us / 1e3 / hbm_peak, "peak_source": peak_src + " (burst copy)",
                     "bytes_per_launch": tot_b / 4, "us_per_launch": tot_us / 4, "launches": per,
                     "share_of_step": tot_us * 1e-3 * len(layers) / ms_per_step,
-                    # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of the ffn.key launch at B = 64
-                    # (profiles/): 36.4 MB against 37.7 MB algorithmic (activations and outputs stay in L2); the other
-                    # launches stream the same format, so the figure is scaled by the weight bytes of a layer
-                    "traffic": (36.4e6 / w4_launch_bytes(64, 4096, 16384)) * tot_b / 4 if B == 64 else None,
+                    # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of the four launches of a 7.2B layer at
+                    # B = 64 (profiles/): 36.2 + 38.4 + 28.3 + 9.5 = 112.4 MB against 114.8 MB algorithmic (activations and
+                    # outputs stay in L2): scaled by the algorithmic bytes of this run's launches
+                    "traffic": (112.4e6 / 114.8e6) * tot_b / 4 if (B == 64 and args.quant == "mm4") else None,
                     "note": "achieved = algorithmic bytes of the four launches / their CUDA-event time, each shape replayed "
-                            "alone as a graph over all layers' weights; at 64 rows the tensor pipe (N = 64 MMAs) bounds this "
-                            "kernel at about 0.7 of the copy peak"}
+                            "alone as a graph over all layers' weights; at 64 rows a [128 x 128] int4 block costs 512 tensor-pipe "
+                            "cycles (a 128 x N x 16 MMA takes about 64 cycles for every N <= 128): about 0.65 of the copy peak over 128 CTAs"}
         del xr, xk, xv, xf, xo, xh, xres
 
     # ---------------- second kernel: the WKV-7 decode recurrence, timed alone over all layers' states
@@ -618,16 +625,20 @@ def main():
                 tiled.append(hb.w4_repack_tiled(pk, sc, K, 128))
                 del pk, sc
             q8 = [torch.randint(-127, 128, (Nout, K), device=dev, dtype=torch.int8) for _ in range(nbuf)]
+            t8 = [hb.w8_repack_tiled(q) for q in q8]
             s8 = (torch.rand(Nout, device=dev) * 0.01 + 0.002).half()
             for M in (1, 8, 64):
                 x = f16(M, K)
                 us4 = time_graph(lambda: [hb.w4_tiled_linear(x, t, Nout, K) for t in tiled], nbuf, reps=5)
-                us8 = time_graph(lambda: [hb.w8_linear(x, q, s8) for q in q8], nbuf, reps=5)
-                b4, b8 = w4_launch_bytes(M, K, Nout), K * Nout + Nout * 2 + M * (K + Nout) * 2
-                ops["gemv"][f"w{Nout}x{K}_m{M}"] = {
-                    "int4_g128_tcgen05": {"us": us4, "gbs": b4 / us4 / 1e3, "frac": b4 / us4 / 1e3 / hbm_peak},
-                    "int8_per_channel": {"us": us8, "gbs": b8 / us8 / 1e3, "frac": b8 / us8 / 1e3 / hbm_peak}}
-            del tiled, q8
+                us8 = time_graph(lambda: [hb.w8_tiled_linear_group((x,), (t,), (s8,), Nout, K) for t in t8], nbuf, reps=5)
+                b4, b8 = w4_launch_bytes(M, K, Nout), w8_launch_bytes(M, K, Nout)
+                entry = {"int4_g128_tcgen05": {"us": us4, "gbs": b4 / us4 / 1e3, "frac": b4 / us4 / 1e3 / hbm_peak},
+                         "int8_per_channel_tcgen05": {"us": us8, "gbs": b8 / us8 / 1e3, "frac": b8 / us8 / 1e3 / hbm_peak}}
+                if M == 1:  # the CUDA-core GEMV on the reference layout, the small-batch route of w8_linear
+                    usg = time_graph(lambda: [hb.w8_linear(x, q, s8) for q in q8], nbuf, reps=5)
+                    entry["int8_per_channel_gemv"] = {"us": usg, "gbs": b8 / usg / 1e3, "frac": b8 / usg / 1e3 / hbm_peak}
+                ops["gemv"][f"w{Nout}x{K}_m{M}"] = entry
+            del tiled, q8, t8
             torch.cuda.empty_cache()
         for (Mg, K, Nout) in ((4096, 4096, 4096), (4096, 4096, 16384)):
             qa = torch.randint(-127, 128, (Mg, K), device=dev, dtype=torch.int8)

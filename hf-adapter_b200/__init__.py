@@ -13,7 +13,8 @@ from .quant import (A8W8Linear, MM4Linear, MM8Linear, a8w8_ffn, a8w8_linear, deq
                     dynamic_a8_quant, int8_mm, mm4_matmul, mm4_matmul_triton, mm8_matmul, mm8_matmul_triton,
                     quantize_mm4, quantize_mm8, quantize_model, quantize_w4_groupwise, quantize_w8_row,
                     quantize_weight_per_channel_int8, w4_dequant, w4_groupwise_linear, w4_repack_tiled,
-                    w4_tiled_linear, w4_tiled_linear_group, w8_dequant, w8_linear)
+                    w4_tiled_linear, w4_tiled_linear_group, w8_dequant, w8_linear, w8_repack_tiled,
+                    w8_tiled_linear_group)
 from .recurrent import (dplr_chunk_scan, fused_recurrent_output_prepare, fused_recurrent_output_prepare_raw,
                         fused_recurrent_scan, fused_recurrent_scan_clampw, fused_recurrent_scan_output_prepare,
                         fused_recurrent_scan_state_prep, fused_recurrent_update, self_chunk_rwkv7)

@@ -49,6 +49,9 @@ SIGNATURES = {
     "rwkv7_w4g_gemv_tiled": (I, [P] * 4 + [I, I, I, I, I, P]),
     "rwkv7_w4g_gemv_tiled_group": (I, [P] * 3 + [I, I, I, I, I, I, P]),
     "rwkv7_w8_gemv": (I, [P] * 5 + [I, I, I, I, I, P]),
+    "rwkv7_w8_tiled_bytes": (L, [I, I]),
+    "rwkv7_w8_repack": (I, [P, P, I, I, P]),
+    "rwkv7_w8_gemv_tiled_group": (I, [P] * 5 + [I, I, I, I, I, I, P]),
     "rwkv7_w4g_dequant": (I, [P] * 4 + [I, I, I, I, P]),
     "rwkv7_w8_dequant": (I, [P] * 3 + [I, I, I, P]),
     "rwkv7_a8_quant": (I, [P, P, P, I, I, I, P]),

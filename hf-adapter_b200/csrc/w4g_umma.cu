@@ -68,19 +68,22 @@ constexpr int KB = 128;      // k elements per block
 constexpr int RAW_BYTES = TILE_N * KB / 2;  // 8192 packed nibbles
 constexpr int SC_OFF = RAW_BYTES;           // then 128 fp16 scales of the k-block
 constexpr int Z_OFF = SC_OFF + TILE_N * 2;  // then 128 u8 zero-points, then padding
-constexpr int BLOCK_BYTES = 8704;           // one tile block in memory = one bulk copy (68 x 128 B)
+constexpr int W4_BLOCK_BYTES = 8704;        // one int4 tile block in memory = one bulk copy (68 x 128 B)
+constexpr int W8_BLOCK_BYTES = TILE_N * KB;  // int8 per-channel format: 16 KiB of offset-binary bytes (q + 128), scales apart
 constexpr int TMEM_COLS = 512;
 constexpr int G = 3;                        // dequant groups (four groups with one A buffer each measured the same)
 constexpr int NA = 6;                       // A buffers (two per group) = weight stages = "done" barriers
 constexpr int HANDOFF_THREADS = 128 + 32;   // a dequant group arrives, its issuer warp syncs
-constexpr int WRING_BYTES = NA * BLOCK_BYTES;
 
 // NB = activation rows per weight pass = UMMA N.  64: two issuers, six activation stages sharing the "done" barriers
 // with the A buffers.  128: one issuer (tensor memory holds 6 A buffers + one 128-column accumulator), three
 // activation stages of 32 KiB with their own barriers.
-template <int NB_>
+// FMT 0 = int4 group-128 (scales and zero-points inside the block), FMT 1 = int8 with one scale per output channel.
+template <int NB_, int FMT_>
 struct Cfg {
-    static constexpr int NB = NB_;
+    static constexpr int NB = NB_, FMT = FMT_;
+    static constexpr int BLOCK_BYTES = FMT_ == 0 ? W4_BLOCK_BYTES : W8_BLOCK_BYTES;
+    static constexpr int WRING_BYTES = NA * BLOCK_BYTES;
     static constexpr int NISS = NB_ == 64 ? 2 : 1;
     static constexpr int XST = NB_ == 64 ? 6 : 3;
     static constexpr bool SHARED_DONE = XST == NA;  // one commit per block releases the activation stage and the A buffer
@@ -91,6 +94,7 @@ struct Cfg {
     static constexpr int Q_BYTES = NB_ * TILE_N * 4;
     static constexpr int NBARS = 2 * XST + 3 * NA + 1;
     static constexpr size_t SMEM = (size_t)XST * X_BYTES + WRING_BYTES + NBARS * 8 + 16 + 1024;
+    static_assert(SMEM <= 227 * 1024, "shared memory capacity");
     static_assert(NA % G == 0 && NA % NISS == 0, "an A buffer must always belong to the same group and issuer");
     static_assert(Q_BYTES <= XST * X_BYTES, "the exchange buffer aliases the activation ring");
     static_assert(D_COL + NISS * NB_ <= TMEM_COLS, "tensor memory capacity");
@@ -100,7 +104,9 @@ struct Cfg {
 constexpr int kW4MaxGroup = 4;  // projections of equal shape served by one launch (r / k / v of a layer)
 
 struct W4UmmaArgs {
-    const uint8_t* tw[kW4MaxGroup];  // tiled weights: [tiles][K/128] blocks of BLOCK_BYTES = [4 chunks][128 channels][16 B] | scales | zeros
+    const uint8_t* tw[kW4MaxGroup];  // tiled weights: [tiles][K/128] blocks; int4: [4 chunks][128 channels][16 B] | scales | zeros,
+                                     // int8: [8 chunks][128 channels][16 B]
+    const __half* rscale[kW4MaxGroup];  // int8 format: one scale per output channel
     __half* out[kW4MaxGroup];
     const __half* residual;          // add epilogue (single projection only)
     int M, K, Nout, epilogue, nkb, kbt, splits, row_blocks;  // kbt = K / 128 (k-blocks per channel tile)
@@ -141,6 +147,18 @@ __device__ __forceinline__ void dequant_word(uint32_t w, uint32_t zlo, uint32_t 
     out[3] = fma_mul_h2(and_or(w2, 0x00F000F0u, kMagic), kSixteenth, zhi, sc);  // 1024 + 16*(k6, k7)
 }
 
+// int8 format: a word holds the offset-binary bytes (q + 128) of four consecutive k.  prmt puts each byte under the high
+// byte 0x64, which is the fp16 number 1024 + byte; subtracting 1152 leaves q exactly.  The per-channel scale is applied
+// to the fp32 accumulator in the epilogue.
+__device__ __forceinline__ void dequant_word8(uint32_t w, uint32_t* out) {
+    constexpr uint32_t kHi = 0x64646464u, kOff = 0x64806480u;  // (1152, 1152)
+    uint32_t a, b;
+    asm("prmt.b32 %0, %1, %2, 0x4140;" : "=r"(a) : "r"(w), "r"(kHi));
+    asm("prmt.b32 %0, %1, %2, 0x4342;" : "=r"(b) : "r"(w), "r"(kHi));
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(out[0]) : "r"(a), "r"(kOff));
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(out[1]) : "r"(b), "r"(kOff));
+}
+
 __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
@@ -154,11 +172,12 @@ __device__ __forceinline__ bool elect_one() {
 __device__ __forceinline__ void named_arrive(int id, int threads) { asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory"); }
 __device__ __forceinline__ void named_sync(int id, int threads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory"); }
 
-template <int NBT>
-__global__ void __launch_bounds__(w4::Cfg<NBT>::NTHREADS, 1)
+template <int NBT, int FMT>
+__global__ void __launch_bounds__(w4::Cfg<NBT, FMT>::NTHREADS, 1)
 w4g_umma_kernel(const __grid_constant__ W4Maps maps, const W4UmmaArgs p) {
     using namespace w4;
-    using C = Cfg<NBT>;
+    using C = Cfg<NBT, FMT>;
+    constexpr int BLOCK_BYTES = C::BLOCK_BYTES, WRING_BYTES = C::WRING_BYTES;
     constexpr int NB = C::NB, NISS = C::NISS, XST = C::XST, X_BYTES = C::X_BYTES, XATOM = C::XATOM;
     constexpr int FIRST_DQ_WARP = C::FIRST_DQ_WARP, NTHREADS = C::NTHREADS, A_COL = C::A_COL, D_COL = C::D_COL;
     extern __shared__ unsigned char smem_unaligned[];
@@ -302,22 +321,39 @@ w4g_umma_kernel(const __grid_constant__ W4Maps maps, const W4UmmaArgs p) {
                 // this channel's 64 packed bytes: chunk c (32 k) of all 128 channels is one 2 KiB slab, so the
                 // threads of a warp read consecutive 16-byte pieces (no bank conflicts, no swizzle)
                 const unsigned char* rrow = wblk + row * 16;
-                uint4 pk[4];
+                if constexpr (FMT == 0) {
+                    uint4 pk[4];
 #pragma unroll
-                for (int c = 0; c < 4; ++c) pk[c] = *reinterpret_cast<const uint4*>(rrow + c * 2048);
-                const uint32_t s16 = reinterpret_cast<const unsigned short*>(wblk + SC_OFF)[row];
-                const uint32_t z = (wblk + Z_OFF)[row];
-                const uint32_t sc = s16 * 0x00010001u;               // (scale, scale)
-                const uint32_t zlo = z * 0x00010001u + 0x64006400u;  // 1024 + z as fp16: 0x6400 | z
-                const uint32_t zhi = z * 0x00100010u + 0xD400D400u;  // -(64 + z) as fp16: 0xD400 | (z << 4)
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&wempty[aa]);
+                    for (int c = 0; c < 4; ++c) pk[c] = *reinterpret_cast<const uint4*>(rrow + c * 2048);
+                    const uint32_t s16 = reinterpret_cast<const unsigned short*>(wblk + SC_OFF)[row];
+                    const uint32_t z = (wblk + Z_OFF)[row];
+                    const uint32_t sc = s16 * 0x00010001u;               // (scale, scale)
+                    const uint32_t zlo = z * 0x00010001u + 0x64006400u;  // 1024 + z as fp16: 0x6400 | z
+                    const uint32_t zhi = z * 0x00100010u + 0xD400D400u;  // -(64 + z) as fp16: 0xD400 | (z << 4)
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&wempty[aa]);
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    dequant_word(pk[c].x, zlo, zhi, sc, v[c] + 0);
-                    dequant_word(pk[c].y, zlo, zhi, sc, v[c] + 4);
-                    dequant_word(pk[c].z, zlo, zhi, sc, v[c] + 8);
-                    dequant_word(pk[c].w, zlo, zhi, sc, v[c] + 12);
+                    for (int c = 0; c < 4; ++c) {
+                        dequant_word(pk[c].x, zlo, zhi, sc, v[c] + 0);
+                        dequant_word(pk[c].y, zlo, zhi, sc, v[c] + 4);
+                        dequant_word(pk[c].z, zlo, zhi, sc, v[c] + 8);
+                        dequant_word(pk[c].w, zlo, zhi, sc, v[c] + 12);
+                    }
+                } else {
+                    // 128 bytes per channel: chunk c (16 k) of all 128 channels is one 2 KiB slab
+                    uint4 pk[8];
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) pk[c] = *reinterpret_cast<const uint4*>(rrow + c * 2048);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&wempty[aa]);
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        uint32_t* o = v[c >> 1] + (c & 1) * 8;
+                        dequant_word8(pk[c].x, o + 0);
+                        dequant_word8(pk[c].y, o + 2);
+                        dequant_word8(pk[c].z, o + 4);
+                        dequant_word8(pk[c].w, o + 6);
+                    }
                 }
             }
             if (i >= NA && ok) {  // the MMAs of the block that used this A buffer before completed
@@ -363,12 +399,13 @@ w4g_umma_kernel(const __grid_constant__ W4Maps maps, const W4UmmaArgs p) {
                     const int nn = n0 + row;
                     grid_dependency_wait();  // returns at once (the accumulator already depends on the activations)
                     if (nn < p.Nout) {
+                        const float rs = FMT == 1 ? __half2float(p.rscale[grp_idx][nn]) : 1.f;
 #pragma unroll
                         for (int e = 0; e < 16; ++e) {
                             const int m = col0 + e;
                             if (m >= m_rows) break;
                             const size_t o = (size_t)(m0 + m) * p.Nout + nn;
-                            float y = __half2float(__float2half_rn(__uint_as_float(v[e])));
+                            float y = __half2float(__float2half_rn(__uint_as_float(v[e]) * rs));
                             if (p.epilogue == RWKV7_EPI_RELU2) {
                                 y = fmaxf(y, 0.f);
                                 y *= y;
@@ -419,6 +456,11 @@ w4g_umma_kernel(const __grid_constant__ W4Maps maps, const W4UmmaArgs p) {
         constexpr int RSTEP = NTHREADS / 64;  // full 64-thread row teams (a trailing half team sits out)
         const float* Q0 = Q + n - (size_t)m_begin * TILE_N;  // slot r, global row m: Q0[(r * rows_per_rank + m) * TILE_N]
         const int slot = rows_per_rank * TILE_N;
+        float rs0 = 1.f, rs1 = 1.f;
+        if (FMT == 1 && n_ok) {
+            rs0 = __half2float(p.rscale[grp_idx][n0 + n]);
+            if (n0 + n + 1 < p.Nout) rs1 = __half2float(p.rscale[grp_idx][n0 + n + 1]);
+        }
         for (int m = m_begin + (tid >> 6); m < m_end && n_ok && (tid >> 6) < RSTEP; m += RSTEP) {
             const float* qq = Q0 + m * TILE_N;
             float2 acc = *reinterpret_cast<const float2*>(qq);
@@ -428,7 +470,7 @@ w4g_umma_kernel(const __grid_constant__ W4Maps maps, const W4UmmaArgs p) {
                 acc.y += t2.y;
             }
             const size_t o = (size_t)(m0 + m) * p.Nout + n0 + n;
-            float y0 = __half2float(__float2half_rn(acc.x)), y1 = __half2float(__float2half_rn(acc.y));
+            float y0 = __half2float(__float2half_rn(acc.x * rs0)), y1 = __half2float(__float2half_rn(acc.y * rs1));
             if (p.epilogue == RWKV7_EPI_RELU2) {
                 y0 = fmaxf(y0, 0.f); y0 *= y0;
                 y1 = fmaxf(y1, 0.f); y1 *= y1;
@@ -483,7 +525,7 @@ __global__ void w4g_repack_kernel(const uint8_t* __restrict__ packed, const T* _
 #pragma unroll
         for (int i = 0; i < 8; ++i) out |= ((w >> (4 * order[i])) & 15u) << (4 * i);
     }
-    uint8_t* block = tiled + blk * w4::BLOCK_BYTES;
+    uint8_t* block = tiled + blk * w4::W4_BLOCK_BYTES;
     reinterpret_cast<uint32_t*>(block)[widx & 2047] = out;
     if (c == 0 && j == 0) {
         const long long gi = n * (K / group) + (b * 128) / group;
@@ -492,7 +534,27 @@ __global__ void w4g_repack_kernel(const uint8_t* __restrict__ packed, const T* _
     }
 }
 
-// Tiled buffers written by rwkv7_w4g_repack and not yet read by a projection.  The projection kernel streams the
+// int8 per-channel weights q [Nout, K] -> [tiles][K/128] blocks of [8 chunks][128 channels][16 B], bytes stored as
+// q + 128 (offset binary: the kernel's byte -> fp16 conversion needs no sign handling).  One thread per 16-byte piece.
+__global__ void w8_repack_kernel(const int8_t* __restrict__ q, uint8_t* __restrict__ tiled, int K, int Nout, long long total_pieces) {
+    const long long pidx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (pidx >= total_pieces) return;
+    // pidx = ((tile * kbt + b) * 8 + c) * 128 + r
+    const int r = (int)(pidx & 127);
+    const int c = (int)((pidx >> 7) & 7);
+    const long long blk = pidx >> 10;
+    const int kbt = K / 128;
+    const int b = (int)(blk % kbt);
+    const long long n = (blk / kbt) * 128 + r;
+    uint4 v = make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);  // padding channels: q = 0
+    if (n < Nout) {
+        v = *reinterpret_cast<const uint4*>(q + n * K + b * 128 + c * 16);
+        v.x ^= 0x80808080u; v.y ^= 0x80808080u; v.z ^= 0x80808080u; v.w ^= 0x80808080u;
+    }
+    reinterpret_cast<uint4*>(tiled)[pidx] = v;
+}
+
+// Tiled buffers written by rwkv7_w4g_repack / rwkv7_w8_repack and not yet read by a projection.  The projection kernel streams the
 // weights BEFORE its grid-dependency wait, so the first projection after a repack is launched with full stream
 // ordering (it may directly follow the repack kernel); every later one is ordered behind that launch.
 static std::mutex g_fresh_mu;
@@ -508,8 +570,19 @@ static bool take_tiled_fresh(const void* tiled) {
 }
 
 // G projections of equal shape (their own activations, weights and outputs) in one launch.
-int launch_w4g_umma_tiled(const void* const* xs, const uint8_t* const* tws, const void* residual, void* const* outs, int G,
-                          int M, int K, int Nout, int epilogue, cudaStream_t st) {
+template <int NBT, int FMT>
+static cudaError_t launch_variant(cudaLaunchConfig_t& cfg, const W4Maps& maps, const W4UmmaArgs& a) {
+    using C = w4::Cfg<NBT, FMT>;
+    cudaError_t e = cudaFuncSetAttribute(w4g_umma_kernel<NBT, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM);
+    if (e != cudaSuccess) return e;
+    cfg.blockDim = dim3(C::NTHREADS);
+    cfg.dynamicSmemBytes = C::SMEM;
+    return cudaLaunchKernelEx(&cfg, w4g_umma_kernel<NBT, FMT>, maps, a);
+}
+
+// fmt 0: int4 group-wise tiled weights; fmt 1: int8 tiled weights with per-channel scales rscales[g] [Nout].
+int launch_w4g_umma_tiled(const void* const* xs, const uint8_t* const* tws, const void* const* rscales, const void* residual,
+                          void* const* outs, int G, int M, int K, int Nout, int epilogue, int fmt, cudaStream_t st) {
     using namespace w4;
     RWKV7_REQUIRE(G >= 1 && G <= kW4MaxGroup, RWKV7_ERR_UNSUPPORTED, "w4g_gemv_tiled: 1..%d projections per launch (got %d)", kW4MaxGroup, G);
     const int NB = M > 64 ? 128 : 64;          // activation rows per pass over the weights
@@ -532,6 +605,7 @@ int launch_w4g_umma_tiled(const void* const* xs, const uint8_t* const* tws, cons
     for (int g = 0; g < G; ++g) {
         if (int e = make_tmap_x3d(&maps.x[g], xs[g], M, K, NB)) return e;
         a.tw[g] = tws[g];
+        a.rscale[g] = rscales ? reinterpret_cast<const __half*>(rscales[g]) : nullptr;
         a.out[g] = reinterpret_cast<__half*>(outs[g]);
         fresh |= take_tiled_fresh(tws[g]);
     }
@@ -541,15 +615,8 @@ int launch_w4g_umma_tiled(const void* const* xs, const uint8_t* const* tws, cons
     a.row_blocks = row_blocks;
     a.error = kernel_error_word();
     RWKV7_REQUIRE(a.error != nullptr, RWKV7_ERR_CUDA, "w4g_gemv_tiled: cannot resolve the device error word");
-    const bool v64 = NB == 64;
-    const size_t smem = v64 ? Cfg<64>::SMEM : Cfg<128>::SMEM;
-    cudaError_t e = v64 ? cudaFuncSetAttribute(w4g_umma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
-                        : cudaFuncSetAttribute(w4g_umma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    RWKV7_REQUIRE(e == cudaSuccess, RWKV7_ERR_CUDA, "w4g_gemv_tiled: %s", cudaGetErrorString(e));
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(tiles, row_blocks * G, splits);
-    cfg.blockDim = dim3(v64 ? Cfg<64>::NTHREADS : Cfg<128>::NTHREADS);
-    cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -561,7 +628,8 @@ int launch_w4g_umma_tiled(const void* const* xs, const uint8_t* const* tws, cons
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = (programmatic_launch_enabled() && !fresh) ? 2 : 1;
-    e = v64 ? cudaLaunchKernelEx(&cfg, w4g_umma_kernel<64>, maps, a) : cudaLaunchKernelEx(&cfg, w4g_umma_kernel<128>, maps, a);
+    const cudaError_t e = NB == 64 ? (fmt == 0 ? launch_variant<64, 0>(cfg, maps, a) : launch_variant<64, 1>(cfg, maps, a))
+                                   : (fmt == 0 ? launch_variant<128, 0>(cfg, maps, a) : launch_variant<128, 1>(cfg, maps, a));
     RWKV7_REQUIRE(e == cudaSuccess, RWKV7_ERR_CUDA, "w4g_gemv_tiled launch: %s", cudaGetErrorString(e));
     return RWKV7_OK;
 }
@@ -573,7 +641,7 @@ using namespace rwkv7;
 extern "C" int64_t rwkv7_w4g_tiled_bytes(int K, int Nout) {
     if (K <= 0 || Nout <= 0 || K % 128) return 0;
     const int64_t tiles = (Nout + 127) / 128, kbt = K / 128;
-    return tiles * kbt * w4::BLOCK_BYTES;
+    return tiles * kbt * w4::W4_BLOCK_BYTES;
 }
 
 extern "C" int rwkv7_w4g_repack(const uint8_t* packed, const void* scales, const uint8_t* zeros, uint8_t* tiled, int K,
@@ -599,7 +667,7 @@ extern "C" int rwkv7_w4g_gemv_tiled(const void* x, const uint8_t* tiled, const v
     RWKV7_REQUIRE(epilogue >= 0 && epilogue <= 2, RWKV7_ERR_INVALID, "w4g_gemv_tiled: bad epilogue code %d", epilogue);
     RWKV7_REQUIRE(epilogue != RWKV7_EPI_ADD || residual, RWKV7_ERR_INVALID, "w4g_gemv_tiled: residual is required for the add epilogue");
     RWKV7_REQUIRE(aligned(x, 16) && aligned(tiled, 16), RWKV7_ERR_ALIGN, "w4g_gemv_tiled: pointers must be 16-byte aligned");
-    return launch_w4g_umma_tiled(&x, &tiled, residual, &out, 1, M, K, Nout, epilogue, static_cast<cudaStream_t>(stream));
+    return launch_w4g_umma_tiled(&x, &tiled, nullptr, residual, &out, 1, M, K, Nout, epilogue, 0, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int rwkv7_w4g_gemv_tiled_group(const void* const* xs, const uint8_t* const* tiled, void* const* outs, int G, int M,
@@ -613,5 +681,38 @@ extern "C" int rwkv7_w4g_gemv_tiled_group(const void* const* xs, const uint8_t* 
         RWKV7_REQUIRE(xs[g] && tiled[g] && outs[g], RWKV7_ERR_INVALID, "w4g_gemv_tiled_group: null pointer in projection %d", g);
         RWKV7_REQUIRE(aligned(xs[g], 16) && aligned(tiled[g], 16), RWKV7_ERR_ALIGN, "w4g_gemv_tiled_group: pointers must be 16-byte aligned");
     }
-    return launch_w4g_umma_tiled(xs, tiled, nullptr, outs, G, M, K, Nout, epilogue, static_cast<cudaStream_t>(stream));
+    return launch_w4g_umma_tiled(xs, tiled, nullptr, nullptr, outs, G, M, K, Nout, epilogue, 0, static_cast<cudaStream_t>(stream));
+}
+
+// ---------------------------------------------------------------- int8 per-output-channel weights
+extern "C" int64_t rwkv7_w8_tiled_bytes(int K, int Nout) {
+    if (K <= 0 || Nout <= 0 || K % 128) return 0;
+    const int64_t tiles = (Nout + 127) / 128, kbt = K / 128;
+    return tiles * kbt * w4::W8_BLOCK_BYTES;
+}
+
+extern "C" int rwkv7_w8_repack(const int8_t* q, uint8_t* tiled, int K, int Nout, void* stream) {
+    RWKV7_REQUIRE(K > 0 && Nout > 0 && K % 128 == 0, RWKV7_ERR_UNSUPPORTED, "w8_repack: K must be a positive multiple of 128");
+    RWKV7_REQUIRE(q && tiled, RWKV7_ERR_INVALID, "w8_repack: null pointer");
+    RWKV7_REQUIRE(aligned(q, 16) && aligned(tiled, 16), RWKV7_ERR_ALIGN, "w8_repack: unaligned pointer");
+    const long long pieces = (long long)((Nout + 127) / 128) * (K / 128) * 1024;
+    w8_repack_kernel<<<(unsigned)((pieces + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(q, tiled, K, Nout, pieces);
+    mark_tiled_fresh(tiled);
+    return check_launch("w8_repack_kernel");
+}
+
+extern "C" int rwkv7_w8_gemv_tiled_group(const void* const* xs, const uint8_t* const* tiled, const void* const* scales,
+                                         const void* residual, void* const* outs, int G, int M, int K, int Nout, int epilogue,
+                                         int dtype, void* stream) {
+    RWKV7_REQUIRE(xs && tiled && scales && outs, RWKV7_ERR_INVALID, "w8_gemv_tiled_group: null pointer");
+    RWKV7_REQUIRE(G >= 1 && G <= kW4MaxGroup, RWKV7_ERR_UNSUPPORTED, "w8_gemv_tiled_group: 1..%d projections (got %d)", kW4MaxGroup, G);
+    RWKV7_REQUIRE(dtype == RWKV7_F16, RWKV7_ERR_UNSUPPORTED, "w8_gemv_tiled_group: fp16 activations only");
+    RWKV7_REQUIRE(epilogue >= 0 && epilogue <= 2, RWKV7_ERR_INVALID, "w8_gemv_tiled_group: bad epilogue code %d", epilogue);
+    RWKV7_REQUIRE(epilogue != RWKV7_EPI_ADD || (residual && G == 1), RWKV7_ERR_INVALID,
+                  "w8_gemv_tiled_group: the add epilogue takes one projection and a residual");
+    for (int g = 0; g < G; ++g) {
+        RWKV7_REQUIRE(xs[g] && tiled[g] && scales[g] && outs[g], RWKV7_ERR_INVALID, "w8_gemv_tiled_group: null pointer in projection %d", g);
+        RWKV7_REQUIRE(aligned(xs[g], 16) && aligned(tiled[g], 16), RWKV7_ERR_ALIGN, "w8_gemv_tiled_group: pointers must be 16-byte aligned");
+    }
+    return launch_w4g_umma_tiled(xs, tiled, scales, residual, outs, G, M, K, Nout, epilogue, 1, static_cast<cudaStream_t>(stream));
 }

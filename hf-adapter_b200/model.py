@@ -117,13 +117,18 @@ def _rkv_grouped(at, xr, xk, xv):
     """r / k / v through one grouped launch when all three are int4 projections of one shape that the tensor-core
     decode kernel takes; None otherwise."""
     mods = (at.r_proj, at.k_proj, at.v_proj)
-    if not all(isinstance(m, _q.MM4Linear) and m.bias is None for m in mods):
+    int4 = all(isinstance(m, _q.MM4Linear) for m in mods)
+    int8 = all(isinstance(m, _q.MM8Linear) and m.sm7x_rowwise for m in mods)
+    if not (int4 or int8) or any(m.bias is not None for m in mods):
         return None
     if len({(m.in_features, m.out_features) for m in mods}) != 1:
         return None
     tiled = [m.tiled_for(x_) for m, x_ in zip(mods, (xr, xk, xv))]
     if any(t is None for t in tiled):
         return None
+    if int8:
+        return _q.w8_tiled_linear_group((xr, xk, xv), tiled, [m.row_scale for m in mods], mods[0].out_features,
+                                        mods[0].in_features)
     return _q.w4_tiled_linear_group((xr, xk, xv), tiled, mods[0].out_features, mods[0].in_features)
 
 

@@ -139,6 +139,44 @@ def w4_tiled_linear_group(xs, tileds, out_features, in_features, *, relu2: bool 
     return [y.reshape(*x.shape[:-1], Nout) for y, x in zip(ys, xs)]
 
 
+def w8_repack_tiled(q):
+    """Tiled copy of an int8 per-output-channel weight ``q [out,in]`` for the tensor-core kernel (16 KiB blocks of
+    [128 channels x 128 k], bytes stored as q + 128).  Done once at load time."""
+    Nout, K = (int(v) for v in q.shape)
+    require_cuda(q, what="w8_repack_tiled")
+    nbytes = int(_lib.lib.rwkv7_w8_tiled_bytes(K, Nout))
+    if nbytes == 0:
+        raise ValueError(f"in_features={K} is not a multiple of 128")
+    tiled = torch.empty((nbytes,), device=q.device, dtype=torch.uint8)
+    _lib.check(_lib.lib.rwkv7_w8_repack(ptr(q.contiguous()), ptr(tiled), K, Nout, stream_ptr(q)), "w8_repack_tiled")
+    return tiled
+
+
+def w8_tiled_linear_group(xs, tileds, scales, out_features, in_features, *, relu2: bool = False, residual=None, out=None):
+    """``ys[g] = epilogue(xs[g] @ (q_g * s_g)^T)`` for up to four int8 projections of one shape in one launch of the
+    tensor-core kernel (fp16).  ``residual`` / ``out`` apply to a single projection.  Returns the list of outputs."""
+    import ctypes
+    K, Nout, G = int(in_features), int(out_features), len(xs)
+    if not 1 <= G <= 4 or len(tileds) != G or len(scales) != G:
+        raise ValueError("w8_tiled_linear_group takes 1..4 activations and as many tiled weights and scales")
+    x2 = [_rows(x, K) for x in xs]
+    M = int(x2[0].shape[0])
+    if any(int(t.shape[0]) != M or t.dtype != x2[0].dtype for t in x2):
+        raise ValueError("grouped projections need the same row count and dtype")
+    sc = [s.contiguous() for s in scales]
+    require_cuda(*x2, *tileds, *sc, what="w8_tiled_linear_group")
+    if any(s.dtype != x2[0].dtype or int(s.numel()) != Nout for s in sc):
+        raise ValueError("scales must be [out_features] in the activation dtype")
+    epi, res = _epi(relu2, residual, M, Nout, x2[0])
+    if (res is not None or out is not None) and G != 1:
+        raise ValueError("residual / out apply to a single projection")
+    ys = [torch.empty((M, Nout), device=x2[0].device, dtype=x2[0].dtype) if out is None else out.reshape(M, Nout) for _ in range(G)]
+    arr = lambda ts: (ctypes.c_void_p * G)(*[t.data_ptr() for t in ts])
+    _lib.check(_lib.lib.rwkv7_w8_gemv_tiled_group(arr(x2), arr(tileds), arr(sc), ptr(res), arr(ys), G, M, K, Nout, epi,
+                                                   dt_code(x2[0]), stream_ptr(x2[0])), "w8_tiled_linear_group")
+    return [y.reshape(*x.shape[:-1], Nout) for y, x in zip(ys, xs)]
+
+
 def w8_dequant(q, s, out=None):
     Nout, K = (int(v) for v in q.shape)
     require_cuda(q, s, what="w8_dequant")
@@ -437,9 +475,31 @@ class MM8Linear(torch.nn.Module):
         else:
             self.bias = None
         self.fused = bool(fused)
+        self._tiled = None  # tiled copy of q_row for the tensor-core kernel (derived, not part of the state dict)
+
+    def _load_from_state_dict(self, *args, **kwargs):
+        self._tiled = None  # new weights: the derived copy is rebuilt on the next decode call
+        return super()._load_from_state_dict(*args, **kwargs)
+
+    def tiled_for(self, x):
+        """The tiled weight copy when ``x`` is eligible for the tensor-core kernel (row-wise format, fp16, CUDA,
+        in_features % 128 == 0; built once per device on first use), else None."""
+        if not self.sm7x_rowwise:
+            return None
+        rows = x.numel() // self.in_features
+        if not (rows <= TILED_MAX_ROWS and x.dtype == torch.float16 and x.is_cuda and self.in_features % 128 == 0
+                and self.row_scale.dtype == torch.float16):
+            return None
+        t = self._tiled
+        if t is None or t.device != x.device:
+            t = self._tiled = w8_repack_tiled(self.q_row)
+        return t
 
     def _lin(self, x, **kw):
         if self.sm7x_rowwise:
+            t = self.tiled_for(x)
+            if t is not None:
+                return w8_tiled_linear_group((x,), (t,), (self.row_scale,), self.out_features, self.in_features, **kw)[0]
             return w8_linear(x, self.q_row, self.row_scale, **kw)
         y = mm8_matmul(x, self.w_u8, self.mx, self.rx, self.my, self.ry)
         if kw.get("relu2"):
@@ -500,6 +560,10 @@ class MM4Linear(torch.nn.Module):
         else:
             self.bias = None
         self.fused = bool(fused)
+
+    def _load_from_state_dict(self, *args, **kwargs):
+        self._tiled = None  # new weights: the derived copy is rebuilt on the next decode call
+        return super()._load_from_state_dict(*args, **kwargs)
 
     def tiled_for(self, x):
         """The tiled weight copy when ``x`` is eligible for the tensor-core decode kernel (built once per device,

@@ -216,6 +216,19 @@ int rwkv7_w4g_gemv_tiled(const void* x, const uint8_t* tiled, const void* residu
 int rwkv7_w4g_gemv_tiled_group(const void* const* xs, const uint8_t* const* tiled, void* const* outs, int G, int M, int K,
                                int Nout, int epilogue, int dtype, void* stream);
 
+/* Tensor-core version of the int8 per-output-channel projection below (rwkv7_w8_gemv), any row count, from a TILED copy
+ * of q built once at load by rwkv7_w8_repack: one 16 KiB block per [128 channels x 128 k] tile, bytes stored as q + 128.
+ * G (1..4) projections of one shape per launch (xs, tiled, scales, outs: host arrays of G device pointers; scales[g]
+ * [Nout] fp16).  The integer weights enter the MMA exactly and the channel scale multiplies the fp32 accumulator, i.e.
+ * out = epilogue(fp16(scale * (x . q^T))): the reference's materialised weight fp16(q * scale) (w8_linear,
+ * rwkv7_hf/sm70_quant.py:522-531) differs from q * scale by one fp16 rounding per weight.  The add epilogue takes G = 1
+ * and a residual.  fp16 only, K % 128 == 0.  rwkv7_w8_tiled_bytes returns the tiled size (0 = unsupported shape). */
+int64_t rwkv7_w8_tiled_bytes(int K, int Nout);
+int rwkv7_w8_repack(const int8_t* q, uint8_t* tiled, int K, int Nout, void* stream);
+int rwkv7_w8_gemv_tiled_group(const void* const* xs, const uint8_t* const* tiled, const void* const* scales,
+                              const void* residual, void* const* outs, int G, int M, int K, int Nout, int epilogue,
+                              int dtype, void* stream);
+
 /* int8 per-output-channel weights, quantize_w8_row format (rwkv7_hf/sm70_quant.py:485-489): q [Nout,K] i8,
  * scale [Nout] in `dtype`.  Replaces w8_linear (:522) / the W8A16 GEMV (native_quant_a8w8.py:50-132). */
 int rwkv7_w8_gemv(const void* x, const int8_t* q, const void* scale, const void* residual, void* out,

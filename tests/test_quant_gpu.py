@@ -198,3 +198,51 @@ def test_w4g_grouped_projections(G, M, K, Nn):
         np.testing.assert_allclose(npf(y), ro, rtol=6e-3, atol=8e-3 * max(1.0, float(np.abs(yo).max())))
     with pytest.raises(ValueError):
         hb.w4_tiled_linear_group(xs * 5, tiled * 5, Nn, K)
+
+
+@pytest.mark.parametrize("G,M,K,Nn", [(1, 1, 128, 8), (1, 5, 512, 200), (3, 64, 2560, 2560), (1, 64, 10240, 2560), (1, 64, 2560, 10240),
+                                      (1, 130, 1024, 256), (2, 512, 1024, 384), (1, 64, 4096, 16384)])
+def test_w8_tensor_core_path(G, M, K, Nn):
+    """int8 per-output-channel weights on the tcgen05 kernel (tiled copy, exact integer weights in the MMA, channel
+    scale on the fp32 accumulator) against the oracle's w8_linear (materialised fp16 weight): all epilogues, grouped
+    launches, determinism, the module route, and no bounded wait giving up."""
+    from hf_adapter_b200 import _lib
+    rng = np.random.default_rng(G * 31 + M + K + Nn)
+    xs, tiled, scales, ref = [], [], [], []
+    for g in range(G):
+        W = (0.02 * rng.standard_normal((Nn, K))).astype(np.float16)
+        x = rng.standard_normal((M, K)).astype(np.float16)
+        q, s = O.quantize_w8_row(W)
+        ref.append(O.w8_linear(x, q, s, hi=True).astype(np.float32))
+        xs.append(cu(x)); scales.append(cu(s)); tiled.append(hb.w8_repack_tiled(cu(q)))
+    _lib.kernel_status(True)
+    ys = hb.w8_tiled_linear_group(xs, tiled, scales, Nn, K)
+    assert _lib.kernel_status(True) == 0 and len(ys) == G
+    for y, yo in zip(ys, ref):
+        tol_abs = 2e-3 * max(1.0, float(np.abs(yo).max()))
+        np.testing.assert_allclose(npf(y), yo, rtol=2e-3, atol=tol_abs)
+    again = hb.w8_tiled_linear_group(xs, tiled, scales, Nn, K)
+    assert all(torch.equal(a, b) for a, b in zip(again, ys))
+    yr = hb.w8_tiled_linear_group(xs, tiled, scales, Nn, K, relu2=True)
+    for y, yo in zip(yr, ref):
+        ro = (np.maximum(yo.astype(np.float16).astype(np.float32), 0) ** 2).astype(np.float16).astype(np.float32)
+        np.testing.assert_allclose(npf(y), ro, rtol=6e-3, atol=8e-3 * max(1.0, float(np.abs(yo).max())))
+    res = rng.standard_normal((M, Nn)).astype(np.float16)
+    (ya,) = hb.w8_tiled_linear_group(xs[:1], tiled[:1], scales[:1], Nn, K, residual=cu(res))
+    np.testing.assert_allclose(npf(ya), ref[0] + res.astype(np.float32), rtol=2e-3, atol=4e-3 * max(1.0, float(np.abs(ref[0]).max())))
+    if K % 128 == 0 and M <= 512:
+        lin = torch.nn.Linear(K, Nn, bias=False)
+        with torch.no_grad():
+            lin.weight.copy_(torch.from_numpy((0.02 * rng.standard_normal((Nn, K))).astype(np.float32)))
+        mod = hb.MM8Linear(lin.half(), rowwise=True).cuda()
+        y_mod = mod(xs[0])
+        assert mod._tiled is not None
+        yo = O.w8_linear(npf(xs[0]).astype(np.float16), mod.q_row.cpu().numpy(), mod.row_scale.cpu().numpy(), hi=True).astype(np.float32)
+        np.testing.assert_allclose(npf(y_mod), yo, rtol=2e-3, atol=2e-3 * max(1.0, float(np.abs(yo).max())))
+        # new weights through load_state_dict drop the derived tiled copy
+        sd = {k_: v_.clone() for k_, v_ in mod.state_dict().items()}
+        sd["q_row"] = -sd["q_row"]
+        mod.load_state_dict(sd)
+        assert mod._tiled is None
+        np.testing.assert_allclose(npf(mod(xs[0])), -yo, rtol=2e-3, atol=2e-3 * max(1.0, float(np.abs(yo).max())))
+    assert _lib.kernel_status(True) == 0
