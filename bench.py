@@ -117,7 +117,8 @@ def shape_config(shape, quant, batch, layers=0):
 
 
 # ------------------------------------------------------------------------------------------ model
-def build_model(shape, tp_world, tp_rank, tp_group, device, layers_override=0, quant="mm4", seed=0, full_then_shard=False):
+def build_model(shape, tp_world, tp_rank, tp_group, device, layers_override=0, quant="mm4", seed=0, full_then_shard=False,
+                state_dtype=None):
     """Random-init model of the named shape, projections quantised on the GPU, fp16 head.
     The token-shift / key-scale parameters the reference constructs as zeros are re-initialised (seeded) so
     that every term of the recurrence is exercised.  ``full_then_shard``: build the unsharded model from the seed
@@ -138,7 +139,8 @@ def build_model(shape, tp_world, tp_rank, tp_group, device, layers_override=0, q
         torch.set_default_dtype(torch.float16)
         try:
             with torch.device(device):
-                return hb.RWKV7ForCausalLM(cfg, tp_world=world, tp_rank=rank, tp_group=group)
+                return hb.RWKV7ForCausalLM(cfg, tp_world=world, tp_rank=rank, tp_group=group,
+                                           state_dtype=state_dtype or torch.float32)
         finally:
             torch.set_default_dtype(old)
 
@@ -229,6 +231,8 @@ def main():
     ap.add_argument("--shape", default="7.2B", choices=sorted(SHAPES))
     ap.add_argument("--quant", default="mm4", choices=["mm4", "w8"],
                     help="projection format: mm4 = int4 group-128 (headline), w8 = int8 per output channel (the 2.9B configuration)")
+    ap.add_argument("--state", default="fp32", choices=["fp32", "fp16"],
+                    help="recurrent-state storage: fp32 (the headline contract) or the reference's opt-in FP16-state lane")
     ap.add_argument("--batch", type=int, default=64, help="sequences per GPU group (global batch = batch for N=1)")
     ap.add_argument("--layers", type=int, default=0, help="debug: override the layer count (invalidates the metric)")
     ap.add_argument("--prefill-tokens", type=int, default=1024)
@@ -401,13 +405,14 @@ def main():
     # ---------------- headline.  N = 1: the model on one GPU.  N > 1 (default): head-sharded tensor parallelism --
     # heads, their state and the projections sharded, a global batch of batch*N on every rank (per-GPU state work
     # fixed: weak scaling), NCCL all-reduces of the [B,D] partial sums inside the decode graph.
+    sdt = torch.float16 if args.state == "fp16" else torch.float32
     if use_tp:
-        model, cfg, nq = build_model(args.shape, world, rank, tp_group, dev, args.layers, args.quant)
+        model, cfg, nq = build_model(args.shape, world, rank, tp_group, dev, args.layers, args.quant, state_dtype=sdt)
         B, shard = args.batch * world, world
         parallelism = (f"tp{world}: heads, recurrent state and projections sharded, global batch {B} on every rank, "
                        "two NCCL all-reduces per layer inside the decode graph")
     else:
-        model, cfg, nq = build_model(args.shape, 1, 0, None, dev, args.layers, args.quant)
+        model, cfg, nq = build_model(args.shape, 1, 0, None, dev, args.layers, args.quant, state_dtype=sdt)
         B, shard = args.batch, 1
         parallelism = "single GPU" if world == 1 else \
             f"dp{world}: independent sequence batches, one full replica per GPU, {args.batch} sequences each, no data-path collective"
@@ -442,7 +447,8 @@ def main():
 
     hbm_peak, tc_burst, tc_sustained, peak_src = measured_peaks()
     Hl, Fl, A_l = H // shard, Fd // shard, (H // shard) * 64
-    step_bytes, w_bytes, s_bytes = decode_step_bytes(Lr, D, Hl, Fl, V, B, args.quant)  # per GPU
+    sbytes = 2 if args.state == "fp16" else 4
+    step_bytes, w_bytes, s_bytes = decode_step_bytes(Lr, D, Hl, Fl, V, B, args.quant, state_bytes=sbytes)  # per GPU
     N = 64
     f16 = lambda *s: torch.randn(*s, device=dev, dtype=torch.float16)
 
@@ -531,14 +537,14 @@ def main():
     k1.record()
     torch.cuda.synchronize()
     wkv_ms = k0.elapsed_time(k1) / (reps * len(states))
-    wkv_bytes = B * Hl * (2 * N * N * 4 + 7 * N * 2)
+    wkv_bytes = B * Hl * (2 * N * N * sbytes + 7 * N * 2)
     achieved = wkv_bytes / (wkv_ms * 1e-3) / 1e9
     roofline_wkv = {"kernel": "wkv7_step_kernel (decode recurrence + fused epilogues)", "bound": "hbm", "achieved": achieved,
                     "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak, "peak_source": peak_src + " (burst copy)",
                     # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture at B*H = 4096 (profiles/): 87.0 MB per
                     # launch (reads = state in; most of the written state is still dirty in L2 when the kernel ends),
                     # scaled by the sequence-heads of this launch
-                    "traffic": 87.0e6 * (B * Hl) / 4096.0, "bytes_per_launch": wkv_bytes, "us_per_launch": wkv_ms * 1e3,
+                    "traffic": 87.0e6 * (B * Hl) / 4096.0 if sbytes == 4 else None, "bytes_per_launch": wkv_bytes, "us_per_launch": wkv_ms * 1e3,
                     "share_of_step": wkv_ms * len(states) / ms_per_step}
     if roofline is None:
         roofline, roofline_wkv = roofline_wkv, None
@@ -552,7 +558,7 @@ def main():
     if not args.no_b256 and world == 1 and args.batch != 256:
         try:
             ms256, _, _, c256, _, _ = time_decode(model, 256, 3, False, n_steps=min(steps, 20), e2e=False)
-            sb256 = decode_step_bytes(Lr, D, H, Fd, V, 256, args.quant)[0]
+            sb256 = decode_step_bytes(Lr, D, H, Fd, V, 256, args.quant, state_bytes=sbytes)[0]
             b256 = {"value": 256 / (ms256 * 1e-3), "unit": "tok/s", "ms_per_step": ms256, "step_bytes": sb256,
                     "step_hbm_frac": sb256 / (ms256 * 1e-3) / 1e9 / hbm_peak}
             model._graphs.pop(256, None)
@@ -658,7 +664,7 @@ def main():
         "metric": METRIC, "value": global_batch / (ms_per_step * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": steps,
         "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f16", "data": "synthetic",
-        "config": dict(base_cfg, global_batch=global_batch, batch_per_gpu_step=B, layers=Lr, quantised_modules=nq,
+        "config": dict(base_cfg, recurrent_state=args.state, global_batch=global_batch, batch_per_gpu_step=B, layers=Lr, quantised_modules=nq,
                        parallelism=parallelism,
                        l2="working set per step (weights + state, GBs) exceeds the 126 MB L2; no flush needed",
                        cuda_graph=True),

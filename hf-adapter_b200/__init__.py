@@ -17,7 +17,8 @@ from .quant import (A8W8Linear, MM4Linear, MM8Linear, a8w8_ffn, a8w8_linear, deq
                     w8_tiled_linear_group)
 from .recurrent import (dplr_chunk_scan, fused_recurrent_output_prepare, fused_recurrent_output_prepare_raw,
                         fused_recurrent_scan, fused_recurrent_scan_clampw, fused_recurrent_scan_output_prepare,
-                        fused_recurrent_scan_state_prep, fused_recurrent_update, self_chunk_rwkv7)
+                        fused_recurrent_scan_state_prep, fused_recurrent_update, native_fp16_recurrent_output_prepare_raw,
+                        native_fp16_recurrent_should_use, native_fp16_sequence, self_chunk_rwkv7)
 
 from .sharding import shard_spec, shard_state_dict
 

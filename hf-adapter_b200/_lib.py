@@ -34,6 +34,9 @@ SIGNATURES = {
     "rwkv7_wkv7_output_prepare": (I, [P] * 13 + [I, I, I, F, I, I, P]),
     "rwkv7_wkv7_output_prepare_raw": (I, [P] * 14 + [P, P, I, P, P, P, I, P, I, I, I, I, F, I, P]),
     "rwkv7_wkv7_scan": (I, [P] * 13 + [F, I, I, I, I, I, I, P]),
+    "rwkv7_wkv7_scan_f16state": (I, [P] * 13 + [F, I, I, I, I, I, I, I, P, P, P]),
+    "rwkv7_wkv7_output_prepare_f16state": (I, [P] * 13 + [I, I, I, F, I, I, P]),
+    "rwkv7_wkv7_output_prepare_raw_f16state": (I, [P] * 14 + [P, P, I, P, P, P, I, P, P, I, I, I, I, I, F, I, P]),
     "rwkv7_wkv7_chunk_scan": (I, [P] * 9 + [I, I, I, I, I, I, I, P]),
     "rwkv7_attn_norm_mix6": (I, [P, P, P, P, PP, PP, I, I, F, I, P]),
     "rwkv7_ffn_add_norm_mix": (I, [P] * 8 + [I, I, F, I, P]),

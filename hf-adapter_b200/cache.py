@@ -10,9 +10,12 @@ import torch
 class NativeRWKV7Cache:
     is_compileable = True
 
-    def __init__(self, state=None, xpa=None, xpf=None, v_first=None, seen_tokens: int = 0):
+    def __init__(self, state=None, xpa=None, xpf=None, v_first=None, seen_tokens: int = 0, elapsed=None):
         self._state, self._xpa, self._xpf, self._v_first = state, xpa, xpf, v_first
         self._seen_tokens = int(seen_tokens)
+        # FP16-state lane only: per-sequence step counters (int32 [B]) that phase the decay dither
+        # (the ``elapsed`` operand of rwkv7_hf/native_wkv_fp16.py:54-71); None for an fp32 state
+        self._elapsed = elapsed
         self._graph_owner = None  # decode-graph runner whose static buffers these tensors are, if any
 
     # -- tuple protocol ---------------------------------------------------
@@ -26,12 +29,26 @@ class NativeRWKV7Cache:
         return (self._state, self._xpa, self._xpf, self._v_first)[i]
 
     @classmethod
-    def allocate(cls, num_layers, batch, hidden, heads, head_dim, device, dtype):
-        """Zero state (rwkv7_hf/native.py:283-295)."""
+    def allocate(cls, num_layers, batch, hidden, heads, head_dim, device, dtype, state_dtype=torch.float32):
+        """Zero state (rwkv7_hf/native.py:283-295).  ``state_dtype=torch.float16`` allocates the FP16-state lane's
+        cache (half the recurrent-state bytes, plus the ``elapsed`` counters of its decay dither)."""
         z = lambda *s, dt=dtype: torch.zeros(*s, device=device, dtype=dt)
-        return cls([z(batch, heads, head_dim, head_dim, dt=torch.float32) for _ in range(num_layers)],
+        return cls([z(batch, heads, head_dim, head_dim, dt=state_dtype) for _ in range(num_layers)],
                    [z(batch, hidden) for _ in range(num_layers)], [z(batch, hidden) for _ in range(num_layers)],
-                   z(batch, heads * head_dim), 0)
+                   z(batch, heads * head_dim), 0,
+                   elapsed=z(batch, dt=torch.int32) if state_dtype == torch.float16 else None)
+
+    def _tensors(self):
+        """Every tensor of the cache as one flat list (the order `_set_tensors` takes)."""
+        t = list(self._state) + list(self._xpa) + list(self._xpf) + [self._v_first]
+        return t + ([self._elapsed] if self._elapsed is not None else [])
+
+    def _set_tensors(self, tensors):
+        L = len(self._state)
+        self._state, self._xpa, self._xpf = list(tensors[:L]), list(tensors[L:2 * L]), list(tensors[2 * L:3 * L])
+        self._v_first = tensors[3 * L]
+        if self._elapsed is not None:
+            self._elapsed = tensors[3 * L + 1]
 
     # -- HF cache contract ---------------------------------------------------
     def get_seq_length(self, layer_idx: int = 0) -> int:
@@ -61,11 +78,12 @@ class NativeRWKV7Cache:
         ml = lambda vs: None if vs is None else [fn(v) for v in vs]
         state, xpa, xpf = ml(self._state), ml(self._xpa), ml(self._xpf)
         vf = None if self._v_first is None else fn(self._v_first)
+        el = None if self._elapsed is None else fn(self._elapsed)
         if inplace:
-            self._state, self._xpa, self._xpf, self._v_first = state, xpa, xpf, vf
+            self._state, self._xpa, self._xpf, self._v_first, self._elapsed = state, xpa, xpf, vf, el
             self._graph_owner = None
             return self
-        return NativeRWKV7Cache(state, xpa, xpf, vf, self._seen_tokens)
+        return NativeRWKV7Cache(state, xpa, xpf, vf, self._seen_tokens, elapsed=el)
 
     def clone(self):
         return self._map(lambda v: v.clone(), inplace=False)
@@ -75,6 +93,9 @@ class NativeRWKV7Cache:
 
     def to(self, *args, copy: bool = False, **kwargs):
         def move(v):
+            if not v.is_floating_point():  # the elapsed counters only change device
+                dev = kwargs.get("device", next((a for a in args if not isinstance(a, torch.dtype)), v.device))
+                return v.to(device=dev, copy=copy)
             if v.dtype == torch.float32 and ("dtype" in kwargs or any(isinstance(a, torch.dtype) for a in args)):
                 # the fp32 recurrent state keeps its dtype; only the device moves
                 dev = kwargs.get("device", next((a for a in args if not isinstance(a, torch.dtype)), v.device))
@@ -88,6 +109,8 @@ class NativeRWKV7Cache:
                 v.zero_()
         if self._v_first is not None:
             self._v_first.zero_()
+        if self._elapsed is not None:
+            self._elapsed.zero_()
         self._seen_tokens = 0
 
     def select_batch(self, indices, *, inplace: bool = True):

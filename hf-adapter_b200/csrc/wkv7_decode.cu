@@ -7,6 +7,11 @@
 // no intermediate vector touches HBM.  The kernel is HBM-bound: algorithmic
 // traffic is 2*64*64*4 + ~7*64*sizeof(T) bytes per (sequence, head).
 //
+// The state may also be stored in fp16 (the reference's opt-in FP16-state lanes: the Triton output-prepare kernels
+// load it to fp32 and round the result back, rwkv7_hf/fused_recurrent_update.py:655-699; the native_wkv_fp16
+// extension additionally dithers the decay, rwkv7_hf/native_wkv_fp16.py:118-128): the arithmetic stays fp32, the
+// traffic halves.
+//
 // Thread map (128 threads): lane16 = tid & 15 owns columns 4*lane16..+3 (key
 // index j), rowgroup = tid >> 4 owns rows rowgroup + 8*it (value index i), so a
 // warp instruction touches two full 256-byte state rows = 512 contiguous bytes.
@@ -21,8 +26,8 @@ enum StepMode { kUpdate = 0, kPrepare = 1, kRaw = 2 };
 
 struct StepArgs {
     const void *r, *w, *k, *v, *kk, *a;
-    const float* state_in;
-    float* state_out;
+    const void* state_in;  // fp32 or fp16 [B,H,64,64]
+    void* state_out;
     void* out;
     const void *g, *r_k, *gn_w, *gn_b;
     const void *k_k, *k_a;
@@ -32,9 +37,46 @@ struct StepArgs {
     int H;
     float eps;
     int prefetch_state;  // load the state tile before the grid-dependency wait (state_prefetch argument of the raw entry point)
+    const int* elapsed;  // fp16 state, raw mode: per-sequence step counters [B] that phase the decay dither (NULL = no dither)
 };
 
-template <typename T, typename TW, int MODE>
+// Deterministic zero-mean rotator of the reference's FP16-state kernel (rwkv7_hf/native_wkv_fp16.py:118-121): the
+// decay of a half-precision state is often smaller than half an ulp of the entry it multiplies, which would freeze it
+// under round-to-nearest; a pseudo-random offset of up to +-2^-10 on (decay - 1), different for every channel and
+// step, makes the rounding unbiased on average.
+__device__ __forceinline__ float rotator1(int x) {
+    const uint32_t bits = 2654435769u * static_cast<uint32_t>(x);
+    return 4.547473508864641e-13f * static_cast<float>(static_cast<int32_t>(bits));
+}
+
+template <typename TS> struct StateIO;
+template <> struct StateIO<float> {
+    static __device__ __forceinline__ float4 load(const void* base, size_t off) {
+        return *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + off);  // plain load: may alias state_out
+    }
+    // streaming store: the new state is not read again before the next token, so it should not linger in L2 and
+    // be written back under the kernels that follow (measured: -8 % time)
+    static __device__ __forceinline__ void store(void* base, size_t off, const float4& s) {
+        __stcs(reinterpret_cast<float4*>(reinterpret_cast<float*>(base) + off), s);
+    }
+};
+template <> struct StateIO<__half> {
+    static __device__ __forceinline__ float4 load(const void* base, size_t off) {
+        const uint2 u = *reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(base) + off);
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
+        const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+    static __device__ __forceinline__ void store(void* base, size_t off, const float4& s) {
+        const __half2 a = __floats2half2_rn(s.x, s.y), b = __floats2half2_rn(s.z, s.w);
+        uint2 u;
+        u.x = *reinterpret_cast<const uint32_t*>(&a);
+        u.y = *reinterpret_cast<const uint32_t*>(&b);
+        __stcs(reinterpret_cast<uint2*>(reinterpret_cast<__half*>(base) + off), u);
+    }
+};
+
+template <typename T, typename TW, int MODE, typename TS>
 __global__ void __launch_bounds__(kStepThreads, 8) wkv7_step_kernel(const StepArgs p) {  // 64 registers: 8 CTAs per SM (measured: 7 -> 8 CTAs is -9 % time)
     const int bh = blockIdx.x;
     const int h = bh % p.H;
@@ -51,11 +93,10 @@ __global__ void __launch_bounds__(kStepThreads, 8) wkv7_step_kernel(const StepAr
     // Launched programmatically: resident under the tail of the preceding kernel.  By default everything waits for it.
     if (!p.prefetch_state) grid_dependency_wait();
     // ---- state tile: issue all 8 row loads first (memory-level parallelism)
-    const float* sin = p.state_in + (size_t)bh * kN * kN;
+    const size_t sbase = (size_t)bh * kN * kN;
     float4 S[8];
 #pragma unroll
-    for (int it = 0; it < 8; ++it)
-        S[it] = *reinterpret_cast<const float4*>(sin + (size_t)(it * 8 + rg) * kN + c0);  // plain load: may alias state_out
+    for (int it = 0; it < 8; ++it) S[it] = StateIO<TS>::load(p.state_in, sbase + (size_t)(it * 8 + rg) * kN + c0);
 
     // With the state-prefetch option the loads above are already in flight while the preceding kernel (the r/k/v
     // projection of a decode step) finishes: the caller promises that kernel does not write the state, and every
@@ -100,6 +141,13 @@ __global__ void __launch_bounds__(kStepThreads, 8) wkv7_step_kernel(const StepAr
             k[c] = kr[c] * (1.0f + (a[c] - 1.0f) * ka[c]);
             w[c] = decay_from_raw(wr[c]);
         }
+        if constexpr (sizeof(TS) == 2) {
+            if (p.elapsed != nullptr) {  // (decay - 1 + rotator) rounded to fp16, as the reference's FP16-state kernel forms it
+                const int phase = p.elapsed[bh / p.H] + hbase + c0;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) w[c] = 1.0f + __half2float(__float2half_rn(w[c] - 1.0f + rotator1(phase + c)));
+            }
+        }
     } else {
         load4(reinterpret_cast<const TW*>(p.w) + vbase + c0, w);
         load4(reinterpret_cast<const T*>(p.k) + vbase + c0, k);
@@ -129,7 +177,6 @@ __global__ void __launch_bounds__(kStepThreads, 8) wkv7_step_kernel(const StepAr
     __syncthreads();
 
     // ---- the recurrence, row by row
-    float* sout = p.state_out + (size_t)bh * kN * kN;
 #pragma unroll
     for (int it = 0; it < 8; ++it) {
         const int i = it * 8 + rg;
@@ -141,9 +188,10 @@ __global__ void __launch_bounds__(kStepThreads, 8) wkv7_step_kernel(const StepAr
         s.y = s.y * w[1] + vi * k[1] - sa * kka[1];
         s.z = s.z * w[2] + vi * k[2] - sa * kka[2];
         s.w = s.w * w[3] + vi * k[3] - sa * kka[3];
-        // streaming store: the new state is not read again before the next token, so it should not linger in L2 and
-        // be written back under the kernels that follow (measured: -8 % time)
-        __stcs(reinterpret_cast<float4*>(sout + (size_t)i * kN + c0), s);
+        StateIO<TS>::store(p.state_out, sbase + (size_t)i * kN + c0, s);
+        if constexpr (sizeof(TS) == 2) {  // the output is formed from the state as stored
+            s.x = round_to<__half>(s.x); s.y = round_to<__half>(s.y); s.z = round_to<__half>(s.z); s.w = round_to<__half>(s.w);
+        }
         float y = s.x * r[0] + s.y * r[1] + s.z * r[2] + s.w * r[3];
         y = group_sum<16>(y);
         if (l16 == 0) s_y[i] = y;
@@ -180,10 +228,15 @@ __global__ void __launch_bounds__(kStepThreads, 8) wkv7_step_kernel(const StepAr
     }
 }
 
-template <typename T, typename TW, int MODE>
+template <typename T, typename TW, int MODE, typename TS = float>
 static int launch_step(StepArgs p, int B, cudaStream_t st) {
-    launch_programmatic(wkv7_step_kernel<T, TW, MODE>, dim3(B * p.H), dim3(kStepThreads), 0, st, p);
+    launch_programmatic(wkv7_step_kernel<T, TW, MODE, TS>, dim3(B * p.H), dim3(kStepThreads), 0, st, p);
     return check_launch("wkv7_step_kernel");
+}
+
+__global__ void advance_elapsed_kernel(int* elapsed, int B) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b < B) elapsed[b] += 1;
 }
 
 static int check_step_common(const StepArgs& p, int B, int H, int N) {
@@ -258,5 +311,60 @@ extern "C" int rwkv7_wkv7_output_prepare_raw(const void* r, const void* w_raw, c
     if (int e = check_step_common(p, B, H, N)) return e;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     RWKV7_DISPATCH_DTYPE(dtype, T, { return launch_step<T, T, kRaw>(p, B, st); });
+    return RWKV7_OK;
+}
+
+// ---------------------------------------------------------------- fp16 recurrent state
+extern "C" int rwkv7_wkv7_output_prepare_f16state(const void* r, const void* w, const void* k, const void* v, const void* kk,
+                                                  const void* a, const void* state_in, void* state_out, const void* g,
+                                                  const void* r_k, const void* gn_w, const void* gn_b, void* out, int B,
+                                                  int H, int N, float eps, int dtype, int w_is_f32, void* stream) {
+    StepArgs p{};
+    p.r = r; p.w = w; p.k = k; p.v = v; p.kk = kk; p.a = a;
+    p.state_in = state_in; p.state_out = state_out; p.out = out; p.H = H;
+    p.g = g; p.r_k = r_k; p.gn_w = gn_w; p.gn_b = gn_b; p.eps = eps;
+    RWKV7_REQUIRE(kk && g && r_k && gn_w && gn_b, RWKV7_ERR_INVALID, "wkv7_output_prepare_f16state: null tensor pointer");
+    if (int e = check_step_common(p, B, H, N)) return e;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    RWKV7_DISPATCH_DTYPE(dtype, T, {
+        if (w_is_f32) return launch_step<T, float, kPrepare, __half>(p, B, st);
+        return launch_step<T, T, kPrepare, __half>(p, B, st);
+    });
+    return RWKV7_OK;
+}
+
+extern "C" int rwkv7_wkv7_output_prepare_raw_f16state(const void* r, const void* w_raw, const void* k_raw, const void* v,
+                                                      const void* a, const void* state_in, void* state_out, const void* g,
+                                                      const void* k_k, const void* k_a, const void* r_k, const void* gn_w,
+                                                      const void* gn_b, void* out, const void* w_bias, const void* a_bias,
+                                                      int a_is_raw, const void* v_first, const void* v_gate,
+                                                      const void* v_gate_bias, int v_gate_is_raw, void* v_out,
+                                                      int* elapsed, int advance_elapsed, int state_prefetch, int B, int H,
+                                                      int N, float eps, int dtype, void* stream) {
+    StepArgs p{};
+    p.r = r; p.w = w_raw; p.k = k_raw; p.v = v; p.a = a;
+    p.state_in = state_in; p.state_out = state_out; p.out = out; p.H = H;
+    p.g = g; p.r_k = r_k; p.gn_w = gn_w; p.gn_b = gn_b; p.eps = eps;
+    p.k_k = k_k; p.k_a = k_a;
+    p.w_bias = w_bias; p.a_bias = a_bias; p.a_is_raw = a_is_raw;
+    p.v_first = v_first; p.v_gate = v_gate; p.v_gate_bias = v_gate_bias; p.v_gate_is_raw = v_gate_is_raw;
+    p.v_out = v_out;
+    p.prefetch_state = state_prefetch != 0;
+    p.elapsed = elapsed;
+    RWKV7_REQUIRE(g && r_k && gn_w && gn_b && k_k && k_a, RWKV7_ERR_INVALID,
+                  "wkv7_output_prepare_raw_f16state: null tensor pointer");
+    RWKV7_REQUIRE((v_first == nullptr) == (v_gate == nullptr), RWKV7_ERR_INVALID,
+                  "wkv7_output_prepare_raw_f16state: v_first and v_gate must be given together");
+    RWKV7_REQUIRE(!advance_elapsed || elapsed, RWKV7_ERR_INVALID, "wkv7_output_prepare_raw_f16state: advance_elapsed needs elapsed");
+    if (int e = check_step_common(p, B, H, N)) return e;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    RWKV7_DISPATCH_DTYPE(dtype, T, {
+        if (int e = launch_step<T, T, kRaw, __half>(p, B, st)) return e;
+        if (advance_elapsed) {  // after the step, in stream order: no CTA of the step can see the new count
+            advance_elapsed_kernel<<<(B + 127) / 128, 128, 0, st>>>(elapsed, B);
+            return check_launch("advance_elapsed_kernel");
+        }
+        return RWKV7_OK;
+    });
     return RWKV7_OK;
 }

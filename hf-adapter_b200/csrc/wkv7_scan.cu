@@ -16,14 +16,25 @@ constexpr int kTS = 16;  // tokens per shared-memory stage
 
 struct ScanArgs {
     const void *r, *w, *k, *v, *kk, *a;
-    const float* state_in;
-    float* state_out;
+    const void* state_in;  // fp32, or fp16 when state_f16
+    void* state_out;
     void* y;
     const void *g, *r_k, *gn_w, *gn_b;
     float eps;
     int T, H;
     int w_mode;  // 0: decay in T, 1: decay fp32, 2: raw w in T
+    // the reference's FP16-state sequence lane (rwkv7_hf/native_wkv_fp16.py:335-452)
+    int state_f16;       // the state is stored in fp16 (loaded to fp32 registers, rounded back once at the end)
+    int ab_mode;         // `kk` holds -kk and `a` holds kk*a (the lane's neg_kk / kka operands)
+    const void* w0;      // w_mode 2: per-channel bias [H*64] added to raw w before the decay (may be NULL)
+    const int* elapsed;  // w_mode 2: per-sequence step counters [B]; token t uses the dither phase elapsed + channel + t
 };
+
+// zero-mean pseudo-random offset of the reference's FP16-state kernels (rwkv7_hf/native_wkv_fp16.py:118-121)
+__device__ __forceinline__ float scan_rotator1(int x) {
+    const uint32_t bits = 2654435769u * static_cast<uint32_t>(x);
+    return 4.547473508864641e-13f * static_cast<float>(static_cast<int32_t>(bits));
+}
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -63,14 +74,28 @@ __global__ void __launch_bounds__(kScanThreads) wkv7_scan_kernel(const ScanArgs 
     const int wbytes = (p.w_mode == 1) ? 4 : (int)sizeof(T);
 
     float S[32];
-    {
-        const float* sin = p.state_in + ((size_t)bh * kSN + row) * kSN + c0;
+    const size_t soff = ((size_t)bh * kSN + row) * kSN + c0;
+    if (p.state_f16) {
+        const __half* sin = reinterpret_cast<const __half*>(p.state_in) + soff;
+#pragma unroll
+        for (int c = 0; c < 32; c += 8) {
+            const uint4 t = *reinterpret_cast<const uint4*>(sin + c);
+            const __half2* h2 = reinterpret_cast<const __half2*>(&t);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f2 = __half22float2(h2[e]);
+                S[c + 2 * e] = f2.x; S[c + 2 * e + 1] = f2.y;
+            }
+        }
+    } else {
+        const float* sin = reinterpret_cast<const float*>(p.state_in) + soff;
 #pragma unroll
         for (int c = 0; c < 32; c += 4) {
             float4 t = *reinterpret_cast<const float4*>(sin + c);
             S[c] = t.x; S[c + 1] = t.y; S[c + 2] = t.z; S[c + 3] = t.w;
         }
     }
+    const int phase0 = p.elapsed ? p.elapsed[b] + h * kSN : 0;
 
     // 16-byte chunks per token vector
     constexpr int CH_T = kSN * sizeof(T) / 16;
@@ -123,13 +148,18 @@ __global__ void __launch_bounds__(kScanThreads) wkv7_scan_kernel(const ScanArgs 
                 fr[tt][c] = to_f<T>(rs.r[tt][c]);
                 fk[tt][c] = to_f<T>(rs.k[tt][c]);
                 fv[tt][c] = to_f<T>(rs.v[tt][c]);
-                fkk[tt][c] = kkv;
-                fkka[tt][c] = kkv * to_f<T>(rs.a[tt][c]);
+                fkk[tt][c] = p.ab_mode ? -kkv : kkv;
+                fkka[tt][c] = p.ab_mode ? to_f<T>(rs.a[tt][c]) : kkv * to_f<T>(rs.a[tt][c]);
                 float wv;
                 if (p.w_mode == 1) wv = rs.w[tt][c];
                 else {
                     wv = to_f<T>(reinterpret_cast<const T*>(rs.w[tt])[c]);
-                    if (p.w_mode == 2) wv = decay_from_raw(wv);
+                    if (p.w_mode == 2) {
+                        if (p.w0) wv += to_f<T>(reinterpret_cast<const T*>(p.w0)[h * kSN + c]);
+                        wv = decay_from_raw(wv);
+                        // (decay - 1 + rotator) rounded to fp16, as the reference's kernel forms its decay operand
+                        if (p.elapsed) wv = 1.0f + __half2float(__float2half_rn(wv - 1.0f + scan_rotator1(phase0 + c + t0 + tt)));
+                    }
                 }
                 fw[tt][c] = wv;
             }
@@ -199,8 +229,18 @@ __global__ void __launch_bounds__(kScanThreads) wkv7_scan_kernel(const ScanArgs 
         // the next iteration's first __syncthreads orders this flush before fy/f* are overwritten
     }
 
-    {
-        float* sout = p.state_out + ((size_t)bh * kSN + row) * kSN + c0;
+    if (p.state_f16) {
+        __half* sout = reinterpret_cast<__half*>(p.state_out) + soff;
+#pragma unroll
+        for (int c = 0; c < 32; c += 8) {
+            uint4 t;
+            __half2* h2 = reinterpret_cast<__half2*>(&t);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) h2[e] = __floats2half2_rn(S[c + 2 * e], S[c + 2 * e + 1]);
+            *reinterpret_cast<uint4*>(sout + c) = t;
+        }
+    } else {
+        float* sout = reinterpret_cast<float*>(p.state_out) + soff;
 #pragma unroll
         for (int c = 0; c < 32; c += 4)
             *reinterpret_cast<float4*>(sout + c) = make_float4(S[c], S[c + 1], S[c + 2], S[c + 3]);
@@ -214,10 +254,10 @@ static size_t scan_smem_bytes() { return 2 * sizeof(RawStage<T>) + 7 * kTS * kSN
 
 using namespace rwkv7;
 
-extern "C" int rwkv7_wkv7_scan(const void* r, const void* w, const void* k, const void* v, const void* kk,
-                               const void* a, const float* state_in, float* state_out, void* y, const void* g,
-                               const void* r_k, const void* gn_w, const void* gn_b, float eps, int B, int T, int H,
-                               int N, int dtype, int w_mode, void* stream) {
+static int scan_impl(const void* r, const void* w, const void* k, const void* v, const void* kk, const void* a,
+                     const void* state_in, void* state_out, void* y, const void* g, const void* r_k, const void* gn_w,
+                     const void* gn_b, float eps, int B, int T, int H, int N, int dtype, int w_mode, int state_f16,
+                     int ab_mode, const void* w0, const int* elapsed, void* stream) {
     RWKV7_REQUIRE(N == kSN, RWKV7_ERR_UNSUPPORTED, "wkv7_scan: head size must be 64, got %d", N);
     RWKV7_REQUIRE(B > 0 && H > 0 && T >= 0, RWKV7_ERR_INVALID, "wkv7_scan: bad sizes B=%d T=%d H=%d", B, T, H);
     RWKV7_REQUIRE(w_mode >= 0 && w_mode <= 2, RWKV7_ERR_INVALID, "wkv7_scan: w_mode must be 0, 1 or 2");
@@ -227,7 +267,7 @@ extern "C" int rwkv7_wkv7_scan(const void* r, const void* w, const void* k, cons
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (T == 0) {  // empty sequence: the state passes through
         if (state_out != state_in) {
-            cudaError_t e = cudaMemcpyAsync(state_out, state_in, (size_t)B * H * N * N * sizeof(float),
+            cudaError_t e = cudaMemcpyAsync(state_out, state_in, (size_t)B * H * N * N * (state_f16 ? 2 : 4),
                                             cudaMemcpyDeviceToDevice, st);
             RWKV7_REQUIRE(e == cudaSuccess, RWKV7_ERR_CUDA, "wkv7_scan: %s", cudaGetErrorString(e));
         }
@@ -236,7 +276,8 @@ extern "C" int rwkv7_wkv7_scan(const void* r, const void* w, const void* k, cons
     RWKV7_REQUIRE(r && w && k && v && kk && a && y, RWKV7_ERR_INVALID, "wkv7_scan: null tensor pointer");
     const void* ptrs[] = {r, w, k, v, kk, a, state_in, state_out, y, g};
     for (const void* q : ptrs) RWKV7_REQUIRE(aligned(q, 16), RWKV7_ERR_ALIGN, "wkv7_scan: pointers must be 16-byte aligned");
-    ScanArgs p{r, w, k, v, kk, a, state_in, state_out, y, g, r_k, gn_w, gn_b, eps, T, H, w_mode};
+    RWKV7_REQUIRE((!w0 && !elapsed) || w_mode == 2, RWKV7_ERR_INVALID, "wkv7_scan: w0 / elapsed apply to raw w (w_mode 2)");
+    ScanArgs p{r, w, k, v, kk, a, state_in, state_out, y, g, r_k, gn_w, gn_b, eps, T, H, w_mode, state_f16 != 0, ab_mode != 0, w0, elapsed};
     RWKV7_DISPATCH_DTYPE(dtype, TT, {
         const size_t smem = scan_smem_bytes<TT>();
         auto kern = prep ? wkv7_scan_kernel<TT, true> : wkv7_scan_kernel<TT, false>;
@@ -246,4 +287,21 @@ extern "C" int rwkv7_wkv7_scan(const void* r, const void* w, const void* k, cons
         return check_launch("wkv7_scan_kernel");
     });
     return RWKV7_OK;
+}
+
+extern "C" int rwkv7_wkv7_scan(const void* r, const void* w, const void* k, const void* v, const void* kk,
+                               const void* a, const float* state_in, float* state_out, void* y, const void* g,
+                               const void* r_k, const void* gn_w, const void* gn_b, float eps, int B, int T, int H,
+                               int N, int dtype, int w_mode, void* stream) {
+    return scan_impl(r, w, k, v, kk, a, state_in, state_out, y, g, r_k, gn_w, gn_b, eps, B, T, H, N, dtype, w_mode, 0, 0,
+                     nullptr, nullptr, stream);
+}
+
+extern "C" int rwkv7_wkv7_scan_f16state(const void* r, const void* w, const void* k, const void* v, const void* kk,
+                                        const void* a, const void* state_in, void* state_out, void* y, const void* g,
+                                        const void* r_k, const void* gn_w, const void* gn_b, float eps, int B, int T,
+                                        int H, int N, int dtype, int w_mode, int ab_mode, const void* w0,
+                                        const int* elapsed, void* stream) {
+    return scan_impl(r, w, k, v, kk, a, state_in, state_out, y, g, r_k, gn_w, gn_b, eps, B, T, H, N, dtype, w_mode, 1,
+                     ab_mode, w0, elapsed, stream);
 }

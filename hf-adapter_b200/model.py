@@ -160,8 +160,14 @@ def _linear(mod, x, *, relu2=False, residual=None, out=None):
 class RWKV7ForCausalLM(nn.Module):
     """``RWKV7ForCausalLM`` == the native model, as in the reference (rwkv7_hf/__init__.py:17-20)."""
 
-    def __init__(self, config: NativeRWKV7Config, tp_world: int = 1, tp_rank: int = 0, tp_group=None):
+    def __init__(self, config: NativeRWKV7Config, tp_world: int = 1, tp_rank: int = 0, tp_group=None,
+                 state_dtype=torch.float32):
+        """``state_dtype=torch.float16`` selects the reference's opt-in FP16-state lane (rwkv7_hf/native_wkv_fp16.py):
+        caches hold the recurrent state in fp16 and the decode step dithers the decay; fp16 activations only."""
         super().__init__()
+        if state_dtype not in (torch.float32, torch.float16):
+            raise ValueError("state_dtype must be torch.float32 or torch.float16")
+        self.state_dtype = state_dtype
         if config.head_dim != 64:
             raise ValueError("the CUDA kernels require head_dim == 64")
         if config.num_heads % tp_world or config.intermediate_size % tp_world:
@@ -184,8 +190,10 @@ class RWKV7ForCausalLM(nn.Module):
 
     def new_cache(self, batch_size: int) -> NativeRWKV7Cache:
         c = self.config
+        if self.state_dtype == torch.float16 and self.dtype != torch.float16:
+            raise ValueError("the FP16-state lane needs fp16 activations")
         return NativeRWKV7Cache.allocate(c.num_hidden_layers, batch_size, c.hidden_size, c.num_heads // self.tp_world,
-                                         c.head_dim, self.device, self.dtype)
+                                         c.head_dim, self.device, self.dtype, state_dtype=self.state_dtype)
 
     def _side_stream(self, device, index: int = 0):
         st = self._side_streams.get((device, index))
@@ -206,6 +214,8 @@ class RWKV7ForCausalLM(nn.Module):
         H, N = self.model.layers[0].attn.num_heads, self.config.head_dim
         x = F.embedding(ids.reshape(-1), self.model.embeddings.weight)
         B = int(x.shape[0])
+        L = len(self.model.layers)
+        elapsed = cache._elapsed if state[0].dtype == torch.float16 else None
         for i, layer in enumerate(self.model.layers):
             at, ff = layer.attn, layer.ffn
             if i == 0:
@@ -255,7 +265,7 @@ class RWKV7ForCausalLM(nn.Module):
             out, _ = _rec.fused_recurrent_output_prepare_raw(
                 r, w_raw, k, v, a_pre, state[i], g, at.k_k, at.k_a, at.r_k, at.g_norm.weight, at.g_norm.bias,
                 eps=N * 1e-5, new_state=state[i], w_bias=wl[2].bias, a_bias=al[2].bias, a_is_raw=True,
-                state_prefetch=True, **extra)
+                state_prefetch=True, elapsed=elapsed, advance_elapsed=elapsed is not None and i == L - 1, **extra)
             attn = self._all_reduce(_linear(at.o_proj, out))
             x, mixed = _nm.fused_ffn_add_norm_mix_decode(x, attn, xpf[i], layer.ffn_norm.weight, layer.ffn_norm.bias, ff.x_k)
             hidden = _linear(ff.key, mixed, relu2=True)
@@ -303,7 +313,8 @@ class RWKV7ForCausalLM(nn.Module):
                 v_first = v
             a_sig = torch.sigmoid(a_pre)
             if scan_chunk and T % scan_chunk == 0 and x.dtype == torch.float16:
-                y, new_state = _rec.self_chunk_rwkv7(r, w, k, v, kk, a_sig, state[i], chunk_size=scan_chunk)
+                # the tensor-core scan carries an fp32 state; an fp16 cache is widened for the call and rounded back
+                y, new_state = _rec.self_chunk_rwkv7(r, w, k, v, kk, a_sig, state[i].float(), chunk_size=scan_chunk)
                 out = _prep.fused_attn_output_prepare(y, r, k, v, g, at.r_k, at.g_norm.weight, at.g_norm.bias,
                                                       num_heads=H, head_dim=N, head_v_dim=N, eps=N * 1e-5)
             else:
@@ -319,6 +330,8 @@ class RWKV7ForCausalLM(nn.Module):
         if v_first is not None:
             v_first_buf.copy_(v_first[:, -1])
         cache._seen_tokens += T
+        if cache._elapsed is not None:
+            cache._elapsed += T
         xn = _nm.layer_norm(x[:, T - keep:].contiguous(), self.model.norm.weight, self.model.norm.bias)
         return _linear(self.lm_head, xn)
 
@@ -423,8 +436,7 @@ class DecodeGraph:
             self.logits = model._decode_step(self.ids, self.cache)
 
     def _static(self):
-        c = self.cache
-        return c._state + c._xpa + c._xpf + [c._v_first]
+        return self.cache._tensors()
 
     def _detach_bound(self):
         """Give the cache bound so far its own copies of the static buffers and drop its binding."""
@@ -432,20 +444,20 @@ class DecodeGraph:
         self._bound = None
         if old is None or old._graph_owner is not self:
             return
-        L = len(self.cache._state)
-        own = [t.clone() for t in self._static()]
-        old._state, old._xpa, old._xpf, old._v_first = own[:L], own[L:2 * L], own[2 * L:3 * L], own[3 * L]
+        old._set_tensors([t.clone() for t in self._static()])
         old._graph_owner = None
 
     def bind(self, cache: NativeRWKV7Cache):
         if cache._graph_owner is self and self._bound is not None and self._bound() is cache:
             return
         self._detach_bound()
-        for dst, src in zip(self._static(), cache._state + cache._xpa + cache._xpf + [cache._v_first]):
+        mine, theirs = self._static(), cache._tensors()
+        if len(mine) != len(theirs) or any(a.dtype != b.dtype for a, b in zip(mine, theirs)):
+            raise ValueError("the cache does not match this model's state dtype")
+        for dst, src in zip(mine, theirs):
             if dst.data_ptr() != src.data_ptr():
                 dst.copy_(src)
-        cache._state, cache._xpa, cache._xpf, cache._v_first = (
-            self.cache._state, self.cache._xpa, self.cache._xpf, self.cache._v_first)
+        cache._set_tensors(list(mine))
         cache._graph_owner = self
         self._bound = weakref.ref(cache)
 

@@ -18,14 +18,15 @@ from . import _lib
 from ._util import dt_code, no_fallback, ptr, require_cuda, same_dtype, stream_ptr
 
 
-def _state_shape(state):
+def _state_shape(state, allow_f16: bool = False):
     if state.dim() != 4:
         raise ValueError("state must be shaped [batch, heads, head_dim, head_dim]")
     B, H, N, N2 = (int(v) for v in state.shape)
     if N != N2:
         raise ValueError("state must be square in the last two dimensions")
-    if state.dtype != torch.float32:
-        raise ValueError("state must be float32 (the fp16-state lane is not part of this build)")
+    if state.dtype != torch.float32 and not (allow_f16 and state.dtype == torch.float16):
+        raise ValueError("state must be float32" + (" or float16" if allow_f16 else
+                         " (only the output-prepare operators and the scans take a float16 state)"))
     return B, H, N
 
 
@@ -94,7 +95,7 @@ def fused_recurrent_output_prepare(r, w, k, v, kk, a, state, g, r_k, group_norm_
                                    block_n: int = 64, force_fallback: bool = False, out=None, new_state=None):
     """Update + GroupNorm + bonus + gate.  Returns ``(prepared, new_state)``."""
     no_fallback(force_fallback, "fused_recurrent_output_prepare")
-    B, H, N = _state_shape(state)
+    B, H, N = _state_shape(state, allow_f16=True)
     r_, flat = _as_bhn(r, B, H, N, "r")
     w_, k_, v_, kk_, a_, g_ = (_as_bhn(t, B, H, N, n)[0] for t, n in
                                ((w, "w"), (k, "k"), (v, "v"), (kk, "kk"), (a, "a"), (g, "g")))
@@ -107,7 +108,8 @@ def fused_recurrent_output_prepare(r, w, k, v, kk, a, state, g, r_k, group_norm_
         new_state = torch.empty_like(state_c)
     if out is None:
         out = torch.empty_like(r_)
-    _lib.check(_lib.lib.rwkv7_wkv7_output_prepare(
+    fn = _lib.lib.rwkv7_wkv7_output_prepare if state_c.dtype == torch.float32 else _lib.lib.rwkv7_wkv7_output_prepare_f16state
+    _lib.check(fn(
         ptr(r_), ptr(w_), ptr(k_), ptr(v_), ptr(kk_), ptr(a_), ptr(state_c), ptr(new_state), ptr(g_), ptr(rk_),
         ptr(gw_), ptr(gb_), ptr(out), B, H, N, float(eps), dt_code(r_), _w_flag(w_, r_.dtype), stream_ptr(r_)),
         "fused_recurrent_output_prepare")
@@ -119,7 +121,7 @@ def fused_recurrent_output_prepare_raw(r, w_raw, k_raw, v, a, state, g, k_k, k_a
                                        force_fallback: bool = False, out=None, new_state=None, w_bias=None,
                                        a_bias=None, a_is_raw: bool = False, v_first=None, v_gate=None,
                                        v_gate_bias=None, v_gate_is_raw: bool = False, v_out=None,
-                                       state_prefetch: bool = False):
+                                       state_prefetch: bool = False, elapsed=None, advance_elapsed: bool = False):
     """Decode recurrence / output prep straight from raw w, k and sigmoid(a).
 
     The keyword arguments after ``force_fallback`` are extensions of this package (the reference
@@ -127,9 +129,18 @@ def fused_recurrent_output_prepare_raw(r, w_raw, k_raw, v, a, state, g, k_k, k_a
     the ``v_first`` interpolation into the same kernel, and allow in-place operation by passing
     ``new_state=state``.  ``state_prefetch=True`` lets the kernel load its state tile before it waits for the
     kernel that precedes it in the stream: only for call sequences in which that kernel never writes ``state``
-    (a decode step, where a projection precedes the recurrence)."""
+    (a decode step, where a projection precedes the recurrence).  A float16 ``state`` selects the FP16-state lane
+    (fp32 arithmetic, state rounded on the store); ``elapsed`` (int32 ``[B]``) adds the decay dither of the reference's
+    native_wkv_fp16 extension and ``advance_elapsed`` increments it after the step."""
     no_fallback(force_fallback, "fused_recurrent_output_prepare_raw")
-    B, H, N = _state_shape(state)
+    B, H, N = _state_shape(state, allow_f16=True)
+    if elapsed is not None:
+        if state.dtype != torch.float16:
+            raise ValueError("elapsed (decay dither) belongs to the float16-state lane")
+        if not (elapsed.is_cuda and elapsed.dtype == torch.int32 and elapsed.is_contiguous() and int(elapsed.numel()) == B):
+            raise ValueError("elapsed must be a contiguous CUDA int32 [B] tensor")
+    elif advance_elapsed:
+        raise ValueError("advance_elapsed needs elapsed")
     if int(block_n) < N:
         raise ValueError(f"block_n must be >= head_dim={N}; got {block_n}")
     if int(num_warps) not in {1, 2, 4, 8}:
@@ -151,16 +162,21 @@ def fused_recurrent_output_prepare_raw(r, w_raw, k_raw, v, a, state, g, k_k, k_a
         new_state = torch.empty_like(state_c)
     if out is None:
         out = torch.empty_like(r_)
-    _lib.check(_lib.lib.rwkv7_wkv7_output_prepare_raw(
-        ptr(r_), ptr(w_), ptr(k_), ptr(v_), ptr(a_), ptr(state_c), ptr(new_state), ptr(g_), ptr(params[0]),
-        ptr(params[1]), ptr(params[2]), ptr(params[3]), ptr(params[4]), ptr(out), ptr(opt[0]), ptr(opt[1]),
-        int(bool(a_is_raw)), ptr(opt[2]), ptr(opt[3]), ptr(opt[4]), int(bool(v_gate_is_raw)), ptr(v_out),
-        int(bool(state_prefetch)), B, H, N, float(eps), dt_code(r_), stream_ptr(r_)), "fused_recurrent_output_prepare_raw")
+    head = (ptr(r_), ptr(w_), ptr(k_), ptr(v_), ptr(a_), ptr(state_c), ptr(new_state), ptr(g_), ptr(params[0]),
+            ptr(params[1]), ptr(params[2]), ptr(params[3]), ptr(params[4]), ptr(out), ptr(opt[0]), ptr(opt[1]),
+            int(bool(a_is_raw)), ptr(opt[2]), ptr(opt[3]), ptr(opt[4]), int(bool(v_gate_is_raw)), ptr(v_out))
+    tail = (int(bool(state_prefetch)), B, H, N, float(eps), dt_code(r_), stream_ptr(r_))
+    if state_c.dtype == torch.float32:
+        _lib.check(_lib.lib.rwkv7_wkv7_output_prepare_raw(*head, *tail), "fused_recurrent_output_prepare_raw")
+    else:
+        _lib.check(_lib.lib.rwkv7_wkv7_output_prepare_raw_f16state(*head, ptr(elapsed), int(bool(advance_elapsed)), *tail),
+                   "fused_recurrent_output_prepare_raw", kernels=2 if advance_elapsed else 1)
     return (out.reshape(B, hidden) if flat else out.reshape(B, H, N)), new_state
 
 
-def _scan(name, r, w, k, v, kk, a, state, w_mode, prep=None, eps=0.0, chunk=0):
-    B, H, N = _state_shape(state)
+def _scan(name, r, w, k, v, kk, a, state, w_mode, prep=None, eps=0.0, chunk=0, ab_mode=False, w0=None, elapsed=None,
+          new_state=None):
+    B, H, N = _state_shape(state, allow_f16=not chunk)
     r_, flat = _as_bthn(r, B, H, N, "r")
     T = int(r_.shape[1])
     w_, k_, v_, kk_, a_ = (_as_bthn(t, B, H, N, n)[0] for t, n in ((w, "w"), (k, "k"), (v, "v"), (kk, "kk"), (a, "a")))
@@ -174,7 +190,8 @@ def _scan(name, r, w, k, v, kk, a, state, w_mode, prep=None, eps=0.0, chunk=0):
     elif w_.dtype != r_.dtype:
         raise ValueError("raw w must have the activation dtype")
     state_c = state.contiguous()
-    new_state = torch.empty_like(state_c)
+    if new_state is None:
+        new_state = torch.empty_like(state_c)
     out = torch.empty_like(r_)
     if chunk:
         _lib.check(_lib.lib.rwkv7_wkv7_chunk_scan(ptr(r_), ptr(w_), ptr(k_), ptr(v_), ptr(kk_), ptr(a_), ptr(state_c),
@@ -189,9 +206,17 @@ def _scan(name, r, w, k, v, kk, a, state, w_mode, prep=None, eps=0.0, chunk=0):
             rk_, gw_, gb_ = r_k.contiguous(), gn_w.contiguous(), gn_b.contiguous()
             require_cuda(g_, rk_, gw_, gb_, what=name)
             same_dtype(r_, g_, rk_, gw_, gb_, what=name)
-        _lib.check(_lib.lib.rwkv7_wkv7_scan(ptr(r_), ptr(w_), ptr(k_), ptr(v_), ptr(kk_), ptr(a_), ptr(state_c),
-                                            ptr(new_state), ptr(out), ptr(g_), ptr(rk_), ptr(gw_), ptr(gb_),
-                                            float(eps), B, T, H, N, dt_code(r_), w_mode, stream_ptr(r_)), name)
+        if state_c.dtype == torch.float32 and not (ab_mode or w0 is not None or elapsed is not None):
+            _lib.check(_lib.lib.rwkv7_wkv7_scan(ptr(r_), ptr(w_), ptr(k_), ptr(v_), ptr(kk_), ptr(a_), ptr(state_c),
+                                                ptr(new_state), ptr(out), ptr(g_), ptr(rk_), ptr(gw_), ptr(gb_),
+                                                float(eps), B, T, H, N, dt_code(r_), w_mode, stream_ptr(r_)), name)
+        else:
+            if state_c.dtype != torch.float16:
+                raise ValueError(f"{name}: the neg_kk / kka / w0 / elapsed operand forms belong to the float16-state lane")
+            _lib.check(_lib.lib.rwkv7_wkv7_scan_f16state(
+                ptr(r_), ptr(w_), ptr(k_), ptr(v_), ptr(kk_), ptr(a_), ptr(state_c), ptr(new_state), ptr(out), ptr(g_),
+                ptr(rk_), ptr(gw_), ptr(gb_), float(eps), B, T, H, N, dt_code(r_), w_mode, int(bool(ab_mode)), ptr(w0),
+                ptr(elapsed), stream_ptr(r_)), name)
     return (out.reshape(B, T, H * N) if flat else out), new_state
 
 
@@ -272,3 +297,49 @@ def dplr_chunk_scan(r, w, k, v, kk, a, state, *, chunk_size: int = 64, force_fal
             and r.dtype == torch.float16:  # the tensor-core kernel is fp16 only
         return _scan("dplr_chunk_scan", r, w, k, v, kk, a, state, 0, chunk=int(chunk_size))
     return _scan("dplr_chunk_scan", r, w, k, v, kk, a, state, 0)
+
+
+# ------------------------------------------------------------------ FP16-state lane of the native_wkv_fp16 extension
+def native_fp16_recurrent_should_use(*, state_dtype, input_dtype, head_dim: int) -> bool:
+    """rwkv7_hf/native_wkv_fp16.py:597-608."""
+    return bool(state_dtype == torch.float16 and input_dtype == torch.float16 and int(head_dim) == 64)
+
+
+def native_fp16_recurrent_output_prepare_raw(r, w_raw, k_raw, v, a, state, g, k_k, k_a, r_k, norm_weight, norm_bias,
+                                             elapsed, *, advance_elapsed: bool, eps: float):
+    """Decode step on an fp16 ``state [B,H,64,64]`` updated IN PLACE, with the decay dither phased by ``elapsed``
+    (int32 ``[B]``; incremented when ``advance_elapsed``).  Same signature, argument checks and return value (the
+    prepared output) as rwkv7_hf/native_wkv_fp16.py:678-770."""
+    if state.dim() != 4:
+        raise ValueError("state must be [B,H,64,64]")
+    if not native_fp16_recurrent_should_use(state_dtype=state.dtype, input_dtype=r.dtype, head_dim=int(state.shape[-1])):
+        raise ValueError("native FP16 recurrence received an unsupported dtype or shape")
+    tensors = (r, w_raw, k_raw, v, a, state, g, k_k, k_a, r_k, norm_weight, norm_bias)
+    if not all(t.is_cuda and t.dtype == torch.float16 and t.is_contiguous() for t in tensors):
+        raise ValueError("native FP16 recurrence requires contiguous CUDA fp16 tensors")
+    if not (elapsed.is_cuda and elapsed.dtype == torch.int32 and elapsed.is_contiguous()):
+        raise ValueError("elapsed must be a contiguous CUDA int32 tensor")
+    out, _ = fused_recurrent_output_prepare_raw(r, w_raw, k_raw, v, a, state, g, k_k, k_a, r_k, norm_weight, norm_bias,
+                                                eps=float(eps), new_state=state, elapsed=elapsed,
+                                                advance_elapsed=bool(advance_elapsed))
+    return out
+
+
+def native_fp16_sequence(r, w, k, v, neg_kk, kka, state, elapsed, *, w0=None):
+    """FP16-state scan over ``[B,T,H,64]`` (rwkv7_hf/native_wkv_fp16.py:773-821): ``w`` is the raw decay input (``w0`` is
+    added to it when given), ``neg_kk = -kk``, ``kka = kk*a``; ``state`` is updated in place; token ``t`` uses the dither
+    phase ``elapsed + t``.  Returns the recurrent output in the layout of ``r``."""
+    if state.dim() != 4 or r.dim() != 4:
+        raise ValueError("state and sequence tensors must be rank four")
+    if not native_fp16_recurrent_should_use(state_dtype=state.dtype, input_dtype=r.dtype, head_dim=int(state.shape[-1])):
+        raise ValueError("native FP16 sequence received an unsupported dtype or shape")
+    if not all(t.is_cuda and t.dtype == torch.float16 and t.is_contiguous() for t in (r, w, k, v, neg_kk, kka, state)):
+        raise ValueError("native FP16 sequence requires contiguous CUDA fp16 tensors")
+    if not (elapsed.is_cuda and elapsed.dtype == torch.int32 and elapsed.is_contiguous()
+            and int(elapsed.numel()) == int(r.shape[0])):
+        raise ValueError("elapsed must be a contiguous CUDA int32 [B] tensor")
+    if w0 is not None and not (w0.is_cuda and w0.dtype == torch.float16 and w0.is_contiguous()):
+        raise ValueError("w0 must be contiguous CUDA fp16")
+    out, _ = _scan("native_fp16_sequence", r, w, k, v, neg_kk, kka, state, 2, ab_mode=True, w0=w0, elapsed=elapsed,
+                   new_state=state)
+    return out

@@ -101,6 +101,29 @@ int rwkv7_wkv7_output_prepare_raw(const void* r, const void* w_raw, const void* 
                                   void* v_out, int state_prefetch,
                                   int B, int H, int N, float eps, int dtype, void* stream);
 
+/* The same two operators with the recurrent state stored in fp16 [B,H,64,64] (half the state traffic of a decode
+ * step); arithmetic stays fp32, the new state is rounded to nearest on the store and the output is formed from the
+ * state as stored.  They replace the reference's opt-in FP16-state lanes: the Triton output-prepare kernels given an fp16
+ * state (rwkv7_hf/fused_recurrent_update.py:655-699,1030,1149) and, with `elapsed`, the native_wkv_fp16 extension
+ * recurrent_output_raw(r,w_raw,k_raw,v,a,state,g,k_k,k_a,r_k,norm_w,norm_b,elapsed,advance,eps)
+ * (rwkv7_hf/native_wkv_fp16.py:54-71,200-333).
+ *   elapsed [B] int32 (may be NULL): per-sequence step counters.  When given, the decay operand is formed as in that
+ *   extension: 1 + fp16(decay - 1 + rot(elapsed[b] + h*64 + j)), rot(x) = 2^-41 * int32(2654435769 * x), a zero-mean
+ *   offset below 2^-10 that keeps round-to-nearest from freezing slowly decaying entries (:118-128).
+ *   advance_elapsed != 0: elapsed[b] += 1 for every b after the step (a second tiny launch in stream order). */
+int rwkv7_wkv7_output_prepare_f16state(const void* r, const void* w, const void* k, const void* v, const void* kk,
+                                       const void* a, const void* state_in, void* state_out, const void* g,
+                                       const void* r_k, const void* gn_w, const void* gn_b, void* out,
+                                       int B, int H, int N, float eps, int dtype, int w_is_f32, void* stream);
+int rwkv7_wkv7_output_prepare_raw_f16state(const void* r, const void* w_raw, const void* k_raw, const void* v,
+                                           const void* a, const void* state_in, void* state_out, const void* g,
+                                           const void* k_k, const void* k_a, const void* r_k,
+                                           const void* gn_w, const void* gn_b, void* out,
+                                           const void* w_bias, const void* a_bias, int a_is_raw,
+                                           const void* v_first, const void* v_gate, const void* v_gate_bias,
+                                           int v_gate_is_raw, void* v_out, int* elapsed, int advance_elapsed,
+                                           int state_prefetch, int B, int H, int N, float eps, int dtype, void* stream);
+
 /* ------------------------------------------------------------------ WKV-7 scan over T tokens
  * Replaces fused_recurrent_scan (rwkv7_hf/fused_recurrent_update.py:1299), _clampw (:1420),
  * _output_prepare (:1710), self_chunk_rwkv7 (rwkv7_hf/self_chunk_rwkv7.py:33) and dplr_chunk_scan
@@ -112,6 +135,18 @@ int rwkv7_wkv7_scan(const void* r, const void* w, const void* k, const void* v, 
                     const float* state_in, float* state_out, void* y,
                     const void* g, const void* r_k, const void* gn_w, const void* gn_b, float eps,
                     int B, int T, int H, int N, int dtype, int w_mode, void* stream);
+
+/* The scan with an fp16 state (loaded to fp32 registers, rounded back once at the end of the call) and the operand
+ * forms of the reference's FP16-state sequence kernel sequence(r,w,k,v,neg_kk,kka,state,elapsed,w0,add_w0)
+ * (rwkv7_hf/native_wkv_fp16.py:335-452,773-821):
+ *   ab_mode != 0: `kk` holds -kk and `a` holds kk*a;  w0 [H*64] (may be NULL): added to raw w before the decay (w_mode 2);
+ *   elapsed [B] int32 (may be NULL, w_mode 2): token t uses the dither phase elapsed[b] + h*64 + j + t (see above).
+ * The reference rounds the state to fp16 after every token; this kernel keeps it in fp32 registers within a call. */
+int rwkv7_wkv7_scan_f16state(const void* r, const void* w, const void* k, const void* v, const void* kk, const void* a,
+                             const void* state_in, void* state_out, void* y,
+                             const void* g, const void* r_k, const void* gn_w, const void* gn_b, float eps,
+                             int B, int T, int H, int N, int dtype, int w_mode, int ab_mode, const void* w0,
+                             const int* elapsed, void* stream);
 
 /* Chunked (WY / DPLR) form of the same scan with the intra-chunk products on tensor cores.
  * chunk in {16, 32, 64}; T % chunk == 0; fp16 activations only (RWKV7_ERR_UNSUPPORTED otherwise: callers route

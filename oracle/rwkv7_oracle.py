@@ -657,3 +657,100 @@ def new_cache(L, B, D, H, N, dtype):
                 xpa=[np.zeros((B, D), dtype) for _ in range(L)],
                 xpf=[np.zeros((B, D), dtype) for _ in range(L)],
                 v_first=np.zeros((B, H * N), dtype))
+
+
+# --------------------------------------------------------------------------
+# FP16-state lane (rwkv7_hf/native_wkv_fp16.py).  The reference's implementation of this lane is a CUDA extension
+# without a CPU route, so these restatements follow its kernels instruction by instruction (every __hfma2 / __hadd
+# rounds to fp16 once) but cannot be checked against reference outputs here: parity of this lane is pinned only
+# through the reference's own gate for it, agreement with the fp32-state operators within atol 3e-3 / rtol 1e-2 on
+# the state and cosine >= 0.999 on the outputs (tests/test_fused_recurrent_output_raw.py:44-141).  exp2f is exact
+# here; the extension is built with --use_fast_math.
+# --------------------------------------------------------------------------
+_H = np.float16
+
+
+def _hfma(a, b, c):
+    """__hfma: a*b + c with one rounding to fp16 (the product of two halves is exact in float64)."""
+    return (np.asarray(a, np.float64) * np.asarray(b, np.float64) + np.asarray(c, np.float64)).astype(_H)
+
+
+def _hadd(a, b):
+    return (np.asarray(a, np.float64) + np.asarray(b, np.float64)).astype(_H)
+
+
+def rotator1(x):
+    """native_wkv_fp16.py:118-121: 2^-41 * int32(2654435769 * uint32(x))."""
+    bits = (np.asarray(x, np.int64).astype(np.uint64) * np.uint64(2654435769)) & np.uint64(0xFFFFFFFF)
+    return np.float32(4.547473508864641e-13) * bits.astype(np.uint32).view(np.int32).astype(np.float32)
+
+
+def w_delta(w_raw, phase, w0=None):
+    """native_wkv_fp16.py:123-139: fp16(exp2(-0.875.../(1+exp2(-1.4427 w))) - 1 + rotator1(phase)), i.e. decay - 1
+    plus the dither; ``w0`` is added to the raw value first when given."""
+    w = np.asarray(w_raw, np.float32)
+    if w0 is not None:
+        w = w + np.asarray(w0, np.float32)
+    d = np.exp2(np.float32(-0.8750387749145276) / (np.float32(1) + np.exp2(np.float32(-1.4426950408889634) * w))) \
+        - np.float32(1) + rotator1(phase)
+    return d.astype(np.float32).astype(_H)
+
+
+def _fp16_state_step(state, neg_kk, bvec, wd, k, v, r):
+    """The half2 recurrence of both kernels (native_wkv_fp16.py:279-300, 398-425) for state [...,64(i),64(j)] fp16 and
+    per-channel fp16 vectors [...,64]: returns (new_state, recurrent [...,64(i)])."""
+    st = np.asarray(state, _H).copy()
+    lead = st.shape[:-2]
+    sa2 = np.zeros(lead + (64, 2), _H)                       # half2 accumulator per row i: lanes = even / odd columns
+    for j in range(32):
+        sa2 = _hfma(neg_kk[..., None, 2 * j:2 * j + 2], st[..., :, 2 * j:2 * j + 2], sa2)
+    sa = _hadd(sa2[..., 0], sa2[..., 1])                     # [...,64(i)]
+    y2 = np.zeros(lead + (64, 2), _H)
+    vi = np.asarray(v, _H)[..., :, None]
+    for j in range(32):
+        sl = slice(2 * j, 2 * j + 2)
+        s = st[..., :, sl]
+        s = _hfma(s, wd[..., None, sl], _hfma(k[..., None, sl], vi, _hfma(sa[..., None], bvec[..., None, sl], s)))
+        st[..., :, sl] = s
+        y2 = _hfma(s, r[..., None, sl], y2)
+    return st, _hadd(y2[..., 0], y2[..., 1])
+
+
+def native_fp16_recurrent_output_prepare_raw(r, w_raw, k_raw, v, a, state, g, k_k, k_a, r_k, gn_w, gn_b, elapsed, eps):
+    """native_wkv_fp16.py:200-333.  Vectors [B,H,64] fp16, state [B,H,64,64] fp16, per-head parameters [H,64] /
+    [H*64], elapsed [B] int.  Returns (prepared [B,H,64] fp16, new_state fp16)."""
+    B, H, N = np.asarray(r).shape
+    f = lambda x: np.asarray(x, _H).astype(np.float32)
+    par = lambda x: np.asarray(x, _H).reshape(H, N).astype(np.float32)[None]
+    kk_un = f(k_raw) * par(k_k)
+    nrm = np.sqrt((kk_un * kk_un).sum(-1, keepdims=True, dtype=np.float32))
+    kk_val = kk_un / np.maximum(nrm, np.float32(1e-12))
+    af, ka = f(a), par(k_a)
+    k_val = (f(k_raw) * (af * ka + (np.float32(1) - ka))).astype(_H)
+    kk_h = kk_val.astype(_H)
+    bvec = (kk_h.astype(np.float32) * af).astype(_H)
+    phase = np.asarray(elapsed, np.int64).reshape(B, 1, 1) + (np.arange(H).reshape(1, H, 1) * N + np.arange(N).reshape(1, 1, N))
+    wd = w_delta(w_raw, phase)
+    new_state, rec = _fp16_state_step(state, -kk_h, bvec, wd, k_val, np.asarray(v, _H), np.asarray(r, _H))
+    rec = rec.astype(np.float32)
+    mean = rec.mean(-1, keepdims=True, dtype=np.float32)
+    cen = rec - mean
+    var = (cen * cen).mean(-1, keepdims=True, dtype=np.float32)
+    corr = (f(r) * k_val.astype(np.float32) * par(r_k)).sum(-1, keepdims=True, dtype=np.float32)
+    prepared = (cen / np.sqrt(var + np.float32(eps)) * par(gn_w) + par(gn_b) + corr * f(v)) * f(g)
+    return prepared.astype(_H), new_state
+
+
+def native_fp16_sequence(r, w, k, v, neg_kk, kka, state, elapsed, w0=None):
+    """native_wkv_fp16.py:335-452: [B,T,H,64] fp16 operands, state [B,H,64,64] fp16.  Token t uses the dither phase
+    elapsed[b] + h*64 + j + t.  Returns (y [B,T,H,64] fp16, final_state fp16)."""
+    B, T, H, N = np.asarray(r).shape
+    st = np.asarray(state, _H).copy()
+    y = np.zeros((B, T, H, N), _H)
+    base = np.asarray(elapsed, np.int64).reshape(B, 1, 1) + (np.arange(H).reshape(1, H, 1) * N + np.arange(N).reshape(1, 1, N))
+    w0v = None if w0 is None else np.asarray(w0, _H).reshape(1, H, N)
+    for t in range(T):
+        wd = w_delta(np.asarray(w, _H)[:, t], base + t, w0v)
+        st, y[:, t] = _fp16_state_step(st, np.asarray(neg_kk, _H)[:, t], np.asarray(kka, _H)[:, t], wd,
+                                       np.asarray(k, _H)[:, t], np.asarray(v, _H)[:, t], np.asarray(r, _H)[:, t])
+    return y, st
