@@ -118,7 +118,7 @@ def shape_config(shape, quant, batch, layers=0):
 
 # ------------------------------------------------------------------------------------------ model
 def build_model(shape, tp_world, tp_rank, tp_group, device, layers_override=0, quant="mm4", seed=0, full_then_shard=False,
-                state_dtype=None):
+                state_dtype=None, overlap_rows=0):
     """Random-init model of the named shape, projections quantised on the GPU, fp16 head.
     The token-shift / key-scale parameters the reference constructs as zeros are re-initialised (seeded) so
     that every term of the recurrence is exercised.  ``full_then_shard``: build the unsharded model from the seed
@@ -140,7 +140,8 @@ def build_model(shape, tp_world, tp_rank, tp_group, device, layers_override=0, q
         try:
             with torch.device(device):
                 return hb.RWKV7ForCausalLM(cfg, tp_world=world, tp_rank=rank, tp_group=group,
-                                           state_dtype=state_dtype or torch.float32)
+                                           state_dtype=state_dtype or torch.float32, tp_shard_head=world > 1,
+                                           tp_overlap_rows=overlap_rows if world > 1 else 0)
         finally:
             torch.set_default_dtype(old)
 
@@ -166,7 +167,7 @@ def build_model(shape, tp_world, tp_rank, tp_group, device, layers_override=0, q
     if full_then_shard and tp_world > 1:
         full = construct(1, 0, None)
         init(full, 1 + seed)
-        sd = hb.shard_state_dict(full.state_dict(), tp_world, tp_rank)
+        sd = hb.shard_state_dict(full.state_dict(), tp_world, tp_rank, shard_head=True)
         model = construct(tp_world, tp_rank, tp_group)
         model.load_state_dict({k: v.contiguous() for k, v in sd.items()})
         del full, sd
@@ -242,6 +243,9 @@ def main():
     ap.add_argument("--parallelism", default="tp", choices=["tp", "dp"],
                     help="N > 1: tp = head-sharded tensor parallelism (headline; independent replicas measured beside "
                          "it), dp = independent sequence batches on full replicas as the headline")
+    ap.add_argument("--tp-overlap-rows", type=int, default=128,
+                    help="tp: batches of at least twice this many rows per rank decode as two halves on two streams with "
+                         "their own communicators, hiding one half's all-reduces under the other half's kernels (0 = off)")
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-scan", action="store_true")
@@ -308,7 +312,8 @@ def main():
         _lib.LAUNCHES = 0
         model.rwkv7_forward_token(ids_host[0].to(dev), cache, use_graph=False)
         launches = _lib.LAUNCHES
-        graph = model._decode_graph(B)
+        greedy = model.tp_world > 1  # sharded head: the step ends in the arg-max token, no rank gathers the logits
+        graph = model._decode_graph(B, greedy)
         graph.bind(cache)
         ids_dev = ids_host.to(dev)
         # the clock sampler starts before the warm-up replays: nvidia-smi needs a moment before its first sample, and
@@ -330,15 +335,17 @@ def main():
         if e2e:
             # end to end: pinned ids -> H2D -> step -> argmax -> D2H, the caller consuming the token before the next step
             tok_host = torch.empty((B,), dtype=torch.long).pin_memory()
+            def step_tokens(i):
+                out = model.rwkv7_forward_token(ids_host[i].to(dev, non_blocking=True), cache, return_tokens=greedy)
+                return out if greedy else out.argmax(-1)
+
             for i in range(3):
-                lg = model.rwkv7_forward_token(ids_host[i].to(dev, non_blocking=True), cache)
-                tok_host.copy_(lg.argmax(-1), non_blocking=True)
+                tok_host.copy_(step_tokens(i), non_blocking=True)
             barrier()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             for i in range(n_steps):
-                lg = model.rwkv7_forward_token(ids_host[warmup + i].to(dev, non_blocking=True), cache)
-                tok_host.copy_(lg.argmax(-1), non_blocking=True)
+                tok_host.copy_(step_tokens(warmup + i), non_blocking=True)
                 torch.cuda.current_stream().synchronize()
             e1.record()
             barrier()
@@ -358,7 +365,8 @@ def main():
         try:
             Bp = 8
             ref_model, _, _ = build_model(args.shape, 1, 0, None, dev, 2, args.quant, seed=7)
-            tpm, _, _ = build_model(args.shape, world, rank, tp_group, dev, 2, args.quant, seed=7, full_then_shard=True)
+            tpm, _, _ = build_model(args.shape, world, rank, tp_group, dev, 2, args.quant, seed=7, full_then_shard=True,
+                                    overlap_rows=4)  # batch 8 -> two halves of 4: the overlapped path is the one checked
             gen = torch.Generator().manual_seed(11)
             pids = torch.randint(0, V, (Bp, 6), generator=gen).to(dev)
             c_ref, c_tp = ref_model.new_cache(Bp), tpm.new_cache(Bp)
@@ -371,6 +379,11 @@ def main():
                 # the sharded run's best logit may differ from the unsharded choice only within fp16 noise
                 top = lr.argmax(-1)
                 same_tokens &= bool(((lt.max(-1).values - lt.gather(1, top[:, None])[:, 0]) < 2e-2).all())
+                if t == 5:  # the fused arg-max of the sharded head == arg-max of the gathered logits (on a cache copy)
+                    tk = tpm.rwkv7_forward_token(pids[:, t], c_chk, use_graph=True, return_tokens=True)
+                    same_tokens &= bool(torch.equal(tk, lt.argmax(-1)))
+                elif t == 4:
+                    c_chk = c_tp.clone()
             s_ref = torch.stack(c_ref._state)[:, :, rank * (H // world):(rank + 1) * (H // world)]
             s_err = float((torch.stack(c_tp._state) - s_ref).norm() / s_ref.norm())
             flag = torch.tensor([1.0 if (worst > 0.9995 and same_tokens and s_err < 1e-2) else 0.0], device=dev)
@@ -391,7 +404,7 @@ def main():
     if world > 1 and not args.no_side:
         other_tp = not use_tp
         m2, _, _ = build_model(args.shape, world if other_tp else 1, rank if other_tp else 0, tp_group if other_tp else None,
-                               dev, args.layers, args.quant)
+                               dev, args.layers, args.quant, overlap_rows=args.tp_overlap_rows)
         B2 = args.batch * world if other_tp else args.batch
         ms2, _, _, c2, _, _ = time_decode(m2, B2, 0 if other_tp else rank, False, n_steps=min(steps, 20), e2e=False)
         side = {"value": args.batch * world / (ms2 * 1e-3), "unit": "tok/s", "ms_per_step": ms2, "global_batch": args.batch * world,
@@ -407,10 +420,14 @@ def main():
     # fixed: weak scaling), NCCL all-reduces of the [B,D] partial sums inside the decode graph.
     sdt = torch.float16 if args.state == "fp16" else torch.float32
     if use_tp:
-        model, cfg, nq = build_model(args.shape, world, rank, tp_group, dev, args.layers, args.quant, state_dtype=sdt)
+        model, cfg, nq = build_model(args.shape, world, rank, tp_group, dev, args.layers, args.quant, state_dtype=sdt,
+                                     overlap_rows=args.tp_overlap_rows)
         B, shard = args.batch * world, world
-        parallelism = (f"tp{world}: heads, recurrent state and projections sharded, global batch {B} on every rank, "
-                       "two NCCL all-reduces per layer inside the decode graph")
+        parallelism = (f"tp{world}: heads, recurrent state, projections and the head's vocabulary sharded, global batch {B} on "
+                       "every rank, two NCCL all-reduces per layer inside the decode graph"
+                       + (f", batch decoded as two halves of {B // 2} rows on two streams / communicators"
+                          if args.tp_overlap_rows and B >= 2 * args.tp_overlap_rows else "")
+                       + "; the step ends in the greedy token (local arg-max + one [B,2] all-gather)")
     else:
         model, cfg, nq = build_model(args.shape, 1, 0, None, dev, args.layers, args.quant, state_dtype=sdt)
         B, shard = args.batch, 1
@@ -427,7 +444,7 @@ def main():
         for Bg in (64, 256):
             ms_s, _, _, c_s, _, _ = time_decode(model, Bg, 0, False, n_steps=min(steps, 20), e2e=False)
             strong[f"global_batch_{Bg}"] = {"value": Bg / (ms_s * 1e-3), "unit": "tok/s", "ms_per_step": ms_s}
-            model._graphs.pop(Bg, None)
+            model._graphs.pop((Bg, True), None)
             del c_s
             torch.cuda.empty_cache()
 

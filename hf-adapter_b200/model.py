@@ -30,6 +30,7 @@ from . import norm_mix as _nm
 from . import prep as _prep
 from . import quant as _q
 from . import recurrent as _rec
+from . import sharding as _sh
 from .cache import NativeRWKV7Cache
 
 
@@ -161,9 +162,13 @@ class RWKV7ForCausalLM(nn.Module):
     """``RWKV7ForCausalLM`` == the native model, as in the reference (rwkv7_hf/__init__.py:17-20)."""
 
     def __init__(self, config: NativeRWKV7Config, tp_world: int = 1, tp_rank: int = 0, tp_group=None,
-                 state_dtype=torch.float32):
+                 state_dtype=torch.float32, tp_shard_head: bool = False, tp_overlap_rows: int = 0):
         """``state_dtype=torch.float16`` selects the reference's opt-in FP16-state lane (rwkv7_hf/native_wkv_fp16.py):
-        caches hold the recurrent state in fp16 and the decode step dithers the decay; fp16 activations only."""
+        caches hold the recurrent state in fp16 and the decode step dithers the decay; fp16 activations only.
+        ``tp_shard_head``: every rank holds ``vocab/P`` rows of the head; full logits are all-gathered, greedy tokens
+        come from a local arg-max and one tiny exchange.  ``tp_overlap_rows`` > 0: decode batches of at least twice
+        that many rows run as two halves on two streams with their own communicators, so one half's all-reduces hide
+        under the other half's kernels."""
         super().__init__()
         if state_dtype not in (torch.float32, torch.float16):
             raise ValueError("state_dtype must be torch.float32 or torch.float16")
@@ -175,7 +180,16 @@ class RWKV7ForCausalLM(nn.Module):
         self.config = config
         self.tp_world, self.tp_rank, self.tp_group = int(tp_world), int(tp_rank), tp_group
         self.model = NativeRWKV7Model(config, tp_world)
-        self.lm_head = nn.Linear(config.hidden_size, config.vocab_size, bias=False)
+        self.tp_shard_head = bool(tp_shard_head) and self.tp_world > 1
+        if self.tp_shard_head and config.vocab_size % self.tp_world:
+            raise ValueError("vocab_size must be divisible by the tensor-parallel world size to shard the head")
+        self.lm_head = nn.Linear(config.hidden_size, config.vocab_size // (self.tp_world if self.tp_shard_head else 1), bias=False)
+        self.tp_overlap_rows = int(tp_overlap_rows) if self.tp_world > 1 else 0
+        # the second half of an overlapped step needs a communicator of its own: two collectives of ONE communicator
+        # launched from two graph branches may start in different orders on different ranks
+        self._tp_group_b = None
+        if self.tp_overlap_rows and tp_group not in (None, False):
+            self._tp_group_b = torch.distributed.new_group(ranks=torch.distributed.get_process_group_ranks(tp_group))
         self._graphs = {}
         self._side_streams = {}
 
@@ -201,21 +215,59 @@ class RWKV7ForCausalLM(nn.Module):
             st = self._side_streams[(device, index)] = torch.cuda.Stream(device=device)
         return st
 
-    def _all_reduce(self, t):
-        if self.tp_world > 1:
-            torch.distributed.all_reduce(t, group=self.tp_group)
+    def _all_reduce(self, t, group=None):
+        # tp_group=False: one rank's share of the work without the collective (single-process timing of a shard)
+        if self.tp_world > 1 and self.tp_group is not False:
+            torch.distributed.all_reduce(t, group=group if group is not None else self.tp_group)
         return t
+
+    def _head(self, xn, greedy: bool, group=None):
+        """Final projection: logits ``[B,V]`` (all-gathered over the vocabulary shards when the head is sharded) or, with
+        ``greedy``, the arg-max token of every row (local arg-max + one [B,2] exchange per rank)."""
+        local = _linear(self.lm_head, xn)
+        if not self.tp_shard_head or self.tp_group is False:
+            return local.argmax(-1) if greedy else local
+        group = group if group is not None else self.tp_group
+        if greedy:
+            return _sh.sharded_argmax(local, self.tp_rank, self.tp_world, group)
+        rows = int(local.shape[0])
+        parts = torch.empty((self.tp_world * rows, int(local.shape[1])), device=local.device, dtype=local.dtype)
+        torch.distributed.all_gather_into_tensor(parts, local.contiguous(), group=group)  # rank-major concatenation
+        return parts.view(self.tp_world, rows, -1).permute(1, 0, 2).reshape(rows, -1)
 
     # ------------------------------------------------------------------ decode
     @torch.no_grad()
-    def _decode_step(self, ids, cache: NativeRWKV7Cache):
-        """One token for every sequence; mutates the cache tensors in place.  Returns logits [B,V]."""
+    def _decode_step(self, ids, cache: NativeRWKV7Cache, greedy: bool = False):
+        """One token for every sequence; mutates the cache tensors in place.  Returns logits ``[B,V]`` (or the greedy
+        tokens ``[B]``).  With ``tp_overlap_rows`` set and enough rows, the batch runs as two halves on two streams."""
         state, xpa, xpf, v_first = cache
+        ids = ids.reshape(-1)
+        B = int(ids.shape[0])
+        if (self.tp_overlap_rows and B >= 2 * self.tp_overlap_rows and B % 2 == 0
+                and (cache._elapsed is None or B % 8 == 0)):  # (a slice of the int32 counters must stay 16-byte aligned)
+            dev = ids.device
+            main, second = torch.cuda.current_stream(dev), self._side_stream(dev, 7)
+            second.wait_stream(main)
+            half = B // 2
+            outs = []
+            for hi, (lo, up) in enumerate(((0, half), (half, B))):
+                view = ([t[lo:up] for t in state], [t[lo:up] for t in xpa], [t[lo:up] for t in xpf], v_first[lo:up],
+                        None if cache._elapsed is None else cache._elapsed[lo:up])
+                with torch.cuda.stream(second if hi else main):
+                    outs.append(self._decode_rows(ids[lo:up], view, greedy, self._tp_group_b if hi else None, 10 * hi))
+            main.wait_stream(second)
+            for o in outs:
+                o.record_stream(main)
+            return torch.cat(outs, 0)
+        return self._decode_rows(ids, (state, xpa, xpf, v_first, cache._elapsed), greedy, None, 0)
+
+    def _decode_rows(self, ids, tensors, greedy, group, stream_base):
+        state, xpa, xpf, v_first, elapsed_t = tensors
         H, N = self.model.layers[0].attn.num_heads, self.config.head_dim
         x = F.embedding(ids.reshape(-1), self.model.embeddings.weight)
         B = int(x.shape[0])
         L = len(self.model.layers)
-        elapsed = cache._elapsed if state[0].dtype == torch.float16 else None
+        elapsed = elapsed_t if state[0].dtype == torch.float16 else None
         for i, layer in enumerate(self.model.layers):
             at, ff = layer.attn, layer.ffn
             if i == 0:
@@ -225,7 +277,7 @@ class RWKV7ForCausalLM(nn.Module):
             # The LoRA chain does not depend on r/k/v: it runs on a side stream (a parallel branch of the decode
             # graph once captured) and joins before the recurrence.
             main = torch.cuda.current_stream(x.device)
-            side = self._side_stream(x.device)
+            side = self._side_stream(x.device, stream_base)
             side.wait_stream(main)
             wl, al, gl = at.w_lora.lora, at.a_lora.lora, at.g_lora.lora
             with torch.cuda.stream(side):
@@ -247,7 +299,7 @@ class RWKV7ForCausalLM(nn.Module):
                 main.wait_stream(side)
             else:
                 # independent projections on separate branches: the tail of one overlaps the ramp-up of the next
-                sk, sv = self._side_stream(x.device, 1), self._side_stream(x.device, 2)
+                sk, sv = self._side_stream(x.device, stream_base + 1), self._side_stream(x.device, stream_base + 2)
                 sk.wait_stream(main)
                 sv.wait_stream(main)
                 with torch.cuda.stream(sk):
@@ -266,15 +318,16 @@ class RWKV7ForCausalLM(nn.Module):
                 r, w_raw, k, v, a_pre, state[i], g, at.k_k, at.k_a, at.r_k, at.g_norm.weight, at.g_norm.bias,
                 eps=N * 1e-5, new_state=state[i], w_bias=wl[2].bias, a_bias=al[2].bias, a_is_raw=True,
                 state_prefetch=True, elapsed=elapsed, advance_elapsed=elapsed is not None and i == L - 1, **extra)
-            attn = self._all_reduce(_linear(at.o_proj, out))
+            attn = self._all_reduce(_linear(at.o_proj, out), group)
             x, mixed = _nm.fused_ffn_add_norm_mix_decode(x, attn, xpf[i], layer.ffn_norm.weight, layer.ffn_norm.bias, ff.x_k)
             hidden = _linear(ff.key, mixed, relu2=True)
             if self.tp_world > 1:
-                x = x + self._all_reduce(_linear(ff.value, hidden))
+                # the residual rides in rank 0's partial sum (the projection's add epilogue): no extra add kernel
+                x = self._all_reduce(_linear(ff.value, hidden, residual=x if self.tp_rank == 0 else None), group)
             else:
                 x = _linear(ff.value, hidden, residual=x)
         xn = _nm.layer_norm(x, self.model.norm.weight, self.model.norm.bias)
-        return _linear(self.lm_head, xn)
+        return self._head(xn, greedy, group)
 
     # ------------------------------------------------------------------ prefill
     @torch.no_grad()
@@ -333,18 +386,20 @@ class RWKV7ForCausalLM(nn.Module):
         if cache._elapsed is not None:
             cache._elapsed += T
         xn = _nm.layer_norm(x[:, T - keep:].contiguous(), self.model.norm.weight, self.model.norm.bias)
-        return _linear(self.lm_head, xn)
+        return self._head(xn.reshape(B * keep, -1), False).reshape(B, keep, -1)
 
     # ------------------------------------------------------------------ reference-facing API
     @torch.no_grad()
-    def rwkv7_forward_token(self, token_ids, cache: NativeRWKV7Cache, *, use_graph: bool = True):
-        """One decode token per sequence (rwkv7_hf/model_fast_api.py:190-244).  Returns logits ``[B,V]``."""
+    def rwkv7_forward_token(self, token_ids, cache: NativeRWKV7Cache, *, use_graph: bool = True, return_tokens: bool = False):
+        """One decode token per sequence (rwkv7_hf/model_fast_api.py:190-244).  Returns logits ``[B,V]``, or with
+        ``return_tokens`` the greedy next tokens ``[B]`` (the head's arg-max inside the step: with a vocabulary-sharded
+        head no rank ever holds, or exchanges, the full logits)."""
         ids = token_ids.reshape(-1)
         if use_graph:
-            g = self._decode_graph(int(ids.shape[0]))
+            g = self._decode_graph(int(ids.shape[0]), bool(return_tokens))
             logits = g.replay(ids, cache)
         else:
-            logits = self._decode_step(ids, cache)
+            logits = self._decode_step(ids, cache, greedy=bool(return_tokens))
         cache._seen_tokens += 1
         return logits
 
@@ -399,10 +454,11 @@ class RWKV7ForCausalLM(nn.Module):
         return torch.cat(out, dim=1)
 
     # ------------------------------------------------------------------ CUDA graph
-    def _decode_graph(self, batch: int) -> "DecodeGraph":
-        g = self._graphs.get(batch)
+    def _decode_graph(self, batch: int, greedy: bool = False) -> "DecodeGraph":
+        key = (batch, True) if greedy else batch
+        g = self._graphs.get(key)
         if g is None:
-            g = self._graphs[batch] = DecodeGraph(self, batch)
+            g = self._graphs[key] = DecodeGraph(self, batch, greedy)
         return g
 
 
@@ -417,8 +473,8 @@ class DecodeGraph:
     stepped alternately through one graph.  ``replay`` returns a copy of the static logits buffer unless
     ``copy_logits=False`` (the reference's default is to copy too)."""
 
-    def __init__(self, model: RWKV7ForCausalLM, batch: int):
-        self.model, self.batch = model, batch
+    def __init__(self, model: RWKV7ForCausalLM, batch: int, greedy: bool = False):
+        self.model, self.batch, self.greedy = model, batch, greedy
         dev = model.device
         self.ids = torch.zeros((batch,), device=dev, dtype=torch.long)
         self.cache = model.new_cache(batch)
@@ -428,12 +484,12 @@ class DecodeGraph:
         side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side):
             for _ in range(2):  # warm-up outside capture (allocator, lazy module loading)
-                model._decode_step(self.ids, self.cache)
+                model._decode_step(self.ids, self.cache, greedy)
         torch.cuda.current_stream(dev).wait_stream(side)
         self.cache.reset()
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
-            self.logits = model._decode_step(self.ids, self.cache)
+            self.logits = model._decode_step(self.ids, self.cache, greedy)
 
     def _static(self):
         return self.cache._tensors()

@@ -25,13 +25,16 @@ def shard_spec(name: str):
     return None
 
 
-def shard_state_dict(full, world: int, rank: int):
-    """Return rank ``rank``'s share of a full (unsharded) state dict of tensors or arrays."""
+def shard_state_dict(full, world: int, rank: int, shard_head: bool = False):
+    """Return rank ``rank``'s share of a full (unsharded) state dict of tensors or arrays.  ``shard_head``: the head's
+    vocabulary rows are split as well (``RWKV7ForCausalLM(tp_shard_head=True)``)."""
     if not 0 <= rank < world:
         raise ValueError("rank out of range")
     out = {}
     for name, t in full.items():
         spec = shard_spec(name)
+        if shard_head and name == "lm_head.weight":
+            spec = "rows"
         if spec is None or world == 1:
             out[name] = t
             continue
@@ -44,3 +47,25 @@ def shard_state_dict(full, world: int, rank: int):
         index[dim] = slice(rank * step, (rank + 1) * step)
         out[name] = t[tuple(index)]
     return out
+
+
+def pick_sharded_argmax(values, indices):
+    """``values`` / ``indices`` ``[P,B]``: every rank's best logit and its GLOBAL vocabulary index.  Returns the arg-max
+    per column with torch.argmax's tie rule (the lowest index wins)."""
+    import torch
+    best = values.max(dim=0).values
+    big = torch.iinfo(indices.dtype).max
+    return torch.where(values == best[None], indices, torch.full_like(indices, big)).min(dim=0).values
+
+
+def sharded_argmax(local_logits, rank: int, world: int, group=None):
+    """Greedy token over a vocabulary-sharded head: local (max, arg-max) per row, one all-gather of ``[B,2]`` floats per
+    rank (indices below 2^24 are exact in fp32), then the pick.  Every rank returns the same ``[B]`` int64 tokens."""
+    import torch
+    import torch.distributed as dist
+    vals, idx = local_logits.float().max(dim=-1)
+    mine = torch.stack([vals, (idx + rank * int(local_logits.shape[-1])).float()], dim=-1).contiguous()  # [B,2]
+    parts = torch.empty((world * int(mine.shape[0]), 2), device=mine.device, dtype=mine.dtype)  # rank-major concatenation
+    dist.all_gather_into_tensor(parts, mine, group=group)
+    parts = parts.view(world, -1, 2)
+    return pick_sharded_argmax(parts[..., 0], parts[..., 1].long())

@@ -76,6 +76,48 @@ def test_head_sharded_tp_two_gloo_ranks():
     assert sorted(results) == [(0, "ok"), (1, "ok")], results
 
 
+def _argmax_worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    from hf_adapter_b200.sharding import shard_state_dict, sharded_argmax
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g = torch.Generator().manual_seed(0)
+        logits = torch.randn(7, 64, generator=g).half()
+        logits[0, 5] = logits[0, 40] = 9.0     # a tie across the two shards: the lower index wins, as in torch.argmax
+        logits[1, 33] = logits[1, 34] = 9.0    # a tie inside one shard
+        logits[2, 63] = 9.0
+        Vl = 64 // world
+        tok = sharded_argmax(logits[:, rank * Vl:(rank + 1) * Vl], rank, world)
+        want = logits.float().argmax(-1)
+        assert torch.equal(tok, want), (tok, want)
+        assert int(tok[0]) == 5 and int(tok[1]) == 33 and int(tok[2]) == 63
+        head = {"lm_head.weight": np.arange(64 * 4).reshape(64, 4), "model.norm.weight": np.ones(4)}
+        sh = shard_state_dict(head, world, rank, shard_head=True)
+        assert sh["lm_head.weight"].shape == (Vl, 4) and sh["lm_head.weight"][0, 0] == rank * Vl * 4
+        assert shard_state_dict(head, world, rank)["lm_head.weight"].shape == (64, 4)
+        q.put((rank, "ok"))
+    except Exception as e:  # noqa: BLE001
+        q.put((rank, f"{type(e).__name__}: {e}"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_vocabulary_sharded_head_argmax_two_gloo_ranks():
+    """Greedy tokens from a vocabulary-sharded head (local arg-max + one [B,2] all-gather) equal torch.argmax over the
+    full logits, ties included."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 31500 + os.getpid() % 2000
+    procs = [ctx.Process(target=_argmax_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=240) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert sorted(results) == [(0, "ok"), (1, "ok")], results
+
+
 def test_shard_state_dict_errors():
     from hf_adapter_b200 import shard_state_dict
     sd = {"model.layers.0.attn.r_proj.weight": np.zeros((6, 4))}

@@ -13,7 +13,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, q):
+def _worker(rank, world, port, q, mode):
     sys.path.insert(0, ROOT)
     import torch.distributed as dist
     import hf_adapter_b200 as hb
@@ -27,8 +27,10 @@ def _worker(rank, world, port, q):
         cfg = hb.NativeRWKV7Config(vocab_size=256, hidden_size=128, num_hidden_layers=2, num_heads=2, head_dim=64,
                                    intermediate_size=256, decay_low_rank_dim=16, a_low_rank_dim=16, v_low_rank_dim=8,
                                    gate_low_rank_dim=32)
-        model = hb.RWKV7ForCausalLM(cfg, tp_world=world, tp_rank=rank, tp_group=dist.group.WORLD)
-        model.load_state_dict({k: v.contiguous() for k, v in hb.shard_state_dict(full, world, rank).items()})
+        fancy = mode == "sharded_head_overlap"  # vocabulary-sharded head, batch decoded as two halves on two communicators
+        model = hb.RWKV7ForCausalLM(cfg, tp_world=world, tp_rank=rank, tp_group=dist.group.WORLD, tp_shard_head=fancy,
+                                    tp_overlap_rows=1 if fancy else 0)
+        model.load_state_dict({k: v.contiguous() for k, v in hb.shard_state_dict(full, world, rank, shard_head=fancy).items()})
         model = model.cuda().eval()
         ids = torch.from_numpy(g["ids"]).cuda()
         logits, cache = model.rwkv7_prefill_native(ids, None)
@@ -37,8 +39,12 @@ def _worker(rank, world, port, q):
         toks, tok = [], logits[:, -1].argmax(-1)
         for i in range(4):
             toks.append(tok)
+            if fancy and i == 3:  # the step that ends in the arg-max token must agree with arg-max of the gathered logits
+                tk = model.rwkv7_forward_token(tok, cache.clone(), use_graph=True, return_tokens=True)
             lg = model.rwkv7_forward_token(tok, cache, use_graph=(i >= 2))
             tok = lg.argmax(-1)
+            if fancy and i == 3:
+                assert torch.equal(tk, tok)
         torch.cuda.synchronize()
         assert np.array_equal(torch.stack(toks, 1).cpu().numpy(), g["greedy"])
         np.testing.assert_allclose(lg.float().cpu().numpy(), g["final_logits"], rtol=3e-4, atol=3e-4)
@@ -53,11 +59,12 @@ def _worker(rank, world, port, q):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_head_sharded_tp_two_gpus():
+@pytest.mark.parametrize("mode", ["plain", "sharded_head_overlap"])
+def test_head_sharded_tp_two_gpus(mode):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29500 + os.getpid() % 2000
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    port = 29500 + os.getpid() % 2000 + (7 if mode == "plain" else 13)
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, mode)) for r in range(2)]
     for p in procs:
         p.start()
     results = [q.get(timeout=300) for _ in procs]
