@@ -118,7 +118,7 @@ def shape_config(shape, quant, batch, layers=0):
 
 # ------------------------------------------------------------------------------------------ model
 def build_model(shape, tp_world, tp_rank, tp_group, device, layers_override=0, quant="mm4", seed=0, full_then_shard=False,
-                state_dtype=None, overlap_rows=0):
+                state_dtype=None, overlap_rows=0, tp_comm="nccl"):
     """Random-init model of the named shape, projections quantised on the GPU, fp16 head.
     The token-shift / key-scale parameters the reference constructs as zeros are re-initialised (seeded) so
     that every term of the recurrence is exercised.  ``full_then_shard``: build the unsharded model from the seed
@@ -141,7 +141,7 @@ def build_model(shape, tp_world, tp_rank, tp_group, device, layers_override=0, q
             with torch.device(device):
                 return hb.RWKV7ForCausalLM(cfg, tp_world=world, tp_rank=rank, tp_group=group,
                                            state_dtype=state_dtype or torch.float32, tp_shard_head=world > 1,
-                                           tp_overlap_rows=overlap_rows if world > 1 else 0)
+                                           tp_overlap_rows=overlap_rows if world > 1 else 0, tp_comm=tp_comm)
         finally:
             torch.set_default_dtype(old)
 
@@ -243,9 +243,13 @@ def main():
     ap.add_argument("--parallelism", default="tp", choices=["tp", "dp"],
                     help="N > 1: tp = head-sharded tensor parallelism (headline; independent replicas measured beside "
                          "it), dp = independent sequence batches on full replicas as the headline")
-    ap.add_argument("--tp-overlap-rows", type=int, default=128,
+    ap.add_argument("--tp-overlap-rows", type=int, default=0,
                     help="tp: batches of at least twice this many rows per rank decode as two halves on two streams with "
                          "their own communicators, hiding one half's all-reduces under the other half's kernels (0 = off)")
+    ap.add_argument("--tp-comm", default="auto", choices=["auto", "peer", "nccl"],
+                    help="tp: sum the [B,D] partial outputs with this library's one-kernel sum over peer-mapped memory (plain "
+                         "peer stores, flags, bounded waits) or with NCCL all-reduce; auto = peer up to 4 GPUs (one-shot: every rank "
+                         "sends its whole partial to every peer), NCCL above")
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-scan", action="store_true")
@@ -254,6 +258,8 @@ def main():
     ap.add_argument("--no-side", action="store_true", help="N > 1: skip the side measurements (replicas, strong scaling)")
     args = ap.parse_args()
     steps, warmup = max(1, args.steps), max(3, args.warmup)
+    if args.tp_comm == "auto":
+        args.tp_comm = "peer" if int(os.environ.get("WORLD_SIZE", "1")) <= 4 else "nccl"
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     L, D, H, Fd, V = SHAPES[args.shape]
@@ -366,7 +372,7 @@ def main():
             Bp = 8
             ref_model, _, _ = build_model(args.shape, 1, 0, None, dev, 2, args.quant, seed=7)
             tpm, _, _ = build_model(args.shape, world, rank, tp_group, dev, 2, args.quant, seed=7, full_then_shard=True,
-                                    overlap_rows=4)  # batch 8 -> two halves of 4: the overlapped path is the one checked
+                                    overlap_rows=4, tp_comm=args.tp_comm)  # batch 8 -> two halves of 4: the overlapped path is checked
             gen = torch.Generator().manual_seed(11)
             pids = torch.randint(0, V, (Bp, 6), generator=gen).to(dev)
             c_ref, c_tp = ref_model.new_cache(Bp), tpm.new_cache(Bp)
@@ -404,7 +410,7 @@ def main():
     if world > 1 and not args.no_side:
         other_tp = not use_tp
         m2, _, _ = build_model(args.shape, world if other_tp else 1, rank if other_tp else 0, tp_group if other_tp else None,
-                               dev, args.layers, args.quant, overlap_rows=args.tp_overlap_rows)
+                               dev, args.layers, args.quant, overlap_rows=args.tp_overlap_rows, tp_comm=args.tp_comm)
         B2 = args.batch * world if other_tp else args.batch
         ms2, _, _, c2, _, _ = time_decode(m2, B2, 0 if other_tp else rank, False, n_steps=min(steps, 20), e2e=False)
         side = {"value": args.batch * world / (ms2 * 1e-3), "unit": "tok/s", "ms_per_step": ms2, "global_batch": args.batch * world,
@@ -421,10 +427,11 @@ def main():
     sdt = torch.float16 if args.state == "fp16" else torch.float32
     if use_tp:
         model, cfg, nq = build_model(args.shape, world, rank, tp_group, dev, args.layers, args.quant, state_dtype=sdt,
-                                     overlap_rows=args.tp_overlap_rows)
+                                     overlap_rows=args.tp_overlap_rows, tp_comm=args.tp_comm)
         B, shard = args.batch * world, world
         parallelism = (f"tp{world}: heads, recurrent state, projections and the head's vocabulary sharded, global batch {B} on "
-                       "every rank, two NCCL all-reduces per layer inside the decode graph"
+                       "every rank, two sums of the [B,D] partial outputs per layer inside the decode graph ("
+                       + ("this library's kernel over peer-mapped memory" if args.tp_comm == "peer" else "NCCL all-reduce") + ")"
                        + (f", batch decoded as two halves of {B // 2} rows on two streams / communicators"
                           if args.tp_overlap_rows and B >= 2 * args.tp_overlap_rows else "")
                        + "; the step ends in the greedy token (local arg-max + one [B,2] all-gather)")

@@ -162,13 +162,14 @@ class RWKV7ForCausalLM(nn.Module):
     """``RWKV7ForCausalLM`` == the native model, as in the reference (rwkv7_hf/__init__.py:17-20)."""
 
     def __init__(self, config: NativeRWKV7Config, tp_world: int = 1, tp_rank: int = 0, tp_group=None,
-                 state_dtype=torch.float32, tp_shard_head: bool = False, tp_overlap_rows: int = 0):
+                 state_dtype=torch.float32, tp_shard_head: bool = False, tp_overlap_rows: int = 0, tp_comm: str = "nccl"):
         """``state_dtype=torch.float16`` selects the reference's opt-in FP16-state lane (rwkv7_hf/native_wkv_fp16.py):
         caches hold the recurrent state in fp16 and the decode step dithers the decay; fp16 activations only.
         ``tp_shard_head``: every rank holds ``vocab/P`` rows of the head; full logits are all-gathered, greedy tokens
         come from a local arg-max and one tiny exchange.  ``tp_overlap_rows`` > 0: decode batches of at least twice
         that many rows run as two halves on two streams with their own communicators, so one half's all-reduces hide
-        under the other half's kernels."""
+        under the other half's kernels.  ``tp_comm``: "nccl" sums the partial outputs with the framework's all-reduce,
+        "peer" with this library's one-kernel sum over peer-mapped memory (fp16, up to 1024 rows; larger calls use NCCL)."""
         super().__init__()
         if state_dtype not in (torch.float32, torch.float16):
             raise ValueError("state_dtype must be torch.float32 or torch.float16")
@@ -184,6 +185,10 @@ class RWKV7ForCausalLM(nn.Module):
         if self.tp_shard_head and config.vocab_size % self.tp_world:
             raise ValueError("vocab_size must be divisible by the tensor-parallel world size to shard the head")
         self.lm_head = nn.Linear(config.hidden_size, config.vocab_size // (self.tp_world if self.tp_shard_head else 1), bias=False)
+        if tp_comm not in ("nccl", "peer"):
+            raise ValueError("tp_comm must be 'nccl' or 'peer'")
+        self.tp_comm = tp_comm
+        self._peer_ar = {}  # lane -> PeerAllReduce (created on first use: a collective set-up, outside graph capture)
         self.tp_overlap_rows = int(tp_overlap_rows) if self.tp_world > 1 else 0
         # the second half of an overlapped step needs a communicator of its own: two collectives of ONE communicator
         # launched from two graph branches may start in different orders on different ranks
@@ -215,19 +220,36 @@ class RWKV7ForCausalLM(nn.Module):
             st = self._side_streams[(device, index)] = torch.cuda.Stream(device=device)
         return st
 
-    def _all_reduce(self, t, group=None):
+    PEER_MAX_ROWS = 1024
+
+    def _all_reduce(self, t, lane: int = 0):
+        """Sum ``t`` over the tensor-parallel ranks in place.  ``lane`` 1 is the second half of an overlapped step (its own
+        communicator / peer buffers)."""
         # tp_group=False: one rank's share of the work without the collective (single-process timing of a shard)
-        if self.tp_world > 1 and self.tp_group is not False:
-            torch.distributed.all_reduce(t, group=group if group is not None else self.tp_group)
+        if self.tp_world == 1 or self.tp_group is False:
+            return t
+        rows = t.numel() // int(t.shape[-1])
+        if self.tp_comm == "peer" and t.dtype == torch.float16 and t.is_contiguous() and rows <= self.PEER_MAX_ROWS:
+            ar = self._peer_ar.get(lane)
+            if ar is None or rows * int(t.shape[-1]) > ar.slot_elems or ar.width != int(t.shape[-1]):
+                from .tp_comm import PeerAllReduce
+                if torch.cuda.is_current_stream_capturing():
+                    raise RuntimeError("the peer all-reduce buffers must exist before graph capture (run one eager step first)")
+                ar = self._peer_ar[lane] = PeerAllReduce(self.tp_group, max(rows, 64), int(t.shape[-1]), t.device)
+            return ar.all_reduce(t, out=t)
+        torch.distributed.all_reduce(t, group=self._lane_group(lane))
         return t
 
-    def _head(self, xn, greedy: bool, group=None):
+    def _lane_group(self, lane: int):
+        return self._tp_group_b if (lane and self._tp_group_b is not None) else self.tp_group
+
+    def _head(self, xn, greedy: bool, lane: int = 0):
         """Final projection: logits ``[B,V]`` (all-gathered over the vocabulary shards when the head is sharded) or, with
         ``greedy``, the arg-max token of every row (local arg-max + one [B,2] exchange per rank)."""
         local = _linear(self.lm_head, xn)
         if not self.tp_shard_head or self.tp_group is False:
             return local.argmax(-1) if greedy else local
-        group = group if group is not None else self.tp_group
+        group = self._lane_group(lane)
         if greedy:
             return _sh.sharded_argmax(local, self.tp_rank, self.tp_world, group)
         rows = int(local.shape[0])
@@ -254,14 +276,14 @@ class RWKV7ForCausalLM(nn.Module):
                 view = ([t[lo:up] for t in state], [t[lo:up] for t in xpa], [t[lo:up] for t in xpf], v_first[lo:up],
                         None if cache._elapsed is None else cache._elapsed[lo:up])
                 with torch.cuda.stream(second if hi else main):
-                    outs.append(self._decode_rows(ids[lo:up], view, greedy, self._tp_group_b if hi else None, 10 * hi))
+                    outs.append(self._decode_rows(ids[lo:up], view, greedy, hi, 10 * hi))
             main.wait_stream(second)
             for o in outs:
                 o.record_stream(main)
             return torch.cat(outs, 0)
-        return self._decode_rows(ids, (state, xpa, xpf, v_first, cache._elapsed), greedy, None, 0)
+        return self._decode_rows(ids, (state, xpa, xpf, v_first, cache._elapsed), greedy, 0, 0)
 
-    def _decode_rows(self, ids, tensors, greedy, group, stream_base):
+    def _decode_rows(self, ids, tensors, greedy, lane, stream_base):
         state, xpa, xpf, v_first, elapsed_t = tensors
         H, N = self.model.layers[0].attn.num_heads, self.config.head_dim
         x = F.embedding(ids.reshape(-1), self.model.embeddings.weight)
@@ -318,16 +340,16 @@ class RWKV7ForCausalLM(nn.Module):
                 r, w_raw, k, v, a_pre, state[i], g, at.k_k, at.k_a, at.r_k, at.g_norm.weight, at.g_norm.bias,
                 eps=N * 1e-5, new_state=state[i], w_bias=wl[2].bias, a_bias=al[2].bias, a_is_raw=True,
                 state_prefetch=True, elapsed=elapsed, advance_elapsed=elapsed is not None and i == L - 1, **extra)
-            attn = self._all_reduce(_linear(at.o_proj, out), group)
+            attn = self._all_reduce(_linear(at.o_proj, out), lane)
             x, mixed = _nm.fused_ffn_add_norm_mix_decode(x, attn, xpf[i], layer.ffn_norm.weight, layer.ffn_norm.bias, ff.x_k)
             hidden = _linear(ff.key, mixed, relu2=True)
             if self.tp_world > 1:
                 # the residual rides in rank 0's partial sum (the projection's add epilogue): no extra add kernel
-                x = self._all_reduce(_linear(ff.value, hidden, residual=x if self.tp_rank == 0 else None), group)
+                x = self._all_reduce(_linear(ff.value, hidden, residual=x if self.tp_rank == 0 else None), lane)
             else:
                 x = _linear(ff.value, hidden, residual=x)
         xn = _nm.layer_norm(x, self.model.norm.weight, self.model.norm.bias)
-        return self._head(xn, greedy, group)
+        return self._head(xn, greedy, lane)
 
     # ------------------------------------------------------------------ prefill
     @torch.no_grad()

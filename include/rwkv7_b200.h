@@ -331,6 +331,20 @@ int64_t rwkv7_a8w8_static_capacity_bytes(void);
 int rwkv7_a8w8_linear_static(const void* x, const int8_t* qw, const float* sw, const void* bias, const void* residual,
                              void* out, int M, int K, int Nout, int dtype, void* stream);
 
+/* ------------------------------------------------------------------ tensor-parallel sum over peer memory
+ * out[rows,D] = sum over the P ranks of partial[rows,D] (fp16, fp32 accumulation in rank order: bit-identical on every
+ * rank): the all-reduce behind the row-sharded o_proj / ffn.value of a head-sharded layer (the reference's TP plan,
+ * rwkv7_hf/model_config.py:37-53, uses the framework's all-reduce).  One kernel per GPU: plain peer stores into every
+ * peer's inbox, per-CTA flags, bounded waits (wait_ms, default 2000; a wait that runs out sets the device error word,
+ * see rwkv7_kernel_status, and the kernel returns without storing).
+ *   inbox_ptrs / flag_ptrs: host arrays of P device pointers, entry r = rank r's inbox [2][P][slot_elems] fp16 and flag
+ *   array [2][P][rwkv7_tp_allreduce_max_ctas()] u32 as mapped into THIS process (peer-mapped memory; zeroed, with a
+ *   barrier, before the first call).  counters: two u32 in local memory, zeroed at set-up.  Every rank must issue the
+ *   same sequence of calls with the same rows and D.  Calls that share inbox / flags / counters must not overlap on a GPU. */
+int rwkv7_tp_allreduce_max_ctas(void);
+int rwkv7_tp_allreduce(const void* partial, void* out, void* const* inbox_ptrs, void* const* flag_ptrs, void* counters,
+                       int rank, int world, int rows, int D, long long slot_elems, int wait_ms, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
