@@ -40,8 +40,8 @@ def decode_step_bytes(L, D, H, Fd, V, B, quant="mm4", group=128, ranks=(64, 64, 
     n_w = 4 * D * A + 2 * D * Fd
     if quant == "mm4":
         w_q, w_scales = n_w // 2, n_w // group * 2
-    else:  # int8 per output channel
-        w_q, w_scales = n_w, (4 * A + 2 * Fd) * 2
+    else:  # int8 per output channel (fp16 scales; the a8w8 format keeps them in fp32)
+        w_q, w_scales = n_w, (4 * A + 2 * Fd) * (4 if quant == "a8w8" else 2)
     rw, ra, rv, rg = ranks
     lora = (rw + ra + rg + rv) * (D + A) * 2
     weights = L * (w_q + w_scales + lora) + V * D * 2
@@ -111,7 +111,8 @@ def measured_peaks():
 
 def shape_config(shape, quant, batch, layers=0):
     L, D, H, Fd, V = SHAPES[shape]
-    return {"workload": f"rwkv7-{shape}-shape {'mm4-g128' if quant == 'mm4' else 'int8-per-channel'} decode, batch {batch}, "
+    fmt = {"mm4": "mm4-g128", "w8": "int8-per-channel", "a8w8": "a8w8 (int8 activations x int8 weights)"}[quant]
+    return {"workload": f"rwkv7-{shape}-shape {fmt} decode, batch {batch}, "
                         "fp16 head, cache resident",
             "layers": layers or L, "d_model": D, "heads": H, "ffn": Fd, "vocab": V, "lora_ranks": RANKS}
 
@@ -230,8 +231,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--shape", default="7.2B", choices=sorted(SHAPES))
-    ap.add_argument("--quant", default="mm4", choices=["mm4", "w8"],
-                    help="projection format: mm4 = int4 group-128 (headline), w8 = int8 per output channel (the 2.9B configuration)")
+    ap.add_argument("--quant", default="mm4", choices=["mm4", "w8", "a8w8"],
+                    help="projection format: mm4 = int4 group-128 (headline), w8 = int8 per output channel (the 2.9B configuration), "
+                         "a8w8 = per-token int8 activations x int8 weights on the int8 tensor-core GEMM (the prefill kernel)")
     ap.add_argument("--state", default="fp32", choices=["fp32", "fp16"],
                     help="recurrent-state storage: fp32 (the headline contract) or the reference's opt-in FP16-state lane")
     ap.add_argument("--batch", type=int, default=64, help="sequences per GPU group (global batch = batch for N=1)")
@@ -285,6 +287,7 @@ def main():
     import hf_adapter_b200 as hb
     from hf_adapter_b200 import _lib
     from hf_adapter_b200 import model as hbm
+    from hf_adapter_b200 import packing as hpk
 
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -507,7 +510,8 @@ def main():
     roofline = None
     layers = list(model.model.layers)
     launch_bytes = w4_launch_bytes if args.quant == "mm4" else w8_launch_bytes
-    if all(isinstance(l.ffn.key, (hb.MM4Linear, hb.MM8Linear)) and l.ffn.key.tiled_for(f16(B, D)) is not None for l in layers):
+    if args.quant != "a8w8" and all(isinstance(l.ffn.key, (hb.MM4Linear, hb.MM8Linear))
+                                    and l.ffn.key.tiled_for(f16(B, D)) is not None for l in layers):
         xr, xk, xv, xf = (f16(B, D) for _ in range(4))
         xo, xh, xres = f16(B, A_l), f16(B, Fl).abs_(), f16(B, D)
         per = {}
@@ -517,8 +521,9 @@ def main():
             per[name] = {"us_per_launch": us, "bytes_per_launch": nbytes, "achieved_gbs": nbytes / us / 1e3,
                          "frac": nbytes / us / 1e3 / hbm_peak}
 
-        assert hbm._rkv_grouped(layers[0].attn, xr, xk, xv) is not None, "r/k/v are not served by the grouped launch"
-        add("rkv_grouped", lambda: [hbm._rkv_grouped(l.attn, xr, xk, xv) for l in layers], launch_bytes(B, D, A_l, 3))
+        rkv_of = lambda at: hpk.rkv_grouped((at.r_proj, at.k_proj, at.v_proj), xr, xk, xv)
+        assert rkv_of(layers[0].attn) is not None, "r/k/v are not served by the grouped launch"
+        add("rkv_grouped", lambda: [rkv_of(l.attn) for l in layers], launch_bytes(B, D, A_l, 3))
         add("o_proj", lambda: [hbm._linear(l.attn.o_proj, xo) for l in layers], launch_bytes(B, A_l, D))
         add("ffn_key_relu2", lambda: [hbm._linear(l.ffn.key, xf, relu2=True) for l in layers], launch_bytes(B, D, Fl))
         add("ffn_value_add", lambda: [hbm._linear(l.ffn.value, xh, residual=xres) for l in layers], launch_bytes(B, Fl, D))

@@ -2,11 +2,14 @@
 contract of rwkv-rs/hf-adapter (package ``rwkv7_hf``).  Importing this package loads the CUDA
 library; there is no CPU or PyTorch fallback."""
 from . import _lib  # noqa: F401  (fails loudly when the library is missing)
-from .cache import NativeRWKV7Cache
+from .cache import NativeRWKV7Cache, NativeRWKV7LegacyCache
+from .install import install, uninstall
 from .lora import dense_small, fused_wa_lora, fused_wag_lora, fused_wavg_lora
-from .model import DecodeGraph, NativeRWKV7Config, RWKV7ForCausalLM
+from .model import DecodeGraph, NativeRWKV7Config, RWKV7ForCausalLM, sample_next_token
 from .norm_mix import (fused_attn_norm_mix6_decode, fused_attn_sequence_shift_mix, fused_attn_shift_mix,
                        fused_ffn_add_norm_mix_decode, fused_ffn_sequence_shift_mix, layer_norm)
+from .packing import (block_ip_batched, extract_graph_packs, graph_linear_is_dense, graph_linear_operand,
+                      init_batched_from_packs, step_batched)
 from .prep import (fused_attn_output_prepare, fused_attn_output_project, fused_ffn, fused_prefill_kv_kk_prep,
                    fused_prefill_state_prep, fused_sequence_ffn)
 from .quant import (A8W8Linear, MM4Linear, MM8Linear, a8w8_ffn, a8w8_linear, dequantize_mm4, dequantize_mm8,

@@ -6,6 +6,37 @@ from __future__ import annotations
 
 import torch
 
+_METRIC_NAMES = ("clones", "detaches", "device_moves", "select_batch_calls", "batch_select_calls", "batch_select_indices_calls",
+                 "batch_repeat_interleave_calls", "reorder_calls", "crops", "resets", "native_graph_bound_selects")
+
+
+class NativeRWKV7LegacyCache(tuple):
+    """The raw 4-tuple ``(state, xpa, xpf, v_first)`` that still knows how many tokens it has seen
+    (rwkv7_hf/model_cache.py:13-45): what ``to_legacy_cache`` returns and ``from_legacy_cache`` takes back."""
+
+    def __new__(cls, state, xpa, xpf, v_first, seen_tokens: int = 0):
+        obj = super().__new__(cls, (state, xpa, xpf, v_first))
+        obj._seen_tokens = int(seen_tokens)
+        return obj
+
+    def get_seq_length(self, layer_idx=0, cache_position=None) -> int:
+        if layer_idx is not None:
+            state = self[0]
+            if int(layer_idx) < 0 or (state is not None and int(layer_idx) >= len(state)) or (state is None and int(layer_idx) != 0):
+                return 0
+        return self._seen_tokens
+
+    @property
+    def seen_tokens(self) -> int:
+        return int(self._seen_tokens)
+
+    @seen_tokens.setter
+    def seen_tokens(self, value: int) -> None:
+        self._seen_tokens = int(value)
+
+    def to_legacy_cache(self):
+        return self
+
 
 class NativeRWKV7Cache:
     is_compileable = True
@@ -17,6 +48,9 @@ class NativeRWKV7Cache:
         # (the ``elapsed`` operand of rwkv7_hf/native_wkv_fp16.py:54-71); None for an fp32 state
         self._elapsed = elapsed
         self._graph_owner = None  # decode-graph runner whose static buffers these tensors are, if any
+        # how often the cache was copied, moved or re-batched: what a serving layer samples to see whether requests
+        # reuse one cache or keep rebuilding it (rwkv7_hf/model_cache.py:71-83,427-436)
+        self._rwkv7_cache_metrics = dict.fromkeys(_METRIC_NAMES, 0)
 
     # -- tuple protocol ---------------------------------------------------
     def __iter__(self):
@@ -58,6 +92,19 @@ class NativeRWKV7Cache:
     def seen_tokens(self) -> int:
         return self._seen_tokens
 
+    @seen_tokens.setter
+    def seen_tokens(self, value: int) -> None:
+        self._seen_tokens = int(value)
+
+    def rwkv7_cache_metrics(self) -> dict:
+        metrics = dict(self._rwkv7_cache_metrics)
+        metrics.update({"seen_tokens": int(self._seen_tokens), "batch_size": self.get_batch_size(),
+                        "layers": len(self._state) if self._state is not None else 0})
+        return metrics
+
+    def to_legacy_cache(self):
+        return NativeRWKV7LegacyCache(self._state, self._xpa, self._xpf, self._v_first, seen_tokens=self._seen_tokens)
+
     def get_max_cache_shape(self):
         return None
 
@@ -74,22 +121,29 @@ class NativeRWKV7Cache:
     def has_previous_state(self, layer_idx=None) -> bool:
         return self._is_initialized(layer_idx) and self._seen_tokens > 0
 
-    def _map(self, fn, *, inplace):
+    def _map(self, fn, *, inplace, count=()):
         ml = lambda vs: None if vs is None else [fn(v) for v in vs]
         state, xpa, xpf = ml(self._state), ml(self._xpa), ml(self._xpf)
         vf = None if self._v_first is None else fn(self._v_first)
         el = None if self._elapsed is None else fn(self._elapsed)
         if inplace:
+            if self._graph_owner is not None and "select_batch_calls" in count:
+                count = tuple(count) + ("native_graph_bound_selects",)
             self._state, self._xpa, self._xpf, self._v_first, self._elapsed = state, xpa, xpf, vf, el
             self._graph_owner = None
-            return self
-        return NativeRWKV7Cache(state, xpa, xpf, vf, self._seen_tokens, elapsed=el)
+            target = self
+        else:
+            target = NativeRWKV7Cache(state, xpa, xpf, vf, self._seen_tokens, elapsed=el)
+            target._rwkv7_cache_metrics = dict(self._rwkv7_cache_metrics)
+        for name in count:
+            target._rwkv7_cache_metrics[name] += 1
+        return target
 
     def clone(self):
-        return self._map(lambda v: v.clone(), inplace=False)
+        return self._map(lambda v: v.clone(), inplace=False, count=("clones",))
 
     def detach(self, *, inplace: bool = True):
-        return self._map(lambda v: v.detach(), inplace=inplace)
+        return self._map(lambda v: v.detach(), inplace=inplace, count=("detaches",))
 
     def to(self, *args, copy: bool = False, **kwargs):
         def move(v):
@@ -101,7 +155,7 @@ class NativeRWKV7Cache:
                 dev = kwargs.get("device", next((a for a in args if not isinstance(a, torch.dtype)), v.device))
                 return v.to(device=dev, copy=copy)
             return v.to(*args, copy=copy, **kwargs)
-        return self._map(move, inplace=False)
+        return self._map(move, inplace=False, count=("device_moves",))
 
     def reset(self) -> None:
         for vs in (self._state, self._xpa, self._xpf):
@@ -112,21 +166,25 @@ class NativeRWKV7Cache:
         if self._elapsed is not None:
             self._elapsed.zero_()
         self._seen_tokens = 0
+        self._rwkv7_cache_metrics["resets"] += 1
 
-    def select_batch(self, indices, *, inplace: bool = True):
-        return self._map(lambda v: v.index_select(0, indices.to(v.device)), inplace=inplace)
+    def select_batch(self, indices, *, inplace: bool = True, _count=("select_batch_calls",)):
+        return self._map(lambda v: v.index_select(0, indices.to(v.device)), inplace=inplace, count=_count)
 
-    batch_select = select_batch
     compact = select_batch
 
+    def batch_select(self, indices, *, inplace: bool = True):
+        return self.select_batch(indices, inplace=inplace, _count=("select_batch_calls", "batch_select_calls"))
+
     def batch_select_indices(self, indices):
-        return self.select_batch(indices, inplace=True)
+        return self.select_batch(indices, inplace=True, _count=("select_batch_calls", "batch_select_indices_calls"))
 
     def reorder_cache(self, beam_idx):
-        return self.select_batch(beam_idx, inplace=True)
+        return self.select_batch(beam_idx, inplace=True, _count=("select_batch_calls", "reorder_calls"))
 
     def batch_repeat_interleave(self, repeats: int):
-        return self._map(lambda v: v.repeat_interleave(int(repeats), dim=0), inplace=True)
+        return self._map(lambda v: v.repeat_interleave(int(repeats), dim=0), inplace=True,
+                         count=("batch_repeat_interleave_calls",))
 
     def crop(self, max_length: int):
         """A recurrent state cannot be rolled back to a shorter positive prefix
@@ -137,6 +195,7 @@ class NativeRWKV7Cache:
             return self
         if max_length == 0:
             self.reset()
+            self._rwkv7_cache_metrics["crops"] += 1
             return self
         raise ValueError("a recurrent RWKV-7 cache cannot be cropped to a positive prefix")
 
@@ -146,5 +205,20 @@ class NativeRWKV7Cache:
             return cls(seen_tokens=seen_tokens)
         if isinstance(legacy, cls):
             return legacy
+        seen = int(seen_tokens)
+        if hasattr(legacy, "get_seq_length"):
+            try:
+                legacy_seen = int(legacy.get_seq_length())
+                if legacy_seen == 0:
+                    return cls(seen_tokens=seen_tokens)
+                seen = legacy_seen
+            except Exception:
+                pass
+        if hasattr(legacy, "to_legacy_cache"):
+            legacy = legacy.to_legacy_cache()
+        if legacy is None or (isinstance(legacy, (list, tuple)) and len(legacy) == 0):
+            return cls(seen_tokens=seen_tokens)
+        if not isinstance(legacy, (list, tuple)) or len(legacy) != 4:
+            raise TypeError("NativeRWKV7Cache.from_legacy_cache expects None, an empty cache, or a 4-tuple recurrent cache")
         state, xpa, xpf, v_first = legacy
-        return cls(state, xpa, xpf, v_first, seen_tokens=seen_tokens)
+        return cls(state, xpa, xpf, v_first, seen_tokens=seen)

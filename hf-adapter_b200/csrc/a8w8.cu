@@ -302,22 +302,27 @@ namespace {
 // In host code the array's name is only a handle for the runtime: the device address has to be asked
 // for, once per device, with that device current.
 void* static_scratch_ptr() {
-    static void* cache[64] = {};
+    static std::atomic<void*> cache[rwkv7::kMaxDevices];  // racing first callers store the same address
     int dev = -1;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) {
         rwkv7::set_error("a8w8_linear_static: cannot query the current device");
         return nullptr;
     }
-    if (cache[dev] == nullptr) {
-        void* p = nullptr;
+    if (dev >= rwkv7::kMaxDevices) {
+        rwkv7::set_error("a8w8_linear_static: device index %d is beyond the %d devices this library keeps per-device addresses for",
+                         dev, rwkv7::kMaxDevices);
+        return nullptr;
+    }
+    void* p = cache[dev].load(std::memory_order_acquire);
+    if (p == nullptr) {
         cudaError_t e = cudaGetSymbolAddress(&p, g_a8w8_static_scratch);
         if (e != cudaSuccess || p == nullptr) {
             rwkv7::set_error("a8w8_linear_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
             return nullptr;
         }
-        cache[dev] = p;
+        cache[dev].store(p, std::memory_order_release);
     }
-    return cache[dev];
+    return p;
 }
 }  // namespace
 

@@ -14,16 +14,24 @@ void set_error(const char* fmt, ...) {
 // Set (first code wins) by a tensor-core kernel whose bounded wait gave up; see umma.cuh.
 __device__ unsigned int rwkv7_kernel_error = 0;
 
+// Device address of the word on the current device.  The per-device cache is filled by whichever thread asks
+// first; the slots are atomics, so two threads that race both store the same address and neither reads a torn one.
 unsigned int* kernel_error_word() {
-    static unsigned int* cache[64] = {};
+    static std::atomic<unsigned int*> cache[kMaxDevices];
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-    if (!cache[dev]) {
-        void* p = nullptr;
-        if (cudaGetSymbolAddress(&p, rwkv7_kernel_error) != cudaSuccess) return nullptr;
-        cache[dev] = static_cast<unsigned int*>(p);
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) return nullptr;
+    if (dev >= kMaxDevices) {
+        set_error("device index %d is beyond the %d devices this library keeps per-device addresses for", dev, kMaxDevices);
+        return nullptr;
     }
-    return cache[dev];
+    unsigned int* p = cache[dev].load(std::memory_order_acquire);
+    if (p == nullptr) {
+        void* q = nullptr;
+        if (cudaGetSymbolAddress(&q, rwkv7_kernel_error) != cudaSuccess) return nullptr;
+        p = static_cast<unsigned int*>(q);
+        cache[dev].store(p, std::memory_order_release);
+    }
+    return p;
 }
 }  // namespace rwkv7
 

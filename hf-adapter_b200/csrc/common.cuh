@@ -5,6 +5,8 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
+
 #include <cstdlib>
 #include <stdint.h>
 
@@ -17,6 +19,7 @@ namespace rwkv7 {
 
 // ---- error plumbing -------------------------------------------------------
 void set_error(const char* fmt, ...);  // defined in capi.cu (thread-local buffer)
+constexpr int kMaxDevices = 64;        // device indices the per-device address caches cover
 
 #define RWKV7_REQUIRE(cond, code, ...)  \
     do {                                \

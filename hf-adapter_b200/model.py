@@ -24,11 +24,9 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from . import _lib
-from . import lora as _lora
 from . import norm_mix as _nm
+from . import packing as _pk
 from . import prep as _prep
-from . import quant as _q
 from . import recurrent as _rec
 from . import sharding as _sh
 from .cache import NativeRWKV7Cache
@@ -114,48 +112,71 @@ class NativeRWKV7Model(nn.Module):
         self.norm = nn.LayerNorm(config.hidden_size)
 
 
-def _rkv_grouped(at, xr, xk, xv):
-    """r / k / v through one grouped launch when all three are int4 projections of one shape that the tensor-core
-    decode kernel takes; None otherwise."""
-    mods = (at.r_proj, at.k_proj, at.v_proj)
-    int4 = all(isinstance(m, _q.MM4Linear) for m in mods)
-    int8 = all(isinstance(m, _q.MM8Linear) and m.sm7x_rowwise for m in mods)
-    if not (int4 or int8) or any(m.bias is not None for m in mods):
-        return None
-    if len({(m.in_features, m.out_features) for m in mods}) != 1:
-        return None
-    tiled = [m.tiled_for(x_) for m, x_ in zip(mods, (xr, xk, xv))]
-    if any(t is None for t in tiled):
-        return None
-    if int8:
-        return _q.w8_tiled_linear_group((xr, xk, xv), tiled, [m.row_scale for m in mods], mods[0].out_features,
-                                        mods[0].in_features)
-    return _q.w4_tiled_linear_group((xr, xk, xv), tiled, mods[0].out_features, mods[0].in_features)
+_linear = _pk.apply_linear  # a projection module (quantised or dense) applied with its fused epilogue
 
 
-def _linear(mod, x, *, relu2=False, residual=None, out=None):
-    """Apply a projection operand: a quantised module of this package (epilogues fused through its
-    rwkv7_forward_* hooks, as the reference's dispatch probes them: native_jit_graph_dispatch.py:487-523)
-    or a dense nn.Linear (one library GEMM)."""
-    if isinstance(mod, (_q.MM4Linear, _q.MM8Linear, _q.A8W8Linear)):
-        if relu2:
-            if hasattr(mod, "rwkv7_forward_relu2"):
-                return mod.rwkv7_forward_relu2(x)
-            return torch.relu(mod(x)) ** 2
-        if residual is not None:
-            return mod.rwkv7_forward_add(x, residual)
-        if out is not None:
-            return mod.rwkv7_forward_into(x, out)
-        return mod(x)
-    y = F.linear(x, mod.weight, mod.bias)
-    if relu2:
-        y = torch.relu(y) ** 2
-    elif residual is not None:
-        y = y + residual
-    if out is not None:
-        out.copy_(y)
-        return out
-    return y
+def _validate_attention_mask(attention_mask, batch_size: int, seq_len: int, device=None, *, allow_trailing: bool = False):
+    """The reference's mask contract (rwkv7_hf/model_backbone.py:28-61): ``[B,T]`` (a longer mask is cut to its last T
+    columns when a cache exists), non-zero = token present; an all-ones mask is no mask."""
+    if attention_mask is None:
+        return None
+    if not isinstance(attention_mask, torch.Tensor):
+        raise TypeError("NativeRWKV7 attention_mask must be a torch.Tensor when provided")
+    if attention_mask.dim() == 1:
+        attention_mask = attention_mask.view(1, -1)
+    if attention_mask.dim() != 2:
+        raise ValueError("NativeRWKV7 attention_mask must be shaped [batch, seq]")
+    if int(attention_mask.shape[0]) != int(batch_size):
+        raise ValueError("NativeRWKV7 attention_mask batch size must match inputs")
+    if int(attention_mask.shape[1]) != int(seq_len):
+        if not allow_trailing or int(attention_mask.shape[1]) < int(seq_len):
+            raise ValueError("NativeRWKV7 attention_mask must have the same [batch, seq] shape as inputs")
+        attention_mask = attention_mask[:, -seq_len:]
+    mask = attention_mask.to(device=device) if device is not None else attention_mask
+    mask = mask[:, :seq_len] != 0
+    if mask.numel() and bool(torch.all(mask)):
+        return None
+    return mask
+
+
+def _resolve_logits_to_keep(logits_to_keep, num_logits_to_keep):
+    keep = logits_to_keep if logits_to_keep is not None else num_logits_to_keep
+    if keep is None:
+        return None
+    if isinstance(keep, torch.Tensor):
+        raise NotImplementedError("logits_to_keep as an index tensor is not supported; pass the number of last tokens")
+    keep = int(keep)
+    if keep < 0:
+        raise ValueError("logits_to_keep must be non-negative")
+    return keep
+
+
+def _causal_lm_output(logits, cache):
+    """``transformers.modeling_outputs.CausalLMOutputWithPast`` when that package imports, else an object with the same
+    two attributes (this library does not depend on transformers)."""
+    try:
+        from transformers.modeling_outputs import CausalLMOutputWithPast
+    except Exception:  # pragma: no cover - transformers absent
+        return SimpleNamespace(logits=logits, past_key_values=cache, loss=None, hidden_states=None, attentions=None)
+    return CausalLMOutputWithPast(logits=logits, past_key_values=cache)
+
+
+def sample_next_token(logits, *, temperature: float = 1.0, top_k: int = 0, top_p: float = 1.0, generator=None):
+    """One token per row of ``logits [B,V]`` from the temperature-scaled distribution restricted to the ``top_k`` most
+    likely tokens and to the smallest set whose probability reaches ``top_p`` (the most likely token always stays)."""
+    if temperature <= 0:
+        return logits.argmax(-1)
+    z = logits.float() / float(temperature)
+    if top_k and 0 < int(top_k) < z.shape[-1]:
+        kth = torch.topk(z, int(top_k), dim=-1).values[:, -1:]
+        z = z.masked_fill(z < kth, float("-inf"))
+    if top_p < 1.0:
+        sz, idx = torch.sort(z, dim=-1, descending=True)
+        pr = torch.softmax(sz, dim=-1)
+        before = pr.cumsum(-1) - pr  # probability mass ahead of each token
+        sz = sz.masked_fill(before >= float(top_p), float("-inf"))
+        z = torch.full_like(z, float("-inf")).scatter(-1, idx, sz)
+    return torch.multinomial(torch.softmax(z, dim=-1), 1, generator=generator).squeeze(-1)
 
 
 class RWKV7ForCausalLM(nn.Module):
@@ -283,71 +304,14 @@ class RWKV7ForCausalLM(nn.Module):
             return torch.cat(outs, 0)
         return self._decode_rows(ids, (state, xpa, xpf, v_first, cache._elapsed), greedy, 0, 0)
 
-    def _decode_rows(self, ids, tensors, greedy, lane, stream_base):
+    def _decode_rows(self, ids, tensors, greedy, lane, stream_base, inputs_embeds=None):
+        """The layers of one decode step, each run from its pack tuple (packing.block_ip_batched), then the head."""
         state, xpa, xpf, v_first, elapsed_t = tensors
-        H, N = self.model.layers[0].attn.num_heads, self.config.head_dim
-        x = F.embedding(ids.reshape(-1), self.model.embeddings.weight)
-        B = int(x.shape[0])
-        L = len(self.model.layers)
+        x = inputs_embeds if inputs_embeds is not None else F.embedding(ids.reshape(-1), self.model.embeddings.weight)
         elapsed = elapsed_t if state[0].dtype == torch.float16 else None
-        for i, layer in enumerate(self.model.layers):
-            at, ff = layer.attn, layer.ffn
-            if i == 0:
-                x = _nm.layer_norm(x, layer.pre_norm.weight, layer.pre_norm.bias)
-            xr, xw, xk, xv, xa, xg = _nm.fused_attn_norm_mix6_decode(
-                x, xpa[i], layer.attn_norm.weight, layer.attn_norm.bias, at.x_r, at.x_w, at.x_k, at.x_v, at.x_a, at.x_g)
-            # The LoRA chain does not depend on r/k/v: it runs on a side stream (a parallel branch of the decode
-            # graph once captured) and joins before the recurrence.
-            main = torch.cuda.current_stream(x.device)
-            side = self._side_stream(x.device, stream_base)
-            side.wait_stream(main)
-            wl, al, gl = at.w_lora.lora, at.a_lora.lora, at.g_lora.lora
-            with torch.cuda.stream(side):
-                if i == 0:
-                    hs = _lora.small_gemm_group((xw, xa, xg), (wl[0].weight, al[0].weight, gl[0].weight), acts=(1, 0, 2))
-                    w_raw, a_pre, g = _lora.small_gemm_group(hs, (wl[2].weight, al[2].weight, gl[2].weight))
-                    extra = dict(v_out=v_first)
-                else:
-                    vl = at.v_lora.lora
-                    hs = _lora.small_gemm_group((xw, xa, xg, xv), (wl[0].weight, al[0].weight, gl[0].weight, vl[0].weight),
-                                                acts=(1, 0, 2, 0))
-                    w_raw, a_pre, g, vg_pre = _lora.small_gemm_group(hs, (wl[2].weight, al[2].weight, gl[2].weight, vl[2].weight))
-                    extra = dict(v_first=v_first, v_gate=vg_pre, v_gate_bias=vl[2].bias, v_gate_is_raw=True)
-            rkv = _rkv_grouped(at, xr, xk, xv)
-            if rkv is not None:
-                # int4 r / k / v of equal shape: one launch streams all three weight sets (one pipeline fill, no
-                # split-K exchange) instead of three launches competing for the SMs
-                r, k, v = rkv
-                main.wait_stream(side)
-            else:
-                # independent projections on separate branches: the tail of one overlaps the ramp-up of the next
-                sk, sv = self._side_stream(x.device, stream_base + 1), self._side_stream(x.device, stream_base + 2)
-                sk.wait_stream(main)
-                sv.wait_stream(main)
-                with torch.cuda.stream(sk):
-                    k = _linear(at.k_proj, xk)
-                with torch.cuda.stream(sv):
-                    v = _linear(at.v_proj, xv)
-                r = _linear(at.r_proj, xr)
-                main.wait_stream(side)
-                main.wait_stream(sk)
-                main.wait_stream(sv)
-                xk.record_stream(sk); k.record_stream(sk); xv.record_stream(sv); v.record_stream(sv)
-            for t_ in (xw, xa, xg, xv, w_raw, a_pre, g):
-                t_.record_stream(side)
-            # the kernel launched just before the recurrence is a projection: it never writes the state
-            out, _ = _rec.fused_recurrent_output_prepare_raw(
-                r, w_raw, k, v, a_pre, state[i], g, at.k_k, at.k_a, at.r_k, at.g_norm.weight, at.g_norm.bias,
-                eps=N * 1e-5, new_state=state[i], w_bias=wl[2].bias, a_bias=al[2].bias, a_is_raw=True,
-                state_prefetch=True, elapsed=elapsed, advance_elapsed=elapsed is not None and i == L - 1, **extra)
-            attn = self._all_reduce(_linear(at.o_proj, out), lane)
-            x, mixed = _nm.fused_ffn_add_norm_mix_decode(x, attn, xpf[i], layer.ffn_norm.weight, layer.ffn_norm.bias, ff.x_k)
-            hidden = _linear(ff.key, mixed, relu2=True)
-            if self.tp_world > 1:
-                # the residual rides in rank 0's partial sum (the projection's add epilogue): no extra add kernel
-                x = self._all_reduce(_linear(ff.value, hidden, residual=x if self.tp_rank == 0 else None), lane)
-            else:
-                x = _linear(ff.value, hidden, residual=x)
+        ctx = _pk.StepContext(self._side_stream, self._all_reduce, self.tp_world, self.tp_rank, lane, stream_base)
+        packs, _, _, _ = _pk.extract_graph_packs(self)
+        x, *_ = _pk.step_batched(self, x, state, xpa, xpf, v_first, packs, fp16_elapsed=elapsed, context=ctx)
         xn = _nm.layer_norm(x, self.model.norm.weight, self.model.norm.bias)
         return self._head(xn, greedy, lane)
 
@@ -446,34 +410,170 @@ class RWKV7ForCausalLM(nn.Module):
                                                       scan_chunk=scan_chunk)
         return logits, cache
 
-    @torch.no_grad()
-    def forward(self, input_ids, past_key_values=None, use_cache=None, logits_to_keep: int = 0, **_):
-        """HF-style forward (rwkv7_hf/native_model.py:618-783).  Returns an object with ``.logits``
-        ``[B,T or keep,V]`` and ``.past_key_values`` (a NativeRWKV7Cache)."""
-        if input_ids.dim() == 1:
-            input_ids = input_ids[None]
-        cache = NativeRWKV7Cache.from_legacy_cache(past_key_values) if past_key_values is not None else None
-        if cache is None or not cache._is_initialized():
-            cache = self.new_cache(int(input_ids.shape[0]))
-        T = int(input_ids.shape[1])
-        if T == 1:
-            logits = self.rwkv7_forward_token(input_ids[:, 0], cache, use_graph=False)[:, None]
-        else:
-            logits, cache = self.rwkv7_prefill_native(input_ids, cache, logits_to_keep=logits_to_keep)
-        return SimpleNamespace(logits=logits, past_key_values=cache if use_cache is not False else None)
+    # ------------------------------------------------------------------ Hugging Face surface
+    def _masked_run(self, input_ids, inputs_embeds, mask, cache, keep: int):
+        """Token-by-token advance for inputs the layer-wise prefill does not take: embeddings instead of ids, or an
+        attention mask with holes.  Rows whose mask is 0 at a token keep their recurrent state, shift states and
+        ``v_first``, and repeat their previous final hidden state (rwkv7_hf/native_model.py:555-590,
+        model_backbone.py:64-75).  Returns logits for the last ``keep`` tokens ``[B,keep,V]``."""
+        B = int(input_ids.shape[0] if input_ids is not None else inputs_embeds.shape[0])
+        T = int(input_ids.shape[1] if input_ids is not None else inputs_embeds.shape[1])
+        logits, last = [], None
+        state, xpa, xpf, v_first = cache
+        tensors = (state, xpa, xpf, v_first, cache._elapsed)
+        for t in range(T):
+            m = None if mask is None else mask[:, t]
+            if m is not None:
+                old = [v.clone() for v in cache._tensors()]
+            ids_t = None if input_ids is None else input_ids[:, t]
+            emb_t = None if inputs_embeds is None else inputs_embeds[:, t].contiguous()
+            lg = self._decode_rows(ids_t, tensors, False, 0, 0, inputs_embeds=emb_t)
+            if m is not None:
+                for new_t, old_t in zip(cache._tensors(), old):
+                    new_t.copy_(torch.where(m.view(-1, *([1] * (new_t.dim() - 1))), new_t, old_t))
+                # a masked row repeats its previous logits (zeros before its first token: the head of a zero vector)
+                lg = torch.where(m.view(-1, 1), lg, last if last is not None else torch.zeros_like(lg))
+            last = lg
+            if t >= T - keep:
+                logits.append(lg)
+        cache._seen_tokens += T
+        return torch.stack(logits, dim=1)
 
     @torch.no_grad()
-    def generate(self, input_ids, max_new_tokens: int = 16, do_sample: bool = False, use_graph: bool = True, **_):
-        """Greedy generation: prefill, then one decode step per new token.  Returns ``[B, T + new]`` ids."""
-        if do_sample:
-            raise NotImplementedError("only greedy decoding is implemented")
-        logits, cache = self.rwkv7_prefill_native(input_ids, None, logits_to_keep=1)
-        tok = logits[:, -1].argmax(-1)
-        out = [input_ids, tok[:, None]]
-        for _ in range(int(max_new_tokens) - 1):
-            tok = self.rwkv7_forward_token(tok, cache, use_graph=use_graph).argmax(-1)
-            out.append(tok[:, None])
-        return torch.cat(out, dim=1)
+    def forward(self, input_ids=None, attention_mask=None, inputs_embeds=None, past_key_values=None, use_cache=None,
+                output_hidden_states=None, output_attentions=None, return_dict=None, labels=None, logits_to_keep=None,
+                num_logits_to_keep=None, position_ids=None, cache_position=None, token_type_ids=None, head_mask=None,
+                return_legacy_cache=None, **kwargs):
+        """The reference's ``NativeRWKV7ForCausalLM.forward`` for inference (rwkv7_hf/native_model.py:618-853): same
+        arguments, same validation messages, ``CausalLMOutputWithPast(logits, past_key_values)`` out (a tuple with
+        ``return_dict=False``; a legacy tuple cache with ``return_legacy_cache``).
+
+        Without a cache the logits of every prompt token are returned unless ``logits_to_keep`` asks for the last n;
+        with one, a single token takes the decode step (CUDA graph) and a longer continuation the layer-wise
+        prefill.  ``attention_mask`` rows that are 0 leave that sequence's recurrent state untouched.  Training
+        (``labels``), per-layer hidden states and attention maps are outside this library."""
+        if labels is not None:
+            raise NotImplementedError("training through labels is not part of this inference library")
+        if output_hidden_states:
+            raise NotImplementedError("per-layer hidden states are not kept by the fused kernels")
+        if output_attentions:
+            raise NotImplementedError("NativeRWKV7 does not expose Transformer-style attention maps")
+        if input_ids is not None and inputs_embeds is not None:
+            raise ValueError("NativeRWKV7ForCausalLM accepts either input_ids or inputs_embeds, not both")
+        if input_ids is None and inputs_embeds is None:
+            raise ValueError("NativeRWKV7ForCausalLM requires input_ids or inputs_embeds")
+        if input_ids is not None and input_ids.dim() == 1:
+            input_ids = input_ids.view(1, -1)
+        if input_ids is not None and input_ids.dim() != 2:
+            raise ValueError("Experimental NativeRWKV7ForCausalLM expects input_ids shaped [batch, seq]")
+        if inputs_embeds is not None:
+            if inputs_embeds.dim() != 3:
+                raise ValueError("NativeRWKV7ForCausalLM expects inputs_embeds shaped [batch, seq, hidden]")
+            if int(inputs_embeds.shape[-1]) != int(self.config.hidden_size):
+                raise ValueError("NativeRWKV7ForCausalLM inputs_embeds last dimension must match hidden_size")
+        B = int(input_ids.shape[0] if input_ids is not None else inputs_embeds.shape[0])
+        T = int(input_ids.shape[1] if input_ids is not None else inputs_embeds.shape[1])
+        if B <= 0 or T <= 0:
+            raise ValueError("NativeRWKV7ForCausalLM requires a non-empty batch and sequence")
+        cache = NativeRWKV7Cache.from_legacy_cache(past_key_values) if past_key_values is not None else None
+        had_cache = cache is not None and cache._is_initialized()
+        if had_cache and cache.get_batch_size() != B:
+            raise ValueError(f"NativeRWKV7 cache batch size {cache.get_batch_size()} does not match input batch size {B}")
+        if not had_cache:
+            cache = self.new_cache(B)
+        mask = _validate_attention_mask(attention_mask, B, T, self.device, allow_trailing=had_cache)
+        keep = _resolve_logits_to_keep(logits_to_keep, num_logits_to_keep)
+        keep_n = T if keep in (None, 0) else min(int(keep), T)
+        if not had_cache and keep in (None,):
+            keep_n = T  # full forward: all-token logits, Hugging Face CausalLM semantics
+        if inputs_embeds is not None or mask is not None:
+            logits = self._masked_run(input_ids, inputs_embeds, mask, cache, keep_n)
+        elif T == 1:
+            logits = self.rwkv7_forward_token(input_ids[:, 0], cache, use_graph=bool(kwargs.get("use_graph", True)))[:, None]
+        else:
+            logits, cache = self.rwkv7_prefill_native(input_ids, cache, logits_to_keep=keep_n)
+        new_cache = cache if (use_cache is None or use_cache) else None
+        if new_cache is not None and (return_legacy_cache or (return_legacy_cache is None and isinstance(past_key_values, tuple))):
+            new_cache = new_cache.to_legacy_cache()
+        if return_dict is not None and not return_dict:
+            return tuple(v for v in (logits, new_cache) if v is not None)
+        return _causal_lm_output(logits, new_cache)
+
+    def prepare_inputs_for_generation(self, input_ids, past_key_values=None, inputs_embeds=None, token_type_ids=None,
+                                      head_mask=None, return_legacy_cache=None, **kwargs):
+        """What a generation loop feeds ``forward`` next (rwkv7_hf/model_generation.py:53-110): with a cache only the
+        last token (and the last column of the mask) is passed on."""
+        cache = NativeRWKV7Cache.from_legacy_cache(past_key_values) if past_key_values is not None else None
+        has = cache is not None and cache._is_initialized()
+        last = lambda t: t[:, -1:] if t is not None else None
+        inputs = {}
+        if has:
+            if input_ids is not None:
+                inputs["input_ids"] = last(input_ids)
+            elif inputs_embeds is not None:
+                inputs["inputs_embeds"] = last(inputs_embeds)
+        elif inputs_embeds is not None:
+            inputs["inputs_embeds"] = inputs_embeds
+        else:
+            inputs["input_ids"] = input_ids
+        inputs["past_key_values"] = past_key_values
+        inputs["use_cache"] = True if kwargs.get("use_cache") is None else kwargs["use_cache"]
+        if return_legacy_cache is not None:
+            inputs["return_legacy_cache"] = return_legacy_cache
+        if kwargs.get("attention_mask") is not None:
+            inputs["attention_mask"] = last(kwargs["attention_mask"]) if has else kwargs["attention_mask"]
+        for name in ("logits_to_keep", "num_logits_to_keep", "return_dict"):
+            if name in kwargs:
+                inputs[name] = kwargs[name]
+        return inputs
+
+    def _reorder_cache(self, past_key_values, beam_idx):
+        """Beam-search reordering of the batch rows of a cache (rwkv7_hf/model_generation.py:25-50)."""
+        cache = NativeRWKV7Cache.from_legacy_cache(past_key_values)
+        out = cache.select_batch(beam_idx)
+        return out.to_legacy_cache() if isinstance(past_key_values, tuple) else out
+
+    @torch.no_grad()
+    def generate(self, input_ids=None, attention_mask=None, max_new_tokens: int = 16, do_sample: bool = False,
+                 temperature: float = 1.0, top_k: int = 0, top_p: float = 1.0, eos_token_id=None, pad_token_id: int = 0,
+                 use_graph: bool = True, generator=None, inputs=None, **_):
+        """Prefill, then one decode step per new token; returns ``[B, T + new]`` ids.  Greedy by default (the head's
+        arg-max runs inside the decode graph); ``do_sample`` draws from the temperature / top-k / top-p filtered
+        distribution on the device.  A left-padded batch passes its ``attention_mask``: padded positions leave the
+        state untouched.  Sequences that produced ``eos_token_id`` are filled with ``pad_token_id``."""
+        if input_ids is None:
+            input_ids = inputs
+        if input_ids.dim() == 1:
+            input_ids = input_ids.view(1, -1)
+        B = int(input_ids.shape[0])
+        n_new = int(max_new_tokens)
+        if n_new <= 0:
+            return input_ids
+        out = self.forward(input_ids, attention_mask=attention_mask, logits_to_keep=1)
+        cache, logits = out.past_key_values, out.logits[:, -1]
+        eos = None
+        if eos_token_id is not None:
+            eos = torch.as_tensor([eos_token_id] if isinstance(eos_token_id, int) else list(eos_token_id), device=input_ids.device)
+        done = torch.zeros(B, dtype=torch.bool, device=input_ids.device)
+        toks = []
+        for step in range(n_new):
+            if step:
+                if do_sample:
+                    logits = self.rwkv7_forward_token(tok, cache, use_graph=use_graph)
+                else:
+                    logits = None
+                    tok = self.rwkv7_forward_token(tok, cache, use_graph=use_graph, return_tokens=True)
+            if do_sample:
+                tok = sample_next_token(logits, temperature=temperature, top_k=top_k, top_p=top_p, generator=generator)
+            elif logits is not None:
+                tok = logits.argmax(-1)
+            if eos is not None:
+                tok = torch.where(done, torch.full_like(tok, int(pad_token_id)), tok)
+                done = done | torch.isin(tok, eos)
+            toks.append(tok[:, None])
+            if eos is not None and step + 1 < n_new and bool(done.all()):
+                break
+        return torch.cat([input_ids] + toks, dim=1)
 
     # ------------------------------------------------------------------ CUDA graph
     def _decode_graph(self, batch: int, greedy: bool = False) -> "DecodeGraph":

@@ -6,7 +6,7 @@ runs on CPU):
 
     python tests/golden/make_golden.py --reference /path/to/hf-adapter
 
-Outputs ``ops_fp32.npz``, ``ops_fp16.npz``, ``quant.npz``, ``model_tiny.npz``,
+Outputs ``ops_fp32.npz``, ``ops_fp16.npz``, ``quant.npz``, ``model_tiny.npz``, ``model_masked.npz``,
 ``config1.npz`` and ``a8w8_ffn.npz`` next to this script (``--only`` selects a subset).  The fixtures hold the seeded inputs
 AND the reference's outputs, so the parity tests never need the reference at
 run time.  All shapes are small (N=64 heads, a few rows) to keep every file
@@ -264,6 +264,40 @@ def gen_model(seed):
     return {k_: npy(v_) for k_, v_ in out.items()}
 
 
+def gen_model_masked(seed):
+    """The Hugging Face surface of the reference on the tiny model of ``gen_model`` (same seeds, so the weights are
+    those of model_tiny.npz): a batch with masked positions (left padding, a hole, a masked first token), the same
+    through ``inputs_embeds``, and a cached continuation that passes the full-length mask."""
+    from rwkv7_hf import NativeRWKV7Config, NativeRWKV7ForCausalLM
+
+    cfg = NativeRWKV7Config(vocab_size=256, hidden_size=128, num_hidden_layers=2, num_heads=2, head_dim=64,
+                            intermediate_size=256, decay_low_rank_dim=16, a_low_rank_dim=16,
+                            v_low_rank_dim=8, gate_low_rank_dim=32)
+    torch.manual_seed(seed)
+    model = NativeRWKV7ForCausalLM(cfg).eval().float()
+    reinit_degenerate(model, seed + 1)
+    g = torch.Generator().manual_seed(seed + 5)
+    ids = torch.randint(0, 256, (3, 7), generator=g)
+    mask = torch.tensor([[0, 0, 0, 1, 1, 1, 1], [1, 1, 1, 1, 1, 1, 1], [0, 1, 1, 0, 1, 1, 1]])
+    out = dict(ids=ids, mask=mask)
+    with torch.no_grad():
+        o = model(ids, attention_mask=mask, use_cache=True)
+        st, xpa, xpf, vf = o.past_key_values
+        out.update(logits=o.logits, state=torch.stack(list(st)), xpa=torch.stack(list(xpa)), xpf=torch.stack(list(xpf)), v_first=vf,
+                   seen=np.int64(o.past_key_values.get_seq_length()))
+        emb = model.model.embeddings(ids)
+        oe = model(inputs_embeds=emb, attention_mask=mask, use_cache=True)
+        out["embeds_logits"] = oe.logits
+        # continuation: two more tokens with the mask grown to the full length (the second new token of row 0 masked)
+        more = torch.randint(0, 256, (3, 2), generator=g)
+        mask2 = torch.cat([mask, torch.tensor([[1, 0], [1, 1], [1, 1]])], dim=1)
+        o2 = model(more, attention_mask=mask2, past_key_values=o.past_key_values, use_cache=True)
+        st2, _, _, _ = o2.past_key_values
+        out.update(more=more, mask2=mask2, more_logits=o2.logits, more_state=torch.stack(list(st2)),
+                   more_seen=np.int64(o2.past_key_values.get_seq_length()))
+    return {k_: (v_ if isinstance(v_, np.generic) else npy(v_)) for k_, v_ in out.items()}
+
+
 def gen_config1(seed, weight_seed):
     """The 0.1B-shape model (12 layers, d_model 768, 12 heads of 64, FFN 3072, vocabulary 65536, LoRA ranks
     64/64/32/128) in fp32 on the reference's CPU path: a 512-token random prompt through ``forward`` (eager prefill),
@@ -333,7 +367,7 @@ def gen_a8w8_ffn(seed):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of the hf-adapter checkout")
-    ap.add_argument("--only", default="", help="comma-separated subset of: ops,quant,model_tiny,config1,a8w8_ffn")
+    ap.add_argument("--only", default="", help="comma-separated subset of: ops,quant,model_tiny,model_masked,config1,a8w8_ffn")
     ap.add_argument("--config1-weight-seed", type=int, default=3)
     ap.add_argument("--out", default=HERE, help="output folder (default: next to this script)")
     args = ap.parse_args()
@@ -349,6 +383,8 @@ def main():
         save("quant.npz", gen_quant(11))
     if want("model_tiny"):
         save("model_tiny.npz", gen_model(0))
+    if want("model_masked"):
+        save("model_masked.npz", gen_model_masked(0))
     if want("config1"):
         save("config1.npz", gen_config1(0, args.config1_weight_seed))
     if want("a8w8_ffn"):

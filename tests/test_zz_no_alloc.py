@@ -45,6 +45,30 @@ def test_static_scratch_entry_matches_workspace_entry_twice():
         assert code == 0 and torch.equal(got2, hb.a8w8_linear(x, q_t, scale))
 
 
+def test_static_scratch_entry_on_the_tensor_core_path():
+    """130 rows x K=1024 takes the tcgen05 int8 GEMM (more than one 128-row tile, a ragged second one) and an
+    accumulator region that starts at a rounded-up offset inside the built-in array; 264 outputs leave a ragged
+    column tile.  Same kernels as the workspace entry, so bit-identical."""
+    torch.manual_seed(6)
+    M, K, Nout = 130, 1024, 264
+    W = (0.02 * torch.randn(Nout, K)).half()
+    q_t, scale = hb.quantize_weight_per_channel_int8(W)
+    q_t, scale = q_t.cuda(), scale.cuda()
+    q_row = q_t.t()
+    assert q_row.is_contiguous()
+    assert int(_lib.lib.rwkv7_a8w8_workspace_bytes(M, K, Nout)) <= int(_lib.lib.rwkv7_a8w8_static_capacity_bytes())
+    bias = (0.1 * torch.randn(Nout)).half().cuda()
+    x = torch.randn(M, K, device="cuda", dtype=torch.float16)
+    res = torch.randn(M, Nout, device="cuda", dtype=torch.float16)
+    want = hb.a8w8_linear(x, q_t, scale, bias, residual=res)
+    for call in range(2):
+        code, got = _static_call(x, q_row, scale, bias, res)
+        assert code == 0, _lib.last_error()
+        torch.cuda.synchronize()
+        assert torch.equal(got, want), f"call {call}: max diff {(got.float() - want.float()).abs().max().item()}"
+    assert _lib.lib.rwkv7_kernel_status(0) == 0
+
+
 def test_static_scratch_entry_rejects_oversize():
     cap = int(_lib.lib.rwkv7_a8w8_static_capacity_bytes())
     assert cap == 8 << 20
