@@ -59,6 +59,7 @@ SIGNATURES = {
     "rwkv7_w8_dequant": (I, [P] * 3 + [I, I, I, P]),
     "rwkv7_a8_quant": (I, [P, P, P, I, I, I, P]),
     "rwkv7_i8_gemm": (I, [P, P, P, I, I, I, P]),
+    "rwkv7_gemm": (I, [P, P, P, P, P, I, I, I, I, I, P]),
     "rwkv7_a8w8_dequant": (I, [P] * 6 + [I, I, I, P]),
     "rwkv7_a8w8_workspace_bytes": (L, [I, I, I]),
     "rwkv7_a8w8_linear": (I, [P] * 7 + [L, I, I, I, I, P]),

@@ -2,7 +2,7 @@
 // -> int32 GEMM (bit-exact integer accumulators), fp32 dequant epilogue.
 //
 // This file holds the quantiser, the epilogue and a warp-level mma.sync (IMMA
-// m16n8k32) GEMM used for shapes the tcgen05 kernel (i8_umma.cu) does not take
+// m16n8k32) GEMM used for shapes the tcgen05 kernel (gemm_umma.cu) does not take
 // (ragged M/N/K) and as the comparison baseline for it.
 #include "common.cuh"
 
@@ -81,9 +81,10 @@ __global__ void __launch_bounds__(256) a8w8_dequant_kernel(const int32_t* __rest
     const long long total = (long long)M * Nout;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int m = (int)(i / Nout), n = (int)(i % Nout);
-        float v = (float)acc[i] * sa[m] * sw[n];
-        if (bias) v += to_f<T>(bias[n]);
-        if (residual) v += to_f<T>(residual[i]);
+        // every step rounded on its own (no fused multiply-add): the tensor-core GEMM's fused epilogue does the same
+        float v = __fmul_rn(__fmul_rn((float)acc[i], sa[m]), sw[n]);
+        if (bias) v = __fadd_rn(v, to_f<T>(bias[n]));
+        if (residual) v = __fadd_rn(v, to_f<T>(residual[i]));
         out[i] = from_f<T>(v);
     }
 }
@@ -208,8 +209,10 @@ int launch_i8_gemm_mma(const int8_t* qa, const int8_t* qw, int32_t* acc, int M, 
     return check_launch("i8_gemm_mma_kernel");
 }
 
-// implemented in i8_umma.cu; returns RWKV7_ERR_UNSUPPORTED when the shape is not eligible
+// implemented in gemm_umma.cu; returns RWKV7_ERR_UNSUPPORTED when the shape is not eligible
 int launch_i8_gemm_umma(const int8_t* qa, const int8_t* qw, int32_t* acc, int M, int K, int Nout, cudaStream_t st);
+int launch_i8_gemm_dequant_umma(const int8_t* qa, const float* sa, const int8_t* qw, const float* sw, const void* bias,
+                                const void* residual, void* out, int M, int K, int Nout, int dtype, cudaStream_t st);
 
 static inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
 
@@ -284,7 +287,11 @@ extern "C" int rwkv7_a8w8_linear(const void* x, const int8_t* qw, const float* s
     float* sa = reinterpret_cast<float*>(ws + align_up((int64_t)M * K, 256));
     int32_t* acc = reinterpret_cast<int32_t*>(ws + align_up((int64_t)M * K, 256) + align_up((int64_t)M * 4, 256));
     if (int e = rwkv7_a8_quant(x, qa, sa, M, K, dtype, stream)) return e;
-    if (int e = rwkv7_i8_gemm(qa, qw, acc, M, K, Nout, stream)) return e;
+    // tensor-core route: the dequantisation rides in the GEMM's epilogue, the int32 accumulators never reach memory
+    RWKV7_REQUIRE(sw && out, RWKV7_ERR_INVALID, "a8w8_linear: null pointer");
+    int e = launch_i8_gemm_dequant_umma(qa, sa, qw, sw, bias, residual, out, M, K, Nout, dtype, static_cast<cudaStream_t>(stream));
+    if (e != RWKV7_ERR_UNSUPPORTED) return e;
+    if (int e2 = rwkv7_i8_gemm(qa, qw, acc, M, K, Nout, stream)) return e2;
     return rwkv7_a8w8_dequant(acc, sa, sw, bias, residual, out, M, Nout, dtype, stream);
 }
 

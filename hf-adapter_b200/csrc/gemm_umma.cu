@@ -1,0 +1,345 @@
+// Persistent tensor-core GEMM with fused epilogues, for the many-row (prefill) side of the projections:
+//
+//   C[M, N] = epilogue( A[M, K] . B[N, K]^T )        A, B K-major (row-major activations, [out, in] weights)
+//
+//   kind f16 / bf16 : fp32 accumulation; epilogue (+ bias) then relu^2 or (+ residual), output in the operand type
+//   kind i8         : int32 accumulation (exact); epilogue raw int32, or the A8W8 dequantisation
+//                     acc * sa[row] * sw[col] (+ bias) (+ residual) in fp32 with every step rounded, output T
+//
+// One CTA per SM walks output tiles of 128 x 256 in an order that keeps a band of 16 row-tiles of A in L2 while the
+// B tiles stream.  TMA (128-byte swizzle, 128 bytes of K per box) lands both operands in the layout the MMA
+// descriptors read; a 4-stage ring feeds tcgen05.mma (one issuing thread); TWO accumulators of 256 columns live in
+// tensor memory, so the epilogue warps drain tile i while the tensor pipe already works on tile i + 1.
+// Warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner, warps 2-5 = epilogue (TMEM -> registers -> global).
+// Ragged M / N / K edges are zero-filled by TMA and masked at the store.  All waits are bounded (umma.cuh).
+#include "umma.cuh"
+
+namespace rwkv7 {
+namespace gm {
+constexpr int BM = 128, BN = 256, BKB = 128, STAGES = 4, THREADS = 192;
+constexpr int A_BYTES = BM * BKB, B_BYTES = BN * BKB, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int TMEM_COLS = 512;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 256 + 1024;
+constexpr int GROUP_M = 16;
+enum { KIND_F16 = 0, KIND_BF16 = 1, KIND_I8 = 2 };
+enum { EPI_STORE = 0, EPI_RELU2 = 1, EPI_DEQUANT = 2, EPI_RAW_I32 = 3 };
+}  // namespace gm
+
+struct GemmArgs {
+    void* C;
+    const void* bias;      // [N] in the output type, or null
+    const void* residual;  // [M, N] in the output type, or null
+    const float* sa;       // [M] row scales (dequant epilogue)
+    const float* sw;       // [N] channel scales (dequant epilogue)
+    int M, N, K;
+    int tiles_m, tiles_n;
+    int epi;
+    int vec;  // 1: N % 16 == 0 and every pointer the epilogue touches is 16-byte aligned
+    unsigned int* error;
+};
+
+// tile -> (row tile, column tile): bands of GROUP_M row tiles, row tile fastest inside a band
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+    const int per_band = gm::GROUP_M * tiles_n;
+    const int band = tile / per_band, within = tile - band * per_band;
+    const int rows = min(gm::GROUP_M, tiles_m - band * gm::GROUP_M);
+    tn = within / rows;
+    tm = band * gm::GROUP_M + (within - tn * rows);
+}
+
+template <int KIND, typename TOut>
+__device__ __forceinline__ void epilogue_chunk(const GemmArgs& p, const uint32_t (&v)[16], int row, int col) {
+    using namespace gm;
+    if (row >= p.M || col >= p.N) return;
+    const size_t off = (size_t)row * p.N + col;
+    const bool full = p.vec && col + 16 <= p.N;
+    if constexpr (KIND == KIND_I8) {
+        if (p.epi == EPI_RAW_I32) {
+            int32_t* dst = reinterpret_cast<int32_t*>(p.C) + off;
+            if (full) {
+#pragma unroll
+                for (int e = 0; e < 16; e += 4)
+                    *reinterpret_cast<int4*>(dst + e) = make_int4((int)v[e], (int)v[e + 1], (int)v[e + 2], (int)v[e + 3]);
+            } else {
+                for (int e = 0; e < 16 && col + e < p.N; ++e) dst[e] = (int)v[e];
+            }
+            return;
+        }
+    }
+    float f[16];
+    if constexpr (KIND == KIND_I8) {
+        const float a_s = p.sa[row];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+            const float s = (col + e < p.N) ? p.sw[col + e] : 0.f;
+            f[e] = __fmul_rn(__fmul_rn((float)(int)v[e], a_s), s);
+        }
+    } else {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) f[e] = __uint_as_float(v[e]);
+    }
+    const TOut* bias = reinterpret_cast<const TOut*>(p.bias);
+    const TOut* res = reinterpret_cast<const TOut*>(p.residual);
+    TOut* dst = reinterpret_cast<TOut*>(p.C) + off;
+    if (full) {
+        if (bias) {
+            float b[8];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                load8(bias + col + 8 * h, b);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[8 * h + e] = __fadd_rn(f[8 * h + e], b[e]);
+            }
+        }
+        if (p.epi == EPI_RELU2) {
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+                const float a = fmaxf(round_to<TOut>(f[e]), 0.f);
+                f[e] = a * a;
+            }
+        } else if (res) {
+            float r[8];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                load8(res + off + 8 * h, r);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[8 * h + e] = __fadd_rn(f[8 * h + e], r[e]);
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            float o[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[e] = f[8 * h + e];
+            store8(dst + 8 * h, o);
+        }
+    } else {
+        for (int e = 0; e < 16 && col + e < p.N; ++e) {
+            float x = f[e];
+            if (bias) x = __fadd_rn(x, to_f<TOut>(bias[col + e]));
+            if (p.epi == EPI_RELU2) {
+                const float a = fmaxf(round_to<TOut>(x), 0.f);
+                x = a * a;
+            } else if (res) {
+                x = __fadd_rn(x, to_f<TOut>(res[off + e]));
+            }
+            dst[e] = from_f<TOut>(x);
+        }
+    }
+}
+
+template <int KIND, typename TOut>
+__global__ void __launch_bounds__(gm::THREADS, 1)
+gemm_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const GemmArgs p) {
+    using namespace gm;
+    extern __shared__ unsigned char smem_unaligned[];
+    unsigned char* sm = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);
+    uint64_t* full = reinterpret_cast<uint64_t*>(sm + STAGES * STAGE_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_full = empty + STAGES;
+    uint64_t* acc_empty = acc_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const AbortCtx actx{abort_flag, p.error};
+
+    constexpr int ES = (KIND == KIND_I8) ? 1 : 2;
+    constexpr int BK = BKB / ES;  // elements of K per stage
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nk = (p.K + BK - 1) / BK;
+    const int ntiles = p.tiles_m * p.tiles_n;
+
+    if (tid == 0) {
+        tma_prefetch_desc(&tm_a);
+        tma_prefetch_desc(&tm_b);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&acc_full[a], 1);
+            mbar_init(&acc_empty[a], 4);  // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < ntiles; tile += gridDim.x) {
+                int tm, tn;
+                tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+                for (int kb = 0; kb < nk; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) - 1) & 1, actx, kErrWaitEmpty)) {
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(&full[s], STAGE_BYTES);
+                    unsigned char* st = sm + s * STAGE_BYTES;
+                    tma_load_2d(st, &tm_a, &full[s], kb * BK, tm * BM);
+                    tma_load_2d(st + A_BYTES, &tm_b, &full[s], kb * BK, tn * BN);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = (KIND == KIND_I8)    ? make_idesc(BM, BN, /*S32*/ 2, /*S8*/ 1, /*S8*/ 1)
+                                       : (KIND == KIND_F16) ? make_idesc(BM, BN, /*F32*/ 1, /*F16*/ 0, /*F16*/ 0)
+                                                            : make_idesc(BM, BN, /*F32*/ 1, /*BF16*/ 1, /*BF16*/ 1);
+            int it = 0, li = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < ntiles; tile += gridDim.x, ++li) {
+                const int as = li & 1;
+                // the epilogue must have drained this accumulator's previous tile
+                if (li >= 2 && !mbar_wait(&acc_empty[as], ((li >> 1) - 1) & 1, actx, kErrWaitDFull)) break;
+                tc_fence_after();
+                const uint32_t d = tmem + (uint32_t)(as * BN);
+                for (int kb = 0; kb < nk; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait_hot(&full[s], (it / STAGES) & 1, actx, kErrWaitFull)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint64_t da = make_sw128_kmajor_desc(smem_u32(sm + s * STAGE_BYTES));
+                    const uint64_t db = make_sw128_kmajor_desc(smem_u32(sm + s * STAGE_BYTES + A_BYTES));
+#pragma unroll
+                    for (int j = 0; j < BKB / 32; ++j) {  // 32 bytes of K per instruction
+                        const uint32_t accumulate = (kb > 0 || j > 0) ? 1u : 0u;
+                        if constexpr (KIND == KIND_I8)
+                            umma_i8_ss(d, da + (uint64_t)(j * 2), db + (uint64_t)(j * 2), idesc, accumulate);
+                        else
+                            umma_f16_ss(d, da + (uint64_t)(j * 2), db + (uint64_t)(j * 2), idesc, accumulate);
+                    }
+                    tc_commit(&empty[s]);
+                }
+                if (ok) tc_commit(&acc_full[as]);
+            }
+        }
+    } else {
+        const int q = warp & 3;  // the TMEM lane quadrant this warp may read
+        int li = 0;
+        for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++li) {
+            const int as = li & 1;
+            int tm, tn;
+            tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+            bool ok = true;
+            if (lane == 0) ok = mbar_wait(&acc_full[as], (li >> 1) & 1, actx, kErrWaitDFull);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            tc_fence_after();
+            const int row = tm * BM + q * 32 + lane;
+            const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(as * BN);
+#pragma unroll 1
+            for (int c = 0; c < BN / 16; ++c) {
+                uint32_t v[16];
+                tmem_ld16(lane_addr + c * 16, v);
+                tc_wait_ld();
+                epilogue_chunk<KIND, TOut>(p, v, row, tn * BN + c * 16);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[as]);
+        }
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem, TMEM_COLS);
+    }
+}
+
+// number of SMs of the current device (cached per device; racing first callers store the same value)
+static int sm_count() {
+    static std::atomic<int> cache[kMaxDevices];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+    int n = cache[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cache[dev].store(n, std::memory_order_relaxed);
+    }
+    return n;
+}
+
+template <int KIND, typename TOut>
+static int launch_gemm(const void* a, const void* b, GemmArgs g, cudaStream_t st) {
+    using namespace gm;
+    constexpr int ES = (KIND == KIND_I8) ? 1 : 2;
+    constexpr CUtensorMapDataType dt = (KIND == KIND_I8)    ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                       : (KIND == KIND_F16) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                            : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    CUtensorMap tm_a, tm_b;
+    if (int e = make_tmap_2d(&tm_a, dt, ES, a, g.M, g.K, BM, BKB / ES, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
+    if (int e = make_tmap_2d(&tm_b, dt, ES, b, g.N, g.K, BN, BKB / ES, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
+    g.tiles_m = (g.M + BM - 1) / BM;
+    g.tiles_n = (g.N + BN - 1) / BN;
+    g.error = kernel_error_word();
+    RWKV7_REQUIRE(g.error != nullptr, RWKV7_ERR_CUDA, "gemm: cannot resolve the device error word");
+    auto kernel = gemm_umma_kernel<KIND, TOut>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    RWKV7_REQUIRE(e == cudaSuccess, RWKV7_ERR_CUDA, "gemm: %s", cudaGetErrorString(e));
+    const long long tiles = (long long)g.tiles_m * g.tiles_n;
+    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+    kernel<<<grid, THREADS, SMEM_BYTES, st>>>(tm_a, tm_b, g);
+    return check_launch("gemm_umma_kernel");
+}
+
+static bool epilogue_vectorisable(const GemmArgs& g) {
+    return g.N % 16 == 0 && aligned(g.C, 16) && (!g.bias || aligned(g.bias, 16)) && (!g.residual || aligned(g.residual, 16));
+}
+
+// int8 x int8 -> raw int32 accumulators.  RWKV7_ERR_UNSUPPORTED = shape / alignment not eligible (the caller falls
+// back to the mma.sync kernel).
+int launch_i8_gemm_umma(const int8_t* qa, const int8_t* qw, int32_t* acc, int M, int K, int Nout, cudaStream_t st) {
+    if (M < 64 || K % 16 || !aligned(qa, 16) || !aligned(qw, 16) || !aligned(acc, 16)) return RWKV7_ERR_UNSUPPORTED;
+    GemmArgs g{};
+    g.C = acc;
+    g.M = M, g.N = Nout, g.K = K;
+    g.epi = gm::EPI_RAW_I32;
+    g.vec = (Nout % 4 == 0);
+    return launch_gemm<gm::KIND_I8, float>(qa, qw, g, st);
+}
+
+// int8 GEMM with the A8W8 dequantisation fused into its epilogue; same eligibility rule
+int launch_i8_gemm_dequant_umma(const int8_t* qa, const float* sa, const int8_t* qw, const float* sw, const void* bias,
+                                const void* residual, void* out, int M, int K, int Nout, int dtype, cudaStream_t st) {
+    if (M < 64 || K % 16 || !aligned(qa, 16) || !aligned(qw, 16)) return RWKV7_ERR_UNSUPPORTED;
+    GemmArgs g{};
+    g.C = out, g.bias = bias, g.residual = residual, g.sa = sa, g.sw = sw;
+    g.M = M, g.N = Nout, g.K = K;
+    g.epi = gm::EPI_DEQUANT;
+    g.vec = epilogue_vectorisable(g);
+    RWKV7_DISPATCH_DTYPE(dtype, T, { return launch_gemm<gm::KIND_I8, T>(qa, qw, g, st); });
+    return RWKV7_OK;
+}
+
+}  // namespace rwkv7
+
+using namespace rwkv7;
+
+extern "C" int rwkv7_gemm(const void* a, const void* b, const void* bias, const void* residual, void* c, int M, int K,
+                          int N, int epilogue, int dtype, void* stream) {
+    RWKV7_REQUIRE(M > 0 && K > 0 && N > 0, RWKV7_ERR_INVALID, "gemm: sizes must be positive");
+    RWKV7_REQUIRE(dtype == RWKV7_F16 || dtype == RWKV7_BF16, RWKV7_ERR_UNSUPPORTED, "gemm: fp16 or bf16 operands only");
+    RWKV7_REQUIRE(K % 8 == 0, RWKV7_ERR_UNSUPPORTED, "gemm: K must be a multiple of 8 (got %d)", K);
+    RWKV7_REQUIRE(a && b && c, RWKV7_ERR_INVALID, "gemm: null pointer");
+    RWKV7_REQUIRE(aligned(a, 16) && aligned(b, 16), RWKV7_ERR_ALIGN, "gemm: operands must be 16-byte aligned");
+    RWKV7_REQUIRE(epilogue == 0 || epilogue == 1, RWKV7_ERR_INVALID, "gemm: epilogue must be 0 (store / add) or 1 (relu^2)");
+    RWKV7_REQUIRE(!(epilogue == 1 && residual), RWKV7_ERR_INVALID, "gemm: the relu^2 epilogue takes no residual");
+    GemmArgs g{};
+    g.C = c, g.bias = bias, g.residual = residual;
+    g.M = M, g.N = N, g.K = K;
+    g.epi = epilogue == 1 ? gm::EPI_RELU2 : gm::EPI_STORE;
+    g.vec = epilogue_vectorisable(g);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == RWKV7_F16) return launch_gemm<gm::KIND_F16, __half>(a, b, g, st);
+    return launch_gemm<gm::KIND_BF16, __nv_bfloat16>(a, b, g, st);
+}

@@ -2,7 +2,8 @@
 (rwkv7_hf/native_model.py:371-853, model_layers.py, model_fast_api.py:58-265) with the same module
 tree, parameter names and cache, so a reference ``state_dict`` loads unchanged.
 
-Two execution paths, both made only of this package's kernels plus plain dense GEMMs:
+Two execution paths, both made of this package's kernels (dense projections over fewer than 64 rows, or in fp32, are plain
+library GEMMs):
 
 * ``_decode_step``: one token for B sequences, every buffer preallocated so the whole step can be
   captured in a CUDA graph (``DecodeGraph``), the role of NativeGraphRunner
@@ -337,14 +338,15 @@ class RWKV7ForCausalLM(nn.Module):
             k_raw = _linear(at.k_proj, xk)
             v_raw = _linear(at.v_proj, xv)
             wl, al, gl = at.w_lora.lora, at.a_lora.lora, at.g_lora.lora
-            w_raw = F.linear(torch.tanh(F.linear(xw, wl[0].weight)), wl[2].weight, wl[2].bias)
-            a_pre = F.linear(F.linear(xa, al[0].weight), al[2].weight, al[2].bias)
-            g = F.linear(torch.sigmoid(F.linear(xg, gl[0].weight)), gl[2].weight)
+            # the rank-R LoRA pairs: dense GEMMs of this library (bias in the epilogue), the activation between them pointwise
+            w_raw = _linear(wl[2], torch.tanh(_linear(wl[0], xw)))
+            a_pre = _linear(al[2], _linear(al[0], xa))
+            g = _linear(gl[2], torch.sigmoid(_linear(gl[0], xg)))
             if i == 0:
                 vf, vg = None, None
             else:
                 vl = at.v_lora.lora
-                vf, vg = v_first, F.linear(F.linear(xv, vl[0].weight), vl[2].weight, vl[2].bias)
+                vf, vg = v_first, _linear(vl[2], _linear(vl[0], xv))
             w, k, v, kk = _prep.fused_prefill_state_prep(
                 w_raw, k_raw, v_raw, a_pre, at.k_k, at.k_a, v_first=vf, v_gate=vg, num_heads=H, head_dim=N,
                 a_is_raw=True, v_gate_is_raw=True)

@@ -20,6 +20,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from . import gemm as _gemm
 from . import lora as _lora
 from . import norm_mix as _nm
 from . import quant as _q
@@ -112,7 +113,7 @@ def init_batched_from_packs(packs, batch_size: int, device, dtype, *, state_dtyp
 def apply_linear(op, x, *, relu2=False, residual=None, out=None):
     """Apply a projection operand of the pack: a quantised module (epilogues fused through its rwkv7_forward_* hooks,
     as the reference's dispatch probes them: rwkv7_hf/native_jit_graph_dispatch.py:487-523), a dense ``[out,in]``
-    weight tensor, or an ``nn.Linear`` (one library GEMM each)."""
+    weight tensor, or an ``nn.Linear`` (this library's GEMM from 64 rows up in fp16 / bf16, else one library GEMM)."""
     if isinstance(op, _QUANT_TYPES):
         if relu2:
             if hasattr(op, "rwkv7_forward_relu2"):
@@ -123,10 +124,12 @@ def apply_linear(op, x, *, relu2=False, residual=None, out=None):
         if out is not None:
             return op.rwkv7_forward_into(x, out)
         return op(x)
-    if isinstance(op, torch.Tensor):
-        y = F.linear(x, op)
-    else:
-        y = F.linear(x, op.weight, op.bias)
+    weight, bias = (op, None) if isinstance(op, torch.Tensor) else (op.weight, op.bias)
+    rows = x.numel() // int(x.shape[-1])
+    if rows >= _gemm.MIN_ROWS and _gemm.takes(x, weight) and (bias is None or bias.dtype == x.dtype):
+        # many rows over a dense fp16 / bf16 weight: this library's tensor-core GEMM, epilogue fused
+        return _gemm.dense_linear(x, weight, bias, relu2=relu2, residual=residual, out=out)
+    y = F.linear(x, weight, bias)
     if relu2:
         y = torch.relu(y) ** 2
     elif residual is not None:

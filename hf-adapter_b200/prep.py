@@ -112,8 +112,8 @@ def fused_prefill_kv_kk_prep(k_raw, v_raw, a, k_k, k_a, *, v_first=None, v_gate=
 def fused_attn_output_project(recurrent_out, r, k, v, g, r_k, group_norm_weight, group_norm_bias, o_proj_weight,
                               o_proj_bias=None, *, num_heads: int, head_dim: int, head_v_dim: int, eps: float,
                               block_m: int = 32, force_fallback: bool = False):
-    """Output prep followed by ``o_proj`` (rwkv7_hf/fused_output.py:278): the prep kernel, then one dense GEMM
-    (a quantised ``o_proj`` module is applied as a callable)."""
+    """Output prep followed by ``o_proj`` (rwkv7_hf/fused_output.py:278): the prep kernel, then this library's GEMM (bias in
+    its epilogue; a quantised ``o_proj`` module is applied as a callable)."""
     no_fallback(force_fallback, "fused_attn_output_project")
     prepared = fused_attn_output_prepare(recurrent_out, r, k, v, g, r_k, group_norm_weight, group_norm_bias,
                                          num_heads=num_heads, head_dim=head_dim, head_v_dim=head_v_dim, eps=eps)
@@ -125,7 +125,20 @@ def fused_attn_output_project(recurrent_out, r, k, v, g, r_k, group_norm_weight,
         raise ValueError(f"o_proj_weight must be [output_dim, {value_dim}], got {tuple(o_proj_weight.shape)}")
     if o_proj_bias is not None and (o_proj_bias.dim() != 1 or int(o_proj_bias.shape[0]) != int(o_proj_weight.shape[0])):
         raise ValueError(f"o_proj_bias must be [{int(o_proj_weight.shape[0])}]")
+    from . import gemm as _gemm
+    if _gemm.takes(prepared, o_proj_weight) and (o_proj_bias is None or o_proj_bias.dtype == prepared.dtype):
+        return _gemm.dense_linear(prepared, o_proj_weight, o_proj_bias)
     return torch.nn.functional.linear(prepared, o_proj_weight, o_proj_bias)
+
+
+def _dense(x, weight, *, relu2: bool = False):
+    """A dense projection: this library's GEMM with the relu^2 fused for fp16 / bf16, a library GEMM plus the relu^2
+    kernel for fp32 operands (the tensor-core kernel has no fp32-operand form)."""
+    from . import gemm as _gemm
+    if _gemm.takes(x, weight):
+        return _gemm.dense_linear(x, weight, relu2=relu2)
+    y = torch.nn.functional.linear(x, weight)
+    return relu2_(y) if relu2 else y
 
 
 def relu2_(x):
@@ -165,8 +178,8 @@ def fused_ffn(hidden_states, prev_states, mix_x, key_weight, value_weight, *, bl
         raise ValueError("hidden_states and prev_states must have identical flattened shape/layout")
     mix = _ffn_checks(hidden, mix_x, key_weight, value_weight)
     mixed, _ = _nm.fused_ffn_sequence_shift_mix(x2.reshape(-1, 1, hidden), prev2.contiguous(), mix)
-    mid = relu2_(torch.nn.functional.linear(mixed.reshape(-1, hidden), key_weight))
-    out = torch.nn.functional.linear(mid, value_weight)
+    mid = _dense(mixed.reshape(-1, hidden), key_weight, relu2=True)
+    out = _dense(mid, value_weight)
     if had_seq:
         return out.unsqueeze(1), hidden_states[:, -1:].contiguous()
     return out, hidden_states.contiguous()
@@ -191,6 +204,6 @@ def fused_sequence_ffn(hidden_states, prev_states, mix_x, key_weight, value_weig
         raise ValueError(f"prev_states must be [{batch},{hidden}], got {tuple(prev_states.shape)}")
     mix = _ffn_checks(hidden, mix_x, key_weight, value_weight)
     mixed, nxt = _nm.fused_ffn_sequence_shift_mix(hidden_states, prev_states.contiguous(), mix)
-    mid = relu2_(torch.nn.functional.linear(mixed.reshape(batch * tokens, hidden), key_weight))
-    out = torch.nn.functional.linear(mid, value_weight)
+    mid = _dense(mixed.reshape(batch * tokens, hidden), key_weight, relu2=True)
+    out = _dense(mid, value_weight)
     return out.reshape(batch, tokens, hidden), nxt

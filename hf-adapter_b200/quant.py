@@ -186,11 +186,31 @@ def w8_dequant(q, s, out=None):
     return out
 
 
+def _dense_after_dequant(x2, weight, relu2, res, out):
+    """Many rows over a quantised weight: the weight was materialised in the activation type as ``[out,in]``; one launch
+    of this library's tensor-core GEMM applies it with the relu^2 / residual epilogue fused (fp16 / bf16; fp32
+    activations take a library GEMM and pointwise kernels)."""
+    from . import gemm as _gemm
+    M, Nout = int(x2.shape[0]), int(weight.shape[0])
+    if _gemm.takes(x2, weight):
+        return _gemm.dense_linear(x2, weight, relu2=relu2, residual=res, out=None if out is None else out.reshape(M, Nout))
+    y = torch.matmul(x2, weight.t())
+    if relu2:
+        y = torch.relu(y) ** 2
+    elif res is not None:
+        y = y + res
+    if out is not None:
+        out.reshape(M, Nout).copy_(y)
+        y = out.reshape(M, Nout)
+    return y
+
+
 def w4_groupwise_linear(x, q, scales, out_features, in_features, *, group_size=128, out=None, zeros=None,
                         relu2: bool = False, residual=None):
     """y = x @ ((nibble - zero) * scale)^T.  Up to GEMV_MAX_ROWS rows run the weight-streaming kernel with the
-    optional relu^2 / residual-add epilogue fused; more rows dequantise the weight and call one dense GEMM
-    (what the reference does on every call off sm_70, rwkv7_hf/sm70_quant.py:598-610)."""
+    optional relu^2 / residual-add epilogue fused; more rows dequantise the weight and run this library's dense GEMM
+    with the same epilogues (the reference dequantises and calls F.linear on every call off sm_70,
+    rwkv7_hf/sm70_quant.py:598-610)."""
     group_size = int(group_size)
     if group_size not in {128, 256} or int(in_features) % group_size:
         raise ValueError("groupwise W4 requires group_size=128/256 and divisible K")
@@ -206,14 +226,7 @@ def w4_groupwise_linear(x, q, scales, out_features, in_features, *, group_size=1
         _lib.check(_lib.lib.rwkv7_w4g_gemv(ptr(x2), ptr(q), ptr(scales), ptr(zeros), ptr(res), ptr(y), M, K, Nout,
                                            group_size, epi, dt_code(x2), stream_ptr(x2)), "w4_groupwise_linear")
     else:
-        y = torch.matmul(x2, w4_dequant(q, scales, K, group_size, zeros).t())
-        if relu2:
-            y = torch.relu(y) ** 2
-        elif res is not None:
-            y = y + res
-        if out is not None:
-            out.reshape(M, Nout).copy_(y)
-            y = out
+        y = _dense_after_dequant(x2, w4_dequant(q, scales, K, group_size, zeros), relu2, res, out)
     return y.reshape(*x.shape[:-1], Nout)
 
 
@@ -231,14 +244,7 @@ def w8_linear(x, q, s, out=None, *, relu2: bool = False, residual=None):
         _lib.check(_lib.lib.rwkv7_w8_gemv(ptr(x2), ptr(q), ptr(s), ptr(res), ptr(y), M, K, Nout, epi, dt_code(x2),
                                           stream_ptr(x2)), "w8_linear")
     else:
-        y = torch.matmul(x2, w8_dequant(q, s).t())
-        if relu2:
-            y = torch.relu(y) ** 2
-        elif res is not None:
-            y = y + res
-        if out is not None:
-            out.reshape(M, Nout).copy_(y)
-            y = out
+        y = _dense_after_dequant(x2, w8_dequant(q, s), relu2, res, out)
     return y.reshape(*x.shape[:-1], Nout)
 
 
@@ -298,7 +304,7 @@ def a8w8_linear(x, q_weight_t, weight_scale, bias=None, *, out=None, residual=No
     y = torch.empty((M, Nout), device=x2.device, dtype=x2.dtype) if out is None else out.reshape(M, Nout)
     _lib.check(_lib.lib.rwkv7_a8w8_linear(ptr(x2), ptr(qw), ptr(weight_scale), ptr(bias), ptr(res), ptr(y),
                                           ptr(workspace), int(workspace.numel()), M, K, Nout, dt_code(x2),
-                                          stream_ptr(x2)), "a8w8_linear", kernels=3)
+                                          stream_ptr(x2)), "a8w8_linear", kernels=2 if M >= 64 else 3)
     return y.reshape(*x.shape[:-1], Nout)
 
 

@@ -301,6 +301,14 @@ int rwkv7_a8_quant(const void* x, int8_t* q, float* scale, int rows, int K, int 
  * acc [M,Nout] i32. */
 int rwkv7_i8_gemm(const int8_t* qa, const int8_t* qw, int32_t* acc, int M, int K, int Nout, void* stream);
 
+/* Dense fp16 / bf16 GEMM with a fused epilogue, for projections over many rows (prefill):
+ *   c[M,N] = a[M,K] . b[N,K]^T (+ bias[N])  then  epilogue 0: (+ residual[M,N])   epilogue 1: relu(.)^2 of the rounded value
+ * a = activations row-major, b = an nn.Linear weight [out,in]; fp32 accumulation; bias / residual / c in `dtype`.
+ * Replaces the tl.dot GEMMs with fused mix / relu^2 / residual of rwkv7_hf/fused_ffn.py:39-232 and the F.linear calls
+ * of the layer-wise prefill (rwkv7_hf/native_jit_prefill.py:964-1040).  K % 8 == 0. */
+int rwkv7_gemm(const void* a, const void* b, const void* bias, const void* residual, void* c, int M, int K, int N,
+               int epilogue, int dtype, void* stream);
+
 /* Dequant epilogue; replaces _a8w8_dequant_kernel / _a8w8_dequant_add_kernel
  * (rwkv7_hf/native_quant_a8w8.py:166-264): out = fp32(acc)*sa[row]*sw[col] (+bias) (+residual). */
 int rwkv7_a8w8_dequant(const int32_t* acc, const float* sa, const float* sw, const void* bias,
@@ -311,7 +319,8 @@ int rwkv7_a8w8_dequant(const int32_t* acc, const float* sa, const float* sw, con
 int rwkv7_a8w8_relu2_requant(const int32_t* acc, const float* sa, const float* sw, const void* bias, int8_t* q,
                              float* scale, int M, int N, int dtype, void* stream);
 
-/* a8w8_linear (rwkv7_hf/native_quant_a8w8.py:323): quantise rows, integer GEMM, dequantise.
+/* a8w8_linear (rwkv7_hf/native_quant_a8w8.py:323): quantise rows, integer GEMM, dequantise.  With 64 rows or more
+ * the dequantisation runs in the epilogue of the tensor-core GEMM and the accumulators never reach memory.
  * workspace: caller-owned scratch of at least rwkv7_a8w8_workspace_bytes(M,K,Nout) bytes, 256-byte aligned. */
 int64_t rwkv7_a8w8_workspace_bytes(int M, int K, int Nout);
 int rwkv7_a8w8_linear(const void* x, const int8_t* qw, const float* sw, const void* bias, const void* residual,
