@@ -25,6 +25,7 @@ from .recurrent import (dplr_chunk_scan, fused_recurrent_output_prepare, fused_r
                         native_fp16_recurrent_should_use, native_fp16_sequence, self_chunk_rwkv7)
 
 from .sharding import shard_spec, shard_state_dict
+from .state_pool import PoolDecodeGraph, PrefixEntry, RWKV7StatePool, StaleSlotError
 
 NativeRWKV7ForCausalLM = RWKV7ForCausalLM
 __version__ = "0.1.0"

@@ -39,6 +39,9 @@ SIGNATURES = {
     "rwkv7_wkv7_output_prepare_raw_f16state": (I, [P] * 14 + [P, P, I, P, P, P, I, P, P, I, I, I, I, I, F, I, P]),
     "rwkv7_wkv7_chunk_scan": (I, [P] * 9 + [I, I, I, I, I, I, I, P]),
     "rwkv7_attn_norm_mix6": (I, [P, P, P, P, PP, PP, I, I, F, I, P]),
+    "rwkv7_attn_norm_mix6_pool": (I, [P, P, P, P, P, PP, PP, I, I, F, I, P]),
+    "rwkv7_ffn_add_norm_mix_pool": (I, [P] * 9 + [I, I, F, I, P]),
+    "rwkv7_wkv7_output_prepare_raw_pool": (I, [P] * 14 + [P, P, I, P, P, P, I, P, I, I, I, I, F, I, P]),
     "rwkv7_ffn_add_norm_mix": (I, [P] * 8 + [I, I, F, I, P]),
     "rwkv7_layer_norm": (I, [P] * 4 + [I, I, F, I, P]),
     "rwkv7_seq_shift_mix": (I, [P, P, PP, PP, P, I, I, I, I, I, I, P]),

@@ -9,15 +9,36 @@
 namespace rwkv7 {
 
 // ---------------------------------------------------------------- quantiser
-// one CTA per row; s = max(amax/127, 1e-5); q = clamp(round_half_away(x / s), +-127)
+// one CTA per row; s = max(amax/127, 1e-5); q = clamp(round_half_away(x / s), +-127).  The row is read from memory
+// ONCE: each thread keeps its 8-element chunks in registers between the amax pass and the quantising pass (rows up to
+// 256 * 8 * kQuantChunks elements; longer rows re-read the tail, which then comes from L2).
+constexpr int kQuantChunks = 8;
+
+__device__ __forceinline__ int8_t quant_one(float v, float s) {
+    const float t = __fdiv_rn(v, s);
+    float r = (t >= 0.f) ? floorf(t + 0.5f) : ceilf(t - 0.5f);
+    r = fminf(fmaxf(r, -127.f), 127.f);
+    return (int8_t)(int)r;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) a8_quant_kernel(const T* __restrict__ x, int8_t* __restrict__ q,
                                                        float* __restrict__ scale, int K) {
     __shared__ float red[32];
     const size_t row = blockIdx.x;
     const T* xr = x + row * K;
+    Vec8<T> keep[kQuantChunks];  // the row's chunks in their storage type: 4 registers per chunk for 16-bit inputs
     float amax = 0.f;
-    for (int k = threadIdx.x * 8; k < K; k += 256 * 8) {
+#pragma unroll
+    for (int c = 0; c < kQuantChunks; ++c) {
+        const int k = (c * 256 + threadIdx.x) * 8;
+        if (k < K) {
+            keep[c] = *reinterpret_cast<const Vec8<T>*>(xr + k);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(to_f<T>(keep[c].v[e])));
+        }
+    }
+    for (int k = (kQuantChunks * 256 + threadIdx.x) * 8; k < K; k += 256 * 8) {
         float v[8];
         load8(xr + k, v);
 #pragma unroll
@@ -26,17 +47,22 @@ __global__ void __launch_bounds__(256) a8_quant_kernel(const T* __restrict__ x, 
     amax = block_max(amax, red);
     const float s = fmaxf(__fdiv_rn(amax, 127.0f), 1.0e-5f);
     if (threadIdx.x == 0) scale[row] = s;
-    for (int k = threadIdx.x * 8; k < K; k += 256 * 8) {
+#pragma unroll
+    for (int c = 0; c < kQuantChunks; ++c) {
+        const int k = (c * 256 + threadIdx.x) * 8;
+        if (k < K) {
+            alignas(8) int8_t o[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[e] = quant_one(to_f<T>(keep[c].v[e]), s);
+            *reinterpret_cast<uint2*>(q + row * K + k) = *reinterpret_cast<const uint2*>(o);
+        }
+    }
+    for (int k = (kQuantChunks * 256 + threadIdx.x) * 8; k < K; k += 256 * 8) {
         float v[8];
         load8(xr + k, v);
         alignas(8) int8_t o[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            const float t = __fdiv_rn(v[e], s);
-            float r = (t >= 0.f) ? floorf(t + 0.5f) : ceilf(t - 0.5f);
-            r = fminf(fmaxf(r, -127.f), 127.f);
-            o[e] = (int8_t)(int)r;
-        }
+        for (int e = 0; e < 8; ++e) o[e] = quant_one(v[e], s);
         *reinterpret_cast<uint2*>(q + row * K + k) = *reinterpret_cast<const uint2*>(o);
     }
 }

@@ -12,6 +12,7 @@
 // tensor memory, so the epilogue warps drain tile i while the tensor pipe already works on tile i + 1.
 // Warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner, warps 2-5 = epilogue (TMEM -> registers -> global).
 // Ragged M / N / K edges are zero-filled by TMA and masked at the store.  All waits are bounded (umma.cuh).
+// With more than 128 rows the same roles run as CTA pairs on 256 x 256 tiles (second kernel below).
 #include "umma.cuh"
 
 namespace rwkv7 {
@@ -256,6 +257,162 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     }
 }
 
+// ---------------------------------------------------------------- CTA-pair variant (tcgen05 cta_group::2)
+// Two CTAs of a cluster share one 256 x 256 output tile.  Each stages its own 128 rows of A and 128 of the 256 rows
+// of B (32 KB per stage instead of 48 KB, so the shared-memory fill per MMA cycle drops by a third and six stages
+// fit); the even CTA issues MMAs of M = 256 that read both CTAs' shared memory and write each CTA's 128 result rows
+// into that CTA's tensor memory.  Barrier protocol: both producers' TMA loads complete on the LEADER's full[s]
+// (armed by the leader with the byte count of both); the leader's commits arrive on empty[s] / acc_full[a] in BOTH
+// CTAs; all eight epilogue warps arrive on the leader's acc_empty[a].  No TMA multicast.
+namespace gp {
+constexpr int BM = 128, PAIR_M = 256, BN = 256, HALF_N = 128, BKB = 128, STAGES = 6, THREADS = 192;
+constexpr int A_BYTES = BM * BKB, B_BYTES = HALF_N * BKB, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int TMEM_COLS = 512;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 256 + 1024;
+}  // namespace gp
+
+template <int KIND, typename TOut>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(gp::THREADS, 1)
+gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const GemmArgs p) {
+    using namespace gp;
+    extern __shared__ unsigned char smem_unaligned[];
+    unsigned char* sm = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);
+    uint64_t* full = reinterpret_cast<uint64_t*>(sm + STAGES * STAGE_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_full = empty + STAGES;
+    uint64_t* acc_empty = acc_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const AbortCtx actx{abort_flag, p.error};
+
+    constexpr int ES = (KIND == gm::KIND_I8) ? 1 : 2;
+    constexpr int BK = BKB / ES;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+    const int nk = (p.K + BK - 1) / BK;
+    const int ntiles = p.tiles_m * p.tiles_n;  // tiles of 256 x 256
+
+    if (tid == 0) {
+        tma_prefetch_desc(&tm_a);
+        tma_prefetch_desc(&tm_b);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], 1);   // used in the leader only
+            mbar_init(&empty[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&acc_full[a], 1);
+            mbar_init(&acc_empty[a], 8);  // used in the leader only: four epilogue warps of each CTA
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    // the peer's barriers must exist before anything of this CTA signals them
+    cluster_arrive_release();
+    cluster_wait();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            bool ok = true;
+            for (int tile = pair; ok && tile < ntiles; tile += npairs) {
+                int tm, tn;
+                tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+                const int row_a = tm * PAIR_M + (int)rank * BM, row_b = tn * BN + (int)rank * HALF_N;
+                for (int kb = 0; kb < nk; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) - 1) & 1, actx, kErrWaitEmpty)) {
+                        ok = false;
+                        break;
+                    }
+                    if (leader) mbar_expect_tx(&full[s], 2 * STAGE_BYTES);
+                    const uint32_t bar = mapa_shared(smem_u32(&full[s]), 0);
+                    unsigned char* st = sm + s * STAGE_BYTES;
+                    tma_load_2d_pair(st, &tm_a, bar, kb * BK, row_a);
+                    tma_load_2d_pair(st + A_BYTES, &tm_b, bar, kb * BK, row_b);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (leader && lane == 0) {
+            constexpr uint32_t idesc = (KIND == gm::KIND_I8)    ? make_idesc(PAIR_M, BN, /*S32*/ 2, /*S8*/ 1, /*S8*/ 1)
+                                       : (KIND == gm::KIND_F16) ? make_idesc(PAIR_M, BN, /*F32*/ 1, /*F16*/ 0, /*F16*/ 0)
+                                                                : make_idesc(PAIR_M, BN, /*F32*/ 1, /*BF16*/ 1, /*BF16*/ 1);
+            int it = 0, li = 0;
+            bool ok = true;
+            for (int tile = pair; ok && tile < ntiles; tile += npairs, ++li) {
+                const int as = li & 1;
+                if (li >= 2 && !mbar_wait(&acc_empty[as], ((li >> 1) - 1) & 1, actx, kErrWaitDFull)) break;
+                tc_fence_after();
+                const uint32_t d = tmem + (uint32_t)(as * BN);
+                for (int kb = 0; kb < nk; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait_hot(&full[s], (it / STAGES) & 1, actx, kErrWaitFull)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint64_t da = make_sw128_kmajor_desc(smem_u32(sm + s * STAGE_BYTES));
+                    const uint64_t db = make_sw128_kmajor_desc(smem_u32(sm + s * STAGE_BYTES + A_BYTES));
+#pragma unroll
+                    for (int j = 0; j < BKB / 32; ++j) {
+                        const uint32_t accumulate = (kb > 0 || j > 0) ? 1u : 0u;
+                        if constexpr (KIND == gm::KIND_I8)
+                            umma_i8_ss_pair(d, da + (uint64_t)(j * 2), db + (uint64_t)(j * 2), idesc, accumulate);
+                        else
+                            umma_f16_ss_pair(d, da + (uint64_t)(j * 2), db + (uint64_t)(j * 2), idesc, accumulate);
+                    }
+                    tc_commit_pair(&empty[s]);
+                }
+                if (ok) tc_commit_pair(&acc_full[as]);
+            }
+        }
+    } else {
+        const int q = warp & 3;
+        int li = 0;
+        for (int tile = pair; tile < ntiles; tile += npairs, ++li) {
+            const int as = li & 1;
+            int tm, tn;
+            tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+            bool ok = true;
+            if (lane == 0) ok = mbar_wait(&acc_full[as], (li >> 1) & 1, actx, kErrWaitDFull);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            tc_fence_after();
+            const int row = tm * PAIR_M + (int)rank * BM + q * 32 + lane;
+            const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(as * BN);
+#pragma unroll 1
+            for (int c = 0; c < BN / 16; ++c) {
+                uint32_t v[16];
+                tmem_ld16(lane_addr + c * 16, v);
+                tc_wait_ld();
+                epilogue_chunk<KIND, TOut>(p, v, row, tn * BN + c * 16);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                if (leader) mbar_arrive(&acc_empty[as]);
+                else mbar_arrive_cluster(mapa_shared(smem_u32(&acc_empty[as]), 0));
+            }
+        }
+    }
+    // neither CTA may free its tensor memory or leave while the other can still touch its memory
+    tc_fence_before();
+    __syncthreads();
+    cluster_arrive_release();
+    cluster_wait();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem, TMEM_COLS);
+    }
+}
+
 // number of SMs of the current device (cached per device; racing first callers store the same value)
 static int sm_count() {
     static std::atomic<int> cache[kMaxDevices];
@@ -277,12 +434,27 @@ static int launch_gemm(const void* a, const void* b, GemmArgs g, cudaStream_t st
                                        : (KIND == KIND_F16) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                                             : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     CUtensorMap tm_a, tm_b;
+    g.error = kernel_error_word();
+    RWKV7_REQUIRE(g.error != nullptr, RWKV7_ERR_CUDA, "gemm: cannot resolve the device error word");
+    if (g.M > BM) {
+        // more than one 128-row tile: CTA pairs on 256 x 256 tiles
+        if (int e = make_tmap_2d(&tm_a, dt, ES, a, g.M, g.K, gp::BM, BKB / ES, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
+        if (int e = make_tmap_2d(&tm_b, dt, ES, b, g.N, g.K, gp::HALF_N, BKB / ES, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
+        g.tiles_m = (g.M + gp::PAIR_M - 1) / gp::PAIR_M;
+        g.tiles_n = (g.N + gp::BN - 1) / gp::BN;
+        auto pk = gemm_umma_pair_kernel<KIND, TOut>;
+        cudaError_t pe = cudaFuncSetAttribute(pk, cudaFuncAttributeMaxDynamicSharedMemorySize, gp::SMEM_BYTES);
+        RWKV7_REQUIRE(pe == cudaSuccess, RWKV7_ERR_CUDA, "gemm: %s", cudaGetErrorString(pe));
+        const long long pairs_wanted = (long long)g.tiles_m * g.tiles_n;
+        const int pairs_fit = sm_count() / 2;
+        const int pairs = (int)(pairs_wanted < pairs_fit ? pairs_wanted : pairs_fit);
+        pk<<<2 * pairs, gp::THREADS, gp::SMEM_BYTES, st>>>(tm_a, tm_b, g);
+        return check_launch("gemm_umma_pair_kernel");
+    }
     if (int e = make_tmap_2d(&tm_a, dt, ES, a, g.M, g.K, BM, BKB / ES, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
     if (int e = make_tmap_2d(&tm_b, dt, ES, b, g.N, g.K, BN, BKB / ES, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
     g.tiles_m = (g.M + BM - 1) / BM;
     g.tiles_n = (g.N + BN - 1) / BN;
-    g.error = kernel_error_word();
-    RWKV7_REQUIRE(g.error != nullptr, RWKV7_ERR_CUDA, "gemm: cannot resolve the device error word");
     auto kernel = gemm_umma_kernel<KIND, TOut>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     RWKV7_REQUIRE(e == cudaSuccess, RWKV7_ERR_CUDA, "gemm: %s", cudaGetErrorString(e));

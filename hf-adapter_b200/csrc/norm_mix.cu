@@ -75,6 +75,7 @@ struct Mix6Args {
     void* out[6];
     int D;
     float eps;
+    const int* slots;  // state pool: the shift state of batch row b is row slots[b] of `prev`; NULL = row b
 };
 
 template <typename T>
@@ -100,7 +101,7 @@ __global__ void __launch_bounds__(kNMThreads) attn_norm_mix6_kernel(const Mix6Ar
     if (threadIdx.x == 0) grid_launch_dependents();
     RowStats<T> rs;
     load_row_stats<T, false>(reinterpret_cast<const T*>(p.x) + row * D, nullptr, nullptr, D, p.eps, rs, red);
-    T* prev = reinterpret_cast<T*>(p.prev) + row * D;
+    T* prev = reinterpret_cast<T*>(p.prev) + (p.slots ? (size_t)__ldg(p.slots + row) : row) * D;
 #pragma unroll
     for (int i = 0; i < kNMMaxVec; ++i) {
         const int vi = threadIdx.x + i * kNMThreads;
@@ -132,6 +133,7 @@ struct FfnMixArgs {
     void *prev, *res_out, *mixed;
     int D;
     float eps;
+    const int* slots;  // as in Mix6Args
 };
 
 // ADD: x = res + attn (stored to res_out; normalised from the fp32 sum like the reference's fused kernel)
@@ -169,7 +171,7 @@ __global__ void __launch_bounds__(kNMThreads) ffn_add_norm_mix_kernel(const FfnM
             for (int e = 0; e < 8; ++e) h[e] = (rs.x[i][e] - rs.mean) * rs.rstd * w[e] + b[e];
             if constexpr (MIX) {
                 float pv[8], mx[8], o[8];
-                T* prev = reinterpret_cast<T*>(p.prev) + row * D;
+                T* prev = reinterpret_cast<T*>(p.prev) + (p.slots ? (size_t)__ldg(p.slots + row) : row) * D;
                 load8(prev + vi * 8, pv);
                 cvt8(cm[i], mx);
 #pragma unroll
@@ -236,13 +238,13 @@ static int check_row_shape(const char* what, int rows, int D) {
 
 using namespace rwkv7;
 
-extern "C" int rwkv7_attn_norm_mix6(const void* x, void* prev, const void* norm_w, const void* norm_b,
-                                    const void* const mixes[6], void* const outs[6], int rows, int D, float eps,
-                                    int dtype, void* stream) {
+static int attn_norm_mix6_impl(const void* x, void* prev, const int32_t* slots, const void* norm_w, const void* norm_b,
+                               const void* const mixes[6], void* const outs[6], int rows, int D, float eps, int dtype,
+                               void* stream) {
     if (int e = check_row_shape("attn_norm_mix6", rows, D)) return e;
     RWKV7_REQUIRE(x && prev && norm_w && norm_b && mixes && outs, RWKV7_ERR_INVALID, "attn_norm_mix6: null pointer");
     RWKV7_REQUIRE(x != prev, RWKV7_ERR_INVALID, "attn_norm_mix6: x and prev must not alias");
-    Mix6Args p{x, norm_w, norm_b, prev, {}, {}, D, eps};
+    Mix6Args p{x, norm_w, norm_b, prev, {}, {}, D, eps, slots};
     for (int m = 0; m < 6; ++m) {
         RWKV7_REQUIRE(mixes[m] && outs[m], RWKV7_ERR_INVALID, "attn_norm_mix6: null mix/out pointer %d", m);
         RWKV7_REQUIRE(aligned(mixes[m], 16) && aligned(outs[m], 16), RWKV7_ERR_ALIGN, "attn_norm_mix6: unaligned pointer");
@@ -259,16 +261,29 @@ extern "C" int rwkv7_attn_norm_mix6(const void* x, void* prev, const void* norm_
     return RWKV7_OK;
 }
 
-extern "C" int rwkv7_ffn_add_norm_mix(const void* residual, const void* attn_out, void* prev, const void* norm_w,
-                                      const void* norm_b, const void* mix, void* residual_out, void* mixed, int rows,
-                                      int D, float eps, int dtype, void* stream) {
+extern "C" int rwkv7_attn_norm_mix6(const void* x, void* prev, const void* norm_w, const void* norm_b,
+                                    const void* const mixes[6], void* const outs[6], int rows, int D, float eps,
+                                    int dtype, void* stream) {
+    return attn_norm_mix6_impl(x, prev, nullptr, norm_w, norm_b, mixes, outs, rows, D, eps, dtype, stream);
+}
+
+extern "C" int rwkv7_attn_norm_mix6_pool(const void* x, void* prev_pool, const int32_t* slot_ids, const void* norm_w,
+                                         const void* norm_b, const void* const mixes[6], void* const outs[6], int rows,
+                                         int D, float eps, int dtype, void* stream) {
+    RWKV7_REQUIRE(slot_ids != nullptr, RWKV7_ERR_INVALID, "attn_norm_mix6_pool: null slot_ids");
+    return attn_norm_mix6_impl(x, prev_pool, slot_ids, norm_w, norm_b, mixes, outs, rows, D, eps, dtype, stream);
+}
+
+static int ffn_add_norm_mix_impl(const void* residual, const void* attn_out, void* prev, const int32_t* slots,
+                                 const void* norm_w, const void* norm_b, const void* mix, void* residual_out, void* mixed,
+                                 int rows, int D, float eps, int dtype, void* stream) {
     if (int e = check_row_shape("ffn_add_norm_mix", rows, D)) return e;
     RWKV7_REQUIRE(residual && prev && norm_w && norm_b && mix && mixed, RWKV7_ERR_INVALID, "ffn_add_norm_mix: null pointer");
     RWKV7_REQUIRE(attn_out == nullptr || residual_out != nullptr, RWKV7_ERR_INVALID,
                   "ffn_add_norm_mix: residual_out is required when attn_out is given");
     const void* ptrs[] = {residual, attn_out, prev, norm_w, norm_b, mix, residual_out, mixed};
     for (const void* q : ptrs) RWKV7_REQUIRE(aligned(q, 16), RWKV7_ERR_ALIGN, "ffn_add_norm_mix: unaligned pointer");
-    FfnMixArgs p{residual, attn_out, norm_w, norm_b, mix, prev, residual_out, mixed, D, eps};
+    FfnMixArgs p{residual, attn_out, norm_w, norm_b, mix, prev, residual_out, mixed, D, eps, slots};
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     RWKV7_DISPATCH_DTYPE(dtype, T, {
         if (attn_out) launch_programmatic(ffn_add_norm_mix_kernel<T, true, true>, dim3(rows), dim3(kNMThreads), 0, st, p);
@@ -278,13 +293,29 @@ extern "C" int rwkv7_ffn_add_norm_mix(const void* residual, const void* attn_out
     return RWKV7_OK;
 }
 
+extern "C" int rwkv7_ffn_add_norm_mix(const void* residual, const void* attn_out, void* prev, const void* norm_w,
+                                      const void* norm_b, const void* mix, void* residual_out, void* mixed, int rows,
+                                      int D, float eps, int dtype, void* stream) {
+    return ffn_add_norm_mix_impl(residual, attn_out, prev, nullptr, norm_w, norm_b, mix, residual_out, mixed, rows, D, eps,
+                                 dtype, stream);
+}
+
+extern "C" int rwkv7_ffn_add_norm_mix_pool(const void* residual, const void* attn_out, void* prev_pool,
+                                           const int32_t* slot_ids, const void* norm_w, const void* norm_b,
+                                           const void* mix, void* residual_out, void* mixed, int rows, int D, float eps,
+                                           int dtype, void* stream) {
+    RWKV7_REQUIRE(slot_ids != nullptr, RWKV7_ERR_INVALID, "ffn_add_norm_mix_pool: null slot_ids");
+    return ffn_add_norm_mix_impl(residual, attn_out, prev_pool, slot_ids, norm_w, norm_b, mix, residual_out, mixed, rows, D,
+                                 eps, dtype, stream);
+}
+
 extern "C" int rwkv7_layer_norm(const void* x, const void* norm_w, const void* norm_b, void* out, int rows, int D,
                                 float eps, int dtype, void* stream) {
     if (int e = check_row_shape("layer_norm", rows, D)) return e;
     RWKV7_REQUIRE(x && norm_w && norm_b && out, RWKV7_ERR_INVALID, "layer_norm: null pointer");
     const void* ptrs[] = {x, norm_w, norm_b, out};
     for (const void* q : ptrs) RWKV7_REQUIRE(aligned(q, 16), RWKV7_ERR_ALIGN, "layer_norm: unaligned pointer");
-    FfnMixArgs p{x, nullptr, norm_w, norm_b, nullptr, nullptr, nullptr, out, D, eps};
+    FfnMixArgs p{x, nullptr, norm_w, norm_b, nullptr, nullptr, nullptr, out, D, eps, nullptr};
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     RWKV7_DISPATCH_DTYPE(dtype, T, {
         launch_programmatic(ffn_add_norm_mix_kernel<T, false, false>, dim3(rows), dim3(kNMThreads), 0, st, p);

@@ -37,6 +37,7 @@ struct StepArgs {
     int H;
     float eps;
     int prefetch_state;  // load the state tile before the grid-dependency wait (state_prefetch argument of the raw entry point)
+    const int* slots;    // state pool: row b of the batch lives in pool row slots[b] (state, v_first / v_out, elapsed); NULL = row b
     const int* elapsed;  // fp16 state, raw mode: per-sequence step counters [B] that phase the decay dither (NULL = no dither)
 };
 
@@ -84,6 +85,10 @@ __global__ void __launch_bounds__(kStepThreads, 8) wkv7_step_kernel(const StepAr
     const int l16 = tid & 15;
     const int rg = tid >> 4;
     const size_t vbase = (size_t)bh * kN;
+    // with a state pool the recurrent rows of sequence b sit at pool row slots[b]; the step's operands stay batch-ordered
+    const int srow = p.slots ? __ldg(p.slots + bh / p.H) : bh / p.H;
+    const size_t sbh = (size_t)srow * p.H + h;
+    const size_t vsbase = sbh * kN;
     const int hbase = h * kN;
     const int c0 = l16 * 4;
 
@@ -93,7 +98,7 @@ __global__ void __launch_bounds__(kStepThreads, 8) wkv7_step_kernel(const StepAr
     // Launched programmatically: resident under the tail of the preceding kernel.  By default everything waits for it.
     if (!p.prefetch_state) grid_dependency_wait();
     // ---- state tile: issue all 8 row loads first (memory-level parallelism)
-    const size_t sbase = (size_t)bh * kN * kN;
+    const size_t sbase = sbh * kN * kN;
     float4 S[8];
 #pragma unroll
     for (int it = 0; it < 8; ++it) S[it] = StateIO<TS>::load(p.state_in, sbase + (size_t)(it * 8 + rg) * kN + c0);
@@ -143,7 +148,7 @@ __global__ void __launch_bounds__(kStepThreads, 8) wkv7_step_kernel(const StepAr
         }
         if constexpr (sizeof(TS) == 2) {
             if (p.elapsed != nullptr) {  // (decay - 1 + rotator) rounded to fp16, as the reference's FP16-state kernel forms it
-                const int phase = p.elapsed[bh / p.H] + hbase + c0;
+                const int phase = p.elapsed[srow] + hbase + c0;
 #pragma unroll
                 for (int c = 0; c < 4; ++c) w[c] = 1.0f + __half2float(__float2half_rn(w[c] - 1.0f + rotator1(phase + c)));
             }
@@ -167,10 +172,10 @@ __global__ void __launch_bounds__(kStepThreads, 8) wkv7_step_kernel(const StepAr
                     const float gb = p.v_gate_bias ? to_f<T>(reinterpret_cast<const T*>(p.v_gate_bias)[hbase + tid]) : 0.f;
                     gate = round_to<T>(sigmoidf_(round_to<T>(gate + gb)));
                 }
-                const float vf = to_f<T>(reinterpret_cast<const T*>(p.v_first)[vbase + tid]);
+                const float vf = to_f<T>(reinterpret_cast<const T*>(p.v_first)[vsbase + tid]);
                 vv = round_to<T>(vv + (vf - vv) * gate);
             }
-            if (p.v_out) reinterpret_cast<T*>(p.v_out)[vbase + tid] = from_f<T>(vv);
+            if (p.v_out) reinterpret_cast<T*>(p.v_out)[vsbase + tid] = from_f<T>(vv);
         }
         s_v[tid] = vv;
     }
@@ -308,6 +313,34 @@ extern "C" int rwkv7_wkv7_output_prepare_raw(const void* r, const void* w_raw, c
                   "wkv7_output_prepare_raw: null tensor pointer");
     RWKV7_REQUIRE((v_first == nullptr) == (v_gate == nullptr), RWKV7_ERR_INVALID,
                   "wkv7_output_prepare_raw: v_first and v_gate must be given together");
+    if (int e = check_step_common(p, B, H, N)) return e;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    RWKV7_DISPATCH_DTYPE(dtype, T, { return launch_step<T, T, kRaw>(p, B, st); });
+    return RWKV7_OK;
+}
+
+// ---------------------------------------------------------------- state pool
+extern "C" int rwkv7_wkv7_output_prepare_raw_pool(const void* r, const void* w_raw, const void* k_raw, const void* v,
+                                                  const void* a, float* state_pool, const int32_t* slot_ids, const void* g,
+                                                  const void* k_k, const void* k_a, const void* r_k, const void* gn_w,
+                                                  const void* gn_b, void* out, const void* w_bias, const void* a_bias,
+                                                  int a_is_raw, const void* v_first_pool, const void* v_gate,
+                                                  const void* v_gate_bias, int v_gate_is_raw, void* v_out_pool,
+                                                  int state_prefetch, int B, int H, int N, float eps, int dtype, void* stream) {
+    StepArgs p{};
+    p.r = r; p.w = w_raw; p.k = k_raw; p.v = v; p.a = a;
+    p.state_in = state_pool; p.state_out = state_pool; p.out = out; p.H = H;
+    p.g = g; p.r_k = r_k; p.gn_w = gn_w; p.gn_b = gn_b; p.eps = eps;
+    p.k_k = k_k; p.k_a = k_a;
+    p.w_bias = w_bias; p.a_bias = a_bias; p.a_is_raw = a_is_raw;
+    p.v_first = v_first_pool; p.v_gate = v_gate; p.v_gate_bias = v_gate_bias; p.v_gate_is_raw = v_gate_is_raw;
+    p.v_out = v_out_pool;
+    p.prefetch_state = state_prefetch != 0;
+    p.slots = slot_ids;
+    RWKV7_REQUIRE(slot_ids && g && r_k && gn_w && gn_b && k_k && k_a, RWKV7_ERR_INVALID,
+                  "wkv7_output_prepare_raw_pool: null tensor pointer");
+    RWKV7_REQUIRE((v_first_pool == nullptr) == (v_gate == nullptr), RWKV7_ERR_INVALID,
+                  "wkv7_output_prepare_raw_pool: v_first_pool and v_gate must be given together");
     if (int e = check_step_common(p, B, H, N)) return e;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     RWKV7_DISPATCH_DTYPE(dtype, T, { return launch_step<T, T, kRaw>(p, B, st); });

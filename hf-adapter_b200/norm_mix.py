@@ -23,15 +23,27 @@ def _vec(value, hidden, name):
     return value.reshape(hidden).contiguous()
 
 
+def _check_slots(slot_ids, rows, pool, hidden):
+    if not (slot_ids.is_cuda and slot_ids.dtype == torch.int32 and slot_ids.is_contiguous() and int(slot_ids.numel()) == rows):
+        raise ValueError("slot_ids must be a contiguous CUDA int32 tensor with one entry per row")
+    if pool.dim() != 2 or int(pool.shape[1]) != hidden:
+        raise ValueError(f"with slot_ids, previous must be a pool [capacity, {hidden}]")
+
+
 def fused_attn_norm_mix6_decode(x, previous, norm_weight, norm_bias, mix_r, mix_w, mix_k, mix_v, mix_a, mix_g, *,
                                 eps: float = 1e-5, num_warps: int = 4, stack_rkv: bool = False,
-                                stack_wav: bool = False, stack_rkv_wagv: bool = False, force_fallback: bool = False):
+                                stack_wav: bool = False, stack_rkv_wagv: bool = False, force_fallback: bool = False,
+                                slot_ids=None):
     """Layer-normalise ``x``, update ``previous`` in place, and emit the six time mixes (r,w,k,v,a,g).
-    The ``stack_*`` options place outputs in one allocation in the same slot orders as the reference."""
+    The ``stack_*`` options place outputs in one allocation in the same slot orders as the reference.
+    ``slot_ids`` (int32 ``[rows]``, an extension): ``previous`` is a state pool ``[capacity, D]`` and row ``b`` of ``x``
+    uses its row ``slot_ids[b]``."""
     no_fallback(force_fallback, "fused_attn_norm_mix6_decode")
     x2, shape = _rows(x, "x")
     prev2, prev_shape = _rows(previous, "previous")
-    if prev_shape != shape:
+    if slot_ids is not None:
+        _check_slots(slot_ids, int(x2.shape[0]), prev2, int(x2.shape[1]))
+    elif prev_shape != shape:
         raise ValueError("x and previous must have identical shapes")
     hidden = int(x2.shape[1])
     names = ("norm_weight", "norm_bias", "mix_r", "mix_w", "mix_k", "mix_v", "mix_a", "mix_g")
@@ -59,20 +71,28 @@ def fused_attn_norm_mix6_decode(x, previous, norm_weight, norm_bias, mix_r, mix_
         outs = tuple(s[i] for i in range(6))
     mixes_p, _k1 = _lib.ptr_array([p.data_ptr() for p in params[2:]])
     outs_p, _k2 = _lib.ptr_array([o.data_ptr() for o in outs])
-    _lib.check(_lib.lib.rwkv7_attn_norm_mix6(ptr(x_c), ptr(prev2), ptr(params[0]), ptr(params[1]), mixes_p, outs_p,
-                                             rows, hidden, float(eps), dt_code(x_c), stream_ptr(x_c)),
-               "fused_attn_norm_mix6_decode")
+    if slot_ids is not None:
+        _lib.check(_lib.lib.rwkv7_attn_norm_mix6_pool(ptr(x_c), ptr(prev2), ptr(slot_ids), ptr(params[0]), ptr(params[1]),
+                                                      mixes_p, outs_p, rows, hidden, float(eps), dt_code(x_c),
+                                                      stream_ptr(x_c)), "fused_attn_norm_mix6_decode")
+    else:
+        _lib.check(_lib.lib.rwkv7_attn_norm_mix6(ptr(x_c), ptr(prev2), ptr(params[0]), ptr(params[1]), mixes_p, outs_p,
+                                                 rows, hidden, float(eps), dt_code(x_c), stream_ptr(x_c)),
+                   "fused_attn_norm_mix6_decode")
     return tuple(o.reshape(shape) for o in outs)
 
 
 def fused_ffn_add_norm_mix_decode(residual, attn_out, previous, norm_weight, norm_bias, mix, *, eps: float = 1e-5,
-                                  num_warps: int = 4, force_fallback: bool = False):
+                                  num_warps: int = 4, force_fallback: bool = False, slot_ids=None):
     """x = residual + attn_out; h = LN(x); mixed = h + (previous - h) * mix; previous <- h.
-    Returns ``(x, mixed)``."""
+    Returns ``(x, mixed)``.  ``slot_ids``: as in ``fused_attn_norm_mix6_decode``."""
     no_fallback(force_fallback, "fused_ffn_add_norm_mix_decode")
     res2, shape = _rows(residual, "residual")
     attn2, attn_shape = _rows(attn_out, "attn_out")
     prev2, prev_shape = _rows(previous, "previous")
+    if slot_ids is not None:
+        _check_slots(slot_ids, int(res2.shape[0]), prev2, int(res2.shape[1]))
+        prev_shape = shape
     if attn_shape != shape or prev_shape != shape:
         raise ValueError("residual, attn_out, and previous must have identical shapes")
     hidden = int(res2.shape[1])
@@ -83,9 +103,15 @@ def fused_ffn_add_norm_mix_decode(residual, attn_out, previous, norm_weight, nor
         raise ValueError("previous must be contiguous (it is updated in place)")
     res_c, attn_c = res2.contiguous(), attn2.contiguous()
     res_out, mixed = torch.empty_like(res_c), torch.empty_like(res_c)
-    _lib.check(_lib.lib.rwkv7_ffn_add_norm_mix(ptr(res_c), ptr(attn_c), ptr(prev2), ptr(w), ptr(b), ptr(m),
-                                               ptr(res_out), ptr(mixed), int(res_c.shape[0]), hidden, float(eps),
-                                               dt_code(res_c), stream_ptr(res_c)), "fused_ffn_add_norm_mix_decode")
+    if slot_ids is not None:
+        _lib.check(_lib.lib.rwkv7_ffn_add_norm_mix_pool(ptr(res_c), ptr(attn_c), ptr(prev2), ptr(slot_ids), ptr(w), ptr(b),
+                                                        ptr(m), ptr(res_out), ptr(mixed), int(res_c.shape[0]), hidden,
+                                                        float(eps), dt_code(res_c), stream_ptr(res_c)),
+                   "fused_ffn_add_norm_mix_decode")
+    else:
+        _lib.check(_lib.lib.rwkv7_ffn_add_norm_mix(ptr(res_c), ptr(attn_c), ptr(prev2), ptr(w), ptr(b), ptr(m),
+                                                   ptr(res_out), ptr(mixed), int(res_c.shape[0]), hidden, float(eps),
+                                                   dt_code(res_c), stream_ptr(res_c)), "fused_ffn_add_norm_mix_decode")
     return res_out.reshape(shape), mixed.reshape(shape)
 
 

@@ -168,7 +168,10 @@ class StepContext:
     GPU with one side stream per device."""
 
     def __init__(self, side_stream=None, all_reduce=None, tp_world: int = 1, tp_rank: int = 0, lane: int = 0,
-                 stream_base: int = 0):
+                 stream_base: int = 0, slot_ids=None):
+        # slot_ids (int32 [B] on the device): the recurrent buffers handed to the layer step are slot pools
+        # ([capacity, ...]) and batch row b lives in pool row slot_ids[b]
+        self.slot_ids = slot_ids
         self._side_stream = side_stream
         self._all_reduce = all_reduce
         self.tp_world, self.tp_rank, self.lane, self.stream_base = int(tp_world), int(tp_rank), int(lane), int(stream_base)
@@ -196,7 +199,7 @@ def block_ip_batched(x, state, xpa, xpf, v_first, p, sparse_ffn_out=None, fp16_e
 
     ``x [B,D]`` residual stream in, new residual stream out; ``state [B,H,N,N]`` (fp32, or fp16 with the
     ``fp16_elapsed`` int32 ``[B]`` phase counters of the FP16-state lane), ``xpa``/``xpf [B,D]`` and ``v_first [B,A]``
-    are overwritten.  Every launch is capturable in a CUDA graph.  ``sparse_ffn_out`` and ``route_observer`` belong to
+    are overwritten (with ``context.slot_ids`` they are slot pools ``[capacity, ...]`` and only the rows named there change).  Every launch is capturable in a CUDA graph.  ``sparse_ffn_out`` and ``route_observer`` belong to
     the reference's sparse-FFN experiment and must be None."""
     if sparse_ffn_out is not None or route_observer is not None:
         raise NotImplementedError("the sparse-FFN route of the reference is not part of this library")
@@ -210,7 +213,9 @@ def block_ip_batched(x, state, xpa, xpf, v_first, p, sparse_ffn_out=None, fp16_e
     ctx = context or _DEFAULT_CONTEXT
     if has_pre:
         x = _nm.layer_norm(x, pre_w, pre_b)
-    xr, xw, xk, xv, xa, xg = _nm.fused_attn_norm_mix6_decode(x, xpa, an_w, an_b, x_r, x_w, x_k, x_v, x_a, x_g)
+    slots = ctx.slot_ids
+    xr, xw, xk, xv, xa, xg = _nm.fused_attn_norm_mix6_decode(x, xpa, an_w, an_b, x_r, x_w, x_k, x_v, x_a, x_g,
+                                                             slot_ids=slots)
     # The LoRA chain does not depend on r/k/v: it runs on a side stream (a parallel branch of the decode graph once
     # captured) and joins before the recurrence.
     main = torch.cuda.current_stream(x.device)
@@ -255,9 +260,9 @@ def block_ip_batched(x, state, xpa, xpf, v_first, p, sparse_ffn_out=None, fp16_e
     out, _ = _rec.fused_recurrent_output_prepare_raw(
         r, w_raw, k, v, a_pre, state, g, k_k, k_a, r_k, gn_w, gn_b, eps=float(eps), new_state=state, w_bias=w0, a_bias=a0,
         a_is_raw=True, state_prefetch=True, elapsed=elapsed,
-        advance_elapsed=bool(fp16_advance_elapsed) and elapsed is not None, **extra)
+        advance_elapsed=bool(fp16_advance_elapsed) and elapsed is not None, slot_ids=slots, **extra)
     attn = ctx.all_reduce(apply_linear(Ow, out))
-    x, mixed = _nm.fused_ffn_add_norm_mix_decode(x, attn, xpf, fn_w, fn_b, fx_k)
+    x, mixed = _nm.fused_ffn_add_norm_mix_decode(x, attn, xpf, fn_w, fn_b, fx_k, slot_ids=slots)
     hidden = apply_linear(fK, mixed, relu2=True)
     if ctx.tp_world > 1:
         # the residual rides in rank 0's partial sum (the projection's add epilogue): no extra add kernel

@@ -121,7 +121,8 @@ def fused_recurrent_output_prepare_raw(r, w_raw, k_raw, v, a, state, g, k_k, k_a
                                        force_fallback: bool = False, out=None, new_state=None, w_bias=None,
                                        a_bias=None, a_is_raw: bool = False, v_first=None, v_gate=None,
                                        v_gate_bias=None, v_gate_is_raw: bool = False, v_out=None,
-                                       state_prefetch: bool = False, elapsed=None, advance_elapsed: bool = False):
+                                       state_prefetch: bool = False, elapsed=None, advance_elapsed: bool = False,
+                                       slot_ids=None):
     """Decode recurrence / output prep straight from raw w, k and sigmoid(a).
 
     The keyword arguments after ``force_fallback`` are extensions of this package (the reference
@@ -131,8 +132,14 @@ def fused_recurrent_output_prepare_raw(r, w_raw, k_raw, v, a, state, g, k_k, k_a
     kernel that precedes it in the stream: only for call sequences in which that kernel never writes ``state``
     (a decode step, where a projection precedes the recurrence).  A float16 ``state`` selects the FP16-state lane
     (fp32 arithmetic, state rounded on the store); ``elapsed`` (int32 ``[B]``) adds the decay dither of the reference's
-    native_wkv_fp16 extension and ``advance_elapsed`` increments it after the step."""
+    native_wkv_fp16 extension and ``advance_elapsed`` increments it after the step.  ``slot_ids`` (int32 ``[B]``):
+    ``state`` is a pool ``[capacity,H,N,N]`` (fp32) updated in place at rows ``slot_ids[b]``, and ``v_first`` / ``v_out``
+    are pools ``[capacity, H*N]`` indexed the same way; the returned state is the pool."""
     no_fallback(force_fallback, "fused_recurrent_output_prepare_raw")
+    if slot_ids is not None:
+        return _output_prepare_raw_pool(r, w_raw, k_raw, v, a, state, g, k_k, k_a, r_k, group_norm_weight, group_norm_bias,
+                                        float(eps), out, w_bias, a_bias, a_is_raw, v_first, v_gate, v_gate_bias,
+                                        v_gate_is_raw, v_out, state_prefetch, slot_ids)
     B, H, N = _state_shape(state, allow_f16=True)
     if elapsed is not None:
         if state.dtype != torch.float16:
@@ -172,6 +179,39 @@ def fused_recurrent_output_prepare_raw(r, w_raw, k_raw, v, a, state, g, k_k, k_a
         _lib.check(_lib.lib.rwkv7_wkv7_output_prepare_raw_f16state(*head, ptr(elapsed), int(bool(advance_elapsed)), *tail),
                    "fused_recurrent_output_prepare_raw", kernels=2 if advance_elapsed else 1)
     return (out.reshape(B, hidden) if flat else out.reshape(B, H, N)), new_state
+
+
+def _output_prepare_raw_pool(r, w_raw, k_raw, v, a, pool, g, k_k, k_a, r_k, gn_w, gn_b, eps, out, w_bias, a_bias, a_is_raw,
+                             v_first, v_gate, v_gate_bias, v_gate_is_raw, v_out, state_prefetch, slot_ids):
+    _, H, N = _state_shape(pool, allow_f16=False)
+    B = int(slot_ids.numel())
+    if not (slot_ids.is_cuda and slot_ids.dtype == torch.int32 and slot_ids.is_contiguous()):
+        raise ValueError("slot_ids must be a contiguous CUDA int32 tensor")
+    if not pool.is_contiguous():
+        raise ValueError("the state pool must be contiguous (it is updated in place)")
+    r_, flat = _as_bhn(r, B, H, N, "r")
+    w_, k_, v_, a_, g_ = (_as_bhn(t, B, H, N, n)[0] for t, n in
+                          ((w_raw, "w_raw"), (k_raw, "k_raw"), (v, "v"), (a, "a"), (g, "g")))
+    hidden = H * N
+    for value, name in ((k_k, "k_k"), (k_a, "k_a"), (r_k, "r_k"), (gn_w, "group_norm_weight"), (gn_b, "group_norm_bias")):
+        if int(value.numel()) != hidden:
+            raise ValueError(f"{name} must contain {hidden} values")
+    for value, name in ((v_first, "v_first"), (v_out, "v_out")):
+        if value is not None and (value.dim() != 2 or int(value.shape[1]) != hidden or int(value.shape[0]) != int(pool.shape[0])
+                                  or not value.is_contiguous()):
+            raise ValueError(f"with slot_ids, {name} must be a contiguous pool [capacity, {hidden}]")
+    params = [t.contiguous() for t in (k_k, k_a, r_k, gn_w, gn_b)]
+    opt = [None if t is None else t.contiguous() for t in (w_bias, a_bias, v_gate, v_gate_bias)]
+    require_cuda(r_, w_, k_, v_, a_, g_, pool, *params, *opt, v_first, v_out, what="fused_recurrent_output_prepare_raw")
+    same_dtype(r_, w_, k_, v_, a_, g_, *params, *opt, v_first, v_out, what="fused_recurrent_output_prepare_raw")
+    if out is None:
+        out = torch.empty_like(r_)
+    _lib.check(_lib.lib.rwkv7_wkv7_output_prepare_raw_pool(
+        ptr(r_), ptr(w_), ptr(k_), ptr(v_), ptr(a_), ptr(pool), ptr(slot_ids), ptr(g_), ptr(params[0]), ptr(params[1]),
+        ptr(params[2]), ptr(params[3]), ptr(params[4]), ptr(out), ptr(opt[0]), ptr(opt[1]), int(bool(a_is_raw)),
+        ptr(v_first), ptr(opt[2]), ptr(opt[3]), int(bool(v_gate_is_raw)), ptr(v_out), int(bool(state_prefetch)), B, H, N,
+        eps, dt_code(r_), stream_ptr(r_)), "fused_recurrent_output_prepare_raw")
+    return (out.reshape(B, hidden) if flat else out.reshape(B, H, N)), pool
 
 
 def _scan(name, r, w, k, v, kk, a, state, w_mode, prep=None, eps=0.0, chunk=0, ab_mode=False, w0=None, elapsed=None,

@@ -170,6 +170,31 @@ int rwkv7_ffn_add_norm_mix(const void* residual, const void* attn_out, void* pre
                            const void* norm_b, const void* mix, void* residual_out, void* mixed,
                            int rows, int D, float eps, int dtype, void* stream);
 
+/* ------------------------------------------------------------------ serving state pool
+ * The three decode operators that touch per-sequence state, reading and writing it in place inside a slot pool
+ * (docs/integrations/RWKV7_STATE_CACHE_ABI.md of the reference: layer-major pools indexed by slot id, "production
+ * kernels may consume pool pointers and slot_ids directly, removing the gather/scatter copies").  slot_ids: int32 [B]
+ * on the device; batch row b uses pool row slot_ids[b].  Rows must be distinct among the live sequences of a call;
+ * padding rows of a fixed-size graph batch all point at one scratch row that no sequence owns.  Everything else
+ * (activations, outputs) stays batch-ordered.
+ *   prev_pool     [capacity, D]        token-shift state of one layer (xpa or xpf)
+ *   state_pool    [capacity, H,64,64]  fp32 recurrent state of one layer, updated in place
+ *   v_first_pool / v_out_pool [capacity, H*64]  (layer 0 writes v_out_pool, later layers read v_first_pool) */
+int rwkv7_attn_norm_mix6_pool(const void* x, void* prev_pool, const int32_t* slot_ids, const void* norm_w,
+                              const void* norm_b, const void* const mixes[6], void* const outs[6],
+                              int rows, int D, float eps, int dtype, void* stream);
+int rwkv7_ffn_add_norm_mix_pool(const void* residual, const void* attn_out, void* prev_pool, const int32_t* slot_ids,
+                                const void* norm_w, const void* norm_b, const void* mix, void* residual_out,
+                                void* mixed, int rows, int D, float eps, int dtype, void* stream);
+int rwkv7_wkv7_output_prepare_raw_pool(const void* r, const void* w_raw, const void* k_raw, const void* v, const void* a,
+                                       float* state_pool, const int32_t* slot_ids, const void* g,
+                                       const void* k_k, const void* k_a, const void* r_k,
+                                       const void* gn_w, const void* gn_b, void* out,
+                                       const void* w_bias, const void* a_bias, int a_is_raw,
+                                       const void* v_first_pool, const void* v_gate, const void* v_gate_bias,
+                                       int v_gate_is_raw, void* v_out_pool, int state_prefetch,
+                                       int B, int H, int N, float eps, int dtype, void* stream);
+
 /* Plain LayerNorm (pre_norm of layer 0 and the final norm; rwkv7_hf/native.py:404,450). */
 int rwkv7_layer_norm(const void* x, const void* norm_w, const void* norm_b, void* out,
                      int rows, int D, float eps, int dtype, void* stream);
