@@ -6,7 +6,7 @@ from .cache import NativeRWKV7Cache, NativeRWKV7LegacyCache
 from .gemm import dense_linear
 from .install import install, uninstall
 from .lora import dense_small, fused_wa_lora, fused_wag_lora, fused_wavg_lora
-from .model import DecodeGraph, NativeRWKV7Config, RWKV7ForCausalLM, sample_next_token
+from .model import DecodeGraph, NativeRWKV7Config, PrefillGraph, RWKV7ForCausalLM, sample_next_token
 from .norm_mix import (fused_attn_norm_mix6_decode, fused_attn_sequence_shift_mix, fused_attn_shift_mix,
                        fused_ffn_add_norm_mix_decode, fused_ffn_sequence_shift_mix, layer_norm)
 from .packing import (block_ip_batched, extract_graph_packs, graph_linear_is_dense, graph_linear_operand,

@@ -577,6 +577,14 @@ class RWKV7ForCausalLM(nn.Module):
                 break
         return torch.cat([input_ids] + toks, dim=1)
 
+    def rwkv7_speculative_generate(self, input_ids, draft_model, max_new_tokens: int = 32, draft_tokens: int = 4,
+                                   eos_token_id=None, return_stats: bool = False, logits_to_keep: int = 1, **forward_kwargs):
+        """Greedy speculative decoding with ``draft_model`` proposing (rwkv7_hf/model_speculative.py:10-231); the result
+        equals this model's own greedy continuation.  See ``speculative.rwkv7_speculative_generate``."""
+        from .speculative import rwkv7_speculative_generate
+        return rwkv7_speculative_generate(self, input_ids, draft_model, max_new_tokens, draft_tokens, eos_token_id,
+                                          return_stats, logits_to_keep, **forward_kwargs)
+
     # ------------------------------------------------------------------ CUDA graph
     def _decode_graph(self, batch: int, greedy: bool = False) -> "DecodeGraph":
         key = (batch, True) if greedy else batch
@@ -646,3 +654,53 @@ class DecodeGraph:
         self.ids.copy_(ids)
         self.graph.replay()
         return self.logits.clone() if copy_logits else self.logits
+
+
+class PrefillGraph:
+    """Fixed-shape CUDA graph of the layer-wise prefill of one prompt chunk ``[batch, tokens]`` (the role of the
+    reference's prefill graph runner, rwkv7_hf/model_prefill_graph.py): for short chunks and small batches the
+    hundred-odd launches per layer cost more host time than device time, and a replay removes it.
+
+    The graph owns static ids and a static cache.  ``replay`` copies the caller's cache in, replays, and copies the
+    advanced state back (a few MB against a whole chunk of work), so any cache of the right batch size can be served;
+    consecutive chunks of one prompt pass the same cache object, which skips the copy-in."""
+
+    def __init__(self, model: RWKV7ForCausalLM, batch: int, tokens: int, *, logits_to_keep: int = 1, scan_chunk: int = 0):
+        self.model, self.batch, self.tokens = model, int(batch), int(tokens)
+        self.keep = self.tokens if logits_to_keep in (0, None) else min(int(logits_to_keep), self.tokens)
+        dev = model.device
+        self.ids = torch.zeros((self.batch, self.tokens), device=dev, dtype=torch.long)
+        self.cache = model.new_cache(self.batch)
+        self._last = None  # weak reference to the cache whose state the static buffers currently hold
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                model._prefill(self.ids, self.cache, keep=self.keep, scan_chunk=scan_chunk)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        self.cache.reset()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.logits = model._prefill(self.ids, self.cache, keep=self.keep, scan_chunk=scan_chunk)
+        self.cache.reset()
+
+    @torch.no_grad()
+    def replay(self, input_ids, cache: NativeRWKV7Cache | None = None):
+        """Advance ``cache`` (a fresh one when None) over ``input_ids [batch, tokens]``; returns ``(logits, cache)``."""
+        if tuple(input_ids.shape) != (self.batch, self.tokens):
+            raise ValueError(f"this graph was captured for input_ids [{self.batch}, {self.tokens}]")
+        if cache is None:
+            cache = self.model.new_cache(self.batch)
+        mine, theirs = self.cache._tensors(), cache._tensors()
+        if len(mine) != len(theirs) or any(a.shape != b.shape or a.dtype != b.dtype for a, b in zip(mine, theirs)):
+            raise ValueError("the cache does not match the captured batch size or state dtype")
+        if self._last is None or self._last() is not cache or cache._seen_tokens != self._seen_after:
+            for dst, src in zip(mine, theirs):
+                dst.copy_(src)
+        self.ids.copy_(input_ids)
+        self.graph.replay()
+        for dst, src in zip(theirs, mine):
+            dst.copy_(src)
+        cache._seen_tokens += self.tokens
+        self._last, self._seen_after = weakref.ref(cache), cache._seen_tokens
+        return self.logits.clone(), cache

@@ -144,3 +144,61 @@ def test_pack_step_runs_a_dense_and_a_quantised_model():
         assert torch.equal(v_first, cache[3])
     with pytest.raises(ValueError, match="41 slots"):
         hb.block_ip_batched(x, state[0], xpa[0], xpf[0], v_first, packs[0][:40])
+
+
+def test_speculative_generate_equals_target_greedy():
+    """Whatever the draft proposes, the result is the target's greedy continuation: a draft that always agrees (the
+    target itself), one that rarely does (other random weights), block sizes that do and do not divide the length."""
+    g = golden("model_tiny.npz")
+    target = load_tiny(g)
+    ids = cu(g["ids"])[:1]
+    want = target.generate(ids, max_new_tokens=11)
+    same = target.rwkv7_speculative_generate(ids, target, max_new_tokens=11, draft_tokens=4, return_stats=True)
+    assert torch.equal(same["sequences"], want)
+    st = same["stats"]
+    assert st["acceptance_rate"] == 1.0 and st["corrected_tokens"] == 0 and st["generated_tokens"] == 11 and st["resyncs"] == 0
+    assert st["target_forward_calls"] == 1 + 3  # prompt + three verified blocks (4 + 4 + 3)
+    torch.manual_seed(9)
+    other = hb.RWKV7ForCausalLM(tiny_cfg())
+    with torch.no_grad():
+        for p in other.parameters():
+            p.copy_(0.3 * torch.randn_like(p))
+    other = other.cuda().eval()
+    for block in (1, 3, 5):
+        res = target.rwkv7_speculative_generate(ids, other, max_new_tokens=11, draft_tokens=block, return_stats=True)
+        assert torch.equal(res["sequences"], want), block
+        st = res["stats"]
+        assert st["accepted_tokens"] + st["corrected_tokens"] == 11 and st["proposed_tokens"] >= st["accepted_tokens"]
+        assert st["resync_tokens"] <= st["resyncs"] * block
+    eos = int(want[0, ids.shape[1] + 2])
+    stopped = target.rwkv7_speculative_generate(ids, other, max_new_tokens=11, draft_tokens=3, eos_token_id=eos)
+    first = int((want[0, ids.shape[1]:] == eos).nonzero()[0])
+    assert torch.equal(stopped, want[:, :ids.shape[1] + first + 1])
+    with pytest.raises(ValueError):
+        target.rwkv7_speculative_generate(cu(g["ids"]), other)  # batch of two
+    assert torch.equal(target.rwkv7_speculative_generate(ids, other, max_new_tokens=0), ids)
+
+
+def test_prefill_graph_replays_equal_eager_prefill():
+    g = golden("model_tiny.npz")
+    model = load_tiny(g)
+    torch.manual_seed(4)
+    ids = torch.randint(0, 256, (2, 24), device="cuda")
+    want_logits, want_cache = model.rwkv7_prefill_chunks(ids, None, chunk_size=8)
+    runner = hb.PrefillGraph(model, 2, 8)
+    cache = None
+    for t0 in range(0, 24, 8):
+        logits, cache = runner.replay(ids[:, t0:t0 + 8], cache)
+    torch.testing.assert_close(logits, want_logits, rtol=1e-5, atol=1e-5)
+    for a, b in zip(cache._tensors(), want_cache._tensors()):
+        torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6)
+    assert cache.get_seq_length() == 24
+    # another cache through the same graph, interleaved with the first
+    other_logits, other = runner.replay(ids[:, :8].flip(0), None)
+    more, cache = runner.replay(ids[:, :8], cache)
+    ref_logits, ref = model.rwkv7_prefill_native(ids[:, :8].flip(0), None)
+    torch.testing.assert_close(other_logits, ref_logits, rtol=1e-5, atol=1e-5)
+    ref_more, want_cache = model.rwkv7_prefill_native(ids[:, :8], want_cache)
+    torch.testing.assert_close(more, ref_more, rtol=1e-5, atol=1e-5)
+    with pytest.raises(ValueError):
+        runner.replay(ids[:, :4], None)
