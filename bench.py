@@ -113,7 +113,7 @@ def shape_config(shape, quant, batch, layers=0):
     L, D, H, Fd, V = SHAPES[shape]
     fmt = {"mm4": "mm4-g128", "w8": "int8-per-channel", "a8w8": "a8w8 (int8 activations x int8 weights)"}[quant]
     return {"workload": f"rwkv7-{shape}-shape {fmt} decode, batch {batch}, "
-                        "fp16 head, cache resident",
+                        "fp16 head ending in the greedy token (arg-max fused in the head GEMM), cache resident",
             "layers": layers or L, "d_model": D, "heads": H, "ffn": Fd, "vocab": V, "lora_ranks": RANKS}
 
 
@@ -257,6 +257,7 @@ def main():
     ap.add_argument("--no-scan", action="store_true")
     ap.add_argument("--no-ops", action="store_true", help="skip the isolated projection-operator table")
     ap.add_argument("--no-b256", action="store_true", help="skip the batch-256 decode measurement")
+    ap.add_argument("--no-pool", action="store_true", help="skip the state-pool decode measurement")
     ap.add_argument("--no-side", action="store_true", help="N > 1: skip the side measurements (replicas, strong scaling)")
     args = ap.parse_args()
     steps, warmup = max(1, args.steps), max(3, args.warmup)
@@ -321,7 +322,7 @@ def main():
         _lib.LAUNCHES = 0
         model.rwkv7_forward_token(ids_host[0].to(dev), cache, use_graph=False)
         launches = _lib.LAUNCHES
-        greedy = model.tp_world > 1  # sharded head: the step ends in the arg-max token, no rank gathers the logits
+        greedy = True  # the step ends in the greedy token: arg-max in the head GEMM's epilogue, the logits are never stored
         graph = model._decode_graph(B, greedy)
         graph.bind(cache)
         ids_dev = ids_host.to(dev)
@@ -596,6 +597,37 @@ def main():
             b256 = {"error": f"{type(exc).__name__}: {exc}"[:300]}
         torch.cuda.empty_cache()
 
+    # ---------------- serving state pool: the same decode step with every sequence's state addressed through slot ids
+    pool_stats = None
+    if not args.no_pool and world == 1 and args.state == "fp32":
+        try:
+            cap = B + B // 2
+            pool = hb.RWKV7StatePool(model, cap)
+            slots_all, _ = pool.allocate(range(cap))
+            perm = torch.randperm(cap, generator=gen).tolist()
+            sched = [slots_all[i] for i in perm[:B]]  # a scattered, unordered subset of the live slots
+            toks = torch.randint(0, V, (B,), generator=gen).to(dev)
+            for _ in range(3):
+                pool.decode(toks, sched, use_graph=True, greedy=True)
+            gph = pool._graphs[(1 << max(0, (B - 1).bit_length()), True)]
+            slot_vec = pool._slot_vector(sched, gph.rows)
+            torch.cuda.synchronize()
+            q0, q1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            nrep = max(3, min(steps, 20))
+            q0.record()
+            for _ in range(nrep):
+                gph.replay(toks, slot_vec)
+            q1.record()
+            torch.cuda.synchronize()
+            pms = q0.elapsed_time(q1) / nrep
+            pool_stats = {"value": B / (pms * 1e-3), "unit": "tok/s", "ms_per_step": pms, "capacity": cap, "scheduled": B,
+                          "bytes_per_slot": pool.bytes_per_slot,
+                          "note": "graph replay over the pools with a permuted slot vector; no gather / scatter of state"}
+            del pool, gph
+        except Exception as exc:
+            pool_stats = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+        torch.cuda.empty_cache()
+
     # ---------------- prefill tok/s (bounded sample of the 8192-token prompts: the state carries over chunks)
     prefill = None
     if not args.no_prefill and world == 1:
@@ -683,6 +715,29 @@ def main():
             ops["a8w8_gemm"][f"m{Mg}_k{K}_n{Nout}"] = {"us": us, "tops": tops, "frac_of_2x_bf16_burst": tops / (2 * tc_burst)}
             del qa, qws
         torch.cuda.empty_cache()
+        # prefill-sized projections (64 sequences x 512 tokens) on the persistent CTA-pair GEMM: raw int8 accumulators,
+        # the whole A8W8 linear (row quantiser + GEMM with the dequantisation in its epilogue), and the fp16 GEMM with
+        # the FFN's relu^2 fused; the library GEMM on the same fp16 operands stands beside as a yardstick
+        ops["prefill_gemm"] = {}
+        for (Mg, K, Nout) in ((32768, 4096, 4096), (32768, 4096, 16384), (32768, 16384, 4096)):
+            xg = torch.randn(Mg, K, device=dev, dtype=torch.float16)
+            wg = (torch.randn(Nout, K, device=dev, dtype=torch.float16) / 64)
+            qt, sc = hb.quantize_weight_per_channel_int8(wg)
+            qrow = qt.t().contiguous()
+            qa, _sa = hb.dynamic_a8_quant(xg)
+            wsp = hb.quant.a8w8_workspace(Mg, K, Nout, dev)
+            fl = 2.0 * Mg * K * Nout
+            ent = {}
+            for nm, fn, peak in (("int8_raw", lambda: hb.int8_mm(qa, qrow), 2 * tc_burst),
+                                 ("a8w8_linear", lambda: hb.a8w8_linear(xg, qt, sc, workspace=wsp), 2 * tc_burst),
+                                 ("fp16", lambda: hb.dense_linear(xg, wg), tc_burst),
+                                 ("fp16_relu2", lambda: hb.dense_linear(xg, wg, relu2=True), tc_burst),
+                                 ("library_fp16", lambda: torch.nn.functional.linear(xg, wg), tc_burst)):
+                us = time_graph(fn, 1, reps=5)
+                ent[nm] = {"us": us, "tflops": fl / us / 1e6, "frac_of_peak": fl / us / 1e6 / peak}
+            ops["prefill_gemm"][f"m{Mg}_k{K}_n{Nout}"] = ent
+            del xg, wg, qt, qrow, qa, wsp
+            torch.cuda.empty_cache()
 
     cpu_baseline = None
     if not args.no_cpu_baseline and world == 1:
@@ -699,13 +754,13 @@ def main():
                        cuda_graph=True),
         "e2e": {"value": global_batch / (e2e_ms * 1e-3), "unit": "tok/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": global_batch * 8, "d2h_bytes_per_step": global_batch * 8,
-                "api": "RWKV7ForCausalLM.rwkv7_forward_token + argmax"},
+                "api": "RWKV7ForCausalLM.rwkv7_forward_token(return_tokens=True)"},
         # kernels of this library launched in the timed region, summed over the GPUs
         "gpu_launches": launches_per_step * steps * world,
         "gpu_launches_per_step": launches_per_step,
         "tp_parity": tp_parity, "replicas" if use_tp else "head_sharded_tp": replicas, "strong_scaling": strong,
         "clocks": clocks, "roofline": roofline, "roofline_secondary": roofline_wkv, "cpu_baseline": cpu_baseline,
-        "decode_b256": b256, "prefill": prefill, "wkv_scan": scan, "ops": ops,
+        "decode_b256": b256, "state_pool": pool_stats, "prefill": prefill, "wkv_scan": scan, "ops": ops,
         **extra,
     }
     if args.layers:

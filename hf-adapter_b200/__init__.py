@@ -3,7 +3,7 @@ contract of rwkv-rs/hf-adapter (package ``rwkv7_hf``).  Importing this package l
 library; there is no CPU or PyTorch fallback."""
 from . import _lib  # noqa: F401  (fails loudly when the library is missing)
 from .cache import NativeRWKV7Cache, NativeRWKV7LegacyCache
-from .gemm import dense_linear
+from .gemm import dense_argmax, dense_linear
 from .install import install, uninstall
 from .lora import dense_small, fused_wa_lora, fused_wag_lora, fused_wavg_lora
 from .model import DecodeGraph, NativeRWKV7Config, PrefillGraph, RWKV7ForCausalLM, sample_next_token

@@ -63,6 +63,8 @@ SIGNATURES = {
     "rwkv7_a8_quant": (I, [P, P, P, I, I, I, P]),
     "rwkv7_i8_gemm": (I, [P, P, P, I, I, I, P]),
     "rwkv7_gemm": (I, [P, P, P, P, P, I, I, I, I, I, P]),
+    "rwkv7_gemm_argmax_workspace_bytes": (L, [I, I]),
+    "rwkv7_gemm_argmax": (I, [P, P, P, L, P, P, I, I, I, I, P]),
     "rwkv7_a8w8_dequant": (I, [P] * 6 + [I, I, I, P]),
     "rwkv7_a8w8_workspace_bytes": (L, [I, I, I]),
     "rwkv7_a8w8_linear": (I, [P] * 7 + [L, I, I, I, I, P]),

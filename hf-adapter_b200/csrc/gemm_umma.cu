@@ -23,7 +23,7 @@ constexpr int TMEM_COLS = 512;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 256 + 1024;
 constexpr int GROUP_M = 16;
 enum { KIND_F16 = 0, KIND_BF16 = 1, KIND_I8 = 2 };
-enum { EPI_STORE = 0, EPI_RELU2 = 1, EPI_DEQUANT = 2, EPI_RAW_I32 = 3 };
+enum { EPI_STORE = 0, EPI_RELU2 = 1, EPI_DEQUANT = 2, EPI_RAW_I32 = 3, EPI_ARGMAX = 4 };
 }  // namespace gm
 
 struct GemmArgs {
@@ -37,6 +37,9 @@ struct GemmArgs {
     int epi;
     int vec;  // 1: N % 16 == 0 and every pointer the epilogue touches is 16-byte aligned
     unsigned int* error;
+    // arg-max epilogue: per (row, column tile) the best value rounded to the output type and its column, [M, tiles_n] each
+    float* part_val;
+    int* part_idx;
 };
 
 // tile -> (row tile, column tile): bands of GROUP_M row tiles, row tile fastest inside a band
@@ -125,6 +128,21 @@ __device__ __forceinline__ void epilogue_chunk(const GemmArgs& p, const uint32_t
                 x = __fadd_rn(x, to_f<TOut>(res[off + e]));
             }
             dst[e] = from_f<TOut>(x);
+        }
+    }
+}
+
+// Arg-max epilogue: nothing of the product is stored.  A thread owns one row of the tile and folds its 256 columns
+// into (best value, lowest column holding it); values are first rounded to the output type, so the winner is the one
+// torch.argmax picks on the stored logits.
+template <typename TOut>
+__device__ __forceinline__ void argmax_chunk(const GemmArgs& p, const uint32_t (&v)[16], int col, float& best, int& best_col) {
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+        const float x = round_to<TOut>(__uint_as_float(v[e]));
+        if (col + e < p.N && x > best) {
+            best = x;
+            best_col = col + e;
         }
     }
 }
@@ -238,12 +256,19 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             tc_fence_after();
             const int row = tm * BM + q * 32 + lane;
             const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(as * BN);
+            float best = -INFINITY;
+            int best_col = tn * BN;
 #pragma unroll 1
             for (int c = 0; c < BN / 16; ++c) {
                 uint32_t v[16];
                 tmem_ld16(lane_addr + c * 16, v);
                 tc_wait_ld();
-                epilogue_chunk<KIND, TOut>(p, v, row, tn * BN + c * 16);
+                if (KIND != KIND_I8 && p.epi == EPI_ARGMAX) argmax_chunk<TOut>(p, v, tn * BN + c * 16, best, best_col);
+                else epilogue_chunk<KIND, TOut>(p, v, row, tn * BN + c * 16);
+            }
+            if (KIND != KIND_I8 && p.epi == EPI_ARGMAX && row < p.M) {
+                p.part_val[(size_t)row * p.tiles_n + tn] = best;
+                p.part_idx[(size_t)row * p.tiles_n + tn] = best_col;
             }
             tc_fence_before();
             __syncwarp();
@@ -259,14 +284,16 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 
 // ---------------------------------------------------------------- CTA-pair variant (tcgen05 cta_group::2)
 // Two CTAs of a cluster share one 256 x 256 output tile.  Each stages its own 128 rows of A and 128 of the 256 rows
-// of B (32 KB per stage instead of 48 KB, so the shared-memory fill per MMA cycle drops by a third and six stages
-// fit); the even CTA issues MMAs of M = 256 that read both CTAs' shared memory and write each CTA's 128 result rows
-// into that CTA's tensor memory.  Barrier protocol: both producers' TMA loads complete on the LEADER's full[s]
+// of B (32 KB per 128 bytes of K instead of 48 KB, so the shared-memory fill per MMA cycle drops by a third); the
+// even CTA issues MMAs of M = 256 that read both CTAs' shared memory and write each CTA's 128 result rows into that
+// CTA's tensor memory.  Barrier protocol: both producers' TMA loads complete on the LEADER's full[s]
 // (armed by the leader with the byte count of both); the leader's commits arrive on empty[s] / acc_full[a] in BOTH
 // CTAs; all eight epilogue warps arrive on the leader's acc_empty[a].  No TMA multicast.
 namespace gp {
-constexpr int BM = 128, PAIR_M = 256, BN = 256, HALF_N = 128, BKB = 128, STAGES = 6, THREADS = 192;
-constexpr int A_BYTES = BM * BKB, B_BYTES = HALF_N * BKB, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int BM = 128, PAIR_M = 256, BN = 256, HALF_N = 128, BKB = 128, KBOX = 2, STAGES = 3, THREADS = 192;
+// a stage holds KBOX consecutive 128-byte K slices of both operands: [A slice 0][A slice 1][B slice 0][B slice 1];
+// the issuer then waits and commits once per 2 * 4 MMAs, which halves the issue bubble between stages
+constexpr int A_BYTES = BM * BKB, B_BYTES = HALF_N * BKB, STAGE_BYTES = KBOX * (A_BYTES + B_BYTES);
 constexpr int TMEM_COLS = 512;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 256 + 1024;
 }  // namespace gp
@@ -291,7 +318,7 @@ gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
     const uint32_t rank = cluster_ctarank();
     const bool leader = rank == 0;
     const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
-    const int nk = (p.K + BK - 1) / BK;
+    const int nk = (p.K + KBOX * BK - 1) / (KBOX * BK);  // stages per tile (a ragged last stage is zero-filled by TMA)
     const int ntiles = p.tiles_m * p.tiles_n;  // tiles of 256 x 256
 
     if (tid == 0) {
@@ -334,8 +361,11 @@ gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                     if (leader) mbar_expect_tx(&full[s], 2 * STAGE_BYTES);
                     const uint32_t bar = mapa_shared(smem_u32(&full[s]), 0);
                     unsigned char* st = sm + s * STAGE_BYTES;
-                    tma_load_2d_pair(st, &tm_a, bar, kb * BK, row_a);
-                    tma_load_2d_pair(st + A_BYTES, &tm_b, bar, kb * BK, row_b);
+#pragma unroll
+                    for (int x = 0; x < KBOX; ++x) {
+                        tma_load_2d_pair(st + x * A_BYTES, &tm_a, bar, (kb * KBOX + x) * BK, row_a);
+                        tma_load_2d_pair(st + KBOX * A_BYTES + x * B_BYTES, &tm_b, bar, (kb * KBOX + x) * BK, row_b);
+                    }
                 }
             }
         }
@@ -358,15 +388,18 @@ gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                         break;
                     }
                     tc_fence_after();
-                    const uint64_t da = make_sw128_kmajor_desc(smem_u32(sm + s * STAGE_BYTES));
-                    const uint64_t db = make_sw128_kmajor_desc(smem_u32(sm + s * STAGE_BYTES + A_BYTES));
 #pragma unroll
-                    for (int j = 0; j < BKB / 32; ++j) {
-                        const uint32_t accumulate = (kb > 0 || j > 0) ? 1u : 0u;
-                        if constexpr (KIND == gm::KIND_I8)
-                            umma_i8_ss_pair(d, da + (uint64_t)(j * 2), db + (uint64_t)(j * 2), idesc, accumulate);
-                        else
-                            umma_f16_ss_pair(d, da + (uint64_t)(j * 2), db + (uint64_t)(j * 2), idesc, accumulate);
+                    for (int x = 0; x < KBOX; ++x) {
+                        const uint64_t da = make_sw128_kmajor_desc(smem_u32(sm + s * STAGE_BYTES + x * A_BYTES));
+                        const uint64_t db = make_sw128_kmajor_desc(smem_u32(sm + s * STAGE_BYTES + KBOX * A_BYTES + x * B_BYTES));
+#pragma unroll
+                        for (int j = 0; j < BKB / 32; ++j) {
+                            const uint32_t accumulate = (kb > 0 || x > 0 || j > 0) ? 1u : 0u;
+                            if constexpr (KIND == gm::KIND_I8)
+                                umma_i8_ss_pair(d, da + (uint64_t)(j * 2), db + (uint64_t)(j * 2), idesc, accumulate);
+                            else
+                                umma_f16_ss_pair(d, da + (uint64_t)(j * 2), db + (uint64_t)(j * 2), idesc, accumulate);
+                        }
                     }
                     tc_commit_pair(&empty[s]);
                 }
@@ -387,12 +420,19 @@ gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             tc_fence_after();
             const int row = tm * PAIR_M + (int)rank * BM + q * 32 + lane;
             const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(as * BN);
+            float best = -INFINITY;
+            int best_col = tn * BN;
 #pragma unroll 1
             for (int c = 0; c < BN / 16; ++c) {
                 uint32_t v[16];
                 tmem_ld16(lane_addr + c * 16, v);
                 tc_wait_ld();
-                epilogue_chunk<KIND, TOut>(p, v, row, tn * BN + c * 16);
+                if (KIND != gm::KIND_I8 && p.epi == gm::EPI_ARGMAX) argmax_chunk<TOut>(p, v, tn * BN + c * 16, best, best_col);
+                else epilogue_chunk<KIND, TOut>(p, v, row, tn * BN + c * 16);
+            }
+            if (KIND != gm::KIND_I8 && p.epi == gm::EPI_ARGMAX && row < p.M) {
+                p.part_val[(size_t)row * p.tiles_n + tn] = best;
+                p.part_idx[(size_t)row * p.tiles_n + tn] = best_col;
             }
             tc_fence_before();
             __syncwarp();
@@ -493,9 +533,67 @@ int launch_i8_gemm_dequant_umma(const int8_t* qa, const float* sa, const int8_t*
     return RWKV7_OK;
 }
 
+// one CTA per row: fold the per-tile winners; among equal values the lowest column wins (torch.argmax's rule)
+__global__ void __launch_bounds__(256) argmax_reduce_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx,
+                                                            int tiles_n, float* __restrict__ out_val, long long* __restrict__ out_idx) {
+    __shared__ float s_val[256];
+    __shared__ int s_idx[256];
+    const size_t row = blockIdx.x;
+    float best = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int t = threadIdx.x; t < tiles_n; t += 256) {
+        const float v = part_val[row * tiles_n + t];
+        const int i = part_idx[row * tiles_n + t];
+        if (v > best || (v == best && i < idx)) best = v, idx = i;
+    }
+    s_val[threadIdx.x] = best;
+    s_idx[threadIdx.x] = idx;
+    __syncthreads();
+    for (int w = 128; w > 0; w >>= 1) {
+        if ((int)threadIdx.x < w) {
+            const float v = s_val[threadIdx.x + w];
+            const int i = s_idx[threadIdx.x + w];
+            if (v > s_val[threadIdx.x] || (v == s_val[threadIdx.x] && i < s_idx[threadIdx.x])) s_val[threadIdx.x] = v, s_idx[threadIdx.x] = i;
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        if (out_val) out_val[row] = s_val[0];
+        out_idx[row] = s_idx[0];
+    }
+}
+
 }  // namespace rwkv7
 
 using namespace rwkv7;
+
+extern "C" int64_t rwkv7_gemm_argmax_workspace_bytes(int M, int N) {
+    if (M <= 0 || N <= 0) return 0;
+    return (int64_t)M * ((N + gm::BN - 1) / gm::BN) * 8;
+}
+
+extern "C" int rwkv7_gemm_argmax(const void* a, const void* b, void* workspace, int64_t workspace_bytes, float* best_value,
+                                 long long* best_index, int M, int K, int N, int dtype, void* stream) {
+    RWKV7_REQUIRE(M > 0 && K > 0 && N > 0, RWKV7_ERR_INVALID, "gemm_argmax: sizes must be positive");
+    RWKV7_REQUIRE(dtype == RWKV7_F16 || dtype == RWKV7_BF16, RWKV7_ERR_UNSUPPORTED, "gemm_argmax: fp16 or bf16 operands only");
+    RWKV7_REQUIRE(K % 8 == 0, RWKV7_ERR_UNSUPPORTED, "gemm_argmax: K must be a multiple of 8 (got %d)", K);
+    RWKV7_REQUIRE(a && b && workspace && best_index, RWKV7_ERR_INVALID, "gemm_argmax: null pointer");
+    RWKV7_REQUIRE(aligned(a, 16) && aligned(b, 16) && aligned(workspace, 16), RWKV7_ERR_ALIGN, "gemm_argmax: operands must be 16-byte aligned");
+    RWKV7_REQUIRE(workspace_bytes >= rwkv7_gemm_argmax_workspace_bytes(M, N), RWKV7_ERR_WORKSPACE,
+                  "gemm_argmax: workspace of %lld bytes is smaller than the %lld required", (long long)workspace_bytes,
+                  (long long)rwkv7_gemm_argmax_workspace_bytes(M, N));
+    const int tiles_n = (N + gm::BN - 1) / gm::BN;
+    GemmArgs g{};
+    g.M = M, g.N = N, g.K = K;
+    g.epi = gm::EPI_ARGMAX;
+    g.part_val = reinterpret_cast<float*>(workspace);
+    g.part_idx = reinterpret_cast<int*>(workspace) + (size_t)M * tiles_n;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int e = dtype == RWKV7_F16 ? launch_gemm<gm::KIND_F16, __half>(a, b, g, st) : launch_gemm<gm::KIND_BF16, __nv_bfloat16>(a, b, g, st);
+    if (e) return e;
+    argmax_reduce_kernel<<<M, 256, 0, st>>>(g.part_val, g.part_idx, tiles_n, best_value, best_index);
+    return check_launch("argmax_reduce_kernel");
+}
 
 extern "C" int rwkv7_gemm(const void* a, const void* b, const void* bias, const void* residual, void* c, int M, int K,
                           int N, int epilogue, int dtype, void* stream) {

@@ -77,7 +77,7 @@ template <> struct StateIO<__half> {
     }
 };
 
-template <typename T, typename TW, int MODE, typename TS>
+template <typename T, typename TW, int MODE, typename TS, bool POOL = false>
 __global__ void __launch_bounds__(kStepThreads, 8) wkv7_step_kernel(const StepArgs p) {  // 64 registers: 8 CTAs per SM (measured: 7 -> 8 CTAs is -9 % time)
     const int bh = blockIdx.x;
     const int h = bh % p.H;
@@ -86,8 +86,9 @@ __global__ void __launch_bounds__(kStepThreads, 8) wkv7_step_kernel(const StepAr
     const int rg = tid >> 4;
     const size_t vbase = (size_t)bh * kN;
     // with a state pool the recurrent rows of sequence b sit at pool row slots[b]; the step's operands stay batch-ordered
-    const int srow = p.slots ? __ldg(p.slots + bh / p.H) : bh / p.H;
-    const size_t sbh = (size_t)srow * p.H + h;
+    // (a template parameter, not a run-time test: the dense kernel keeps its exact instruction stream and registers)
+    const int srow = POOL ? __ldg(p.slots + bh / p.H) : bh / p.H;
+    const size_t sbh = POOL ? (size_t)srow * p.H + h : (size_t)bh;
     const size_t vsbase = sbh * kN;
     const int hbase = h * kN;
     const int c0 = l16 * 4;
@@ -233,9 +234,9 @@ __global__ void __launch_bounds__(kStepThreads, 8) wkv7_step_kernel(const StepAr
     }
 }
 
-template <typename T, typename TW, int MODE, typename TS = float>
+template <typename T, typename TW, int MODE, typename TS = float, bool POOL = false>
 static int launch_step(StepArgs p, int B, cudaStream_t st) {
-    launch_programmatic(wkv7_step_kernel<T, TW, MODE, TS>, dim3(B * p.H), dim3(kStepThreads), 0, st, p);
+    launch_programmatic(wkv7_step_kernel<T, TW, MODE, TS, POOL>, dim3(B * p.H), dim3(kStepThreads), 0, st, p);
     return check_launch("wkv7_step_kernel");
 }
 
@@ -343,7 +344,7 @@ extern "C" int rwkv7_wkv7_output_prepare_raw_pool(const void* r, const void* w_r
                   "wkv7_output_prepare_raw_pool: v_first_pool and v_gate must be given together");
     if (int e = check_step_common(p, B, H, N)) return e;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    RWKV7_DISPATCH_DTYPE(dtype, T, { return launch_step<T, T, kRaw>(p, B, st); });
+    RWKV7_DISPATCH_DTYPE(dtype, T, { return launch_step<T, T, kRaw, float, true>(p, B, st); });
     return RWKV7_OK;
 }
 

@@ -46,3 +46,26 @@ def dense_linear(x, weight, bias=None, *, relu2: bool = False, residual=None, ou
     _lib.check(_lib.lib.rwkv7_gemm(ptr(x2), ptr(w), ptr(bias), ptr(res), ptr(y), M, K, N, 1 if relu2 else 0, dt_code(x2),
                                    stream_ptr(x2)), "gemm")
     return y.reshape(*x.shape[:-1], N)
+
+
+def dense_argmax(x, weight, *, return_values: bool = False):
+    """``argmax(x @ weight.T, dim=-1)`` per row without materialising the logits: the GEMM's epilogue keeps the best
+    column of every tile and a small second kernel folds the tiles.  Equal to ``torch.argmax`` of the fp16 / bf16
+    logits (values are rounded to that type before they are compared; the lowest index wins a tie).  With
+    ``return_values`` also the winning logit per row (fp32), which a vocabulary-sharded head exchanges."""
+    if not takes(x, weight):
+        raise ValueError("dense_argmax needs fp16 / bf16 CUDA operands of one dtype with K % 8 == 0")
+    N, K = (int(v) for v in weight.shape)
+    x2 = x.reshape(-1, K)
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    w = weight if weight.is_contiguous() else weight.contiguous()
+    M = int(x2.shape[0])
+    nbytes = int(_lib.lib.rwkv7_gemm_argmax_workspace_bytes(M, N))
+    ws = torch.empty((nbytes,), device=x.device, dtype=torch.uint8)
+    idx = torch.empty((M,), device=x.device, dtype=torch.int64)
+    val = torch.empty((M,), device=x.device, dtype=torch.float32) if return_values else None
+    _lib.check(_lib.lib.rwkv7_gemm_argmax(ptr(x2), ptr(w), ptr(ws), nbytes, ptr(val), ptr(idx), M, K, N, dt_code(x2),
+                                          stream_ptr(x2)), "gemm_argmax", kernels=2)
+    idx = idx.reshape(x.shape[:-1])
+    return (idx, val.reshape(x.shape[:-1])) if return_values else idx

@@ -25,6 +25,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from . import gemm as _gemm
 from . import norm_mix as _nm
 from . import packing as _pk
 from . import prep as _prep
@@ -268,8 +269,17 @@ class RWKV7ForCausalLM(nn.Module):
     def _head(self, xn, greedy: bool, lane: int = 0):
         """Final projection: logits ``[B,V]`` (all-gathered over the vocabulary shards when the head is sharded) or, with
         ``greedy``, the arg-max token of every row (local arg-max + one [B,2] exchange per rank)."""
+        sharded = self.tp_shard_head and self.tp_group is not False
+        w = self.lm_head.weight
+        if greedy and _gemm.takes(xn, w) and int(xn.shape[0]) >= _gemm.MIN_ROWS:
+            # the arg-max rides in the head GEMM's epilogue: the logits are never written
+            if not sharded:
+                return _gemm.dense_argmax(xn, w)
+            idx, val = _gemm.dense_argmax(xn, w, return_values=True)
+            return _sh.sharded_argmax(None, self.tp_rank, self.tp_world, self._lane_group(lane), local_best=(val, idx),
+                                      shard_width=int(w.shape[0]))
         local = _linear(self.lm_head, xn)
-        if not self.tp_shard_head or self.tp_group is False:
+        if not sharded:
             return local.argmax(-1) if greedy else local
         group = self._lane_group(lane)
         if greedy:

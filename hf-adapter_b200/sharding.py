@@ -58,13 +58,20 @@ def pick_sharded_argmax(values, indices):
     return torch.where(values == best[None], indices, torch.full_like(indices, big)).min(dim=0).values
 
 
-def sharded_argmax(local_logits, rank: int, world: int, group=None):
+def sharded_argmax(local_logits, rank: int, world: int, group=None, *, local_best=None, shard_width: int = 0):
     """Greedy token over a vocabulary-sharded head: local (max, arg-max) per row, one all-gather of ``[B,2]`` floats per
-    rank (indices below 2^24 are exact in fp32), then the pick.  Every rank returns the same ``[B]`` int64 tokens."""
+    rank (indices below 2^24 are exact in fp32), then the pick.  Every rank returns the same ``[B]`` int64 tokens.
+    ``local_best = (values [B] fp32, indices [B])`` with ``shard_width`` replaces ``local_logits`` when the head kernel
+    already folded its shard (the logits then never exist)."""
     import torch
     import torch.distributed as dist
-    vals, idx = local_logits.float().max(dim=-1)
-    mine = torch.stack([vals, (idx + rank * int(local_logits.shape[-1])).float()], dim=-1).contiguous()  # [B,2]
+    if local_best is not None:
+        vals, idx = local_best
+        width = int(shard_width)
+    else:
+        vals, idx = local_logits.float().max(dim=-1)
+        width = int(local_logits.shape[-1])
+    mine = torch.stack([vals.float(), (idx + rank * width).float()], dim=-1).contiguous()  # [B,2]
     parts = torch.empty((world * int(mine.shape[0]), 2), device=mine.device, dtype=mine.dtype)  # rank-major concatenation
     dist.all_gather_into_tensor(parts, mine, group=group)
     parts = parts.view(world, -1, 2)

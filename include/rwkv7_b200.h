@@ -334,6 +334,15 @@ int rwkv7_i8_gemm(const int8_t* qa, const int8_t* qw, int32_t* acc, int M, int K
 int rwkv7_gemm(const void* a, const void* b, const void* bias, const void* residual, void* c, int M, int K, int N,
                int epilogue, int dtype, void* stream);
 
+/* The output head of a greedy decode step: arg-max over the columns of a[M,K] . b[N,K]^T without ever storing the
+ * [M,N] logits (rwkv7_hf/native_jit_decode.py:953-1000 computes the head GEMM and then torch.argmax).  Values are
+ * rounded to `dtype` before they are compared and the lowest column wins a tie, so best_index equals torch.argmax of
+ * the stored logits.  best_value [M] fp32 may be NULL; best_index [M] int64; workspace of
+ * rwkv7_gemm_argmax_workspace_bytes(M, N) bytes, 16-byte aligned. */
+int64_t rwkv7_gemm_argmax_workspace_bytes(int M, int N);
+int rwkv7_gemm_argmax(const void* a, const void* b, void* workspace, int64_t workspace_bytes, float* best_value,
+                      long long* best_index, int M, int K, int N, int dtype, void* stream);
+
 /* Dequant epilogue; replaces _a8w8_dequant_kernel / _a8w8_dequant_add_kernel
  * (rwkv7_hf/native_quant_a8w8.py:166-264): out = fp32(acc)*sa[row]*sw[col] (+bias) (+residual). */
 int rwkv7_a8w8_dequant(const int32_t* acc, const float* sa, const float* sw, const void* bias,

@@ -145,6 +145,50 @@ def test_config5_one_layer_at_7p2b_width_against_oracle():
     np.testing.assert_allclose(npf(lg), lo.astype(np.float32), rtol=3e-2, atol=3e-2)
 
 
+def test_config4_layers_at_2p9b_width_int8_against_oracle():
+    """Two layers at d_model 2560, 40 heads, FFN 10240 with per-output-channel int8 on all six projections (the 2.9B
+    configuration's format), batch 64 as that configuration decodes it, three tokens, fp16: logits cosine >= 0.9995
+    and state relative error <= 1e-2 against the oracle's token step on the same quantised weights; then a 64-token
+    prefill chunk of the same model (dequantised weights through the dense GEMM, tensor-core scan) against 64 decode
+    steps of it."""
+    cfg = hb.NativeRWKV7Config(vocab_size=512, hidden_size=2560, num_hidden_layers=2, num_heads=40, head_dim=64,
+                               intermediate_size=10240, decay_low_rank_dim=64, a_low_rank_dim=64, v_low_rank_dim=32,
+                               gate_low_rank_dim=128)
+    model = hb.RWKV7ForCausalLM(cfg)
+    sd = seeded_state_dict({k: v.shape for k, v in model.state_dict().items()}, 6, dtype=torch.float16)
+    model.load_state_dict(sd)
+    model = model.half()
+    assert hb.quantize_model(model, "w8", min_params=1 << 20) == 12
+    model = model.cuda().eval()
+    g = {"param::" + k: v.numpy() for k, v in sd.items()}
+    params = params_from_golden(g)
+    for d in params["layers"]:
+        for nm in ("Rw", "Kw", "Vw", "Ow", "fK", "fV"):
+            q_, s_ = O.quantize_w8_row(d[nm])
+            d[nm] = dict(kind="w8", q=q_, s=s_)
+    B, H = 64, 40
+    ids = np.random.default_rng(4).integers(0, 512, (B, 3))
+    cache_o = O.new_cache(2, B, 2560, H, N, np.float16)
+    cache = model.new_cache(B)
+    for t in range(3):
+        lo = O.model_step(params, ids[:, t], cache_o, H, N)
+        lg = model.rwkv7_forward_token(cu(ids[:, t]), cache, use_graph=(t == 2))
+        a, b = npf(lg).astype(np.float64).ravel(), lo.astype(np.float64).ravel()
+        assert a @ b / np.linalg.norm(a) / np.linalg.norm(b) > 0.9995, f"token {t}"
+    so = np.stack(cache_o["state"])
+    assert np.linalg.norm(npf(torch.stack(cache._state)) - so) / np.linalg.norm(so) < 1e-2
+    # prefill chunk == the same tokens one by one (different kernels: GEMM on dequantised weights, chunked scan)
+    pids = torch.randint(0, 512, (4, 64), device="cuda", generator=torch.Generator(device="cuda").manual_seed(1))
+    lp, cp = model.rwkv7_prefill_native(pids, None, logits_to_keep=1, scan_chunk=64)
+    cd = model.new_cache(4)
+    for t in range(64):
+        ld = model.rwkv7_forward_token(pids[:, t], cd, use_graph=False)
+    a, b = npf(lp[:, -1]).astype(np.float64).ravel(), npf(ld).astype(np.float64).ravel()
+    assert a @ b / np.linalg.norm(a) / np.linalg.norm(b) > 0.999
+    sp, sdec = npf(torch.stack(cp._state)), npf(torch.stack(cd._state))
+    assert np.linalg.norm(sp - sdec) / np.linalg.norm(sdec) < 1e-2
+
+
 def test_a8w8_ffn_against_reference_composition():
     """The fused A8W8 FFN (int8 hidden activation) against the reference's own up -> relu^2 -> down + residual on its
     CPU route (fixture a8w8_ffn.npz), at the reference's gate for this approximation (cosine >= 0.999,

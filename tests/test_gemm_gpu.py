@@ -77,3 +77,18 @@ def test_fused_sequence_ffn_runs_on_the_library_gemm():
     want = mid.float() @ wv.float().t()
     torch.testing.assert_close(out.float(), want, rtol=4e-3, atol=4e-3)
     assert torch.equal(nxt, x[:, -1])
+
+
+@pytest.mark.parametrize("M,K,N", [(64, 256, 1000), (5, 128, 65536), (200, 512, 4096), (64, 4096, 65536)])
+def test_fused_argmax_equals_argmax_of_stored_logits(M, K, N):
+    g = torch.Generator(device="cuda").manual_seed(M + N)
+    x = torch.randn(M, K, device="cuda", generator=g).half()
+    w = (torch.randn(N, K, device="cuda", generator=g) / K ** 0.5).half()
+    w[N // 2] = w[3]  # two identical columns: a guaranteed tie wherever column 3 wins
+    x[0] = 0  # an all-equal row: index 0 must win
+    logits = hb.dense_linear(x, w)
+    idx, val = hb.dense_argmax(x, w, return_values=True)
+    assert idx.dtype == torch.int64 and torch.equal(idx, logits.argmax(-1))
+    assert torch.equal(val, logits.float().max(-1).values)
+    assert torch.equal(hb.dense_argmax(x, w), idx) and int(idx[0]) == 0
+    assert _lib.kernel_status() == 0
