@@ -68,6 +68,7 @@ SIGNATURES = {
     "rwkv7_a8w8_dequant": (I, [P] * 6 + [I, I, I, P]),
     "rwkv7_a8w8_workspace_bytes": (L, [I, I, I]),
     "rwkv7_a8w8_linear": (I, [P] * 7 + [L, I, I, I, I, P]),
+    "rwkv7_a8w8_linear_relu2": (I, [P] * 6 + [L, I, I, I, I, P]),
     "rwkv7_tp_allreduce_max_ctas": (I, []),
     "rwkv7_tp_allreduce": (I, [P, P, PP, PP, P, I, I, I, I, ctypes.c_longlong, I, I, P]),
     "rwkv7_a8w8_static_capacity_bytes": (L, []),

@@ -103,14 +103,19 @@ template <typename T>
 __global__ void __launch_bounds__(256) a8w8_dequant_kernel(const int32_t* __restrict__ acc, const float* __restrict__ sa,
                                                            const float* __restrict__ sw, const T* __restrict__ bias,
                                                            const T* __restrict__ residual, T* __restrict__ out,
-                                                           int M, int Nout) {
+                                                           int M, int Nout, int relu2) {
     const long long total = (long long)M * Nout;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int m = (int)(i / Nout), n = (int)(i % Nout);
         // every step rounded on its own (no fused multiply-add): the tensor-core GEMM's fused epilogue does the same
         float v = __fmul_rn(__fmul_rn((float)acc[i], sa[m]), sw[n]);
         if (bias) v = __fadd_rn(v, to_f<T>(bias[n]));
-        if (residual) v = __fadd_rn(v, to_f<T>(residual[i]));
+        if (relu2) {
+            const float a = fmaxf(round_to<T>(v), 0.f);
+            v = a * a;
+        } else if (residual) {
+            v = __fadd_rn(v, to_f<T>(residual[i]));
+        }
         out[i] = from_f<T>(v);
     }
 }
@@ -238,7 +243,8 @@ int launch_i8_gemm_mma(const int8_t* qa, const int8_t* qw, int32_t* acc, int M, 
 // implemented in gemm_umma.cu; returns RWKV7_ERR_UNSUPPORTED when the shape is not eligible
 int launch_i8_gemm_umma(const int8_t* qa, const int8_t* qw, int32_t* acc, int M, int K, int Nout, cudaStream_t st);
 int launch_i8_gemm_dequant_umma(const int8_t* qa, const float* sa, const int8_t* qw, const float* sw, const void* bias,
-                                const void* residual, void* out, int M, int K, int Nout, int dtype, cudaStream_t st);
+                                const void* residual, void* out, int M, int K, int Nout, int relu2, int dtype,
+                                cudaStream_t st);
 
 static inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
 
@@ -270,8 +276,8 @@ extern "C" int rwkv7_i8_gemm(const int8_t* qa, const int8_t* qw, int32_t* acc, i
     return launch_i8_gemm_mma(qa, qw, acc, M, K, Nout, st);
 }
 
-extern "C" int rwkv7_a8w8_dequant(const int32_t* acc, const float* sa, const float* sw, const void* bias,
-                                  const void* residual, void* out, int M, int Nout, int dtype, void* stream) {
+static int a8w8_dequant_impl(const int32_t* acc, const float* sa, const float* sw, const void* bias, const void* residual,
+                             void* out, int M, int Nout, int relu2, int dtype, void* stream) {
     RWKV7_REQUIRE(M > 0 && Nout > 0, RWKV7_ERR_INVALID, "a8w8_dequant: sizes must be positive");
     RWKV7_REQUIRE(acc && sa && sw && out, RWKV7_ERR_INVALID, "a8w8_dequant: null pointer");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -279,10 +285,15 @@ extern "C" int rwkv7_a8w8_dequant(const int32_t* acc, const float* sa, const flo
     const int grid = (int)((total + 255) / 256 < 148LL * 16 ? (total + 255) / 256 : 148LL * 16);
     RWKV7_DISPATCH_DTYPE(dtype, T, {
         a8w8_dequant_kernel<T><<<grid, 256, 0, st>>>(acc, sa, sw, reinterpret_cast<const T*>(bias),
-                                                    reinterpret_cast<const T*>(residual), reinterpret_cast<T*>(out), M, Nout);
+                                                    reinterpret_cast<const T*>(residual), reinterpret_cast<T*>(out), M, Nout, relu2);
         return check_launch("a8w8_dequant_kernel");
     });
     return RWKV7_OK;
+}
+
+extern "C" int rwkv7_a8w8_dequant(const int32_t* acc, const float* sa, const float* sw, const void* bias,
+                                  const void* residual, void* out, int M, int Nout, int dtype, void* stream) {
+    return a8w8_dequant_impl(acc, sa, sw, bias, residual, out, M, Nout, 0, dtype, stream);
 }
 
 extern "C" int rwkv7_a8w8_relu2_requant(const int32_t* acc, const float* sa, const float* sw, const void* bias, int8_t* q,
@@ -300,9 +311,9 @@ extern "C" int64_t rwkv7_a8w8_workspace_bytes(int M, int K, int Nout) {
     return align_up((int64_t)M * K, 256) + align_up((int64_t)M * 4, 256) + align_up((int64_t)M * Nout * 4, 256);
 }
 
-extern "C" int rwkv7_a8w8_linear(const void* x, const int8_t* qw, const float* sw, const void* bias,
-                                 const void* residual, void* out, void* workspace, int64_t workspace_bytes, int M,
-                                 int K, int Nout, int dtype, void* stream) {
+static int a8w8_linear_impl(const void* x, const int8_t* qw, const float* sw, const void* bias, const void* residual,
+                            void* out, void* workspace, int64_t workspace_bytes, int M, int K, int Nout, int relu2,
+                            int dtype, void* stream) {
     RWKV7_REQUIRE(M > 0 && K > 0 && Nout > 0, RWKV7_ERR_INVALID, "a8w8_linear: sizes must be positive");
     RWKV7_REQUIRE(workspace && aligned(workspace, 256), RWKV7_ERR_ALIGN, "a8w8_linear: workspace must be 256-byte aligned");
     RWKV7_REQUIRE(workspace_bytes >= rwkv7_a8w8_workspace_bytes(M, K, Nout), RWKV7_ERR_WORKSPACE,
@@ -315,10 +326,22 @@ extern "C" int rwkv7_a8w8_linear(const void* x, const int8_t* qw, const float* s
     if (int e = rwkv7_a8_quant(x, qa, sa, M, K, dtype, stream)) return e;
     // tensor-core route: the dequantisation rides in the GEMM's epilogue, the int32 accumulators never reach memory
     RWKV7_REQUIRE(sw && out, RWKV7_ERR_INVALID, "a8w8_linear: null pointer");
-    int e = launch_i8_gemm_dequant_umma(qa, sa, qw, sw, bias, residual, out, M, K, Nout, dtype, static_cast<cudaStream_t>(stream));
+    int e = launch_i8_gemm_dequant_umma(qa, sa, qw, sw, bias, residual, out, M, K, Nout, relu2, dtype, static_cast<cudaStream_t>(stream));
     if (e != RWKV7_ERR_UNSUPPORTED) return e;
     if (int e2 = rwkv7_i8_gemm(qa, qw, acc, M, K, Nout, stream)) return e2;
-    return rwkv7_a8w8_dequant(acc, sa, sw, bias, residual, out, M, Nout, dtype, stream);
+    return a8w8_dequant_impl(acc, sa, sw, bias, residual, out, M, Nout, relu2, dtype, stream);
+}
+
+extern "C" int rwkv7_a8w8_linear(const void* x, const int8_t* qw, const float* sw, const void* bias,
+                                 const void* residual, void* out, void* workspace, int64_t workspace_bytes, int M,
+                                 int K, int Nout, int dtype, void* stream) {
+    return a8w8_linear_impl(x, qw, sw, bias, residual, out, workspace, workspace_bytes, M, K, Nout, 0, dtype, stream);
+}
+
+extern "C" int rwkv7_a8w8_linear_relu2(const void* x, const int8_t* qw, const float* sw, const void* bias, void* out,
+                                       void* workspace, int64_t workspace_bytes, int M, int K, int Nout, int dtype,
+                                       void* stream) {
+    return a8w8_linear_impl(x, qw, sw, bias, nullptr, out, workspace, workspace_bytes, M, K, Nout, 1, dtype, stream);
 }
 
 // ---------------------------------------------------------------- no-allocation variant

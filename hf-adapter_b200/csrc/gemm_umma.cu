@@ -35,6 +35,7 @@ struct GemmArgs {
     int M, N, K;
     int tiles_m, tiles_n;
     int epi;
+    int relu2;  // with EPI_DEQUANT: relu^2 of the dequantised value rounded to the output type (instead of + residual)
     int vec;  // 1: N % 16 == 0 and every pointer the epilogue touches is 16-byte aligned
     unsigned int* error;
     // arg-max epilogue: per (row, column tile) the best value rounded to the output type and its column, [M, tiles_n] each
@@ -95,7 +96,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmArgs& p, const uint32_t
                 for (int e = 0; e < 8; ++e) f[8 * h + e] = __fadd_rn(f[8 * h + e], b[e]);
             }
         }
-        if (p.epi == EPI_RELU2) {
+        if (p.epi == EPI_RELU2 || p.relu2) {
 #pragma unroll
             for (int e = 0; e < 16; ++e) {
                 const float a = fmaxf(round_to<TOut>(f[e]), 0.f);
@@ -121,7 +122,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmArgs& p, const uint32_t
         for (int e = 0; e < 16 && col + e < p.N; ++e) {
             float x = f[e];
             if (bias) x = __fadd_rn(x, to_f<TOut>(bias[col + e]));
-            if (p.epi == EPI_RELU2) {
+            if (p.epi == EPI_RELU2 || p.relu2) {
                 const float a = fmaxf(round_to<TOut>(x), 0.f);
                 x = a * a;
             } else if (res) {
@@ -522,12 +523,14 @@ int launch_i8_gemm_umma(const int8_t* qa, const int8_t* qw, int32_t* acc, int M,
 
 // int8 GEMM with the A8W8 dequantisation fused into its epilogue; same eligibility rule
 int launch_i8_gemm_dequant_umma(const int8_t* qa, const float* sa, const int8_t* qw, const float* sw, const void* bias,
-                                const void* residual, void* out, int M, int K, int Nout, int dtype, cudaStream_t st) {
+                                const void* residual, void* out, int M, int K, int Nout, int relu2, int dtype,
+                                cudaStream_t st) {
     if (M < 64 || K % 16 || !aligned(qa, 16) || !aligned(qw, 16)) return RWKV7_ERR_UNSUPPORTED;
     GemmArgs g{};
     g.C = out, g.bias = bias, g.residual = residual, g.sa = sa, g.sw = sw;
     g.M = M, g.N = Nout, g.K = K;
     g.epi = gm::EPI_DEQUANT;
+    g.relu2 = relu2;
     g.vec = epilogue_vectorisable(g);
     RWKV7_DISPATCH_DTYPE(dtype, T, { return launch_gemm<gm::KIND_I8, T>(qa, qw, g, st); });
     return RWKV7_OK;

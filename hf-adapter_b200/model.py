@@ -372,12 +372,18 @@ class RWKV7ForCausalLM(nn.Module):
                 out, new_state = _rec.fused_recurrent_scan_output_prepare(
                     r, w, k, v, kk, a_sig, state[i], g, at.r_k, at.g_norm.weight, at.g_norm.bias, eps=N * 1e-5)
             state[i].copy_(new_state)
-            x = x + self._all_reduce(_linear(at.o_proj, out))
+            if self.tp_world == 1:
+                x = _linear(at.o_proj, out, residual=x)  # the residual add rides in the projection's epilogue
+            else:
+                x = x + self._all_reduce(_linear(at.o_proj, out))
             h2 = _nm.layer_norm(x, layer.ffn_norm.weight, layer.ffn_norm.bias)
             mixed, nxt = _nm.fused_ffn_sequence_shift_mix(h2, xpf[i], ff.x_k)
             xpf[i].copy_(nxt)
             hidden = _linear(ff.key, mixed, relu2=True)
-            x = x + self._all_reduce(_linear(ff.value, hidden))
+            if self.tp_world == 1:
+                x = _linear(ff.value, hidden, residual=x)
+            else:
+                x = x + self._all_reduce(_linear(ff.value, hidden))
         if v_first is not None:
             v_first_buf.copy_(v_first[:, -1])
         cache._seen_tokens += T

@@ -285,9 +285,10 @@ def a8w8_workspace(M, K, Nout, device):
     return torch.empty((n,), device=device, dtype=torch.uint8)
 
 
-def a8w8_linear(x, q_weight_t, weight_scale, bias=None, *, out=None, residual=None, workspace=None):
+def a8w8_linear(x, q_weight_t, weight_scale, bias=None, *, out=None, residual=None, workspace=None, relu2: bool = False):
     """Dynamic-A8 / W8 linear (rwkv7_hf/native_quant_a8w8.py:323): quantise rows, int8 GEMM with exact int32
-    accumulators, dequantise (+bias, +residual)."""
+    accumulators, dequantise (+bias, +residual).  ``relu2`` (an extension): relu(.)**2 of the rounded output instead of
+    a residual, in the same epilogue."""
     K = int(q_weight_t.shape[0])
     Nout = int(q_weight_t.shape[1])
     x2 = _rows(x, K)
@@ -302,6 +303,13 @@ def a8w8_linear(x, q_weight_t, weight_scale, bias=None, *, out=None, residual=No
     if workspace is None:
         workspace = a8w8_workspace(M, K, Nout, x2.device)
     y = torch.empty((M, Nout), device=x2.device, dtype=x2.dtype) if out is None else out.reshape(M, Nout)
+    if relu2:
+        if res is not None:
+            raise ValueError("the relu^2 epilogue takes no residual")
+        _lib.check(_lib.lib.rwkv7_a8w8_linear_relu2(ptr(x2), ptr(qw), ptr(weight_scale), ptr(bias), ptr(y), ptr(workspace),
+                                                    int(workspace.numel()), M, K, Nout, dt_code(x2), stream_ptr(x2)),
+                   "a8w8_linear", kernels=2 if M >= 64 else 3)
+        return y.reshape(*x.shape[:-1], Nout)
     _lib.check(_lib.lib.rwkv7_a8w8_linear(ptr(x2), ptr(qw), ptr(weight_scale), ptr(bias), ptr(res), ptr(y),
                                           ptr(workspace), int(workspace.numel()), M, K, Nout, dt_code(x2),
                                           stream_ptr(x2)), "a8w8_linear", kernels=2 if M >= 64 else 3)
@@ -639,6 +647,9 @@ class A8W8Linear(torch.nn.Module):
 
     def rwkv7_forward_add(self, x, residual):
         return a8w8_linear(x, self.q_weight_t, self.weight_scale, self.bias, residual=residual)
+
+    def rwkv7_forward_relu2(self, x):
+        return a8w8_linear(x, self.q_weight_t, self.weight_scale, self.bias, relu2=True)
 
     def rwkv7_forward_ffn(self, x, down, residual):
         """up -> relu^2 (fp16 boundary) -> down + residual; returns None when the pairing does not apply."""

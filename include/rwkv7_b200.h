@@ -361,6 +361,11 @@ int rwkv7_a8w8_linear(const void* x, const int8_t* qw, const float* sw, const vo
                       void* out, void* workspace, int64_t workspace_bytes, int M, int K, int Nout, int dtype,
                       void* stream);
 
+/* The FFN key projection of an A8W8 model: a8w8_linear followed by relu(.)^2 of the value rounded to `dtype`, the
+ * activation in the same epilogue (rwkv7_hf/native_jit_prefill.py:964-975 probes rwkv7_forward_relu2 for it). */
+int rwkv7_a8w8_linear_relu2(const void* x, const int8_t* qw, const float* sw, const void* bias, void* out,
+                            void* workspace, int64_t workspace_bytes, int M, int K, int Nout, int dtype, void* stream);
+
 /* rwkv7_a8w8_linear for callers that cannot allocate device memory when they call (a server that gave the whole
  * GPU to its own memory pool, a thread that must not enter the CUDA allocator, a host that forbids cudaMalloc inside
  * operators).  No counterpart in the reference.  The scratch is a fixed array of rwkv7_a8w8_static_capacity_bytes()

@@ -246,3 +246,20 @@ def test_w8_tensor_core_path(G, M, K, Nn):
         assert mod._tiled is None
         np.testing.assert_allclose(npf(mod(xs[0])), -yo, rtol=2e-3, atol=2e-3 * max(1.0, float(np.abs(yo).max())))
     assert _lib.kernel_status(True) == 0
+
+
+@pytest.mark.parametrize("M", [5, 64, 300])
+def test_a8w8_relu2_epilogue(M):
+    """relu^2 in the A8W8 linear's epilogue == relu(a8w8_linear(x))**2 computed on the stored fp16 output, on the
+    mma.sync route (M < 64) and on the tensor-core route with the fused dequantisation."""
+    torch.manual_seed(M)
+    K, Nn = 512, 264
+    lin = torch.nn.Linear(K, Nn, bias=True).half()
+    mod = hb.A8W8Linear(lin).cuda()
+    x = torch.randn(M, K, device="cuda", dtype=torch.float16)
+    plain = mod(x)
+    want = (torch.relu(plain.float()) ** 2).half()
+    got = mod.rwkv7_forward_relu2(x)
+    assert torch.equal(got, want)
+    with pytest.raises(ValueError):
+        hb.a8w8_linear(x, mod.q_weight_t, mod.weight_scale, relu2=True, residual=plain)
