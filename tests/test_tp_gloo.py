@@ -92,6 +92,11 @@ def _argmax_worker(rank, world, port, q):
         want = logits.float().argmax(-1)
         assert torch.equal(tok, want), (tok, want)
         assert int(tok[0]) == 5 and int(tok[1]) == 33 and int(tok[2]) == 63
+        # the same from a pre-folded shard (what the head kernel's arg-max epilogue hands over): no local logits at all
+        local = logits[:, rank * Vl:(rank + 1) * Vl].float()
+        val, idx = local.max(dim=-1)
+        tok2 = sharded_argmax(None, rank, world, local_best=(val, idx), shard_width=Vl)
+        assert torch.equal(tok2, want), (tok2, want)
         head = {"lm_head.weight": np.arange(64 * 4).reshape(64, 4), "model.norm.weight": np.ones(4)}
         sh = shard_state_dict(head, world, rank, shard_head=True)
         assert sh["lm_head.weight"].shape == (Vl, 4) and sh["lm_head.weight"][0, 0] == rank * Vl * 4
