@@ -20,7 +20,8 @@ namespace gm {
 constexpr int BM = 128, BN = 256, BKB = 128, STAGES = 4, THREADS = 192;
 constexpr int A_BYTES = BM * BKB, B_BYTES = BN * BKB, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int TMEM_COLS = 512;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 256 + 1024;
+constexpr int STG_BYTES = 4 * 32 * 64 * 4;  // epilogue staging: per epilogue warp 32 rows x 64 fp32 columns
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 256 + STG_BYTES + 1024;
 constexpr int GROUP_M = 16;
 enum { KIND_F16 = 0, KIND_BF16 = 1, KIND_I8 = 2 };
 enum { EPI_STORE = 0, EPI_RELU2 = 1, EPI_DEQUANT = 2, EPI_RAW_I32 = 3, EPI_ARGMAX = 4 };
@@ -36,7 +37,7 @@ struct GemmArgs {
     int tiles_m, tiles_n;
     int epi;
     int relu2;  // with EPI_DEQUANT: relu^2 of the dequantised value rounded to the output type (instead of + residual)
-    int vec;  // 1: N % 16 == 0 and every pointer the epilogue touches is 16-byte aligned
+    int vec;  // 1: N % 8 == 0 and every pointer the epilogue touches is 16-byte aligned
     unsigned int* error;
     // arg-max epilogue: per (row, column tile) the best value rounded to the output type and its column, [M, tiles_n] each
     float* part_val;
@@ -52,85 +53,114 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
     tm = band * gm::GROUP_M + (within - tn * rows);
 }
 
+// The epilogue of one warp for 64 columns of its 32 accumulator rows.  A thread owns one TMEM lane (= one row), so
+// storing straight from the registers tcgen05.ld fills would write 32-byte pieces of 32 different rows per instruction:
+// a quarter of every 128-byte line at a time and 32 wavefronts per store.  Instead the raw accumulators go through a
+// per-warp staging tile in shared memory (16-byte units, unit index XORed with the row so both passes are
+// conflict-free) and come back with eight lanes on the eight 16-byte pieces of one row: scales, bias and residual
+// are then loaded, and the result stored, as whole 128-byte row segments, four rows per instruction.
 template <int KIND, typename TOut>
-__device__ __forceinline__ void epilogue_chunk(const GemmArgs& p, const uint32_t (&v)[16], int row, int col) {
+__device__ __forceinline__ void epilogue_group(const GemmArgs& p, uint32_t* stg, uint32_t taddr, int row0, int col0, int lane) {
     using namespace gm;
-    if (row >= p.M || col >= p.N) return;
-    const size_t off = (size_t)row * p.N + col;
-    const bool full = p.vec && col + 16 <= p.N;
-    if constexpr (KIND == KIND_I8) {
-        if (p.epi == EPI_RAW_I32) {
-            int32_t* dst = reinterpret_cast<int32_t*>(p.C) + off;
-            if (full) {
-#pragma unroll
-                for (int e = 0; e < 16; e += 4)
-                    *reinterpret_cast<int4*>(dst + e) = make_int4((int)v[e], (int)v[e + 1], (int)v[e + 2], (int)v[e + 3]);
-            } else {
-                for (int e = 0; e < 16 && col + e < p.N; ++e) dst[e] = (int)v[e];
-            }
-            return;
-        }
-    }
-    float f[16];
-    if constexpr (KIND == KIND_I8) {
-        const float a_s = p.sa[row];
-#pragma unroll
-        for (int e = 0; e < 16; ++e) {
-            const float s = (col + e < p.N) ? p.sw[col + e] : 0.f;
-            f[e] = __fmul_rn(__fmul_rn((float)(int)v[e], a_s), s);
-        }
-    } else {
-#pragma unroll
-        for (int e = 0; e < 16; ++e) f[e] = __uint_as_float(v[e]);
-    }
-    const TOut* bias = reinterpret_cast<const TOut*>(p.bias);
+    const int j8 = (lane & 7) * 8;  // this lane's eight columns inside the group
+    const int col = col0 + j8;
     const TOut* res = reinterpret_cast<const TOut*>(p.residual);
-    TOut* dst = reinterpret_cast<TOut*>(p.C) + off;
-    if (full) {
-        if (bias) {
-            float b[8];
+    const bool full = p.vec && col + 8 <= p.N;
+    // the residual does not depend on the accumulators: its eight row pieces are requested before the TMEM loads
+    Vec8<TOut> rres[8];
+    const bool pre_res = res != nullptr && full && !(p.epi == EPI_RELU2 || p.relu2);
+    if (pre_res) {
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                load8(bias + col + 8 * h, b);
+        for (int i = 0; i < 8; ++i) {
+            const int row = row0 + (lane >> 3) + 4 * i;
+            if (row < p.M) rres[i] = *reinterpret_cast<const Vec8<TOut>*>(res + (size_t)row * p.N + col);
+        }
+    }
 #pragma unroll
-                for (int e = 0; e < 8; ++e) f[8 * h + e] = __fadd_rn(f[8 * h + e], b[e]);
+    for (int c = 0; c < 4; ++c) {
+        uint32_t v[16];
+        tmem_ld16(taddr + c * 16, v);
+        tc_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 16; e += 4) {
+            const int u = c * 4 + (e >> 2);  // 16-byte unit of this row, 0..15
+            const int pos = (u & 8) | ((u & 7) ^ (lane & 7));
+            *reinterpret_cast<uint4*>(stg + lane * 64 + pos * 4) = make_uint4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+        }
+    }
+    __syncwarp();
+    const TOut* bias = reinterpret_cast<const TOut*>(p.bias);
+    float bv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, sv[8];
+    if (col < p.N) {
+        if (full) {
+            if (bias) load8(bias + col, bv);
+            if constexpr (KIND == KIND_I8) {
+                if (p.epi == EPI_DEQUANT) load8(p.sw + col, sv);
             }
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                bv[e] = (bias && col + e < p.N) ? to_f<TOut>(bias[col + e]) : 0.f;
+                if constexpr (KIND == KIND_I8) sv[e] = (p.epi == EPI_DEQUANT && col + e < p.N) ? p.sw[col + e] : 0.f;
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int r = (lane >> 3) + 4 * i, row = row0 + r;
+        const int u0 = (lane & 7) * 2;
+        const uint4 a0 = *reinterpret_cast<const uint4*>(stg + r * 64 + ((u0 & 8) | ((u0 & 7) ^ (r & 7))) * 4);
+        const uint4 a1 = *reinterpret_cast<const uint4*>(stg + r * 64 + (((u0 + 1) & 8) | (((u0 + 1) & 7) ^ (r & 7))) * 4);
+        if (row >= p.M || col >= p.N) continue;
+        const uint32_t raw[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+        const size_t off = (size_t)row * p.N + col;
+        if constexpr (KIND == KIND_I8) {
+            if (p.epi == EPI_RAW_I32) {
+                int32_t* dst = reinterpret_cast<int32_t*>(p.C) + off;
+                if (full) {
+                    *reinterpret_cast<uint4*>(dst) = a0;
+                    *reinterpret_cast<uint4*>(dst + 4) = a1;
+                } else {
+                    for (int e = 0; e < 8 && col + e < p.N; ++e) dst[e] = (int)raw[e];
+                }
+                continue;
+            }
+        }
+        float f[8];
+        if constexpr (KIND == KIND_I8) {
+            const float a_s = p.sa[row];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] = __fmul_rn(__fmul_rn((float)(int)raw[e], a_s), sv[e]);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(raw[e]);
+        }
+        if (bias) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] = __fadd_rn(f[e], bv[e]);
         }
         if (p.epi == EPI_RELU2 || p.relu2) {
 #pragma unroll
-            for (int e = 0; e < 16; ++e) {
+            for (int e = 0; e < 8; ++e) {
                 const float a = fmaxf(round_to<TOut>(f[e]), 0.f);
                 f[e] = a * a;
             }
         } else if (res) {
-            float r[8];
+            if (full) {
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                load8(res + off + 8 * h, r);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) f[8 * h + e] = __fadd_rn(f[8 * h + e], r[e]);
+                for (int e = 0; e < 8; ++e) f[e] = __fadd_rn(f[e], to_f<TOut>(rres[i].v[e]));
+            } else {
+                for (int e = 0; e < 8 && col + e < p.N; ++e) f[e] = __fadd_rn(f[e], to_f<TOut>(res[off + e]));
             }
         }
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            float o[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) o[e] = f[8 * h + e];
-            store8(dst + 8 * h, o);
-        }
-    } else {
-        for (int e = 0; e < 16 && col + e < p.N; ++e) {
-            float x = f[e];
-            if (bias) x = __fadd_rn(x, to_f<TOut>(bias[col + e]));
-            if (p.epi == EPI_RELU2 || p.relu2) {
-                const float a = fmaxf(round_to<TOut>(x), 0.f);
-                x = a * a;
-            } else if (res) {
-                x = __fadd_rn(x, to_f<TOut>(res[off + e]));
-            }
-            dst[e] = from_f<TOut>(x);
+        TOut* dst = reinterpret_cast<TOut*>(p.C) + off;
+        if (full) {
+            store8(dst, f);
+        } else {
+            for (int e = 0; e < 8 && col + e < p.N; ++e) dst[e] = from_f<TOut>(f[e]);
         }
     }
+    __syncwarp();  // the staging tile is overwritten by the next group
 }
 
 // Arg-max epilogue: nothing of the product is stored.  A thread owns one row of the tile and folds its 256 columns
@@ -161,6 +191,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const AbortCtx actx{abort_flag, p.error};
+    uint32_t* stg = reinterpret_cast<uint32_t*>(sm + STAGES * STAGE_BYTES + 256) + ((threadIdx.x >> 5) & 3) * (32 * 64);
 
     constexpr int ES = (KIND == KIND_I8) ? 1 : 2;
     constexpr int BK = BKB / ES;  // elements of K per stage
@@ -257,19 +288,24 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             tc_fence_after();
             const int row = tm * BM + q * 32 + lane;
             const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(as * BN);
-            float best = -INFINITY;
-            int best_col = tn * BN;
+            if (KIND != KIND_I8 && p.epi == EPI_ARGMAX) {
+                float best = -INFINITY;
+                int best_col = tn * BN;
 #pragma unroll 1
-            for (int c = 0; c < BN / 16; ++c) {
-                uint32_t v[16];
-                tmem_ld16(lane_addr + c * 16, v);
-                tc_wait_ld();
-                if (KIND != KIND_I8 && p.epi == EPI_ARGMAX) argmax_chunk<TOut>(p, v, tn * BN + c * 16, best, best_col);
-                else epilogue_chunk<KIND, TOut>(p, v, row, tn * BN + c * 16);
-            }
-            if (KIND != KIND_I8 && p.epi == EPI_ARGMAX && row < p.M) {
-                p.part_val[(size_t)row * p.tiles_n + tn] = best;
-                p.part_idx[(size_t)row * p.tiles_n + tn] = best_col;
+                for (int c = 0; c < BN / 16; ++c) {
+                    uint32_t v[16];
+                    tmem_ld16(lane_addr + c * 16, v);
+                    tc_wait_ld();
+                    argmax_chunk<TOut>(p, v, tn * BN + c * 16, best, best_col);
+                }
+                if (row < p.M) {
+                    p.part_val[(size_t)row * p.tiles_n + tn] = best;
+                    p.part_idx[(size_t)row * p.tiles_n + tn] = best_col;
+                }
+            } else {
+#pragma unroll 1
+                for (int gidx = 0; gidx < BN / 64; ++gidx)
+                    epilogue_group<KIND, TOut>(p, stg, lane_addr + gidx * 64, tm * BM + q * 32, tn * BN + gidx * 64, lane);
             }
             tc_fence_before();
             __syncwarp();
@@ -296,7 +332,7 @@ constexpr int BM = 128, PAIR_M = 256, BN = 256, HALF_N = 128, BKB = 128, KBOX = 
 // the issuer then waits and commits once per 2 * 4 MMAs, which halves the issue bubble between stages
 constexpr int A_BYTES = BM * BKB, B_BYTES = HALF_N * BKB, STAGE_BYTES = KBOX * (A_BYTES + B_BYTES);
 constexpr int TMEM_COLS = 512;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 256 + 1024;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 256 + gm::STG_BYTES + 1024;
 }  // namespace gp
 
 template <int KIND, typename TOut>
@@ -312,6 +348,7 @@ gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const AbortCtx actx{abort_flag, p.error};
+    uint32_t* stg = reinterpret_cast<uint32_t*>(sm + STAGES * STAGE_BYTES + 256) + ((threadIdx.x >> 5) & 3) * (32 * 64);
 
     constexpr int ES = (KIND == gm::KIND_I8) ? 1 : 2;
     constexpr int BK = BKB / ES;
@@ -421,19 +458,24 @@ gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             tc_fence_after();
             const int row = tm * PAIR_M + (int)rank * BM + q * 32 + lane;
             const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(as * BN);
-            float best = -INFINITY;
-            int best_col = tn * BN;
+            if (KIND != gm::KIND_I8 && p.epi == gm::EPI_ARGMAX) {
+                float best = -INFINITY;
+                int best_col = tn * BN;
 #pragma unroll 1
-            for (int c = 0; c < BN / 16; ++c) {
-                uint32_t v[16];
-                tmem_ld16(lane_addr + c * 16, v);
-                tc_wait_ld();
-                if (KIND != gm::KIND_I8 && p.epi == gm::EPI_ARGMAX) argmax_chunk<TOut>(p, v, tn * BN + c * 16, best, best_col);
-                else epilogue_chunk<KIND, TOut>(p, v, row, tn * BN + c * 16);
-            }
-            if (KIND != gm::KIND_I8 && p.epi == gm::EPI_ARGMAX && row < p.M) {
-                p.part_val[(size_t)row * p.tiles_n + tn] = best;
-                p.part_idx[(size_t)row * p.tiles_n + tn] = best_col;
+                for (int c = 0; c < BN / 16; ++c) {
+                    uint32_t v[16];
+                    tmem_ld16(lane_addr + c * 16, v);
+                    tc_wait_ld();
+                    argmax_chunk<TOut>(p, v, tn * BN + c * 16, best, best_col);
+                }
+                if (row < p.M) {
+                    p.part_val[(size_t)row * p.tiles_n + tn] = best;
+                    p.part_idx[(size_t)row * p.tiles_n + tn] = best_col;
+                }
+            } else {
+#pragma unroll 1
+                for (int gidx = 0; gidx < BN / 64; ++gidx)
+                    epilogue_group<KIND, TOut>(p, stg, lane_addr + gidx * 64, tm * PAIR_M + (int)rank * BM + q * 32, tn * BN + gidx * 64, lane);
             }
             tc_fence_before();
             __syncwarp();
@@ -506,7 +548,8 @@ static int launch_gemm(const void* a, const void* b, GemmArgs g, cudaStream_t st
 }
 
 static bool epilogue_vectorisable(const GemmArgs& g) {
-    return g.N % 16 == 0 && aligned(g.C, 16) && (!g.bias || aligned(g.bias, 16)) && (!g.residual || aligned(g.residual, 16));
+    return g.N % 8 == 0 && aligned(g.C, 16) && (!g.bias || aligned(g.bias, 16)) && (!g.residual || aligned(g.residual, 16)) &&
+           (!g.sw || aligned(g.sw, 16));
 }
 
 // int8 x int8 -> raw int32 accumulators.  RWKV7_ERR_UNSUPPORTED = shape / alignment not eligible (the caller falls
