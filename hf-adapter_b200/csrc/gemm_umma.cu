@@ -76,19 +76,7 @@ __device__ __forceinline__ void epilogue_group(const GemmArgs& p, uint32_t* stg,
             if (row < p.M) rres[i] = *reinterpret_cast<const Vec8<TOut>*>(res + (size_t)row * p.N + col);
         }
     }
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-        uint32_t v[16];
-        tmem_ld16(taddr + c * 16, v);
-        tc_wait_ld();
-#pragma unroll
-        for (int e = 0; e < 16; e += 4) {
-            const int u = c * 4 + (e >> 2);  // 16-byte unit of this row, 0..15
-            const int pos = (u & 8) | ((u & 7) ^ (lane & 7));
-            *reinterpret_cast<uint4*>(stg + lane * 64 + pos * 4) = make_uint4(v[e], v[e + 1], v[e + 2], v[e + 3]);
-        }
-    }
-    __syncwarp();
+    // so do the tile-constant vectors of this lane's eight columns (bias, channel scales)
     const TOut* bias = reinterpret_cast<const TOut*>(p.bias);
     float bv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, sv[8];
     if (col < p.N) {
@@ -105,6 +93,17 @@ __device__ __forceinline__ void epilogue_group(const GemmArgs& p, uint32_t* stg,
             }
         }
     }
+    {
+        uint32_t v[64];
+        tmem_ld64(taddr, v);
+        tc_wait_ld();
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {  // 16-byte units of this row
+            const int pos = (u & 8) | ((u & 7) ^ (lane & 7));
+            *reinterpret_cast<uint4*>(stg + lane * 64 + pos * 4) = make_uint4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]);
+        }
+    }
+    __syncwarp();
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int r = (lane >> 3) + 4 * i, row = row0 + r;
