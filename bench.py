@@ -250,8 +250,8 @@ def main():
                          "their own communicators, hiding one half's all-reduces under the other half's kernels (0 = off)")
     ap.add_argument("--tp-comm", default="auto", choices=["auto", "peer", "nccl"],
                     help="tp: sum the [B,D] partial outputs with this library's one-kernel sum over peer-mapped memory (plain "
-                         "peer stores, flags, bounded waits) or with NCCL all-reduce; auto = peer up to 4 GPUs (one-shot: every rank "
-                         "sends its whole partial to every peer), NCCL above")
+                         "peer stores, flags, bounded waits) or with NCCL all-reduce; auto = peer at 2 GPUs, NCCL above (one-shot: every "
+                         "rank sends its whole partial to every peer, which stops paying from 4 GPUs up)")
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-scan", action="store_true")
@@ -262,7 +262,9 @@ def main():
     args = ap.parse_args()
     steps, warmup = max(1, args.steps), max(3, args.warmup)
     if args.tp_comm == "auto":
-        args.tp_comm = "peer" if int(os.environ.get("WORLD_SIZE", "1")) <= 4 else "nccl"
+        # measured: the peer kernel's sums are shorter at 2 GPUs (17-18 us against 26-27 us), while from 4 GPUs up the
+        # (P - 1)-fold peer traffic per rank makes the step a little longer than with NCCL (6.05 against 5.93 ms at N = 4)
+        args.tp_comm = "peer" if int(os.environ.get("WORLD_SIZE", "1")) <= 2 else "nccl"
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     L, D, H, Fd, V = SHAPES[args.shape]
