@@ -3,6 +3,7 @@ contract of rwkv-rs/hf-adapter (package ``rwkv7_hf``).  Importing this package l
 library; there is no CPU or PyTorch fallback."""
 from . import _lib  # noqa: F401  (fails loudly when the library is missing)
 from .cache import NativeRWKV7Cache, NativeRWKV7LegacyCache
+from .checkpoint import convert_state_dict, infer_config, load_checkpoint, to_upstream_state_dict, translate_name
 from .gemm import dense_argmax, dense_linear
 from .install import install, uninstall
 from .lora import dense_small, fused_wa_lora, fused_wag_lora, fused_wavg_lora
@@ -25,6 +26,7 @@ from .recurrent import (dplr_chunk_scan, fused_recurrent_output_prepare, fused_r
                         native_fp16_recurrent_should_use, native_fp16_sequence, self_chunk_rwkv7)
 
 from .sharding import shard_spec, shard_state_dict
+from .tokenizer import RWKVWorldTokenizer
 from .state_pool import PoolDecodeGraph, PrefixEntry, RWKV7StatePool, StaleSlotError
 
 NativeRWKV7ForCausalLM = RWKV7ForCausalLM

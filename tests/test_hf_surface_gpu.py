@@ -202,3 +202,23 @@ def test_prefill_graph_replays_equal_eager_prefill():
     torch.testing.assert_close(more, ref_more, rtol=1e-5, atol=1e-5)
     with pytest.raises(ValueError):
         runner.replay(ids[:, :4], None)
+
+
+def test_checkpoint_to_tokens_end_to_end():
+    """Upstream-layout weights -> load_checkpoint (fp16, int4 projections) -> tokenizer batch with left padding ->
+    generate: the padded row continues exactly as the same prompt alone."""
+    g = golden("model_tiny.npz")
+    sd = {k[len("param::"):]: torch.from_numpy(v) for k, v in g.items() if k.startswith("param::")}
+    upstream = hb.to_upstream_state_dict(sd)
+    model = hb.load_checkpoint(upstream, dtype=torch.float16, quant="mm4", min_params=1)
+    assert isinstance(model.model.layers[0].attn.r_proj, hb.MM4Linear) and model.dtype == torch.float16
+    tokens = {i + 1: bytes([i]) for i in range(200)}
+    tokens.update({210: b"the", 211: b" state", 212: b" machine"})
+    tok = hb.RWKVWorldTokenizer(tokens=tokens)
+    batch = tok(["the state", "the state machine runs"], device="cuda")
+    assert batch["attention_mask"][0, 0] == 0 and batch["input_ids"].shape[0] == 2
+    out = model.generate(batch["input_ids"], attention_mask=batch["attention_mask"], max_new_tokens=4)
+    alone = tok(["the state"], device="cuda")
+    out_alone = model.generate(alone["input_ids"], max_new_tokens=4)
+    assert torch.equal(out[0, -4:], out_alone[0, -4:])
+    assert isinstance(tok.decode(out[1].tolist()), str)
