@@ -357,20 +357,24 @@ class RWKV7ForCausalLM(nn.Module):
             else:
                 vl = at.v_lora.lora
                 vf, vg = v_first, _linear(vl[2], _linear(vl[0], xv))
-            w, k, v, kk = _prep.fused_prefill_state_prep(
-                w_raw, k_raw, v_raw, a_pre, at.k_k, at.k_a, v_first=vf, v_gate=vg, num_heads=H, head_dim=N,
-                a_is_raw=True, v_gate_is_raw=True)
-            if i == 0:
-                v_first = v
             a_sig = torch.sigmoid(a_pre)
-            if scan_chunk and T % scan_chunk == 0 and x.dtype == torch.float16:
-                # the tensor-core scan carries an fp32 state; an fp16 cache is widened for the call and rounded back
-                y, new_state = _rec.self_chunk_rwkv7(r, w, k, v, kk, a_sig, state[i].float(), chunk_size=scan_chunk)
+            chunked = bool(scan_chunk) and T % scan_chunk == 0 and x.dtype == torch.float16
+            if chunked:
+                # the tensor-core scan forms the decay from the raw logits itself: no decay tensor is written or read.
+                # It carries an fp32 state; an fp16 cache is widened for the call and rounded back
+                k, v, kk = _prep.fused_prefill_kv_kk_prep(k_raw, v_raw, a_pre, at.k_k, at.k_a, v_first=vf, v_gate=vg, num_heads=H,
+                                                          head_dim=N, a_is_raw=True, v_gate_is_raw=True)
+                y, new_state = _rec.self_chunk_rwkv7(r, w_raw, k, v, kk, a_sig, state[i].float(), chunk_size=scan_chunk, w_is_raw=True)
                 out = _prep.fused_attn_output_prepare(y, r, k, v, g, at.r_k, at.g_norm.weight, at.g_norm.bias,
                                                       num_heads=H, head_dim=N, head_v_dim=N, eps=N * 1e-5)
             else:
+                w, k, v, kk = _prep.fused_prefill_state_prep(
+                    w_raw, k_raw, v_raw, a_pre, at.k_k, at.k_a, v_first=vf, v_gate=vg, num_heads=H, head_dim=N,
+                    a_is_raw=True, v_gate_is_raw=True)
                 out, new_state = _rec.fused_recurrent_scan_output_prepare(
                     r, w, k, v, kk, a_sig, state[i], g, at.r_k, at.g_norm.weight, at.g_norm.bias, eps=N * 1e-5)
+            if i == 0:
+                v_first = v
             state[i].copy_(new_state)
             if self.tp_world == 1:
                 x = _linear(at.o_proj, out, residual=x)  # the residual add rides in the projection's epilogue

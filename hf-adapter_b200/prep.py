@@ -78,9 +78,10 @@ def fused_attn_output_prepare(recurrent_out, r, k, v, g, r_k, group_norm_weight,
 
 
 def fused_prefill_kv_kk_prep(k_raw, v_raw, a, k_k, k_a, *, v_first=None, v_gate=None, num_heads: int, head_dim: int,
-                             force_fallback: bool = False):
+                             force_fallback: bool = False, a_is_raw: bool = False, v_gate_is_raw: bool = False):
     """State prep without the decay (rwkv7_hf/fused_prefill.py:324), the companion of the raw-w scan.
-    Returns ``(k_adjusted, v_interpolated, kk_normalized)`` in the input layout."""
+    Returns ``(k_adjusted, v_interpolated, kk_normalized)`` in the input layout.  ``a_is_raw`` / ``v_gate_is_raw``
+    (extensions, as in ``fused_prefill_state_prep``): the sigmoid of ``a`` / of the v gate is applied in the kernel."""
     no_fallback(force_fallback, "fused_prefill_kv_kk_prep")
     hidden = int(num_heads) * int(head_dim)
     k2, prefix = _flat(k_raw, hidden, "k_raw")
@@ -104,7 +105,8 @@ def fused_prefill_kv_kk_prep(k_raw, v_raw, a, k_k, k_a, *, v_first=None, v_gate=
     k_out, v_out, kk_out = torch.empty_like(k2), torch.empty_like(k2), torch.empty_like(k2)
     _lib.check(_lib.lib.rwkv7_prefill_state_prep(
         None, ptr(k2), ptr(v2), ptr(a2), ptr(kk_c), ptr(ka_c), ptr(vf2), ptr(vg2), None, ptr(k_out), ptr(v_out),
-        ptr(kk_out), rows, int(num_heads), int(head_dim), 0, 0, 0, dt_code(k2), stream_ptr(k2)), "fused_prefill_kv_kk_prep")
+        ptr(kk_out), rows, int(num_heads), int(head_dim), int(bool(a_is_raw)), int(bool(v_gate_is_raw)), 0, dt_code(k2),
+        stream_ptr(k2)), "fused_prefill_kv_kk_prep")
     rs = lambda t: t.reshape(*prefix, hidden)
     return rs(k_out), rs(v_out), rs(kk_out)
 

@@ -312,9 +312,19 @@ def fused_recurrent_scan_state_prep(r, w_raw, k_raw, v_raw, a, state, k_k, k_a, 
 
 
 def self_chunk_rwkv7(r, w_decay, k, v, kk, a_gate, state_native, *, chunk_size: int = 16, w_is_log: bool = False,
-                     safe_gate=None, h_tiles=None):
+                     safe_gate=None, h_tiles=None, w_is_raw: bool = False):
     """Chunked WY/DPLR scan on tensor cores (rwkv7_hf/self_chunk_rwkv7.py:33).  ``T`` must be a
-    multiple of ``chunk_size`` and the head size 64, as in the reference (:56-62)."""
+    multiple of ``chunk_size`` and the head size 64, as in the reference (:56-62).  ``w_is_raw`` (an extension):
+    ``w_decay`` holds the raw decay logits and the kernel forms ``exp(-0.606531 * sigmoid(w))`` itself, as the
+    reference's clamp-w scans do (rwkv7_hf/fused_recurrent_update.py:1420), so no decay tensor is materialised."""
+    if w_is_raw:
+        if w_is_log:
+            raise ValueError("w_is_raw and w_is_log exclude each other")
+        T = int(r.shape[1])
+        if chunk_size not in (16, 32, 64) or T % int(chunk_size):
+            raise ValueError(f"self_chunk_rwkv7 requires chunk_size in (16, 32, 64) dividing T={T}; got {chunk_size}")
+        return _scan("self_chunk_rwkv7", r, w_decay, k, v, kk, a_gate, state_native, 2,
+                     chunk=int(chunk_size) if r.dtype == torch.float16 else 0)
     if w_is_log:
         w_decay = torch.exp(w_decay.float())
     T = int(r.shape[1])
