@@ -430,10 +430,17 @@ def dynamic_a8_quant(x):
     return np.clip(q, -127, 127).astype(np.int8), s
 
 
-def int8_gemm_i32(qa, qw_t):
-    """Exact integer truth of torch._int_mm (native_quant_a8w8.py:413):
-    [rows,K] int8 x [K,out] int8 -> int32 (computed in int64)."""
-    acc = qa.astype(np.int64) @ qw_t.astype(np.int64)
+def int8_gemm_i32(qa, qw_t, exact_int64=False):
+    """Exact integer truth of torch._int_mm (native_quant_a8w8.py:413): [rows,K] int8 x [K,out] int8 -> int32.
+    Computed in float64 through BLAS when every partial sum provably stays below 2^53 (|q| <= 128, so K * 2^14 < 2^53:
+    products and sums of integers of that size are exact in float64), which is hundreds of times faster than NumPy's
+    int64 matmul at projection sizes; ``exact_int64`` (or a longer K) takes the int64 route.  The two agree bit for
+    bit (tests/test_oracle_golden.py)."""
+    K = int(qa.shape[-1])
+    if exact_int64 or K * (1 << 14) >= (1 << 53):
+        acc = qa.astype(np.int64) @ qw_t.astype(np.int64)
+    else:
+        acc = np.rint(qa.astype(np.float64) @ qw_t.astype(np.float64)).astype(np.int64)
     assert np.abs(acc).max(initial=0) < 2 ** 31
     return acc.astype(np.int32)
 

@@ -103,7 +103,7 @@ def test_config3_int8_gemm_4096_rows_bit_exact(Nout):
     assert np.abs(ref).max() < 2 ** 31
     assert np.array_equal(acc.astype(np.int64), ref)
     # a slice of rows through the int64 restatement as well (the two references agree)
-    assert np.array_equal(acc[:16], O.int8_gemm_i32(qa[:16], qw.T))
+    assert np.array_equal(acc[:16], O.int8_gemm_i32(qa[:16], qw.T, exact_int64=True))
     W = (0.02 * rng.standard_normal((Nout, K))).astype(np.float16)
     x = rng.standard_normal((256, K)).astype(np.float16)
     qt, st = O.quantize_weight_per_channel_int8(W)
