@@ -10,7 +10,8 @@
 // B tiles stream.  TMA (128-byte swizzle, 128 bytes of K per box) lands both operands in the layout the MMA
 // descriptors read; a 4-stage ring feeds tcgen05.mma (one issuing thread); TWO accumulators of 256 columns live in
 // tensor memory, so the epilogue warps drain tile i while the tensor pipe already works on tile i + 1.
-// Warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner, warps 2-5 = epilogue (TMEM -> registers -> global).
+// Warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner, warps 2-5 = epilogue (TMEM -> staging -> global); the CTA-pair
+// kernel has a second form with eight epilogue warps for products with a tiny K, which are all epilogue.
 // Ragged M / N / K edges are zero-filled by TMA and masked at the store.  All waits are bounded (umma.cuh).
 // With more than 128 rows the same roles run as CTA pairs on 256 x 256 tiles (second kernel below).
 #include "umma.cuh"
@@ -20,7 +21,9 @@ namespace gm {
 constexpr int BM = 128, BN = 256, BKB = 128, STAGES = 4, THREADS = 192;
 constexpr int A_BYTES = BM * BKB, B_BYTES = BN * BKB, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int TMEM_COLS = 512;
-constexpr int STG_BYTES = 4 * 32 * 64 * 4;  // epilogue staging: per epilogue warp 32 rows x 64 fp32 columns
+constexpr int EPI_WARPS = 4;                        // one per TMEM lane quadrant
+constexpr int STG_WARP_BYTES = 32 * 64 * 4;         // epilogue staging per epilogue warp: 32 rows x 64 fp32 columns
+constexpr int STG_BYTES = EPI_WARPS * STG_WARP_BYTES;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 256 + STG_BYTES + 1024;
 constexpr int GROUP_M = 16;
 enum { KIND_F16 = 0, KIND_BF16 = 1, KIND_I8 = 2 };
@@ -207,7 +210,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&acc_full[a], 1);
-            mbar_init(&acc_empty[a], 4);  // one arrival per epilogue warp
+            mbar_init(&acc_empty[a], EPI_WARPS);  // one arrival per epilogue warp
         }
         *abort_flag = 0;
         mbar_fence_init();
@@ -287,7 +290,9 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             tc_fence_after();
             const int row = tm * BM + q * 32 + lane;
             const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(as * BN);
+            constexpr int half = 0;  // (the CTA-pair kernel splits the columns over two warps per quadrant)
             if (KIND != KIND_I8 && p.epi == EPI_ARGMAX) {
+                if (half == 0) {
                 float best = -INFINITY;
                 int best_col = tn * BN;
 #pragma unroll 1
@@ -300,6 +305,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 if (row < p.M) {
                     p.part_val[(size_t)row * p.tiles_n + tn] = best;
                     p.part_idx[(size_t)row * p.tiles_n + tn] = best_col;
+                }
                 }
             } else {
 #pragma unroll 1
@@ -324,20 +330,27 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 // even CTA issues MMAs of M = 256 that read both CTAs' shared memory and write each CTA's 128 result rows into that
 // CTA's tensor memory.  Barrier protocol: both producers' TMA loads complete on the LEADER's full[s]
 // (armed by the leader with the byte count of both); the leader's commits arrive on empty[s] / acc_full[a] in BOTH
-// CTAs; all eight epilogue warps arrive on the leader's acc_empty[a].  No TMA multicast.
+// CTAs; the epilogue warps of both CTAs arrive on the leader's acc_empty[a].  No TMA multicast.
 namespace gp {
-constexpr int BM = 128, PAIR_M = 256, BN = 256, HALF_N = 128, BKB = 128, KBOX = 2, STAGES = 3, THREADS = 192;
-// a stage holds KBOX consecutive 128-byte K slices of both operands: [A slice 0][A slice 1][B slice 0][B slice 1];
-// the issuer then waits and commits once per 2 * 4 MMAs, which halves the issue bubble between stages
-constexpr int A_BYTES = BM * BKB, B_BYTES = HALF_N * BKB, STAGE_BYTES = KBOX * (A_BYTES + B_BYTES);
+constexpr int BM = 128, PAIR_M = 256, BN = 256, HALF_N = 128, BKB = 128;
+constexpr int A_BYTES = BM * BKB, B_BYTES = HALF_N * BKB;
 constexpr int TMEM_COLS = 512;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 256 + gm::STG_BYTES + 1024;
+// Two forms, chosen by the number of epilogue warps EW.  EW = 4 (one per TMEM lane quadrant): a stage holds two
+// 128-byte K slices of both operands, [A slices][B slices], three stages.  EW = 8 (two per quadrant, each on half of the
+// tile's columns) for products whose K is so short that the epilogue is all there is (the LoRA up-projections of a
+// prefill): the larger staging area leaves room for five one-slice stages.
+constexpr int kbox(int ew) { return ew == 8 ? 1 : 2; }
+constexpr int stages(int ew) { return ew == 8 ? 5 : 3; }
+constexpr int threads(int ew) { return 64 + 32 * ew; }
+constexpr int stage_bytes(int ew) { return kbox(ew) * (A_BYTES + B_BYTES); }
+constexpr int smem_bytes(int ew) { return stages(ew) * stage_bytes(ew) + 256 + ew * gm::STG_WARP_BYTES + 1024; }
 }  // namespace gp
 
-template <int KIND, typename TOut>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(gp::THREADS, 1)
+template <int KIND, typename TOut, int EW>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(gp::threads(EW), 1)
 gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const GemmArgs p) {
     using namespace gp;
+    constexpr int KBOX = kbox(EW), STAGES = stages(EW), STAGE_BYTES = stage_bytes(EW);
     extern __shared__ unsigned char smem_unaligned[];
     unsigned char* sm = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);
     uint64_t* full = reinterpret_cast<uint64_t*>(sm + STAGES * STAGE_BYTES);
@@ -347,7 +360,7 @@ gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const AbortCtx actx{abort_flag, p.error};
-    uint32_t* stg = reinterpret_cast<uint32_t*>(sm + STAGES * STAGE_BYTES + 256) + ((threadIdx.x >> 5) & 3) * (32 * 64);
+    uint32_t* stg = reinterpret_cast<uint32_t*>(sm + STAGES * STAGE_BYTES + 256) + (threadIdx.x >= 64 ? (threadIdx.x >> 5) - 2 : 0) * (32 * 64);
 
     constexpr int ES = (KIND == gm::KIND_I8) ? 1 : 2;
     constexpr int BK = BKB / ES;
@@ -367,7 +380,7 @@ gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&acc_full[a], 1);
-            mbar_init(&acc_empty[a], 8);  // used in the leader only: four epilogue warps of each CTA
+            mbar_init(&acc_empty[a], 2 * EW);  // used in the leader only: the epilogue warps of both CTAs
         }
         *abort_flag = 0;
         mbar_fence_init();
@@ -457,7 +470,10 @@ gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             tc_fence_after();
             const int row = tm * PAIR_M + (int)rank * BM + q * 32 + lane;
             const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(as * BN);
+            constexpr int GPW = 16 / EW;  // 64-column groups per epilogue warp
+            const int half = (warp - 2) >> 2;
             if (KIND != gm::KIND_I8 && p.epi == gm::EPI_ARGMAX) {
+                if (half == 0) {
                 float best = -INFINITY;
                 int best_col = tn * BN;
 #pragma unroll 1
@@ -471,9 +487,10 @@ gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
                     p.part_val[(size_t)row * p.tiles_n + tn] = best;
                     p.part_idx[(size_t)row * p.tiles_n + tn] = best_col;
                 }
+                }
             } else {
 #pragma unroll 1
-                for (int gidx = 0; gidx < BN / 64; ++gidx)
+                for (int gidx = half * GPW; gidx < half * GPW + GPW; ++gidx)
                     epilogue_group<KIND, TOut>(p, stg, lane_addr + gidx * 64, tm * PAIR_M + (int)rank * BM + q * 32, tn * BN + gidx * 64, lane);
             }
             tc_fence_before();
@@ -524,13 +541,21 @@ static int launch_gemm(const void* a, const void* b, GemmArgs g, cudaStream_t st
         if (int e = make_tmap_2d(&tm_b, dt, ES, b, g.N, g.K, gp::HALF_N, BKB / ES, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
         g.tiles_m = (g.M + gp::PAIR_M - 1) / gp::PAIR_M;
         g.tiles_n = (g.N + gp::BN - 1) / gp::BN;
-        auto pk = gemm_umma_pair_kernel<KIND, TOut>;
-        cudaError_t pe = cudaFuncSetAttribute(pk, cudaFuncAttributeMaxDynamicSharedMemorySize, gp::SMEM_BYTES);
-        RWKV7_REQUIRE(pe == cudaSuccess, RWKV7_ERR_CUDA, "gemm: %s", cudaGetErrorString(pe));
         const long long pairs_wanted = (long long)g.tiles_m * g.tiles_n;
         const int pairs_fit = sm_count() / 2;
         const int pairs = (int)(pairs_wanted < pairs_fit ? pairs_wanted : pairs_fit);
-        pk<<<2 * pairs, gp::THREADS, gp::SMEM_BYTES, st>>>(tm_a, tm_b, g);
+        // up to four 128-byte K slices the tile's mainloop is shorter than its epilogue: eight epilogue warps
+        if ((long long)g.K * ES <= 4 * BKB) {
+            auto pk = gemm_umma_pair_kernel<KIND, TOut, 8>;
+            cudaError_t pe = cudaFuncSetAttribute(pk, cudaFuncAttributeMaxDynamicSharedMemorySize, gp::smem_bytes(8));
+            RWKV7_REQUIRE(pe == cudaSuccess, RWKV7_ERR_CUDA, "gemm: %s", cudaGetErrorString(pe));
+            pk<<<2 * pairs, gp::threads(8), gp::smem_bytes(8), st>>>(tm_a, tm_b, g);
+        } else {
+            auto pk = gemm_umma_pair_kernel<KIND, TOut, 4>;
+            cudaError_t pe = cudaFuncSetAttribute(pk, cudaFuncAttributeMaxDynamicSharedMemorySize, gp::smem_bytes(4));
+            RWKV7_REQUIRE(pe == cudaSuccess, RWKV7_ERR_CUDA, "gemm: %s", cudaGetErrorString(pe));
+            pk<<<2 * pairs, gp::threads(4), gp::smem_bytes(4), st>>>(tm_a, tm_b, g);
+        }
         return check_launch("gemm_umma_pair_kernel");
     }
     if (int e = make_tmap_2d(&tm_a, dt, ES, a, g.M, g.K, BM, BKB / ES, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
