@@ -248,7 +248,7 @@ def main():
     ap.add_argument("--tp-overlap-rows", type=int, default=0,
                     help="tp: batches of at least twice this many rows per rank decode as two halves on two streams with "
                          "their own communicators, hiding one half's all-reduces under the other half's kernels (0 = off)")
-    ap.add_argument("--tp-comm", default="auto", choices=["auto", "peer", "nccl"],
+    ap.add_argument("--tp-comm", default="auto", choices=["auto", "peer", "peer_rows", "nccl"],
                     help="tp: sum the [B,D] partial outputs with this library's one-kernel sum over peer-mapped memory (plain "
                          "peer stores, flags, bounded waits) or with NCCL all-reduce; auto = peer at 2 GPUs, NCCL above (one-shot: every "
                          "rank sends its whole partial to every peer, which stops paying from 4 GPUs up)")
@@ -437,7 +437,9 @@ def main():
         B, shard = args.batch * world, world
         parallelism = (f"tp{world}: heads, recurrent state, projections and the head's vocabulary sharded, global batch {B} on "
                        "every rank, two sums of the [B,D] partial outputs per layer inside the decode graph ("
-                       + ("this library's kernel over peer-mapped memory" if args.tp_comm == "peer" else "NCCL all-reduce") + ")"
+                       + ({"peer": "this library's kernel over peer-mapped memory",
+                           "peer_rows": "taken over peer-mapped memory inside the LayerNorm / token-shift kernels that consume them"}
+                          .get(args.tp_comm, "NCCL all-reduce")) + ")"
                        + (f", batch decoded as two halves of {B // 2} rows on two streams / communicators"
                           if args.tp_overlap_rows and B >= 2 * args.tp_overlap_rows else "")
                        + "; the step ends in the greedy token (local arg-max + one [B,2] all-gather)")

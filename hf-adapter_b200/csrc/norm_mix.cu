@@ -350,3 +350,392 @@ extern "C" int rwkv7_seq_shift_mix(const void* x, const void* initial_prev, cons
     });
     return RWKV7_OK;
 }
+
+namespace rwkv7 {
+
+unsigned int* kernel_error_word();  // capi.cu
+
+// ---- tensor-parallel forms: the sum over ranks happens inside the row kernel -----------------------------------------
+// Under head-sharded tensor parallelism the [rows, D] outputs of o_proj and ffn.value are partial sums, and the kernel
+// that consumes each of them is one of the two row kernels above.  These forms take this rank's PARTIAL instead of the
+// summed tensor.  The CTA of row r
+//   1. stores its partial row into slot [rank] of every peer's inbox (plain 16-byte peer stores) and, after a
+//      system-scope fence, writes the call number into flag [rank][r] of every peer,
+//   2. waits (bounded) until its own flags [s][r] show the call number for every peer s,
+//   3. adds the P rows in rank order in fp32 and rounds the sum to the storage type (bit for bit what the stand-alone
+//      all-reduce kernel stores), and carries on with LayerNorm and the mixes from registers.
+// One launch and one pass over the row replace the all-reduce kernel, its [rows, D] round trip and a kernel boundary.
+// The protocol (two inbox buffers alternating by call number, a call counter on the device, rank-ordered sums, error
+// word 7 when a wait runs out) is the all-reduce kernel's; the flags are per ROW here, so the communicator memory is
+// its own.  A CTA waits for the same row's CTA on every peer: the host admits only row counts whose CTAs are all
+// resident at once, so no CTA waits for one that cannot start.
+constexpr int kTpMaxRanks = 8;
+constexpr unsigned kErrPeerWait = 7;
+
+struct TpRowsArgs {
+    const void* partial;            // this rank's [rows, D] partial sums
+    void* inbox[kTpMaxRanks];       // per rank: [2][P][slot_elems] values
+    uint32_t* flags[kTpMaxRanks];   // per rank: [2][P][max_rows]
+    uint32_t* counters;             // local: [0] completed calls, [1] CTAs of the current call that are through
+    unsigned int* error;
+    int rank, world, max_rows;
+    long long slot_elems;
+    unsigned long long wait_ns;
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Steps 1-3 for the row of this CTA: x[i][e] receives the rounded sum.  Returns the call number, or 0 when a wait ran
+// out (the caller skips its stores and still calls tp_rows_finish).  T is a 2-byte type.
+template <typename T, int NV>
+__device__ __forceinline__ uint32_t tp_rows_exchange(const TpRowsArgs& t, size_t row, int D, float (&x)[kNMMaxVec][8],
+                                                     uint32_t* s_epoch, int* s_abort) {
+    static_assert(sizeof(T) == 2, "the inbox holds 2-byte values");
+    const int tid = threadIdx.x, nvec = D / 8;
+    if (tid == 0) {
+        *s_epoch = *reinterpret_cast<volatile uint32_t*>(t.counters) + 1u;
+        *s_abort = 0;
+    }
+    __syncthreads();
+    const uint32_t e = *s_epoch;
+    const long long buf = (long long)(e & 1u);
+    const uint4* mine = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(t.partial) + row * D);
+    uint4 own[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int vi = tid + i * kNMThreads;
+        if (vi < nvec) own[i] = mine[vi];
+    }
+    for (int s = 1; s < t.world; ++s) {
+        const int peer = (t.rank + s) % t.world;
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<T*>(t.inbox[peer]) + (buf * t.world + t.rank) * t.slot_elems + row * D);
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int vi = tid + i * kNMThreads;
+            if (vi < nvec) dst[vi] = own[i];
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < t.world && tid != t.rank) {
+        st_release_sys_u32(t.flags[tid] + (buf * t.world + t.rank) * t.max_rows + row, e);
+        const uint32_t* f = t.flags[t.rank] + (buf * t.world + tid) * t.max_rows + row;
+        const unsigned long long t0 = timer_ns();
+        while ((int32_t)(ld_acquire_sys_u32(f) - e) < 0) {
+            if (timer_ns() - t0 > t.wait_ns) {
+                *s_abort = 1;
+                atomicCAS(t.error, 0u, kErrPeerWait);
+                break;
+            }
+            __nanosleep(32);
+        }
+    }
+    __syncthreads();
+    if (*s_abort) return 0u;
+    const T* box = reinterpret_cast<const T*>(t.inbox[t.rank]) + buf * t.world * t.slot_elems + row * D;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int vi = tid + i * kNMThreads;
+        if (vi < nvec) {
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int s = 0; s < t.world; ++s) {
+                // inbox rows were written by other GPUs: read them past L1, which is not coherent with peer writes
+                const uint4 raw = s == t.rank ? own[i] : __ldcg(reinterpret_cast<const uint4*>(box + (long long)s * t.slot_elems) + vi);
+                const T* h = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+                for (int q = 0; q < 8; ++q) acc[q] += to_f<T>(h[q]);
+            }
+#pragma unroll
+            for (int q = 0; q < 8; ++q) x[i][q] = round_to<T>(acc[q]);
+        }
+    }
+    return e;
+}
+
+// The call counter advances when the last CTA of the launch is through (every CTA read it at its start).
+__device__ __forceinline__ void tp_rows_finish(const TpRowsArgs& t, uint32_t* s_epoch) {
+    __syncthreads();
+    if (threadIdx.x == 0 && atomicAdd(t.counters + 1, 1u) == gridDim.x - 1) {
+        t.counters[1] = 0;
+        __threadfence();
+        *reinterpret_cast<volatile uint32_t*>(t.counters) = *s_epoch;
+    }
+}
+
+template <typename T, int NV>
+__device__ __forceinline__ void row_stats(RowStats<T>& rs, int D, float eps, float* red) {
+    const int nvec = D / 8;
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+        if (threadIdx.x + i * kNMThreads < nvec) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) s += rs.x[i][e];
+        }
+    rs.mean = block_sum(s, red) / (float)D;
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+        if (threadIdx.x + i * kNMThreads < nvec) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float d = rs.x[i][e] - rs.mean;
+                q += d * d;
+            }
+        }
+    rs.rstd = rsqrtf(block_sum(q, red) / (float)D + eps);
+}
+
+// attn_norm_mix6 of (sum over ranks of partial); the summed row is also stored to x_out (the residual stream).
+template <typename T, int NV>
+__global__ void __launch_bounds__(kNMThreads) tp_attn_norm_mix6_kernel(const Mix6Args p, const TpRowsArgs t, void* x_out) {
+    __shared__ float red[32];
+    __shared__ uint32_t s_epoch;
+    __shared__ int s_abort;
+    const size_t row = blockIdx.x;
+    const int D = p.D, nvec = D / 8;
+    Raw8<T> cw[NV], cb[NV], cm[6][NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int vi = threadIdx.x + i * kNMThreads;
+        if (vi < nvec) {
+            cw[i] = ld_raw8(reinterpret_cast<const T*>(p.nw) + vi * 8);
+            cb[i] = ld_raw8(reinterpret_cast<const T*>(p.nb) + vi * 8);
+#pragma unroll
+            for (int m = 0; m < 6; ++m) cm[m][i] = ld_raw8(reinterpret_cast<const T*>(p.mix[m]) + vi * 8);
+        }
+    }
+    grid_dependency_wait();
+    if (threadIdx.x == 0) grid_launch_dependents();
+    RowStats<T> rs;
+    if (tp_rows_exchange<T, NV>(t, row, D, rs.x, &s_epoch, &s_abort)) {
+        row_stats<T, NV>(rs, D, p.eps, red);
+        T* prev = reinterpret_cast<T*>(p.prev) + (p.slots ? (size_t)__ldg(p.slots + row) : row) * D;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int vi = threadIdx.x + i * kNMThreads;
+            if (vi < nvec) {
+                float w[8], b[8], pv[8], h[8], d[8];
+                cvt8(cw[i], w);
+                cvt8(cb[i], b);
+                load8(prev + vi * 8, pv);
+                store8(reinterpret_cast<T*>(x_out) + row * D + vi * 8, rs.x[i]);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    h[e] = (rs.x[i][e] - rs.mean) * rs.rstd * w[e] + b[e];
+                    d[e] = pv[e] - h[e];
+                }
+                store8(prev + vi * 8, h);
+#pragma unroll
+                for (int m = 0; m < 6; ++m) {
+                    float mx[8], o[8];
+                    cvt8(cm[m][i], mx);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) o[e] = h[e] + d[e] * mx[e];
+                    store8(reinterpret_cast<T*>(p.out[m]) + row * D + vi * 8, o);
+                }
+            }
+        }
+    }
+    tp_rows_finish(t, &s_epoch);
+}
+
+// ffn_add_norm_mix with attn = sum over ranks of partial: res_out = res + attn (normalised from the fp32 sum).
+template <typename T, int NV>
+__global__ void __launch_bounds__(kNMThreads) tp_ffn_add_norm_mix_kernel(const FfnMixArgs p, const TpRowsArgs t) {
+    __shared__ float red[32];
+    __shared__ uint32_t s_epoch;
+    __shared__ int s_abort;
+    const size_t row = blockIdx.x;
+    const int D = p.D, nvec = D / 8;
+    Raw8<T> cw[NV], cb[NV], cm[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int vi = threadIdx.x + i * kNMThreads;
+        if (vi < nvec) {
+            cw[i] = ld_raw8(reinterpret_cast<const T*>(p.nw) + vi * 8);
+            cb[i] = ld_raw8(reinterpret_cast<const T*>(p.nb) + vi * 8);
+            cm[i] = ld_raw8(reinterpret_cast<const T*>(p.mix) + vi * 8);
+        }
+    }
+    grid_dependency_wait();
+    if (threadIdx.x == 0) grid_launch_dependents();
+    RowStats<T> rs;
+    if (tp_rows_exchange<T, NV>(t, row, D, rs.x, &s_epoch, &s_abort)) {
+        const T* res = reinterpret_cast<const T*>(p.res) + row * D;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int vi = threadIdx.x + i * kNMThreads;
+            if (vi < nvec) {
+                float r[8];
+                load8(res + vi * 8, r);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) rs.x[i][e] = r[e] + rs.x[i][e];
+                store8(reinterpret_cast<T*>(p.res_out) + row * D + vi * 8, rs.x[i]);
+            }
+        }
+        row_stats<T, NV>(rs, D, p.eps, red);
+        T* prev = reinterpret_cast<T*>(p.prev) + (p.slots ? (size_t)__ldg(p.slots + row) : row) * D;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int vi = threadIdx.x + i * kNMThreads;
+            if (vi < nvec) {
+                float w[8], b[8], h[8], pv[8], mx[8], o[8];
+                cvt8(cw[i], w);
+                cvt8(cb[i], b);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) h[e] = (rs.x[i][e] - rs.mean) * rs.rstd * w[e] + b[e];
+                load8(prev + vi * 8, pv);
+                cvt8(cm[i], mx);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] = h[e] + (pv[e] - h[e]) * mx[e];
+                store8(prev + vi * 8, h);
+                store8(reinterpret_cast<T*>(p.mixed) + row * D + vi * 8, o);
+            }
+        }
+    }
+    tp_rows_finish(t, &s_epoch);
+}
+
+// Largest row count whose CTAs are all resident at once on this device (0 on error): the admission bound of the
+// tensor-parallel forms.
+template <typename K>
+static int resident_rows(K kernel) {
+    int dev = 0, sms = 0, per_sm = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kNMThreads, 0) != cudaSuccess) return 0;
+    return sms * per_sm;
+}
+
+static int fill_tp_args(const char* what, TpRowsArgs& t, const void* partial, void* const* inbox_ptrs, void* const* flag_ptrs,
+                        void* counters, int rank, int world, int rows, int D, int max_rows, long long slot_elems, int wait_ms) {
+    RWKV7_REQUIRE(world >= 2 && world <= kTpMaxRanks && rank >= 0 && rank < world, RWKV7_ERR_INVALID,
+                  "%s: world must be 2..%d and rank inside it (world=%d rank=%d)", what, kTpMaxRanks, world, rank);
+    RWKV7_REQUIRE(partial && inbox_ptrs && flag_ptrs && counters, RWKV7_ERR_INVALID, "%s: null pointer", what);
+    RWKV7_REQUIRE(rows <= max_rows && slot_elems % 8 == 0 && (long long)rows * D <= slot_elems, RWKV7_ERR_WORKSPACE,
+                  "%s: %d x %d values do not fit the communicator (%d rows, slots of %lld)", what, rows, D, max_rows, slot_elems);
+    RWKV7_REQUIRE(aligned(partial, 16) && aligned(counters, 8), RWKV7_ERR_ALIGN, "%s: unaligned pointer", what);
+    t.partial = partial;
+    for (int r = 0; r < world; ++r) {
+        RWKV7_REQUIRE(inbox_ptrs[r] && flag_ptrs[r] && aligned(inbox_ptrs[r], 16) && aligned(flag_ptrs[r], 4), RWKV7_ERR_INVALID,
+                      "%s: bad inbox / flag pointer of rank %d", what, r);
+        t.inbox[r] = inbox_ptrs[r];
+        t.flags[r] = reinterpret_cast<uint32_t*>(flag_ptrs[r]);
+    }
+    t.counters = reinterpret_cast<uint32_t*>(counters);
+    t.error = kernel_error_word();
+    RWKV7_REQUIRE(t.error != nullptr, RWKV7_ERR_CUDA, "%s: cannot resolve the device error word", what);
+    t.rank = rank;
+    t.world = world;
+    t.max_rows = max_rows;
+    t.slot_elems = slot_elems;
+    t.wait_ns = (unsigned long long)(wait_ms > 0 ? wait_ms : 2000) * 1000000ull;
+    return RWKV7_OK;
+}
+
+}  // namespace rwkv7
+
+using namespace rwkv7;
+
+// vectors per thread for a row of D values: rows of <= 4096 values keep half the registers, so two CTAs share an SM
+static int tp_vectors(int D) { return D <= 8 * kNMThreads ? 1 : (D <= 16 * kNMThreads ? 2 : 4); }
+
+template <typename T>
+static int tp_mix6_launch(int nv, int rows, cudaStream_t st, const Mix6Args& p, const TpRowsArgs& t, void* x_out) {
+#define RWKV7_TP_MIX6(NV)                                                                                         \
+    {                                                                                                             \
+        RWKV7_REQUIRE(rows <= resident_rows(tp_attn_norm_mix6_kernel<T, NV>), RWKV7_ERR_UNSUPPORTED,              \
+                      "tp_attn_norm_mix6: %d rows are more than are resident at once", rows);                     \
+        launch_programmatic(tp_attn_norm_mix6_kernel<T, NV>, dim3(rows), dim3(kNMThreads), 0, st, p, t, x_out);   \
+    }
+    if (nv == 1) RWKV7_TP_MIX6(1) else if (nv == 2) RWKV7_TP_MIX6(2) else RWKV7_TP_MIX6(4)
+#undef RWKV7_TP_MIX6
+    return check_launch("tp_attn_norm_mix6_kernel");
+}
+
+template <typename T>
+static int tp_ffn_launch(int nv, int rows, cudaStream_t st, const FfnMixArgs& p, const TpRowsArgs& t) {
+#define RWKV7_TP_FFN(NV)                                                                                          \
+    {                                                                                                             \
+        RWKV7_REQUIRE(rows <= resident_rows(tp_ffn_add_norm_mix_kernel<T, NV>), RWKV7_ERR_UNSUPPORTED,            \
+                      "tp_ffn_add_norm_mix: %d rows are more than are resident at once", rows);                   \
+        launch_programmatic(tp_ffn_add_norm_mix_kernel<T, NV>, dim3(rows), dim3(kNMThreads), 0, st, p, t);        \
+    }
+    if (nv == 1) RWKV7_TP_FFN(1) else if (nv == 2) RWKV7_TP_FFN(2) else RWKV7_TP_FFN(4)
+#undef RWKV7_TP_FFN
+    return check_launch("tp_ffn_add_norm_mix_kernel");
+}
+
+extern "C" int rwkv7_tp_rows_resident(int D, int dtype) {
+    if (D <= 0 || D % 8 || D > 8 * kNMThreads * kNMMaxVec) return 0;
+    const int nv = tp_vectors(D);
+    int a = 0, b = 0;
+    if (dtype == RWKV7_F16) {
+        a = nv == 1 ? resident_rows(tp_attn_norm_mix6_kernel<__half, 1>) : nv == 2 ? resident_rows(tp_attn_norm_mix6_kernel<__half, 2>) : resident_rows(tp_attn_norm_mix6_kernel<__half, 4>);
+        b = nv == 1 ? resident_rows(tp_ffn_add_norm_mix_kernel<__half, 1>) : nv == 2 ? resident_rows(tp_ffn_add_norm_mix_kernel<__half, 2>) : resident_rows(tp_ffn_add_norm_mix_kernel<__half, 4>);
+    } else if (dtype == RWKV7_BF16) {
+        a = nv == 1 ? resident_rows(tp_attn_norm_mix6_kernel<__nv_bfloat16, 1>) : nv == 2 ? resident_rows(tp_attn_norm_mix6_kernel<__nv_bfloat16, 2>) : resident_rows(tp_attn_norm_mix6_kernel<__nv_bfloat16, 4>);
+        b = nv == 1 ? resident_rows(tp_ffn_add_norm_mix_kernel<__nv_bfloat16, 1>) : nv == 2 ? resident_rows(tp_ffn_add_norm_mix_kernel<__nv_bfloat16, 2>) : resident_rows(tp_ffn_add_norm_mix_kernel<__nv_bfloat16, 4>);
+    }
+    return a < b ? a : b;
+}
+
+extern "C" int rwkv7_tp_attn_norm_mix6(const void* partial, void* x_out, void* prev, const int32_t* slot_ids,
+                                       const void* norm_w, const void* norm_b, const void* const mixes[6],
+                                       void* const outs[6], void* const* inbox_ptrs, void* const* flag_ptrs, void* counters,
+                                       int rank, int world, int rows, int D, int max_rows, long long slot_elems, float eps,
+                                       int wait_ms, int dtype, void* stream) {
+    if (int e = check_row_shape("tp_attn_norm_mix6", rows, D)) return e;
+    RWKV7_REQUIRE(dtype == RWKV7_F16 || dtype == RWKV7_BF16, RWKV7_ERR_UNSUPPORTED, "tp_attn_norm_mix6: fp16 or bf16");
+    RWKV7_REQUIRE(x_out && prev && norm_w && norm_b && mixes && outs, RWKV7_ERR_INVALID, "tp_attn_norm_mix6: null pointer");
+    Mix6Args p{nullptr, norm_w, norm_b, prev, {}, {}, D, eps, slot_ids};
+    for (int m = 0; m < 6; ++m) {
+        RWKV7_REQUIRE(mixes[m] && outs[m] && aligned(mixes[m], 16) && aligned(outs[m], 16), RWKV7_ERR_INVALID,
+                      "tp_attn_norm_mix6: bad mix / out pointer %d", m);
+        p.mix[m] = mixes[m];
+        p.out[m] = outs[m];
+    }
+    const void* ptrs[] = {x_out, prev, norm_w, norm_b};
+    for (const void* q : ptrs) RWKV7_REQUIRE(aligned(q, 16), RWKV7_ERR_ALIGN, "tp_attn_norm_mix6: unaligned pointer");
+    TpRowsArgs t{};
+    if (int e = fill_tp_args("tp_attn_norm_mix6", t, partial, inbox_ptrs, flag_ptrs, counters, rank, world, rows, D, max_rows,
+                             slot_elems, wait_ms))
+        return e;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return dtype == RWKV7_F16 ? tp_mix6_launch<__half>(tp_vectors(D), rows, st, p, t, x_out)
+                              : tp_mix6_launch<__nv_bfloat16>(tp_vectors(D), rows, st, p, t, x_out);
+}
+
+extern "C" int rwkv7_tp_ffn_add_norm_mix(const void* residual, const void* partial, void* prev, const int32_t* slot_ids,
+                                         const void* norm_w, const void* norm_b, const void* mix, void* residual_out,
+                                         void* mixed, void* const* inbox_ptrs, void* const* flag_ptrs, void* counters,
+                                         int rank, int world, int rows, int D, int max_rows, long long slot_elems, float eps,
+                                         int wait_ms, int dtype, void* stream) {
+    if (int e = check_row_shape("tp_ffn_add_norm_mix", rows, D)) return e;
+    RWKV7_REQUIRE(dtype == RWKV7_F16 || dtype == RWKV7_BF16, RWKV7_ERR_UNSUPPORTED, "tp_ffn_add_norm_mix: fp16 or bf16");
+    RWKV7_REQUIRE(residual && prev && norm_w && norm_b && mix && residual_out && mixed, RWKV7_ERR_INVALID,
+                  "tp_ffn_add_norm_mix: null pointer");
+    const void* ptrs[] = {residual, prev, norm_w, norm_b, mix, residual_out, mixed};
+    for (const void* q : ptrs) RWKV7_REQUIRE(aligned(q, 16), RWKV7_ERR_ALIGN, "tp_ffn_add_norm_mix: unaligned pointer");
+    FfnMixArgs p{residual, nullptr, norm_w, norm_b, mix, prev, residual_out, mixed, D, eps, slot_ids};
+    TpRowsArgs t{};
+    if (int e = fill_tp_args("tp_ffn_add_norm_mix", t, partial, inbox_ptrs, flag_ptrs, counters, rank, world, rows, D, max_rows,
+                             slot_elems, wait_ms))
+        return e;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return dtype == RWKV7_F16 ? tp_ffn_launch<__half>(tp_vectors(D), rows, st, p, t)
+                              : tp_ffn_launch<__nv_bfloat16>(tp_vectors(D), rows, st, p, t);
+}

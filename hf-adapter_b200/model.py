@@ -192,7 +192,9 @@ class RWKV7ForCausalLM(nn.Module):
         come from a local arg-max and one tiny exchange.  ``tp_overlap_rows`` > 0: decode batches of at least twice
         that many rows run as two halves on two streams with their own communicators, so one half's all-reduces hide
         under the other half's kernels.  ``tp_comm``: "nccl" sums the partial outputs with the framework's all-reduce,
-        "peer" with this library's one-kernel sum over peer-mapped memory (fp16, up to 1024 rows; larger calls use NCCL)."""
+        "peer" with this library's one-kernel sum over peer-mapped memory (fp16, up to 1024 rows; larger calls use NCCL),
+        "peer_rows" moves the sums of a decode step into the LayerNorm / token-shift kernels that consume them (as many
+        rows as those kernels keep resident at once; otherwise as "peer")."""
         super().__init__()
         if state_dtype not in (torch.float32, torch.float16):
             raise ValueError("state_dtype must be torch.float32 or torch.float16")
@@ -208,9 +210,10 @@ class RWKV7ForCausalLM(nn.Module):
         if self.tp_shard_head and config.vocab_size % self.tp_world:
             raise ValueError("vocab_size must be divisible by the tensor-parallel world size to shard the head")
         self.lm_head = nn.Linear(config.hidden_size, config.vocab_size // (self.tp_world if self.tp_shard_head else 1), bias=False)
-        if tp_comm not in ("nccl", "peer"):
-            raise ValueError("tp_comm must be 'nccl' or 'peer'")
+        if tp_comm not in ("nccl", "peer", "peer_rows"):
+            raise ValueError("tp_comm must be 'nccl', 'peer' or 'peer_rows'")
         self.tp_comm = tp_comm
+        self._peer_rows = {}  # lane -> PeerRowSum (the sums taken inside the row kernels; same set-up rule)
         self._peer_ar = {}  # lane -> PeerAllReduce (created on first use: a collective set-up, outside graph capture)
         self.tp_overlap_rows = int(tp_overlap_rows) if self.tp_world > 1 else 0
         # the second half of an overlapped step needs a communicator of its own: two collectives of ONE communicator
@@ -252,7 +255,7 @@ class RWKV7ForCausalLM(nn.Module):
         if self.tp_world == 1 or self.tp_group is False:
             return t
         rows = t.numel() // int(t.shape[-1])
-        if self.tp_comm == "peer" and t.dtype == torch.float16 and t.is_contiguous() and rows <= self.PEER_MAX_ROWS:
+        if self.tp_comm in ("peer", "peer_rows") and t.dtype == torch.float16 and t.is_contiguous() and rows <= self.PEER_MAX_ROWS:
             ar = self._peer_ar.get(lane)
             if ar is None or rows * int(t.shape[-1]) > ar.slot_elems or ar.width != int(t.shape[-1]):
                 from .tp_comm import PeerAllReduce
@@ -262,6 +265,27 @@ class RWKV7ForCausalLM(nn.Module):
             return ar.all_reduce(t, out=t)
         torch.distributed.all_reduce(t, group=self._lane_group(lane))
         return t
+
+    def _row_sum(self, partial, lane: int = 0):
+        """The communicator whose row kernels sum ``partial [rows, D]`` over the ranks themselves, or None when the sum
+        has to run as its own all-reduce (another ``tp_comm``, or more rows than those kernels keep resident at once;
+        every rank decides alike because the answer depends on the shape alone)."""
+        if self.tp_comm != "peer_rows" or self.tp_world == 1 or self.tp_group is False:
+            return None
+        from .tp_comm import PeerRowSum
+        rows, width = int(partial.shape[0]), int(partial.shape[1])
+        limit = PeerRowSum.resident_rows(width, partial.dtype)
+        if self.tp_overlap_rows:
+            limit //= 2  # two half-batches run side by side: the row kernels of both must fit together
+        if not partial.is_contiguous() or rows > min(limit, self.PEER_MAX_ROWS):
+            return None
+        comm = self._peer_rows.get(lane)
+        if comm is None or rows > comm.max_rows or comm.width != width or comm.dtype != partial.dtype:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("the peer row-sum buffers must exist before graph capture (run one eager step first)")
+            comm = self._peer_rows[lane] = PeerRowSum(self.tp_group, min(max(rows, 64), limit), width, partial.device,
+                                                      partial.dtype)
+        return comm
 
     def _lane_group(self, lane: int):
         return self._tp_group_b if (lane and self._tp_group_b is not None) else self.tp_group
@@ -320,7 +344,8 @@ class RWKV7ForCausalLM(nn.Module):
         state, xpa, xpf, v_first, elapsed_t = tensors
         x = inputs_embeds if inputs_embeds is not None else F.embedding(ids.reshape(-1), self.model.embeddings.weight)
         elapsed = elapsed_t if state[0].dtype == torch.float16 else None
-        ctx = _pk.StepContext(self._side_stream, self._all_reduce, self.tp_world, self.tp_rank, lane, stream_base)
+        ctx = _pk.StepContext(self._side_stream, self._all_reduce, self.tp_world, self.tp_rank, lane, stream_base,
+                              row_sum=self._row_sum)
         packs, _, _, _ = _pk.extract_graph_packs(self)
         x, *_ = _pk.step_batched(self, x, state, xpa, xpf, v_first, packs, fp16_elapsed=elapsed, context=ctx)
         xn = _nm.layer_norm(x, self.model.norm.weight, self.model.norm.bias)

@@ -168,12 +168,18 @@ class StepContext:
     GPU with one side stream per device."""
 
     def __init__(self, side_stream=None, all_reduce=None, tp_world: int = 1, tp_rank: int = 0, lane: int = 0,
-                 stream_base: int = 0, slot_ids=None):
+                 stream_base: int = 0, slot_ids=None, row_sum=None):
         # slot_ids (int32 [B] on the device): the recurrent buffers handed to the layer step are slot pools
         # ([capacity, ...]) and batch row b lives in pool row slot_ids[b]
         self.slot_ids = slot_ids
         self._side_stream = side_stream
         self._all_reduce = all_reduce
+        # row_sum(partial, lane) -> tp_comm.PeerRowSum or None: the communicator whose row kernels take the sum over
+        # ranks in themselves.  defer_sum (set by step_batched between layers): the layer may return its UNSUMMED
+        # ffn.value partial and raise `pending`; the next layer's first kernel then sums it.
+        self._row_sum = row_sum
+        self.defer_sum = False
+        self.pending = False
         self.tp_world, self.tp_rank, self.lane, self.stream_base = int(tp_world), int(tp_rank), int(lane), int(stream_base)
         self._own = {}
 
@@ -187,6 +193,11 @@ class StepContext:
 
     def all_reduce(self, t):
         return t if self._all_reduce is None else self._all_reduce(t, self.lane)
+
+    def row_sum(self, partial):
+        if self.tp_world == 1 or self._row_sum is None or partial.dim() != 2:
+            return None
+        return self._row_sum(partial, self.lane)
 
 
 _DEFAULT_CONTEXT = StepContext()
@@ -214,8 +225,18 @@ def block_ip_batched(x, state, xpa, xpf, v_first, p, sparse_ffn_out=None, fp16_e
     if has_pre:
         x = _nm.layer_norm(x, pre_w, pre_b)
     slots = ctx.slot_ids
-    xr, xw, xk, xv, xa, xg = _nm.fused_attn_norm_mix6_decode(x, xpa, an_w, an_b, x_r, x_w, x_k, x_v, x_a, x_g,
-                                                             slot_ids=slots)
+    rows_comm = ctx.row_sum(x)
+    if ctx.pending and rows_comm is None:
+        ctx.pending = False
+        x = ctx.all_reduce(x)
+    if ctx.pending:
+        # x is the previous layer's ffn.value partial: the sum over ranks happens inside this kernel
+        ctx.pending = False
+        x, (xr, xw, xk, xv, xa, xg) = rows_comm.attn_norm_mix6(x, xpa, an_w, an_b, (x_r, x_w, x_k, x_v, x_a, x_g),
+                                                              slot_ids=slots)
+    else:
+        xr, xw, xk, xv, xa, xg = _nm.fused_attn_norm_mix6_decode(x, xpa, an_w, an_b, x_r, x_w, x_k, x_v, x_a, x_g,
+                                                                 slot_ids=slots)
     # The LoRA chain does not depend on r/k/v: it runs on a side stream (a parallel branch of the decode graph once
     # captured) and joins before the recurrence.
     main = torch.cuda.current_stream(x.device)
@@ -261,12 +282,19 @@ def block_ip_batched(x, state, xpa, xpf, v_first, p, sparse_ffn_out=None, fp16_e
         r, w_raw, k, v, a_pre, state, g, k_k, k_a, r_k, gn_w, gn_b, eps=float(eps), new_state=state, w_bias=w0, a_bias=a0,
         a_is_raw=True, state_prefetch=True, elapsed=elapsed,
         advance_elapsed=bool(fp16_advance_elapsed) and elapsed is not None, slot_ids=slots, **extra)
-    attn = ctx.all_reduce(apply_linear(Ow, out))
-    x, mixed = _nm.fused_ffn_add_norm_mix_decode(x, attn, xpf, fn_w, fn_b, fx_k, slot_ids=slots)
+    attn = apply_linear(Ow, out)
+    if rows_comm is not None:
+        x, mixed = rows_comm.ffn_add_norm_mix(x, attn, xpf, fn_w, fn_b, fx_k, slot_ids=slots)
+    else:
+        x, mixed = _nm.fused_ffn_add_norm_mix_decode(x, ctx.all_reduce(attn), xpf, fn_w, fn_b, fx_k, slot_ids=slots)
     hidden = apply_linear(fK, mixed, relu2=True)
     if ctx.tp_world > 1:
         # the residual rides in rank 0's partial sum (the projection's add epilogue): no extra add kernel
-        return ctx.all_reduce(apply_linear(fV, hidden, residual=x if ctx.tp_rank == 0 else None))
+        part = apply_linear(fV, hidden, residual=x if ctx.tp_rank == 0 else None)
+        if rows_comm is not None and ctx.defer_sum:
+            ctx.pending = True
+            return part
+        return ctx.all_reduce(part)
     return apply_linear(fV, hidden, residual=x)
 
 
@@ -276,6 +304,8 @@ def step_batched(model, x, state, xpa, xpf, v_first, packs, *, fp16_elapsed=None
     reference's argument order)."""
     last = len(packs) - 1
     for li, p in enumerate(packs):
+        if context is not None:
+            context.defer_sum = li != last  # between layers the sum moves into the next layer's first kernel
         x = block_ip_batched(x, state[li], xpa[li], xpf[li], v_first, p, fp16_elapsed=fp16_elapsed,
                              fp16_advance_elapsed=li == last, context=context)
     return x, state, xpa, xpf, v_first
