@@ -359,58 +359,75 @@ unsigned int* kernel_error_word();  // capi.cu
 // Under head-sharded tensor parallelism the [rows, D] outputs of o_proj and ffn.value are partial sums, and the kernel
 // that consumes each of them is one of the two row kernels above.  These forms take this rank's PARTIAL instead of the
 // summed tensor.  The CTA of row r
-//   1. stores its partial row into slot [rank] of every peer's inbox (plain 16-byte peer stores) and, after a
-//      system-scope fence, writes the call number into flag [rank][r] of every peer,
-//   2. waits (bounded) until its own flags [s][r] show the call number for every peer s,
+//   1. stores its partial row into slot [rank] of every peer's inbox, every 4 bytes of payload paired with the 4-byte
+//      call number in one 8-byte unit (plain 16-byte peer stores of two such units),
+//   2. polls its own inbox until every unit of row r from every peer carries the call number (bounded),
 //   3. adds the P rows in rank order in fp32 and rounds the sum to the storage type (bit for bit what the stand-alone
 //      all-reduce kernel stores), and carries on with LayerNorm and the mixes from registers.
-// One launch and one pass over the row replace the all-reduce kernel, its [rows, D] round trip and a kernel boundary.
-// The protocol (two inbox buffers alternating by call number, a call counter on the device, rank-ordered sums, error
-// word 7 when a wait runs out) is the all-reduce kernel's; the flags are per ROW here, so the communicator memory is
-// its own.  A CTA waits for the same row's CTA on every peer: the host admits only row counts whose CTAs are all
-// resident at once, so no CTA waits for one that cannot start.
+// An aligned 8-byte store arrives whole, so a unit that shows the call number holds this call's payload: no fence, no
+// separate flag, and the exchange costs ONE trip over the link instead of three (data, acknowledgement, flag).  One
+// launch and one pass over the row replace the all-reduce kernel, its [rows, D] round trip and a kernel boundary.
+// Two inbox buffers alternate by call number (a rank that starts call e + 2 has finished call e + 1, whose wait
+// proves that every peer had started e + 1, i.e. finished reading e); the call counter lives on the device; the sum
+// runs in rank order on every rank; a wait that runs out raises error word 7 and the kernel stores nothing.  A CTA
+// waits for the same row's CTA on every peer: the host admits only row counts whose CTAs are all resident at once, so
+// no CTA waits for one that cannot start.
 constexpr int kTpMaxRanks = 8;
 constexpr unsigned kErrPeerWait = 7;
 
 struct TpRowsArgs {
     const void* partial;            // this rank's [rows, D] partial sums
-    void* inbox[kTpMaxRanks];       // per rank: [2][P][slot_elems] values
-    uint32_t* flags[kTpMaxRanks];   // per rank: [2][P][max_rows]
+    uint4* inbox[kTpMaxRanks];      // per rank: [2][P][slot_elems / 2] units of {payload word, call number}, two per uint4
     uint32_t* counters;             // local: [0] completed calls, [1] CTAs of the current call that are through
     unsigned int* error;
-    int rank, world, max_rows;
-    long long slot_elems;
+    int rank, world;
+    long long slot_elems;           // payload values per inbox slot (a multiple of 8)
     unsigned long long wait_ns;
 };
 
-__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ void st_volatile_v4(uint4* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ uint4 ld_volatile_v4(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
+template <typename T> __device__ __forceinline__ T word_lo(uint32_t w);
+template <typename T> __device__ __forceinline__ T word_hi(uint32_t w);
+template <> __device__ __forceinline__ __half word_lo<__half>(uint32_t w) { return __ushort_as_half((unsigned short)(w & 0xffffu)); }
+template <> __device__ __forceinline__ __half word_hi<__half>(uint32_t w) { return __ushort_as_half((unsigned short)(w >> 16)); }
+template <> __device__ __forceinline__ __nv_bfloat16 word_lo<__nv_bfloat16>(uint32_t w) { return __ushort_as_bfloat16((unsigned short)(w & 0xffffu)); }
+template <> __device__ __forceinline__ __nv_bfloat16 word_hi<__nv_bfloat16>(uint32_t w) { return __ushort_as_bfloat16((unsigned short)(w >> 16)); }
 __device__ __forceinline__ unsigned long long timer_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
 
-// Steps 1-3 for the row of this CTA: x[i][e] receives the rounded sum.  Returns the call number, or 0 when a wait ran
-// out (the caller skips its stores and still calls tp_rows_finish).  T is a 2-byte type.
+// inbox[r] without indexing the kernel parameters dynamically (which would copy the argument block to local memory)
+__device__ __forceinline__ uint4* tp_inbox(const TpRowsArgs& t, int r) {
+    uint4* p = t.inbox[0];
+#pragma unroll
+    for (int k = 1; k < kTpMaxRanks; ++k)
+        if (r == k) p = t.inbox[k];
+    return p;
+}
+
+// Steps 1-3 for the row of this CTA: x[i][e] receives the rounded sum.  Returns false when a wait ran out (the caller
+// skips its stores and still calls tp_rows_finish).  T is a 2-byte type.
 template <typename T, int NV>
-__device__ __forceinline__ uint32_t tp_rows_exchange(const TpRowsArgs& t, size_t row, int D, float (&x)[kNMMaxVec][8],
-                                                     uint32_t* s_epoch, int* s_abort) {
+__device__ __forceinline__ bool tp_rows_exchange(const TpRowsArgs& t, size_t row, int D, float (&x)[kNMMaxVec][8],
+                                                 uint32_t* s_epoch) {
     static_assert(sizeof(T) == 2, "the inbox holds 2-byte values");
     const int tid = threadIdx.x, nvec = D / 8;
-    if (tid == 0) {
-        *s_epoch = *reinterpret_cast<volatile uint32_t*>(t.counters) + 1u;
-        *s_abort = 0;
-    }
+    if (tid == 0) *s_epoch = *reinterpret_cast<volatile uint32_t*>(t.counters) + 1u;
     __syncthreads();
     const uint32_t e = *s_epoch;
+    const uint32_t tag = e ? e : 1u;  // never 0 (fresh memory); calls 0 and 1 use different buffers
     const long long buf = (long long)(e & 1u);
+    const long long slot_u4 = t.slot_elems / 4;                    // uint4 per slot: 2 per 8 payload values
+    const long long row_u4 = (long long)row * (D / 4);
     const uint4* mine = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(t.partial) + row * D);
     uint4 own[NV];
 #pragma unroll
@@ -419,49 +436,59 @@ __device__ __forceinline__ uint32_t tp_rows_exchange(const TpRowsArgs& t, size_t
         if (vi < nvec) own[i] = mine[vi];
     }
     for (int s = 1; s < t.world; ++s) {
-        const int peer = (t.rank + s) % t.world;
-        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<T*>(t.inbox[peer]) + (buf * t.world + t.rank) * t.slot_elems + row * D);
+        const int peer = (t.rank + s) % t.world;  // start with the next rank: the peers' links are loaded evenly
+        uint4* dst = tp_inbox(t, peer) + (buf * t.world + t.rank) * slot_u4 + row_u4;
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
             const int vi = tid + i * kNMThreads;
-            if (vi < nvec) dst[vi] = own[i];
-        }
-    }
-    __threadfence_system();
-    __syncthreads();
-    if (tid < t.world && tid != t.rank) {
-        st_release_sys_u32(t.flags[tid] + (buf * t.world + t.rank) * t.max_rows + row, e);
-        const uint32_t* f = t.flags[t.rank] + (buf * t.world + tid) * t.max_rows + row;
-        const unsigned long long t0 = timer_ns();
-        while ((int32_t)(ld_acquire_sys_u32(f) - e) < 0) {
-            if (timer_ns() - t0 > t.wait_ns) {
-                *s_abort = 1;
-                atomicCAS(t.error, 0u, kErrPeerWait);
-                break;
+            if (vi < nvec) {
+                st_volatile_v4(dst + 2 * vi, own[i].x, tag, own[i].y, tag);
+                st_volatile_v4(dst + 2 * vi + 1, own[i].z, tag, own[i].w, tag);
             }
-            __nanosleep(32);
         }
     }
-    __syncthreads();
-    if (*s_abort) return 0u;
-    const T* box = reinterpret_cast<const T*>(t.inbox[t.rank]) + buf * t.world * t.slot_elems + row * D;
+    float acc[NV][8];
 #pragma unroll
-    for (int i = 0; i < NV; ++i) {
-        const int vi = tid + i * kNMThreads;
-        if (vi < nvec) {
-            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            for (int s = 0; s < t.world; ++s) {
-                // inbox rows were written by other GPUs: read them past L1, which is not coherent with peer writes
-                const uint4 raw = s == t.rank ? own[i] : __ldcg(reinterpret_cast<const uint4*>(box + (long long)s * t.slot_elems) + vi);
-                const T* h = reinterpret_cast<const T*>(&raw);
+    for (int i = 0; i < NV; ++i)
 #pragma unroll
-                for (int q = 0; q < 8; ++q) acc[q] += to_f<T>(h[q]);
+        for (int q = 0; q < 8; ++q) acc[i][q] = 0.f;
+    bool gave_up = false;
+    const unsigned long long t0 = timer_ns();
+    const uint4* box = tp_inbox(t, t.rank) + buf * t.world * slot_u4 + row_u4;
+    for (int s = 0; s < t.world; ++s) {
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int vi = tid + i * kNMThreads;
+            if (vi < nvec) {
+                uint4 raw = own[i];
+                if (s != t.rank) {
+                    const uint4* src = box + (long long)s * slot_u4 + 2 * vi;
+                    uint4 lo = ld_volatile_v4(src), hi = ld_volatile_v4(src + 1);
+                    for (uint32_t spin = 1; !gave_up && (lo.y != tag || lo.w != tag || hi.y != tag || hi.w != tag); ++spin) {
+                        if ((spin & 15u) == 0 && timer_ns() - t0 > t.wait_ns) gave_up = true;
+                        lo = ld_volatile_v4(src);
+                        hi = ld_volatile_v4(src + 1);
+                    }
+                    raw = make_uint4(lo.x, lo.z, hi.x, hi.z);
+                }
+                const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    acc[i][2 * q] += to_f<T>(word_lo<T>(w[q]));
+                    acc[i][2 * q + 1] += to_f<T>(word_hi<T>(w[q]));
+                }
             }
-#pragma unroll
-            for (int q = 0; q < 8; ++q) x[i][q] = round_to<T>(acc[q]);
         }
     }
-    return e;
+    if (__syncthreads_or(gave_up ? 1 : 0)) {
+        if (tid == 0) atomicCAS(t.error, 0u, kErrPeerWait);
+        return false;
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+#pragma unroll
+        for (int q = 0; q < 8; ++q) x[i][q] = round_to<T>(acc[i][q]);
+    return true;
 }
 
 // The call counter advances when the last CTA of the launch is through (every CTA read it at its start).
@@ -503,7 +530,6 @@ template <typename T, int NV>
 __global__ void __launch_bounds__(kNMThreads) tp_attn_norm_mix6_kernel(const Mix6Args p, const TpRowsArgs t, void* x_out) {
     __shared__ float red[32];
     __shared__ uint32_t s_epoch;
-    __shared__ int s_abort;
     const size_t row = blockIdx.x;
     const int D = p.D, nvec = D / 8;
     Raw8<T> cw[NV], cb[NV], cm[6][NV];
@@ -520,7 +546,7 @@ __global__ void __launch_bounds__(kNMThreads) tp_attn_norm_mix6_kernel(const Mix
     grid_dependency_wait();
     if (threadIdx.x == 0) grid_launch_dependents();
     RowStats<T> rs;
-    if (tp_rows_exchange<T, NV>(t, row, D, rs.x, &s_epoch, &s_abort)) {
+    if (tp_rows_exchange<T, NV>(t, row, D, rs.x, &s_epoch)) {
         row_stats<T, NV>(rs, D, p.eps, red);
         T* prev = reinterpret_cast<T*>(p.prev) + (p.slots ? (size_t)__ldg(p.slots + row) : row) * D;
 #pragma unroll
@@ -557,7 +583,6 @@ template <typename T, int NV>
 __global__ void __launch_bounds__(kNMThreads) tp_ffn_add_norm_mix_kernel(const FfnMixArgs p, const TpRowsArgs t) {
     __shared__ float red[32];
     __shared__ uint32_t s_epoch;
-    __shared__ int s_abort;
     const size_t row = blockIdx.x;
     const int D = p.D, nvec = D / 8;
     Raw8<T> cw[NV], cb[NV], cm[NV];
@@ -573,7 +598,7 @@ __global__ void __launch_bounds__(kNMThreads) tp_ffn_add_norm_mix_kernel(const F
     grid_dependency_wait();
     if (threadIdx.x == 0) grid_launch_dependents();
     RowStats<T> rs;
-    if (tp_rows_exchange<T, NV>(t, row, D, rs.x, &s_epoch, &s_abort)) {
+    if (tp_rows_exchange<T, NV>(t, row, D, rs.x, &s_epoch)) {
         const T* res = reinterpret_cast<const T*>(p.res) + row * D;
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
@@ -620,27 +645,24 @@ static int resident_rows(K kernel) {
     return sms * per_sm;
 }
 
-static int fill_tp_args(const char* what, TpRowsArgs& t, const void* partial, void* const* inbox_ptrs, void* const* flag_ptrs,
-                        void* counters, int rank, int world, int rows, int D, int max_rows, long long slot_elems, int wait_ms) {
+static int fill_tp_args(const char* what, TpRowsArgs& t, const void* partial, void* const* inbox_ptrs, void* counters,
+                        int rank, int world, int rows, int D, long long slot_elems, int wait_ms) {
     RWKV7_REQUIRE(world >= 2 && world <= kTpMaxRanks && rank >= 0 && rank < world, RWKV7_ERR_INVALID,
                   "%s: world must be 2..%d and rank inside it (world=%d rank=%d)", what, kTpMaxRanks, world, rank);
-    RWKV7_REQUIRE(partial && inbox_ptrs && flag_ptrs && counters, RWKV7_ERR_INVALID, "%s: null pointer", what);
-    RWKV7_REQUIRE(rows <= max_rows && slot_elems % 8 == 0 && (long long)rows * D <= slot_elems, RWKV7_ERR_WORKSPACE,
-                  "%s: %d x %d values do not fit the communicator (%d rows, slots of %lld)", what, rows, D, max_rows, slot_elems);
+    RWKV7_REQUIRE(partial && inbox_ptrs && counters, RWKV7_ERR_INVALID, "%s: null pointer", what);
+    RWKV7_REQUIRE(slot_elems % 8 == 0 && (long long)rows * D <= slot_elems, RWKV7_ERR_WORKSPACE,
+                  "%s: %d x %d values do not fit an inbox slot of %lld", what, rows, D, slot_elems);
     RWKV7_REQUIRE(aligned(partial, 16) && aligned(counters, 8), RWKV7_ERR_ALIGN, "%s: unaligned pointer", what);
     t.partial = partial;
     for (int r = 0; r < world; ++r) {
-        RWKV7_REQUIRE(inbox_ptrs[r] && flag_ptrs[r] && aligned(inbox_ptrs[r], 16) && aligned(flag_ptrs[r], 4), RWKV7_ERR_INVALID,
-                      "%s: bad inbox / flag pointer of rank %d", what, r);
-        t.inbox[r] = inbox_ptrs[r];
-        t.flags[r] = reinterpret_cast<uint32_t*>(flag_ptrs[r]);
+        RWKV7_REQUIRE(inbox_ptrs[r] && aligned(inbox_ptrs[r], 16), RWKV7_ERR_INVALID, "%s: bad inbox pointer of rank %d", what, r);
+        t.inbox[r] = reinterpret_cast<uint4*>(inbox_ptrs[r]);
     }
     t.counters = reinterpret_cast<uint32_t*>(counters);
     t.error = kernel_error_word();
     RWKV7_REQUIRE(t.error != nullptr, RWKV7_ERR_CUDA, "%s: cannot resolve the device error word", what);
     t.rank = rank;
     t.world = world;
-    t.max_rows = max_rows;
     t.slot_elems = slot_elems;
     t.wait_ns = (unsigned long long)(wait_ms > 0 ? wait_ms : 2000) * 1000000ull;
     return RWKV7_OK;
@@ -695,9 +717,9 @@ extern "C" int rwkv7_tp_rows_resident(int D, int dtype) {
 
 extern "C" int rwkv7_tp_attn_norm_mix6(const void* partial, void* x_out, void* prev, const int32_t* slot_ids,
                                        const void* norm_w, const void* norm_b, const void* const mixes[6],
-                                       void* const outs[6], void* const* inbox_ptrs, void* const* flag_ptrs, void* counters,
-                                       int rank, int world, int rows, int D, int max_rows, long long slot_elems, float eps,
-                                       int wait_ms, int dtype, void* stream) {
+                                       void* const outs[6], void* const* inbox_ptrs, void* counters, int rank, int world,
+                                       int rows, int D, long long slot_elems, float eps, int wait_ms, int dtype,
+                                       void* stream) {
     if (int e = check_row_shape("tp_attn_norm_mix6", rows, D)) return e;
     RWKV7_REQUIRE(dtype == RWKV7_F16 || dtype == RWKV7_BF16, RWKV7_ERR_UNSUPPORTED, "tp_attn_norm_mix6: fp16 or bf16");
     RWKV7_REQUIRE(x_out && prev && norm_w && norm_b && mixes && outs, RWKV7_ERR_INVALID, "tp_attn_norm_mix6: null pointer");
@@ -711,8 +733,7 @@ extern "C" int rwkv7_tp_attn_norm_mix6(const void* partial, void* x_out, void* p
     const void* ptrs[] = {x_out, prev, norm_w, norm_b};
     for (const void* q : ptrs) RWKV7_REQUIRE(aligned(q, 16), RWKV7_ERR_ALIGN, "tp_attn_norm_mix6: unaligned pointer");
     TpRowsArgs t{};
-    if (int e = fill_tp_args("tp_attn_norm_mix6", t, partial, inbox_ptrs, flag_ptrs, counters, rank, world, rows, D, max_rows,
-                             slot_elems, wait_ms))
+    if (int e = fill_tp_args("tp_attn_norm_mix6", t, partial, inbox_ptrs, counters, rank, world, rows, D, slot_elems, wait_ms))
         return e;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return dtype == RWKV7_F16 ? tp_mix6_launch<__half>(tp_vectors(D), rows, st, p, t, x_out)
@@ -721,9 +742,8 @@ extern "C" int rwkv7_tp_attn_norm_mix6(const void* partial, void* x_out, void* p
 
 extern "C" int rwkv7_tp_ffn_add_norm_mix(const void* residual, const void* partial, void* prev, const int32_t* slot_ids,
                                          const void* norm_w, const void* norm_b, const void* mix, void* residual_out,
-                                         void* mixed, void* const* inbox_ptrs, void* const* flag_ptrs, void* counters,
-                                         int rank, int world, int rows, int D, int max_rows, long long slot_elems, float eps,
-                                         int wait_ms, int dtype, void* stream) {
+                                         void* mixed, void* const* inbox_ptrs, void* counters, int rank, int world, int rows,
+                                         int D, long long slot_elems, float eps, int wait_ms, int dtype, void* stream) {
     if (int e = check_row_shape("tp_ffn_add_norm_mix", rows, D)) return e;
     RWKV7_REQUIRE(dtype == RWKV7_F16 || dtype == RWKV7_BF16, RWKV7_ERR_UNSUPPORTED, "tp_ffn_add_norm_mix: fp16 or bf16");
     RWKV7_REQUIRE(residual && prev && norm_w && norm_b && mix && residual_out && mixed, RWKV7_ERR_INVALID,
@@ -732,8 +752,7 @@ extern "C" int rwkv7_tp_ffn_add_norm_mix(const void* residual, const void* parti
     for (const void* q : ptrs) RWKV7_REQUIRE(aligned(q, 16), RWKV7_ERR_ALIGN, "tp_ffn_add_norm_mix: unaligned pointer");
     FfnMixArgs p{residual, nullptr, norm_w, norm_b, mix, prev, residual_out, mixed, D, eps, slot_ids};
     TpRowsArgs t{};
-    if (int e = fill_tp_args("tp_ffn_add_norm_mix", t, partial, inbox_ptrs, flag_ptrs, counters, rank, world, rows, D, max_rows,
-                             slot_elems, wait_ms))
+    if (int e = fill_tp_args("tp_ffn_add_norm_mix", t, partial, inbox_ptrs, counters, rank, world, rows, D, slot_elems, wait_ms))
         return e;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return dtype == RWKV7_F16 ? tp_ffn_launch<__half>(tp_vectors(D), rows, st, p, t)

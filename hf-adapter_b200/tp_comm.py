@@ -55,8 +55,8 @@ class PeerAllReduce:
 
 class PeerRowSum:
     """The sums that the row kernels take in themselves (``rwkv7_tp_ffn_add_norm_mix`` after ``o_proj``,
-    ``rwkv7_tp_attn_norm_mix6`` after ``ffn.value``): an inbox ``[2][P][max_rows * width]`` and one flag per row on every
-    rank.  Same rules as ``PeerAllReduce``: one instance per stream, the same sequence of calls on every rank."""
+    ``rwkv7_tp_attn_norm_mix6`` after ``ffn.value``): an inbox ``[2][P][max_rows * width]`` on every rank in which every
+    4 bytes of payload sit beside the 4-byte call number (no flag array).  Same rules as ``PeerAllReduce``: one instance per stream, the same sequence of calls on every rank."""
 
     @staticmethod
     def resident_rows(width: int, dtype) -> int:
@@ -78,19 +78,14 @@ class PeerRowSum:
         if self.max_rows <= 0:
             raise ValueError(f"rows of {self.width} values are not supported by the tensor-parallel row kernels")
         self.slot_elems = (self.max_rows * self.width + 7) // 8 * 8
-        inbox_bytes = 2 * self.world * self.slot_elems * 2
-        flag_bytes = 2 * self.world * self.max_rows * 4
-        self._inbox_bytes = (inbox_bytes + 255) // 256 * 256
-        self.buf = symm_mem.empty(self._inbox_bytes + flag_bytes, dtype=torch.uint8, device=device)
+        self.buf = symm_mem.empty(2 * self.world * self.slot_elems * 4, dtype=torch.uint8, device=device)
         self.handle = symm_mem.rendezvous(self.buf, group)
         self.buf.zero_()
         self.counters = torch.zeros(2, device=device, dtype=torch.int32)
         torch.cuda.synchronize(device)
-        dist.barrier(group)  # nobody pushes before every inbox and flag array is zero
-        bases = [int(p) for p in self.handle.buffer_ptrs]
-        self._inbox_arr = (ctypes.c_void_p * self.world)(*bases)
-        self._flags_arr = (ctypes.c_void_p * self.world)(*[b + self._inbox_bytes for b in bases])
-        self._inbox, self._flags = ctypes.cast(self._inbox_arr, _lib.PP), ctypes.cast(self._flags_arr, _lib.PP)
+        dist.barrier(group)  # nobody pushes before every inbox is zero
+        self._inbox_arr = (ctypes.c_void_p * self.world)(*[int(p) for p in self.handle.buffer_ptrs])
+        self._inbox = ctypes.cast(self._inbox_arr, _lib.PP)
 
     def takes(self, partial) -> bool:
         return (partial.is_cuda and partial.dtype == self.dtype and partial.dim() == 2 and partial.is_contiguous()
@@ -115,8 +110,8 @@ class PeerRowSum:
         res_out, mixed = torch.empty_like(partial), torch.empty_like(partial)
         _lib.check(_lib.lib.rwkv7_tp_ffn_add_norm_mix(
             ptr(residual), ptr(partial), ptr(previous), ptr(slot_ids), ptr(norm_weight),
-            ptr(norm_bias), ptr(mix), ptr(res_out), ptr(mixed), self._inbox, self._flags, ptr(self.counters), self.rank,
-            self.world, rows, self.width, self.max_rows, self.slot_elems, float(eps), self.wait_ms, self.dtype_code,
+            ptr(norm_bias), ptr(mix), ptr(res_out), ptr(mixed), self._inbox, ptr(self.counters), self.rank,
+            self.world, rows, self.width, self.slot_elems, float(eps), self.wait_ms, self.dtype_code,
             stream_ptr(partial)), "tp_ffn_add_norm_mix")
         return res_out, mixed
 
@@ -135,7 +130,7 @@ class PeerRowSum:
         outs_p, _k2 = _lib.ptr_array([s[i].data_ptr() for i in range(6)])
         _lib.check(_lib.lib.rwkv7_tp_attn_norm_mix6(
             ptr(partial), ptr(x), ptr(previous), ptr(slot_ids), ptr(norm_weight),
-            ptr(norm_bias), mixes_p, outs_p, self._inbox, self._flags, ptr(self.counters), self.rank, self.world, rows,
-            self.width, self.max_rows, self.slot_elems, float(eps), self.wait_ms, self.dtype_code, stream_ptr(partial)),
+            ptr(norm_bias), mixes_p, outs_p, self._inbox, ptr(self.counters), self.rank, self.world, rows,
+            self.width, self.slot_elems, float(eps), self.wait_ms, self.dtype_code, stream_ptr(partial)),
             "tp_attn_norm_mix6")
         return x, tuple(s[i] for i in range(6))

@@ -396,25 +396,28 @@ int rwkv7_tp_allreduce(const void* partial, void* out, void* const* inbox_ptrs, 
 /* The two row kernels that CONSUME those sums, with the sum inside them: `partial` is this rank's [rows,D] partial
  * output of o_proj (rwkv7_tp_ffn_add_norm_mix: residual_out = residual + sum, then as rwkv7_ffn_add_norm_mix) or of
  * ffn.value (rwkv7_tp_attn_norm_mix6: x_out = sum, then as rwkv7_attn_norm_mix6).  The CTA of a row pushes it to every
- * peer, waits (bounded, as above) for the peers' copies of that row, adds them in rank order and rounds the sum to the
+ * peer, polls (bounded, as above) for the peers' copies of that row, adds them in rank order and rounds the sum to the
  * storage type - the values rwkv7_tp_allreduce would have stored - before it normalises: one launch replaces the
  * all-reduce kernel, a [rows,D] round trip and a kernel boundary (the reference runs the framework's all-reduce and
- * then its fused norm kernels, rwkv7_hf/native_jit_decode.py:481-901 under rwkv7_hf/model_config.py:37-53).
- *   inbox_ptrs as above; flag_ptrs: entry r = rank r's flag array [2][P][max_rows] u32 (one flag per ROW, so this
- *   memory is not shared with rwkv7_tp_allreduce); counters: two u32, zeroed at set-up.  slot_ids NULL or the state-pool
- *   rows of `prev`.  rows must not exceed rwkv7_tp_rows_resident(D, dtype): every row's CTA waits for a peer's CTA of
- *   the same row, so all of them have to be resident at once (RWKV7_ERR_UNSUPPORTED otherwise - use rwkv7_tp_allreduce
- *   and the plain kernels).  fp16 or bf16.  The same-sequence and no-overlap rules above apply. */
+ * then its fused norm kernels, rwkv7_hf/native_jit_decode.py:481-901 under rwkv7_hf/model_config.py:37-53).  On the
+ * wire every 4 bytes of payload travel with the 4-byte call number in one aligned 8-byte unit, which arrives whole: a
+ * unit that shows the call number holds this call's payload, so the exchange needs no fence and no separate flag.
+ *   inbox_ptrs: host array of P device pointers, entry r = rank r's inbox as mapped into THIS process,
+ *   2 * P * slot_elems * 4 bytes (two buffers, a slot per rank, 4 bytes per 2-byte payload value; zeroed, with a
+ *   barrier, before the first call; not shared with rwkv7_tp_allreduce).  slot_elems: a multiple of 8, >= rows * D.
+ *   counters: two u32 in local memory, zeroed at set-up.  slot_ids NULL or the state-pool rows of `prev`.
+ *   rows must not exceed rwkv7_tp_rows_resident(D, dtype): every row's CTA waits for a peer's CTA of the same row, so
+ *   all of them have to be resident at once (RWKV7_ERR_UNSUPPORTED otherwise - use rwkv7_tp_allreduce and the plain
+ *   kernels).  fp16 or bf16.  The same-sequence and no-overlap rules above apply. */
 int rwkv7_tp_rows_resident(int D, int dtype);
 int rwkv7_tp_attn_norm_mix6(const void* partial, void* x_out, void* prev, const int32_t* slot_ids, const void* norm_w,
                             const void* norm_b, const void* const mixes[6], void* const outs[6], void* const* inbox_ptrs,
-                            void* const* flag_ptrs, void* counters, int rank, int world, int rows, int D, int max_rows,
-                            long long slot_elems, float eps, int wait_ms, int dtype, void* stream);
+                            void* counters, int rank, int world, int rows, int D, long long slot_elems, float eps,
+                            int wait_ms, int dtype, void* stream);
 int rwkv7_tp_ffn_add_norm_mix(const void* residual, const void* partial, void* prev, const int32_t* slot_ids,
                               const void* norm_w, const void* norm_b, const void* mix, void* residual_out, void* mixed,
-                              void* const* inbox_ptrs, void* const* flag_ptrs, void* counters, int rank, int world,
-                              int rows, int D, int max_rows, long long slot_elems, float eps, int wait_ms, int dtype,
-                              void* stream);
+                              void* const* inbox_ptrs, void* counters, int rank, int world, int rows, int D,
+                              long long slot_elems, float eps, int wait_ms, int dtype, void* stream);
 
 #ifdef __cplusplus
 }

@@ -160,15 +160,16 @@ def test_peer_sum_wait_runs_out_without_a_peer():
 
 def test_row_sum_kernels_with_a_prefilled_inbox():
     """The row kernels that take the tensor-parallel sum in themselves, on ONE GPU and without a peer: this GPU plays
-    rank 0 of two, the "peer" memory is local, and the test itself puts rank 1's partial rows and flags for call 1 into
-    rank 0's inbox before the launch.  The results must equal the plain row kernels on the rounded sum bit for bit.  A
-    second launch (call 2, nothing prefilled) must give up after its 30 ms limit with code 7 and store nothing."""
+    rank 0 of two, the "peer" memory is local, and the test itself puts rank 1's partial rows for call 1 into rank 0's
+    inbox before the launch (wire format: every 4-byte payload word followed by the call number).  The results must
+    equal the plain row kernels on the rounded sum bit for bit.  A second launch (call 2, nothing prefilled) must give
+    up after its 30 ms limit with code 7 and store nothing."""
     import ctypes
     import hf_adapter_b200 as hb
     from hf_adapter_b200 import _lib
     rows, D = 40, 1024
     assert int(_lib.lib.rwkv7_tp_rows_resident(D, _lib.F16)) >= 148
-    slot = rows * D
+    slot = rows * D  # payload values per slot = int32 words per slot on the wire
     g = torch.Generator(device="cuda").manual_seed(3)
     rnd = lambda *sh: torch.randn(*sh, device="cuda", generator=g).half()
     mine, theirs, res, prev = rnd(rows, D), rnd(rows, D), rnd(rows, D), rnd(rows, D)
@@ -176,29 +177,27 @@ def test_row_sum_kernels_with_a_prefilled_inbox():
     total = (mine.float() + theirs.float()).half()
     arr = lambda ts: ctypes.cast((ctypes.c_void_p * 2)(*[t.data_ptr() for t in ts]), _lib.PP)
     stream = torch.cuda.current_stream().cuda_stream
+    wire = lambda t, call: torch.stack([t.reshape(-1).view(torch.int32), torch.full((slot // 2,), call, device="cuda",
+                                                                                    dtype=torch.int32)], 1).reshape(-1)
 
     def fresh():
-        inbox = [torch.zeros(2 * 2 * slot, device="cuda", dtype=torch.float16) for _ in range(2)]
-        flags = [torch.zeros(2 * 2 * rows, device="cuda", dtype=torch.int32) for _ in range(2)]
-        inbox[0][(1 * 2 + 1) * slot:(1 * 2 + 2) * slot] = theirs.reshape(-1)  # call 1 -> buffer 1, slot of rank 1
-        flags[0][(1 * 2 + 1) * rows:(1 * 2 + 2) * rows] = 1
-        return inbox, flags, torch.zeros(2, device="cuda", dtype=torch.int32)
+        inbox = [torch.zeros(2 * 2 * slot, device="cuda", dtype=torch.int32) for _ in range(2)]
+        inbox[0][(1 * 2 + 1) * slot:(1 * 2 + 2) * slot] = wire(theirs, 1)  # call 1 -> buffer 1, slot of rank 1
+        return inbox, torch.zeros(2, device="cuda", dtype=torch.int32)
 
     _lib.kernel_status(True)
-    inbox, flags, counters = fresh()
+    inbox, counters = fresh()
     p1, p2 = prev.clone(), prev.clone()
     want_x, want_m = hb.fused_ffn_add_norm_mix_decode(res, total, p1, nw, nb, mixes[0])
     got_x, got_m = torch.full_like(res, -1.0), torch.full_like(res, -1.0)
     call = lambda: _lib.lib.rwkv7_tp_ffn_add_norm_mix(
         res.data_ptr(), mine.data_ptr(), p2.data_ptr(), None, nw.data_ptr(), nb.data_ptr(), mixes[0].data_ptr(),
-        got_x.data_ptr(), got_m.data_ptr(), arr(inbox), arr(flags), counters.data_ptr(), 0, 2, rows, D, rows, slot, 1e-5, 30,
-        _lib.F16, stream)
+        got_x.data_ptr(), got_m.data_ptr(), arr(inbox), counters.data_ptr(), 0, 2, rows, D, slot, 1e-5, 30, _lib.F16, stream)
     assert call() == 0
     torch.cuda.synchronize()
     assert _lib.kernel_status(True) == 0 and int(counters[0]) == 1
     assert torch.equal(got_x, want_x) and torch.equal(got_m, want_m) and torch.equal(p1, p2)
-    assert torch.equal(inbox[1][2 * slot:3 * slot], mine.reshape(-1))  # this rank's rows reached the "peer" (buffer 1, slot 0)
-    assert bool((flags[1][2 * rows:3 * rows] == 1).all())
+    assert torch.equal(inbox[1][2 * slot:3 * slot], wire(mine, 1))  # this rank's rows reached the "peer" (buffer 1, slot 0)
     # call 2: nobody fills buffer 0 -> every row's wait runs out, nothing is stored
     got_x.fill_(-1.0)
     keep = p2.clone()
@@ -208,7 +207,7 @@ def test_row_sum_kernels_with_a_prefilled_inbox():
     assert float(got_x.min()) == -1.0 and float(got_x.max()) == -1.0 and torch.equal(p2, keep)
     assert int(counters[0]) == 2
 
-    inbox, flags, counters = fresh()
+    inbox, counters = fresh()
     p1, p2 = prev.clone(), prev.clone()
     want6 = hb.fused_attn_norm_mix6_decode(total, p1, nw, nb, *mixes)
     x_out = torch.empty_like(mine)
@@ -216,8 +215,8 @@ def test_row_sum_kernels_with_a_prefilled_inbox():
     mp_, _k1 = _lib.ptr_array([m.data_ptr() for m in mixes])
     op_, _k2 = _lib.ptr_array([outs[i].data_ptr() for i in range(6)])
     assert _lib.lib.rwkv7_tp_attn_norm_mix6(mine.data_ptr(), x_out.data_ptr(), p2.data_ptr(), None, nw.data_ptr(), nb.data_ptr(),
-                                            mp_, op_, arr(inbox), arr(flags), counters.data_ptr(), 0, 2, rows, D, rows, slot,
-                                            1e-5, 30, _lib.F16, stream) == 0
+                                            mp_, op_, arr(inbox), counters.data_ptr(), 0, 2, rows, D, slot, 1e-5, 30, _lib.F16,
+                                            stream) == 0
     torch.cuda.synchronize()
     assert _lib.kernel_status(True) == 0
     assert torch.equal(x_out, total) and torch.equal(p1, p2)
@@ -225,5 +224,5 @@ def test_row_sum_kernels_with_a_prefilled_inbox():
     # more rows than are resident at once are refused on the host
     big = int(_lib.lib.rwkv7_tp_rows_resident(D, _lib.F16)) + 1
     assert _lib.lib.rwkv7_tp_attn_norm_mix6(mine.data_ptr(), x_out.data_ptr(), p2.data_ptr(), None, nw.data_ptr(), nb.data_ptr(),
-                                            mp_, op_, arr(inbox), arr(flags), counters.data_ptr(), 0, 2, big, D, big, big * D,
-                                            1e-5, 30, _lib.F16, stream) == _lib.ERR_UNSUPPORTED
+                                            mp_, op_, arr(inbox), counters.data_ptr(), 0, 2, big, D, big * D, 1e-5, 30, _lib.F16,
+                                            stream) == _lib.ERR_UNSUPPORTED
