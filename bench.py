@@ -305,6 +305,11 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    def note(msg):
+        """Progress on stderr (RWKV7_BENCH_VERBOSE=1): which phase a failed multi-rank run was in."""
+        if os.environ.get("RWKV7_BENCH_VERBOSE"):
+            print(f"[bench rank {rank}] {msg}", file=sys.stderr, flush=True)
+
     def max_over_ranks(ms):
         t = torch.tensor([ms], device=dev)
         if world > 1:
@@ -414,6 +419,7 @@ def main():
     replicas = None
     use_tp = world > 1 and args.parallelism == "tp"
     if world > 1 and not args.no_side:
+        note("side measurement: the other parallelism")
         other_tp = not use_tp
         m2, _, _ = build_model(args.shape, world if other_tp else 1, rank if other_tp else 0, tp_group if other_tp else None,
                                dev, args.layers, args.quant, overlap_rows=args.tp_overlap_rows, tp_comm=args.tp_comm)
@@ -449,7 +455,9 @@ def main():
         parallelism = "single GPU" if world == 1 else \
             f"dp{world}: independent sequence batches, one full replica per GPU, {args.batch} sequences each, no data-path collective"
     Lr = cfg.num_hidden_layers
+    note(f"headline: batch {B}")
     ms_per_step, e2e_ms, launches_per_step, cache, clocks, gen = time_decode(model, B, 0 if use_tp else rank, True)
+    note(f"headline done: {ms_per_step:.3f} ms per step")
     global_batch = B if use_tp else args.batch * world
 
     # ---------------- N > 1: strong scaling of the head-sharded form (the global batch stays 64 and 256)
@@ -457,6 +465,7 @@ def main():
     if use_tp and not args.no_side:
         strong = {}
         for Bg in (64, 256):
+            note(f"strong scaling: global batch {Bg}")
             ms_s, _, _, c_s, _, _ = time_decode(model, Bg, 0, False, n_steps=min(steps, 20), e2e=False)
             strong[f"global_batch_{Bg}"] = {"value": Bg / (ms_s * 1e-3), "unit": "tok/s", "ms_per_step": ms_s}
             model._graphs.pop((Bg, True), None)
@@ -477,6 +486,7 @@ def main():
         leave()  # the remaining sections are rank-0 measurements
         return
 
+    note("rank-0 sections: rooflines, operator table")
     hbm_peak, tc_burst, tc_sustained, peak_src = measured_peaks()
     Hl, Fl, A_l = H // shard, Fd // shard, (H // shard) * 64
     sbytes = 2 if args.state == "fp16" else 4
@@ -771,6 +781,7 @@ def main():
         line["config"]["INVALID"] = "layer count overridden for debugging"
     if tp_parity is not None and tp_parity.get("status") != "ok":
         line["config"]["INVALID"] = "head-sharded parity check failed: " + json.dumps(tp_parity)[:200]
+    note("line ready")
     print(json.dumps(line), flush=True)
     if tp_parity is not None and tp_parity.get("status") != "ok":
         sys.stdout.flush()

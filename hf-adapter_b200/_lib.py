@@ -72,8 +72,8 @@ SIGNATURES = {
     "rwkv7_tp_allreduce_max_ctas": (I, []),
     "rwkv7_tp_allreduce": (I, [P, P, PP, PP, P, I, I, I, I, ctypes.c_longlong, I, I, P]),
     "rwkv7_tp_rows_resident": (I, [I, I]),
-    "rwkv7_tp_attn_norm_mix6": (I, [P, P, P, P, P, P, PP, PP, PP, P, I, I, I, I, ctypes.c_longlong, F, I, I, P]),
-    "rwkv7_tp_ffn_add_norm_mix": (I, [P] * 9 + [PP, P, I, I, I, I, ctypes.c_longlong, F, I, I, P]),
+    "rwkv7_tp_attn_norm_mix6": (I, [P, P, P, P, P, P, PP, PP, PP, P, I, I, I, I, ctypes.c_longlong, I, F, I, I, P]),
+    "rwkv7_tp_ffn_add_norm_mix": (I, [P] * 9 + [PP, P, I, I, I, I, ctypes.c_longlong, I, F, I, I, P]),
     "rwkv7_a8w8_static_capacity_bytes": (L, []),
     "rwkv7_a8w8_linear_static": (I, [P] * 6 + [I, I, I, I, P]),
 }

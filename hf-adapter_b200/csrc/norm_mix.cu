@@ -2,6 +2,8 @@
 // Each row is read once into registers (128-bit loads), normalised in fp32 with a
 // centred two-pass variance, and every consumer of the normalised row (the six
 // time-mix streams, the shift state) is written from registers in the same pass.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace rwkv7 {
@@ -380,7 +382,7 @@ struct TpRowsArgs {
     uint4* inbox[kTpMaxRanks];      // per rank: [2][P][slot_elems / 2] units of {payload word, call number}, two per uint4
     uint32_t* counters;             // local: [0] completed calls, [1] CTAs of the current call that are through
     unsigned int* error;
-    int rank, world;
+    int rank, world, rows;
     long long slot_elems;           // payload values per inbox slot (a multiple of 8)
     unsigned long long wait_ns;
 };
@@ -414,39 +416,54 @@ __device__ __forceinline__ uint4* tp_inbox(const TpRowsArgs& t, int r) {
     return p;
 }
 
-// Steps 1-3 for the row of this CTA: x[i][e] receives the rounded sum.  Returns false when a wait ran out (the caller
-// skips its stores and still calls tp_rows_finish).  T is a 2-byte type.
-template <typename T, int NV>
-__device__ __forceinline__ bool tp_rows_exchange(const TpRowsArgs& t, size_t row, int D, float (&x)[kNMMaxVec][8],
-                                                 uint32_t* s_epoch) {
-    static_assert(sizeof(T) == 2, "the inbox holds 2-byte values");
-    const int tid = threadIdx.x, nvec = D / 8;
-    if (tid == 0) *s_epoch = *reinterpret_cast<volatile uint32_t*>(t.counters) + 1u;
+// The call number of this launch (every thread of the CTA gets it) - read before any row is pushed.
+__device__ __forceinline__ uint32_t tp_rows_begin(const TpRowsArgs& t, uint32_t* s_epoch) {
+    if (threadIdx.x == 0) *s_epoch = *reinterpret_cast<volatile uint32_t*>(t.counters) + 1u;
     __syncthreads();
-    const uint32_t e = *s_epoch;
-    const uint32_t tag = e ? e : 1u;  // never 0 (fresh memory); calls 0 and 1 use different buffers
-    const long long buf = (long long)(e & 1u);
-    const long long slot_u4 = t.slot_elems / 4;                    // uint4 per slot: 2 per 8 payload values
-    const long long row_u4 = (long long)row * (D / 4);
+    return *s_epoch;
+}
+
+template <typename T, int NV>
+__device__ __forceinline__ void tp_load_own(const TpRowsArgs& t, size_t row, int D, uint4 (&own)[NV]) {
     const uint4* mine = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(t.partial) + row * D);
-    uint4 own[NV];
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
-        const int vi = tid + i * kNMThreads;
-        if (vi < nvec) own[i] = mine[vi];
+        const int vi = threadIdx.x + i * kNMThreads;
+        if (vi < D / 8) own[i] = mine[vi];
     }
+}
+
+// Step 1 for one row.
+template <typename T, int NV>
+__device__ __forceinline__ void tp_rows_push(const TpRowsArgs& t, uint32_t e, size_t row, int D) {
+    static_assert(sizeof(T) == 2, "the inbox holds 2-byte values");
+    const uint32_t tag = e ? e : 1u;  // never 0 (fresh memory); calls 0 and 1 use different buffers
+    const long long slot_u4 = t.slot_elems / 4;  // uint4 per slot: 2 per 8 payload values
+    uint4 own[NV];
+    tp_load_own<T, NV>(t, row, D, own);
     for (int s = 1; s < t.world; ++s) {
         const int peer = (t.rank + s) % t.world;  // start with the next rank: the peers' links are loaded evenly
-        uint4* dst = tp_inbox(t, peer) + (buf * t.world + t.rank) * slot_u4 + row_u4;
+        uint4* dst = tp_inbox(t, peer) + ((long long)(e & 1u) * t.world + t.rank) * slot_u4 + (long long)row * (D / 4);
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
-            const int vi = tid + i * kNMThreads;
-            if (vi < nvec) {
+            const int vi = threadIdx.x + i * kNMThreads;
+            if (vi < D / 8) {
                 st_volatile_v4(dst + 2 * vi, own[i].x, tag, own[i].y, tag);
                 st_volatile_v4(dst + 2 * vi + 1, own[i].z, tag, own[i].w, tag);
             }
         }
     }
+}
+
+// Steps 2-3 for one row: x[i][e] receives the rounded sum.  Returns false when a wait ran out (the caller stores
+// nothing more and still calls tp_rows_finish).
+template <typename T, int NV>
+__device__ __forceinline__ bool tp_rows_sum(const TpRowsArgs& t, uint32_t e, size_t row, int D, float (&x)[kNMMaxVec][8]) {
+    const int tid = threadIdx.x, nvec = D / 8;
+    const uint32_t tag = e ? e : 1u;
+    const long long slot_u4 = t.slot_elems / 4;
+    uint4 own[NV];
+    tp_load_own<T, NV>(t, row, D, own);
     float acc[NV][8];
 #pragma unroll
     for (int i = 0; i < NV; ++i)
@@ -454,7 +471,7 @@ __device__ __forceinline__ bool tp_rows_exchange(const TpRowsArgs& t, size_t row
         for (int q = 0; q < 8; ++q) acc[i][q] = 0.f;
     bool gave_up = false;
     const unsigned long long t0 = timer_ns();
-    const uint4* box = tp_inbox(t, t.rank) + buf * t.world * slot_u4 + row_u4;
+    const uint4* box = tp_inbox(t, t.rank) + (long long)(e & 1u) * t.world * slot_u4 + (long long)row * (D / 4);
     for (int s = 0; s < t.world; ++s) {
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
@@ -527,26 +544,39 @@ __device__ __forceinline__ void row_stats(RowStats<T>& rs, int D, float eps, flo
 
 // attn_norm_mix6 of (sum over ranks of partial); the summed row is also stored to x_out (the residual stream).
 template <typename T, int NV>
-__global__ void __launch_bounds__(kNMThreads) tp_attn_norm_mix6_kernel(const Mix6Args p, const TpRowsArgs t, void* x_out) {
+__global__ void __launch_bounds__(kNMThreads, NV <= 2 ? 2 : 1) tp_attn_norm_mix6_kernel(const Mix6Args p, const TpRowsArgs t, void* x_out) {
     __shared__ float red[32];
     __shared__ uint32_t s_epoch;
-    const size_t row = blockIdx.x;
     const int D = p.D, nvec = D / 8;
-    Raw8<T> cw[NV], cb[NV], cm[6][NV];
+    Raw8<T> cw[NV], cb[NV];
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         const int vi = threadIdx.x + i * kNMThreads;
         if (vi < nvec) {
             cw[i] = ld_raw8(reinterpret_cast<const T*>(p.nw) + vi * 8);
             cb[i] = ld_raw8(reinterpret_cast<const T*>(p.nb) + vi * 8);
-#pragma unroll
-            for (int m = 0; m < 6; ++m) cm[m][i] = ld_raw8(reinterpret_cast<const T*>(p.mix[m]) + vi * 8);
         }
     }
     grid_dependency_wait();
     if (threadIdx.x == 0) grid_launch_dependents();
-    RowStats<T> rs;
-    if (tp_rows_exchange<T, NV>(t, row, D, rs.x, &s_epoch)) {
+    const uint32_t call = tp_rows_begin(t, &s_epoch);
+#pragma unroll 1
+    for (size_t row = blockIdx.x; row < (size_t)t.rows; row += gridDim.x) tp_rows_push<T, NV>(t, call, row, D);
+#pragma unroll 1
+    for (size_t row = blockIdx.x; row < (size_t)t.rows; row += gridDim.x) {
+        // the six mix vectors are fetched per row, ahead of the wait for the peers, which hides their latency; held
+        // across the row loop they would not fit the registers of two CTAs per SM
+        Raw8<T> cm[6][NV];
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int vi = threadIdx.x + i * kNMThreads;
+            if (vi < nvec) {
+#pragma unroll
+                for (int m = 0; m < 6; ++m) cm[m][i] = ld_raw8(reinterpret_cast<const T*>(p.mix[m]) + vi * 8);
+            }
+        }
+        RowStats<T> rs;
+        if (!tp_rows_sum<T, NV>(t, call, row, D, rs.x)) break;
         row_stats<T, NV>(rs, D, p.eps, red);
         T* prev = reinterpret_cast<T*>(p.prev) + (p.slots ? (size_t)__ldg(p.slots + row) : row) * D;
 #pragma unroll
@@ -580,10 +610,9 @@ __global__ void __launch_bounds__(kNMThreads) tp_attn_norm_mix6_kernel(const Mix
 
 // ffn_add_norm_mix with attn = sum over ranks of partial: res_out = res + attn (normalised from the fp32 sum).
 template <typename T, int NV>
-__global__ void __launch_bounds__(kNMThreads) tp_ffn_add_norm_mix_kernel(const FfnMixArgs p, const TpRowsArgs t) {
+__global__ void __launch_bounds__(kNMThreads, NV <= 2 ? 2 : 1) tp_ffn_add_norm_mix_kernel(const FfnMixArgs p, const TpRowsArgs t) {
     __shared__ float red[32];
     __shared__ uint32_t s_epoch;
-    const size_t row = blockIdx.x;
     const int D = p.D, nvec = D / 8;
     Raw8<T> cw[NV], cb[NV], cm[NV];
 #pragma unroll
@@ -597,8 +626,13 @@ __global__ void __launch_bounds__(kNMThreads) tp_ffn_add_norm_mix_kernel(const F
     }
     grid_dependency_wait();
     if (threadIdx.x == 0) grid_launch_dependents();
-    RowStats<T> rs;
-    if (tp_rows_exchange<T, NV>(t, row, D, rs.x, &s_epoch)) {
+    const uint32_t call = tp_rows_begin(t, &s_epoch);
+#pragma unroll 1
+    for (size_t row = blockIdx.x; row < (size_t)t.rows; row += gridDim.x) tp_rows_push<T, NV>(t, call, row, D);
+#pragma unroll 1
+    for (size_t row = blockIdx.x; row < (size_t)t.rows; row += gridDim.x) {
+        RowStats<T> rs;
+        if (!tp_rows_sum<T, NV>(t, call, row, D, rs.x)) break;
         const T* res = reinterpret_cast<const T*>(p.res) + row * D;
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
@@ -634,15 +668,20 @@ __global__ void __launch_bounds__(kNMThreads) tp_ffn_add_norm_mix_kernel(const F
     tp_rows_finish(t, &s_epoch);
 }
 
-// Largest row count whose CTAs are all resident at once on this device (0 on error): the admission bound of the
-// tensor-parallel forms.
-template <typename K>
-static int resident_rows(K kernel) {
+// How many CTAs of a row kernel are resident at once on this device (0 on error): the largest grid of the
+// tensor-parallel forms, whose CTAs wait for the peers' CTAs of the same index.
+template <auto kernel>  // (a template VALUE: every kernel has its own cache; all of them share one pointer type)
+static int resident_ctas() {
+    static std::atomic<int> cached{0};
+    int n = cached.load(std::memory_order_relaxed);
+    if (n > 0) return n;
     int dev = 0, sms = 0, per_sm = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kNMThreads, 0) != cudaSuccess) return 0;
-    return sms * per_sm;
+    n = sms * per_sm;
+    cached.store(n, std::memory_order_relaxed);
+    return n;
 }
 
 static int fill_tp_args(const char* what, TpRowsArgs& t, const void* partial, void* const* inbox_ptrs, void* counters,
@@ -663,6 +702,7 @@ static int fill_tp_args(const char* what, TpRowsArgs& t, const void* partial, vo
     RWKV7_REQUIRE(t.error != nullptr, RWKV7_ERR_CUDA, "%s: cannot resolve the device error word", what);
     t.rank = rank;
     t.world = world;
+    t.rows = rows;
     t.slot_elems = slot_elems;
     t.wait_ns = (unsigned long long)(wait_ms > 0 ? wait_ms : 2000) * 1000000ull;
     return RWKV7_OK;
@@ -675,13 +715,23 @@ using namespace rwkv7;
 // vectors per thread for a row of D values: rows of <= 4096 values keep half the registers, so two CTAs share an SM
 static int tp_vectors(int D) { return D <= 8 * kNMThreads ? 1 : (D <= 16 * kNMThreads ? 2 : 4); }
 
+// Every CTA pushes all of its rows before it waits for any, and CTA c of one rank waits for CTA c of the others only:
+// with the whole grid resident (on every rank alike: same kernel, same device type) nobody waits for a CTA that
+// cannot start.  max_ctas > 0 lowers the bound (two such kernels side by side on two streams share the SMs).
+static int tp_grid(const char* what, int rows, int resident, int max_ctas, int* grid) {
+    RWKV7_REQUIRE(resident > 0, RWKV7_ERR_CUDA, "%s: cannot determine how many CTAs are resident", what);
+    int g = max_ctas > 0 && max_ctas < resident ? max_ctas : resident;
+    *grid = rows < g ? rows : g;
+    return RWKV7_OK;
+}
+
 template <typename T>
-static int tp_mix6_launch(int nv, int rows, cudaStream_t st, const Mix6Args& p, const TpRowsArgs& t, void* x_out) {
+static int tp_mix6_launch(int nv, int rows, int max_ctas, cudaStream_t st, const Mix6Args& p, const TpRowsArgs& t, void* x_out) {
+    int grid = 0;
 #define RWKV7_TP_MIX6(NV)                                                                                         \
     {                                                                                                             \
-        RWKV7_REQUIRE(rows <= resident_rows(tp_attn_norm_mix6_kernel<T, NV>), RWKV7_ERR_UNSUPPORTED,              \
-                      "tp_attn_norm_mix6: %d rows are more than are resident at once", rows);                     \
-        launch_programmatic(tp_attn_norm_mix6_kernel<T, NV>, dim3(rows), dim3(kNMThreads), 0, st, p, t, x_out);   \
+        if (int e = tp_grid("tp_attn_norm_mix6", rows, resident_ctas<tp_attn_norm_mix6_kernel<T, NV>>(), max_ctas, &grid)) return e; \
+        launch_programmatic(tp_attn_norm_mix6_kernel<T, NV>, dim3(grid), dim3(kNMThreads), 0, st, p, t, x_out);   \
     }
     if (nv == 1) RWKV7_TP_MIX6(1) else if (nv == 2) RWKV7_TP_MIX6(2) else RWKV7_TP_MIX6(4)
 #undef RWKV7_TP_MIX6
@@ -689,12 +739,12 @@ static int tp_mix6_launch(int nv, int rows, cudaStream_t st, const Mix6Args& p, 
 }
 
 template <typename T>
-static int tp_ffn_launch(int nv, int rows, cudaStream_t st, const FfnMixArgs& p, const TpRowsArgs& t) {
+static int tp_ffn_launch(int nv, int rows, int max_ctas, cudaStream_t st, const FfnMixArgs& p, const TpRowsArgs& t) {
+    int grid = 0;
 #define RWKV7_TP_FFN(NV)                                                                                          \
     {                                                                                                             \
-        RWKV7_REQUIRE(rows <= resident_rows(tp_ffn_add_norm_mix_kernel<T, NV>), RWKV7_ERR_UNSUPPORTED,            \
-                      "tp_ffn_add_norm_mix: %d rows are more than are resident at once", rows);                   \
-        launch_programmatic(tp_ffn_add_norm_mix_kernel<T, NV>, dim3(rows), dim3(kNMThreads), 0, st, p, t);        \
+        if (int e = tp_grid("tp_ffn_add_norm_mix", rows, resident_ctas<tp_ffn_add_norm_mix_kernel<T, NV>>(), max_ctas, &grid)) return e; \
+        launch_programmatic(tp_ffn_add_norm_mix_kernel<T, NV>, dim3(grid), dim3(kNMThreads), 0, st, p, t);        \
     }
     if (nv == 1) RWKV7_TP_FFN(1) else if (nv == 2) RWKV7_TP_FFN(2) else RWKV7_TP_FFN(4)
 #undef RWKV7_TP_FFN
@@ -706,11 +756,11 @@ extern "C" int rwkv7_tp_rows_resident(int D, int dtype) {
     const int nv = tp_vectors(D);
     int a = 0, b = 0;
     if (dtype == RWKV7_F16) {
-        a = nv == 1 ? resident_rows(tp_attn_norm_mix6_kernel<__half, 1>) : nv == 2 ? resident_rows(tp_attn_norm_mix6_kernel<__half, 2>) : resident_rows(tp_attn_norm_mix6_kernel<__half, 4>);
-        b = nv == 1 ? resident_rows(tp_ffn_add_norm_mix_kernel<__half, 1>) : nv == 2 ? resident_rows(tp_ffn_add_norm_mix_kernel<__half, 2>) : resident_rows(tp_ffn_add_norm_mix_kernel<__half, 4>);
+        a = nv == 1 ? resident_ctas<tp_attn_norm_mix6_kernel<__half, 1>>() : nv == 2 ? resident_ctas<tp_attn_norm_mix6_kernel<__half, 2>>() : resident_ctas<tp_attn_norm_mix6_kernel<__half, 4>>();
+        b = nv == 1 ? resident_ctas<tp_ffn_add_norm_mix_kernel<__half, 1>>() : nv == 2 ? resident_ctas<tp_ffn_add_norm_mix_kernel<__half, 2>>() : resident_ctas<tp_ffn_add_norm_mix_kernel<__half, 4>>();
     } else if (dtype == RWKV7_BF16) {
-        a = nv == 1 ? resident_rows(tp_attn_norm_mix6_kernel<__nv_bfloat16, 1>) : nv == 2 ? resident_rows(tp_attn_norm_mix6_kernel<__nv_bfloat16, 2>) : resident_rows(tp_attn_norm_mix6_kernel<__nv_bfloat16, 4>);
-        b = nv == 1 ? resident_rows(tp_ffn_add_norm_mix_kernel<__nv_bfloat16, 1>) : nv == 2 ? resident_rows(tp_ffn_add_norm_mix_kernel<__nv_bfloat16, 2>) : resident_rows(tp_ffn_add_norm_mix_kernel<__nv_bfloat16, 4>);
+        a = nv == 1 ? resident_ctas<tp_attn_norm_mix6_kernel<__nv_bfloat16, 1>>() : nv == 2 ? resident_ctas<tp_attn_norm_mix6_kernel<__nv_bfloat16, 2>>() : resident_ctas<tp_attn_norm_mix6_kernel<__nv_bfloat16, 4>>();
+        b = nv == 1 ? resident_ctas<tp_ffn_add_norm_mix_kernel<__nv_bfloat16, 1>>() : nv == 2 ? resident_ctas<tp_ffn_add_norm_mix_kernel<__nv_bfloat16, 2>>() : resident_ctas<tp_ffn_add_norm_mix_kernel<__nv_bfloat16, 4>>();
     }
     return a < b ? a : b;
 }
@@ -718,8 +768,8 @@ extern "C" int rwkv7_tp_rows_resident(int D, int dtype) {
 extern "C" int rwkv7_tp_attn_norm_mix6(const void* partial, void* x_out, void* prev, const int32_t* slot_ids,
                                        const void* norm_w, const void* norm_b, const void* const mixes[6],
                                        void* const outs[6], void* const* inbox_ptrs, void* counters, int rank, int world,
-                                       int rows, int D, long long slot_elems, float eps, int wait_ms, int dtype,
-                                       void* stream) {
+                                       int rows, int D, long long slot_elems, int max_ctas, float eps, int wait_ms,
+                                       int dtype, void* stream) {
     if (int e = check_row_shape("tp_attn_norm_mix6", rows, D)) return e;
     RWKV7_REQUIRE(dtype == RWKV7_F16 || dtype == RWKV7_BF16, RWKV7_ERR_UNSUPPORTED, "tp_attn_norm_mix6: fp16 or bf16");
     RWKV7_REQUIRE(x_out && prev && norm_w && norm_b && mixes && outs, RWKV7_ERR_INVALID, "tp_attn_norm_mix6: null pointer");
@@ -736,14 +786,15 @@ extern "C" int rwkv7_tp_attn_norm_mix6(const void* partial, void* x_out, void* p
     if (int e = fill_tp_args("tp_attn_norm_mix6", t, partial, inbox_ptrs, counters, rank, world, rows, D, slot_elems, wait_ms))
         return e;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    return dtype == RWKV7_F16 ? tp_mix6_launch<__half>(tp_vectors(D), rows, st, p, t, x_out)
-                              : tp_mix6_launch<__nv_bfloat16>(tp_vectors(D), rows, st, p, t, x_out);
+    return dtype == RWKV7_F16 ? tp_mix6_launch<__half>(tp_vectors(D), rows, max_ctas, st, p, t, x_out)
+                              : tp_mix6_launch<__nv_bfloat16>(tp_vectors(D), rows, max_ctas, st, p, t, x_out);
 }
 
 extern "C" int rwkv7_tp_ffn_add_norm_mix(const void* residual, const void* partial, void* prev, const int32_t* slot_ids,
                                          const void* norm_w, const void* norm_b, const void* mix, void* residual_out,
                                          void* mixed, void* const* inbox_ptrs, void* counters, int rank, int world, int rows,
-                                         int D, long long slot_elems, float eps, int wait_ms, int dtype, void* stream) {
+                                         int D, long long slot_elems, int max_ctas, float eps, int wait_ms, int dtype,
+                                         void* stream) {
     if (int e = check_row_shape("tp_ffn_add_norm_mix", rows, D)) return e;
     RWKV7_REQUIRE(dtype == RWKV7_F16 || dtype == RWKV7_BF16, RWKV7_ERR_UNSUPPORTED, "tp_ffn_add_norm_mix: fp16 or bf16");
     RWKV7_REQUIRE(residual && prev && norm_w && norm_b && mix && residual_out && mixed, RWKV7_ERR_INVALID,
@@ -755,6 +806,6 @@ extern "C" int rwkv7_tp_ffn_add_norm_mix(const void* residual, const void* parti
     if (int e = fill_tp_args("tp_ffn_add_norm_mix", t, partial, inbox_ptrs, counters, rank, world, rows, D, slot_elems, wait_ms))
         return e;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    return dtype == RWKV7_F16 ? tp_ffn_launch<__half>(tp_vectors(D), rows, st, p, t)
-                              : tp_ffn_launch<__nv_bfloat16>(tp_vectors(D), rows, st, p, t);
+    return dtype == RWKV7_F16 ? tp_ffn_launch<__half>(tp_vectors(D), rows, max_ctas, st, p, t)
+                              : tp_ffn_launch<__nv_bfloat16>(tp_vectors(D), rows, max_ctas, st, p, t);
 }

@@ -193,8 +193,8 @@ class RWKV7ForCausalLM(nn.Module):
         that many rows run as two halves on two streams with their own communicators, so one half's all-reduces hide
         under the other half's kernels.  ``tp_comm``: "nccl" sums the partial outputs with the framework's all-reduce,
         "peer" with this library's one-kernel sum over peer-mapped memory (fp16, up to 1024 rows; larger calls use NCCL),
-        "peer_rows" moves the sums of a decode step into the LayerNorm / token-shift kernels that consume them (as many
-        rows as those kernels keep resident at once; otherwise as "peer")."""
+        "peer_rows" moves the sums of a decode step into the LayerNorm / token-shift kernels that consume them (fp16 / bf16,
+        up to 1024 rows; otherwise as "peer")."""
         super().__init__()
         if state_dtype not in (torch.float32, torch.float16):
             raise ValueError("state_dtype must be torch.float32 or torch.float16")
@@ -214,6 +214,7 @@ class RWKV7ForCausalLM(nn.Module):
             raise ValueError("tp_comm must be 'nccl', 'peer' or 'peer_rows'")
         self.tp_comm = tp_comm
         self._peer_rows = {}  # lane -> PeerRowSum (the sums taken inside the row kernels; same set-up rule)
+        self._retired = []    # communicators replaced by one of another width or dtype stay mapped until the model goes
         self._peer_ar = {}  # lane -> PeerAllReduce (created on first use: a collective set-up, outside graph capture)
         self.tp_overlap_rows = int(tp_overlap_rows) if self.tp_world > 1 else 0
         # the second half of an overlapped step needs a communicator of its own: two collectives of ONE communicator
@@ -261,30 +262,35 @@ class RWKV7ForCausalLM(nn.Module):
                 from .tp_comm import PeerAllReduce
                 if torch.cuda.is_current_stream_capturing():
                     raise RuntimeError("the peer all-reduce buffers must exist before graph capture (run one eager step first)")
-                ar = self._peer_ar[lane] = PeerAllReduce(self.tp_group, max(rows, 64), int(t.shape[-1]), t.device)
+                # sized for the largest call once: communicators are never re-created (and so never freed) while
+                # another rank may still hold kernels that address them
+                if ar is not None:
+                    self._retired.append(ar)
+                ar = self._peer_ar[lane] = PeerAllReduce(self.tp_group, self.PEER_MAX_ROWS, int(t.shape[-1]), t.device)
             return ar.all_reduce(t, out=t)
         torch.distributed.all_reduce(t, group=self._lane_group(lane))
         return t
 
     def _row_sum(self, partial, lane: int = 0):
         """The communicator whose row kernels sum ``partial [rows, D]`` over the ranks themselves, or None when the sum
-        has to run as its own all-reduce (another ``tp_comm``, or more rows than those kernels keep resident at once;
-        every rank decides alike because the answer depends on the shape alone)."""
+        has to run as its own all-reduce (another ``tp_comm``, an unsupported width or dtype, more than 1024 rows; every
+        rank decides alike because the answer depends on the shape alone)."""
         if self.tp_comm != "peer_rows" or self.tp_world == 1 or self.tp_group is False:
             return None
         from .tp_comm import PeerRowSum
         rows, width = int(partial.shape[0]), int(partial.shape[1])
-        limit = PeerRowSum.resident_rows(width, partial.dtype)
-        if self.tp_overlap_rows:
-            limit //= 2  # two half-batches run side by side: the row kernels of both must fit together
-        if not partial.is_contiguous() or rows > min(limit, self.PEER_MAX_ROWS):
+        if not partial.is_contiguous() or rows > self.PEER_MAX_ROWS or PeerRowSum.resident_rows(width, partial.dtype) <= 0:
             return None
         comm = self._peer_rows.get(lane)
         if comm is None or rows > comm.max_rows or comm.width != width or comm.dtype != partial.dtype:
             if torch.cuda.is_current_stream_capturing():
                 raise RuntimeError("the peer row-sum buffers must exist before graph capture (run one eager step first)")
-            comm = self._peer_rows[lane] = PeerRowSum(self.tp_group, min(max(rows, 64), limit), width, partial.device,
-                                                      partial.dtype)
+            # two half-batches run side by side: the grids of both lanes' row kernels must be resident together
+            ctas = PeerRowSum.resident_rows(width, partial.dtype) // 2 if self.tp_overlap_rows else 0
+            if comm is not None:
+                self._retired.append(comm)
+            comm = self._peer_rows[lane] = PeerRowSum(self.tp_group, self.PEER_MAX_ROWS, width, partial.device, partial.dtype,
+                                                      max_ctas=ctas)
         return comm
 
     def _lane_group(self, lane: int):

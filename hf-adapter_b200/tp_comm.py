@@ -60,22 +60,26 @@ class PeerRowSum:
 
     @staticmethod
     def resident_rows(width: int, dtype) -> int:
-        """Largest row count the row kernels admit on the current device (0: unsupported width or dtype)."""
+        """CTAs (one row at a time each) of the row kernels that are resident at once on the current device: their
+        largest grid (0: unsupported width or dtype)."""
         if dtype not in (torch.float16, torch.bfloat16):
             return 0
         return int(_lib.lib.rwkv7_tp_rows_resident(int(width), _lib.F16 if dtype == torch.float16 else _lib.BF16))
 
-    def __init__(self, group, max_rows: int, width: int, device, dtype=torch.float16, wait_ms: int = 2000):
+    def __init__(self, group, max_rows: int, width: int, device, dtype=torch.float16, wait_ms: int = 2000,
+                 max_ctas: int = 0):
+        """``max_ctas`` > 0 bounds the grid of the row kernels below what is resident at once: instances whose kernels
+        run side by side on two streams pass ``resident_rows(...) // 2`` each."""
         import torch.distributed as dist
         import torch.distributed._symmetric_memory as symm_mem
         if dtype not in (torch.float16, torch.bfloat16):
             raise ValueError("PeerRowSum takes fp16 or bf16 rows")
+        self.max_ctas = int(max_ctas)
         self.group, self.rank, self.world = group, dist.get_rank(group), dist.get_world_size(group)
         self.width, self.wait_ms, self.dtype = int(width), int(wait_ms), dtype
         self.dtype_code = _lib.F16 if dtype == torch.float16 else _lib.BF16
-        # every row's CTA waits for the same row's CTA of the peers: all of them must be resident at once
-        self.max_rows = min(int(max_rows), int(_lib.lib.rwkv7_tp_rows_resident(self.width, self.dtype_code)))
-        if self.max_rows <= 0:
+        self.max_rows = int(max_rows)
+        if self.max_rows <= 0 or self.resident_rows(self.width, dtype) <= 0:
             raise ValueError(f"rows of {self.width} values are not supported by the tensor-parallel row kernels")
         self.slot_elems = (self.max_rows * self.width + 7) // 8 * 8
         self.buf = symm_mem.empty(2 * self.world * self.slot_elems * 4, dtype=torch.uint8, device=device)
@@ -111,7 +115,7 @@ class PeerRowSum:
         _lib.check(_lib.lib.rwkv7_tp_ffn_add_norm_mix(
             ptr(residual), ptr(partial), ptr(previous), ptr(slot_ids), ptr(norm_weight),
             ptr(norm_bias), ptr(mix), ptr(res_out), ptr(mixed), self._inbox, ptr(self.counters), self.rank,
-            self.world, rows, self.width, self.slot_elems, float(eps), self.wait_ms, self.dtype_code,
+            self.world, rows, self.width, self.slot_elems, self.max_ctas, float(eps), self.wait_ms, self.dtype_code,
             stream_ptr(partial)), "tp_ffn_add_norm_mix")
         return res_out, mixed
 
@@ -131,6 +135,6 @@ class PeerRowSum:
         _lib.check(_lib.lib.rwkv7_tp_attn_norm_mix6(
             ptr(partial), ptr(x), ptr(previous), ptr(slot_ids), ptr(norm_weight),
             ptr(norm_bias), mixes_p, outs_p, self._inbox, ptr(self.counters), self.rank, self.world, rows,
-            self.width, self.slot_elems, float(eps), self.wait_ms, self.dtype_code, stream_ptr(partial)),
+            self.width, self.slot_elems, self.max_ctas, float(eps), self.wait_ms, self.dtype_code, stream_ptr(partial)),
             "tp_attn_norm_mix6")
         return x, tuple(s[i] for i in range(6))

@@ -406,18 +406,20 @@ int rwkv7_tp_allreduce(const void* partial, void* out, void* const* inbox_ptrs, 
  *   2 * P * slot_elems * 4 bytes (two buffers, a slot per rank, 4 bytes per 2-byte payload value; zeroed, with a
  *   barrier, before the first call; not shared with rwkv7_tp_allreduce).  slot_elems: a multiple of 8, >= rows * D.
  *   counters: two u32 in local memory, zeroed at set-up.  slot_ids NULL or the state-pool rows of `prev`.
- *   rows must not exceed rwkv7_tp_rows_resident(D, dtype): every row's CTA waits for a peer's CTA of the same row, so
- *   all of them have to be resident at once (RWKV7_ERR_UNSUPPORTED otherwise - use rwkv7_tp_allreduce and the plain
- *   kernels).  fp16 or bf16.  The same-sequence and no-overlap rules above apply. */
+ *   The grid is min(rows, rwkv7_tp_rows_resident(D, dtype)) CTAs, CTA c taking rows c, c + grid, ...: a CTA pushes all
+ *   of its rows before it waits for any and waits only for the peers' CTAs of its own index, so with the whole grid
+ *   resident at once no CTA waits for one that cannot start.  max_ctas > 0 lowers the grid bound (callers that run two
+ *   of these kernels side by side on two streams pass half of rwkv7_tp_rows_resident); 0 = no extra bound.
+ *   fp16 or bf16.  The same-sequence and no-overlap rules above apply. */
 int rwkv7_tp_rows_resident(int D, int dtype);
 int rwkv7_tp_attn_norm_mix6(const void* partial, void* x_out, void* prev, const int32_t* slot_ids, const void* norm_w,
                             const void* norm_b, const void* const mixes[6], void* const outs[6], void* const* inbox_ptrs,
-                            void* counters, int rank, int world, int rows, int D, long long slot_elems, float eps,
-                            int wait_ms, int dtype, void* stream);
+                            void* counters, int rank, int world, int rows, int D, long long slot_elems, int max_ctas,
+                            float eps, int wait_ms, int dtype, void* stream);
 int rwkv7_tp_ffn_add_norm_mix(const void* residual, const void* partial, void* prev, const int32_t* slot_ids,
                               const void* norm_w, const void* norm_b, const void* mix, void* residual_out, void* mixed,
                               void* const* inbox_ptrs, void* counters, int rank, int world, int rows, int D,
-                              long long slot_elems, float eps, int wait_ms, int dtype, void* stream);
+                              long long slot_elems, int max_ctas, float eps, int wait_ms, int dtype, void* stream);
 
 #ifdef __cplusplus
 }

@@ -49,7 +49,8 @@ def _worker(rank, world, port, q, mode):
             dev = torch.device("cuda", rank)
             D = 512
             ar, rs = PeerAllReduce(dist.group.WORLD, 256, D, dev), PeerRowSum(dist.group.WORLD, 256, D, dev)
-            assert rs.max_rows >= 148
+            few = PeerRowSum(dist.group.WORLD, 256, D, dev, max_ctas=24)  # several rows per CTA
+            assert PeerRowSum.resident_rows(D, torch.float16) >= 148
             gen = torch.Generator(device="cuda").manual_seed(200 + rank)
             shared = torch.Generator(device="cuda").manual_seed(7)  # the same on every rank: replicated operands
             rnd = lambda *sh, g=shared: torch.randn(*sh, device="cuda", generator=g).half()
@@ -66,6 +67,9 @@ def _worker(rank, world, port, q, mode):
                 got_t, got6 = rs.attn_norm_mix6(part, p2, nw, nb, mixes)
                 assert torch.equal(got_t, total) and torch.equal(p1, p2)
                 assert all(torch.equal(a, b) for a, b in zip(got6, want6))
+                p2 = prev.clone()
+                got_t, got6 = few.attn_norm_mix6(part, p2, nw, nb, mixes)
+                assert torch.equal(got_t, total) and torch.equal(p1, p2) and all(torch.equal(a, b) for a, b in zip(got6, want6))
             # pool rows: the shift state of batch row b lives in row slots[b] of a larger pool
             slots = torch.tensor([5, 0, 9, 2], device="cuda", dtype=torch.int32)
             part, res, pool = rnd(4, D, g=gen), rnd(4, D), rnd(12, D)
@@ -158,7 +162,8 @@ def test_peer_sum_wait_runs_out_without_a_peer():
     assert torch.isfinite(y).all() and _lib.kernel_status(True) == 0  # the context still works
 
 
-def test_row_sum_kernels_with_a_prefilled_inbox():
+@pytest.mark.parametrize("rows,D", [(40, 1024), (128, 4096), (19, 8192)])
+def test_row_sum_kernels_with_a_prefilled_inbox(rows, D):
     """The row kernels that take the tensor-parallel sum in themselves, on ONE GPU and without a peer: this GPU plays
     rank 0 of two, the "peer" memory is local, and the test itself puts rank 1's partial rows for call 1 into rank 0's
     inbox before the launch (wire format: every 4-byte payload word followed by the call number).  The results must
@@ -167,7 +172,6 @@ def test_row_sum_kernels_with_a_prefilled_inbox():
     import ctypes
     import hf_adapter_b200 as hb
     from hf_adapter_b200 import _lib
-    rows, D = 40, 1024
     assert int(_lib.lib.rwkv7_tp_rows_resident(D, _lib.F16)) >= 148
     slot = rows * D  # payload values per slot = int32 words per slot on the wire
     g = torch.Generator(device="cuda").manual_seed(3)
@@ -192,7 +196,7 @@ def test_row_sum_kernels_with_a_prefilled_inbox():
     got_x, got_m = torch.full_like(res, -1.0), torch.full_like(res, -1.0)
     call = lambda: _lib.lib.rwkv7_tp_ffn_add_norm_mix(
         res.data_ptr(), mine.data_ptr(), p2.data_ptr(), None, nw.data_ptr(), nb.data_ptr(), mixes[0].data_ptr(),
-        got_x.data_ptr(), got_m.data_ptr(), arr(inbox), counters.data_ptr(), 0, 2, rows, D, slot, 1e-5, 30, _lib.F16, stream)
+        got_x.data_ptr(), got_m.data_ptr(), arr(inbox), counters.data_ptr(), 0, 2, rows, D, slot, 0, 1e-5, 30, _lib.F16, stream)
     assert call() == 0
     torch.cuda.synchronize()
     assert _lib.kernel_status(True) == 0 and int(counters[0]) == 1
@@ -214,15 +218,11 @@ def test_row_sum_kernels_with_a_prefilled_inbox():
     outs = torch.empty(6, rows, D, device="cuda", dtype=torch.float16)
     mp_, _k1 = _lib.ptr_array([m.data_ptr() for m in mixes])
     op_, _k2 = _lib.ptr_array([outs[i].data_ptr() for i in range(6)])
+    # 16 CTAs: a CTA pushes all of its rows, then sums them one after the other
     assert _lib.lib.rwkv7_tp_attn_norm_mix6(mine.data_ptr(), x_out.data_ptr(), p2.data_ptr(), None, nw.data_ptr(), nb.data_ptr(),
-                                            mp_, op_, arr(inbox), counters.data_ptr(), 0, 2, rows, D, slot, 1e-5, 30, _lib.F16,
-                                            stream) == 0
+                                            mp_, op_, arr(inbox), counters.data_ptr(), 0, 2, rows, D, slot, 16, 1e-5, 30,
+                                            _lib.F16, stream) == 0
     torch.cuda.synchronize()
     assert _lib.kernel_status(True) == 0
     assert torch.equal(x_out, total) and torch.equal(p1, p2)
     assert all(torch.equal(outs[i], want6[i]) for i in range(6))
-    # more rows than are resident at once are refused on the host
-    big = int(_lib.lib.rwkv7_tp_rows_resident(D, _lib.F16)) + 1
-    assert _lib.lib.rwkv7_tp_attn_norm_mix6(mine.data_ptr(), x_out.data_ptr(), p2.data_ptr(), None, nw.data_ptr(), nb.data_ptr(),
-                                            mp_, op_, arr(inbox), counters.data_ptr(), 0, 2, big, D, big * D, 1e-5, 30, _lib.F16,
-                                            stream) == _lib.ERR_UNSUPPORTED
