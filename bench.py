@@ -262,9 +262,10 @@ def main():
     args = ap.parse_args()
     steps, warmup = max(1, args.steps), max(3, args.warmup)
     if args.tp_comm == "auto":
-        # measured: the peer kernel's sums are shorter at 2 GPUs (17-18 us against 26-27 us), while from 4 GPUs up the
-        # (P - 1)-fold peer traffic per rank makes the step a little longer than with NCCL (6.05 against 5.93 ms at N = 4)
-        args.tp_comm = "peer" if int(os.environ.get("WORLD_SIZE", "1")) <= 2 else "nccl"
+        # measured: at 2 GPUs the sums taken inside the row kernels (one trip over the link, no extra launch) give
+        # 4.2 ms per step against 5.1 ms with the stand-alone peer kernel; from 4 GPUs up every rank would send its
+        # rows to P - 1 peers (6.6 ms at N = 4) and NCCL's in-switch reduction moves fewer bytes (5.9 ms)
+        args.tp_comm = "peer_rows" if int(os.environ.get("WORLD_SIZE", "1")) <= 2 else "nccl"
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     L, D, H, Fd, V = SHAPES[args.shape]

@@ -214,7 +214,6 @@ class RWKV7ForCausalLM(nn.Module):
             raise ValueError("tp_comm must be 'nccl', 'peer' or 'peer_rows'")
         self.tp_comm = tp_comm
         self._peer_rows = {}  # lane -> PeerRowSum (the sums taken inside the row kernels; same set-up rule)
-        self._retired = []    # communicators replaced by one of another width or dtype stay mapped until the model goes
         self._peer_ar = {}  # lane -> PeerAllReduce (created on first use: a collective set-up, outside graph capture)
         self.tp_overlap_rows = int(tp_overlap_rows) if self.tp_world > 1 else 0
         # the second half of an overlapped step needs a communicator of its own: two collectives of ONE communicator
@@ -259,14 +258,12 @@ class RWKV7ForCausalLM(nn.Module):
         if self.tp_comm in ("peer", "peer_rows") and t.dtype == torch.float16 and t.is_contiguous() and rows <= self.PEER_MAX_ROWS:
             ar = self._peer_ar.get(lane)
             if ar is None or rows * int(t.shape[-1]) > ar.slot_elems or ar.width != int(t.shape[-1]):
-                from .tp_comm import PeerAllReduce
+                from .tp_comm import shared_all_reduce
                 if torch.cuda.is_current_stream_capturing():
                     raise RuntimeError("the peer all-reduce buffers must exist before graph capture (run one eager step first)")
-                # sized for the largest call once: communicators are never re-created (and so never freed) while
-                # another rank may still hold kernels that address them
-                if ar is not None:
-                    self._retired.append(ar)
-                ar = self._peer_ar[lane] = PeerAllReduce(self.tp_group, self.PEER_MAX_ROWS, int(t.shape[-1]), t.device)
+                # sized for the largest call once and owned by the process, not by the model: a buffer that other
+                # ranks have mapped is never released while they run
+                ar = self._peer_ar[lane] = shared_all_reduce(self.tp_group, lane, self.PEER_MAX_ROWS, int(t.shape[-1]), t.device)
             return ar.all_reduce(t, out=t)
         torch.distributed.all_reduce(t, group=self._lane_group(lane))
         return t
@@ -283,14 +280,13 @@ class RWKV7ForCausalLM(nn.Module):
             return None
         comm = self._peer_rows.get(lane)
         if comm is None or rows > comm.max_rows or comm.width != width or comm.dtype != partial.dtype:
+            from .tp_comm import shared_row_sum
             if torch.cuda.is_current_stream_capturing():
                 raise RuntimeError("the peer row-sum buffers must exist before graph capture (run one eager step first)")
             # two half-batches run side by side: the grids of both lanes' row kernels must be resident together
             ctas = PeerRowSum.resident_rows(width, partial.dtype) // 2 if self.tp_overlap_rows else 0
-            if comm is not None:
-                self._retired.append(comm)
-            comm = self._peer_rows[lane] = PeerRowSum(self.tp_group, self.PEER_MAX_ROWS, width, partial.device, partial.dtype,
-                                                      max_ctas=ctas)
+            comm = self._peer_rows[lane] = shared_row_sum(self.tp_group, lane, self.PEER_MAX_ROWS, width, partial.device,
+                                                          partial.dtype, max_ctas=ctas)
         return comm
 
     def _lane_group(self, lane: int):
