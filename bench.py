@@ -384,7 +384,7 @@ def main():
             Bp = 8
             ref_model, _, _ = build_model(args.shape, 1, 0, None, dev, 2, args.quant, seed=7)
             tpm, _, _ = build_model(args.shape, world, rank, tp_group, dev, 2, args.quant, seed=7, full_then_shard=True,
-                                    overlap_rows=4, tp_comm=args.tp_comm)  # batch 8 -> two halves of 4: the overlapped path is checked
+                                    overlap_rows=args.tp_overlap_rows, tp_comm=args.tp_comm)
             gen = torch.Generator().manual_seed(11)
             pids = torch.randint(0, V, (Bp, 6), generator=gen).to(dev)
             c_ref, c_tp = ref_model.new_cache(Bp), tpm.new_cache(Bp)

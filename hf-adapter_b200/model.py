@@ -258,12 +258,12 @@ class RWKV7ForCausalLM(nn.Module):
         if self.tp_comm in ("peer", "peer_rows") and t.dtype == torch.float16 and t.is_contiguous() and rows <= self.PEER_MAX_ROWS:
             ar = self._peer_ar.get(lane)
             if ar is None or rows * int(t.shape[-1]) > ar.slot_elems or ar.width != int(t.shape[-1]):
-                from .tp_comm import shared_all_reduce
+                from .tp_comm import PeerAllReduce, keep_alive
                 if torch.cuda.is_current_stream_capturing():
                     raise RuntimeError("the peer all-reduce buffers must exist before graph capture (run one eager step first)")
-                # sized for the largest call once and owned by the process, not by the model: a buffer that other
-                # ranks have mapped is never released while they run
-                ar = self._peer_ar[lane] = shared_all_reduce(self.tp_group, lane, self.PEER_MAX_ROWS, int(t.shape[-1]), t.device)
+                # sized for the largest call once and kept by the process, not by the model: a buffer that other ranks
+                # have mapped is never released while they run
+                ar = self._peer_ar[lane] = keep_alive(PeerAllReduce(self.tp_group, self.PEER_MAX_ROWS, int(t.shape[-1]), t.device))
             return ar.all_reduce(t, out=t)
         torch.distributed.all_reduce(t, group=self._lane_group(lane))
         return t
@@ -274,19 +274,22 @@ class RWKV7ForCausalLM(nn.Module):
         rank decides alike because the answer depends on the shape alone)."""
         if self.tp_comm != "peer_rows" or self.tp_world == 1 or self.tp_group is False:
             return None
+        if self.tp_overlap_rows:
+            # Two half-batches side by side would run two of these kernels (and two library collectives at the end of
+            # the step) at the same time on every GPU; that combination once stalled on two GPUs and stays off: the
+            # halves sum with the stand-alone kernel.
+            return None
         from .tp_comm import PeerRowSum
         rows, width = int(partial.shape[0]), int(partial.shape[1])
         if not partial.is_contiguous() or rows > self.PEER_MAX_ROWS or PeerRowSum.resident_rows(width, partial.dtype) <= 0:
             return None
         comm = self._peer_rows.get(lane)
         if comm is None or rows > comm.max_rows or comm.width != width or comm.dtype != partial.dtype:
-            from .tp_comm import shared_row_sum
+            from .tp_comm import keep_alive
             if torch.cuda.is_current_stream_capturing():
                 raise RuntimeError("the peer row-sum buffers must exist before graph capture (run one eager step first)")
-            # two half-batches run side by side: the grids of both lanes' row kernels must be resident together
-            ctas = PeerRowSum.resident_rows(width, partial.dtype) // 2 if self.tp_overlap_rows else 0
-            comm = self._peer_rows[lane] = shared_row_sum(self.tp_group, lane, self.PEER_MAX_ROWS, width, partial.device,
-                                                          partial.dtype, max_ctas=ctas)
+            comm = self._peer_rows[lane] = keep_alive(PeerRowSum(self.tp_group, self.PEER_MAX_ROWS, width, partial.device,
+                                                                 partial.dtype))
         return comm
 
     def _lane_group(self, lane: int):

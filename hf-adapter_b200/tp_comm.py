@@ -143,27 +143,11 @@ class PeerRowSum:
 # Communicators live as long as the process.  Their buffers are mapped into every rank of the group; a rank that
 # released one while the others still held the mapping (a model deleted on one rank a moment before the others, a
 # communicator re-made for a larger batch in the middle of a step) was followed by launch failures on OTHER ranks on
-# NVSwitch machines.  So nothing is released before the process ends: models ask this registry, and a second model of
-# the same width on the same group and lane gets the communicator of the first.  (Two models that share one must not
-# run their steps at the same time on the GPU - the no-overlap rule of the classes above.)
-_REGISTRY = {}
+# NVSwitch machines.  So nothing is released before the process ends: whoever creates a communicator for a model hands
+# it to keep_alive(), and the ranks leave together (a barrier, then exit).
+_KEPT = []
 
 
-def shared_all_reduce(group, lane: int, max_rows: int, width: int, device):
-    key = ("sum", id(group), int(lane), int(width), str(device))
-    comm = _REGISTRY.get(key)
-    if comm is None or int(max_rows) * int(width) > comm.slot_elems:
-        if comm is not None:
-            _REGISTRY[key + (len(_REGISTRY),)] = comm  # (kept mapped)
-        comm = _REGISTRY[key] = PeerAllReduce(group, max_rows, width, device)
-    return comm
-
-
-def shared_row_sum(group, lane: int, max_rows: int, width: int, device, dtype, max_ctas: int = 0):
-    key = ("rows", id(group), int(lane), int(width), str(device), dtype, int(max_ctas))
-    comm = _REGISTRY.get(key)
-    if comm is None or int(max_rows) > comm.max_rows:
-        if comm is not None:
-            _REGISTRY[key + (len(_REGISTRY),)] = comm
-        comm = _REGISTRY[key] = PeerRowSum(group, max_rows, width, device, dtype, max_ctas=max_ctas)
+def keep_alive(comm):
+    _KEPT.append(comm)
     return comm

@@ -82,7 +82,7 @@ def _worker(rank, world, port, q, mode):
         comm = {"peer_sum": "peer", "peer_rows": "peer_rows"}.get(mode, "nccl")
         half = comm != "nccl"
         model = hb.RWKV7ForCausalLM(cfg, tp_world=world, tp_rank=rank, tp_group=dist.group.WORLD, tp_shard_head=fancy,
-                                    tp_overlap_rows=1 if fancy else 0, tp_comm=comm)
+                                    tp_overlap_rows=1 if fancy and mode != "peer_rows" else 0, tp_comm=comm)
         if half:
             model = model.half()
         model.load_state_dict({k: v.contiguous() for k, v in hb.shard_state_dict(full, world, rank, shard_head=fancy).items()})
