@@ -259,6 +259,10 @@ def main():
     ap.add_argument("--no-b256", action="store_true", help="skip the batch-256 decode measurement")
     ap.add_argument("--no-pool", action="store_true", help="skip the state-pool decode measurement")
     ap.add_argument("--no-side", action="store_true", help="N > 1: skip the side measurements (replicas, strong scaling)")
+    ap.add_argument("--stall-limit", type=int, default=480,
+                    help="N > 1: seconds after which a run that has not finished ends itself with exit code 5 (a rank "
+                         "waiting for a collective that never completes would otherwise sit until the library's own "
+                         "10-minute watchdog); 0 = no limit")
     args = ap.parse_args()
     steps, warmup = max(1, args.steps), max(3, args.warmup)
     if args.tp_comm == "auto":
@@ -268,6 +272,13 @@ def main():
         args.tp_comm = "peer_rows" if int(os.environ.get("WORLD_SIZE", "1")) <= 2 else "nccl"
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1 and args.stall_limit > 0 and args.impl == "ours":
+        def give_up():
+            print(f"[bench rank {rank}] not finished after {args.stall_limit} s: leaving with exit code 5", file=sys.stderr, flush=True)
+            os._exit(5)
+        stall_timer = threading.Timer(args.stall_limit, give_up)
+        stall_timer.daemon = True
+        stall_timer.start()
     L, D, H, Fd, V = SHAPES[args.shape]
     base_cfg = shape_config(args.shape, args.quant, args.batch, args.layers)
 
