@@ -309,6 +309,10 @@ def main():
     dev = torch.device("cuda", local)
     tp_group = None
     if world > 1:
+        if args.tp_overlap_rows:
+            # two half-batches = two library communicators with collectives in flight at the same time on every GPU;
+            # the library orders them by host program order (and so alike on all ranks) only when told to
+            os.environ.setdefault("NCCL_LAUNCH_ORDER_IMPLICIT", "1")
         dist.init_process_group("nccl", device_id=dev)
         tp_group = dist.group.WORLD
 

@@ -191,7 +191,10 @@ class RWKV7ForCausalLM(nn.Module):
         ``tp_shard_head``: every rank holds ``vocab/P`` rows of the head; full logits are all-gathered, greedy tokens
         come from a local arg-max and one tiny exchange.  ``tp_overlap_rows`` > 0: decode batches of at least twice
         that many rows run as two halves on two streams with their own communicators, so one half's all-reduces hide
-        under the other half's kernels.  ``tp_comm``: "nccl" sums the partial outputs with the framework's all-reduce,
+        under the other half's kernels (two library communicators are then in flight at once on every GPU: NCCL asks for
+        ``NCCL_LAUNCH_ORDER_IMPLICIT=1``, or equal GPU-side order on all ranks, for that to be free of deadlock; with
+        "peer_rows" the halves sum with the stand-alone kernel).
+        ``tp_comm``: "nccl" sums the partial outputs with the framework's all-reduce,
         "peer" with this library's one-kernel sum over peer-mapped memory (fp16, up to 1024 rows; larger calls use NCCL),
         "peer_rows" moves the sums of a decode step into the LayerNorm / token-shift kernels that consume them (fp16 / bf16,
         up to 1024 rows; otherwise as "peer")."""
