@@ -149,5 +149,8 @@ _KEPT = []
 
 
 def keep_alive(comm):
+    """Hold ``comm`` until the process ends.  The price: every tensor-parallel model made in a process adds its
+    communicators' buffers (2 * P * 1024 rows * width * 4 bytes for the row kernels, half of that for the stand-alone
+    sum) to what the process holds; a server makes one model per process."""
     _KEPT.append(comm)
     return comm
